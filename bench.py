@@ -1,0 +1,438 @@
+#!/usr/bin/env python3
+"""Benchmark of the quantized-matmul hot path on B200.
+
+Default workload (N = 1): the Qwen3.6-27B-shaped NVFP4 decode weight sweep:
+64 layers x 6 GEMVs (M = 1, bf16 activation, W4A16 semantics), 13.4 GB of
+packed weights + block scales resident in HBM, hidden state running from GEMV
+to GEMV.  One "step" = one pass over all 384 matrices through the C ABI
+(qwen36_nvfp4_matvec).  `value` = algorithmic bytes per step / device time.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Under torchrun (N > 1) every matrix is split by output rows across the ranks
+and each GEMV is followed by an NCCL all-gather of the bf16 slices.
+
+`--impl reference` times the reference's scalar semantics on the host cores
+(the CPU oracle, an OpenMP C restatement) on a bounded sample: one layer per
+step.  One JSON line is printed by rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "NVFP4 GEMV HBM GB/s & GEMM TFLOPS (% roofline) at Qwen3.6-27B shapes"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def gemv_bytes(n: int, k: int) -> int:
+    """Algorithmic bytes of one W4A16 GEMV: packed weights + block scales + x + y."""
+    return n * k // 2 + n * k // 16 + 2 * k + 2 * n
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            parts = [p.strip() for p in s.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------- ours
+
+def build_sweep(backend, torch, synth, rank: int, world: int, layers: int, seed: int):
+    """Per layer: [(name, n_local, k, weight, tiled scales, tensor scale)], rows split across ranks."""
+    gen = torch.Generator(device="cuda").manual_seed(seed)          # same seed on every rank: same model
+    sweep = []
+    for _ in range(layers):
+        mats = []
+        for name, n, k in synth.DECODE_SHAPES:
+            # full matrix generated identically on every rank, then sliced (keeps ranks consistent
+            # with the 1-GPU model); slices are multiples of 128 rows so scale tiles stay whole
+            packed, sf_rm = synth.nvfp4_weight_device(gen, n, k, "cuda")
+            lo, hi = shard_rows(n, rank, world)
+            packed, sf_rm = packed[lo:hi].contiguous(), sf_rm[lo:hi].contiguous()
+            sf = backend.nvfp4_retile_scales(sf_rm)
+            # per-tensor scale: 1/2688 times a gain that keeps the running hidden state at unit RMS
+            gain = 2688.0 / (2.926 * 4.80 * (k ** 0.5))
+            ts = torch.tensor([synth.WEIGHT_GLOBAL_SCALE * gain], dtype=torch.float32, device="cuda")
+            mats.append((name, hi - lo, k, packed, sf, ts, n))
+        sweep.append(mats)
+    torch.cuda.synchronize()
+    return sweep
+
+
+def shard_rows(n: int, rank: int, world: int):
+    blocks = n // 128
+    per = (blocks + world - 1) // world
+    lo = min(blocks, per * rank) * 128
+    hi = min(blocks, per * (rank + 1)) * 128
+    if rank == world - 1:
+        hi = n
+    return lo, hi
+
+
+class SweepRunner:
+    """Chains the six GEMVs of every layer: q_gate, k, v <- x ; o <- q_gate[:6144] ;
+    gate_up <- o ; down <- gate_up[:17408] ; next x <- down."""
+
+    def __init__(self, backend, torch, sweep, world: int, dist=None):
+        self.b, self.torch, self.sweep, self.world, self.dist = backend, torch, sweep, world, dist
+        dev = "cuda"
+        self.full = {name: torch.zeros(n, dtype=torch.bfloat16, device=dev) for name, n, _ in
+                     __import__("speedoza_b200.synth", fromlist=["x"]).DECODE_SHAPES}
+        self.local = {m[0]: torch.zeros(max(m[1], 1), dtype=torch.bfloat16, device=dev) for m in sweep[0]}
+        self.x = torch.zeros(5120, dtype=torch.bfloat16, device=dev)
+        self.launches = 0
+
+    def gemv(self, mat, x):
+        name, n_local, k, packed, sf, ts, n_full = mat
+        if self.world == 1:
+            out = self.full[name]
+            self.b.nvfp4_matvec(x, packed, sf, ts, out)
+        else:
+            out_local = self.local[name]
+            if n_local > 0:
+                self.b.nvfp4_matvec(x, packed, sf, ts, out_local)
+            out = self.full[name]
+            self.gather(out, out_local, n_full)
+        self.launches += 1
+        return out
+
+    def gather(self, out, out_local, n_full):
+        # equal 128-row-block shards except possibly the last: gather padded slices
+        per = ((n_full // 128 + self.world - 1) // self.world) * 128
+        if per * self.world == n_full:
+            self.dist.all_gather_into_tensor(out, out_local[:per])
+        else:
+            buf = self.torch.zeros(per * self.world, dtype=out.dtype, device=out.device)
+            src = self.torch.zeros(per, dtype=out.dtype, device=out.device)
+            src[:out_local.numel()] = out_local[:min(per, out_local.numel())]
+            self.dist.all_gather_into_tensor(buf, src)
+            out.copy_(buf[:n_full])
+
+    def step(self, x0):
+        x = x0
+        for mats in self.sweep:
+            qg = self.gemv(mats[0], x)
+            self.gemv(mats[1], x)
+            self.gemv(mats[2], x)
+            o = self.gemv(mats[3], qg[:6144])
+            gu = self.gemv(mats[4], o)
+            x = self.gemv(mats[5], gu[:17408])
+        return x
+
+    def capture(self):
+        """Records one step (all C-ABI launches, and the all-gathers when sharded) into a CUDA
+        graph, the way the reference engine replays its decode step; returns launches per step."""
+        torch = self.torch
+        self.x_static = torch.zeros(5120, dtype=torch.bfloat16, device="cuda")
+        self.graph = torch.cuda.CUDAGraph()
+        before = self.launches
+        with torch.cuda.graph(self.graph):
+            self.b.sync_stream()                  # library's ambient stream = the capturing stream
+            self.y_static = self.step(self.x_static)
+        self.b.sync_stream()
+        per_step = self.launches - before
+        self.launches = before
+        return per_step
+
+    def replay(self, x):
+        self.x_static.copy_(x, non_blocking=True)
+        self.graph.replay()
+        return self.y_static
+
+
+def per_shape_cold(backend, torch, sweep, synth):
+    """Each decode shape alone, rotating through the 64 layer copies so every launch reads cold
+    weights; 20 warm-up + 192 timed launches between CUDA events."""
+    out = {}
+    for idx, (name, n, k) in enumerate(synth.DECODE_SHAPES):
+        x = torch.randn(k, device="cuda").to(torch.bfloat16)
+        y = torch.empty(n, dtype=torch.bfloat16, device="cuda")
+        mats = [layer[idx] for layer in sweep]
+        for i in range(20):
+            m = mats[i % len(mats)]
+            backend.nvfp4_matvec(x, m[3], m[4], m[5], y)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 192
+        torch.cuda.synchronize()
+        e0.record()
+        for i in range(reps):
+            m = mats[i % len(mats)]
+            backend.nvfp4_matvec(x, m[3], m[4], m[5], y)
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / reps
+        out[name] = {"n": n, "k": k, "us": round(us, 3), "gbs": round(gemv_bytes(n, k) / us / 1e3, 1)}
+    return out
+
+
+def cpu_baseline(seconds: float = 10.0):
+    """Oracle W4A16 matvec on the host cores, 5120 x 5120 shape repeated for ~`seconds`."""
+    import numpy as np
+    from oracle import oracle as orc
+    from speedoza_b200 import synth
+    rng = np.random.default_rng(0)
+    n = k = 5120
+    packed, sf_rm = synth.nvfp4_weight(rng, n, k)
+    sf = orc.retile_scales(sf_rm)
+    x = synth.activations(rng, 1, k)[0]
+    orc.nvfp4_matvec(x, packed, sf, synth.WEIGHT_GLOBAL_SCALE, k)
+    t0 = time.perf_counter()
+    reps = 0
+    while time.perf_counter() - t0 < seconds:
+        orc.nvfp4_matvec(x, packed, sf, synth.WEIGHT_GLOBAL_SCALE, k)
+        reps += 1
+    dt = time.perf_counter() - t0
+    return {"value": round(gemv_bytes(n, k) * reps / dt / 1e9, 3), "unit": "GB/s", "cores": orc.num_threads(),
+            "kind": "port", "sample": f"{reps} x W4A16 GEMV 5120x5120 (config 0 shape), OpenMP oracle, {dt:.1f} s"}
+
+
+def run_ours(args):
+    import torch
+    from speedoza_b200 import synth
+    from speedoza_b200.backend import CudaBackend
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    backend = CudaBackend()
+    layers = args.layers
+    sweep = build_sweep(backend, torch, synth, rank, world, layers, seed=1234)
+    runner = SweepRunner(backend, torch, sweep, world, dist)
+    step_bytes = layers * sum(gemv_bytes(n, k) for _, n, k in synth.DECODE_SHAPES)
+    launches_per_step = layers * len(synth.DECODE_SHAPES)
+
+    gen = torch.Generator(device="cuda").manual_seed(99)
+    x_dev = torch.randn(5120, generator=gen, device="cuda").to(torch.bfloat16)
+    x_host = x_dev.cpu().pin_memory()
+    y_host = torch.empty(5120, dtype=torch.bfloat16).pin_memory()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing ------------------------------------------------
+    runner.step(x_dev)                       # eager once: lazy one-time setup happens outside capture
+    barrier()
+    use_graph = not args.no_graph
+    if use_graph:
+        per_step = runner.capture()
+        run_step = runner.replay
+    else:
+        per_step = launches_per_step
+        run_step = runner.step
+    for _ in range(args.warmup):
+        run_step(x_dev)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        y = run_step(x_dev)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    gpu_launches = per_step * args.steps
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- end to end: host buffers in, host result out, every step ---------------
+    barrier()
+    t0 = time.perf_counter()
+    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2.record()
+    for _ in range(args.steps):
+        y = run_step(x_host)                               # pinned host -> device inside the step
+        y_host.copy_(y, non_blocking=True)
+        torch.cuda.current_stream().synchronize()          # the caller reads the result
+    e3.record()
+    barrier()
+    ms_e2e = e2.elapsed_time(e3)
+    wall_e2e = (time.perf_counter() - t0) * 1e3
+
+    if world > 1:
+        t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, ms_e2e = float(t[0]), float(t[1])
+
+    extra = {}
+    if rank == 0 and world == 1 and not args.no_extras:
+        extra["per_shape_cold"] = per_shape_cold(backend, torch, sweep, synth)
+    if rank == 0:
+        peak, peak_kind = measured_peaks()
+        ms_per_step = ms / args.steps
+        value = step_bytes / (ms_per_step * 1e-3) / 1e9
+        e2e_value = step_bytes / (ms_e2e / args.steps * 1e-3) / 1e9
+        launch_us = ms_per_step * 1e3 / launches_per_step
+        achieved = (step_bytes / launches_per_step) / (launch_us * 1e-6) / 1e9
+        line = {
+            "metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
+            "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "e2m1 x bf16 -> f32",
+            "data": "synthetic",
+            "config": {"workload": f"config 1: NVFP4 W4A16 decode GEMV sweep, {layers} layers x 6 shapes, M=1",
+                       "launch": "CUDA graph replay of the C-ABI calls" if use_graph else "eager C-ABI calls",
+                       "bytes_per_step": step_bytes, "l2": "inputs larger than L2 (13.4 GB of weights per step)",
+                       "parallelism": "1 GPU" if world == 1 else f"output rows split {world}-way + NCCL all-gather per GEMV"},
+            "gpu_launches": gpu_launches,
+            "e2e": {"value": round(e2e_value, 1), "unit": "GB/s", "h2d_bytes_per_step": x_host.numel() * 2,
+                    "d2h_bytes_per_step": y_host.numel() * 2, "ms_per_step": round(ms_e2e / args.steps, 4),
+                    "wall_ms_per_step": round(wall_e2e / args.steps, 4)},
+            "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+                         "frac": round(achieved / peak, 4), "traffic": None, "peak_kind": peak_kind,
+                         "kernel": "nvfp4_matvec_kernel", "launch_us": round(launch_us, 3),
+                         "bytes_per_launch": step_bytes // launches_per_step,
+                         "frac_of_nominal_8TBs": round(achieved / 8000.0, 4)},
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu:
+            line["cpu_baseline"] = cpu_baseline(args.cpu_seconds)
+        line.update(extra)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# --------------------------------------------------------------------------- reference arm
+
+def run_reference(args):
+    """The reference's scalar W4A16 semantics on the host cores (OpenMP oracle).  One step = one
+    layer of the sweep (6 GEMVs, 209.6 MB of weights)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import numpy as np
+    from oracle import oracle as orc
+    from speedoza_b200 import synth
+    rng = np.random.default_rng(1234)
+    mats = []
+    for name, n, k in synth.DECODE_SHAPES:
+        packed, sf_rm = synth.nvfp4_weight(rng, n, k)
+        gain = 2688.0 / (2.926 * 4.80 * (k ** 0.5))
+        mats.append((n, k, packed, orc.retile_scales(sf_rm), synth.WEIGHT_GLOBAL_SCALE * gain))
+    x0 = synth.activations(rng, 1, 5120)[0]
+
+    def layer(x):
+        qg = orc.nvfp4_matvec(x, mats[0][2], mats[0][3], mats[0][4], 5120)
+        orc.nvfp4_matvec(x, mats[1][2], mats[1][3], mats[1][4], 5120)
+        orc.nvfp4_matvec(x, mats[2][2], mats[2][3], mats[2][4], 5120)
+        o = orc.nvfp4_matvec(np.ascontiguousarray(qg[:6144]), mats[3][2], mats[3][3], mats[3][4], 6144)
+        gu = orc.nvfp4_matvec(o, mats[4][2], mats[4][3], mats[4][4], 5120)
+        return orc.nvfp4_matvec(np.ascontiguousarray(gu[:17408]), mats[5][2], mats[5][3], mats[5][4], 17408)
+
+    x = x0
+    for _ in range(args.warmup):
+        x = layer(x)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        x = layer(x)
+    dt = time.perf_counter() - t0
+    layer_bytes = sum(gemv_bytes(n, k) for _, n, k in synth.DECODE_SHAPES)
+    value = layer_bytes * args.steps / dt / 1e9
+    cores = orc.num_threads()
+    line = {
+        "impl": "reference", "metric": METRIC, "value": round(value, 3), "unit": "GB/s",
+        "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(dt / args.steps * 1e3, 3), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "e2m1 x bf16 -> f32", "data": "synthetic",
+        "config": {"workload": "config 1: NVFP4 W4A16 decode GEMV sweep; bounded sample: one layer (6 GEMVs) per step",
+                   "bytes_per_step": layer_bytes},
+        "cpu_baseline": {"value": round(value, 3), "unit": "GB/s", "cores": cores, "kind": "port",
+                         "sample": "one layer of the sweep per step, OpenMP oracle (oracle/oracle.c)"},
+        "e2e": {"value": round(value, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=64)
+    ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        if args.warmup < 3:
+            args.warmup = max(args.warmup, 1)
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

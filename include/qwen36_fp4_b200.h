@@ -1,0 +1,372 @@
+/*
+ * C ABI of libqwen36_fp4_kernels.so, the sm_100a (B200) build of the
+ * quantized-matmul hot path.
+ *
+ * Every "replaces" note names the interface of the reference project that the
+ * entry point is binary-compatible with (paths relative to the reference
+ * root; the reference header is kernels-cuda/include/qwen36_fp4.h).  Struct
+ * field order and types are ABI: the Rust side binds them as #[repr(C)]
+ * mirrors (crates/kernels/src/backend.rs:600-1771).  New fields and new entry
+ * points are only ever appended.
+ *
+ * Conventions (same as the reference): every entry point returns an int
+ * status, validates its arguments on the host, launches on the process-wide
+ * ambient stream (qwen36_set_active_stream) and returns without
+ * synchronising.  Device pointers travel as 64-bit integers.  Nothing here
+ * allocates device memory except qwen36_cuda_malloc.
+ *
+ * Dimension names: the GEMM spec uses m = output features (weight rows),
+ * n = tokens, k = input features.  The output c_bf16 is column-major [m, n]
+ * with ld = m, i.e. row-major [tokens, features].
+ */
+#ifndef QWEN36_FP4_B200_H_
+#define QWEN36_FP4_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- handles and status -------------------------------------------------- */
+
+typedef struct { uint64_t ptr; } qwen36_device_ptr_t;            /* qwen36_fp4.h:10-12 */
+typedef struct { qwen36_device_ptr_t ptr; size_t bytes; } qwen36_device_allocation_t; /* :14-17 */
+
+enum {                                   /* qwen36_fp4.h:54-65 */
+  QWEN36_STATUS_SUCCESS = 0,
+  QWEN36_STATUS_NULL_POINTER = 1,
+  QWEN36_STATUS_INVALID_ARGUMENT = 2,
+  QWEN36_STATUS_CUDA_ERROR = 3,
+  QWEN36_STATUS_CUBLAS_ERROR = 4,        /* never produced by this build */
+  QWEN36_STATUS_NOT_IMPLEMENTED = 5      /* soft "use another path" signal */
+};
+
+typedef struct CUstream_st *qwen36_cuda_stream_t;
+typedef struct CUevent_st *qwen36_cuda_event_t;
+typedef struct CUgraph_st *qwen36_cuda_graph_t;
+typedef struct CUgraphExec_st *qwen36_cuda_graph_exec_t;
+
+typedef struct {                         /* qwen36_fp4.h:19-34 */
+  int driver_version, runtime_version, device_count, active_device;
+  int sm_major, sm_minor, multiprocessor_count;
+  size_t total_global_mem;
+  char device_name[128];
+  char libcuda_path[512];
+  char cudart_path[512];
+  int last_cuda_error;
+  char last_cuda_error_name[64];
+  char last_cuda_error_string[256];
+} qwen36_cuda_diagnostics_t;
+
+typedef struct {                         /* qwen36_fp4.h:36-52 */
+  uint64_t malloc_calls, free_calls, h2d_calls, h2d_bytes, d2h_calls, d2h_bytes;
+  uint64_t d2d_calls, d2d_bytes, d2d_async_calls, d2d_async_bytes;
+  uint64_t memset_calls, memset_bytes, synchronize_calls, stream_synchronize_calls;
+  uint64_t graph_launch_calls;
+} qwen36_cuda_counters_t;
+
+/* ---- NVFP4 linear layers -------------------------------------------------- */
+
+/* qwen36_fp4.h:67-81.  A = weights [m, k/2] packed E2M1 (low nibble = even
+ * column) with UE4M3 block scales in the 128x4 tiled layout (outer = feature);
+ * B = activations [n, k/2] with tiled scales (outer = token).  alpha carries
+ * both per-tensor scales; a_scale_2 / b_scale_2 are accepted and ignored.
+ * workspace is accepted and unused. */
+typedef struct {
+  size_t m, n, k;
+  qwen36_device_ptr_t a_fp4, a_scale, a_scale_2;
+  qwen36_device_ptr_t b_fp4, b_scale, b_scale_2;
+  qwen36_device_ptr_t c_bf16;
+  qwen36_device_ptr_t workspace;
+  size_t workspace_bytes;
+  float alpha;
+} qwen36_nvfp4_gemm_spec_t;
+
+/* qwen36_fp4.h:463-471.  W4A16: bf16 activation [in_features]. */
+typedef struct {
+  size_t out_features, in_features;
+  qwen36_device_ptr_t input_bf16, weight_u8, block_scale_e4m3, tensor_scale_f32, output_bf16;
+} qwen36_nvfp4_matvec_spec_t;
+
+/* qwen36_fp4.h:473-480 */
+typedef struct {
+  size_t values;
+  qwen36_device_ptr_t input_bf16, output_fp4, output_scale_e4m3, output_tensor_scale_f32;
+  float input_tensor_scale_f32;
+} qwen36_nvfp4_quantize_spec_t;
+
+/* qwen36_fp4.h:482-490 */
+typedef struct {
+  size_t rows, values;
+  qwen36_device_ptr_t input_bf16, output_fp4, output_scale_e4m3, output_tensor_scale_f32;
+  float input_tensor_scale_f32;
+} qwen36_nvfp4_quantize_rows_spec_t;
+
+/* qwen36_fp4.h:492-497 */
+typedef struct {
+  size_t rows, inner_groups;
+  qwen36_device_ptr_t input_row_major_u8, output_tiled_u8;
+} qwen36_nvfp4_retile_scales_spec_t;
+
+/* Replaces qwen36_nvfp4_gemm (kernels-cuda/nvfp4_gemm.cu:341-409, a cuBLASLt
+ * call).  Any m, n, k with k % 16 == 0.  alpha == 0 is read as 1.  Shapes with
+ * m % 128 == 0 and k % 256 == 0 run on tcgen05 block-scaled MMA (n <= 64: a
+ * weight-streaming split-K form; larger n: the tiled GEMM); anything else
+ * takes a generic SIMT kernel. */
+int qwen36_nvfp4_gemm(const qwen36_nvfp4_gemm_spec_t *spec);
+
+/* Replaces qwen36_decode_nvfp4_gemv
+ * (kernels-cuda/decode_gemv/nvfp4_gemv_sm120.cu:203-331).  n in [1, 8],
+ * m % 128 == 0, k % 256 == 0; other shapes return NOT_IMPLEMENTED, which the
+ * Rust dispatcher turns into a qwen36_nvfp4_gemm call
+ * (crates/kernels/src/backend.rs:225-229).  alpha is used as given. */
+int qwen36_decode_nvfp4_gemv(const qwen36_nvfp4_gemm_spec_t *spec);
+
+/* Replaces the test hook of the same name (nvfp4_gemv_sm120.cu:173-175);
+ * kept for linkage, has no effect. */
+void qwen36_nvfp4_chunk_gemv_set_mtile(int mtile);
+
+/* Replaces qwen36_nvfp4_matvec (kernels-cuda/ops.cu:547-639,1155-1180). */
+int qwen36_nvfp4_matvec(const qwen36_nvfp4_matvec_spec_t *spec);
+
+/* Replace qwen36_nvfp4_quantize_bf16 / _rows
+ * (kernels-cuda/ops.cu:641-761,1182-1227).  Codes, packing and scale bytes
+ * follow the reference bit for bit (E2M1 ties toward zero, UE4M3 ties down).
+ * Only scale bytes of real (row, group) pairs are written. */
+int qwen36_nvfp4_quantize_bf16(const qwen36_nvfp4_quantize_spec_t *spec);
+int qwen36_nvfp4_quantize_rows(const qwen36_nvfp4_quantize_rows_spec_t *spec);
+
+/* Replaces qwen36_nvfp4_retile_scales (kernels-cuda/ops.cu:763-774,1229-1255).
+ * Padding bytes are zeroed by the same kernel on the ambient stream (the
+ * reference issues a synchronous cudaMemset first). */
+int qwen36_nvfp4_retile_scales(const qwen36_nvfp4_retile_scales_spec_t *spec);
+
+/* ---- lm_head: FP8 weight, greedy argmax ----------------------------------- */
+
+#define QWEN36_LM_HEAD_FP8_MAX_N 16      /* qwen36_fp4.h:364 */
+
+typedef struct {                         /* qwen36_fp4.h:366-372 */
+  size_t rows, cols;
+  qwen36_device_ptr_t weight_bf16, weight_e4m3, row_scales_f32;
+} qwen36_lm_head_fp8_quantize_spec_t;
+
+typedef struct {                         /* qwen36_fp4.h:374-382 */
+  size_t rows, cols, n;
+  qwen36_device_ptr_t weight_e4m3, row_scales_f32, input_bf16, output_bf16;
+} qwen36_lm_head_fp8_gemv_spec_t;
+
+typedef struct {                         /* qwen36_fp4.h:314-323 */
+  size_t vocab_size;
+  qwen36_device_ptr_t logits_bf16, output_token_u32;
+  float temperature;
+  size_t top_k;
+  float top_p, repetition_penalty;
+  qwen36_device_ptr_t mirror_output_token_u32;
+} qwen36_sampling_spec_t;
+
+typedef struct {                         /* qwen36_fp4.h:334-341 */
+  size_t rows, vocab_size;
+  qwen36_device_ptr_t logits_bf16, output_token_u32, mirror_last_output_token_u32;
+  float temperature;
+} qwen36_sampling_rows_spec_t;
+
+/* Replace kernels-cuda/lm_head_fp8.cu:511-526 and :592-620.  The GEMV keeps
+ * the reference's float32 summation order, so its bf16 logits are identical. */
+int qwen36_lm_head_fp8_quantize(const qwen36_lm_head_fp8_quantize_spec_t *spec);
+int qwen36_lm_head_fp8_gemv(const qwen36_lm_head_fp8_gemv_spec_t *spec);
+
+/* Replace qwen36_sample / qwen36_sample_rows (kernels-cuda/ops.cu:299-427,
+ * 1523-1560): greedy argmax over bf16 logits, ties to the lowest index. */
+int qwen36_sample(const qwen36_sampling_spec_t *spec);
+int qwen36_sample_rows(const qwen36_sampling_rows_spec_t *spec);
+
+/* ---- int8 per-vector KV cache + decode attention --------------------------- */
+
+typedef struct { size_t q_heads, kv_heads, head_dim, rope_dims; } qwen36_attention_shape_t; /* :94-99 */
+
+typedef struct {                         /* qwen36_fp4.h:185-194 */
+  size_t layer_index, position;
+  qwen36_device_ptr_t k_bf16, v_bf16, k_quantized_i8, v_quantized_i8, metadata_f32;
+  qwen36_attention_shape_t shape;
+} qwen36_turboquant_encode_spec_t;
+
+typedef struct {                         /* qwen36_fp4.h:196-208 */
+  size_t layer_index, position;
+  qwen36_device_ptr_t q_bf16, k_quantized_i8, v_quantized_i8, metadata_f32, output_bf16;
+  qwen36_device_ptr_t workspace;
+  size_t workspace_bytes;
+  qwen36_attention_shape_t shape;
+  int mode;
+} qwen36_turboquant_attention_spec_t;
+
+/* Replaces qwen36_turboquant_encode_kv (kernels-cuda/turboquant.cu:23-67,
+ * 139-159): one position, K and V of every kv head. */
+int qwen36_turboquant_encode_kv(const qwen36_turboquant_encode_spec_t *spec);
+
+/* Replaces qwen36_turboquant_attention (kernels-cuda/turboquant.cu:69-135,
+ * 161-183).  Split-KV: needs qwen36_turboquant_attention_workspace_bytes()
+ * of caller scratch in `workspace` (the reference ignores the field); returns
+ * INVALID_ARGUMENT when it is missing or too small.  `mode` is ignored. */
+int qwen36_turboquant_attention(const qwen36_turboquant_attention_spec_t *spec);
+
+/* ---- additions of this build (no ABI change to anything above) ------------ */
+
+/* Scratch needed by qwen36_turboquant_attention / _partial for a shape. */
+size_t qwen36_turboquant_attention_workspace_bytes(size_t q_heads, size_t head_dim);
+
+/* Batched form of qwen36_turboquant_encode_kv: k, v bf16
+ * [tokens, kv_heads, head_dim] are written to cache rows
+ * [position, position + tokens).  Same arithmetic per (token, head). */
+typedef struct {
+  size_t position, tokens;
+  qwen36_device_ptr_t k_bf16, v_bf16, k_quantized_i8, v_quantized_i8, metadata_f32;
+  qwen36_attention_shape_t shape;
+} qwen36_turboquant_encode_rows_spec_t;
+int qwen36_turboquant_encode_kv_rows(const qwen36_turboquant_encode_rows_spec_t *spec);
+
+/* Attention over cache rows [t_begin, t_end) only, leaving one un-normalised
+ * partial per q head in the (m, l, o) form of the reference's split paths
+ * (kernels-cuda/attention.cu:1083-1094,1473-1554): partial_max_f32 [q_heads],
+ * partial_denom_f32 [q_heads], partial_acc_f32 [q_heads, head_dim].  An empty
+ * range yields (-inf, 0, 0).  Used to shard a long context across GPUs. */
+typedef struct {
+  size_t t_begin, t_end;
+  qwen36_device_ptr_t q_bf16, k_quantized_i8, v_quantized_i8, metadata_f32;
+  qwen36_device_ptr_t partial_acc_f32, partial_max_f32, partial_denom_f32;
+  qwen36_device_ptr_t workspace;
+  size_t workspace_bytes;
+  qwen36_attention_shape_t shape;
+} qwen36_turboquant_attention_partial_spec_t;
+int qwen36_turboquant_attention_partial(const qwen36_turboquant_attention_partial_spec_t *spec);
+
+/* Log-sum-exp merge of n_parts partials laid out [q_heads, n_parts(, head_dim)]
+ * into bf16 [q_heads, head_dim]; the arithmetic of
+ * kernels-cuda/attention.cu:1473-1554 with the zero-denominator guard of
+ * kernels-cuda/attention_flash_splitk.cu:419. */
+typedef struct {
+  size_t q_heads, head_dim, n_parts;
+  qwen36_device_ptr_t partial_acc_f32, partial_max_f32, partial_denom_f32, output_bf16;
+} qwen36_attention_merge_spec_t;
+int qwen36_attention_merge_partials(const qwen36_attention_merge_spec_t *spec);
+
+/* lm_head GEMV fused with the greedy argmax: no logits are written.  Each
+ * logit is rounded to bf16 exactly as qwen36_lm_head_fp8_gemv would store it
+ * before it is compared, so the winner equals qwen36_sample_rows over that
+ * GEMV's output.  row_offset is added to every index (vocab shards);
+ * best_value_f32 (optional) receives the winning bf16 logit as float per
+ * token, for the cross-shard combine.  workspace: at least
+ * qwen36_lm_head_fp8_argmax_workspace_bytes(rows, n) bytes, zero-filled once
+ * before first use (the kernel leaves it zeroed). */
+typedef struct {
+  size_t rows, cols, n;
+  qwen36_device_ptr_t weight_e4m3, row_scales_f32, input_bf16;
+  qwen36_device_ptr_t output_token_u32, best_value_f32;
+  qwen36_device_ptr_t workspace;
+  size_t workspace_bytes;
+  uint32_t row_offset;
+} qwen36_lm_head_fp8_argmax_spec_t;
+size_t qwen36_lm_head_fp8_argmax_workspace_bytes(size_t rows, size_t n);
+int qwen36_lm_head_fp8_gemv_argmax(const qwen36_lm_head_fp8_argmax_spec_t *spec);
+
+/* Dequantised NVFP4 weight as float32 [out_features, in_features]:
+ * lut(code) * (decode(scale) * tensor_scale), the value the reference matvec
+ * multiplies by (kernels-cuda/ops.cu:574-575,622-631).  For parity checks. */
+typedef struct {
+  size_t out_features, in_features;
+  qwen36_device_ptr_t weight_u8, block_scale_e4m3, tensor_scale_f32, output_f32;
+} qwen36_nvfp4_dequantize_spec_t;
+int qwen36_nvfp4_dequantize(const qwen36_nvfp4_dequantize_spec_t *spec);
+
+/* Host-side producer of the tiled scale layout, for loaders that want to
+ * upload block scales already tiled instead of staging them row-major and
+ * calling qwen36_nvfp4_retile_scales (crates/runtime/src/gpu.rs:1199-1239).
+ * `tiled` must hold qwen36_nvfp4_tiled_scale_bytes(rows, inner_groups) bytes;
+ * padding is zero-filled.  Pure CPU code, no CUDA call. */
+size_t qwen36_nvfp4_tiled_scale_bytes(size_t rows, size_t inner_groups);
+int qwen36_nvfp4_tile_scales_host(const uint8_t *row_major, uint8_t *tiled, size_t rows,
+                                  size_t inner_groups);
+
+/* ---- runtime plumbing (replaces kernels-cuda/runtime.cu) ------------------- */
+
+int qwen36_cuda_malloc(qwen36_device_allocation_t *out, size_t bytes);
+int qwen36_cuda_free(qwen36_device_ptr_t ptr);
+int qwen36_cuda_memcpy_h2d(qwen36_device_ptr_t dst, const void *src, size_t bytes);
+int qwen36_cuda_memcpy_d2h(void *dst, qwen36_device_ptr_t src, size_t bytes);
+int qwen36_cuda_memcpy_d2d(qwen36_device_ptr_t dst, qwen36_device_ptr_t src, size_t bytes);
+int qwen36_cuda_memcpy_d2d_async(qwen36_device_ptr_t dst, qwen36_device_ptr_t src, size_t bytes);
+int qwen36_cuda_memset(qwen36_device_ptr_t dst, int value, size_t bytes);
+int qwen36_cuda_memset_async(qwen36_device_ptr_t dst, int value, size_t bytes);
+int qwen36_cuda_synchronize(void);
+int qwen36_cuda_get_diagnostics(qwen36_cuda_diagnostics_t *out);
+int qwen36_cuda_counters_reset(void);
+int qwen36_cuda_counters_read(qwen36_cuda_counters_t *out);
+int qwen36_cuda_set_l2_access_window(qwen36_device_ptr_t base, size_t bytes, float hit_ratio);
+int qwen36_cuda_clear_l2_access_window(void);
+int qwen36_l2_prefetch(qwen36_device_ptr_t base, size_t bytes, int target_cta_count);
+qwen36_cuda_stream_t qwen36_get_active_stream(void);
+void qwen36_set_active_stream(qwen36_cuda_stream_t stream);
+qwen36_cuda_stream_t qwen36_get_prefetch_stream(void);
+void qwen36_set_prefetch_stream(qwen36_cuda_stream_t stream);
+qwen36_cuda_stream_t qwen36_internal_active_stream(void);
+qwen36_cuda_stream_t qwen36_internal_prefetch_stream(void);
+int qwen36_cuda_stream_create(qwen36_cuda_stream_t *out);
+int qwen36_cuda_stream_destroy(qwen36_cuda_stream_t stream);
+int qwen36_cuda_stream_synchronize(qwen36_cuda_stream_t stream);
+int qwen36_cuda_event_create(qwen36_cuda_event_t *out);
+int qwen36_cuda_event_destroy(qwen36_cuda_event_t event);
+int qwen36_cuda_event_record(qwen36_cuda_event_t event, qwen36_cuda_stream_t stream);
+int qwen36_cuda_stream_wait_event(qwen36_cuda_stream_t stream, qwen36_cuda_event_t event);
+int qwen36_cuda_stream_begin_capture(qwen36_cuda_stream_t stream);
+int qwen36_cuda_stream_end_capture(qwen36_cuda_stream_t stream, qwen36_cuda_graph_t *out);
+int qwen36_cuda_graph_instantiate(qwen36_cuda_graph_t graph, qwen36_cuda_graph_exec_t *out);
+int qwen36_cuda_graph_destroy(qwen36_cuda_graph_t graph);
+int qwen36_cuda_graph_exec_destroy(qwen36_cuda_graph_exec_t exec);
+int qwen36_cuda_graph_launch(qwen36_cuda_graph_exec_t exec, qwen36_cuda_stream_t stream);
+int qwen36_increment_i32(qwen36_device_ptr_t target_i32);
+int qwen36_mtp_assume_accept_chain_advance(qwen36_device_ptr_t position_i32, size_t draft_count,
+                                           size_t position_count, int32_t position_delta);
+
+/* ---- exported so crates/kernels links; not part of this path --------------- */
+/* Each returns QWEN36_STATUS_NOT_IMPLEMENTED.  The argument is the reference's
+ * spec struct for that operator (qwen36_fp4.h), which this build never reads. */
+int qwen36_bf16_gemm(const void *spec);
+int qwen36_bf16_matvec(const void *spec);
+int qwen36_bf16_matvec_argmax_rows(const void *spec);
+int qwen36_attention_prefill(const void *spec);
+int qwen36_attention_flash_prefill(const void *spec);
+int qwen36_attention_sage_prefill(const void *spec);
+int qwen36_attention_decode(const void *spec);
+int qwen36_attention_decode_split_tiled(const void *spec, int a, int b);
+int qwen36_attention_flash_splitk_prefill_bf16(const void *spec, int n_splits);
+int qwen36_deltanet_decode(const void *spec);
+int qwen36_deltanet_prefill(const void *spec);
+void qwen36_deltanet_set_resident(int mode);
+void qwen36_deltanet_prefill_set_tiny(int mode);
+int qwen36_interpreter_decode_sm120(const void *program);
+int qwen36_drafter_attention_block_bf16(const void *spec);
+int qwen36_drafter_attention_block_flash_bf16(const void *spec);
+int qwen36_rmsnorm(const void *spec);
+int qwen36_rmsnorm_nvfp4_quantize(const void *spec);
+int qwen36_partial_rope(const void *spec);
+int qwen36_swiglu(const void *spec);
+int qwen36_swiglu_nvfp4_quantize(const void *spec);
+int qwen36_topk_argmax(const void *spec);
+int qwen36_embedding_lookup(const void *spec);
+int qwen36_lm_head_top2_margin(const void *spec);
+int qwen36_lm_head_top8_rescore(const void *spec);
+int qwen36_conv1d_update(const void *spec);
+int qwen36_conv1d_prefill(const void *spec);
+int qwen36_gdn_gate(const void *spec);
+int qwen36_conv1d_gdn_gate_fused(const void *spec);
+int qwen36_sigmoid_gate(const void *spec);
+int qwen36_sigmoid_gate_strided(const void *spec);
+int qwen36_q_proj_deinterleave(const void *spec);
+int qwen36_q_proj_sigmoid_gate(const void *spec);
+int qwen36_copy_strided_rows(const void *spec);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QWEN36_FP4_B200_H_ */

@@ -1,0 +1,119 @@
+// Shared helpers of the sm_100a kernel library: status codes, pointer casts,
+// the ambient stream, and the NVFP4 / UE4M3 codecs whose rounding rules the
+// whole path depends on.  Citations name files of the reference project.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/qwen36_fp4_b200.h"
+
+namespace q36 {
+
+template <typename T>
+static inline T *as_ptr(qwen36_device_ptr_t p) {
+  return reinterpret_cast<T *>(static_cast<uintptr_t>(p.ptr));
+}
+
+static inline int cuda_status(cudaError_t e) {
+  return e == cudaSuccess ? QWEN36_STATUS_SUCCESS : QWEN36_STATUS_CUDA_ERROR;
+}
+
+// Status of the launch just issued (no synchronisation), as the reference's
+// entry points report it (e.g. kernels-cuda/ops.cu:1178-1179).
+static inline int launch_status() { return cuda_status(cudaGetLastError()); }
+
+// The stream every launch goes to (runtime.cu).
+static inline cudaStream_t stream() {
+  return reinterpret_cast<cudaStream_t>(qwen36_internal_active_stream());
+}
+
+__host__ __device__ static inline size_t div_ceil(size_t a, size_t b) { return (a + b - 1) / b; }
+__host__ __device__ static inline size_t round_up(size_t a, size_t b) { return div_ceil(a, b) * b; }
+
+// Tiled block-scale layout (kernels-cuda/ops.cu:64-79): 128 outer rows x 4
+// inner groups form one 512-byte tile; inside it row r sits at
+// (r % 32) * 16 + (r / 32) * 4 and the 4 groups are adjacent bytes.  Tiles of
+// one 128-row block are contiguous along the inner (K) direction.  This is
+// also the shared-memory image that a tcgen05.cp 32x128b.warpx4 copy turns
+// into the TMEM scale-factor operand of a block-scaled MMA.
+__host__ __device__ static inline size_t sf_offset(size_t inner, size_t outer, size_t sf_inner_dim) {
+  const size_t tile = (inner / 4) + (outer / 128) * (sf_inner_dim / 4);
+  const size_t r = outer % 128;
+  return tile * 512 + (r % 32) * 16 + (r / 32) * 4 + (inner % 4);
+}
+__host__ __device__ static inline size_t sf_bytes(size_t inner_groups, size_t outer) {
+  return div_ceil(outer, 128) * (round_up(inner_groups, 4) / 4) * 512;
+}
+
+// UE4M3 / E4M3 byte -> float, all 256 codes as the reference reads them
+// (kernels-cuda/ops.cu:39-54): sign honoured, 0x7F and 0xFF are 448.
+__host__ __device__ static inline float decode_e4m3(uint32_t code) {
+  const uint32_t e = (code >> 3) & 15u, m = code & 7u;
+  float v;
+  if (e == 0) {
+    v = static_cast<float>(m) * 0x1p-9f;
+  } else if (e == 15u && m == 7u) {
+    v = 448.0f;
+  } else {
+#ifdef __CUDA_ARCH__
+    v = __uint_as_float(((e + 120u) << 23) | (m << 20));
+#else
+    union { uint32_t u; float f; } cvt;
+    cvt.u = ((e + 120u) << 23) | (m << 20);
+    v = cvt.f;
+#endif
+  }
+  return (code & 0x80u) ? -v : v;
+}
+
+#ifdef __CUDACC__
+// Positive float -> UE4M3 byte (kernels-cuda/ops.cu:81-117): ties on the
+// normal grid round DOWN (+0x7FFFF before the shift), the subnormal grid uses
+// floorf(v / 2^-9 + 0.49999994f) in float32, 448 and above clamp to 0x7E.
+__device__ static inline uint32_t encode_ue4m3(float v) {
+  if (!(v > 0.0f)) return 0u;
+  if (v >= 448.0f) return 0x7eu;
+  if (v < 0x1p-6f) {
+    if (v >= (7.0f * 0x1p-9f + 0x1p-6f) * 0.5f) return 0x08u;
+    const int m = static_cast<int>(floorf(__fadd_rn(__fmul_rn(v, 512.0f), 0.49999994f)));
+    return m <= 0 ? 0u : static_cast<uint32_t>(m);
+  }
+  const uint32_t bits = __float_as_uint(v);
+  uint32_t e = ((bits >> 23) & 0xffu) - 120u;
+  uint32_t m = ((bits & 0x007fffffu) + 0x0007ffffu) >> 20;
+  if (m >= 8u) { m = 0u; ++e; }
+  if (e >= 15u) { e = 15u; if (m > 6u) m = 6u; }
+  return (e << 3) | m;
+}
+
+// float -> E2M1 nibble (kernels-cuda/ops.cu:119-139): `<=` thresholds, so
+// exact ties go toward zero; NaN lands on magnitude 7; -0.0 keeps sign clear.
+__device__ static inline uint32_t encode_e2m1(float v) {
+  const float a = fminf(fabsf(v), 6.0f);
+  uint32_t idx = 7u;
+  if (a <= 0.25f) idx = 0u;
+  else if (a <= 0.75f) idx = 1u;
+  else if (a <= 1.25f) idx = 2u;
+  else if (a <= 1.75f) idx = 3u;
+  else if (a <= 2.5f) idx = 4u;
+  else if (a <= 3.5f) idx = 5u;
+  else if (a <= 5.0f) idx = 6u;
+  return (v < 0.0f ? 8u : 0u) | idx;
+}
+
+// E2M1 nibble -> float (kernels-cuda/ops.cu:520-523) without a table:
+// magnitude code c = (e << 1) | m is 0.5 * m for e == 0, else 2^(e-1)*(1+m/2).
+__device__ static inline float e2m1_value(uint32_t code) {
+  const uint32_t c = code & 7u;
+  const uint32_t e = c >> 1, m = c & 1u;
+  const float mag = e == 0u ? 0.5f * static_cast<float>(m)
+                            : __uint_as_float(((e + 126u) << 23) | (m << 22));
+  return (code & 8u) ? -mag : mag;
+}
+
+__device__ static inline float bf16_bits_to_f32(uint32_t h) { return __uint_as_float(h << 16); }
+#endif  // __CUDACC__
+
+}  // namespace q36

@@ -1,0 +1,426 @@
+// int8 per-vector KV cache: encode, split-KV decode attention, (m, l, o) merge.
+//
+// Cache layout (kernels-cuda/turboquant.cu:23-67 in the reference): int8
+// [position, kv_heads, head_dim] for K and for V, float32 metadata
+// [position, kv_heads, 2] = (k_scale, v_scale), scale = absmax / 127, code =
+// clamp(round-to-nearest-even(v / scale), -127, 127), all-zero vector -> 0.
+//
+// Decode attention is HBM-bound on the cache read.  One CTA owns one kv head
+// and one contiguous token range ("split"); it serves every q head of that kv
+// head's group from the same K/V bytes, so the cache is read exactly once.  A
+// warp takes a token, the 32 lanes take head_dim/32 dims each (coalesced 256-
+// byte rows at head_dim 256), scores meet in a butterfly, the softmax is the
+// online (running max) form.  Every split leaves an un-normalised partial
+// (m, l, o) in caller scratch in the layout of the reference's split paths
+// (kernels-cuda/attention.cu:1083-1094); a second kernel merges them.
+#include "common.cuh"
+
+namespace {
+
+using q36::as_ptr;
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+constexpr int kMaxSplits = 128;
+constexpr int kMinTokensPerSplit = 64;
+
+// ------------------------------------------------------------------ encode
+
+__device__ __forceinline__ int quantize_s8(float v, float scale) {
+  const float scaled = scale == 0.0f ? 0.0f : __fdiv_rn(v, scale);
+  int r = __float2int_rn(scaled);          // round-to-nearest-even, as lrintf
+  r = r > 127 ? 127 : r;
+  return r < -127 ? -127 : r;
+}
+
+// One warp per (token, kv head, K|V) vector.
+__global__ void __launch_bounds__(kThreads)
+kv_encode_kernel(const __nv_bfloat16 *__restrict__ k, const __nv_bfloat16 *__restrict__ v,
+                 int8_t *__restrict__ kq, int8_t *__restrict__ vq, float *__restrict__ meta, size_t position,
+                 size_t tokens, size_t kv_heads, size_t head_dim) {
+  const size_t vec = static_cast<size_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
+  const unsigned lane = threadIdx.x & 31u;
+  if (vec >= tokens * kv_heads * 2) return;
+  const size_t which = vec & 1, th = vec >> 1;          // th = token * kv_heads + head
+  const __nv_bfloat16 *src = (which ? v : k) + th * head_dim;
+  const size_t row = position * kv_heads + th;
+  int8_t *dst = (which ? vq : kq) + row * head_dim;
+  const bool vec8 = head_dim % 8 == 0 && (reinterpret_cast<uintptr_t>(src) & 15u) == 0 &&
+                    (reinterpret_cast<uintptr_t>(dst) & 7u) == 0;
+  float amax = 0.f;
+  if (vec8) {
+    for (size_t d = lane * 8; d < head_dim; d += 256) {
+      const uint4 p = __ldcs(reinterpret_cast<const uint4 *>(src + d));
+      const uint32_t w[4] = {p.x, p.y, p.z, p.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        amax = fmaxf(amax, fmaxf(fabsf(__uint_as_float(w[i] << 16)), fabsf(__uint_as_float(w[i] & 0xffff0000u))));
+    }
+  } else {
+    for (size_t d = lane; d < head_dim; d += 32) amax = fmaxf(amax, fabsf(__bfloat162float(src[d])));
+  }
+  for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+  const float scale = __fdiv_rn(amax, 127.0f);
+  if (lane == 0) meta[row * 2 + which] = scale;
+  if (vec8) {
+    for (size_t d = lane * 8; d < head_dim; d += 256) {
+      const uint4 p = __ldg(reinterpret_cast<const uint4 *>(src + d));   // second touch: L1/L2 hit
+      const uint32_t w[4] = {p.x, p.y, p.z, p.w};
+      uint32_t lo = 0, hi = 0;
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        lo |= (quantize_s8(__uint_as_float(w[i] << 16), scale) & 0xff) << (16 * i);
+        lo |= (quantize_s8(__uint_as_float(w[i] & 0xffff0000u), scale) & 0xff) << (16 * i + 8);
+        hi |= (quantize_s8(__uint_as_float(w[2 + i] << 16), scale) & 0xff) << (16 * i);
+        hi |= (quantize_s8(__uint_as_float(w[2 + i] & 0xffff0000u), scale) & 0xff) << (16 * i + 8);
+      }
+      *reinterpret_cast<uint2 *>(dst + d) = make_uint2(lo, hi);
+    }
+  } else {
+    for (size_t d = lane; d < head_dim; d += 32)
+      dst[d] = static_cast<int8_t>(quantize_s8(__bfloat162float(src[d]), scale));
+  }
+}
+
+// --------------------------------------------------------------- attention
+
+// 4 signed bytes -> 4 floats without integer-to-float conversions: flip the
+// sign bit (value + 128 as unsigned), splice each byte under the exponent of
+// 2^23 with a byte permute, subtract 2^23 + 128.
+__device__ __forceinline__ void s8x4_to_f32(uint32_t w, float (&f)[4]) {
+  const uint32_t u = w ^ 0x80808080u;
+  f[0] = __uint_as_float(__byte_perm(u, 0x4b000000u, 0x7440)) - 8388736.0f;
+  f[1] = __uint_as_float(__byte_perm(u, 0x4b000000u, 0x7441)) - 8388736.0f;
+  f[2] = __uint_as_float(__byte_perm(u, 0x4b000000u, 0x7442)) - 8388736.0f;
+  f[3] = __uint_as_float(__byte_perm(u, 0x4b000000u, 0x7443)) - 8388736.0f;
+}
+
+// G = q heads per kv head handled together, DPL = dims per lane
+// (head_dim = 32 * DPL exactly when VEC, else head_dim <= 32 * DPL).
+// Grid (kv head groups, n_splits).  Partials: part_o [q_heads, n_splits, D],
+// part_m / part_l [q_heads, n_splits].
+template <int G, int DPL, bool VEC>
+__global__ void __launch_bounds__(kThreads)
+kv_attention_split_kernel(const __nv_bfloat16 *__restrict__ q, const int8_t *__restrict__ kq,
+                          const int8_t *__restrict__ vq, const float *__restrict__ meta,
+                          float *__restrict__ part_o, float *__restrict__ part_m, float *__restrict__ part_l,
+                          size_t t_begin, size_t t_end, uint32_t kv_heads, uint32_t q_per_kv,
+                          uint32_t head_dim, uint32_t n_splits) {
+  __shared__ float s_m[kWarps][G], s_l[kWarps][G];
+  __shared__ float s_o[G][32 * DPL];
+
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+  const uint32_t head0 = blockIdx.x * G;                 // first q head of this CTA
+  const uint32_t kvh = head0 / q_per_kv;
+  const uint32_t split = blockIdx.y;
+  const size_t total = t_end - t_begin;
+  const size_t per_split = q36::div_ceil(total, n_splits);
+  const size_t s_begin = t_begin + min(total, per_split * split);
+  const size_t s_end = t_begin + min(total, per_split * (split + 1));
+  const float sm_scale = rsqrtf(static_cast<float>(head_dim)) * 1.4426950408889634f;   // * log2(e)
+
+  float qv[G][DPL];
+#pragma unroll
+  for (int g = 0; g < G; ++g)
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) {
+      const uint32_t d = lane * DPL + i;
+      qv[g][i] = d < head_dim ? __bfloat162float(q[static_cast<size_t>(head0 + g) * head_dim + d]) : 0.f;
+    }
+
+  float m[G], l[G], o[G][DPL];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    m[g] = -INFINITY;
+    l[g] = 0.f;
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) o[g][i] = 0.f;
+  }
+
+  for (size_t t = s_begin + warp; t < s_end; t += kWarps) {
+    const size_t row = t * kv_heads + kvh;
+    const float2 sc = __ldg(reinterpret_cast<const float2 *>(meta) + row);
+    float kf[DPL], vf[DPL];
+    if constexpr (VEC && DPL == 8) {
+      const uint2 kw = __ldcs(reinterpret_cast<const uint2 *>(kq + row * head_dim) + lane);
+      const uint2 vw = __ldcs(reinterpret_cast<const uint2 *>(vq + row * head_dim) + lane);
+      float t4[4];
+      s8x4_to_f32(kw.x, t4); kf[0] = t4[0]; kf[1] = t4[1]; kf[2] = t4[2]; kf[3] = t4[3];
+      s8x4_to_f32(kw.y, t4); kf[4] = t4[0]; kf[5] = t4[1]; kf[6] = t4[2]; kf[7] = t4[3];
+      s8x4_to_f32(vw.x, t4); vf[0] = t4[0]; vf[1] = t4[1]; vf[2] = t4[2]; vf[3] = t4[3];
+      s8x4_to_f32(vw.y, t4); vf[4] = t4[0]; vf[5] = t4[1]; vf[6] = t4[2]; vf[7] = t4[3];
+    } else if constexpr (VEC && DPL == 4) {
+      float t4[4];
+      s8x4_to_f32(__ldcs(reinterpret_cast<const uint32_t *>(kq + row * head_dim) + lane), t4);
+      kf[0] = t4[0]; kf[1] = t4[1]; kf[2] = t4[2]; kf[3] = t4[3];
+      s8x4_to_f32(__ldcs(reinterpret_cast<const uint32_t *>(vq + row * head_dim) + lane), t4);
+      vf[0] = t4[0]; vf[1] = t4[1]; vf[2] = t4[2]; vf[3] = t4[3];
+    } else {
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) {
+        const uint32_t d = lane * DPL + i;
+        kf[i] = d < head_dim ? static_cast<float>(kq[row * head_dim + d]) : 0.f;
+        vf[i] = d < head_dim ? static_cast<float>(vq[row * head_dim + d]) : 0.f;
+      }
+    }
+    float s[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float a = 0.f;
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) a = fmaf(qv[g][i], kf[i], a);
+      s[g] = a;
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1)
+#pragma unroll
+      for (int g = 0; g < G; ++g) s[g] += __shfl_xor_sync(0xffffffffu, s[g], off);
+    const float kscale = sc.x * sm_scale;     // score in log2 units
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const float sg = s[g] * kscale;
+      if (sg > m[g]) {                         // warp-uniform: every lane holds the same score
+        const float corr = exp2f(m[g] - sg);   // 0 on the first token (m = -inf)
+        l[g] *= corr;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) o[g][i] *= corr;
+        m[g] = sg;
+      }
+      const float p = exp2f(sg - m[g]);
+      l[g] += p;
+      const float pv = p * sc.y;
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) o[g][i] = fmaf(pv, vf[i], o[g][i]);
+    }
+  }
+
+  // Merge the warps of the CTA: bring every warp to the common maximum, then
+  // add the warps' accumulators into shared memory one warp per round (a
+  // fixed order, so results do not depend on scheduling).
+  if (lane == 0) {
+#pragma unroll
+    for (int g = 0; g < G; ++g) { s_m[warp][g] = m[g]; s_l[warp][g] = l[g]; }
+  }
+  __syncthreads();
+  float wgt[G];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    float M = -INFINITY;
+    for (int w = 0; w < kWarps; ++w) M = fmaxf(M, s_m[w][g]);
+    wgt[g] = m[g] == -INFINITY ? 0.f : exp2f(m[g] - M);
+  }
+  for (int w = 0; w < kWarps; ++w) {
+    if (warp == w) {
+#pragma unroll
+      for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) {
+          float *dst = &s_o[g][lane * DPL + i];
+          *dst = w == 0 ? wgt[g] * o[g][i] : fmaf(wgt[g], o[g][i], *dst);
+        }
+    }
+    __syncthreads();
+  }
+  for (uint32_t idx = threadIdx.x; idx < G * head_dim; idx += kThreads) {
+    const uint32_t g = idx / head_dim, d = idx % head_dim;
+    const size_t slot = static_cast<size_t>(head0 + g) * n_splits + split;
+    part_o[slot * head_dim + d] = s_o[g][d];
+    if (d == 0) {
+      float M = -INFINITY, den = 0.f;
+      for (int w = 0; w < kWarps; ++w) M = fmaxf(M, s_m[w][g]);
+      for (int w = 0; w < kWarps; ++w)
+        den = fmaf(s_m[w][g] == -INFINITY ? 0.f : exp2f(s_m[w][g] - M), s_l[w][g], den);
+      part_m[slot] = M * 0.6931471805599453f;      // back to natural-log units
+      part_l[slot] = den;
+    }
+  }
+}
+
+// Merge n_parts partials per q head.  FINAL: write bf16 output (sum w*o /
+// sum w*l, 0 when the denominator is 0).  !FINAL: write one combined partial.
+template <bool FINAL>
+__global__ void __launch_bounds__(kThreads)
+kv_merge_kernel(const float *__restrict__ part_o, const float *__restrict__ part_m,
+                const float *__restrict__ part_l, uint32_t n_parts, uint32_t head_dim,
+                __nv_bfloat16 *__restrict__ out, float *__restrict__ out_o, float *__restrict__ out_m,
+                float *__restrict__ out_l) {
+  const size_t qh = blockIdx.x;
+  const float *pm = part_m + qh * n_parts, *pl = part_l + qh * n_parts;
+  const float *po = part_o + qh * n_parts * head_dim;
+  float M = -INFINITY;
+  for (uint32_t s = 0; s < n_parts; ++s) M = fmaxf(M, __ldcg(pm + s));
+  float den = 0.f;
+  for (uint32_t s = 0; s < n_parts; ++s) {
+    const float ms = __ldcg(pm + s);
+    den = fmaf(ms == -INFINITY ? 0.f : __expf(ms - M), __ldcg(pl + s), den);
+  }
+  for (uint32_t d = threadIdx.x; d < head_dim; d += kThreads) {
+    float acc = 0.f;
+    for (uint32_t s = 0; s < n_parts; ++s) {
+      const float ms = __ldcg(pm + s);
+      acc = fmaf(ms == -INFINITY ? 0.f : __expf(ms - M), __ldcg(po + static_cast<size_t>(s) * head_dim + d), acc);
+    }
+    if (FINAL) out[qh * head_dim + d] = __float2bfloat16(den > 0.f ? __fdiv_rn(acc, den) : 0.f);
+    else out_o[qh * head_dim + d] = acc;
+  }
+  if (!FINAL && threadIdx.x == 0) { out_m[qh] = M; out_l[qh] = den; }
+}
+
+struct Scratch { float *o, *m, *l; };
+
+size_t scratch_bytes(size_t q_heads, size_t head_dim) {
+  return q_heads * kMaxSplits * (head_dim + 2) * sizeof(float);
+}
+
+Scratch carve(qwen36_device_ptr_t ws, size_t q_heads, size_t head_dim) {
+  float *base = as_ptr<float>(ws);
+  return {base, base + q_heads * kMaxSplits * head_dim, base + q_heads * kMaxSplits * (head_dim + 1)};
+}
+
+uint32_t pick_splits(size_t tokens, size_t ctas_per_split) {
+  // fill ~2 CTAs per SM on a 148-SM part, at least kMinTokensPerSplit tokens each
+  size_t want = q36::div_ceil(296, ctas_per_split);
+  size_t cap = q36::div_ceil(tokens, kMinTokensPerSplit);
+  size_t n = want < cap ? want : cap;
+  if (n < 1) n = 1;
+  if (n > kMaxSplits) n = kMaxSplits;
+  return static_cast<uint32_t>(n);
+}
+
+template <int G>
+int launch_split_g(const __nv_bfloat16 *q, const int8_t *kq, const int8_t *vq, const float *meta, Scratch sc,
+                   size_t t_begin, size_t t_end, const qwen36_attention_shape_t &sh, uint32_t q_per_kv,
+                   uint32_t n_splits) {
+  const dim3 grid(static_cast<unsigned>(sh.q_heads / G), n_splits);
+  const uint32_t D = static_cast<uint32_t>(sh.head_dim), KV = static_cast<uint32_t>(sh.kv_heads);
+  const bool aligned = ((reinterpret_cast<uintptr_t>(kq) | reinterpret_cast<uintptr_t>(vq)) & 7u) == 0;
+#define Q36_GO(DPL, VEC)                                                                              \
+  kv_attention_split_kernel<G, DPL, VEC><<<grid, kThreads, 0, q36::stream()>>>(                        \
+      q, kq, vq, meta, sc.o, sc.m, sc.l, t_begin, t_end, KV, q_per_kv, D, n_splits)
+  if (D == 256 && aligned) Q36_GO(8, true);
+  else if (D == 128 && aligned) Q36_GO(4, true);
+  else if (D == 64) Q36_GO(2, true);
+  else if (D <= 64) Q36_GO(2, false);
+  else if (D <= 128) Q36_GO(4, false);
+  else Q36_GO(8, false);
+#undef Q36_GO
+  return q36::launch_status();
+}
+
+// Runs the split kernel over [t_begin, t_end) and returns the number of
+// splits used (0 on error, with *status set).
+uint32_t run_splits(qwen36_device_ptr_t q, qwen36_device_ptr_t kq, qwen36_device_ptr_t vq,
+                    qwen36_device_ptr_t meta, Scratch sc, size_t t_begin, size_t t_end,
+                    const qwen36_attention_shape_t &sh, int *status) {
+  const uint32_t q_per_kv = static_cast<uint32_t>(sh.q_heads / sh.kv_heads);
+  const int G = (q_per_kv == 1 || q_per_kv == 2 || q_per_kv == 4 || q_per_kv == 6 || q_per_kv == 8)
+                    ? static_cast<int>(q_per_kv) : 1;
+  const size_t tokens = t_end > t_begin ? t_end - t_begin : 0;
+  const uint32_t n_splits = pick_splits(tokens, sh.q_heads / G);
+  const __nv_bfloat16 *qp = as_ptr<const __nv_bfloat16>(q);
+  const int8_t *kp = as_ptr<const int8_t>(kq), *vp = as_ptr<const int8_t>(vq);
+  const float *mp = as_ptr<const float>(meta);
+  const size_t tb = t_begin, te = t_begin + tokens;
+  switch (G) {
+    case 2: *status = launch_split_g<2>(qp, kp, vp, mp, sc, tb, te, sh, q_per_kv, n_splits); break;
+    case 4: *status = launch_split_g<4>(qp, kp, vp, mp, sc, tb, te, sh, q_per_kv, n_splits); break;
+    case 6: *status = launch_split_g<6>(qp, kp, vp, mp, sc, tb, te, sh, q_per_kv, n_splits); break;
+    case 8: *status = launch_split_g<8>(qp, kp, vp, mp, sc, tb, te, sh, q_per_kv, n_splits); break;
+    default: *status = launch_split_g<1>(qp, kp, vp, mp, sc, tb, te, sh, q_per_kv, n_splits); break;
+  }
+  return *status == QWEN36_STATUS_SUCCESS ? n_splits : 0;
+}
+
+bool shape_ok(const qwen36_attention_shape_t &sh) {
+  return sh.q_heads != 0 && sh.kv_heads != 0 && sh.head_dim != 0 && sh.q_heads % sh.kv_heads == 0;
+}
+
+}  // namespace
+
+extern "C" int qwen36_turboquant_encode_kv_rows(const qwen36_turboquant_encode_rows_spec_t *spec) {
+  if (spec == nullptr) return QWEN36_STATUS_NULL_POINTER;
+  if (spec->k_bf16.ptr == 0 || spec->v_bf16.ptr == 0 || spec->k_quantized_i8.ptr == 0 ||
+      spec->v_quantized_i8.ptr == 0 || spec->metadata_f32.ptr == 0 || spec->shape.kv_heads == 0 ||
+      spec->shape.head_dim == 0)
+    return QWEN36_STATUS_INVALID_ARGUMENT;
+  if (spec->tokens == 0) return QWEN36_STATUS_SUCCESS;
+  const size_t vecs = spec->tokens * spec->shape.kv_heads * 2;
+  kv_encode_kernel<<<static_cast<unsigned>(q36::div_ceil(vecs, kWarps)), kThreads, 0, q36::stream()>>>(
+      as_ptr<const __nv_bfloat16>(spec->k_bf16), as_ptr<const __nv_bfloat16>(spec->v_bf16),
+      as_ptr<int8_t>(spec->k_quantized_i8), as_ptr<int8_t>(spec->v_quantized_i8),
+      as_ptr<float>(spec->metadata_f32), spec->position, spec->tokens, spec->shape.kv_heads,
+      spec->shape.head_dim);
+  return q36::launch_status();
+}
+
+extern "C" int qwen36_turboquant_encode_kv(const qwen36_turboquant_encode_spec_t *spec) {
+  if (spec == nullptr) return QWEN36_STATUS_NULL_POINTER;
+  qwen36_turboquant_encode_rows_spec_t rows{};
+  rows.position = spec->position;
+  rows.tokens = 1;
+  rows.k_bf16 = spec->k_bf16;
+  rows.v_bf16 = spec->v_bf16;
+  rows.k_quantized_i8 = spec->k_quantized_i8;
+  rows.v_quantized_i8 = spec->v_quantized_i8;
+  rows.metadata_f32 = spec->metadata_f32;
+  rows.shape = spec->shape;
+  return qwen36_turboquant_encode_kv_rows(&rows);
+}
+
+extern "C" size_t qwen36_turboquant_attention_workspace_bytes(size_t q_heads, size_t head_dim) {
+  return scratch_bytes(q_heads, head_dim);
+}
+
+extern "C" int qwen36_turboquant_attention(const qwen36_turboquant_attention_spec_t *spec) {
+  if (spec == nullptr) return QWEN36_STATUS_NULL_POINTER;
+  if (spec->q_bf16.ptr == 0 || spec->k_quantized_i8.ptr == 0 || spec->v_quantized_i8.ptr == 0 ||
+      spec->metadata_f32.ptr == 0 || spec->output_bf16.ptr == 0 || !shape_ok(spec->shape))
+    return QWEN36_STATUS_INVALID_ARGUMENT;
+  if (spec->shape.head_dim > 256) return QWEN36_STATUS_NOT_IMPLEMENTED;
+  if (spec->workspace.ptr == 0 || (spec->workspace.ptr & 15u) != 0 ||
+      spec->workspace_bytes < scratch_bytes(spec->shape.q_heads, spec->shape.head_dim))
+    return QWEN36_STATUS_INVALID_ARGUMENT;
+  const Scratch sc = carve(spec->workspace, spec->shape.q_heads, spec->shape.head_dim);
+  int status = QWEN36_STATUS_SUCCESS;
+  const uint32_t n = run_splits(spec->q_bf16, spec->k_quantized_i8, spec->v_quantized_i8, spec->metadata_f32,
+                                sc, 0, spec->position + 1, spec->shape, &status);
+  if (n == 0) return status;
+  kv_merge_kernel<true><<<static_cast<unsigned>(spec->shape.q_heads), kThreads, 0, q36::stream()>>>(
+      sc.o, sc.m, sc.l, n, static_cast<uint32_t>(spec->shape.head_dim), as_ptr<__nv_bfloat16>(spec->output_bf16),
+      nullptr, nullptr, nullptr);
+  return q36::launch_status();
+}
+
+extern "C" int qwen36_turboquant_attention_partial(const qwen36_turboquant_attention_partial_spec_t *spec) {
+  if (spec == nullptr) return QWEN36_STATUS_NULL_POINTER;
+  if (spec->q_bf16.ptr == 0 || spec->k_quantized_i8.ptr == 0 || spec->v_quantized_i8.ptr == 0 ||
+      spec->metadata_f32.ptr == 0 || spec->partial_acc_f32.ptr == 0 || spec->partial_max_f32.ptr == 0 ||
+      spec->partial_denom_f32.ptr == 0 || !shape_ok(spec->shape) || spec->t_end < spec->t_begin)
+    return QWEN36_STATUS_INVALID_ARGUMENT;
+  if (spec->shape.head_dim > 256) return QWEN36_STATUS_NOT_IMPLEMENTED;
+  if (spec->workspace.ptr == 0 || (spec->workspace.ptr & 15u) != 0 ||
+      spec->workspace_bytes < scratch_bytes(spec->shape.q_heads, spec->shape.head_dim))
+    return QWEN36_STATUS_INVALID_ARGUMENT;
+  const Scratch sc = carve(spec->workspace, spec->shape.q_heads, spec->shape.head_dim);
+  int status = QWEN36_STATUS_SUCCESS;
+  const uint32_t n = run_splits(spec->q_bf16, spec->k_quantized_i8, spec->v_quantized_i8, spec->metadata_f32,
+                                sc, spec->t_begin, spec->t_end, spec->shape, &status);
+  if (n == 0) return status;
+  kv_merge_kernel<false><<<static_cast<unsigned>(spec->shape.q_heads), kThreads, 0, q36::stream()>>>(
+      sc.o, sc.m, sc.l, n, static_cast<uint32_t>(spec->shape.head_dim), nullptr,
+      as_ptr<float>(spec->partial_acc_f32), as_ptr<float>(spec->partial_max_f32),
+      as_ptr<float>(spec->partial_denom_f32));
+  return q36::launch_status();
+}
+
+extern "C" int qwen36_attention_merge_partials(const qwen36_attention_merge_spec_t *spec) {
+  if (spec == nullptr) return QWEN36_STATUS_NULL_POINTER;
+  if (spec->q_heads == 0 || spec->head_dim == 0 || spec->n_parts == 0 || spec->partial_acc_f32.ptr == 0 ||
+      spec->partial_max_f32.ptr == 0 || spec->partial_denom_f32.ptr == 0 || spec->output_bf16.ptr == 0)
+    return QWEN36_STATUS_INVALID_ARGUMENT;
+  kv_merge_kernel<true><<<static_cast<unsigned>(spec->q_heads), kThreads, 0, q36::stream()>>>(
+      as_ptr<const float>(spec->partial_acc_f32), as_ptr<const float>(spec->partial_max_f32),
+      as_ptr<const float>(spec->partial_denom_f32), static_cast<uint32_t>(spec->n_parts),
+      static_cast<uint32_t>(spec->head_dim), as_ptr<__nv_bfloat16>(spec->output_bf16), nullptr, nullptr, nullptr);
+  return q36::launch_status();
+}

@@ -1,0 +1,447 @@
+// lm_head: FP8 E4M3 weight with one float scale per row.
+//   quantise (one-off), W8A16 GEMV for n <= 16 tokens, greedy argmax over bf16
+//   logits, and the GEMV fused with the argmax (no logits written).
+//
+// The GEMV is HBM-bound (1.27 GB of weight per call at vocab 248320).  Each
+// warp streams whole rows with 16-byte loads, 512 contiguous bytes per warp
+// instruction, R rows and two K-steps in flight.  It keeps the reference's
+// float32 summation order (kernels-cuda/lm_head_fp8.cu:122-194): lane l adds
+// the products of bytes 16*l + 512*j .. +15 in ascending order with fused
+// multiply-adds, the lanes meet in a 16,8,4,2,1 xor butterfly, then the row
+// scale is applied and the value rounded to bf16.  Every product is exact in
+// float32 (4-bit x 8-bit significands), so the logits are bit-identical to the
+// reference's and the greedy argmax picks the same token.
+#include "common.cuh"
+
+#include <cooperative_groups.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <mutex>
+
+namespace cg = cooperative_groups;
+
+namespace {
+
+using q36::as_ptr;
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+
+// ---------------------------------------------------------------- quantise
+
+// One CTA per row: amax, scale = amax/448 (1 for an all-zero row), then
+// saturating round-to-nearest-even cast of w * (1/scale)
+// (kernels-cuda/lm_head_fp8.cu:37-80).
+__global__ void __launch_bounds__(kThreads)
+lm_head_quantize_kernel(const __nv_bfloat16 *__restrict__ w, uint8_t *__restrict__ q,
+                        float *__restrict__ scales, size_t rows, size_t cols) {
+  __shared__ float warp_amax[kWarps];
+  __shared__ float s_scale;
+  const size_t row = blockIdx.x;
+  const __nv_bfloat16 *src = w + row * cols;
+  float amax = 0.f;
+  for (size_t c = threadIdx.x; c < cols; c += kThreads) amax = fmaxf(amax, fabsf(__bfloat162float(src[c])));
+  for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+  if ((threadIdx.x & 31) == 0) warp_amax[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float m = 0.f;
+    for (int i = 0; i < kWarps; ++i) m = fmaxf(m, warp_amax[i]);
+    s_scale = m > 0.f ? __fdiv_rn(m, 448.0f) : 1.0f;
+    scales[row] = s_scale;
+  }
+  __syncthreads();
+  const float inv = __fdiv_rn(1.0f, s_scale);
+  for (size_t c = threadIdx.x; c < cols; c += kThreads) {
+    const __nv_fp8_e4m3 v(__fmul_rn(__bfloat162float(src[c]), inv));
+    q[row * cols + c] = reinterpret_cast<const uint8_t &>(v);
+  }
+}
+
+// -------------------------------------------------------------------- GEMV
+
+__device__ __forceinline__ bool better(float cand, uint32_t cand_idx, float cur, uint32_t cur_idx) {
+  return cand > cur || (cand == cur && cand_idx < cur_idx);   // kernels-cuda/ops.cu:19-23
+}
+
+// two E4M3 bytes (low 16 bits of `pair`) -> two floats, exact
+__device__ __forceinline__ float2 e4m3x2_to_f32(uint32_t pair) {
+  uint32_t h2;
+  asm("{\n\t.reg .b16 p;\n\tcvt.u16.u32 p, %1;\n\tcvt.rn.f16x2.e4m3x2 %0, p;\n\t}" : "=r"(h2) : "r"(pair));
+  return __half22float2(*reinterpret_cast<__half2 *>(&h2));
+}
+
+template <int N> struct RowsPerWarp { static constexpr int value = N == 1 ? 4 : (N <= 4 ? 2 : 1); };
+
+// x lives in shared memory as bf16, 16-byte chunks, chunk c stored at
+// c ^ ((c >> 3) & 1) so that a quarter warp (chunks 2l+i, l = 0..7) hits eight
+// distinct bank groups.
+__device__ __forceinline__ uint32_t xswz(uint32_t chunk) { return chunk ^ ((chunk >> 3) & 1u); }
+
+// FUSED = false: writes y[t * rows + row] (bf16).
+// FUSED = true : keeps the running (value, index) of the bf16-rounded logits
+//   per token; per-CTA winners go to `partials`, the last CTA to finish (ticket
+//   counter) merges them, writes the tokens and re-zeroes the ticket.
+template <int N, bool FUSED>
+__global__ void __launch_bounds__(kThreads)
+lm_head_gemv_kernel(const uint8_t *__restrict__ weight, const float *__restrict__ row_scales,
+                    const __nv_bfloat16 *__restrict__ x, __nv_bfloat16 *__restrict__ y, size_t rows,
+                    uint32_t cols, uint32_t row_offset, uint32_t *__restrict__ out_tokens,
+                    float *__restrict__ out_best, float2 *__restrict__ partials,
+                    unsigned *__restrict__ ticket) {
+  constexpr int R = RowsPerWarp<N>::value;
+  extern __shared__ __align__(16) uint8_t smem[];
+  uint4 *xs = reinterpret_cast<uint4 *>(smem);        // N * cols bf16, swizzled chunks
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+  const uint32_t chunks_per_tok = cols / 8u;
+
+  for (uint32_t c = threadIdx.x; c < N * chunks_per_tok; c += kThreads)
+    xs[xswz(c)] = __ldcg(reinterpret_cast<const uint4 *>(x) + c);
+  __syncthreads();
+
+  float best[N];
+  uint32_t best_idx[N];
+#pragma unroll
+  for (int t = 0; t < N; ++t) { best[t] = -INFINITY; best_idx[t] = 0u; }
+
+  const size_t warps_total = static_cast<size_t>(gridDim.x) * kWarps;
+  const uint32_t steps = cols / 512u;            // full 512-byte K-steps; the reference loop
+                                                 // (kk + 15 < cols) also covers a ragged last
+                                                 // step for lanes whose 16 bytes still fit
+  const bool tail = lane * 16u + steps * 512u + 15u < cols;
+
+  for (size_t row0 = (static_cast<size_t>(blockIdx.x) * kWarps + warp) * R; row0 < rows;
+       row0 += warps_total * R) {
+    const int r_count = static_cast<int>(min(static_cast<size_t>(R), rows - row0));
+    float acc[R][N];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int t = 0; t < N; ++t) acc[r][t] = 0.f;
+
+    const uint8_t *w0 = weight + row0 * cols + lane * 16u;
+    uint4 cur[R], nxt[R];
+    auto load = [&](uint4 (&dst)[R], uint32_t step) {
+#pragma unroll
+      for (int r = 0; r < R; ++r)
+        dst[r] = r < r_count ? __ldcs(reinterpret_cast<const uint4 *>(w0 + static_cast<size_t>(r) * cols + step * 512u))
+                             : make_uint4(0, 0, 0, 0);
+    };
+    const uint32_t my_steps = steps + (tail ? 1u : 0u);
+    if (my_steps > 0) load(cur, 0);
+    for (uint32_t s = 0; s < my_steps; ++s) {
+      if (s + 1 < my_steps) load(nxt, s + 1);
+      const uint32_t chunk0 = (lane * 16u + s * 512u) / 8u;        // first of two x chunks
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        float wf[R][8];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          const uint32_t w_lo = half == 0 ? cur[r].x : cur[r].z;
+          const uint32_t w_hi = half == 0 ? cur[r].y : cur[r].w;
+          const float2 f0 = e4m3x2_to_f32(w_lo), f1 = e4m3x2_to_f32(w_lo >> 16);
+          const float2 f2 = e4m3x2_to_f32(w_hi), f3 = e4m3x2_to_f32(w_hi >> 16);
+          wf[r][0] = f0.x; wf[r][1] = f0.y; wf[r][2] = f1.x; wf[r][3] = f1.y;
+          wf[r][4] = f2.x; wf[r][5] = f2.y; wf[r][6] = f3.x; wf[r][7] = f3.y;
+        }
+#pragma unroll
+        for (int t = 0; t < N; ++t) {
+          const uint4 xc = xs[xswz(t * chunks_per_tok + chunk0 + half)];
+          const uint32_t xw[4] = {xc.x, xc.y, xc.z, xc.w};
+          float xv[8];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            xv[2 * i] = __uint_as_float(xw[i] << 16);
+            xv[2 * i + 1] = __uint_as_float(xw[i] & 0xffff0000u);
+          }
+#pragma unroll
+          for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[r][t] = fmaf(wf[r][i], xv[i], acc[r][t]);
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < R; ++r) cur[r] = nxt[r];
+    }
+
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      if (r >= r_count) break;
+      const float scale = __ldg(row_scales + row0 + r);
+#pragma unroll
+      for (int t = 0; t < N; ++t) {
+        float v = acc[r][t];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+        const __nv_bfloat16 logit = __float2bfloat16(__fmul_rn(v, scale));
+        if (!FUSED) {
+          if (lane == 0) y[static_cast<size_t>(t) * rows + row0 + r] = logit;
+        } else {
+          const float lv = __bfloat162float(logit);
+          const uint32_t idx = static_cast<uint32_t>(row0 + r) + row_offset;
+          if (better(lv, idx, best[t], best_idx[t])) { best[t] = lv; best_idx[t] = idx; }
+        }
+      }
+    }
+  }
+
+  if (FUSED) {
+    __shared__ float s_val[kWarps][N];
+    __shared__ uint32_t s_idx[kWarps][N];
+    __shared__ bool s_last;
+    if (lane == 0) {
+#pragma unroll
+      for (int t = 0; t < N; ++t) { s_val[warp][t] = best[t]; s_idx[warp][t] = best_idx[t]; }
+    }
+    __syncthreads();
+    if (threadIdx.x < N) {
+      float bv = s_val[0][threadIdx.x];
+      uint32_t bi = s_idx[0][threadIdx.x];
+      for (int w = 1; w < kWarps; ++w)
+        if (better(s_val[w][threadIdx.x], s_idx[w][threadIdx.x], bv, bi)) { bv = s_val[w][threadIdx.x]; bi = s_idx[w][threadIdx.x]; }
+      partials[static_cast<size_t>(blockIdx.x) * N + threadIdx.x] = make_float2(bv, __uint_as_float(bi));
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = atomicAdd(ticket, 1u) == gridDim.x - 1;
+    __syncthreads();
+    if (s_last) {
+      __threadfence();
+      if (threadIdx.x < N) {
+        float bv = -INFINITY;
+        uint32_t bi = 0u;
+        for (uint32_t b = 0; b < gridDim.x; ++b) {
+          const float2 p = __ldcg(partials + static_cast<size_t>(b) * N + threadIdx.x);
+          const uint32_t pi = __float_as_uint(p.y);
+          if (better(p.x, pi, bv, bi)) { bv = p.x; bi = pi; }
+        }
+        out_tokens[threadIdx.x] = bi;
+        if (out_best != nullptr) out_best[threadIdx.x] = bv;
+      }
+      if (threadIdx.x == 0) *ticket = 0u;      // ready for the next call
+    }
+  }
+}
+
+// ------------------------------------------------------------------ argmax
+
+constexpr int kArgmaxCluster = 8;
+constexpr int kArgmaxThreads = 512;
+
+// One cluster of 8 CTAs per logits row.  Each thread scans 8 bf16 logits per
+// 16-byte load; CTA winners meet in the shared memory of cluster rank 0
+// (distributed shared memory), which writes the token.  Greedy rule of
+// kernels-cuda/ops.cu:299-427: score = logit / temperature (1.0 when <= 0),
+// strictly greater wins, ties keep the lower index, the scan starts from
+// (-inf, 0) so NaN never wins.
+__global__ void __launch_bounds__(kArgmaxThreads)
+argmax_rows_kernel(const __nv_bfloat16 *__restrict__ logits, uint32_t *__restrict__ out,
+                   uint32_t *__restrict__ mirror_last, size_t rows, size_t vocab, float temperature) {
+  cg::cluster_group cluster = cg::this_cluster();
+  __shared__ float s_val[kArgmaxThreads / 32];
+  __shared__ uint32_t s_idx[kArgmaxThreads / 32];
+  __shared__ float c_val[kArgmaxCluster];
+  __shared__ uint32_t c_idx[kArgmaxCluster];
+
+  const size_t row = blockIdx.x / kArgmaxCluster;
+  const uint32_t rank = cluster.block_rank();
+  const __nv_bfloat16 *l = logits + row * vocab;
+  const float temp = temperature > 0.f ? temperature : 1.0f;
+  const bool divide = temp != 1.0f;
+
+  float bv = -INFINITY;
+  uint32_t bi = 0u;
+  auto consider = [&](float raw, uint32_t idx) {
+    const float s = divide ? __fdiv_rn(raw, temp) : raw;
+    if (better(s, idx, bv, bi)) { bv = s; bi = idx; }
+  };
+  // head elements until 16-byte alignment, then vector body, then tail
+  const uintptr_t addr = reinterpret_cast<uintptr_t>(l);
+  const size_t head = min(vocab, static_cast<size_t>(((16 - (addr & 15)) & 15) / 2));
+  const size_t vec = (vocab - head) / 8;
+  const uint32_t tid = rank * kArgmaxThreads + threadIdx.x;
+  const uint32_t nthreads = kArgmaxCluster * kArgmaxThreads;
+  if (tid < head) consider(__bfloat162float(l[tid]), tid);
+  const uint4 *lv = reinterpret_cast<const uint4 *>(l + head);
+  for (size_t v = tid; v < vec; v += nthreads) {
+    const uint4 p = __ldcs(lv + v);
+    const uint32_t w[4] = {p.x, p.y, p.z, p.w};
+    const uint32_t base = static_cast<uint32_t>(head + v * 8);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      consider(__uint_as_float(w[i] << 16), base + 2 * i);
+      consider(__uint_as_float(w[i] & 0xffff0000u), base + 2 * i + 1);
+    }
+  }
+  for (size_t i = head + vec * 8 + tid; i < vocab; i += nthreads) consider(__bfloat162float(l[i]), static_cast<uint32_t>(i));
+
+  for (int off = 16; off > 0; off >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+    const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, off);
+    if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+  }
+  if ((threadIdx.x & 31) == 0) { s_val[threadIdx.x >> 5] = bv; s_idx[threadIdx.x >> 5] = bi; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < kArgmaxThreads / 32; ++w)
+      if (better(s_val[w], s_idx[w], bv, bi)) { bv = s_val[w]; bi = s_idx[w]; }
+    float *dst_v = cluster.map_shared_rank(c_val, 0);
+    uint32_t *dst_i = cluster.map_shared_rank(c_idx, 0);
+    dst_v[rank] = bv;
+    dst_i[rank] = bi;
+  }
+  cluster.sync();
+  if (rank == 0 && threadIdx.x == 0) {
+    bv = c_val[0]; bi = c_idx[0];
+    for (int r = 1; r < kArgmaxCluster; ++r)
+      if (better(c_val[r], c_idx[r], bv, bi)) { bv = c_val[r]; bi = c_idx[r]; }
+    out[row] = bi;
+    if (mirror_last != nullptr && row + 1 == rows) *mirror_last = bi;
+  }
+}
+
+int launch_argmax(const __nv_bfloat16 *logits, uint32_t *out, uint32_t *mirror, size_t rows, size_t vocab,
+                  float temperature) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>(rows * kArgmaxCluster));
+  cfg.blockDim = dim3(kArgmaxThreads);
+  cfg.stream = q36::stream();
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = kArgmaxCluster;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return q36::cuda_status(cudaLaunchKernelEx(&cfg, argmax_rows_kernel, logits, out, mirror, rows, vocab, temperature));
+}
+
+int g_sm_count = 0;
+int sm_count() {
+  if (g_sm_count == 0) {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess &&
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
+      g_sm_count = n;
+    else
+      return 148;
+  }
+  return g_sm_count;
+}
+
+template <int N, bool FUSED>
+int launch_gemv_n(const uint8_t *w, const float *scales, const __nv_bfloat16 *x, __nv_bfloat16 *y, size_t rows,
+                  size_t cols, uint32_t row_offset, uint32_t *tokens, float *best, float2 *partials,
+                  unsigned *ticket, unsigned grid) {
+  const size_t smem = static_cast<size_t>(N) * cols * 2;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(lm_head_gemv_kernel<N, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    200 * 1024);
+  });
+  if (attr_err != cudaSuccess) return QWEN36_STATUS_CUDA_ERROR;
+  lm_head_gemv_kernel<N, FUSED><<<grid, kThreads, smem, q36::stream()>>>(
+      w, scales, x, y, rows, static_cast<uint32_t>(cols), row_offset, tokens, best, partials, ticket);
+  return q36::launch_status();
+}
+
+template <bool FUSED>
+int launch_gemv(size_t n, const uint8_t *w, const float *scales, const __nv_bfloat16 *x, __nv_bfloat16 *y,
+                size_t rows, size_t cols, uint32_t row_offset, uint32_t *tokens, float *best, float2 *partials,
+                unsigned *ticket, unsigned grid) {
+#define Q36_CASE(NN) \
+  case NN: return launch_gemv_n<NN, FUSED>(w, scales, x, y, rows, cols, row_offset, tokens, best, partials, ticket, grid);
+  switch (n) {
+    Q36_CASE(1) Q36_CASE(2) Q36_CASE(3) Q36_CASE(4) Q36_CASE(5) Q36_CASE(6) Q36_CASE(7) Q36_CASE(8)
+    Q36_CASE(9) Q36_CASE(10) Q36_CASE(11) Q36_CASE(12) Q36_CASE(13) Q36_CASE(14) Q36_CASE(15) Q36_CASE(16)
+    default: return QWEN36_STATUS_INVALID_ARGUMENT;
+  }
+#undef Q36_CASE
+}
+
+// Persistent grid: enough CTAs to fill the GPU, never more than there is work.
+unsigned gemv_grid(size_t rows, size_t n, size_t cols) {
+  const int r = n == 1 ? 4 : (n <= 4 ? 2 : 1);
+  const size_t need = q36::div_ceil(rows, static_cast<size_t>(kWarps) * r);
+  const size_t smem = n * cols * 2;
+  const size_t per_sm = smem > 100 * 1024 ? 1 : (smem > 48 * 1024 ? 2 : 4);
+  const size_t cap = static_cast<size_t>(sm_count()) * per_sm;
+  return static_cast<unsigned>(need < cap ? need : cap);
+}
+
+bool gemv_args_ok(size_t rows, size_t cols, size_t n, uint64_t w, uint64_t s, uint64_t x) {
+  // cols % 16: kernels-cuda/lm_head_fp8.cu:594; 16-byte aligned operands for
+  // the vector loads (row starts inherit it from cols % 16).
+  return rows != 0 && cols != 0 && n != 0 && n <= QWEN36_LM_HEAD_FP8_MAX_N && cols % 16 == 0 && w != 0 &&
+         s != 0 && x != 0 && ((w | x) & 15u) == 0 && n * cols * 2 <= 200 * 1024;
+}
+
+}  // namespace
+
+extern "C" int qwen36_lm_head_fp8_quantize(const qwen36_lm_head_fp8_quantize_spec_t *spec) {
+  if (spec == nullptr) return QWEN36_STATUS_NULL_POINTER;
+  if (spec->rows == 0 || spec->cols == 0 || spec->weight_bf16.ptr == 0 || spec->weight_e4m3.ptr == 0 ||
+      spec->row_scales_f32.ptr == 0 || spec->rows > 0x7fffffffull)
+    return QWEN36_STATUS_INVALID_ARGUMENT;
+  lm_head_quantize_kernel<<<static_cast<unsigned>(spec->rows), kThreads, 0, q36::stream()>>>(
+      as_ptr<const __nv_bfloat16>(spec->weight_bf16), as_ptr<uint8_t>(spec->weight_e4m3),
+      as_ptr<float>(spec->row_scales_f32), spec->rows, spec->cols);
+  return q36::launch_status();
+}
+
+extern "C" int qwen36_lm_head_fp8_gemv(const qwen36_lm_head_fp8_gemv_spec_t *spec) {
+  if (spec == nullptr) return QWEN36_STATUS_NULL_POINTER;
+  if (spec->output_bf16.ptr == 0 ||
+      !gemv_args_ok(spec->rows, spec->cols, spec->n, spec->weight_e4m3.ptr, spec->row_scales_f32.ptr,
+                    spec->input_bf16.ptr))
+    return QWEN36_STATUS_INVALID_ARGUMENT;
+  return launch_gemv<false>(spec->n, as_ptr<const uint8_t>(spec->weight_e4m3),
+                            as_ptr<const float>(spec->row_scales_f32),
+                            as_ptr<const __nv_bfloat16>(spec->input_bf16), as_ptr<__nv_bfloat16>(spec->output_bf16),
+                            spec->rows, spec->cols, 0u, nullptr, nullptr, nullptr, nullptr,
+                            gemv_grid(spec->rows, spec->n, spec->cols));
+}
+
+extern "C" size_t qwen36_lm_head_fp8_argmax_workspace_bytes(size_t rows, size_t n) {
+  (void)rows;
+  // ticket word (padded to 16 bytes) + one (value, index) pair per CTA per token
+  return 16 + static_cast<size_t>(148 * 4) * 8 * (n == 0 ? 1 : n);
+}
+
+extern "C" int qwen36_lm_head_fp8_gemv_argmax(const qwen36_lm_head_fp8_argmax_spec_t *spec) {
+  if (spec == nullptr) return QWEN36_STATUS_NULL_POINTER;
+  if (spec->output_token_u32.ptr == 0 || spec->workspace.ptr == 0 || (spec->workspace.ptr & 15u) != 0 ||
+      !gemv_args_ok(spec->rows, spec->cols, spec->n, spec->weight_e4m3.ptr, spec->row_scales_f32.ptr,
+                    spec->input_bf16.ptr))
+    return QWEN36_STATUS_INVALID_ARGUMENT;
+  unsigned grid = gemv_grid(spec->rows, spec->n, spec->cols);
+  const size_t slots = (spec->workspace_bytes < 16 ? 0 : spec->workspace_bytes - 16) / (8 * spec->n);
+  if (slots == 0) return QWEN36_STATUS_INVALID_ARGUMENT;
+  if (grid > slots) grid = static_cast<unsigned>(slots);
+  return launch_gemv<true>(spec->n, as_ptr<const uint8_t>(spec->weight_e4m3),
+                           as_ptr<const float>(spec->row_scales_f32),
+                           as_ptr<const __nv_bfloat16>(spec->input_bf16), nullptr, spec->rows, spec->cols,
+                           spec->row_offset, as_ptr<uint32_t>(spec->output_token_u32),
+                           as_ptr<float>(spec->best_value_f32),
+                           reinterpret_cast<float2 *>(static_cast<uintptr_t>(spec->workspace.ptr + 16)),
+                           as_ptr<unsigned>(spec->workspace), grid);
+}
+
+extern "C" int qwen36_sample(const qwen36_sampling_spec_t *spec) {
+  if (spec == nullptr) return QWEN36_STATUS_NULL_POINTER;
+  if (spec->vocab_size == 0 || spec->logits_bf16.ptr == 0 || spec->output_token_u32.ptr == 0)
+    return QWEN36_STATUS_INVALID_ARGUMENT;
+  return launch_argmax(as_ptr<const __nv_bfloat16>(spec->logits_bf16), as_ptr<uint32_t>(spec->output_token_u32),
+                       as_ptr<uint32_t>(spec->mirror_output_token_u32), 1, spec->vocab_size, spec->temperature);
+}
+
+extern "C" int qwen36_sample_rows(const qwen36_sampling_rows_spec_t *spec) {
+  if (spec == nullptr) return QWEN36_STATUS_NULL_POINTER;
+  if (spec->rows == 0 || spec->vocab_size == 0 || spec->logits_bf16.ptr == 0 || spec->output_token_u32.ptr == 0 ||
+      spec->rows > (1u << 24))
+    return QWEN36_STATUS_INVALID_ARGUMENT;
+  return launch_argmax(as_ptr<const __nv_bfloat16>(spec->logits_bf16), as_ptr<uint32_t>(spec->output_token_u32),
+                       as_ptr<uint32_t>(spec->mirror_last_output_token_u32), spec->rows, spec->vocab_size,
+                       spec->temperature);
+}

@@ -1,0 +1,217 @@
+// NVFP4 activation quantisation, block-scale retiling and weight
+// dequantisation.  All three are HBM-bound byte shuffles: one thread owns one
+// 16-value group, four neighbouring lanes own the four groups of one scale
+// word, loads and stores are 16/8/4-byte vectors.
+//
+// Rounding follows the reference bit for bit (kernels-cuda/ops.cu:81-139,
+// 704-761): IEEE float32 division by the decoded scale, E2M1 ties toward zero,
+// UE4M3 ties down.
+#include "common.cuh"
+
+namespace {
+
+using q36::as_ptr;
+
+constexpr int kThreads = 256;
+
+// One thread per 16-group.  `quads` = ceil(groups / 4): the group index space
+// of a row is padded to a multiple of four so that the lanes 4q..4q+3 always
+// belong to one row and one 4-byte scale word.
+__global__ void __launch_bounds__(kThreads)
+nvfp4_quantize_kernel(const __nv_bfloat16 *__restrict__ in, uint8_t *__restrict__ out_fp4,
+                      uint8_t *__restrict__ out_sf, float *__restrict__ tensor_scale, size_t rows,
+                      size_t values, float input_tensor_scale) {
+  const float g = input_tensor_scale > 0.0f ? input_tensor_scale : 1.0f;
+  const size_t groups = q36::div_ceil(values, 16);
+  const size_t padded = q36::round_up(groups, 4);
+  const size_t idx = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x;
+  const size_t row = idx / padded;
+  const size_t group = idx % padded;
+  const bool valid = row < rows && group < groups;
+
+  if (idx == 0 && tensor_scale != nullptr) *tensor_scale = g;
+
+  uint32_t sf_code = 0;
+  if (valid) {
+    const size_t start = group * 16;
+    const __nv_bfloat16 *src = in + row * values + start;
+    const bool full = start + 16 <= values;
+    float x[16];
+    if (full && (reinterpret_cast<uintptr_t>(src) & 15u) == 0) {
+      const uint4 lo = __ldg(reinterpret_cast<const uint4 *>(src));
+      const uint4 hi = __ldg(reinterpret_cast<const uint4 *>(src) + 1);
+      const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        x[2 * i] = __uint_as_float(w[i] << 16);
+        x[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; ++i)
+        x[i] = start + i < values ? __bfloat162float(src[i]) : 0.0f;
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(x[i]));
+
+    const float sv = amax > 0.0f ? fmaxf(__fdiv_rn(amax, __fmul_rn(6.0f, g)), 1.0e-8f) : 1.0f;
+    sf_code = q36::encode_ue4m3(sv);
+    const float ds = fmaxf(__fmul_rn(q36::decode_e4m3(sf_code), g), 1.0e-8f);
+
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) lo |= q36::encode_e2m1(__fdiv_rn(x[i], ds)) << (4 * i);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) hi |= q36::encode_e2m1(__fdiv_rn(x[8 + i], ds)) << (4 * i);
+
+    uint8_t *dst = out_fp4 + row * q36::div_ceil(values, 2) + start / 2;
+    if (full && (reinterpret_cast<uintptr_t>(dst) & 7u) == 0) {
+      *reinterpret_cast<uint2 *>(dst) = make_uint2(lo, hi);
+    } else {
+      const uint64_t both = (static_cast<uint64_t>(hi) << 32) | lo;
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (start + 2 * i < values) dst[i] = static_cast<uint8_t>(both >> (8 * i));
+    }
+  }
+
+  // Gather the four scale bytes of the quad into one word.
+  const unsigned lane4 = threadIdx.x & 3u;
+  uint32_t word = sf_code << (8 * lane4);
+  word |= __shfl_xor_sync(0xffffffffu, word, 1);
+  word |= __shfl_xor_sync(0xffffffffu, word, 2);
+  if (valid) {
+    const size_t off = q36::sf_offset(group, row, padded);
+    if ((group | 3) < groups) {          // the whole quad is real: one 4-byte store
+      if (lane4 == 0) *reinterpret_cast<uint32_t *>(out_sf + off) = word;
+    } else {
+      out_sf[off] = static_cast<uint8_t>(sf_code);
+    }
+  }
+}
+
+// Row-major [rows, inner_groups] scale bytes -> tiled layout.  One thread per
+// 4-byte word of the OUTPUT, so that every byte of the tiled buffer (padding
+// included, as zero) is written exactly once and no separate memset is needed.
+__global__ void __launch_bounds__(kThreads)
+nvfp4_retile_kernel(const uint8_t *__restrict__ in, uint32_t *__restrict__ out, size_t rows,
+                    size_t inner_groups, size_t words) {
+  const size_t w = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x;
+  if (w >= words) return;
+  const size_t tiles_per_block = q36::round_up(inner_groups, 4) / 4;
+  const size_t tile = w / 128, in_tile = w % 128;
+  const size_t row = (tile / tiles_per_block) * 128 + (in_tile % 4) * 32 + in_tile / 4;
+  const size_t g0 = (tile % tiles_per_block) * 4;
+  uint32_t v = 0;
+  if (row < rows) {
+    const uint8_t *src = in + row * inner_groups + g0;
+    if (g0 + 4 <= inner_groups && (reinterpret_cast<uintptr_t>(src) & 3u) == 0) {
+      v = __ldg(reinterpret_cast<const uint32_t *>(src));
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (g0 + i < inner_groups) v |= static_cast<uint32_t>(__ldg(src + i)) << (8 * i);
+    }
+  }
+  out[w] = v;
+}
+
+// One thread per 16-group: 8 weight bytes in, 16 floats out.
+__global__ void __launch_bounds__(kThreads)
+nvfp4_dequantize_kernel(const uint8_t *__restrict__ weight, const uint8_t *__restrict__ sf,
+                        const float *__restrict__ tensor_scale, float *__restrict__ out,
+                        size_t out_features, size_t in_features) {
+  const size_t groups = q36::div_ceil(in_features, 16);
+  const size_t idx = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x;
+  if (idx >= out_features * groups) return;
+  const size_t row = idx / groups, group = idx % groups;
+  const float global = tensor_scale == nullptr ? 1.0f : __ldg(tensor_scale);
+  const float scale =
+      __fmul_rn(q36::decode_e4m3(__ldg(sf + q36::sf_offset(group, row, q36::round_up(groups, 4)))), global);
+  const uint8_t *w = weight + row * q36::div_ceil(in_features, 2) + group * 8;
+  float *dst = out + row * in_features + group * 16;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const size_t col = group * 16 + i;
+    if (col < in_features) {
+      const uint32_t b = __ldg(w + i / 2);
+      dst[i] = __fmul_rn(q36::e2m1_value((i & 1) ? (b >> 4) : b), scale);
+    }
+  }
+}
+
+int launch_quantize(qwen36_device_ptr_t in, qwen36_device_ptr_t fp4, qwen36_device_ptr_t sf,
+                    qwen36_device_ptr_t ts, size_t rows, size_t values, float its) {
+  const size_t padded = q36::round_up(q36::div_ceil(values, 16), 4);
+  const size_t total = rows * padded;
+  const size_t blocks = q36::div_ceil(total, kThreads);
+  if (blocks > 0x7fffffffull) return QWEN36_STATUS_INVALID_ARGUMENT;
+  nvfp4_quantize_kernel<<<static_cast<unsigned>(blocks), kThreads, 0, q36::stream()>>>(
+      as_ptr<const __nv_bfloat16>(in), as_ptr<uint8_t>(fp4), as_ptr<uint8_t>(sf), as_ptr<float>(ts), rows,
+      values, its);
+  return q36::launch_status();
+}
+
+}  // namespace
+
+extern "C" int qwen36_nvfp4_quantize_bf16(const qwen36_nvfp4_quantize_spec_t *spec) {
+  if (spec == nullptr) return QWEN36_STATUS_NULL_POINTER;
+  if (spec->values == 0 || spec->input_bf16.ptr == 0 || spec->output_fp4.ptr == 0 ||
+      spec->output_scale_e4m3.ptr == 0)
+    return QWEN36_STATUS_INVALID_ARGUMENT;
+  return launch_quantize(spec->input_bf16, spec->output_fp4, spec->output_scale_e4m3,
+                         spec->output_tensor_scale_f32, 1, spec->values, spec->input_tensor_scale_f32);
+}
+
+extern "C" int qwen36_nvfp4_quantize_rows(const qwen36_nvfp4_quantize_rows_spec_t *spec) {
+  if (spec == nullptr) return QWEN36_STATUS_NULL_POINTER;
+  if (spec->rows == 0 || spec->values == 0 || spec->input_bf16.ptr == 0 || spec->output_fp4.ptr == 0 ||
+      spec->output_scale_e4m3.ptr == 0)
+    return QWEN36_STATUS_INVALID_ARGUMENT;
+  return launch_quantize(spec->input_bf16, spec->output_fp4, spec->output_scale_e4m3,
+                         spec->output_tensor_scale_f32, spec->rows, spec->values,
+                         spec->input_tensor_scale_f32);
+}
+
+extern "C" int qwen36_nvfp4_retile_scales(const qwen36_nvfp4_retile_scales_spec_t *spec) {
+  if (spec == nullptr) return QWEN36_STATUS_NULL_POINTER;
+  if (spec->rows == 0 || spec->inner_groups == 0 || spec->input_row_major_u8.ptr == 0 ||
+      spec->output_tiled_u8.ptr == 0 || (spec->output_tiled_u8.ptr & 3u) != 0)
+    return QWEN36_STATUS_INVALID_ARGUMENT;
+  const size_t words = q36::sf_bytes(spec->inner_groups, spec->rows) / 4;
+  nvfp4_retile_kernel<<<static_cast<unsigned>(q36::div_ceil(words, kThreads)), kThreads, 0, q36::stream()>>>(
+      as_ptr<const uint8_t>(spec->input_row_major_u8), as_ptr<uint32_t>(spec->output_tiled_u8), spec->rows,
+      spec->inner_groups, words);
+  return q36::launch_status();
+}
+
+extern "C" int qwen36_nvfp4_dequantize(const qwen36_nvfp4_dequantize_spec_t *spec) {
+  if (spec == nullptr) return QWEN36_STATUS_NULL_POINTER;
+  if (spec->out_features == 0 || spec->in_features == 0 || spec->weight_u8.ptr == 0 ||
+      spec->block_scale_e4m3.ptr == 0 || spec->output_f32.ptr == 0)
+    return QWEN36_STATUS_INVALID_ARGUMENT;
+  const size_t total = spec->out_features * q36::div_ceil(spec->in_features, 16);
+  nvfp4_dequantize_kernel<<<static_cast<unsigned>(q36::div_ceil(total, kThreads)), kThreads, 0, q36::stream()>>>(
+      as_ptr<const uint8_t>(spec->weight_u8), as_ptr<const uint8_t>(spec->block_scale_e4m3),
+      as_ptr<const float>(spec->tensor_scale_f32), as_ptr<float>(spec->output_f32), spec->out_features,
+      spec->in_features);
+  return q36::launch_status();
+}
+
+extern "C" size_t qwen36_nvfp4_tiled_scale_bytes(size_t rows, size_t inner_groups) {
+  return q36::sf_bytes(inner_groups, rows);
+}
+
+extern "C" int qwen36_nvfp4_tile_scales_host(const uint8_t *row_major, uint8_t *tiled, size_t rows,
+                                             size_t inner_groups) {
+  if (row_major == nullptr || tiled == nullptr) return QWEN36_STATUS_NULL_POINTER;
+  if (rows == 0 || inner_groups == 0) return QWEN36_STATUS_INVALID_ARGUMENT;
+  const size_t sf_inner = q36::round_up(inner_groups, 4);
+  const size_t bytes = q36::sf_bytes(inner_groups, rows);
+  for (size_t i = 0; i < bytes; ++i) tiled[i] = 0;
+  for (size_t r = 0; r < rows; ++r)
+    for (size_t g = 0; g < inner_groups; ++g)
+      tiled[q36::sf_offset(g, r, sf_inner)] = row_major[r * inner_groups + g];
+  return QWEN36_STATUS_SUCCESS;
+}

@@ -1,0 +1,130 @@
+"""GPU parity of the int8 KV path: codes and scales bit-exact; attention output rel-L2 <= 1e-2
+against the oracle (which restates the reference's two-pass float32 softmax)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as orc
+from speedoza_b200 import synth
+from conftest import bf16_host, to_dev
+
+pytestmark = pytest.mark.gpu
+
+
+def rel_l2(got, want):
+    return np.linalg.norm(got.astype(np.float64) - want) / max(np.linalg.norm(want), 1e-30)
+
+
+def encode_both(backend, k, v, tokens, kv_heads, head_dim):
+    kq = torch.zeros((tokens, kv_heads, head_dim), dtype=torch.int8, device="cuda")
+    vq = torch.zeros_like(kq)
+    meta = torch.zeros((tokens, kv_heads, 2), dtype=torch.float32, device="cuda")
+    backend.turboquant_encode_kv_rows(to_dev(k), to_dev(v), kq, vq, meta, 0)
+    kq_o = np.zeros((tokens, kv_heads, head_dim), np.int8); vq_o = np.zeros_like(kq_o)
+    meta_o = np.zeros((tokens, kv_heads, 2), np.float32)
+    orc.kv_encode(k, v, 0, kq_o, vq_o, meta_o)
+    return (kq, vq, meta), (kq_o, vq_o, meta_o)
+
+
+@pytest.mark.parametrize("tokens,kv_heads,head_dim", [(1, 4, 256), (300, 4, 256), (17, 2, 128), (9, 3, 40)])
+def test_encode_bit_exact(backend, tokens, kv_heads, head_dim):
+    rng = np.random.default_rng(tokens + head_dim)
+    _, k, v = synth.qkv(rng, tokens, 2 * kv_heads, kv_heads, head_dim, outliers=min(4, head_dim))
+    k[0, 0] = 0                                             # zero vector: scale 0, codes 0
+    # exact .5 ties after scaling: amax 127 -> scale 1
+    k[-1, -1] = synth.f32_to_bf16_bits(np.resize(np.array([127, 0.5, 1.5, 2.5, -0.5, -1.5, 126.5, -126.5], np.float32), head_dim))
+    (kq, vq, meta), (kq_o, vq_o, meta_o) = encode_both(backend, k, v, tokens, kv_heads, head_dim)
+    assert np.array_equal(meta.cpu().numpy().view(np.uint32), meta_o.view(np.uint32))
+    assert np.array_equal(kq.cpu().numpy(), kq_o) and np.array_equal(vq.cpu().numpy(), vq_o)
+
+
+def test_encode_single_position_entry_appends(backend):
+    rng = np.random.default_rng(4)
+    _, k, v = synth.qkv(rng, 6, 8, 4, 256)
+    kq = torch.zeros((6, 4, 256), dtype=torch.int8, device="cuda"); vq = torch.zeros_like(kq)
+    meta = torch.zeros((6, 4, 2), dtype=torch.float32, device="cuda")
+    for t in range(6):
+        backend.turboquant_encode_kv(to_dev(k[t]), to_dev(v[t]), kq, vq, meta, t, q_heads=8)
+    (kq2, vq2, meta2), _ = encode_both(backend, k, v, 6, 4, 256)
+    assert torch.equal(kq, kq2) and torch.equal(vq, vq2) and torch.equal(meta, meta2)
+
+
+@pytest.mark.parametrize("tokens,q_heads,kv_heads,head_dim", [
+    (1, 24, 4, 256), (63, 24, 4, 256), (513, 24, 4, 256), (8192, 24, 4, 256),
+    (200, 8, 8, 128), (100, 6, 2, 64), (77, 10, 2, 256), (50, 4, 2, 40)])
+def test_attention_vs_oracle(backend, tokens, q_heads, kv_heads, head_dim):
+    rng = np.random.default_rng(tokens * 3 + q_heads)
+    q, k, v = synth.qkv(rng, tokens, q_heads, kv_heads, head_dim, outliers=min(4, head_dim))
+    (kq, vq, meta), (kq_o, vq_o, meta_o) = encode_both(backend, k, v, tokens, kv_heads, head_dim)
+    ws = backend.attention_workspace(q_heads, head_dim, "cuda")
+    out = backend.turboquant_attention(to_dev(q), kq, vq, meta, tokens - 1, ws)
+    want = synth.bf16_bits_to_f32(orc.kv_attention(q, kq_o, vq_o, meta_o, tokens - 1))
+    err = rel_l2(synth.bf16_bits_to_f32(bf16_host(out)), want)
+    assert err <= 1e-2, err
+
+
+def test_attention_position_inside_longer_cache(backend):
+    """position < cache length: rows after `position` must not be read into the result."""
+    rng = np.random.default_rng(12)
+    q, k, v = synth.qkv(rng, 400)
+    (kq, vq, meta), (kq_o, vq_o, meta_o) = encode_both(backend, k, v, 400, 4, 256)
+    ws = backend.attention_workspace(24, 256, "cuda")
+    out = backend.turboquant_attention(to_dev(q), kq, vq, meta, 249, ws)
+    want = synth.bf16_bits_to_f32(orc.kv_attention(q, kq_o, vq_o, meta_o, 249))
+    assert rel_l2(synth.bf16_bits_to_f32(bf16_host(out)), want) <= 1e-2
+
+
+def test_partials_and_merge_equal_whole(backend):
+    """KV-range sharding: partials over disjoint ranges (one empty) merged == single call."""
+    rng = np.random.default_rng(21)
+    T = 3000
+    q, k, v = synth.qkv(rng, T)
+    (kq, vq, meta), (kq_o, vq_o, meta_o) = encode_both(backend, k, v, T, 4, 256)
+    ws = backend.attention_workspace(24, 256, "cuda")
+    qd = to_dev(q)
+    whole = backend.turboquant_attention(qd, kq, vq, meta, T - 1, ws)
+    ranges = [(0, 1000), (1000, 1000), (1000, 2500), (2500, T)]
+    pm = torch.empty((24, len(ranges)), dtype=torch.float32, device="cuda")
+    pl = torch.empty_like(pm)
+    po = torch.empty((24, len(ranges), 256), dtype=torch.float32, device="cuda")
+    for i, (a, b) in enumerate(ranges):
+        m_, l_, o_ = backend.turboquant_attention_partial(qd, kq, vq, meta, a, b, ws)
+        pm[:, i], pl[:, i], po[:, i] = m_, l_, o_
+    assert torch.isneginf(pm[:, 1]).all() and (pl[:, 1] == 0).all() and (po[:, 1] == 0).all()
+    merged = backend.attention_merge_partials(pm, pl, po)
+    a = merged.float().cpu().numpy(); b = whole.float().cpu().numpy()
+    assert rel_l2(a, b.astype(np.float64)) <= 2e-3
+    # oracle partial contract: same (m, l, o) up to float rounding
+    om, ol, oo = orc.kv_attention_partial(q, kq_o, vq_o, meta_o, 1000, 2500)
+    assert np.allclose(pm[:, 2].cpu().numpy(), om, rtol=1e-4, atol=1e-4)
+    assert np.allclose(pl[:, 2].cpu().numpy(), ol, rtol=2e-3)
+    assert rel_l2(po[:, 2].cpu().numpy(), oo.astype(np.float64)) <= 2e-3
+    want = synth.bf16_bits_to_f32(orc.merge_partials(pm.cpu().numpy(), pl.cpu().numpy(), po.cpu().numpy()))
+    assert rel_l2(a, want.astype(np.float64)) <= 1e-2
+
+
+def test_attention_missing_workspace_is_an_error(backend):
+    from speedoza_b200.abi import KernelError
+    rng = np.random.default_rng(2)
+    q, k, v = synth.qkv(rng, 8)
+    (kq, vq, meta), _ = encode_both(backend, k, v, 8, 4, 256)
+    with pytest.raises(KernelError):
+        backend.turboquant_attention(to_dev(q), kq, vq, meta, 7, None)
+
+
+def test_long_context_softmax_property(backend):
+    """ctx 131072 (config-4 maximum): with V rows all equal to one vector the output must be that
+    vector (softmax weights sum to 1) whatever the scores are."""
+    T = 131072
+    gen = torch.Generator(device="cuda").manual_seed(8)
+    k = torch.randn((T, 4, 256), generator=gen, device="cuda").to(torch.bfloat16)
+    vrow = torch.randn((1, 4, 256), generator=gen, device="cuda").to(torch.bfloat16)
+    v = vrow.expand(T, 4, 256).contiguous()
+    q = torch.randn((24, 256), generator=gen, device="cuda").to(torch.bfloat16)
+    kq = torch.empty((T, 4, 256), dtype=torch.int8, device="cuda"); vq = torch.empty_like(kq)
+    meta = torch.empty((T, 4, 2), dtype=torch.float32, device="cuda")
+    backend.turboquant_encode_kv_rows(k, v, kq, vq, meta, 0)
+    ws = backend.attention_workspace(24, 256, "cuda")
+    out = backend.turboquant_attention(q, kq, vq, meta, T - 1, ws).float()
+    vd = (vq[0].float() * meta[0, :, 1:2]).repeat_interleave(6, dim=0)
+    assert torch.allclose(out, vd, rtol=1e-2, atol=1e-2)

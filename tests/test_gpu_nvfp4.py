@@ -1,0 +1,230 @@
+"""GPU parity of the NVFP4 kernels against the CPU oracle, through the C ABI.
+
+Bit-exact: quantised codes, packing, scale bytes, retiled scales, dequantised
+weights.  Floating-point outputs: rel-L2 against the oracle with the tolerance
+stated in each test (1e-3 for the W4A16 GEMV, 1e-2 for the W4A4 product)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as orc
+from speedoza_b200 import abi, synth
+from conftest import bf16_host, to_dev
+
+pytestmark = pytest.mark.gpu
+
+
+def rel_l2(got, want):
+    got = got.astype(np.float64); want = want.astype(np.float64)
+    return np.linalg.norm(got - want) / max(np.linalg.norm(want), 1e-30)
+
+
+def make_weight(rng, n, k):
+    packed, sf_rm = synth.nvfp4_weight(rng, n, k)
+    return packed, sf_rm, orc.retile_scales(sf_rm)
+
+
+# ---------------------------------------------------------------- retile / quantise
+
+@pytest.mark.parametrize("rows,groups", [(1, 1), (5, 3), (128, 4), (130, 12), (257, 7), (5120, 320)])
+def test_retile_scales_bit_exact(backend, rows, groups):
+    rng = np.random.default_rng(rows * 1000 + groups)
+    sf = rng.integers(0, 256, size=(rows, groups), dtype=np.uint8)
+    got = backend.nvfp4_retile_scales(to_dev(sf)).cpu().numpy()
+    assert np.array_equal(got, orc.retile_scales(sf))
+
+
+def adversarial_activations(rng, rows, k):
+    x = rng.standard_normal((rows, k)).astype(np.float32)
+    x[:, ::37] *= 20.0                       # outlier channels
+    if rows > 1:
+        ties = np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 6.0], dtype=np.float32)
+        x[1, :16] = np.concatenate([ties, -ties])          # amax 6 -> scale 1 -> exact ties
+    if rows > 2:
+        x[2] = 0.0
+        x[2, 5] = 1e-3                        # scale code underflows to 0
+        x[2, 17] = -1e-30
+    if rows > 3:
+        x[3] *= 1e-4
+    if rows > 4:
+        x[4] *= 3000.0                        # scales near the UE4M3 clamp
+    return synth.f32_to_bf16_bits(x)
+
+
+@pytest.mark.parametrize("rows,k,its", [(1, 128, 0.0), (5, 5120, 0.0), (7, 40, 1.25), (130, 192, 0.5),
+                                        (3, 33, 1.25), (64, 17408, 1.0 / 2688.0), (512, 5120, 0.37)])
+def test_quantize_rows_bit_exact(backend, rows, k, its):
+    rng = np.random.default_rng(rows * 7 + k)
+    x = adversarial_activations(rng, rows, k)
+    w_fp4, w_sf, w_ts = orc.nvfp4_quantize_rows(x, its)
+    fp4, sf, ts = backend.nvfp4_quantize_rows(to_dev(x), its)
+    assert float(ts.item()) == np.float32(w_ts)
+    assert np.array_equal(fp4.cpu().numpy(), w_fp4), "packed codes"
+    assert np.array_equal(sf.cpu().numpy(), w_sf), "scale bytes"
+
+
+def test_quantize_single_row_entry_and_known_answer(backend):
+    # kernels-cuda/smoke.cu:2140-2180: ones -> scale byte 0x23, codes 0x77
+    x = synth.f32_to_bf16_bits(np.ones((1, 128), dtype=np.float32))
+    fp4, sf, ts = backend.nvfp4_quantize_bf16(to_dev(x).reshape(-1))
+    assert float(ts.item()) == 1.0
+    assert np.all(fp4.cpu().numpy() == 0x77)
+    sfh = sf.cpu().numpy()
+    assert all(sfh[orc.sf_offset(g, 0, 8)] == 0x23 for g in range(8))
+    rng = np.random.default_rng(9)
+    x = adversarial_activations(rng, 1, 5120)
+    w_fp4, w_sf, _ = orc.nvfp4_quantize_rows(x, 1.25)
+    fp4, sf, _ = backend.nvfp4_quantize_bf16(to_dev(x).reshape(-1), 1.25)
+    assert np.array_equal(fp4.cpu().numpy(), w_fp4.reshape(-1)) and np.array_equal(sf.cpu().numpy(), w_sf)
+
+
+def test_quantize_subnormal_scale_ties(backend):
+    """amax/6 landing exactly between two subnormal UE4M3 codes: the float32 expression of
+    kernels-cuda/ops.cu:96 rounds those up."""
+    vals = np.array([(c + 0.5) * 2.0 ** -9 * 6.0 for c in range(1, 7)], dtype=np.float32)
+    x = np.zeros((1, 16 * len(vals)), dtype=np.float32)
+    x[0, ::16] = vals
+    xb = synth.f32_to_bf16_bits(x)
+    assert np.array_equal(synth.bf16_bits_to_f32(xb), x)       # exactly representable
+    w_fp4, w_sf, _ = orc.nvfp4_quantize_rows(xb, 0.0)
+    fp4, sf, _ = backend.nvfp4_quantize_rows(to_dev(xb), 0.0)
+    assert np.array_equal(sf.cpu().numpy(), w_sf) and np.array_equal(fp4.cpu().numpy(), w_fp4)
+    assert [int(w_sf[orc.sf_offset(g, 0, 8)]) for g in range(6)] == [2, 3, 4, 5, 6, 7]
+
+
+def test_quantize_round_trip_property_large(backend):
+    """At full prefill size (M = 8192, K = 5120): requantising the dequantised tensor gives the
+    same bytes (idempotence), checked on the device without the oracle."""
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn((8192, 5120), generator=g, device="cuda", dtype=torch.float32)
+    x[:, ::97] *= 20
+    x = x.to(torch.bfloat16)
+    fp4, sf, ts = backend.nvfp4_quantize_rows(x, 0.5)
+    deq = backend.nvfp4_dequantize(fp4, sf, ts, 5120).to(torch.bfloat16)
+    fp4b, sfb, _ = backend.nvfp4_quantize_rows(deq, 0.5)
+    assert torch.equal(sf, sfb)
+    assert torch.equal(fp4 & 0x77, fp4b & 0x77)      # magnitudes; a -0 code may lose its sign bit
+
+
+# ---------------------------------------------------------------- dequantise / W4A16 GEMV
+
+@pytest.mark.parametrize("n,k", [(1, 4), (160, 192), (5120, 5120), (130, 40)])
+def test_dequantised_weights_bit_exact(backend, n, k):
+    rng = np.random.default_rng(n + k)
+    packed = rng.integers(0, 256, size=(n, (k + 1) // 2), dtype=np.uint8)
+    sf_rm = rng.integers(0, 256, size=(n, (k + 15) // 16), dtype=np.uint8)      # every byte value
+    sf = orc.retile_scales(sf_rm)
+    ts = torch.tensor([synth.WEIGHT_GLOBAL_SCALE], dtype=torch.float32, device="cuda")
+    got = backend.nvfp4_dequantize(to_dev(packed), to_dev(sf), ts, k).cpu().numpy()
+    want = orc.nvfp4_dequant(packed, sf, synth.WEIGHT_GLOBAL_SCALE, k)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def test_matvec_known_answer(backend):
+    # kernels-cuda/smoke.cu:2114-2138
+    w = to_dev(np.array([[0x42, 0xA1]], dtype=np.uint8))
+    sf = backend.nvfp4_retile_scales(to_dev(np.array([[0x38]], dtype=np.uint8)))
+    assert sf.numel() == 512
+    x = to_dev(synth.f32_to_bf16_bits(np.array([1, 2, 3, 4], dtype=np.float32)))
+    one = torch.ones(1, dtype=torch.float32, device="cuda")
+    assert backend.nvfp4_matvec(x, w, sf, one).float().item() == 2.5
+    assert backend.nvfp4_matvec(x, w, sf, None).float().item() == 2.5
+
+
+@pytest.mark.parametrize("mode", [1, 0])
+@pytest.mark.parametrize("n,k", [(5120, 5120), (1024, 5120), (5120, 6144), (12288, 5120), (5120, 17408),
+                                 (34816, 5120), (130, 96), (40, 2080), (7, 33)])
+def test_matvec_w4a16_vs_oracle(backend, n, k, mode):
+    """Config-0 bar: rel-L2 <= 1e-3 on the bf16 output against the reference's scalar semantics."""
+    rng = np.random.default_rng(n * 3 + k + mode)
+    packed = rng.integers(0, 256, size=(n, (k + 1) // 2), dtype=np.uint8)
+    sf_rm = rng.integers(synth.SF_CODE_LO, synth.SF_CODE_HI + 1, size=(n, (k + 15) // 16), dtype=np.uint8)
+    sf = orc.retile_scales(sf_rm)
+    x = synth.activations(rng, 1, k)[0]
+    ts = torch.tensor([synth.WEIGHT_GLOBAL_SCALE], dtype=torch.float32, device="cuda")
+    backend.lib.qwen36_nvfp4_matvec_set_mode(mode)
+    try:
+        got = bf16_host(backend.nvfp4_matvec(to_dev(x), to_dev(packed), to_dev(sf), ts))
+    finally:
+        backend.lib.qwen36_nvfp4_matvec_set_mode(1)
+    want = orc.nvfp4_matvec(x, packed, sf, synth.WEIGHT_GLOBAL_SCALE, k)
+    err = rel_l2(synth.bf16_bits_to_f32(got), synth.bf16_bits_to_f32(want))
+    assert err <= 1e-3, err
+    assert (got == want).mean() > 0.98       # nearly every bf16 output identical
+
+
+def test_matvec_extreme_activation_ranges(backend):
+    """Scaled-float16 activation path: tiny, huge and mixed magnitudes stay within tolerance."""
+    rng = np.random.default_rng(77)
+    n, k = 256, 1024
+    packed, sf_rm, sf = make_weight(rng, n, k)
+    ts = torch.ones(1, dtype=torch.float32, device="cuda")
+    for gain in (1e-30, 1e-12, 1.0, 1e12, 1e30):
+        x = (rng.standard_normal(k) * gain).astype(np.float32)
+        x[::50] *= 1e-6
+        xb = synth.f32_to_bf16_bits(x)
+        got = synth.bf16_bits_to_f32(bf16_host(backend.nvfp4_matvec(to_dev(xb), to_dev(packed), to_dev(sf), ts)))
+        want = synth.bf16_bits_to_f32(orc.nvfp4_matvec(xb, packed, sf, 1.0, k))
+        assert rel_l2(got, want) <= 1e-3, gain
+
+
+def test_matvec_linearity_full_size(backend):
+    """Size-independent property at the largest decode shape: W(2x) == 2 W(x) exactly in bf16."""
+    gen = torch.Generator(device="cuda").manual_seed(1)
+    n, k = 34816, 5120
+    packed, sf_rm = synth.nvfp4_weight_device(gen, n, k, "cuda")
+    sf = backend.nvfp4_retile_scales(sf_rm)
+    x = torch.randn(k, generator=gen, device="cuda").to(torch.bfloat16)
+    ts = torch.tensor([synth.WEIGHT_GLOBAL_SCALE], dtype=torch.float32, device="cuda")
+    y1 = backend.nvfp4_matvec(x, packed, sf, ts)
+    y2 = backend.nvfp4_matvec(x * 2, packed, sf, ts)
+    assert torch.equal(y1.float() * 2, y2.float())
+
+
+# ---------------------------------------------------------------- W4A4 product
+
+def w4a4_case(rng, m, n, k, its=1.25):
+    packed, sf_rm, a_sf = make_weight(rng, m, k)
+    x = synth.activations(rng, n, k, outlier_frac=0.01)
+    b, b_sf, ts = orc.nvfp4_quantize_rows(x, its)
+    return packed, a_sf, x, b, b_sf, synth.WEIGHT_GLOBAL_SCALE * ts
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 1, 128), (256, 1, 5120), (40, 3, 96), (384, 5, 1024), (256, 8, 512),
+                                   (128, 17, 256), (256, 130, 512), (384, 512, 768)])
+def test_w4a4_gemm_vs_oracle(backend, m, n, k):
+    """rel-L2 <= 1e-2 against the double-precision dequantise-and-multiply oracle."""
+    rng = np.random.default_rng(m + 31 * n + k)
+    a, a_sf, x, b, b_sf, alpha = w4a4_case(rng, m, n, k)
+    got = bf16_host(backend.nvfp4_gemm(to_dev(a), to_dev(a_sf), to_dev(b), to_dev(b_sf), alpha, m, n, k))
+    want = orc.nvfp4_gemm(a, a_sf, b, b_sf, alpha, m, n, k)
+    err = rel_l2(synth.bf16_bits_to_f32(got), synth.bf16_bits_to_f32(want))
+    assert err <= 1e-2, err
+
+
+def test_w4a4_known_answer_132_and_alpha_zero(backend):
+    # kernels-cuda/smoke.cu:2140-2180
+    k = m = 128
+    x = to_dev(synth.f32_to_bf16_bits(np.ones((1, k), dtype=np.float32)))
+    fp4, sf, _ = backend.nvfp4_quantize_rows(x)
+    a = torch.full((m, k // 2), 0x22, dtype=torch.uint8, device="cuda")
+    a_sf = torch.full((m * k // 16,), 0x38, dtype=torch.uint8, device="cuda")
+    out = torch.empty((1, m), dtype=torch.bfloat16, device="cuda")
+    assert backend.nvfp4_gemm_raw(a, a_sf, fp4, sf, 1.0, m, 1, k, out) == abi.SUCCESS
+    assert torch.all(out.float() == 132.0)
+    assert backend.nvfp4_gemm_raw(a, a_sf, fp4, sf, 0.0, m, 1, k, out) == abi.SUCCESS      # alpha 0 -> 1
+    assert torch.all(out.float() == 132.0)
+
+
+def test_quantise_then_gemm_end_to_end(backend):
+    """The prefill chain on the device: quantize_rows -> nvfp4_gemm, against oracle of the same chain."""
+    rng = np.random.default_rng(2024)
+    m, n, k = 512, 160, 1024
+    packed, sf_rm, a_sf = make_weight(rng, m, k)
+    x = synth.activations(rng, n, k, outlier_frac=0.01)
+    fp4, sf, ts = backend.nvfp4_quantize_rows(to_dev(x), 0.37)
+    alpha = synth.WEIGHT_GLOBAL_SCALE * float(ts.item())
+    got = bf16_host(backend.nvfp4_gemm(to_dev(packed), to_dev(a_sf), fp4, sf, alpha, m, n, k))
+    b, b_sf, ts_o = orc.nvfp4_quantize_rows(x, 0.37)
+    want = orc.nvfp4_gemm(packed, a_sf, b, b_sf, synth.WEIGHT_GLOBAL_SCALE * ts_o, m, n, k)
+    assert rel_l2(synth.bf16_bits_to_f32(got), synth.bf16_bits_to_f32(want)) <= 1e-2

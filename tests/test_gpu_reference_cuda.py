@@ -1,0 +1,124 @@
+"""Pins the CPU oracle to the reference itself: the reference's own CUDA kernels (compiled for
+sm_100a from the reference checkout into oracle/_ref by oracle/Makefile, never copied) run on
+the GPU and their outputs are compared with the oracle on the same seeded inputs.  Skipped when
+that library has not been built.  The reference's sm_120-only decode GEMV is not part of it."""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as orc
+from speedoza_b200 import abi, synth
+from conftest import bf16_host, to_dev
+
+pytestmark = pytest.mark.gpu
+
+REF_SO = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle", "_ref",
+                      "libqwen36_ref.so")
+
+
+@pytest.fixture(scope="module")
+def ref():
+    if not os.path.exists(REF_SO) or not torch.cuda.is_available():
+        pytest.skip("oracle/_ref/libqwen36_ref.so not built")
+    torch.zeros(1, device="cuda")
+    return C.CDLL(REF_SO, mode=os.RTLD_LOCAL | os.RTLD_DEEPBIND)
+
+
+def dp(t):
+    return abi.DevicePtr(0 if t is None else t.data_ptr())
+
+
+def test_reference_quantize_and_retile_equal_oracle(ref):
+    rng = np.random.default_rng(11)
+    x = synth.activations(rng, 37, 5120, outlier_frac=0.01)
+    x[1, :16] = synth.f32_to_bf16_bits(np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 6.0] * 2, np.float32))
+    # amax/6 exactly between subnormal UE4M3 codes (float32 tie behaviour of the encoder)
+    x[2, ::16] = synth.f32_to_bf16_bits(np.resize(np.array([(c + 0.5) * 2.0 ** -9 * 6 for c in range(1, 7)], np.float32), 320))
+    for its in (0.0, 1.25, 0.37):
+        xd = to_dev(x)
+        fp4 = torch.zeros((37, 2560), dtype=torch.uint8, device="cuda")
+        sf = torch.zeros(orc.sf_bytes(320, 37), dtype=torch.uint8, device="cuda")
+        ts = torch.zeros(1, dtype=torch.float32, device="cuda")
+        spec = abi.Nvfp4QuantizeRowsSpec(37, 5120, dp(xd), dp(fp4), dp(sf), dp(ts), its)
+        assert ref.qwen36_nvfp4_quantize_rows(C.byref(spec)) == 0
+        torch.cuda.synchronize()
+        w_fp4, w_sf, w_ts = orc.nvfp4_quantize_rows(x, its)
+        assert np.array_equal(fp4.cpu().numpy(), w_fp4)
+        assert np.array_equal(sf.cpu().numpy(), w_sf)
+        assert ts.item() == np.float32(w_ts)
+    sf_rm = rng.integers(0, 256, size=(300, 13), dtype=np.uint8)
+    out = torch.full((orc.sf_bytes(13, 300),), 0xAA, dtype=torch.uint8, device="cuda")
+    spec = abi.Nvfp4RetileScalesSpec(300, 13, dp(to_dev(sf_rm)), dp(out))
+    assert ref.qwen36_nvfp4_retile_scales(C.byref(spec)) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy(), orc.retile_scales(sf_rm))
+
+
+def test_reference_matvec_equals_oracle_bitwise(ref):
+    rng = np.random.default_rng(12)
+    n, k = 1024, 5120
+    packed, sf_rm = synth.nvfp4_weight(rng, n, k)
+    sf = orc.retile_scales(sf_rm)
+    x = synth.activations(rng, 1, k)[0]
+    ts = torch.tensor([synth.WEIGHT_GLOBAL_SCALE], dtype=torch.float32, device="cuda")
+    y = torch.zeros(n, dtype=torch.bfloat16, device="cuda")
+    spec = abi.Nvfp4MatvecSpec(n, k, dp(to_dev(x)), dp(to_dev(packed)), dp(to_dev(sf)), dp(ts), dp(y))
+    assert ref.qwen36_nvfp4_matvec(C.byref(spec)) == 0
+    torch.cuda.synchronize()
+    want = orc.nvfp4_matvec(x, packed, sf, synth.WEIGHT_GLOBAL_SCALE, k)
+    assert np.array_equal(bf16_host(y), want)      # same summation order, same fused multiply-adds
+
+
+def test_reference_lm_head_equals_oracle_bitwise(ref):
+    rng = np.random.default_rng(13)
+    rows, cols, n = 1500, 5120, 4
+    wb = synth.f32_to_bf16_bits((rng.standard_normal((rows, cols)) * 0.05).astype(np.float32))
+    wd = to_dev(wb)
+    q = torch.zeros((rows, cols), dtype=torch.uint8, device="cuda")
+    s = torch.zeros(rows, dtype=torch.float32, device="cuda")
+    spec = abi.LmHeadFp8QuantizeSpec(rows, cols, dp(wd), dp(q), dp(s))
+    assert ref.qwen36_lm_head_fp8_quantize(C.byref(spec)) == 0
+    torch.cuda.synchronize()
+    oq, os_ = orc.lm_head_fp8_quantize(wb)
+    assert np.array_equal(q.cpu().numpy(), oq) and np.array_equal(s.cpu().numpy().view(np.uint32), os_.view(np.uint32))
+    x = synth.activations(rng, n, cols)
+    y = torch.zeros((n, rows), dtype=torch.bfloat16, device="cuda")
+    spec = abi.LmHeadFp8GemvSpec(rows, cols, n, dp(q), dp(s), dp(to_dev(x)), dp(y))
+    assert ref.qwen36_lm_head_fp8_gemv(C.byref(spec)) == 0
+    torch.cuda.synchronize()
+    want = orc.lm_head_fp8_gemv(oq, os_, x)
+    assert np.array_equal(bf16_host(y), want)
+    tok = torch.zeros(n, dtype=torch.int32, device="cuda")
+    spec = abi.SamplingRowsSpec(n, rows, dp(y), dp(tok), abi.DevicePtr(0), 1.0)
+    assert ref.qwen36_sample_rows(C.byref(spec)) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(tok.cpu().numpy().astype(np.uint32), orc.argmax_rows(want))
+
+
+def test_reference_int8_kv_equals_oracle(ref):
+    rng = np.random.default_rng(14)
+    T = 40
+    q, k, v = synth.qkv(rng, T)
+    kq = torch.zeros((T, 4, 256), dtype=torch.int8, device="cuda"); vq = torch.zeros_like(kq)
+    meta = torch.zeros((T, 4, 2), dtype=torch.float32, device="cuda")
+    shape = abi.AttentionShape(24, 4, 256, 0)
+    kd, vd = to_dev(k), to_dev(v)
+    for t in range(T):
+        spec = abi.TurboquantEncodeSpec(0, t, dp(kd[t]), dp(vd[t]), dp(kq), dp(vq), dp(meta), shape)
+        assert ref.qwen36_turboquant_encode_kv(C.byref(spec)) == 0
+    torch.cuda.synchronize()
+    kq_o = np.zeros((T, 4, 256), np.int8); vq_o = np.zeros_like(kq_o); meta_o = np.zeros((T, 4, 2), np.float32)
+    orc.kv_encode(k, v, 0, kq_o, vq_o, meta_o)
+    assert np.array_equal(kq.cpu().numpy(), kq_o) and np.array_equal(vq.cpu().numpy(), vq_o)
+    assert np.array_equal(meta.cpu().numpy().view(np.uint32), meta_o.view(np.uint32))
+    out = torch.zeros((24, 256), dtype=torch.bfloat16, device="cuda")
+    spec = abi.TurboquantAttentionSpec(0, T - 1, dp(to_dev(q)), dp(kq), dp(vq), dp(meta), dp(out),
+                                       abi.DevicePtr(0), 0, shape, 0)
+    assert ref.qwen36_turboquant_attention(C.byref(spec)) == 0
+    torch.cuda.synchronize()
+    want = synth.bf16_bits_to_f32(orc.kv_attention(q, kq_o, vq_o, meta_o, T - 1)).astype(np.float64)
+    got = synth.bf16_bits_to_f32(bf16_host(out)).astype(np.float64)
+    assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 2e-3     # expf differs by an ulp or two
