@@ -51,6 +51,7 @@ __host__ __device__ static inline size_t sf_bytes(size_t inner_groups, size_t ou
 // (kernels-cuda/ops.cu:39-54): sign honoured, 0x7F and 0xFF are 448.
 __host__ __device__ static inline float decode_e4m3(uint32_t code) {
   const uint32_t e = (code >> 3) & 15u, m = code & 7u;
+  if ((code & 0x7fu) == 0u) return 0.0f;   // 0x80 reads as +0, as in the reference
   float v;
   if (e == 0) {
     v = static_cast<float>(m) * 0x1p-9f;

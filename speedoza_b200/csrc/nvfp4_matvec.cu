@@ -1,21 +1,24 @@
 // W4A16 NVFP4 GEMV: y[row] = bf16( sum_g (sum_{i<16} x[16g+i] * e2m1(w)) * (ue4m3(sf[g,row]) * global) )
 // (semantics of kernels-cuda/ops.cu:547-639 in the reference).
 //
-// HBM-bound weight streaming.  Work unit = a "row quad": rows r, r+32, r+64,
+// HBM-bound weight streaming.  Persistent CTAs; a producer warp drives the TMA
+// engine (descriptor-free cp.async.bulk row segments, mbarrier ring of four
+// 18 KB stages per CTA), so the bytes in flight do not depend on occupancy or
+// registers.  Eight consumer warps each own a "row quad": rows r, r+32, r+64,
 // r+96 of one 128-row block.  Those four rows share one 16-byte word per scale
-// tile (4 rows x 4 groups), so a lane fetches its scales with ONE 16-byte load
-// per 128 weights, and reuses every activation register four times.  Lanes of
-// a warp stride along K with 16-byte weight loads (512 contiguous bytes per
-// row per warp instruction); two iterations of loads stay in flight per lane.
-// Nibbles are expanded by cvt.rn.f16x2.e2m1x2 (two weights per instruction);
-// products accumulate in float32.
+// tile (4 rows x 4 groups), so a lane fetches its scales with ONE 16-byte
+// shared-memory load per 128 weights and reuses every activation register four
+// times.  Lanes stride along K (32 columns each per stage).  Nibbles are
+// expanded by cvt.rn.f16x2.e2m1x2 (two weights per instruction); products
+// accumulate in float32; the lanes of a warp meet in a butterfly once per row.
 //
-// The weight and scale loads of the first iteration are issued before
-// griddepcontrol.wait, so under programmatic dependent launch they overlap
-// the tail of the kernel that produces x.
+// Weights and scales are streamed before griddepcontrol.wait, so under
+// programmatic dependent launch the ring fills while the kernel that produces
+// x is still finishing.
 #include "common.cuh"
 
 #include <atomic>
+#include <cuda.h>
 #include <cuda_fp16.h>
 #include <mutex>
 
@@ -73,73 +76,155 @@ __device__ __forceinline__ void fma_f32x2(float2 &acc, float2 a, float2 b) {
   acc = *reinterpret_cast<float2 *>(&c);
 }
 
-struct Frag {
-  uint4 w[4];   // 32 weights of each of the four rows
-  uint4 s;      // scale bytes [row j][group c] at byte 4*j + c
-};
+// ---- shared-memory ring fed by the TMA engine --------------------------------------------
+//
+// Work unit = 32 rows of one 128-row block: rows r0 + w + 32 j for consumer warp w = 0..7 and
+// j = 0..3 (r0 in {0, 8, 16, 24}).  One pipeline stage = 1024 columns of a unit:
+//   weights  [j][w][512 B]      16 KB : ONE 4-D tiled TMA box over the view
+//                                       [N/128][4][32][K/2 bytes] of the weight matrix
+//   scales   [16 tiles][128 B]   2 KB : ONE 3-D box (128-byte swizzle, so that the 16 tiles a
+//                                       warp reads land on different banks) over the view
+//                                       [N/128][tiles][512 B] of the tiled scale buffer
+// The producer warp's elected lane issues both copies against the stage's "full" mbarrier; the
+// eight consumer warps release a stage through its "empty" mbarrier.  CTAs are persistent:
+// unit = blockIdx.x, += gridDim.x, and the stream of stages runs across unit borders.
+// When N is not a multiple of 128 the tiled views would reach past the allocation, so that
+// (rare) case feeds the same ring with one cp.async.bulk per row segment instead.
+constexpr int kStages = 4;
+constexpr uint32_t kSegBytes = 512;                         // 1024 columns of one row
+constexpr uint32_t kStageW = 32 * kSegBytes;                // 16384
+constexpr uint32_t kStageBytes = kStageW + 2048;            // 18432, a multiple of 1024
+constexpr uint32_t kHeaderBytes = 2048;
+constexpr uint32_t kSpinLimit = 1u << 24;
 
-template <int MODE, int KSPLIT>
-__global__ void __launch_bounds__(kThreads)
-nvfp4_matvec_kernel(const __nv_bfloat16 *__restrict__ x, const uint8_t *__restrict__ weight,
+__device__ unsigned int g_matvec_error = 0;                 // set when a bounded wait gives up
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Bounded wait: gives up after kSpinLimit polls, records it and returns false.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+    uint32_t done;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  atomicExch(&g_matvec_error, 1u);
+  return false;
+}
+__device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tma_load_4d(void *dst, const CUtensorMap *map, uint32_t c0, uint32_t c1, uint32_t c2,
+                                            uint32_t c3, uint64_t *bar) {
+  asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+               ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, uint32_t c0, uint32_t c1, uint32_t c2,
+                                            uint64_t *bar) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+               ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+
+// TMAP: stages are filled by tiled TMA through the two tensor maps (N % 128 == 0); otherwise by
+// per-row cp.async.bulk copies (scales then sit unswizzled).
+template <int MODE, bool TMAP>
+__global__ void __launch_bounds__(kThreads + 32)
+nvfp4_matvec_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_sf,
+                    const __nv_bfloat16 *__restrict__ x, const uint8_t *__restrict__ weight,
                     const uint8_t *__restrict__ sf, const float *__restrict__ tensor_scale,
                     __nv_bfloat16 *__restrict__ y, uint32_t K, uint32_t N) {
-  using xt = typename XT<MODE>::type;
-  extern __shared__ __align__(16) uint8_t smem[];
-  float *lut = reinterpret_cast<float *>(smem);                 // 256 decoded scales * global
-  float *red = lut + 256;                                       // kWarps * 4 partial sums
-  uint32_t *amax_bits = reinterpret_cast<uint32_t *>(red + kWarps * 4);
-  uint4 *xs = reinterpret_cast<uint4 *>(smem + 2048);           // activations, swizzled 16-byte chunks
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  // the swizzled scale boxes need 1024-byte aligned stages
+  uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  float *lut = reinterpret_cast<float *>(smem);                          // 256 decoded scales * global
+  uint64_t *full = reinterpret_cast<uint64_t *>(smem + 1024);            // kStages
+  uint64_t *empty = full + kStages;                                      // kStages
+  uint32_t *amax_bits = reinterpret_cast<uint32_t *>(smem + 1024 + 128);
+  uint8_t *ring = smem + kHeaderBytes;
+  uint4 *xs = reinterpret_cast<uint4 *>(ring + kStages * kStageBytes);   // activations, swizzled chunks
 
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-  constexpr uint32_t kQuadsPerCta = kWarps / KSPLIT;
-  const uint32_t quad = blockIdx.x * kQuadsPerCta + warp / KSPLIT;
-  const uint32_t ks = warp % KSPLIT;
-  const uint32_t rb = quad >> 5, r = quad & 31u;                // 128-row block, row within sub-block
-  const uint32_t row0 = rb * 128u + r;
   const uint32_t iters = (K + 1023u) / 1024u;
   const uint32_t tiles_per_block = (K / 16u + 3u) / 4u;
-  const bool quad_valid = row0 < N;
+  const uint32_t units = ((N + 127u) / 128u) * 4u;
+  const uint32_t row_bytes = K / 2u;
 
-  const uint8_t *wrow[4];
-  bool rvalid[4];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    rvalid[j] = row0 + 32u * j < N;
-    wrow[j] = weight + static_cast<size_t>(row0 + 32u * j) * (K / 2u);
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], kWarps); }
+    *amax_bits = 0u;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  const uint8_t *sfrow = sf + static_cast<size_t>(rb) * tiles_per_block * 512u + r * 16u;
-
-  auto load = [&](Frag &f, uint32_t it) {
-    const uint32_t col = lane * 32u + it * 1024u;
-    if (quad_valid && col < K) {
-#pragma unroll
-      for (int j = 0; j < 4; ++j)
-        f.w[j] = rvalid[j] ? __ldcs(reinterpret_cast<const uint4 *>(wrow[j] + col / 2u)) : make_uint4(0, 0, 0, 0);
-      f.s = __ldcs(reinterpret_cast<const uint4 *>(sfrow + static_cast<size_t>(col / 64u) * 512u));
-    } else {
-#pragma unroll
-      for (int j = 0; j < 4; ++j) f.w[j] = make_uint4(0, 0, 0, 0);
-      f.s = make_uint4(0, 0, 0, 0);
-    }
-  };
-
-  // Scale table and first loads do not depend on the previous kernel.
-  {
+  if (threadIdx.x < 256) {
     const float global = tensor_scale == nullptr ? 1.0f : __ldg(tensor_scale);
     lut[threadIdx.x] = __fmul_rn(q36::decode_e4m3(threadIdx.x), global);
-    if (threadIdx.x == 0) *amax_bits = 0u;
   }
-  Frag cur, nxt;
-  load(cur, ks);
+  __syncthreads();
 
+  if (warp == kWarps) {
+    // ------------------------------------------------------------------ producer warp
+    // Weights and scales do not depend on the kernel that produced x: stream right away.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    uint32_t stage = 0, phase = 0;
+    if (TMAP) {
+      if (lane == 0) {
+        for (uint32_t unit = blockIdx.x; unit < units; unit += gridDim.x) {
+          const uint32_t rb = unit >> 2, r0 = (unit & 3u) * 8u;
+          for (uint32_t it = 0; it < iters; ++it) {
+            if (!mbar_wait(&empty[stage], phase ^ 1u)) return;
+            uint8_t *dst = ring + stage * kStageBytes;
+            mbar_expect_tx(&full[stage], kStageBytes);      // whole boxes, out-of-range columns arrive as zeros
+            tma_load_4d(dst, &map_w, it * 128u, r0, 0u, rb, &full[stage]);
+            tma_load_3d(dst + kStageW, &map_sf, r0 * 4u, it * 16u, rb, &full[stage]);
+            if (++stage == kStages) { stage = 0; phase ^= 1u; }
+          }
+        }
+      }
+      return;
+    }
+    const uint32_t j = lane >> 3, w = lane & 7u;
+    for (uint32_t unit = blockIdx.x; unit < units; unit += gridDim.x) {
+      const uint32_t rb = unit >> 2, r0 = (unit & 3u) * 8u;
+      const uint32_t row = rb * 128u + r0 + w + 32u * j;
+      const bool row_ok = row < N;
+      const uint32_t rows_ok = __popc(__ballot_sync(0xffffffffu, row_ok));
+      const uint8_t *wsrc = weight + static_cast<size_t>(row) * row_bytes;
+      const uint8_t *ssrc = sf + static_cast<size_t>(rb) * tiles_per_block * 512u + r0 * 16u;
+      for (uint32_t it = 0; it < iters; ++it) {
+        if (!mbar_wait(&empty[stage], phase ^ 1u)) return;
+        const uint32_t seg = min(kSegBytes, row_bytes - it * kSegBytes);
+        const uint32_t tiles = min(16u, tiles_per_block - it * 16u);
+        uint8_t *dst = ring + stage * kStageBytes;
+        if (lane == 0) mbar_expect_tx(&full[stage], rows_ok * seg + tiles * 128u);
+        __syncwarp();
+        if (row_ok) bulk_g2s(dst + lane * kSegBytes, wsrc + it * kSegBytes, seg, &full[stage]);
+        if (lane < tiles)
+          bulk_g2s(dst + kStageW + lane * 128u, ssrc + static_cast<size_t>(it * 16u + lane) * 512u, 128u, &full[stage]);
+        if (++stage == kStages) { stage = 0; phase ^= 1u; }
+      }
+    }
+    return;
+  }
+
+  // -------------------------------------------------------------------- consumer warps
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-  // Stage x.  Slot = 32 consecutive activations (what one lane consumes per
-  // iteration); K is a multiple of 32.
+  // Stage x once per CTA.  Slot = 32 consecutive activations (one lane, one iteration).
   int shift = 0;
   if (MODE == 1) {
-    __syncthreads();
     uint32_t m = 0;
     for (uint32_t i = threadIdx.x; i < K / 2u; i += kThreads) {
       const uint32_t v = __ldcg(reinterpret_cast<const uint32_t *>(x) + i);
@@ -147,14 +232,13 @@ nvfp4_matvec_kernel(const __nv_bfloat16 *__restrict__ x, const uint8_t *__restri
     }
     m = __reduce_max_sync(0xffffffffu, m);
     if (lane == 0) atomicMax(amax_bits, m);
-    __syncthreads();
+    asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory");
     const uint32_t e = (*amax_bits >> 7) & 0xffu;
     shift = e == 255u ? 0 : (e < 15u ? 126 : 141 - static_cast<int>(e));
   }
   {
     const float up = __uint_as_float(static_cast<uint32_t>(127 + shift) << 23);
     const uint32_t slots = K / 32u;
-    // one thread converts 8 activations (one 16-byte load) at a time
     for (uint32_t c = threadIdx.x; c < slots * 4u; c += kThreads) {
       const uint4 v = __ldcg(reinterpret_cast<const uint4 *>(x) + c);   // L2 only: x may be fresh from the previous kernel
       const uint32_t slot = c >> 2, sub = c & 3u;
@@ -176,91 +260,89 @@ nvfp4_matvec_kernel(const __nv_bfloat16 *__restrict__ x, const uint8_t *__restri
       }
     }
   }
-  __syncthreads();
+  asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory");
 
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  const float down = __uint_as_float(static_cast<uint32_t>(127 - shift) << 23);
   const uint32_t cbase = 2u * (lane & 1u);       // first of this lane's two groups inside its scale tile
+  uint32_t stage = 0, phase = 0;
 
-  for (uint32_t it = ks; it < iters; it += KSPLIT) {
-    if (it + KSPLIT < iters) load(nxt, it + KSPLIT);
-    const uint32_t slot = lane + it * 32u;
-    if (slot * 32u < K) {
-      const uint32_t sw[4] = {cur.s.x, cur.s.y, cur.s.z, cur.s.w};
+  for (uint32_t unit = blockIdx.x; unit < units; unit += gridDim.x) {
+    const uint32_t row0 = (unit >> 2) * 128u + (unit & 3u) * 8u + warp;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (uint32_t it = 0; it < iters; ++it) {
+      if (!mbar_wait(&full[stage], phase)) return;
+      const uint8_t *st = ring + stage * kStageBytes;
+      const uint32_t slot = lane + it * 32u;
+      if (slot * 32u < K) {
+        uint4 wq[4];
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {          // the two 16-groups of this slot
-        float local[4];
-        if (MODE == 0) {
-          float2 a2[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
-          const uint4 xa = xs[x_chunk<0>(slot, half * 4u + 0u)], xb = xs[x_chunk<0>(slot, half * 4u + 1u)];
-          const uint4 xc = xs[x_chunk<0>(slot, half * 4u + 2u)], xd = xs[x_chunk<0>(slot, half * 4u + 3u)];
-          const float2 xv[8] = {{__uint_as_float(xa.x), __uint_as_float(xa.y)}, {__uint_as_float(xa.z), __uint_as_float(xa.w)},
-                                {__uint_as_float(xb.x), __uint_as_float(xb.y)}, {__uint_as_float(xb.z), __uint_as_float(xb.w)},
-                                {__uint_as_float(xc.x), __uint_as_float(xc.y)}, {__uint_as_float(xc.z), __uint_as_float(xc.w)},
-                                {__uint_as_float(xd.x), __uint_as_float(xd.y)}, {__uint_as_float(xd.z), __uint_as_float(xd.w)}};
+        for (int j = 0; j < 4; ++j) wq[j] = *reinterpret_cast<const uint4 *>(st + (j * 8u + warp) * kSegBytes + lane * 16u);
+        const uint32_t tile = lane >> 1;
+        const uint32_t sf_chunk = TMAP ? (warp ^ (tile & 7u)) : warp;      // 128-byte swizzle of the TMA box
+        const uint4 sq = *reinterpret_cast<const uint4 *>(st + kStageW + tile * 128u + sf_chunk * 16u);
+        const uint32_t sw[4] = {sq.x, sq.y, sq.z, sq.w};
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {          // the two 16-groups of this slot
+          float local[4];
+          if (MODE == 0) {
+            float2 a2[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
+            const uint4 xa = xs[x_chunk<0>(slot, half * 4u + 0u)], xb = xs[x_chunk<0>(slot, half * 4u + 1u)];
+            const uint4 xc = xs[x_chunk<0>(slot, half * 4u + 2u)], xd = xs[x_chunk<0>(slot, half * 4u + 3u)];
+            const float2 xv[8] = {{__uint_as_float(xa.x), __uint_as_float(xa.y)}, {__uint_as_float(xa.z), __uint_as_float(xa.w)},
+                                  {__uint_as_float(xb.x), __uint_as_float(xb.y)}, {__uint_as_float(xb.z), __uint_as_float(xb.w)},
+                                  {__uint_as_float(xc.x), __uint_as_float(xc.y)}, {__uint_as_float(xc.z), __uint_as_float(xc.w)},
+                                  {__uint_as_float(xd.x), __uint_as_float(xd.y)}, {__uint_as_float(xd.z), __uint_as_float(xd.w)}};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t w0 = half == 0 ? wq[j].x : wq[j].z;
+              const uint32_t w1 = half == 0 ? wq[j].y : wq[j].w;
+              uint32_t h[4];
+              e2m1x8_to_h2(w0, h);
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                fma_f32x2(a2[j], __half22float2(*reinterpret_cast<__half2 *>(&h[i])), xv[i]);
+              e2m1x8_to_h2(w1, h);
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                fma_f32x2(a2[j], __half22float2(*reinterpret_cast<__half2 *>(&h[i])), xv[4 + i]);
+              local[j] = a2[j].x + a2[j].y;
+            }
+          } else {
+            const uint4 xa = xs[x_chunk<1>(slot, half * 2u)], xb = xs[x_chunk<1>(slot, half * 2u + 1u)];
+            const uint32_t xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t w0 = half == 0 ? wq[j].x : wq[j].z;
+              const uint32_t w1 = half == 0 ? wq[j].y : wq[j].w;
+              uint32_t h[4];
+              float a = 0.f;
+              e2m1x8_to_h2(w0, h);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) fma_mixed(a, h[i], xv[i]);
+              e2m1x8_to_h2(w1, h);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) fma_mixed(a, h[i], xv[4 + i]);
+              local[j] = a;
+            }
+          }
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            const uint32_t w0 = half == 0 ? cur.w[j].x : cur.w[j].z;
-            const uint32_t w1 = half == 0 ? cur.w[j].y : cur.w[j].w;
-            uint32_t h[4];
-            e2m1x8_to_h2(w0, h);
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-              fma_f32x2(a2[j], __half22float2(*reinterpret_cast<__half2 *>(&h[i])), xv[i]);
-            e2m1x8_to_h2(w1, h);
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-              fma_f32x2(a2[j], __half22float2(*reinterpret_cast<__half2 *>(&h[i])), xv[4 + i]);
-            local[j] = a2[j].x + a2[j].y;
+            const uint32_t code = (sw[j] >> (8u * (cbase + half))) & 0xffu;
+            acc[j] = fmaf(local[j], lut[code], acc[j]);
           }
-        } else {
-          const uint4 xa = xs[x_chunk<1>(slot, half * 2u)], xb = xs[x_chunk<1>(slot, half * 2u + 1u)];
-          const uint32_t xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const uint32_t w0 = half == 0 ? cur.w[j].x : cur.w[j].z;
-            const uint32_t w1 = half == 0 ? cur.w[j].y : cur.w[j].w;
-            uint32_t h[4];
-            float a = 0.f;
-            e2m1x8_to_h2(w0, h);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) fma_mixed(a, h[i], xv[i]);
-            e2m1x8_to_h2(w1, h);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) fma_mixed(a, h[i], xv[4 + i]);
-            local[j] = a;
-          }
-        }
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const uint32_t code = (sw[j] >> (8u * (cbase + half))) & 0xffu;
-          acc[j] = fmaf(local[j], lut[code], acc[j]);
         }
       }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[stage]);
+      if (++stage == kStages) { stage = 0; phase ^= 1u; }
     }
-    cur = nxt;
-  }
-
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < 4; ++j) {
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], off);
-  }
-  const float down = __uint_as_float(static_cast<uint32_t>(127 - shift) << 23);
-  if (KSPLIT == 1) {
-    if (lane < 4 && quad_valid && row0 + 32u * lane < N) {
+      for (int off = 16; off > 0; off >>= 1) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], off);
+    }
+    if (lane < 4 && row0 + 32u * lane < N) {
       const float v = lane == 0 ? acc[0] : lane == 1 ? acc[1] : lane == 2 ? acc[2] : acc[3];
-      y[row0 + 32u * lane] = __float2bfloat16(v * down);
-    }
-  } else {
-    if (lane == 0) {
-#pragma unroll
-      for (int j = 0; j < 4; ++j) red[warp * 4 + j] = acc[j];
-    }
-    __syncthreads();
-    if (ks == 0 && lane < 4 && quad_valid && row0 + 32u * lane < N) {
-      float v = 0.f;
-#pragma unroll
-      for (int k2 = 0; k2 < KSPLIT; ++k2) v += red[(warp + k2) * 4 + lane];
       y[row0 + 32u * lane] = __float2bfloat16(v * down);
     }
   }
@@ -296,22 +378,79 @@ nvfp4_matvec_generic_kernel(const __nv_bfloat16 *__restrict__ x, const uint8_t *
 
 std::atomic<int> g_mode{1};
 
-template <int MODE, int KSPLIT>
-int launch_fast(const qwen36_nvfp4_matvec_spec_t *s) {
+int g_sms = 0;
+int sm_count() {
+  if (g_sms == 0) {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      return 148;
+    g_sms = n;
+  }
+  return g_sms;
+}
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point lookup (no link against libcuda).
+using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                              const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeFn encode_fn() {
+  static EncodeFn fn = [] {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeFn>(p);
+  }();
+  return fn;
+}
+
+bool make_maps(const qwen36_nvfp4_matvec_spec_t *s, CUtensorMap *map_w, CUtensorMap *map_sf) {
+  EncodeFn enc = encode_fn();
+  if (enc == nullptr) return false;
+  const uint64_t K = s->in_features, N = s->out_features;
+  const uint64_t row_bytes = K / 2, blocks = N / 128, tiles = (K / 16 + 3) / 4;
+  const cuuint32_t ones[4] = {1, 1, 1, 1};
+  {   // weights as uint32 [blocks][4][32][K/8]
+    const cuuint64_t dims[4] = {K / 8, 32, 4, blocks};
+    const cuuint64_t strides[3] = {row_bytes, 32 * row_bytes, 128 * row_bytes};
+    const cuuint32_t box[4] = {128, 8, 4, 1};
+    if (enc(map_w, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, reinterpret_cast<void *>(s->weight_u8.ptr), dims, strides, box,
+            ones, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return false;
+  }
+  {   // scales as uint32 [blocks][tiles][128]
+    const cuuint64_t dims[3] = {128, tiles, blocks};
+    const cuuint64_t strides[2] = {512, tiles * 512};
+    const cuuint32_t box[3] = {32, 16, 1};
+    if (enc(map_sf, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, reinterpret_cast<void *>(s->block_scale_e4m3.ptr), dims,
+            strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return false;
+  }
+  return true;
+}
+
+template <int MODE, bool TMAP>
+int launch_kernel(const qwen36_nvfp4_matvec_spec_t *s, const CUtensorMap &map_w, const CUtensorMap &map_sf) {
   const uint32_t K = static_cast<uint32_t>(s->in_features), N = static_cast<uint32_t>(s->out_features);
-  const size_t smem = 2048 + static_cast<size_t>(K) * sizeof(typename XT<MODE>::type);
+  const size_t smem = 1024 + kHeaderBytes + static_cast<size_t>(kStages) * kStageBytes +
+                      static_cast<size_t>(K) * sizeof(typename XT<MODE>::type);
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(nvfp4_matvec_kernel<MODE, KSPLIT>,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    attr_err = cudaFuncSetAttribute(nvfp4_matvec_kernel<MODE, TMAP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    227 * 1024);
   });
   if (attr_err != cudaSuccess) return QWEN36_STATUS_CUDA_ERROR;
-  const uint32_t quads = ((N + 127u) / 128u) * 32u;
-  constexpr uint32_t per_cta = kWarps / KSPLIT;
+  const uint32_t units = ((N + 127u) / 128u) * 4u;
+  const uint32_t per_sm = smem <= 112 * 1024 ? 2u : 1u;
+  const uint32_t cap = static_cast<uint32_t>(sm_count()) * per_sm;
   cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3((quads + per_cta - 1) / per_cta);
-  cfg.blockDim = dim3(kThreads);
+  cfg.gridDim = dim3(units < cap ? units : cap);
+  cfg.blockDim = dim3(kThreads + 32);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = q36::stream();
   cudaLaunchAttribute attr[1];
@@ -320,25 +459,16 @@ int launch_fast(const qwen36_nvfp4_matvec_spec_t *s) {
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   return q36::cuda_status(cudaLaunchKernelEx(
-      &cfg, nvfp4_matvec_kernel<MODE, KSPLIT>, as_ptr<const __nv_bfloat16>(s->input_bf16),
+      &cfg, nvfp4_matvec_kernel<MODE, TMAP>, map_w, map_sf, as_ptr<const __nv_bfloat16>(s->input_bf16),
       as_ptr<const uint8_t>(s->weight_u8), as_ptr<const uint8_t>(s->block_scale_e4m3),
       as_ptr<const float>(s->tensor_scale_f32), as_ptr<__nv_bfloat16>(s->output_bf16), K, N));
 }
 
 template <int MODE>
 int launch_mode(const qwen36_nvfp4_matvec_spec_t *s) {
-  // Aim for at least ~16 warps per SM on a 148-SM part: split K across the
-  // warps of a CTA when there are few row quads.
-  const size_t quads = q36::div_ceil(s->out_features, 128) * 32;
-  const size_t iters = q36::div_ceil(s->in_features, 1024);
-  int ksplit = 1;
-  while (ksplit < 8 && quads * ksplit < 2368 && static_cast<size_t>(ksplit) * 2 <= iters) ksplit *= 2;
-  switch (ksplit) {
-    case 1: return launch_fast<MODE, 1>(s);
-    case 2: return launch_fast<MODE, 2>(s);
-    case 4: return launch_fast<MODE, 4>(s);
-    default: return launch_fast<MODE, 8>(s);
-  }
+  CUtensorMap map_w{}, map_sf{};
+  if (s->out_features % 128 == 0 && make_maps(s, &map_w, &map_sf)) return launch_kernel<MODE, true>(s, map_w, map_sf);
+  return launch_kernel<MODE, false>(s, map_w, map_sf);
 }
 
 }  // namespace
@@ -353,7 +483,7 @@ extern "C" int qwen36_nvfp4_matvec(const qwen36_nvfp4_matvec_spec_t *spec) {
   if (spec->out_features == 0 || spec->in_features == 0 || spec->input_bf16.ptr == 0 ||
       spec->weight_u8.ptr == 0 || spec->block_scale_e4m3.ptr == 0 || spec->output_bf16.ptr == 0)
     return QWEN36_STATUS_INVALID_ARGUMENT;
-  const bool fast = spec->in_features % 32 == 0 && spec->in_features <= 48 * 1024 &&
+  const bool fast = spec->in_features % 32 == 0 && spec->in_features <= 32 * 1024 &&
                     spec->out_features < (1u << 31) &&
                     ((spec->input_bf16.ptr | spec->weight_u8.ptr | spec->block_scale_e4m3.ptr) & 15u) == 0;
   if (!fast) {
