@@ -1,7 +1,376 @@
+// W4A4 NVFP4 product on the 5th-generation tensor cores:
+//   c[token][row] = bf16( alpha * sum_k e2m1(a[row,k]) * ue4m3(sfa) * e2m1(b[token,k]) * ue4m3(sfb) )
+// tcgen05.mma kind::mxf4nvf4 with 16-element block scales, accumulators in TMEM.
+//
+// Tile: 128 weight rows (MMA M, TMEM lanes) x BN tokens (MMA N, TMEM columns) x 256 K per
+// pipeline stage (four K=64 MMAs).  Per stage the TMA engine brings
+//   A  : 128 rows x 128 bytes of packed weights      (2-D tiled TMA, 128-byte swizzle)
+//   B  : BN tokens x 128 bytes of packed activations (2-D tiled TMA, 128-byte swizzle)
+//   SFA: 2 KB  = four 512-byte scale tiles of the 128-row block   (1-D bulk copy)
+//   SFB: 2 KB per 128 tokens                                      (1-D bulk copy)
+// The 512-byte scale tile of the caller's layout (32 x 16 bytes: row r at (r%32)*16 + (r/32)*4)
+// is exactly the shared-memory image that tcgen05.cp 32x128b.warpx4 turns into the TMEM
+// scale operand, so scales go HBM -> smem -> TMEM without being touched by a thread.
+//
+// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM allocator + MMA issuer,
+// warps 2..5 = epilogue (TMEM -> registers -> alpha, bf16 -> global).  CTAs are persistent over
+// (row block, token block) tiles; with two accumulator stages the epilogue of one tile overlaps
+// the MMAs of the next.  No cluster, no multicast: every CTA loads its own tiles.
+//
+// Every mbarrier wait is bounded; a wait that gives up sets g_gemm_error, and all roles fall
+// through to the common exit where TMEM is released.
 #include "nvfp4_gemm_tc.cuh"
+
+#include <cuda.h>
+#include <mutex>
+
 namespace q36 {
-int nvfp4_gemm_tc(const qwen36_nvfp4_gemm_spec_t *spec, float alpha) {
-  (void)spec; (void)alpha;
-  return QWEN36_STATUS_NOT_IMPLEMENTED;
+namespace {
+
+constexpr uint32_t kThreads = 192;
+constexpr uint32_t kBM = 128;
+constexpr uint32_t kBKBytes = 128;            // 256 fp4 values
+constexpr uint32_t kSpinLimit = 1u << 26;
+
+__device__ unsigned int g_gemm_error = 0;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
 }
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+    uint32_t done;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  atomicExch(&g_gemm_error, 1u);
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, uint32_t c0, uint32_t c1, uint64_t *bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+               ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+// Shared-memory matrix descriptor, K-major operand tile with 128-byte swizzle: rows of 128 bytes,
+// 8-row groups 1024 bytes apart.  Bits: [0,14) start >> 4, [16,30) leading offset >> 4 (unused
+// for swizzled K-major, set to 1), [32,46) stride offset >> 4 = 64, [46,48) version = 1,
+// [61,64) layout = 2 (128-byte swizzle).
+__device__ __forceinline__ uint64_t desc_sw128(uint32_t smem_addr) {
+  return static_cast<uint64_t>((smem_addr & 0x3ffffu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// Descriptor of one 512-byte scale tile for tcgen05.cp: no swizzle, 8 rows x 16 bytes per core
+// matrix, core matrices 128 bytes apart.
+__device__ __forceinline__ uint64_t desc_sf(uint32_t smem_addr) {
+  return static_cast<uint64_t>((smem_addr & 0x3ffffu) >> 4) | (8ull << 32) | (1ull << 46);
+}
+
+__device__ __forceinline__ void tmem_cp_sf(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+__device__ __forceinline__ void mma_mxf4nvf4(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+               ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem) : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint64_t *bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+               "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+               "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                 "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                 "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+               : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr));
+}
+
+template <uint32_t BN> struct Cfg {
+  static constexpr uint32_t kSfbTiles = (BN + 127) / 128;              // 512-byte scale tiles per K=64 for B
+  static constexpr uint32_t kBRows = BN < 8 ? 8 : BN;
+  static constexpr uint32_t kABytes = kBM * kBKBytes;                  // 16384
+  static constexpr uint32_t kBBytes = ((kBRows * kBKBytes + 1023) / 1024) * 1024;
+  static constexpr uint32_t kSfaBytes = 2048;
+  static constexpr uint32_t kSfbBytes = 2048 * kSfbTiles;
+  static constexpr uint32_t kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
+  static constexpr uint32_t kStages = BN >= 256 ? 3 : (BN >= 128 ? 5 : 6);
+  static constexpr uint32_t kAccStages = BN >= 256 ? 1 : 2;
+  static constexpr uint32_t kAccCols = BN < 32 ? 32 : BN;              // columns reserved per accumulator stage
+  static constexpr uint32_t kSfCols = 16 + 16 * kSfbTiles;             // per smem stage: SFA 4x4, SFB 4x4 per 128 tokens
+  static constexpr uint32_t kTmemUsed = kAccStages * kAccCols + kStages * kSfCols;
+  static constexpr uint32_t kTmemCols = kTmemUsed <= 32 ? 32 : kTmemUsed <= 64 ? 64 : kTmemUsed <= 128 ? 128
+                                        : kTmemUsed <= 256 ? 256 : 512;
+  static_assert(kTmemUsed <= 512, "TMEM budget");
+  static constexpr uint32_t kSmemBytes = 1024 /*align slack*/ + 1024 /*barriers*/ + kStages * kStageBytes;
+  static constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | ((kBRows >> 3) << 17) | ((kBM >> 4) << 24);
+};
+
+// Tiles are numbered with the row block fastest, so that CTAs running at the same time share
+// the activation tile (L2) while each streams its own weight rows.
+template <uint32_t BN>
+__global__ void __launch_bounds__(kThreads, 1)
+nvfp4_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                     const uint8_t *__restrict__ a_sf, const uint8_t *__restrict__ b_sf,
+                     __nv_bfloat16 *__restrict__ c, uint32_t m, uint32_t n, uint32_t k, float alpha) {
+  using C = Cfg<BN>;
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint64_t *full = reinterpret_cast<uint64_t *>(smem);                   // [kStages]
+  uint64_t *empty = full + 8;                                            // [kStages]
+  uint64_t *acc_full = empty + 8;                                        // [kAccStages]
+  uint64_t *acc_empty = acc_full + 2;                                    // [kAccStages]
+  uint32_t *tmem_base_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
+  uint8_t *stages = smem + 1024;
+
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+  const uint32_t m_blocks = m / kBM, n_blocks = (n + BN - 1) / BN;
+  const uint32_t tiles = m_blocks * n_blocks;
+  const uint32_t k_blocks = k / 256u;
+  const uint32_t sf_tiles_per_block = k / 64u;                           // 512-byte tiles per 128 rows
+  const uint32_t sf_tok_blocks = (n + 127u) / 128u;                      // 128-token scale blocks that exist
+
+  if (threadIdx.x == 0) {
+    for (uint32_t s = 0; s < C::kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (uint32_t s = 0; s < C::kAccStages; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 4); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_base_slot)), "r"(C::kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_base_slot;
+  const uint32_t tmem_sf = tmem_base + C::kAccStages * C::kAccCols;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      uint32_t g = 0;
+      bool dead = false;
+      for (uint32_t tile = blockIdx.x; tile < tiles && !dead; tile += gridDim.x) {
+        const uint32_t mb = tile % m_blocks, nb = tile / m_blocks;
+        for (uint32_t kb = 0; kb < k_blocks; ++kb, ++g) {
+          const uint32_t s = g % C::kStages, ph = (g / C::kStages) & 1u;
+          if (!mbar_wait(&empty[s], ph ^ 1u)) { dead = true; break; }
+          uint8_t *st = stages + s * C::kStageBytes;
+          // scale tiles of token blocks past the end of the activation tensor do not exist in
+          // the caller's buffer: they are skipped (their columns are never stored)
+          uint32_t sfb_tiles = 0;
+#pragma unroll
+          for (uint32_t t = 0; t < C::kSfbTiles; ++t)
+            if ((static_cast<size_t>(nb) * BN) / 128u + t < sf_tok_blocks) ++sfb_tiles;
+          mbar_expect_tx(&full[s], C::kABytes + C::kBRows * kBKBytes + C::kSfaBytes + sfb_tiles * 2048u);
+          tma_load_2d(st, &map_a, kb * kBKBytes, mb * kBM, &full[s]);
+          tma_load_2d(st + C::kABytes, &map_b, kb * kBKBytes, nb * BN, &full[s]);
+          bulk_g2s(st + C::kABytes + C::kBBytes, a_sf + (static_cast<size_t>(mb) * sf_tiles_per_block + kb * 4u) * 512u,
+                   2048u, &full[s]);
+#pragma unroll
+          for (uint32_t t = 0; t < C::kSfbTiles; ++t) {
+            const size_t tok_block = (static_cast<size_t>(nb) * BN) / 128u + t;
+            if (tok_block < sf_tok_blocks)
+              bulk_g2s(st + C::kABytes + C::kBBytes + C::kSfaBytes + t * 2048u,
+                       b_sf + (tok_block * sf_tiles_per_block + kb * 4u) * 512u, 2048u, &full[s]);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      uint32_t g = 0, t_local = 0;
+      bool dead = false;
+      for (uint32_t tile = blockIdx.x; tile < tiles && !dead; tile += gridDim.x, ++t_local) {
+        const uint32_t as = t_local % C::kAccStages, aph = (t_local / C::kAccStages) & 1u;
+        if (!mbar_wait(&acc_empty[as], aph ^ 1u)) { dead = true; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t d_tmem = tmem_base + as * C::kAccCols;
+        for (uint32_t kb = 0; kb < k_blocks; ++kb, ++g) {
+          const uint32_t s = g % C::kStages, ph = (g / C::kStages) & 1u;
+          if (!mbar_wait(&full[s], ph)) { dead = true; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t st = smem_u32(stages + s * C::kStageBytes);
+          const uint32_t sfa_t = tmem_sf + s * C::kSfCols, sfb_t = sfa_t + 16u;
+#pragma unroll
+          for (uint32_t kk = 0; kk < 4; ++kk) {
+            tmem_cp_sf(sfa_t + kk * 4u, desc_sf(st + C::kABytes + C::kBBytes + kk * 512u));
+#pragma unroll
+            for (uint32_t t = 0; t < C::kSfbTiles; ++t)
+              tmem_cp_sf(sfb_t + (kk * C::kSfbTiles + t) * 4u,
+                         desc_sf(st + C::kABytes + C::kBBytes + C::kSfaBytes + t * 2048u + kk * 512u));
+          }
+#pragma unroll
+          for (uint32_t kk = 0; kk < 4; ++kk)
+            mma_mxf4nvf4(d_tmem, desc_sw128(st + kk * 32u), desc_sw128(st + C::kABytes + kk * 32u), C::kIdesc,
+                         sfa_t + kk * 4u, sfb_t + kk * C::kSfbTiles * 4u, (kb | kk) != 0u);
+          mma_commit(&empty[s]);                 // frees the smem stage once these MMAs have read it
+        }
+        if (!dead) mma_commit(&acc_full[as]);    // accumulator complete
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue warps 2..5
+    const uint32_t quarter = warp & 3u;           // TMEM lanes [32*quarter, +32) are this warp's
+    uint32_t t_local = 0;
+    bool dead = false;
+    for (uint32_t tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++t_local) {
+      const uint32_t mb = tile % m_blocks, nb = tile / m_blocks;
+      const uint32_t as = t_local % C::kAccStages, aph = (t_local / C::kAccStages) & 1u;
+      if (!dead && !mbar_wait(&acc_full[as], aph)) dead = true;
+      if (dead) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t row = mb * kBM + quarter * 32u + lane;           // feature index
+      const uint32_t taddr = tmem_base + as * C::kAccCols + ((quarter * 32u) << 16);
+      const uint32_t tok0 = nb * BN;
+      if constexpr (BN >= 32) {
+#pragma unroll 1
+        for (uint32_t c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld32(taddr + c0, r);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          // Lane pairs swap so that the even lane holds features (f, f+1) of token t and the odd
+          // lane those of token t+1: 4-byte stores, 64 contiguous bytes per token per warp.
+#pragma unroll
+          for (uint32_t j = 0; j < 32; j += 2) {
+            const float mine_a = __uint_as_float(r[j]) * alpha, mine_b = __uint_as_float(r[j + 1]) * alpha;
+            const float send = (lane & 1u) ? mine_a : mine_b;
+            const float got = __shfl_xor_sync(0xffffffffu, send, 1);
+            const uint32_t tok = tok0 + c0 + j + (lane & 1u);
+            const __nv_bfloat162 v = (lane & 1u) ? __floats2bfloat162_rn(got, mine_b) : __floats2bfloat162_rn(mine_a, got);
+            if (tok < n) *reinterpret_cast<__nv_bfloat162 *>(c + static_cast<size_t>(tok) * m + (row & ~1u)) = v;
+          }
+        }
+      } else {
+        uint32_t r[8];
+#pragma unroll 1
+        for (uint32_t c0 = 0; c0 < C::kBRows; c0 += 8) {
+          tmem_ld8(taddr + c0, r);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+          for (uint32_t j = 0; j < 8; ++j) {
+            const uint32_t tok = tok0 + c0 + j;
+            if (tok < n) c[static_cast<size_t>(tok) * m + row] = __float2bfloat16(__uint_as_float(r[j]) * alpha);
+          }
+        }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[as]);
+    }
+  }
+
+  // Common exit: everyone meets, then the allocating warp releases TMEM.
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::kTmemCols) : "memory");
+  }
+}
+
+using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                              const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeFn encode_fn() {
+  static EncodeFn fn = [] {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeFn>(p);
+  }();
+  return fn;
+}
+
+// Packed fp4 bytes [rows][k/2] -> 2-D map, box = 128 bytes x box_rows, 128-byte swizzle.
+bool make_operand_map(CUtensorMap *map, uint64_t ptr, uint64_t rows, uint64_t k, uint32_t box_rows) {
+  EncodeFn enc = encode_fn();
+  if (enc == nullptr) return false;
+  const cuuint64_t dims[2] = {k / 2, rows};
+  const cuuint64_t strides[1] = {k / 2};
+  const cuuint32_t box[2] = {kBKBytes, box_rows};
+  const cuuint32_t ones[2] = {1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, reinterpret_cast<void *>(ptr), dims, strides, box, ones,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int sm_count() {
+  static int n = [] {
+    int dev = 0, v = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0)
+      return 148;
+    return v;
+  }();
+  return n;
+}
+
+template <uint32_t BN>
+int launch(const qwen36_nvfp4_gemm_spec_t *s, float alpha) {
+  using C = Cfg<BN>;
+  CUtensorMap map_a, map_b;
+  if (!make_operand_map(&map_a, s->a_fp4.ptr, s->m, s->k, kBM) ||
+      !make_operand_map(&map_b, s->b_fp4.ptr, s->n, s->k, C::kBRows))
+    return QWEN36_STATUS_NOT_IMPLEMENTED;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(nvfp4_gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    static_cast<int>(C::kSmemBytes));
+  });
+  if (attr_err != cudaSuccess) return QWEN36_STATUS_CUDA_ERROR;
+  const uint32_t tiles = static_cast<uint32_t>((s->m / kBM) * ((s->n + BN - 1) / BN));
+  const uint32_t grid = tiles < static_cast<uint32_t>(sm_count()) ? tiles : static_cast<uint32_t>(sm_count());
+  nvfp4_gemm_tc_kernel<BN><<<grid, kThreads, C::kSmemBytes, q36::stream()>>>(
+      map_a, map_b, as_ptr<const uint8_t>(s->a_scale), as_ptr<const uint8_t>(s->b_scale),
+      as_ptr<__nv_bfloat16>(s->c_bf16), static_cast<uint32_t>(s->m), static_cast<uint32_t>(s->n),
+      static_cast<uint32_t>(s->k), alpha);
+  return q36::launch_status();
+}
+
+}  // namespace
+
+int nvfp4_gemm_tc(const qwen36_nvfp4_gemm_spec_t *s, float alpha) {
+  if (s->m % kBM != 0 || s->k % 256 != 0 || s->m > (1u << 30) || s->n > (1u << 30) || s->k > (1u << 30) ||
+      ((s->a_fp4.ptr | s->b_fp4.ptr | s->a_scale.ptr | s->b_scale.ptr) & 15u) != 0 || (s->c_bf16.ptr & 3u) != 0)
+    return QWEN36_STATUS_NOT_IMPLEMENTED;
+  if (s->n <= 8) return launch<8>(s, alpha);
+  if (s->n <= 16) return launch<16>(s, alpha);
+  if (s->n <= 32) return launch<32>(s, alpha);
+  if (s->n <= 64) return launch<64>(s, alpha);
+  if (s->n <= 128) return launch<128>(s, alpha);
+  return launch<256>(s, alpha);
+}
+
+// 1 when a bounded wait inside the tensor-core GEMM ever gave up.  Synchronises.
+extern "C" int qwen36_nvfp4_gemm_last_error(void) {
+  unsigned int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_gemm_error, sizeof(v)) != cudaSuccess) return -1;
+  return static_cast<int>(v);
+}
+
 }  // namespace q36

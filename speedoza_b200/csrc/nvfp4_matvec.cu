@@ -29,21 +29,11 @@ using q36::as_ptr;
 constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
 
-// How activations are held in shared memory / multiplied:
-//   0: float32, one fma.rn.f32x2 per weight pair (exact products).
-//   1: float16 scaled by a power of two so that max|x| lands in [2^14, 2^15),
-//      one mixed-precision fma.rn.f32.f16 per weight (exact products; values
-//      below max|x| * 2^-38 flush, far below float32 accumulation error).
-template <int MODE> struct XT;
-template <> struct XT<0> { using type = float; };
-template <> struct XT<1> { using type = __half; };
-
-// 16-byte chunk swizzle of the activation buffer so that the eight lanes of a
-// quarter warp, which read chunks that are a whole number of 128-byte rows
-// apart, land on distinct bank groups.
-template <int MODE> __device__ __forceinline__ uint32_t x_chunk(uint32_t lane_slot, uint32_t i) {
-  if (MODE == 0) return lane_slot * 8u + (i ^ (lane_slot & 7u));             // 8 chunks per slot
-  return lane_slot * 4u + (i ^ ((lane_slot >> 1) & 3u));                      // 4 chunks per slot
+// 16-byte chunk swizzle of the activation buffer (float16, four chunks per 32-value slot) so
+// that the eight lanes of a quarter warp, which read chunks 64 bytes apart, land on distinct
+// bank groups.
+__device__ __forceinline__ uint32_t x_chunk(uint32_t slot, uint32_t i) {
+  return slot * 4u + (i ^ ((slot >> 1) & 3u));
 }
 
 __device__ __forceinline__ void e2m1x8_to_h2(uint32_t w, uint32_t (&h)[4]) {
@@ -57,47 +47,42 @@ __device__ __forceinline__ void e2m1x8_to_h2(uint32_t w, uint32_t (&h)[4]) {
       : "r"(w));
 }
 
-// acc += w.lo * x.lo + w.hi * x.hi, float16 operands, float32 accumulate.
-__device__ __forceinline__ void fma_mixed(float &acc, uint32_t w_h2, uint32_t x_h2) {
+// even += w.lo * x.lo ; odd += w.hi * x.hi : float16 operands, float32 accumulate, products exact.
+__device__ __forceinline__ void fma_mixed_eo(float &even, float &odd, uint32_t w_h2, uint32_t x_h2) {
   asm("{\n\t.reg .f16 wl, wh, xl, xh;\n\t"
-      "mov.b32 {wl, wh}, %1;\n\t"
-      "mov.b32 {xl, xh}, %2;\n\t"
+      "mov.b32 {wl, wh}, %2;\n\t"
+      "mov.b32 {xl, xh}, %3;\n\t"
       "fma.rn.f32.f16 %0, wl, xl, %0;\n\t"
-      "fma.rn.f32.f16 %0, wh, xh, %0;\n\t}"
-      : "+f"(acc)
+      "fma.rn.f32.f16 %1, wh, xh, %1;\n\t}"
+      : "+f"(even), "+f"(odd)
       : "r"(w_h2), "r"(x_h2));
-}
-
-__device__ __forceinline__ void fma_f32x2(float2 &acc, float2 a, float2 b) {
-  unsigned long long c = *reinterpret_cast<unsigned long long *>(&acc);
-  asm("fma.rn.f32x2 %0, %1, %2, %0;"
-      : "+l"(c)
-      : "l"(*reinterpret_cast<unsigned long long *>(&a)), "l"(*reinterpret_cast<unsigned long long *>(&b)));
-  acc = *reinterpret_cast<float2 *>(&c);
 }
 
 // ---- shared-memory ring fed by the TMA engine --------------------------------------------
 //
-// Work unit = 32 rows of one 128-row block: rows r0 + w + 32 j for consumer warp w = 0..7 and
-// j = 0..3 (r0 in {0, 8, 16, 24}).  One pipeline stage = 1024 columns of a unit:
-//   weights  [j][w][512 B]      16 KB : ONE 4-D tiled TMA box over the view
-//                                       [N/128][4][32][K/2 bytes] of the weight matrix
-//   scales   [16 tiles][128 B]   2 KB : ONE 3-D box (128-byte swizzle, so that the 16 tiles a
-//                                       warp reads land on different banks) over the view
-//                                       [N/128][tiles][512 B] of the tiled scale buffer
+// QUADS (8, 4, 2 or 1) row quads form a work unit: rows r0 + q + 32 j of one 128-row block,
+// q < QUADS, j < 4.  Consumer warp w serves quad w % QUADS and K-part w / QUADS: with fewer
+// quads per unit the eight warps split K between them (stage s of a unit belongs to K-part
+// s % KPARTS), so small matrices still spread over every SM.  One pipeline stage = 1024
+// columns of a unit:
+//   weights  [j][q][512 B]        : ONE 4-D tiled TMA box over the view
+//                                   [N/128][4][32][K/2 bytes] of the weight matrix
+//   scales   [16 tiles][QUADS*16 B]: ONE 3-D box over the view [N/128][tiles][512 B] of the tiled
+//                                   scale buffer (128-byte swizzle when QUADS == 8, so that the
+//                                   16 tiles a warp reads land on different banks)
 // The producer warp's elected lane issues both copies against the stage's "full" mbarrier; the
-// eight consumer warps release a stage through its "empty" mbarrier.  CTAs are persistent:
-// unit = blockIdx.x, += gridDim.x, and the stream of stages runs across unit borders.
+// QUADS warps that read a stage release it through its "empty" mbarrier.  CTAs are persistent:
+// unit = blockIdx.x, += gridDim.x, and the stream of stages runs across unit borders.  The ring
+// always holds 72 KB (32 / QUADS stages).
 // When N is not a multiple of 128 the tiled views would reach past the allocation, so that
-// (rare) case feeds the same ring with one cp.async.bulk per row segment instead.
-constexpr int kStages = 4;
+// (rare) case feeds the same ring (QUADS = 8) with one cp.async.bulk per row segment instead.
 constexpr uint32_t kSegBytes = 512;                         // 1024 columns of one row
-constexpr uint32_t kStageW = 32 * kSegBytes;                // 16384
-constexpr uint32_t kStageBytes = kStageW + 2048;            // 18432, a multiple of 1024
+constexpr uint32_t kRingBytes = 32u * (4u * kSegBytes + 256u);   // 73728
 constexpr uint32_t kHeaderBytes = 2048;
 constexpr uint32_t kSpinLimit = 1u << 24;
 
-__device__ unsigned int g_matvec_error = 0;                 // set when a bounded wait gives up
+__device__ unsigned int g_matvec_error = 0;
+__device__ unsigned int g_prefetch_distance = 8;            // stages of L2 prefetch ahead of the ring                 // set when a bounded wait gives up
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -126,7 +111,6 @@ __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t by
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
-
 __device__ __forceinline__ void tma_load_4d(void *dst, const CUtensorMap *map, uint32_t c0, uint32_t c1, uint32_t c2,
                                             uint32_t c3, uint64_t *bar) {
   asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
@@ -138,32 +122,52 @@ __device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, u
                ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
 
-// TMAP: stages are filled by tiled TMA through the two tensor maps (N % 128 == 0); otherwise by
-// per-row cp.async.bulk copies (scales then sit unswizzled).
-template <int MODE, bool TMAP>
+// L2 prefetch of a tile (no shared memory involved): lets the producer run further ahead of the
+// ring than shared memory alone allows, so HBM latency under load is hidden by L2.
+__device__ __forceinline__ void tma_prefetch_4d(const CUtensorMap *map, uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3) {
+  asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];"
+               ::"l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap *map, uint32_t c0, uint32_t c1, uint32_t c2) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];"
+               ::"l"(map), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+
+// TMAP: stages are filled by tiled TMA through the two tensor maps (N % 128 == 0); otherwise
+// (QUADS == 8 only) by per-row cp.async.bulk copies.
+template <int QUADS, bool TMAP>
 __global__ void __launch_bounds__(kThreads + 32)
 nvfp4_matvec_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_sf,
                     const __nv_bfloat16 *__restrict__ x, const uint8_t *__restrict__ weight,
                     const uint8_t *__restrict__ sf, const float *__restrict__ tensor_scale,
                     __nv_bfloat16 *__restrict__ y, uint32_t K, uint32_t N) {
+  constexpr uint32_t kStages = 32u / QUADS;                 // 4, 8, 16, 32
+  constexpr uint32_t KPARTS = kWarps / QUADS;               // warps that split K of one quad
+  constexpr uint32_t kStageW = QUADS * 4u * kSegBytes;
+  constexpr uint32_t kSfRow = QUADS * 16u;                  // bytes of one scale tile kept per stage
+  constexpr uint32_t kStageBytes = kStageW + 16u * kSfRow;
+  constexpr uint32_t kUnitsPerBlock = 32u / QUADS;
+  static_assert(kStages * kStageBytes == kRingBytes, "ring size");
+
   extern __shared__ __align__(128) uint8_t smem_raw[];
   // the swizzled scale boxes need 1024-byte aligned stages
   uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   float *lut = reinterpret_cast<float *>(smem);                          // 256 decoded scales * global
-  uint64_t *full = reinterpret_cast<uint64_t *>(smem + 1024);            // kStages
-  uint64_t *empty = full + kStages;                                      // kStages
-  uint32_t *amax_bits = reinterpret_cast<uint32_t *>(smem + 1024 + 128);
+  uint64_t *full = reinterpret_cast<uint64_t *>(smem + 1024);            // kStages (<= 32)
+  uint64_t *empty = full + 32;
+  uint32_t *amax_bits = reinterpret_cast<uint32_t *>(smem + 1024 + 512);
+  float *red = reinterpret_cast<float *>(smem + 1024 + 512 + 16);        // [2][kWarps][4] K-part sums
   uint8_t *ring = smem + kHeaderBytes;
-  uint4 *xs = reinterpret_cast<uint4 *>(ring + kStages * kStageBytes);   // activations, swizzled chunks
+  uint4 *xs = reinterpret_cast<uint4 *>(ring + kRingBytes);              // activations, swizzled chunks
 
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
   const uint32_t iters = (K + 1023u) / 1024u;
   const uint32_t tiles_per_block = (K / 16u + 3u) / 4u;
-  const uint32_t units = ((N + 127u) / 128u) * 4u;
+  const uint32_t units = ((N + 127u) / 128u) * kUnitsPerBlock;
   const uint32_t row_bytes = K / 2u;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], kWarps); }
+    for (uint32_t s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], QUADS); }
     *amax_bits = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -177,24 +181,37 @@ nvfp4_matvec_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     // ------------------------------------------------------------------ producer warp
     // Weights and scales do not depend on the kernel that produced x: stream right away.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    uint32_t stage = 0, phase = 0;
+    uint32_t g = 0;                                          // running stage number
     if (TMAP) {
       if (lane == 0) {
+        // Two cursors over the same (unit, stage) sequence: `pf` runs kPrefetch stages ahead of
+        // `ld` and only asks L2 to fetch the tiles; `ld` fills the ring.
+        const uint32_t kPrefetch = g_prefetch_distance;
+        uint32_t pf_unit = blockIdx.x, pf_it = 0;
+        auto prefetch_one = [&]() {
+          if (pf_unit >= units) return;
+          const uint32_t rb = pf_unit / kUnitsPerBlock, r0 = (pf_unit % kUnitsPerBlock) * QUADS;
+          tma_prefetch_4d(&map_w, pf_it * 128u, r0, 0u, rb);
+          tma_prefetch_3d(&map_sf, r0 * 4u, pf_it * 16u, rb);
+          if (++pf_it == iters) { pf_it = 0; pf_unit += gridDim.x; }
+        };
+        for (uint32_t i = 0; i < kStages + kPrefetch; ++i) prefetch_one();
         for (uint32_t unit = blockIdx.x; unit < units; unit += gridDim.x) {
-          const uint32_t rb = unit >> 2, r0 = (unit & 3u) * 8u;
-          for (uint32_t it = 0; it < iters; ++it) {
+          const uint32_t rb = unit / kUnitsPerBlock, r0 = (unit % kUnitsPerBlock) * QUADS;
+          for (uint32_t it = 0; it < iters; ++it, ++g) {
+            const uint32_t stage = g % kStages, phase = (g / kStages) & 1u;
             if (!mbar_wait(&empty[stage], phase ^ 1u)) return;
             uint8_t *dst = ring + stage * kStageBytes;
-            mbar_expect_tx(&full[stage], kStageBytes);      // whole boxes, out-of-range columns arrive as zeros
+            mbar_expect_tx(&full[stage], kStageBytes);      // whole boxes; out-of-range columns arrive as zeros
             tma_load_4d(dst, &map_w, it * 128u, r0, 0u, rb, &full[stage]);
             tma_load_3d(dst + kStageW, &map_sf, r0 * 4u, it * 16u, rb, &full[stage]);
-            if (++stage == kStages) { stage = 0; phase ^= 1u; }
+            prefetch_one();
           }
         }
       }
       return;
     }
-    const uint32_t j = lane >> 3, w = lane & 7u;
+    const uint32_t j = lane >> 3, w = lane & 7u;            // QUADS == 8 here
     for (uint32_t unit = blockIdx.x; unit < units; unit += gridDim.x) {
       const uint32_t rb = unit >> 2, r0 = (unit & 3u) * 8u;
       const uint32_t row = rb * 128u + r0 + w + 32u * j;
@@ -202,7 +219,8 @@ nvfp4_matvec_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       const uint32_t rows_ok = __popc(__ballot_sync(0xffffffffu, row_ok));
       const uint8_t *wsrc = weight + static_cast<size_t>(row) * row_bytes;
       const uint8_t *ssrc = sf + static_cast<size_t>(rb) * tiles_per_block * 512u + r0 * 16u;
-      for (uint32_t it = 0; it < iters; ++it) {
+      for (uint32_t it = 0; it < iters; ++it, ++g) {
+        const uint32_t stage = g % kStages, phase = (g / kStages) & 1u;
         if (!mbar_wait(&empty[stage], phase ^ 1u)) return;
         const uint32_t seg = min(kSegBytes, row_bytes - it * kSegBytes);
         const uint32_t tiles = min(16u, tiles_per_block - it * 16u);
@@ -212,7 +230,6 @@ nvfp4_matvec_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         if (row_ok) bulk_g2s(dst + lane * kSegBytes, wsrc + it * kSegBytes, seg, &full[stage]);
         if (lane < tiles)
           bulk_g2s(dst + kStageW + lane * 128u, ssrc + static_cast<size_t>(it * 16u + lane) * 512u, 128u, &full[stage]);
-        if (++stage == kStages) { stage = 0; phase ^= 1u; }
       }
     }
     return;
@@ -222,13 +239,29 @@ nvfp4_matvec_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-  // Stage x once per CTA.  Slot = 32 consecutive activations (one lane, one iteration).
+  // Stage x once per CTA as float16 scaled by a power of two that brings max|x| into
+  // [2^14, 2^15): every product e2m1 * x is then exact in the mixed-precision FMA and values
+  // below max|x| * 2^-38 flush, far below the float32 accumulation error.  Slot = 32 consecutive
+  // activations (one lane, one stage).  Loads go out in batches of eight independent 16-byte L2
+  // reads per thread, so a pass over x costs one memory latency per 16384 activations.
+  constexpr uint32_t kBatch = 8;
+  const uint32_t n_chunks = K / 8u;
   int shift = 0;
-  if (MODE == 1) {
+  {
     uint32_t m = 0;
-    for (uint32_t i = threadIdx.x; i < K / 2u; i += kThreads) {
-      const uint32_t v = __ldcg(reinterpret_cast<const uint32_t *>(x) + i);
-      m = max(m, max(v & 0x7fffu, (v >> 16) & 0x7fffu));
+    for (uint32_t base = 0; base < n_chunks; base += kBatch * kThreads) {
+      uint4 xr[kBatch];
+#pragma unroll
+      for (uint32_t i = 0; i < kBatch; ++i) {
+        const uint32_t c = base + threadIdx.x + i * kThreads;
+        xr[i] = c < n_chunks ? __ldcg(reinterpret_cast<const uint4 *>(x) + c) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (uint32_t i = 0; i < kBatch; ++i) {
+        const uint32_t wv[4] = {xr[i].x, xr[i].y, xr[i].z, xr[i].w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) m = max(m, max(wv[q] & 0x7fffu, (wv[q] >> 16) & 0x7fffu));
+      }
     }
     m = __reduce_max_sync(0xffffffffu, m);
     if (lane == 0) atomicMax(amax_bits, m);
@@ -238,112 +271,108 @@ nvfp4_matvec_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   }
   {
     const float up = __uint_as_float(static_cast<uint32_t>(127 + shift) << 23);
-    const uint32_t slots = K / 32u;
-    for (uint32_t c = threadIdx.x; c < slots * 4u; c += kThreads) {
-      const uint4 v = __ldcg(reinterpret_cast<const uint4 *>(x) + c);   // L2 only: x may be fresh from the previous kernel
-      const uint32_t slot = c >> 2, sub = c & 3u;
-      const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
-      float f[8];
+    for (uint32_t base = 0; base < n_chunks; base += kBatch * kThreads) {
+      uint4 xr[kBatch];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        f[2 * i] = __uint_as_float(wv[i] << 16);
-        f[2 * i + 1] = __uint_as_float(wv[i] & 0xffff0000u);
+      for (uint32_t i = 0; i < kBatch; ++i) {
+        const uint32_t c = base + threadIdx.x + i * kThreads;
+        xr[i] = c < n_chunks ? __ldcg(reinterpret_cast<const uint4 *>(x) + c)   // L2 only: x may be fresh
+                             : make_uint4(0, 0, 0, 0);
       }
-      if (MODE == 0) {
-        xs[x_chunk<0>(slot, sub * 2u)] = *reinterpret_cast<uint4 *>(&f[0]);
-        xs[x_chunk<0>(slot, sub * 2u + 1u)] = *reinterpret_cast<uint4 *>(&f[4]);
-      } else {
-        __half2 h[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(f[2 * i] * up, f[2 * i + 1] * up);
-        xs[x_chunk<1>(slot, sub)] = *reinterpret_cast<uint4 *>(h);
+      for (uint32_t i = 0; i < kBatch; ++i) {
+        const uint32_t c = base + threadIdx.x + i * kThreads;
+        if (c < n_chunks) {
+          const uint32_t wv[4] = {xr[i].x, xr[i].y, xr[i].z, xr[i].w};
+          __half2 h[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            h[q] = __floats2half2_rn(__uint_as_float(wv[q] << 16) * up, __uint_as_float(wv[q] & 0xffff0000u) * up);
+          xs[x_chunk(c >> 2, c & 3u)] = *reinterpret_cast<uint4 *>(h);
+        }
       }
     }
   }
   asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory");
 
   const float down = __uint_as_float(static_cast<uint32_t>(127 - shift) << 23);
-  const uint32_t cbase = 2u * (lane & 1u);       // first of this lane's two groups inside its scale tile
-  uint32_t stage = 0, phase = 0;
+  const uint32_t quad = warp % QUADS, kpart = warp / QUADS;
+  const uint32_t sh0 = 16u * (lane & 1u);        // bit offset of this lane's two scale bytes in a row word
+  uint32_t g0 = 0;                               // stage number of the current unit's first stage
+  uint32_t flip = 0;
+  bool dead = false;
 
-  for (uint32_t unit = blockIdx.x; unit < units; unit += gridDim.x) {
-    const uint32_t row0 = (unit >> 2) * 128u + (unit & 3u) * 8u + warp;
+  for (uint32_t unit = blockIdx.x; unit < units; unit += gridDim.x, g0 += iters, flip ^= 1u) {
+    const uint32_t row0 = (unit / kUnitsPerBlock) * 128u + (unit % kUnitsPerBlock) * QUADS + quad;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    for (uint32_t it = 0; it < iters; ++it) {
-      if (!mbar_wait(&full[stage], phase)) return;
+    for (uint32_t it = kpart; it < iters; it += KPARTS) {
+      const uint32_t g = g0 + it;
+      const uint32_t stage = g % kStages, phase = (g / kStages) & 1u;
+      // A wait that gives up (never seen in practice) only stops the arithmetic: the warp keeps
+      // walking its stages and barriers so that nobody else is left waiting for it.
+      if (!dead && !mbar_wait(&full[stage], phase)) dead = true;
       const uint8_t *st = ring + stage * kStageBytes;
       const uint32_t slot = lane + it * 32u;
-      if (slot * 32u < K) {
+      if (!dead && slot * 32u < K) {
         uint4 wq[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) wq[j] = *reinterpret_cast<const uint4 *>(st + (j * 8u + warp) * kSegBytes + lane * 16u);
+        for (int j = 0; j < 4; ++j) wq[j] = *reinterpret_cast<const uint4 *>(st + (j * QUADS + quad) * kSegBytes + lane * 16u);
         const uint32_t tile = lane >> 1;
-        const uint32_t sf_chunk = TMAP ? (warp ^ (tile & 7u)) : warp;      // 128-byte swizzle of the TMA box
-        const uint4 sq = *reinterpret_cast<const uint4 *>(st + kStageW + tile * 128u + sf_chunk * 16u);
+        const uint32_t sf_chunk = (TMAP && QUADS == 8) ? (quad ^ (tile & 7u)) : quad;   // 128-byte swizzle of the TMA box
+        const uint4 sq = *reinterpret_cast<const uint4 *>(st + kStageW + tile * kSfRow + sf_chunk * 16u);
         const uint32_t sw[4] = {sq.x, sq.y, sq.z, sq.w};
 #pragma unroll
         for (int half = 0; half < 2; ++half) {          // the two 16-groups of this slot
-          float local[4];
-          if (MODE == 0) {
-            float2 a2[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
-            const uint4 xa = xs[x_chunk<0>(slot, half * 4u + 0u)], xb = xs[x_chunk<0>(slot, half * 4u + 1u)];
-            const uint4 xc = xs[x_chunk<0>(slot, half * 4u + 2u)], xd = xs[x_chunk<0>(slot, half * 4u + 3u)];
-            const float2 xv[8] = {{__uint_as_float(xa.x), __uint_as_float(xa.y)}, {__uint_as_float(xa.z), __uint_as_float(xa.w)},
-                                  {__uint_as_float(xb.x), __uint_as_float(xb.y)}, {__uint_as_float(xb.z), __uint_as_float(xb.w)},
-                                  {__uint_as_float(xc.x), __uint_as_float(xc.y)}, {__uint_as_float(xc.z), __uint_as_float(xc.w)},
-                                  {__uint_as_float(xd.x), __uint_as_float(xd.y)}, {__uint_as_float(xd.z), __uint_as_float(xd.w)}};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const uint32_t w0 = half == 0 ? wq[j].x : wq[j].z;
-              const uint32_t w1 = half == 0 ? wq[j].y : wq[j].w;
-              uint32_t h[4];
-              e2m1x8_to_h2(w0, h);
-#pragma unroll
-              for (int i = 0; i < 4; ++i)
-                fma_f32x2(a2[j], __half22float2(*reinterpret_cast<__half2 *>(&h[i])), xv[i]);
-              e2m1x8_to_h2(w1, h);
-#pragma unroll
-              for (int i = 0; i < 4; ++i)
-                fma_f32x2(a2[j], __half22float2(*reinterpret_cast<__half2 *>(&h[i])), xv[4 + i]);
-              local[j] = a2[j].x + a2[j].y;
-            }
-          } else {
-            const uint4 xa = xs[x_chunk<1>(slot, half * 2u)], xb = xs[x_chunk<1>(slot, half * 2u + 1u)];
-            const uint32_t xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const uint32_t w0 = half == 0 ? wq[j].x : wq[j].z;
-              const uint32_t w1 = half == 0 ? wq[j].y : wq[j].w;
-              uint32_t h[4];
-              float a = 0.f;
-              e2m1x8_to_h2(w0, h);
-#pragma unroll
-              for (int i = 0; i < 4; ++i) fma_mixed(a, h[i], xv[i]);
-              e2m1x8_to_h2(w1, h);
-#pragma unroll
-              for (int i = 0; i < 4; ++i) fma_mixed(a, h[i], xv[4 + i]);
-              local[j] = a;
-            }
-          }
+          // The mixed-precision FMA has a long latency, so every row keeps two accumulators
+          // (even / odd column) and the four rows advance together: eight independent chains.
+          const uint4 xa = xs[x_chunk(slot, half * 2u)], xb = xs[x_chunk(slot, half * 2u + 1u)];
+          const uint32_t xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+          uint32_t h[4][8];
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            const uint32_t code = (sw[j] >> (8u * (cbase + half))) & 0xffu;
-            acc[j] = fmaf(local[j], lut[code], acc[j]);
+            uint32_t t[4];
+            e2m1x8_to_h2(half == 0 ? wq[j].x : wq[j].z, t);
+            h[j][0] = t[0]; h[j][1] = t[1]; h[j][2] = t[2]; h[j][3] = t[3];
+            e2m1x8_to_h2(half == 0 ? wq[j].y : wq[j].w, t);
+            h[j][4] = t[0]; h[j][5] = t[1]; h[j][6] = t[2]; h[j][7] = t[3];
+          }
+          float ae[4] = {0.f, 0.f, 0.f, 0.f}, ao[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) fma_mixed_eo(ae[j], ao[j], h[j][i], xv[i]);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t code = (sw[j] >> (sh0 + 8u * half)) & 0xffu;
+            acc[j] = fmaf(ae[j] + ao[j], lut[code], acc[j]);
           }
         }
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty[stage]);
-      if (++stage == kStages) { stage = 0; phase ^= 1u; }
     }
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
 #pragma unroll
       for (int off = 16; off > 0; off >>= 1) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], off);
     }
-    if (lane < 4 && row0 + 32u * lane < N) {
-      const float v = lane == 0 ? acc[0] : lane == 1 ? acc[1] : lane == 2 ? acc[2] : acc[3];
-      y[row0 + 32u * lane] = __float2bfloat16(v * down);
+    if (KPARTS == 1) {
+      if (lane < 4 && row0 + 32u * lane < N) {
+        const float v = lane == 0 ? acc[0] : lane == 1 ? acc[1] : lane == 2 ? acc[2] : acc[3];
+        y[row0 + 32u * lane] = __float2bfloat16(v * down);
+      }
+    } else {
+      // K-parts of a quad meet in shared memory (two buffers alternate between units) and are
+      // added in a fixed order.
+      float *buf = red + flip * (kWarps * 4u);
+      if (lane < 4) buf[warp * 4u + lane] = lane == 0 ? acc[0] : lane == 1 ? acc[1] : lane == 2 ? acc[2] : acc[3];
+      asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory");
+      if (kpart == 0 && lane < 4 && row0 + 32u * lane < N) {
+        float v = 0.f;
+#pragma unroll
+        for (uint32_t kp = 0; kp < KPARTS; ++kp) v += buf[(kp * QUADS + quad) * 4u + lane];
+        y[row0 + 32u * lane] = __float2bfloat16(v * down);
+      }
     }
   }
 }
@@ -376,8 +405,6 @@ nvfp4_matvec_generic_kernel(const __nv_bfloat16 *__restrict__ x, const uint8_t *
   if (lane == 0) y[row] = __float2bfloat16(sum);
 }
 
-std::atomic<int> g_mode{1};
-
 int g_sms = 0;
 int sm_count() {
   if (g_sms == 0) {
@@ -406,7 +433,7 @@ EncodeFn encode_fn() {
   return fn;
 }
 
-bool make_maps(const qwen36_nvfp4_matvec_spec_t *s, CUtensorMap *map_w, CUtensorMap *map_sf) {
+bool make_maps(const qwen36_nvfp4_matvec_spec_t *s, uint32_t quads, CUtensorMap *map_w, CUtensorMap *map_sf) {
   EncodeFn enc = encode_fn();
   if (enc == nullptr) return false;
   const uint64_t K = s->in_features, N = s->out_features;
@@ -415,7 +442,7 @@ bool make_maps(const qwen36_nvfp4_matvec_spec_t *s, CUtensorMap *map_w, CUtensor
   {   // weights as uint32 [blocks][4][32][K/8]
     const cuuint64_t dims[4] = {K / 8, 32, 4, blocks};
     const cuuint64_t strides[3] = {row_bytes, 32 * row_bytes, 128 * row_bytes};
-    const cuuint32_t box[4] = {128, 8, 4, 1};
+    const cuuint32_t box[4] = {128, quads, 4, 1};
     if (enc(map_w, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, reinterpret_cast<void *>(s->weight_u8.ptr), dims, strides, box,
             ones, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
@@ -424,30 +451,29 @@ bool make_maps(const qwen36_nvfp4_matvec_spec_t *s, CUtensorMap *map_w, CUtensor
   {   // scales as uint32 [blocks][tiles][128]
     const cuuint64_t dims[3] = {128, tiles, blocks};
     const cuuint64_t strides[2] = {512, tiles * 512};
-    const cuuint32_t box[3] = {32, 16, 1};
+    const cuuint32_t box[3] = {quads * 4, 16, 1};
     if (enc(map_sf, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, reinterpret_cast<void *>(s->block_scale_e4m3.ptr), dims,
-            strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            quads == 8 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return false;
   }
   return true;
 }
 
-template <int MODE, bool TMAP>
+template <int QUADS, bool TMAP>
 int launch_kernel(const qwen36_nvfp4_matvec_spec_t *s, const CUtensorMap &map_w, const CUtensorMap &map_sf) {
   const uint32_t K = static_cast<uint32_t>(s->in_features), N = static_cast<uint32_t>(s->out_features);
-  const size_t smem = 1024 + kHeaderBytes + static_cast<size_t>(kStages) * kStageBytes +
-                      static_cast<size_t>(K) * sizeof(typename XT<MODE>::type);
+  const size_t smem = 1024 + kHeaderBytes + kRingBytes + static_cast<size_t>(K) * 2;
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(nvfp4_matvec_kernel<MODE, TMAP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    attr_err = cudaFuncSetAttribute(nvfp4_matvec_kernel<QUADS, TMAP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     227 * 1024);
   });
   if (attr_err != cudaSuccess) return QWEN36_STATUS_CUDA_ERROR;
-  const uint32_t units = ((N + 127u) / 128u) * 4u;
-  const uint32_t per_sm = smem <= 112 * 1024 ? 2u : 1u;
-  const uint32_t cap = static_cast<uint32_t>(sm_count()) * per_sm;
+  const uint32_t units = ((N + 127u) / 128u) * (32u / QUADS);
+  const uint32_t cap = static_cast<uint32_t>(sm_count()) * 2u;
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(units < cap ? units : cap);
   cfg.blockDim = dim3(kThreads + 32);
@@ -459,24 +485,45 @@ int launch_kernel(const qwen36_nvfp4_matvec_spec_t *s, const CUtensorMap &map_w,
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   return q36::cuda_status(cudaLaunchKernelEx(
-      &cfg, nvfp4_matvec_kernel<MODE, TMAP>, map_w, map_sf, as_ptr<const __nv_bfloat16>(s->input_bf16),
+      &cfg, nvfp4_matvec_kernel<QUADS, TMAP>, map_w, map_sf, as_ptr<const __nv_bfloat16>(s->input_bf16),
       as_ptr<const uint8_t>(s->weight_u8), as_ptr<const uint8_t>(s->block_scale_e4m3),
       as_ptr<const float>(s->tensor_scale_f32), as_ptr<__nv_bfloat16>(s->output_bf16), K, N));
 }
 
-template <int MODE>
-int launch_mode(const qwen36_nvfp4_matvec_spec_t *s) {
+int launch_fast(const qwen36_nvfp4_matvec_spec_t *s) {
   CUtensorMap map_w{}, map_sf{};
-  if (s->out_features % 128 == 0 && make_maps(s, &map_w, &map_sf)) return launch_kernel<MODE, true>(s, map_w, map_sf);
-  return launch_kernel<MODE, false>(s, map_w, map_sf);
+  if (s->out_features % 128 != 0) return launch_kernel<8, false>(s, map_w, map_sf);
+  // Fewest K-parts that still give every SM two CTAs (8 consumer warps each).
+  const uint32_t blocks = static_cast<uint32_t>(s->out_features / 128);
+  const uint32_t iters = static_cast<uint32_t>((s->in_features + 1023) / 1024);
+  uint32_t quads = 8;
+  while (quads > 1 && blocks * (32u / quads) < 2u * static_cast<uint32_t>(sm_count()) && 8u / (quads / 2u) <= iters)
+    quads /= 2;
+  if (!make_maps(s, quads, &map_w, &map_sf)) return launch_kernel<8, false>(s, map_w, map_sf);
+  switch (quads) {
+    case 8: return launch_kernel<8, true>(s, map_w, map_sf);
+    case 4: return launch_kernel<4, true>(s, map_w, map_sf);
+    case 2: return launch_kernel<2, true>(s, map_w, map_sf);
+    default: return launch_kernel<1, true>(s, map_w, map_sf);
+  }
 }
 
 }  // namespace
 
-// Test/bench hook: 0 = float32 activations + packed f32x2 FMA, 1 = scaled
-// float16 activations + mixed-precision FMA (default).  Not part of the
-// reference ABI.
-extern "C" void qwen36_nvfp4_matvec_set_mode(int mode) { g_mode.store(mode == 0 ? 0 : 1); }
+// Tuning hook (not part of the reference ABI): stages of L2 prefetch the producer keeps ahead of
+// the shared-memory ring.  Synchronises.
+extern "C" void qwen36_nvfp4_matvec_set_mode(int mode) {
+  const unsigned int v = mode < 0 ? 0u : static_cast<unsigned int>(mode);
+  cudaMemcpyToSymbol(g_prefetch_distance, &v, sizeof(v));
+}
+
+// 1 when a bounded wait inside the GEMV pipeline ever gave up (a stage never arrived); the
+// kernel then returns without finishing its rows.  Reads device memory: synchronises.
+extern "C" int qwen36_nvfp4_matvec_last_error(void) {
+  unsigned int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_matvec_error, sizeof(v)) != cudaSuccess) return -1;
+  return static_cast<int>(v);
+}
 
 extern "C" int qwen36_nvfp4_matvec(const qwen36_nvfp4_matvec_spec_t *spec) {
   if (spec == nullptr) return QWEN36_STATUS_NULL_POINTER;
@@ -494,5 +541,5 @@ extern "C" int qwen36_nvfp4_matvec(const qwen36_nvfp4_matvec_spec_t *spec) {
         as_ptr<__nv_bfloat16>(spec->output_bf16), spec->in_features, spec->out_features);
     return q36::launch_status();
   }
-  return g_mode.load() == 0 ? launch_mode<0>(spec) : launch_mode<1>(spec);
+  return launch_fast(spec);
 }

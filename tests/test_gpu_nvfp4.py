@@ -131,7 +131,7 @@ def test_matvec_known_answer(backend):
     assert backend.nvfp4_matvec(x, w, sf, None).float().item() == 2.5
 
 
-@pytest.mark.parametrize("mode", [1, 0])
+@pytest.mark.parametrize("mode", [1])
 @pytest.mark.parametrize("n,k", [(5120, 5120), (1024, 5120), (5120, 6144), (12288, 5120), (5120, 17408),
                                  (34816, 5120), (130, 96), (40, 2080), (7, 33)])
 def test_matvec_w4a16_vs_oracle(backend, n, k, mode):
