@@ -227,6 +227,104 @@ def per_shape_cold(backend, torch, sweep, synth):
     return out
 
 
+def _time_cuda(torch, fn, reps, warm=3):
+    for _ in range(warm):
+        fn(0)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for i in range(reps):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / reps          # microseconds per call
+
+
+def other_configs(backend, torch, synth):
+    """The remaining benchmark configurations at 1 GPU, each timed with CUDA events over
+    back-to-back launches on inputs larger than L2 (weights alternate between two copies where a
+    single copy would fit): prefill GEMM + activation quantisation (config 2), FP8 lm_head with
+    fused argmax (config 3), int8 KV encode + split-KV decode attention (config 4)."""
+    out = {}
+    gen = torch.Generator(device="cuda").manual_seed(7)
+    # ---- config 2: NVFP4 prefill GEMM ------------------------------------------------------
+    gemm = []
+    for name, n_out, k in (("mlp.gate_up", 34816, 5120), ("mlp.down", 5120, 17408)):
+        ws = []
+        for _ in range(2):
+            packed, sf_rm = synth.nvfp4_weight_device(gen, n_out, k, "cuda")
+            ws.append((packed, backend.nvfp4_retile_scales(sf_rm)))
+        for m_tok in (512, 2048, 8192):
+            x = torch.randn((m_tok, k), generator=gen, device="cuda")
+            ch = torch.randperm(k, generator=gen, device="cuda")[: k // 100]
+            x[:, ch] *= 20.0
+            x = x.to(torch.bfloat16)
+            fp4 = torch.empty((m_tok, k // 2), dtype=torch.uint8, device="cuda")
+            sf = torch.zeros(backend_tiled_bytes(m_tok, k // 16), dtype=torch.uint8, device="cuda")
+            ts = torch.empty(1, dtype=torch.float32, device="cuda")
+            q_us = _time_cuda(torch, lambda i: backend.nvfp4_quantize_rows(x, 0.37, fp4, sf, ts), 10)
+            alpha = synth.WEIGHT_GLOBAL_SCALE * 0.37
+            c = torch.empty((m_tok, n_out), dtype=torch.bfloat16, device="cuda")
+            reps = 10 if m_tok >= 8192 else 20
+            g_us = _time_cuda(torch, lambda i: backend.nvfp4_gemm(ws[i & 1][0], ws[i & 1][1], fp4, sf, alpha,
+                                                                   n_out, m_tok, k, c), reps)
+            flops = 2.0 * m_tok * n_out * k
+            gemm.append({"shape": name, "M": m_tok, "N": n_out, "K": k, "gemm_us": round(g_us, 2),
+                         "tflops": round(flops / g_us / 1e6, 1),
+                         "frac_of_nominal_9PF": round(flops / g_us / 1e6 / 9000.0, 4),
+                         "quantize_us": round(q_us, 2),
+                         "quantize_gbs": round((2.0 * m_tok * k + m_tok * k * 0.5625) / q_us / 1e3, 1)})
+            del x, fp4, sf, c
+        del ws
+    out["prefill_gemm"] = gemm
+    # ---- config 3: FP8 lm_head + greedy argmax ---------------------------------------------
+    rows, cols = synth.VOCAB, synth.HIDDEN
+    w = torch.randint(0, 0x7F, (rows, cols), generator=gen, dtype=torch.uint8, device="cuda")
+    w |= (torch.randint(0, 2, (rows, cols), generator=gen, dtype=torch.uint8, device="cuda") << 7)
+    sc = torch.exp2(torch.rand(rows, generator=gen, device="cuda") * 4 - 6)
+    lm = []
+    for m_tok in (1, 4):
+        xh = torch.randn((m_tok, cols), generator=gen, device="cuda").to(torch.bfloat16)
+        logits = torch.empty((m_tok, rows), dtype=torch.bfloat16, device="cuda")
+        wsb = backend.lm_head_argmax_workspace(rows, m_tok, "cuda")
+        tok = torch.empty(m_tok, dtype=torch.int32, device="cuda")
+        best = torch.empty(m_tok, dtype=torch.float32, device="cuda")
+        byts = rows * cols + 4 * rows + 2 * m_tok * cols + 8 * m_tok
+        us_gemv = _time_cuda(torch, lambda i: backend.lm_head_fp8_gemv(w, sc, xh, logits), 10)
+        us_samp = _time_cuda(torch, lambda i: backend.sample_rows(logits), 10)
+        us_fused = _time_cuda(torch, lambda i: backend.lm_head_fp8_gemv_argmax(w, sc, xh, wsb, 0, tok, best), 10)
+        lm.append({"M": m_tok, "gemv_us": round(us_gemv, 1), "sample_rows_us": round(us_samp, 1),
+                   "fused_us": round(us_fused, 1), "fused_gbs": round(byts / us_fused / 1e3, 1),
+                   "gemv_gbs": round(byts / us_gemv / 1e3, 1)})
+    out["lm_head_fp8"] = lm
+    del w, sc
+    # ---- config 4: int8 KV + decode attention ----------------------------------------------
+    att = []
+    T = 131072
+    k_ = torch.randn((T, 4, 256), generator=gen, device="cuda").to(torch.bfloat16)
+    v_ = torch.randn((T, 4, 256), generator=gen, device="cuda").to(torch.bfloat16)
+    q_ = torch.randn((24, 256), generator=gen, device="cuda").to(torch.bfloat16)
+    kq = torch.empty((T, 4, 256), dtype=torch.int8, device="cuda")
+    vq = torch.empty_like(kq)
+    meta = torch.empty((T, 4, 2), dtype=torch.float32, device="cuda")
+    enc_us = _time_cuda(torch, lambda i: backend.turboquant_encode_kv_rows(k_, v_, kq, vq, meta, 0), 5)
+    enc_bytes = T * (2 * 4 * 256 * 2 + 2 * 4 * 256 + 32)
+    wsa = backend.attention_workspace(24, 256, "cuda")
+    o_ = torch.empty((24, 256), dtype=torch.bfloat16, device="cuda")
+    for ctx in (8192, 32768, 131072):
+        us = _time_cuda(torch, lambda i: backend.turboquant_attention(q_, kq, vq, meta, ctx - 1, wsa, o_), 20)
+        byts = ctx * (2 * 4 * 256 + 4 * 2 * 4) + 24 * 256 * 4
+        att.append({"ctx": ctx, "us": round(us, 2), "gbs": round(byts / us / 1e3, 1)})
+    out["int8_kv_attention"] = att
+    out["int8_kv_encode"] = {"tokens": T, "us": round(enc_us, 1), "gbs": round(enc_bytes / enc_us / 1e3, 1)}
+    return out
+
+
+def backend_tiled_bytes(rows, groups):
+    from speedoza_b200.backend import tiled_scale_bytes
+    return tiled_scale_bytes(rows, groups)
+
+
 def cpu_baseline(seconds: float = 10.0):
     """Oracle W4A16 matvec on the host cores, 5120 x 5120 shape repeated for ~`seconds`."""
     import numpy as np
@@ -327,6 +425,9 @@ def run_ours(args):
     extra = {}
     if rank == 0 and world == 1 and not args.no_extras:
         extra["per_shape_cold"] = per_shape_cold(backend, torch, sweep, synth)
+        del runner, sweep
+        torch.cuda.empty_cache()
+        extra.update(other_configs(backend, torch, synth))
     if rank == 0:
         peak, peak_kind = measured_peaks()
         ms_per_step = ms / args.steps

@@ -82,7 +82,7 @@ constexpr uint32_t kHeaderBytes = 2048;
 constexpr uint32_t kSpinLimit = 1u << 24;
 
 __device__ unsigned int g_matvec_error = 0;
-__device__ unsigned int g_prefetch_distance = 8;            // stages of L2 prefetch ahead of the ring                 // set when a bounded wait gives up
+__device__ unsigned int g_prefetch_distance = 0;            // stages of L2 prefetch ahead of the ring                 // set when a bounded wait gives up
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -159,6 +159,7 @@ nvfp4_matvec_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   float *red = reinterpret_cast<float *>(smem + 1024 + 512 + 16);        // [2][kWarps][4] K-part sums
   uint8_t *ring = smem + kHeaderBytes;
   uint4 *xs = reinterpret_cast<uint4 *>(ring + kRingBytes);              // activations, swizzled chunks
+  float *xscale = reinterpret_cast<float *>(ring + kRingBytes + K * 2u); // inverse scale of every 32-value slot
 
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
   const uint32_t iters = (K + 1023u) / 1024u;
@@ -239,65 +240,49 @@ nvfp4_matvec_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-  // Stage x once per CTA as float16 scaled by a power of two that brings max|x| into
-  // [2^14, 2^15): every product e2m1 * x is then exact in the mixed-precision FMA and values
-  // below max|x| * 2^-38 flush, far below the float32 accumulation error.  Slot = 32 consecutive
-  // activations (one lane, one stage).  Loads go out in batches of eight independent 16-byte L2
-  // reads per thread, so a pass over x costs one memory latency per 16384 activations.
+  // Stage x once per CTA as float16.  Every 32-value slot (what one lane consumes per stage) is
+  // scaled by its own power of two that brings the slot's max|x| into [2^14, 2^15): every
+  // product e2m1 * x is then exact in the mixed-precision FMA, values below the slot maximum
+  // times 2^-38 flush (far below the float32 accumulation error), and no pass over the whole
+  // vector is needed to find a common scale.  The inverse scale of each slot is kept beside it
+  // and folded into the block scale.  Loads go out in batches of eight independent 16-byte L2
+  // reads per thread.
   constexpr uint32_t kBatch = 8;
   const uint32_t n_chunks = K / 8u;
-  int shift = 0;
-  {
-    uint32_t m = 0;
-    for (uint32_t base = 0; base < n_chunks; base += kBatch * kThreads) {
-      uint4 xr[kBatch];
+  for (uint32_t base = 0; base < n_chunks; base += kBatch * kThreads) {
+    uint4 xr[kBatch];
 #pragma unroll
-      for (uint32_t i = 0; i < kBatch; ++i) {
-        const uint32_t c = base + threadIdx.x + i * kThreads;
-        xr[i] = c < n_chunks ? __ldcg(reinterpret_cast<const uint4 *>(x) + c) : make_uint4(0, 0, 0, 0);
-      }
-#pragma unroll
-      for (uint32_t i = 0; i < kBatch; ++i) {
-        const uint32_t wv[4] = {xr[i].x, xr[i].y, xr[i].z, xr[i].w};
-#pragma unroll
-        for (int q = 0; q < 4; ++q) m = max(m, max(wv[q] & 0x7fffu, (wv[q] >> 16) & 0x7fffu));
-      }
+    for (uint32_t i = 0; i < kBatch; ++i) {
+      const uint32_t c = base + threadIdx.x + i * kThreads;
+      xr[i] = c < n_chunks ? __ldcg(reinterpret_cast<const uint4 *>(x) + c)   // L2 only: x may be fresh
+                           : make_uint4(0, 0, 0, 0);
     }
-    m = __reduce_max_sync(0xffffffffu, m);
-    if (lane == 0) atomicMax(amax_bits, m);
-    asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory");
-    const uint32_t e = (*amax_bits >> 7) & 0xffu;
-    shift = e == 255u ? 0 : (e < 15u ? 126 : 141 - static_cast<int>(e));
-  }
-  {
-    const float up = __uint_as_float(static_cast<uint32_t>(127 + shift) << 23);
-    for (uint32_t base = 0; base < n_chunks; base += kBatch * kThreads) {
-      uint4 xr[kBatch];
 #pragma unroll
-      for (uint32_t i = 0; i < kBatch; ++i) {
-        const uint32_t c = base + threadIdx.x + i * kThreads;
-        xr[i] = c < n_chunks ? __ldcg(reinterpret_cast<const uint4 *>(x) + c)   // L2 only: x may be fresh
-                             : make_uint4(0, 0, 0, 0);
-      }
+    for (uint32_t i = 0; i < kBatch; ++i) {
+      const uint32_t c = base + threadIdx.x + i * kThreads;      // four consecutive lanes share a slot
+      const uint32_t wv[4] = {xr[i].x, xr[i].y, xr[i].z, xr[i].w};
+      uint32_t mx = 0;
 #pragma unroll
-      for (uint32_t i = 0; i < kBatch; ++i) {
-        const uint32_t c = base + threadIdx.x + i * kThreads;
-        if (c < n_chunks) {
-          const uint32_t wv[4] = {xr[i].x, xr[i].y, xr[i].z, xr[i].w};
-          __half2 h[4];
+      for (int q = 0; q < 4; ++q) mx = max(mx, max(wv[q] & 0x7fffu, (wv[q] >> 16) & 0x7fffu));
+      mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const uint32_t e = (mx >> 7) & 0xffu;
+      const int shift = e == 255u ? 0 : (e < 15u ? 126 : 141 - static_cast<int>(e));
+      if (c < n_chunks) {
+        const float up = __uint_as_float(static_cast<uint32_t>(127 + shift) << 23);
+        __half2 h[4];
 #pragma unroll
-          for (int q = 0; q < 4; ++q)
-            h[q] = __floats2half2_rn(__uint_as_float(wv[q] << 16) * up, __uint_as_float(wv[q] & 0xffff0000u) * up);
-          xs[x_chunk(c >> 2, c & 3u)] = *reinterpret_cast<uint4 *>(h);
-        }
+        for (int q = 0; q < 4; ++q)
+          h[q] = __floats2half2_rn(__uint_as_float(wv[q] << 16) * up, __uint_as_float(wv[q] & 0xffff0000u) * up);
+        xs[x_chunk(c >> 2, c & 3u)] = *reinterpret_cast<uint4 *>(h);
+        if ((c & 3u) == 0u) xscale[c >> 2] = __uint_as_float(static_cast<uint32_t>(127 - shift) << 23);
       }
     }
   }
   asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory");
 
-  const float down = __uint_as_float(static_cast<uint32_t>(127 - shift) << 23);
   const uint32_t quad = warp % QUADS, kpart = warp / QUADS;
-  const uint32_t sh0 = 16u * (lane & 1u);        // bit offset of this lane's two scale bytes in a row word
+  const uint32_t rot0 = (16u * (lane & 1u) + 30u) & 31u;   // rotation that brings this lane's first scale byte to bits [9:2]
   uint32_t g0 = 0;                               // stage number of the current unit's first stage
   uint32_t flip = 0;
   bool dead = false;
@@ -321,6 +306,7 @@ nvfp4_matvec_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         const uint32_t sf_chunk = (TMAP && QUADS == 8) ? (quad ^ (tile & 7u)) : quad;   // 128-byte swizzle of the TMA box
         const uint4 sq = *reinterpret_cast<const uint4 *>(st + kStageW + tile * kSfRow + sf_chunk * 16u);
         const uint32_t sw[4] = {sq.x, sq.y, sq.z, sq.w};
+        const float slot_inv = xscale[slot];
 #pragma unroll
         for (int half = 0; half < 2; ++half) {          // the two 16-groups of this slot
           // The mixed-precision FMA has a long latency, so every row keeps two accumulators
@@ -343,8 +329,8 @@ nvfp4_matvec_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             for (int j = 0; j < 4; ++j) fma_mixed_eo(ae[j], ao[j], h[j][i], xv[i]);
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            const uint32_t code = (sw[j] >> (sh0 + 8u * half)) & 0xffu;
-            acc[j] = fmaf(ae[j] + ao[j], lut[code], acc[j]);
+            const uint32_t off = __funnelshift_r(sw[j], sw[j], rot0 + 8u * half) & 0x3fcu;    // 4 * scale byte
+            acc[j] = fmaf(ae[j] + ao[j], *reinterpret_cast<const float *>(reinterpret_cast<const uint8_t *>(lut) + off) * slot_inv, acc[j]);
           }
         }
       }
@@ -359,7 +345,7 @@ nvfp4_matvec_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     if (KPARTS == 1) {
       if (lane < 4 && row0 + 32u * lane < N) {
         const float v = lane == 0 ? acc[0] : lane == 1 ? acc[1] : lane == 2 ? acc[2] : acc[3];
-        y[row0 + 32u * lane] = __float2bfloat16(v * down);
+        y[row0 + 32u * lane] = __float2bfloat16(v);
       }
     } else {
       // K-parts of a quad meet in shared memory (two buffers alternate between units) and are
@@ -371,7 +357,7 @@ nvfp4_matvec_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         float v = 0.f;
 #pragma unroll
         for (uint32_t kp = 0; kp < KPARTS; ++kp) v += buf[(kp * QUADS + quad) * 4u + lane];
-        y[row0 + 32u * lane] = __float2bfloat16(v * down);
+        y[row0 + 32u * lane] = __float2bfloat16(v);
       }
     }
   }
@@ -405,6 +391,7 @@ nvfp4_matvec_generic_kernel(const __nv_bfloat16 *__restrict__ x, const uint8_t *
   if (lane == 0) y[row] = __float2bfloat16(sum);
 }
 
+std::atomic<int> g_force_quads{0};
 int g_sms = 0;
 int sm_count() {
   if (g_sms == 0) {
@@ -464,7 +451,7 @@ bool make_maps(const qwen36_nvfp4_matvec_spec_t *s, uint32_t quads, CUtensorMap 
 template <int QUADS, bool TMAP>
 int launch_kernel(const qwen36_nvfp4_matvec_spec_t *s, const CUtensorMap &map_w, const CUtensorMap &map_sf) {
   const uint32_t K = static_cast<uint32_t>(s->in_features), N = static_cast<uint32_t>(s->out_features);
-  const size_t smem = 1024 + kHeaderBytes + kRingBytes + static_cast<size_t>(K) * 2;
+  const size_t smem = 1024 + kHeaderBytes + kRingBytes + static_cast<size_t>(K) * 2 + static_cast<size_t>(K) / 8;
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [] {
@@ -493,12 +480,22 @@ int launch_kernel(const qwen36_nvfp4_matvec_spec_t *s, const CUtensorMap &map_w,
 int launch_fast(const qwen36_nvfp4_matvec_spec_t *s) {
   CUtensorMap map_w{}, map_sf{};
   if (s->out_features % 128 != 0) return launch_kernel<8, false>(s, map_w, map_sf);
-  // Fewest K-parts that still give every SM two CTAs (8 consumer warps each).
+  // Unit size (QUADS row quads per unit, 8 / QUADS K-parts).  Coarse units have the least
+  // per-unit overhead; finer ones are only worth it when coarse units cannot give every SM two
+  // CTAs or leave the last round-robin pass mostly empty.
   const uint32_t blocks = static_cast<uint32_t>(s->out_features / 128);
   const uint32_t iters = static_cast<uint32_t>((s->in_features + 1023) / 1024);
+  const uint32_t ctas = 2u * static_cast<uint32_t>(sm_count());
   uint32_t quads = 8;
-  while (quads > 1 && blocks * (32u / quads) < 2u * static_cast<uint32_t>(sm_count()) && 8u / (quads / 2u) <= iters)
-    quads /= 2;
+  const int forced = g_force_quads.load();
+  if (forced == 1 || forced == 2 || forced == 4 || forced == 8) {
+    quads = static_cast<uint32_t>(forced);
+  } else {
+    // measured on B200: halve the unit while the coarser one cannot give every SM two CTAs
+    // for at least ~1.5 rounds
+    while (quads > 2 && 8u / (quads / 2u) <= iters && blocks * (32u / quads) < ctas + ctas / 2u) quads /= 2;
+  }
+  if (8u / quads > iters) quads = 8;
   if (!make_maps(s, quads, &map_w, &map_sf)) return launch_kernel<8, false>(s, map_w, map_sf);
   switch (quads) {
     case 8: return launch_kernel<8, true>(s, map_w, map_sf);
@@ -516,6 +513,8 @@ extern "C" void qwen36_nvfp4_matvec_set_mode(int mode) {
   const unsigned int v = mode < 0 ? 0u : static_cast<unsigned int>(mode);
   cudaMemcpyToSymbol(g_prefetch_distance, &v, sizeof(v));
 }
+// Tuning hook: force the unit size (1, 2, 4 or 8 row quads); anything else restores the heuristic.
+extern "C" void qwen36_nvfp4_matvec_force_quads(int quads) { g_force_quads.store(quads); }
 
 // 1 when a bounded wait inside the GEMV pipeline ever gave up (a stage never arrived); the
 // kernel then returns without finishing its rows.  Reads device memory: synchronises.
