@@ -51,7 +51,8 @@ def test_reference_quantize_and_retile_equal_oracle(ref):
         assert ts.item() == np.float32(w_ts)
     sf_rm = rng.integers(0, 256, size=(300, 13), dtype=np.uint8)
     out = torch.full((orc.sf_bytes(13, 300),), 0xAA, dtype=torch.uint8, device="cuda")
-    spec = abi.Nvfp4RetileScalesSpec(300, 13, dp(to_dev(sf_rm)), dp(out))
+    sf_rm_d = to_dev(sf_rm)
+    spec = abi.Nvfp4RetileScalesSpec(300, 13, dp(sf_rm_d), dp(out))
     assert ref.qwen36_nvfp4_retile_scales(C.byref(spec)) == 0
     torch.cuda.synchronize()
     assert np.array_equal(out.cpu().numpy(), orc.retile_scales(sf_rm))
@@ -65,7 +66,8 @@ def test_reference_matvec_equals_oracle_bitwise(ref):
     x = synth.activations(rng, 1, k)[0]
     ts = torch.tensor([synth.WEIGHT_GLOBAL_SCALE], dtype=torch.float32, device="cuda")
     y = torch.zeros(n, dtype=torch.bfloat16, device="cuda")
-    spec = abi.Nvfp4MatvecSpec(n, k, dp(to_dev(x)), dp(to_dev(packed)), dp(to_dev(sf)), dp(ts), dp(y))
+    xd, pd, sd = to_dev(x), to_dev(packed), to_dev(sf)          # keep the buffers alive across the call
+    spec = abi.Nvfp4MatvecSpec(n, k, dp(xd), dp(pd), dp(sd), dp(ts), dp(y))
     assert ref.qwen36_nvfp4_matvec(C.byref(spec)) == 0
     torch.cuda.synchronize()
     want = orc.nvfp4_matvec(x, packed, sf, synth.WEIGHT_GLOBAL_SCALE, k)
@@ -86,7 +88,8 @@ def test_reference_lm_head_equals_oracle_bitwise(ref):
     assert np.array_equal(q.cpu().numpy(), oq) and np.array_equal(s.cpu().numpy().view(np.uint32), os_.view(np.uint32))
     x = synth.activations(rng, n, cols)
     y = torch.zeros((n, rows), dtype=torch.bfloat16, device="cuda")
-    spec = abi.LmHeadFp8GemvSpec(rows, cols, n, dp(q), dp(s), dp(to_dev(x)), dp(y))
+    xd = to_dev(x)
+    spec = abi.LmHeadFp8GemvSpec(rows, cols, n, dp(q), dp(s), dp(xd), dp(y))
     assert ref.qwen36_lm_head_fp8_gemv(C.byref(spec)) == 0
     torch.cuda.synchronize()
     want = orc.lm_head_fp8_gemv(oq, os_, x)
@@ -115,7 +118,8 @@ def test_reference_int8_kv_equals_oracle(ref):
     assert np.array_equal(kq.cpu().numpy(), kq_o) and np.array_equal(vq.cpu().numpy(), vq_o)
     assert np.array_equal(meta.cpu().numpy().view(np.uint32), meta_o.view(np.uint32))
     out = torch.zeros((24, 256), dtype=torch.bfloat16, device="cuda")
-    spec = abi.TurboquantAttentionSpec(0, T - 1, dp(to_dev(q)), dp(kq), dp(vq), dp(meta), dp(out),
+    qd = to_dev(q)
+    spec = abi.TurboquantAttentionSpec(0, T - 1, dp(qd), dp(kq), dp(vq), dp(meta), dp(out),
                                        abi.DevicePtr(0), 0, shape, 0)
     assert ref.qwen36_turboquant_attention(C.byref(spec)) == 0
     torch.cuda.synchronize()
