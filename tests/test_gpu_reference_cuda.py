@@ -59,6 +59,11 @@ def test_reference_quantize_and_retile_equal_oracle(ref):
 
 
 def test_reference_matvec_equals_oracle_bitwise(ref):
+    """The reference's scalar matvec has two input paths.  Its vector path reads sixteen bf16
+    activations through a 16-byte `uint4` (kernels-cuda/ops.cu:597-604: eight bf16 pairs are
+    indexed out of a value that holds four), so half of every group's activations are
+    indeterminate there.  Its element-wise path (taken when the activation pointer is not
+    16-byte aligned) is the documented arithmetic, and that is what the oracle is pinned to."""
     rng = np.random.default_rng(12)
     n, k = 1024, 5120
     packed, sf_rm = synth.nvfp4_weight(rng, n, k)
@@ -66,8 +71,12 @@ def test_reference_matvec_equals_oracle_bitwise(ref):
     x = synth.activations(rng, 1, k)[0]
     ts = torch.tensor([synth.WEIGHT_GLOBAL_SCALE], dtype=torch.float32, device="cuda")
     y = torch.zeros(n, dtype=torch.bfloat16, device="cuda")
-    xd, pd, sd = to_dev(x), to_dev(packed), to_dev(sf)          # keep the buffers alive across the call
-    spec = abi.Nvfp4MatvecSpec(n, k, dp(xd), dp(pd), dp(sd), dp(ts), dp(y))
+    x_pad = torch.zeros(k + 8, dtype=torch.bfloat16, device="cuda")
+    x_pad[1:k + 1] = to_dev(x)
+    x_unaligned = x_pad[1:k + 1]                     # 2 bytes past a 16-byte boundary
+    assert x_unaligned.data_ptr() % 16 == 2
+    pd, sd = to_dev(packed), to_dev(sf)              # keep the buffers alive across the call
+    spec = abi.Nvfp4MatvecSpec(n, k, dp(x_unaligned), dp(pd), dp(sd), dp(ts), dp(y))
     assert ref.qwen36_nvfp4_matvec(C.byref(spec)) == 0
     torch.cuda.synchronize()
     want = orc.nvfp4_matvec(x, packed, sf, synth.WEIGHT_GLOBAL_SCALE, k)
