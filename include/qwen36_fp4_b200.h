@@ -241,6 +241,27 @@ typedef struct {
 } qwen36_turboquant_attention_partial_spec_t;
 int qwen36_turboquant_attention_partial(const qwen36_turboquant_attention_partial_spec_t *spec);
 
+/* No counterpart in the reference.  Same computation and same spec as
+ * qwen36_turboquant_attention, for callers that cannot hand over scratch
+ * memory: code running where cudaMalloc is off limits (inside a stream capture,
+ * under a memory budget that is already fully committed, in a plug-in whose host
+ * forbids allocation after start-up).  The split-KV partials go to a fixed
+ * 4 MiB buffer inside the library image instead of `workspace` /
+ * `workspace_bytes`, which are ignored.  The entry point allocates nothing.
+ * Limits and rules:
+ *  - q_heads * (head_dim + 2) must not exceed
+ *    qwen36_turboquant_attention_static_max_head_floats() (8256: e.g. 32 heads of
+ *    256 dims); larger shapes return QWEN36_STATUS_INVALID_ARGUMENT.
+ *  - The first call on each device looks up the buffer's device address; make that
+ *    call once, with the device current, before any stream capture.
+ *  - All calls on a device share the one buffer: two calls whose kernels overlap
+ *    on the GPU (different streams, or graphs launched side by side) race.  Calls
+ *    ordered on one stream are fine; nothing in the buffer has to be cleared
+ *    between them, every partial is written before it is read.
+ *  - Every GPU that loads the library carries the 4 MiB until the process exits. */
+int qwen36_turboquant_attention_static(const qwen36_turboquant_attention_spec_t *spec);
+size_t qwen36_turboquant_attention_static_max_head_floats(void);
+
 /* Log-sum-exp merge of n_parts partials laid out [q_heads, n_parts(, head_dim)]
  * into bf16 [q_heads, head_dim]; the arithmetic of
  * kernels-cuda/attention.cu:1473-1554 with the zero-denominator guard of

@@ -212,6 +212,19 @@ class CudaBackend:
         _check("turboquant_attention", self.lib.qwen36_turboquant_attention(C.byref(spec)))
         return out
 
+    def turboquant_attention_static(self, q_bf16, kq, vq, meta, position: int, out=None) -> torch.Tensor:
+        """Same result as turboquant_attention, but the split-KV partials live in a fixed buffer
+        inside the library, so no scratch is passed and nothing is allocated by the call."""
+        q_heads, head_dim = q_bf16.shape
+        kv_heads = kq.shape[1]
+        if out is None:
+            out = torch.empty((q_heads, head_dim), dtype=torch.bfloat16, device=q_bf16.device)
+        shape = abi.AttentionShape(q_heads, kv_heads, head_dim, 0)
+        spec = abi.TurboquantAttentionSpec(0, position, _dp(q_bf16), _dp(kq), _dp(vq), _dp(meta), _dp(out),
+                                           DevicePtr(0), 0, shape, 0)
+        _check("turboquant_attention_static", self.lib.qwen36_turboquant_attention_static(C.byref(spec)))
+        return out
+
     def turboquant_attention_partial(self, q_bf16, kq, vq, meta, t_begin: int, t_end: int, workspace,
                                      part_o=None, part_m=None, part_l=None):
         q_heads, head_dim = q_bf16.shape

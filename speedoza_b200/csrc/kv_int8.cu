@@ -15,6 +15,8 @@
 // (kernels-cuda/attention.cu:1083-1094); a second kernel merges them.
 #include "common.cuh"
 
+#include <mutex>
+
 namespace {
 
 using q36::as_ptr;
@@ -268,12 +270,18 @@ kv_merge_kernel(const float *__restrict__ part_o, const float *__restrict__ part
 
 struct Scratch { float *o, *m, *l; };
 
+// Scratch for qwen36_turboquant_attention_static: lives in the library image, so every GPU that
+// loads the library holds these 4 MiB until the process exits.  Sized for
+// q_heads * (head_dim + 2) <= kStaticHeadFloats (e.g. 32 heads of 256 dims).
+constexpr size_t kStaticHeadFloats = 32 * (256 + 2);
+constexpr size_t kStaticScratchFloats = kMaxSplits * kStaticHeadFloats;
+static __device__ __align__(256) float g_static_attention_scratch[kStaticScratchFloats];
+
 size_t scratch_bytes(size_t q_heads, size_t head_dim) {
   return q_heads * kMaxSplits * (head_dim + 2) * sizeof(float);
 }
 
-Scratch carve(qwen36_device_ptr_t ws, size_t q_heads, size_t head_dim) {
-  float *base = as_ptr<float>(ws);
+Scratch carve(float *base, size_t q_heads, size_t head_dim) {
   return {base, base + q_heads * kMaxSplits * head_dim, base + q_heads * kMaxSplits * (head_dim + 1)};
 }
 
@@ -380,7 +388,7 @@ extern "C" int qwen36_turboquant_attention(const qwen36_turboquant_attention_spe
   if (spec->workspace.ptr == 0 || (spec->workspace.ptr & 15u) != 0 ||
       spec->workspace_bytes < scratch_bytes(spec->shape.q_heads, spec->shape.head_dim))
     return QWEN36_STATUS_INVALID_ARGUMENT;
-  const Scratch sc = carve(spec->workspace, spec->shape.q_heads, spec->shape.head_dim);
+  const Scratch sc = carve(as_ptr<float>(spec->workspace), spec->shape.q_heads, spec->shape.head_dim);
   int status = QWEN36_STATUS_SUCCESS;
   const uint32_t n = run_splits(spec->q_bf16, spec->k_quantized_i8, spec->v_quantized_i8, spec->metadata_f32,
                                 sc, 0, spec->position + 1, spec->shape, &status);
@@ -401,7 +409,7 @@ extern "C" int qwen36_turboquant_attention_partial(const qwen36_turboquant_atten
   if (spec->workspace.ptr == 0 || (spec->workspace.ptr & 15u) != 0 ||
       spec->workspace_bytes < scratch_bytes(spec->shape.q_heads, spec->shape.head_dim))
     return QWEN36_STATUS_INVALID_ARGUMENT;
-  const Scratch sc = carve(spec->workspace, spec->shape.q_heads, spec->shape.head_dim);
+  const Scratch sc = carve(as_ptr<float>(spec->workspace), spec->shape.q_heads, spec->shape.head_dim);
   int status = QWEN36_STATUS_SUCCESS;
   const uint32_t n = run_splits(spec->q_bf16, spec->k_quantized_i8, spec->v_quantized_i8, spec->metadata_f32,
                                 sc, spec->t_begin, spec->t_end, spec->shape, &status);
@@ -410,6 +418,53 @@ extern "C" int qwen36_turboquant_attention_partial(const qwen36_turboquant_atten
       sc.o, sc.m, sc.l, n, static_cast<uint32_t>(spec->shape.head_dim), nullptr,
       as_ptr<float>(spec->partial_acc_f32), as_ptr<float>(spec->partial_max_f32),
       as_ptr<float>(spec->partial_denom_f32));
+  return q36::launch_status();
+}
+
+// Device address of g_static_attention_scratch on the current device, looked up once per
+// device.  In host code the array's name is only a handle for cudaGetSymbolAddress, never a
+// pointer a kernel could use.
+static float *static_scratch_for_current_device(int *status) {
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static float *ptrs[kMaxDevices] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    *status = QWEN36_STATUS_CUDA_ERROR;
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (ptrs[dev] == nullptr) {
+    float *p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void **>(&p), g_static_attention_scratch) != cudaSuccess || p == nullptr) {
+      *status = QWEN36_STATUS_CUDA_ERROR;
+      return nullptr;
+    }
+    ptrs[dev] = p;
+  }
+  return ptrs[dev];
+}
+
+extern "C" size_t qwen36_turboquant_attention_static_max_head_floats(void) { return kStaticHeadFloats; }
+
+extern "C" int qwen36_turboquant_attention_static(const qwen36_turboquant_attention_spec_t *spec) {
+  if (spec == nullptr) return QWEN36_STATUS_NULL_POINTER;
+  if (spec->q_bf16.ptr == 0 || spec->k_quantized_i8.ptr == 0 || spec->v_quantized_i8.ptr == 0 ||
+      spec->metadata_f32.ptr == 0 || spec->output_bf16.ptr == 0 || !shape_ok(spec->shape))
+    return QWEN36_STATUS_INVALID_ARGUMENT;
+  if (spec->shape.head_dim > 256) return QWEN36_STATUS_NOT_IMPLEMENTED;
+  // the built-in scratch has a fixed size: larger shapes must use qwen36_turboquant_attention
+  if (spec->shape.q_heads * (spec->shape.head_dim + 2) > kStaticHeadFloats) return QWEN36_STATUS_INVALID_ARGUMENT;
+  int status = QWEN36_STATUS_SUCCESS;
+  float *base = static_scratch_for_current_device(&status);
+  if (base == nullptr) return status;
+  const Scratch sc = carve(base, spec->shape.q_heads, spec->shape.head_dim);
+  const uint32_t n = run_splits(spec->q_bf16, spec->k_quantized_i8, spec->v_quantized_i8, spec->metadata_f32,
+                                sc, 0, spec->position + 1, spec->shape, &status);
+  if (n == 0) return status;
+  kv_merge_kernel<true><<<static_cast<unsigned>(spec->shape.q_heads), kThreads, 0, q36::stream()>>>(
+      sc.o, sc.m, sc.l, n, static_cast<uint32_t>(spec->shape.head_dim), as_ptr<__nv_bfloat16>(spec->output_bf16),
+      nullptr, nullptr, nullptr);
   return q36::launch_status();
 }
 
