@@ -320,6 +320,70 @@ def other_configs(backend, torch, synth):
     return out
 
 
+def profile_case(name: str):
+    """Runs one small, fixed case of a single kernel a few times (for `ncu -k ... -c ...`):
+    gemv_gate_up | gemv_down | gemm_gate_up_2048 | gemm_down_2048 | lm_head_m1 | lm_head_m4 |
+    attention_32768 | quantize_2048.  Inputs exceed L2 but stay well under a few GB."""
+    import torch
+    from speedoza_b200 import synth
+    from speedoza_b200.backend import CudaBackend
+    torch.cuda.set_device(0)
+    b = CudaBackend()
+    gen = torch.Generator(device="cuda").manual_seed(11)
+    if name.startswith("gemv_"):
+        n, k = (34816, 5120) if name == "gemv_gate_up" else (5120, 17408)
+        mats = []
+        for _ in range(3):
+            p, sf = synth.nvfp4_weight_device(gen, n, k, "cuda")
+            mats.append((p, b.nvfp4_retile_scales(sf)))
+        ts = torch.tensor([synth.WEIGHT_GLOBAL_SCALE], device="cuda")
+        x = torch.randn(k, generator=gen, device="cuda").to(torch.bfloat16)
+        y = torch.empty(n, dtype=torch.bfloat16, device="cuda")
+        for i in range(6):
+            b.nvfp4_matvec(x, mats[i % 3][0], mats[i % 3][1], ts, y)
+    elif name.startswith("gemm_"):
+        n, k = (34816, 5120) if "gate_up" in name else (5120, 17408)
+        m_tok = int(name.rsplit("_", 1)[1])
+        ws = []
+        for _ in range(2):
+            p, sf = synth.nvfp4_weight_device(gen, n, k, "cuda")
+            ws.append((p, b.nvfp4_retile_scales(sf)))
+        x = torch.randn((m_tok, k), generator=gen, device="cuda").to(torch.bfloat16)
+        fp4, sfb, ts = b.nvfp4_quantize_rows(x, 0.37)
+        c = torch.empty((m_tok, n), dtype=torch.bfloat16, device="cuda")
+        for i in range(4):
+            b.nvfp4_gemm(ws[i & 1][0], ws[i & 1][1], fp4, sfb, 0.37 / 2688.0, n, m_tok, k, c)
+    elif name.startswith("lm_head_"):
+        m_tok = 1 if name.endswith("m1") else 4
+        rows, cols = synth.VOCAB, synth.HIDDEN
+        w = torch.randint(0, 0x7F, (rows, cols), generator=gen, dtype=torch.uint8, device="cuda")
+        sc = torch.exp2(torch.rand(rows, generator=gen, device="cuda") * 4 - 6)
+        xh = torch.randn((m_tok, cols), generator=gen, device="cuda").to(torch.bfloat16)
+        ws = b.lm_head_argmax_workspace(rows, m_tok, "cuda")
+        for _ in range(3):
+            b.lm_head_fp8_gemv_argmax(w, sc, xh, ws)
+    elif name.startswith("attention_"):
+        ctx = int(name.rsplit("_", 1)[1])
+        k_ = torch.randn((ctx, 4, 256), generator=gen, device="cuda").to(torch.bfloat16)
+        v_ = torch.randn((ctx, 4, 256), generator=gen, device="cuda").to(torch.bfloat16)
+        q_ = torch.randn((24, 256), generator=gen, device="cuda").to(torch.bfloat16)
+        kq = torch.empty((ctx, 4, 256), dtype=torch.int8, device="cuda"); vq = torch.empty_like(kq)
+        meta = torch.empty((ctx, 4, 2), dtype=torch.float32, device="cuda")
+        b.turboquant_encode_kv_rows(k_, v_, kq, vq, meta, 0)
+        ws = b.attention_workspace(24, 256, "cuda")
+        for _ in range(3):
+            b.turboquant_attention(q_, kq, vq, meta, ctx - 1, ws)
+    elif name.startswith("quantize_"):
+        m_tok = int(name.rsplit("_", 1)[1])
+        x = torch.randn((m_tok, 17408), generator=gen, device="cuda").to(torch.bfloat16)
+        for _ in range(3):
+            b.nvfp4_quantize_rows(x, 0.37)
+    else:
+        raise SystemExit(f"unknown profile case {name}")
+    torch.cuda.synchronize()
+    print(json.dumps({"profile_case": name, "status": "ok"}))
+
+
 def backend_tiled_bytes(rows, groups):
     from speedoza_b200.backend import tiled_scale_bytes
     return tiled_scale_bytes(rows, groups)
@@ -526,8 +590,11 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    ap.add_argument("--profile-case", default=None, help="run one small kernel case (for ncu) and exit")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.profile_case:
+        profile_case(args.profile_case)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         if args.warmup < 3:
