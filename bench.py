@@ -122,13 +122,8 @@ def build_sweep(backend, torch, synth, rank: int, world: int, layers: int, seed:
 
 
 def shard_rows(n: int, rank: int, world: int):
-    blocks = n // 128
-    per = (blocks + world - 1) // world
-    lo = min(blocks, per * rank) * 128
-    hi = min(blocks, per * (rank + 1)) * 128
-    if rank == world - 1:
-        hi = n
-    return lo, hi
+    from speedoza_b200 import shard
+    return shard.shard_rows(n, rank, world)
 
 
 class SweepRunner:
@@ -159,16 +154,8 @@ class SweepRunner:
         return out
 
     def gather(self, out, out_local, n_full):
-        # equal 128-row-block shards except possibly the last: gather padded slices
-        per = ((n_full // 128 + self.world - 1) // self.world) * 128
-        if per * self.world == n_full:
-            self.dist.all_gather_into_tensor(out, out_local[:per])
-        else:
-            buf = self.torch.zeros(per * self.world, dtype=out.dtype, device=out.device)
-            src = self.torch.zeros(per, dtype=out.dtype, device=out.device)
-            src[:out_local.numel()] = out_local[:min(per, out_local.numel())]
-            self.dist.all_gather_into_tensor(buf, src)
-            out.copy_(buf[:n_full])
+        from speedoza_b200 import shard
+        shard.all_gather_rows(out_local, n_full, self.world, out)
 
     def step(self, x0):
         x = x0
@@ -188,7 +175,9 @@ class SweepRunner:
         self.x_static = torch.zeros(5120, dtype=torch.bfloat16, device="cuda")
         self.graph = torch.cuda.CUDAGraph()
         before = self.launches
-        with torch.cuda.graph(self.graph):
+        # thread-local capture mode: the NCCL watchdog thread may touch CUDA while this thread captures
+        mode = "thread_local" if self.world > 1 else "global"
+        with torch.cuda.graph(self.graph, capture_error_mode=mode):
             self.b.sync_stream()                  # library's ambient stream = the capturing stream
             self.y_static = self.step(self.x_static)
         self.b.sync_stream()
@@ -445,8 +434,15 @@ def run_ours(args):
     barrier()
     use_graph = not args.no_graph
     if use_graph:
-        per_step = runner.capture()
-        run_step = runner.replay
+        try:
+            per_step = runner.capture()
+            run_step = runner.replay
+        except Exception as exc:                 # capture refused (e.g. a collective): same launches, eagerly
+            print(f"[bench] graph capture failed on rank {rank}: {exc!r}; running eagerly", file=sys.stderr, flush=True)
+            backend.sync_stream()
+            use_graph = False
+            per_step = launches_per_step
+            run_step = runner.step
     else:
         per_step = launches_per_step
         run_step = runner.step
@@ -527,6 +523,101 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_sharded_workload(args):
+    """--workload lm_head | attention | prefill at N GPUs (strong scaling: the total work is fixed,
+    each rank holds 1/N of the vocab rows, of the KV range, or of the weight rows)."""
+    import torch
+    import torch.distributed as dist
+    from speedoza_b200 import shard, synth
+    from speedoza_b200.backend import CudaBackend
+    world = int(os.environ.get("WORLD_SIZE", "1")); rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    b = CudaBackend()
+    gen = torch.Generator(device="cuda").manual_seed(4321)
+    extra = {}
+    if args.workload == "lm_head":
+        m_tok = args.tokens or 4
+        rows, cols = synth.VOCAB, synth.HIDDEN
+        lo, hi = shard.shard_rows(rows, rank, world)
+        gen.manual_seed(100 + rank)
+        w = torch.randint(0, 0x7F, (hi - lo, cols), generator=gen, dtype=torch.uint8, device="cuda")
+        sc = torch.exp2(torch.rand(hi - lo, generator=gen, device="cuda") * 4 - 6)
+        gen.manual_seed(7)
+        x = torch.randn((m_tok, cols), generator=gen, device="cuda").to(torch.bfloat16)
+        head = shard.ShardedLmHead(b, rows, w, sc, lo, world, m_tok)
+        step = lambda: head.argmax(x)
+        work, unit, name = rows * cols + 4 * rows + 2 * m_tok * cols + 8 * m_tok, "GB/s", \
+            f"config 3: FP8 lm_head 248320x5120 + fused greedy argmax, M={m_tok}, vocab split {world}-way + all-gather of (value, index)"
+        dtype = "e4m3 x bf16 -> f32"
+    elif args.workload == "attention":
+        ctx = args.tokens or 131072
+        lo, hi = shard.shard_tokens(ctx, rank, world)
+        gen.manual_seed(200 + rank)
+        k_ = torch.randn((hi - lo, 4, 256), generator=gen, device="cuda").to(torch.bfloat16)
+        v_ = torch.randn((hi - lo, 4, 256), generator=gen, device="cuda").to(torch.bfloat16)
+        kq = torch.empty((hi - lo, 4, 256), dtype=torch.int8, device="cuda"); vq = torch.empty_like(kq)
+        meta = torch.empty((hi - lo, 4, 2), dtype=torch.float32, device="cuda")
+        b.turboquant_encode_kv_rows(k_, v_, kq, vq, meta, 0)
+        gen.manual_seed(7)
+        q_ = torch.randn((24, 256), generator=gen, device="cuda").to(torch.bfloat16)
+        att = shard.ShardedKvAttention(b, kq, vq, meta, lo, world, 24, 256)
+        step = lambda: att.attend(q_, ctx - 1)
+        work, unit, name = ctx * (2 * 4 * 256 + 32) + 24 * 256 * 4, "GB/s", \
+            f"config 4: int8 KV decode attention, ctx {ctx}, 24 q / 4 kv heads, KV range split {world}-way + all-gather of (m, l, o)"
+        dtype = "int8 x bf16 -> f32"
+    else:
+        m_tok = args.tokens or 8192
+        n_out, k = 34816, 5120
+        lo, hi = shard.shard_rows(n_out, rank, world)
+        gen.manual_seed(300 + rank)
+        packed, sf_rm = synth.nvfp4_weight_device(gen, hi - lo, k, "cuda")
+        a_sf = b.nvfp4_retile_scales(sf_rm)
+        gen.manual_seed(7)
+        x = torch.randn((m_tok, k), generator=gen, device="cuda").to(torch.bfloat16)
+        fp4 = torch.empty((m_tok, k // 2), dtype=torch.uint8, device="cuda")
+        sfb = torch.zeros(backend_tiled_bytes(m_tok, k // 16), dtype=torch.uint8, device="cuda")
+        ts = torch.empty(1, dtype=torch.float32, device="cuda")
+        c = torch.empty((m_tok, hi - lo), dtype=torch.bfloat16, device="cuda")
+
+        def step():
+            b.nvfp4_quantize_rows(x, 0.37, fp4, sfb, ts)          # replicated on every rank
+            return b.nvfp4_gemm(packed, a_sf, fp4, sfb, 0.37 / 2688.0, hi - lo, m_tok, k, c)
+        work, unit, name = 2.0 * m_tok * n_out * k, "TFLOP/s", \
+            f"config 2: NVFP4 prefill (quantise + tcgen05 GEMM) gate_up 34816x5120, M={m_tok}, weight rows split {world}-way, output kept sharded"
+        dtype = "nvfp4 x nvfp4 -> f32"
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+    for _ in range(max(3, args.warmup)):
+        step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+    if rank == 0:
+        per = ms / args.steps
+        value = work / (per * 1e-3) / (1e9 if unit == "GB/s" else 1e12)
+        print(json.dumps({"metric": METRIC, "value": round(value, 1), "unit": unit, "n_gpus": world, "steps": args.steps,
+                          "warmup": max(3, args.warmup), "ms_per_step": round(per, 4), "higher_is_better": True,
+                          "scaling": "strong", "vs_baseline": None, "dtype": dtype, "data": "synthetic",
+                          "config": {"workload": name}}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 # --------------------------------------------------------------------------- reference arm
 
 def run_reference(args):
@@ -590,12 +681,16 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    ap.add_argument("--workload", default="sweep", choices=["sweep", "lm_head", "attention", "prefill"])
+    ap.add_argument("--tokens", type=int, default=0, help="M (lm_head, prefill) or context length (attention)")
     ap.add_argument("--profile-case", default=None, help="run one small kernel case (for ncu) and exit")
     args = ap.parse_args()
     if args.profile_case:
         profile_case(args.profile_case)
     elif args.impl == "reference":
         run_reference(args)
+    elif args.workload != "sweep":
+        run_sharded_workload(args)
     else:
         if args.warmup < 3:
             args.warmup = max(args.warmup, 1)

@@ -126,8 +126,9 @@ template <uint32_t BN> struct Cfg {
   static constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | ((kBRows >> 3) << 17) | ((kBM >> 4) << 24);
 };
 
-// Tiles are numbered with the row block fastest, so that CTAs running at the same time share
-// the activation tile (L2) while each streams its own weight rows.
+// Tiles are numbered with the token block fastest: the CTAs that run at the same time cover a few
+// weight row blocks times all token blocks, so every weight tile is fetched from HBM once (its
+// other readers hit L2) and the much smaller activation matrix stays L2-resident.
 template <uint32_t BN>
 __global__ void __launch_bounds__(kThreads, 1)
 nvfp4_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -171,7 +172,7 @@ nvfp4_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       uint32_t g = 0;
       bool dead = false;
       for (uint32_t tile = blockIdx.x; tile < tiles && !dead; tile += gridDim.x) {
-        const uint32_t mb = tile % m_blocks, nb = tile / m_blocks;
+        const uint32_t nb = tile % n_blocks, mb = tile / n_blocks;
         for (uint32_t kb = 0; kb < k_blocks; ++kb, ++g) {
           const uint32_t s = g % C::kStages, ph = (g / C::kStages) & 1u;
           if (!mbar_wait(&empty[s], ph ^ 1u)) { dead = true; break; }
@@ -236,7 +237,7 @@ nvfp4_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     uint32_t t_local = 0;
     bool dead = false;
     for (uint32_t tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++t_local) {
-      const uint32_t mb = tile % m_blocks, nb = tile / m_blocks;
+      const uint32_t nb = tile % n_blocks, mb = tile / n_blocks;
       const uint32_t as = t_local % C::kAccStages, aph = (t_local / C::kAccStages) & 1u;
       if (!dead && !mbar_wait(&acc_full[as], aph)) dead = true;
       if (dead) break;

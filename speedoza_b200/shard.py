@@ -1,0 +1,125 @@
+"""Multi-GPU partitioning of the hot path (one process per GPU, torch.distributed).
+
+The reference is single-GPU; these are the natural shards of its path:
+  * NVFP4 linear layers: output rows split in 128-row blocks (block-scale tiles stay whole),
+    activations replicated, all-gather of the bf16 output slices;
+  * lm_head: vocab rows split, each rank runs the fused GEMV+argmax on its slice with
+    ``row_offset`` = first row, all-gather of (value, index) pairs, lowest index wins ties;
+  * int8 KV decode attention: contiguous token ranges per rank, each rank produces one (m, l, o)
+    partial per q head, all-gather, log-sum-exp merge.
+The collectives move a few bytes to a few hundred KB; they are there because the path has a real
+exchange step, nothing else is communicated.  Works with any backend of torch.distributed (NCCL on
+GPUs; gloo on CPU tensors for the host-side logic tests).
+"""
+from __future__ import annotations
+
+from typing import List, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def shard_rows(n: int, rank: int, world: int, block: int = 128) -> Tuple[int, int]:
+    """Rows [lo, hi) of rank: whole `block`-row blocks, ceil-split, the tail goes to the last rank."""
+    blocks = n // block
+    per = (blocks + world - 1) // world
+    lo = min(blocks, per * rank) * block
+    hi = min(blocks, per * (rank + 1)) * block
+    if rank == world - 1:
+        hi = n
+    return lo, hi
+
+
+def shard_tokens(tokens: int, rank: int, world: int) -> Tuple[int, int]:
+    """Contiguous token range of rank (KV appends stay local to the owner of the tail)."""
+    per = (tokens + world - 1) // world
+    return min(tokens, per * rank), min(tokens, per * (rank + 1))
+
+
+def all_gather_rows(local: torch.Tensor, n_full: int, world: int, out: torch.Tensor = None) -> torch.Tensor:
+    """Gathers 1-D row slices produced by shard_rows() back into the full vector."""
+    per = ((n_full // 128 + world - 1) // world) * 128
+    if per * world == n_full and local.numel() == per:
+        if out is None:
+            out = torch.empty(n_full, dtype=local.dtype, device=local.device)
+        dist.all_gather_into_tensor(out, local)
+        return out
+    pad = torch.zeros(per, dtype=local.dtype, device=local.device)
+    pad[: local.numel()] = local
+    buf = torch.empty(per * world, dtype=local.dtype, device=local.device)
+    dist.all_gather_into_tensor(buf, pad)
+    pieces, r = [], 0
+    for rank in range(world):
+        lo, hi = shard_rows(n_full, rank, world)
+        pieces.append(buf[rank * per: rank * per + (hi - lo)])
+    full = torch.cat(pieces)
+    if out is not None:
+        out.copy_(full)
+        return out
+    return full
+
+
+def combine_argmax(values: torch.Tensor, indices: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """values/indices [world, tokens]: per-rank winners -> global winner per token.  Greedy rule of
+    the reference (kernels-cuda/ops.cu:19-23): strictly greater wins, equal values keep the lower
+    index, NaN never wins, the scan starts from (-inf, 0)."""
+    world, tokens = values.shape
+    best_v = torch.full((tokens,), float("-inf"), dtype=values.dtype, device=values.device)
+    best_i = torch.zeros(tokens, dtype=torch.int64, device=values.device)
+    for r in range(world):
+        v, i = values[r], indices[r].to(torch.int64)
+        better = (v > best_v) | ((v == best_v) & (i < best_i))
+        best_v = torch.where(better, v, best_v)
+        best_i = torch.where(better, i, best_i)
+    return best_v, best_i
+
+
+def gather_argmax(value: torch.Tensor, index: torch.Tensor, world: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """All-gather of this rank's (value [tokens] f32, index [tokens] i32) and the global combine."""
+    pair = torch.stack([value.to(torch.float32), index.to(torch.int32).view(torch.float32)])   # [2, tokens]
+    buf = torch.empty((world * 2, pair.shape[1]), dtype=torch.float32, device=pair.device)   # concatenated on dim 0
+    dist.all_gather_into_tensor(buf, pair)
+    buf = buf.view(world, 2, -1)
+    return combine_argmax(buf[:, 0].contiguous(), buf[:, 1].contiguous().view(torch.int32))
+
+
+def gather_partials(part_m: torch.Tensor, part_l: torch.Tensor, part_o: torch.Tensor, world: int):
+    """All-gather of one (m [H], l [H], o [H, D]) partial per rank into the [H, world(, D)] layout
+    that qwen36_attention_merge_partials consumes."""
+    h, d = part_o.shape
+    packed = torch.cat([part_o, part_m[:, None], part_l[:, None]], dim=1).contiguous()       # [H, D+2]
+    buf = torch.empty((world * h, d + 2), dtype=packed.dtype, device=packed.device)          # concatenated on dim 0
+    dist.all_gather_into_tensor(buf, packed)
+    buf = buf.view(world, h, d + 2).permute(1, 0, 2).contiguous()                             # [H, world, D+2]
+    return buf[:, :, d].contiguous(), buf[:, :, d + 1].contiguous(), buf[:, :, :d].contiguous()
+
+
+class ShardedLmHead:
+    """Vocab-sharded FP8 lm_head with fused greedy argmax."""
+
+    def __init__(self, backend, w_e4m3_full_rows: int, w_local, scales_local, row_lo: int, world: int, max_tokens: int):
+        self.b, self.w, self.s, self.row_lo, self.world = backend, w_local, scales_local, row_lo, world
+        self.ws = backend.lm_head_argmax_workspace(w_local.shape[0], max_tokens, w_local.device)
+
+    def argmax(self, x_bf16):
+        tok, best = self.b.lm_head_fp8_gemv_argmax(self.w, self.s, x_bf16, self.ws, row_offset=self.row_lo)
+        if self.world == 1:
+            return tok.to(torch.int64)
+        return gather_argmax(best, tok, self.world)[1]
+
+
+class ShardedKvAttention:
+    """KV-range-sharded int8 decode attention: this rank holds cache rows [t_lo, t_hi)."""
+
+    def __init__(self, backend, kq_local, vq_local, meta_local, t_lo: int, world: int, q_heads: int, head_dim: int):
+        self.b, self.kq, self.vq, self.meta, self.t_lo, self.world = backend, kq_local, vq_local, meta_local, t_lo, world
+        self.ws = backend.attention_workspace(q_heads, head_dim, kq_local.device)
+
+    def attend(self, q_bf16, position: int):
+        local_end = max(0, min(self.kq.shape[0], position + 1 - self.t_lo))
+        m, l, o = self.b.turboquant_attention_partial(q_bf16, self.kq, self.vq, self.meta, 0, local_end, self.ws)
+        if self.world == 1:
+            return self.b.attention_merge_partials(m[:, None].contiguous(), l[:, None].contiguous(),
+                                                   o[:, None, :].contiguous())
+        pm, pl, po = gather_partials(m, l, o, self.world)
+        return self.b.attention_merge_partials(pm, pl, po)
