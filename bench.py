@@ -193,40 +193,51 @@ class SweepRunner:
 
 def per_shape_cold(backend, torch, sweep, synth):
     """Each decode shape alone, rotating through the 64 layer copies so every launch reads cold
-    weights; 20 warm-up + 192 timed launches between CUDA events."""
+    weights; 192 launches per timing, replayed from a CUDA graph."""
     out = {}
     for idx, (name, n, k) in enumerate(synth.DECODE_SHAPES):
         x = torch.randn(k, device="cuda").to(torch.bfloat16)
         y = torch.empty(n, dtype=torch.bfloat16, device="cuda")
         mats = [layer[idx] for layer in sweep]
-        for i in range(20):
+
+        def call(i, mats=mats, x=x, y=y):
             m = mats[i % len(mats)]
             backend.nvfp4_matvec(x, m[3], m[4], m[5], y)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        reps = 192
-        torch.cuda.synchronize()
-        e0.record()
-        for i in range(reps):
-            m = mats[i % len(mats)]
-            backend.nvfp4_matvec(x, m[3], m[4], m[5], y)
-        e1.record()
-        torch.cuda.synchronize()
-        us = e0.elapsed_time(e1) * 1e3 / reps
+        us = _time_cuda(torch, call, 192, warm=20, backend=backend)
         out[name] = {"n": n, "k": k, "us": round(us, 3), "gbs": round(gemv_bytes(n, k) / us / 1e3, 1)}
     return out
 
 
-def _time_cuda(torch, fn, reps, warm=3):
-    for _ in range(warm):
-        fn(0)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
-    e0.record()
-    for i in range(reps):
+def _time_cuda(torch, fn, reps, warm=3, backend=None):
+    """Microseconds per call of fn(i), timed with CUDA events around a CUDA-graph replay of `reps`
+    calls (so that Python/ctypes launch overhead does not hide short kernels); eager if capture fails."""
+    for i in range(warm):
         fn(i)
+    torch.cuda.synchronize()
+    graph = None
+    if backend is not None:
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                backend.sync_stream()
+                for i in range(reps):
+                    fn(i)
+            backend.sync_stream()
+            graph.replay()
+            torch.cuda.synchronize()
+        except Exception:
+            graph = None
+            backend.sync_stream()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    if graph is not None:
+        graph.replay()
+    else:
+        for i in range(reps):
+            fn(i)
     e1.record()
     torch.cuda.synchronize()
-    return e0.elapsed_time(e1) * 1e3 / reps          # microseconds per call
+    return e0.elapsed_time(e1) * 1e3 / reps
 
 
 def other_configs(backend, torch, synth):
@@ -251,12 +262,12 @@ def other_configs(backend, torch, synth):
             fp4 = torch.empty((m_tok, k // 2), dtype=torch.uint8, device="cuda")
             sf = torch.zeros(backend_tiled_bytes(m_tok, k // 16), dtype=torch.uint8, device="cuda")
             ts = torch.empty(1, dtype=torch.float32, device="cuda")
-            q_us = _time_cuda(torch, lambda i: backend.nvfp4_quantize_rows(x, 0.37, fp4, sf, ts), 10)
+            q_us = _time_cuda(torch, lambda i: backend.nvfp4_quantize_rows(x, 0.37, fp4, sf, ts), 10, backend=backend)
             alpha = synth.WEIGHT_GLOBAL_SCALE * 0.37
             c = torch.empty((m_tok, n_out), dtype=torch.bfloat16, device="cuda")
             reps = 10 if m_tok >= 8192 else 20
             g_us = _time_cuda(torch, lambda i: backend.nvfp4_gemm(ws[i & 1][0], ws[i & 1][1], fp4, sf, alpha,
-                                                                   n_out, m_tok, k, c), reps)
+                                                                   n_out, m_tok, k, c), reps, backend=backend)
             flops = 2.0 * m_tok * n_out * k
             gemm.append({"shape": name, "M": m_tok, "N": n_out, "K": k, "gemm_us": round(g_us, 2),
                          "tflops": round(flops / g_us / 1e6, 1),
@@ -279,9 +290,9 @@ def other_configs(backend, torch, synth):
         tok = torch.empty(m_tok, dtype=torch.int32, device="cuda")
         best = torch.empty(m_tok, dtype=torch.float32, device="cuda")
         byts = rows * cols + 4 * rows + 2 * m_tok * cols + 8 * m_tok
-        us_gemv = _time_cuda(torch, lambda i: backend.lm_head_fp8_gemv(w, sc, xh, logits), 10)
-        us_samp = _time_cuda(torch, lambda i: backend.sample_rows(logits), 10)
-        us_fused = _time_cuda(torch, lambda i: backend.lm_head_fp8_gemv_argmax(w, sc, xh, wsb, 0, tok, best), 10)
+        us_gemv = _time_cuda(torch, lambda i: backend.lm_head_fp8_gemv(w, sc, xh, logits), 10, backend=backend)
+        us_samp = _time_cuda(torch, lambda i: backend.sample_rows(logits), 10, backend=backend)
+        us_fused = _time_cuda(torch, lambda i: backend.lm_head_fp8_gemv_argmax(w, sc, xh, wsb, 0, tok, best), 10, backend=backend)
         lm.append({"M": m_tok, "gemv_us": round(us_gemv, 1), "sample_rows_us": round(us_samp, 1),
                    "fused_us": round(us_fused, 1), "fused_gbs": round(byts / us_fused / 1e3, 1),
                    "gemv_gbs": round(byts / us_gemv / 1e3, 1)})
@@ -296,12 +307,12 @@ def other_configs(backend, torch, synth):
     kq = torch.empty((T, 4, 256), dtype=torch.int8, device="cuda")
     vq = torch.empty_like(kq)
     meta = torch.empty((T, 4, 2), dtype=torch.float32, device="cuda")
-    enc_us = _time_cuda(torch, lambda i: backend.turboquant_encode_kv_rows(k_, v_, kq, vq, meta, 0), 5)
+    enc_us = _time_cuda(torch, lambda i: backend.turboquant_encode_kv_rows(k_, v_, kq, vq, meta, 0), 5, backend=backend)
     enc_bytes = T * (2 * 4 * 256 * 2 + 2 * 4 * 256 + 32)
     wsa = backend.attention_workspace(24, 256, "cuda")
     o_ = torch.empty((24, 256), dtype=torch.bfloat16, device="cuda")
     for ctx in (8192, 32768, 131072):
-        us = _time_cuda(torch, lambda i: backend.turboquant_attention(q_, kq, vq, meta, ctx - 1, wsa, o_), 20)
+        us = _time_cuda(torch, lambda i: backend.turboquant_attention(q_, kq, vq, meta, ctx - 1, wsa, o_), 20, backend=backend)
         byts = ctx * (2 * 4 * 256 + 4 * 2 * 4) + 24 * 256 * 4
         att.append({"ctx": ctx, "us": round(us, 2), "gbs": round(byts / us / 1e3, 1)})
     out["int8_kv_attention"] = att

@@ -24,7 +24,7 @@ using q36::as_ptr;
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
 constexpr int kMaxSplits = 128;
-constexpr int kMinTokensPerSplit = 64;
+constexpr int kMinTokensPerSplit = 256;
 
 // ------------------------------------------------------------------ encode
 
@@ -238,6 +238,177 @@ kv_attention_split_kernel(const __nv_bfloat16 *__restrict__ q, const int8_t *__r
   }
 }
 
+// Fast path for head_dim 256: same grid and outputs as kv_attention_split_kernel, but a warp
+// handles FOUR consecutive tokens per iteration.  All loads of the next four tokens are issued
+// before the current four are consumed (register prefetch).  The 4 x G partial scores of a lane
+// are summed across the warp with a transpose-reduce (31 shuffles for up to 32 values, after which
+// lane 8 t + h holds the score of token t, head h) instead of one 5-step butterfly per score; the
+// online softmax runs once per four tokens, with the per-head state living on lane h.
+template <int G>
+__global__ void __launch_bounds__(kThreads)
+kv_attention_fast_kernel(const __nv_bfloat16 *__restrict__ q, const int8_t *__restrict__ kq,
+                         const int8_t *__restrict__ vq, const float *__restrict__ meta,
+                         float *__restrict__ part_o, float *__restrict__ part_m, float *__restrict__ part_l,
+                         size_t t_begin, size_t t_end, uint32_t kv_heads, uint32_t q_per_kv, uint32_t n_splits) {
+  constexpr uint32_t D = 256;
+  __shared__ float s_m[kWarps][8], s_l[kWarps][8];
+  __shared__ float s_o[G][D];
+
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+  const uint32_t head0 = blockIdx.x * G;
+  const uint32_t kvh = head0 / q_per_kv;
+  const uint32_t split = blockIdx.y;
+  const size_t total = t_end - t_begin;
+  const size_t per_split = q36::div_ceil(total, n_splits);
+  const size_t s_begin = t_begin + min(total, per_split * split);
+  const size_t s_end = t_begin + min(total, per_split * (split + 1));
+  const float sm_scale = 0.0625f * 1.4426950408889634f;        // rsqrt(256) * log2(e)
+
+  float qv[G][8];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    const uint4 p = __ldg(reinterpret_cast<const uint4 *>(q + static_cast<size_t>(head0 + g) * D) + lane);
+    const uint32_t w[4] = {p.x, p.y, p.z, p.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      qv[g][2 * i] = __uint_as_float(w[i] << 16);
+      qv[g][2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
+  float o[G][8];
+#pragma unroll
+  for (int g = 0; g < G; ++g)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[g][i] = 0.f;
+  float m_run = -INFINITY, l_run = 0.f;          // state of head (lane & 7), identical on its 4 lanes
+
+  struct Batch { uint2 k[4], v[4]; float2 sc[4]; };
+  auto load = [&](Batch &b, size_t t0) {
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const size_t tok = t0 + t;
+      if (tok < s_end) {
+        const size_t row = tok * kv_heads + kvh;
+        b.k[t] = __ldcs(reinterpret_cast<const uint2 *>(kq + row * D) + lane);
+        b.v[t] = __ldcs(reinterpret_cast<const uint2 *>(vq + row * D) + lane);
+        b.sc[t] = __ldg(reinterpret_cast<const float2 *>(meta) + row);
+      } else {
+        b.k[t] = make_uint2(0x0, 0x0); b.v[t] = make_uint2(0, 0); b.sc[t] = make_float2(0.f, 0.f);
+      }
+    }
+  };
+
+  const size_t stride = static_cast<size_t>(kWarps) * 4;
+  Batch cur, nxt;
+  size_t t0 = s_begin + static_cast<size_t>(warp) * 4;
+  if (t0 < s_end) load(cur, t0);
+  for (; t0 < s_end; t0 += stride) {
+    if (t0 + stride < s_end) load(nxt, t0 + stride);
+    // ---- partial scores: v[8 t + g] = sum over this lane's 8 dims of q[g] * k[t]
+    float v[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = 0.f;
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      float kf[8], t4[4];
+      s8x4_to_f32(cur.k[t].x, t4); kf[0] = t4[0]; kf[1] = t4[1]; kf[2] = t4[2]; kf[3] = t4[3];
+      s8x4_to_f32(cur.k[t].y, t4); kf[4] = t4[0]; kf[5] = t4[1]; kf[6] = t4[2]; kf[7] = t4[3];
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        float a = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) a = fmaf(qv[g][i], kf[i], a);
+        v[8 * t + g] = a;
+      }
+    }
+    // ---- transpose-reduce: afterwards v[0] on lane L is the warp total of value index L
+#pragma unroll
+    for (int width = 16; width >= 1; width >>= 1) {
+      const bool upper = (lane & width) != 0;
+#pragma unroll
+      for (int i = 0; i < width; ++i) {
+        const float send = upper ? v[i] : v[i + width];
+        const float keep = upper ? v[i + width] : v[i];
+        v[i] = keep + __shfl_xor_sync(0xffffffffu, send, width);
+      }
+    }
+    // ---- online softmax for (token = lane >> 3, head = lane & 7)
+    const uint32_t tl = lane >> 3;
+    const bool valid = (lane & 7u) < G && t0 + tl < s_end;
+    const float kscale = tl == 0 ? cur.sc[0].x : tl == 1 ? cur.sc[1].x : tl == 2 ? cur.sc[2].x : cur.sc[3].x;
+    const float s_log2 = valid ? v[0] * kscale * sm_scale : -INFINITY;
+    float tile_max = fmaxf(s_log2, __shfl_xor_sync(0xffffffffu, s_log2, 8));
+    tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 16));
+    const float m_new = fmaxf(m_run, tile_max);
+    const float corr = m_new == -INFINITY ? 1.f : exp2f(m_run - m_new);      // exp2(-inf) = 0 on first use
+    const float p = valid ? exp2f(s_log2 - m_new) : 0.f;
+    float p_sum = p + __shfl_xor_sync(0xffffffffu, p, 8);
+    p_sum += __shfl_xor_sync(0xffffffffu, p_sum, 16);
+    l_run = l_run * corr + p_sum;
+    m_run = m_new;
+    // ---- P V: every lane needs corr[g] and p[t][g]
+    float vf[4][8];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      float t4[4];
+      s8x4_to_f32(cur.v[t].x, t4); vf[t][0] = t4[0]; vf[t][1] = t4[1]; vf[t][2] = t4[2]; vf[t][3] = t4[3];
+      s8x4_to_f32(cur.v[t].y, t4); vf[t][4] = t4[0]; vf[t][5] = t4[1]; vf[t][6] = t4[2]; vf[t][7] = t4[3];
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const float cg = __shfl_sync(0xffffffffu, corr, g);
+      if (cg != 1.f) {                      // warp-uniform
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[g][i] *= cg;
+      }
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const float pv = __shfl_sync(0xffffffffu, p, 8 * t + g) * cur.sc[t].y;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[g][i] = fmaf(pv, vf[t][i], o[g][i]);
+      }
+    }
+    cur = nxt;
+  }
+
+  // ---- merge the warps of the CTA (same scheme as the general kernel)
+  if (lane < G) { s_m[warp][lane] = m_run; s_l[warp][lane] = l_run; }
+  __syncthreads();
+  float wgt[G];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    float M = -INFINITY;
+    for (int w = 0; w < kWarps; ++w) M = fmaxf(M, s_m[w][g]);
+    const float mine = s_m[warp][g];
+    wgt[g] = mine == -INFINITY ? 0.f : exp2f(mine - M);
+  }
+  for (int w = 0; w < kWarps; ++w) {
+    if (warp == w) {
+#pragma unroll
+      for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          float *dst = &s_o[g][lane * 8 + i];
+          *dst = w == 0 ? wgt[g] * o[g][i] : fmaf(wgt[g], o[g][i], *dst);
+        }
+    }
+    __syncthreads();
+  }
+  for (uint32_t idx = threadIdx.x; idx < G * D; idx += kThreads) {
+    const uint32_t g = idx / D, d = idx % D;
+    const size_t slot = static_cast<size_t>(head0 + g) * n_splits + split;
+    part_o[slot * D + d] = s_o[g][d];
+    if (d == 0) {
+      float M = -INFINITY, den = 0.f;
+      for (int w = 0; w < kWarps; ++w) M = fmaxf(M, s_m[w][g]);
+      for (int w = 0; w < kWarps; ++w)
+        den = fmaf(s_m[w][g] == -INFINITY ? 0.f : exp2f(s_m[w][g] - M), s_l[w][g], den);
+      part_m[slot] = M * 0.6931471805599453f;
+      part_l[slot] = den;
+    }
+  }
+}
+
 // Merge n_parts partials per q head.  FINAL: write bf16 output (sum w*o /
 // sum w*l, 0 when the denominator is 0).  !FINAL: write one combined partial.
 template <bool FINAL>
@@ -246,22 +417,36 @@ kv_merge_kernel(const float *__restrict__ part_o, const float *__restrict__ part
                 const float *__restrict__ part_l, uint32_t n_parts, uint32_t head_dim,
                 __nv_bfloat16 *__restrict__ out, float *__restrict__ out_o, float *__restrict__ out_m,
                 float *__restrict__ out_l) {
+  __shared__ float s_w[kThreads];        // weight of every part (n_parts <= kThreads)
+  __shared__ float s_red[kWarps];
   const size_t qh = blockIdx.x;
   const float *pm = part_m + qh * n_parts, *pl = part_l + qh * n_parts;
   const float *po = part_o + qh * n_parts * head_dim;
-  float M = -INFINITY;
-  for (uint32_t s = 0; s < n_parts; ++s) M = fmaxf(M, __ldcg(pm + s));
-  float den = 0.f;
-  for (uint32_t s = 0; s < n_parts; ++s) {
-    const float ms = __ldcg(pm + s);
-    den = fmaf(ms == -INFINITY ? 0.f : __expf(ms - M), __ldcg(pl + s), den);
-  }
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+
+  // one part per thread: global maximum, weights, weighted denominator
+  const float my_m = threadIdx.x < n_parts ? __ldcg(pm + threadIdx.x) : -INFINITY;
+  const float my_l = threadIdx.x < n_parts ? __ldcg(pl + threadIdx.x) : 0.f;
+  float M = my_m;
+  for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
+  if (lane == 0) s_red[warp] = M;
+  __syncthreads();
+  M = s_red[0];
+  for (int w = 1; w < kWarps; ++w) M = fmaxf(M, s_red[w]);
+  const float wgt = my_m == -INFINITY ? 0.f : __expf(my_m - M);
+  s_w[threadIdx.x] = wgt;
+  float den = wgt * my_l;
+  for (int off = 16; off > 0; off >>= 1) den += __shfl_xor_sync(0xffffffffu, den, off);
+  __syncthreads();
+  if (lane == 0) s_red[warp] = den;
+  __syncthreads();
+  den = 0.f;
+  for (int w = 0; w < kWarps; ++w) den += s_red[w];
+
   for (uint32_t d = threadIdx.x; d < head_dim; d += kThreads) {
     float acc = 0.f;
-    for (uint32_t s = 0; s < n_parts; ++s) {
-      const float ms = __ldcg(pm + s);
-      acc = fmaf(ms == -INFINITY ? 0.f : __expf(ms - M), __ldcg(po + static_cast<size_t>(s) * head_dim + d), acc);
-    }
+#pragma unroll 8
+    for (uint32_t s = 0; s < n_parts; ++s) acc = fmaf(s_w[s], __ldcg(po + static_cast<size_t>(s) * head_dim + d), acc);
     if (FINAL) out[qh * head_dim + d] = __float2bfloat16(den > 0.f ? __fdiv_rn(acc, den) : 0.f);
     else out_o[qh * head_dim + d] = acc;
   }
@@ -269,6 +454,7 @@ kv_merge_kernel(const float *__restrict__ part_o, const float *__restrict__ part
 }
 
 struct Scratch { float *o, *m, *l; };
+bool g_use_fast_attention = true;
 
 // Scratch for qwen36_turboquant_attention_static: lives in the library image, so every GPU that
 // loads the library holds these 4 MiB until the process exits.  Sized for
@@ -305,6 +491,11 @@ int launch_split_g(const __nv_bfloat16 *q, const int8_t *kq, const int8_t *vq, c
 #define Q36_GO(DPL, VEC)                                                                              \
   kv_attention_split_kernel<G, DPL, VEC><<<grid, kThreads, 0, q36::stream()>>>(                        \
       q, kq, vq, meta, sc.o, sc.m, sc.l, t_begin, t_end, KV, q_per_kv, D, n_splits)
+  if (D == 256 && aligned && (reinterpret_cast<uintptr_t>(q) & 15u) == 0 && g_use_fast_attention) {
+    kv_attention_fast_kernel<G><<<grid, kThreads, 0, q36::stream()>>>(q, kq, vq, meta, sc.o, sc.m, sc.l, t_begin,
+                                                                       t_end, KV, q_per_kv, n_splits);
+    return q36::launch_status();
+  }
   if (D == 256 && aligned) Q36_GO(8, true);
   else if (D == 128 && aligned) Q36_GO(4, true);
   else if (D == 64) Q36_GO(2, true);
@@ -374,6 +565,9 @@ extern "C" int qwen36_turboquant_encode_kv(const qwen36_turboquant_encode_spec_t
   rows.shape = spec->shape;
   return qwen36_turboquant_encode_kv_rows(&rows);
 }
+
+// Test hook: 0 routes head_dim 256 through the general kernel instead of the 4-token fast path.
+extern "C" void qwen36_turboquant_attention_set_fast(int enable) { g_use_fast_attention = enable != 0; }
 
 extern "C" size_t qwen36_turboquant_attention_workspace_bytes(size_t q_heads, size_t head_dim) {
   return scratch_bytes(q_heads, head_dim);
@@ -470,7 +664,8 @@ extern "C" int qwen36_turboquant_attention_static(const qwen36_turboquant_attent
 
 extern "C" int qwen36_attention_merge_partials(const qwen36_attention_merge_spec_t *spec) {
   if (spec == nullptr) return QWEN36_STATUS_NULL_POINTER;
-  if (spec->q_heads == 0 || spec->head_dim == 0 || spec->n_parts == 0 || spec->partial_acc_f32.ptr == 0 ||
+  if (spec->q_heads == 0 || spec->head_dim == 0 || spec->n_parts == 0 || spec->n_parts > kThreads ||
+      spec->partial_acc_f32.ptr == 0 ||
       spec->partial_max_f32.ptr == 0 || spec->partial_denom_f32.ptr == 0 || spec->output_bf16.ptr == 0)
     return QWEN36_STATUS_INVALID_ARGUMENT;
   kv_merge_kernel<true><<<static_cast<unsigned>(spec->q_heads), kThreads, 0, q36::stream()>>>(

@@ -128,3 +128,21 @@ def test_long_context_softmax_property(backend):
     out = backend.turboquant_attention(q, kq, vq, meta, T - 1, ws).float()
     vd = (vq[0].float() * meta[0, :, 1:2]).repeat_interleave(6, dim=0)
     assert torch.allclose(out, vd, rtol=1e-2, atol=1e-2)
+
+
+def test_general_kernel_agrees_with_fast_path(backend):
+    """head_dim 256 has a 4-token fast path; the general kernel must give the same attention."""
+    rng = np.random.default_rng(33)
+    q, k, v = synth.qkv(rng, 1500)
+    (kq, vq, meta), (kq_o, vq_o, meta_o) = encode_both(backend, k, v, 1500, 4, 256)
+    ws = backend.attention_workspace(24, 256, "cuda")
+    qd = to_dev(q)
+    fast = backend.turboquant_attention(qd, kq, vq, meta, 1499, ws).clone()
+    backend.lib.qwen36_turboquant_attention_set_fast(0)
+    try:
+        general = backend.turboquant_attention(qd, kq, vq, meta, 1499, ws).clone()
+    finally:
+        backend.lib.qwen36_turboquant_attention_set_fast(1)
+    want = synth.bf16_bits_to_f32(orc.kv_attention(q, kq_o, vq_o, meta_o, 1499))
+    for got in (fast, general):
+        assert rel_l2(synth.bf16_bits_to_f32(bf16_host(got)), want) <= 1e-2
