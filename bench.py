@@ -425,12 +425,20 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     backend = CudaBackend()
     layers = args.layers
-    sweep = build_sweep(backend, torch, synth, rank, world, layers, seed=1234)
-    runner = SweepRunner(backend, torch, sweep, world, dist)
+    # The M = 1 decode sweep is a chain of 384 dependent GEMVs of a few microseconds each: splitting
+    # every matrix across GPUs puts a collective on each link of that chain and is slower than one
+    # GPU (measured, `--workload sweep_split`).  At N > 1 the default is therefore N independent
+    # decode streams, one full model replica per GPU, no data-path collective ("replicas only").
+    split = world > 1 and args.workload == "sweep_split"
+    shard_world = world if split else 1
+    sweep = build_sweep(backend, torch, synth, rank if split else 0, shard_world, layers, seed=1234)
+    runner = SweepRunner(backend, torch, sweep, shard_world, dist)
     step_bytes = layers * sum(gemv_bytes(n, k) for _, n, k in synth.DECODE_SHAPES)
+    if world > 1 and not split:
+        step_bytes *= world                      # every rank streams its own replica
     launches_per_step = layers * len(synth.DECODE_SHAPES)
 
-    gen = torch.Generator(device="cuda").manual_seed(99)
+    gen = torch.Generator(device="cuda").manual_seed(99 + (0 if split else rank))     # replicas: own hidden state
     x_dev = torch.randn(5120, generator=gen, device="cuda").to(torch.bfloat16)
     x_host = x_dev.cpu().pin_memory()
     y_host = torch.empty(5120, dtype=torch.bfloat16).pin_memory()
@@ -471,7 +479,7 @@ def run_ours(args):
     e1.record()
     barrier()
     ms = e0.elapsed_time(e1)
-    gpu_launches = per_step * args.steps
+    gpu_launches = per_step * args.steps * (world if (world > 1 and not split) else 1)
     clocks = sampler.stop() if rank == 0 else None
 
     # ---- end to end: host buffers in, host result out, every step ---------------
@@ -496,25 +504,44 @@ def run_ours(args):
     extra = {}
     if rank == 0 and world == 1 and not args.no_extras:
         extra["per_shape_cold"] = per_shape_cold(backend, torch, sweep, synth)
+        run_step = None
+        try:
+            del runner.graph
+        except AttributeError:
+            pass
         del runner, sweep
         torch.cuda.empty_cache()
         extra.update(other_configs(backend, torch, synth))
+    if world > 1 and not split and not args.no_extras:
+        # north_star's sharded paths at this GPU count, in the same line (strong scaling each)
+        try:
+            del runner.graph
+        except AttributeError:
+            pass
+        run_step = None
+        del runner, sweep
+        torch.cuda.empty_cache()
+        extra["sharded"] = [measure_sharded(w, 0, 10, 3, backend, torch, dist, world, rank)
+                            for w in ("lm_head", "attention", "prefill")]
     if rank == 0:
         peak, peak_kind = measured_peaks()
         ms_per_step = ms / args.steps
         value = step_bytes / (ms_per_step * 1e-3) / 1e9
         e2e_value = step_bytes / (ms_e2e / args.steps * 1e-3) / 1e9
+        per_gpu_bytes = step_bytes // (world if (world > 1 and not split) else 1)
         launch_us = ms_per_step * 1e3 / launches_per_step
-        achieved = (step_bytes / launches_per_step) / (launch_us * 1e-6) / 1e9
+        achieved = (per_gpu_bytes / launches_per_step) / (launch_us * 1e-6) / 1e9
         line = {
             "metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
-            "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "e2m1 x bf16 -> f32",
+            "scaling": "strong" if split else "weak", "vs_baseline": None, "dtype": "e2m1 x bf16 -> f32",
             "data": "synthetic",
             "config": {"workload": f"config 1: NVFP4 W4A16 decode GEMV sweep, {layers} layers x 6 shapes, M=1",
                        "launch": "CUDA graph replay of the C-ABI calls" if use_graph else "eager C-ABI calls",
                        "bytes_per_step": step_bytes, "l2": "inputs larger than L2 (13.4 GB of weights per step)",
-                       "parallelism": "1 GPU" if world == 1 else f"output rows split {world}-way + NCCL all-gather per GEMV"},
+                       "parallelism": "1 GPU" if world == 1 else (
+                           f"output rows split {world}-way + NCCL all-gather per GEMV" if split else
+                           f"replicas only: {world} independent decode streams, one model replica per GPU, no collective")},
             "gpu_launches": gpu_launches,
             "e2e": {"value": round(e2e_value, 1), "unit": "GB/s", "h2d_bytes_per_step": x_host.numel() * 2,
                     "d2h_bytes_per_step": y_host.numel() * 2, "ms_per_step": round(ms_e2e / args.steps, 4),
@@ -522,7 +549,7 @@ def run_ours(args):
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(achieved / peak, 4), "traffic": None, "peak_kind": peak_kind,
                          "kernel": "nvfp4_matvec_kernel", "launch_us": round(launch_us, 3),
-                         "bytes_per_launch": step_bytes // launches_per_step,
+                         "bytes_per_launch": per_gpu_bytes // launches_per_step,
                          "frac_of_nominal_8TBs": round(achieved / 8000.0, 4)},
             "clocks": clocks,
         }
@@ -531,26 +558,22 @@ def run_ours(args):
         line.update(extra)
         print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # Leave without tearing NCCL down: destroying a communicator that captured graphs still
+        # reference was seen to block at exit.  Everything has been synchronised and printed.
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
-def run_sharded_workload(args):
-    """--workload lm_head | attention | prefill at N GPUs (strong scaling: the total work is fixed,
-    each rank holds 1/N of the vocab rows, of the KV range, or of the weight rows)."""
-    import torch
-    import torch.distributed as dist
+def measure_sharded(workload, tokens, steps, warmup, b, torch, dist, world, rank):
+    """One sharded configuration at `world` GPUs (strong scaling: the total work is fixed, each rank
+    holds 1/world of the vocab rows, of the KV range, or of the weight rows).  Returns a dict."""
     from speedoza_b200 import shard, synth
-    from speedoza_b200.backend import CudaBackend
-    world = int(os.environ.get("WORLD_SIZE", "1")); rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    b = CudaBackend()
     gen = torch.Generator(device="cuda").manual_seed(4321)
-    extra = {}
-    if args.workload == "lm_head":
-        m_tok = args.tokens or 4
+    if workload == "lm_head":
+        m_tok = tokens or 4
         rows, cols = synth.VOCAB, synth.HIDDEN
         lo, hi = shard.shard_rows(rows, rank, world)
         gen.manual_seed(100 + rank)
@@ -560,27 +583,31 @@ def run_sharded_workload(args):
         x = torch.randn((m_tok, cols), generator=gen, device="cuda").to(torch.bfloat16)
         head = shard.ShardedLmHead(b, rows, w, sc, lo, world, m_tok)
         step = lambda: head.argmax(x)
-        work, unit, name = rows * cols + 4 * rows + 2 * m_tok * cols + 8 * m_tok, "GB/s", \
-            f"config 3: FP8 lm_head 248320x5120 + fused greedy argmax, M={m_tok}, vocab split {world}-way + all-gather of (value, index)"
+        work, unit = rows * cols + 4 * rows + 2 * m_tok * cols + 8 * m_tok, "GB/s"
+        name = (f"config 3: FP8 lm_head 248320x5120 + fused greedy argmax, M={m_tok}, vocab split {world}-way "
+                "+ all-gather of (value, index)")
         dtype = "e4m3 x bf16 -> f32"
-    elif args.workload == "attention":
-        ctx = args.tokens or 131072
+    elif workload == "attention":
+        ctx = tokens or 131072
         lo, hi = shard.shard_tokens(ctx, rank, world)
         gen.manual_seed(200 + rank)
         k_ = torch.randn((hi - lo, 4, 256), generator=gen, device="cuda").to(torch.bfloat16)
         v_ = torch.randn((hi - lo, 4, 256), generator=gen, device="cuda").to(torch.bfloat16)
-        kq = torch.empty((hi - lo, 4, 256), dtype=torch.int8, device="cuda"); vq = torch.empty_like(kq)
+        kq = torch.empty((hi - lo, 4, 256), dtype=torch.int8, device="cuda")
+        vq = torch.empty_like(kq)
         meta = torch.empty((hi - lo, 4, 2), dtype=torch.float32, device="cuda")
         b.turboquant_encode_kv_rows(k_, v_, kq, vq, meta, 0)
+        del k_, v_
         gen.manual_seed(7)
         q_ = torch.randn((24, 256), generator=gen, device="cuda").to(torch.bfloat16)
         att = shard.ShardedKvAttention(b, kq, vq, meta, lo, world, 24, 256)
         step = lambda: att.attend(q_, ctx - 1)
-        work, unit, name = ctx * (2 * 4 * 256 + 32) + 24 * 256 * 4, "GB/s", \
-            f"config 4: int8 KV decode attention, ctx {ctx}, 24 q / 4 kv heads, KV range split {world}-way + all-gather of (m, l, o)"
+        work, unit = ctx * (2 * 4 * 256 + 32) + 24 * 256 * 4, "GB/s"
+        name = (f"config 4: int8 KV decode attention, ctx {ctx}, 24 q / 4 kv heads, KV range split {world}-way "
+                "+ all-gather of (m, l, o)")
         dtype = "int8 x bf16 -> f32"
     else:
-        m_tok = args.tokens or 8192
+        m_tok = tokens or 8192
         n_out, k = 34816, 5120
         lo, hi = shard.shard_rows(n_out, rank, world)
         gen.manual_seed(300 + rank)
@@ -596,20 +623,21 @@ def run_sharded_workload(args):
         def step():
             b.nvfp4_quantize_rows(x, 0.37, fp4, sfb, ts)          # replicated on every rank
             return b.nvfp4_gemm(packed, a_sf, fp4, sfb, 0.37 / 2688.0, hi - lo, m_tok, k, c)
-        work, unit, name = 2.0 * m_tok * n_out * k, "TFLOP/s", \
-            f"config 2: NVFP4 prefill (quantise + tcgen05 GEMM) gate_up 34816x5120, M={m_tok}, weight rows split {world}-way, output kept sharded"
+        work, unit = 2.0 * m_tok * n_out * k, "TFLOP/s"
+        name = (f"config 2: NVFP4 prefill (quantise + tcgen05 GEMM) gate_up 34816x5120, M={m_tok}, weight rows "
+                f"split {world}-way, output kept sharded")
         dtype = "nvfp4 x nvfp4 -> f32"
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
-    for _ in range(max(3, args.warmup)):
+    for _ in range(max(3, warmup)):
         step()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
+    for _ in range(steps):
         step()
     e1.record()
     barrier()
@@ -618,15 +646,34 @@ def run_sharded_workload(args):
         t = torch.tensor([ms], dtype=torch.float64, device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t[0])
-    if rank == 0:
-        per = ms / args.steps
-        value = work / (per * 1e-3) / (1e9 if unit == "GB/s" else 1e12)
-        print(json.dumps({"metric": METRIC, "value": round(value, 1), "unit": unit, "n_gpus": world, "steps": args.steps,
-                          "warmup": max(3, args.warmup), "ms_per_step": round(per, 4), "higher_is_better": True,
-                          "scaling": "strong", "vs_baseline": None, "dtype": dtype, "data": "synthetic",
-                          "config": {"workload": name}}), flush=True)
+    per = ms / steps
+    value = work / (per * 1e-3) / (1e9 if unit == "GB/s" else 1e12)
+    return {"workload": name, "value": round(value, 1), "unit": unit, "ms_per_step": round(per, 4), "dtype": dtype}
+
+
+def run_sharded_workload(args):
+    """--workload lm_head | attention | prefill at N GPUs."""
+    import torch
+    import torch.distributed as dist
+    from speedoza_b200.backend import CudaBackend
+    world = int(os.environ.get("WORLD_SIZE", "1")); rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
     if world > 1:
-        dist.destroy_process_group()
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    b = CudaBackend()
+    r = measure_sharded(args.workload, args.tokens, args.steps, args.warmup, b, torch, dist, world, rank)
+    if rank == 0:
+        print(json.dumps({"metric": METRIC, "value": r["value"], "unit": r["unit"], "n_gpus": world, "steps": args.steps,
+                          "warmup": max(3, args.warmup), "ms_per_step": r["ms_per_step"], "higher_is_better": True,
+                          "scaling": "strong", "vs_baseline": None, "dtype": r["dtype"], "data": "synthetic",
+                          "config": {"workload": r["workload"]}}), flush=True)
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 # --------------------------------------------------------------------------- reference arm
@@ -692,7 +739,8 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
-    ap.add_argument("--workload", default="sweep", choices=["sweep", "lm_head", "attention", "prefill"])
+    ap.add_argument("--workload", default="sweep",
+                    choices=["sweep", "sweep_split", "lm_head", "attention", "prefill"])
     ap.add_argument("--tokens", type=int, default=0, help="M (lm_head, prefill) or context length (attention)")
     ap.add_argument("--profile-case", default=None, help="run one small kernel case (for ncu) and exit")
     args = ap.parse_args()
@@ -700,7 +748,7 @@ def main():
         profile_case(args.profile_case)
     elif args.impl == "reference":
         run_reference(args)
-    elif args.workload != "sweep":
+    elif args.workload not in ("sweep", "sweep_split"):
         run_sharded_workload(args)
     else:
         if args.warmup < 3:
