@@ -12,8 +12,9 @@
 // is exactly the shared-memory image that tcgen05.cp 32x128b.warpx4 turns into the TMEM
 // scale operand, so scales go HBM -> smem -> TMEM without being touched by a thread.
 //
-// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM allocator + MMA issuer,
-// warps 2..5 = epilogue (TMEM -> registers -> alpha, bf16 -> global).  CTAs are persistent over
+// Warp roles (224 threads): warp 0 = TMA producer, warp 1 = TMEM allocator + MMA issuer,
+// warps 2..5 = epilogue (TMEM -> registers -> alpha, bf16 -> global), warp 6 = scale copier
+// (tcgen05.cp shared memory -> TMEM).  CTAs are persistent over
 // (row block, token block) tiles; with two accumulator stages the epilogue of one tile overlaps
 // the MMAs of the next.  No cluster, no multicast: every CTA loads its own tiles.
 //
@@ -27,12 +28,15 @@
 namespace q36 {
 namespace {
 
-constexpr uint32_t kThreads = 192;
+constexpr uint32_t kThreads = 224;
 constexpr uint32_t kBM = 128;
 constexpr uint32_t kBKBytes = 128;            // 256 fp4 values
 constexpr uint32_t kSpinLimit = 1u << 26;
 
 __device__ unsigned int g_gemm_error = 0;
+int g_force_bn = 0;
+__device__ unsigned int g_debug = 0;        // timing experiments only (results become wrong): 1 skip scale copies, 2 skip stores
+__device__ unsigned int g_prefetch = 0;     // stages of L2 prefetch ahead of the shared-memory ring
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -59,6 +63,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
 __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, uint32_t c0, uint32_t c1, uint64_t *bar) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+// L2 prefetch of a tile (no shared memory): the producer asks for the weight tile it will load a
+// few stages later, so that the load that fills shared memory hits L2 instead of waiting on HBM.
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap *map, uint32_t c0, uint32_t c1) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(c0), "r"(c1) : "memory");
 }
 __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -139,7 +148,8 @@ nvfp4_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint64_t *full = reinterpret_cast<uint64_t *>(smem);                   // [kStages]
   uint64_t *empty = full + 8;                                            // [kStages]
-  uint64_t *acc_full = empty + 8;                                        // [kAccStages]
+  uint64_t *sf_full = empty + 8;                                         // [kStages] scales are in TMEM
+  uint64_t *acc_full = sf_full + 8;                                      // [kAccStages]
   uint64_t *acc_empty = acc_full + 2;                                    // [kAccStages]
   uint32_t *tmem_base_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
   uint8_t *stages = smem + 1024;
@@ -152,7 +162,7 @@ nvfp4_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   const uint32_t sf_tok_blocks = (n + 127u) / 128u;                      // 128-token scale blocks that exist
 
   if (threadIdx.x == 0) {
-    for (uint32_t s = 0; s < C::kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (uint32_t s = 0; s < C::kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); mbar_init(&sf_full[s], 1); }
     for (uint32_t s = 0; s < C::kAccStages; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 4); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -165,15 +175,26 @@ nvfp4_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_base_slot;
   const uint32_t tmem_sf = tmem_base + C::kAccStages * C::kAccCols;
+  const uint32_t dbg = g_debug;
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
       uint32_t g = 0;
       bool dead = false;
+      // prefetch cursor: runs `g_prefetch` stages ahead of the load cursor over the same sequence
+      const uint32_t ahead = g_prefetch;
+      uint32_t pf_tile = blockIdx.x, pf_kb = 0;
+      auto prefetch_one = [&]() {
+        if (pf_tile >= tiles) return;
+        tma_prefetch_2d(&map_a, pf_kb * kBKBytes, (pf_tile / n_blocks) * kBM);
+        if (++pf_kb == k_blocks) { pf_kb = 0; pf_tile += gridDim.x; }
+      };
+      for (uint32_t i = 0; i < ahead; ++i) prefetch_one();
       for (uint32_t tile = blockIdx.x; tile < tiles && !dead; tile += gridDim.x) {
         const uint32_t nb = tile % n_blocks, mb = tile / n_blocks;
         for (uint32_t kb = 0; kb < k_blocks; ++kb, ++g) {
+          if (ahead) prefetch_one();
           const uint32_t s = g % C::kStages, ph = (g / C::kStages) & 1u;
           if (!mbar_wait(&empty[s], ph ^ 1u)) { dead = true; break; }
           uint8_t *st = stages + s * C::kStageBytes;
@@ -214,14 +235,8 @@ nvfp4_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t st = smem_u32(stages + s * C::kStageBytes);
           const uint32_t sfa_t = tmem_sf + s * C::kSfCols, sfb_t = sfa_t + 16u;
-#pragma unroll
-          for (uint32_t kk = 0; kk < 4; ++kk) {
-            tmem_cp_sf(sfa_t + kk * 4u, desc_sf(st + C::kABytes + C::kBBytes + kk * 512u));
-#pragma unroll
-            for (uint32_t t = 0; t < C::kSfbTiles; ++t)
-              tmem_cp_sf(sfb_t + (kk * C::kSfbTiles + t) * 4u,
-                         desc_sf(st + C::kABytes + C::kBBytes + C::kSfaBytes + t * 2048u + kk * 512u));
-          }
+          if (!mbar_wait(&sf_full[s], ph)) { dead = true; break; }     // the copier warp has put this stage's scales in TMEM
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
           for (uint32_t kk = 0; kk < 4; ++kk)
             mma_mxf4nvf4(d_tmem, desc_sw128(st + kk * 32u), desc_sw128(st + C::kABytes + kk * 32u), C::kIdesc,
@@ -229,6 +244,34 @@ nvfp4_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           mma_commit(&empty[s]);                 // frees the smem stage once these MMAs have read it
         }
         if (!dead) mma_commit(&acc_full[as]);    // accumulator complete
+      }
+    }
+  } else if (warp == 6) {
+    // ---------------------------------------------------------------- scale copier
+    // Moves each stage's scale tiles shared memory -> TMEM from its own instruction stream, so that
+    // the copies of stage s+1 can run while the MMAs of stage s execute.
+    if (lane == 0) {
+      uint32_t g = 0;
+      bool dead = false;
+      for (uint32_t tile = blockIdx.x; tile < tiles && !dead; tile += gridDim.x) {
+        for (uint32_t kb = 0; kb < k_blocks; ++kb, ++g) {
+          const uint32_t s = g % C::kStages, ph = (g / C::kStages) & 1u;
+          if (!mbar_wait(&full[s], ph)) { dead = true; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t st = smem_u32(stages + s * C::kStageBytes);
+          const uint32_t sfa_t = tmem_sf + s * C::kSfCols, sfb_t = sfa_t + 16u;
+          if (!(dbg & 1u) || g == 0) {
+#pragma unroll
+            for (uint32_t kk = 0; kk < 4; ++kk) {
+              tmem_cp_sf(sfa_t + kk * 4u, desc_sf(st + C::kABytes + C::kBBytes + kk * 512u));
+#pragma unroll
+              for (uint32_t t = 0; t < C::kSfbTiles; ++t)
+                tmem_cp_sf(sfb_t + (kk * C::kSfbTiles + t) * 4u,
+                           desc_sf(st + C::kABytes + C::kBBytes + C::kSfaBytes + t * 2048u + kk * 512u));
+            }
+          }
+          mma_commit(&sf_full[s]);
+        }
       }
     }
   } else {
@@ -260,7 +303,7 @@ nvfp4_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             const float got = __shfl_xor_sync(0xffffffffu, send, 1);
             const uint32_t tok = tok0 + c0 + j + (lane & 1u);
             const __nv_bfloat162 v = (lane & 1u) ? __floats2bfloat162_rn(got, mine_b) : __floats2bfloat162_rn(mine_a, got);
-            if (tok < n) *reinterpret_cast<__nv_bfloat162 *>(c + static_cast<size_t>(tok) * m + (row & ~1u)) = v;
+            if (tok < n && !(dbg & 2u)) *reinterpret_cast<__nv_bfloat162 *>(c + static_cast<size_t>(tok) * m + (row & ~1u)) = v;
           }
         }
       } else {
@@ -359,12 +402,26 @@ int nvfp4_gemm_tc(const qwen36_nvfp4_gemm_spec_t *s, float alpha) {
   if (s->m % kBM != 0 || s->k % 256 != 0 || s->m > (1u << 30) || s->n > (1u << 30) || s->k > (1u << 30) ||
       ((s->a_fp4.ptr | s->b_fp4.ptr | s->a_scale.ptr | s->b_scale.ptr) & 15u) != 0 || (s->c_bf16.ptr & 3u) != 0)
     return QWEN36_STATUS_NOT_IMPLEMENTED;
+  const int forced = g_force_bn;
+  if (forced == 128 && s->n > 128) return launch<128>(s, alpha);
   if (s->n <= 8) return launch<8>(s, alpha);
   if (s->n <= 16) return launch<16>(s, alpha);
   if (s->n <= 32) return launch<32>(s, alpha);
   if (s->n <= 64) return launch<64>(s, alpha);
   if (s->n <= 128) return launch<128>(s, alpha);
   return launch<256>(s, alpha);
+}
+
+// Tuning hook: 128 forces 128-token tiles (two accumulator stages) for large n; 0 = default.
+extern "C" void qwen36_nvfp4_gemm_force_bn(int bn) { g_force_bn = bn; }
+extern "C" void qwen36_nvfp4_gemm_debug(int mask) {
+  const unsigned int v = static_cast<unsigned int>(mask);
+  cudaMemcpyToSymbol(g_debug, &v, sizeof(v));
+}
+// Tuning hook: stages of L2 prefetch the TMA producer keeps ahead of its loads.  Synchronises.
+extern "C" void qwen36_nvfp4_gemm_set_prefetch(int stages) {
+  const unsigned int v = stages < 0 ? 0u : static_cast<unsigned int>(stages);
+  cudaMemcpyToSymbol(g_prefetch, &v, sizeof(v));
 }
 
 // 1 when a bounded wait inside the tensor-core GEMM ever gave up.  Synchronises.
