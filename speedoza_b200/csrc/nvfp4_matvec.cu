@@ -47,6 +47,12 @@ __device__ __forceinline__ void e2m1x8_to_h2(uint32_t w, uint32_t (&h)[4]) {
       : "r"(w));
 }
 
+__device__ __forceinline__ uint32_t max_u16x2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("max.u16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
 // even += w.lo * x.lo ; odd += w.hi * x.hi : float16 operands, float32 accumulate, products exact.
 __device__ __forceinline__ void fma_mixed_eo(float &even, float &odd, uint32_t w_h2, uint32_t x_h2) {
   asm("{\n\t.reg .f16 wl, wh, xl, xh;\n\t"
@@ -82,8 +88,23 @@ constexpr uint32_t kRingBytes = kRingStagesX8 * 8u * (4u * kSegBytes + 256u);   
 constexpr uint32_t kHeaderBytes = 2048;
 constexpr uint32_t kSpinLimit = 1u << 24;
 
-__device__ unsigned int g_matvec_error = 0;
-__device__ unsigned int g_prefetch_distance = 0;            // stages of L2 prefetch ahead of the ring                 // set when a bounded wait gives up
+__device__ unsigned int g_matvec_error = 0;                 // set when a bounded wait gives up
+
+// Per-CTA timestamps for pipeline analysis; compiled in only with -DQ36_MATVEC_TRACE.
+#ifdef Q36_MATVEC_TRACE
+constexpr uint32_t kTraceLaunches = 64, kTraceCtas = 320, kTraceEvents = 8;
+__device__ unsigned long long g_trace[kTraceLaunches][kTraceCtas][kTraceEvents];
+#define Q36_TRACE_PARAM , uint32_t trace_id
+#define Q36_TRACE(ev)                                                                   \
+  do {                                                                                  \
+    unsigned long long t_;                                                              \
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                              \
+    if (blockIdx.x < kTraceCtas) g_trace[trace_id % kTraceLaunches][blockIdx.x][ev] = t_; \
+  } while (0)
+#else
+#define Q36_TRACE_PARAM
+#define Q36_TRACE(ev)
+#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -123,17 +144,6 @@ __device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, u
                ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
 
-// L2 prefetch of a tile (no shared memory involved): lets the producer run further ahead of the
-// ring than shared memory alone allows, so HBM latency under load is hidden by L2.
-__device__ __forceinline__ void tma_prefetch_4d(const CUtensorMap *map, uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3) {
-  asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];"
-               ::"l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
-}
-__device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap *map, uint32_t c0, uint32_t c1, uint32_t c2) {
-  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];"
-               ::"l"(map), "r"(c0), "r"(c1), "r"(c2) : "memory");
-}
-
 // TMAP: stages are filled by tiled TMA through the two tensor maps (N % 128 == 0); otherwise
 // (QUADS == 8 only) by per-row cp.async.bulk copies.
 template <int QUADS, bool TMAP>
@@ -141,7 +151,7 @@ __global__ void __launch_bounds__(kThreads + 32)
 nvfp4_matvec_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_sf,
                     const __nv_bfloat16 *__restrict__ x, const uint8_t *__restrict__ weight,
                     const uint8_t *__restrict__ sf, const float *__restrict__ tensor_scale,
-                    __nv_bfloat16 *__restrict__ y, uint32_t K, uint32_t N) {
+                    __nv_bfloat16 *__restrict__ y, uint32_t K, uint32_t N Q36_TRACE_PARAM) {
   constexpr uint32_t kStages = kRingStagesX8 * 8u / QUADS;  // 4, 8, 16, 32
   constexpr uint32_t KPARTS = kWarps / QUADS;               // warps that split K of one quad
   constexpr uint32_t kStageW = QUADS * 4u * kSegBytes;
@@ -156,7 +166,6 @@ nvfp4_matvec_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   float *lut = reinterpret_cast<float *>(smem);                          // 256 decoded scales * global
   uint64_t *full = reinterpret_cast<uint64_t *>(smem + 1024);            // kStages (<= 32)
   uint64_t *empty = full + 32;
-  uint32_t *amax_bits = reinterpret_cast<uint32_t *>(smem + 1024 + 512);
   float *red = reinterpret_cast<float *>(smem + 1024 + 512 + 16);        // [2][kWarps][4] K-part sums
   uint8_t *ring = smem + kHeaderBytes;
   uint4 *xs = reinterpret_cast<uint4 *>(ring + kRingBytes);              // activations, swizzled chunks
@@ -168,16 +177,17 @@ nvfp4_matvec_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   const uint32_t units = ((N + 127u) / 128u) * kUnitsPerBlock;
   const uint32_t row_bytes = K / 2u;
 
-  if (threadIdx.x == 0) {
-    for (uint32_t s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], QUADS); }
-    *amax_bits = 0u;
+  if (threadIdx.x == 0) Q36_TRACE(0);
+  if (warp == kWarps) {
+    // The producer warp owns the barriers: it initialises them (one stage per lane), signals the
+    // consumers through a named barrier it does not wait on, and starts streaming at once.
+    if (lane < kStages) { mbar_init(&full[lane], 1); mbar_init(&empty[lane], QUADS); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (threadIdx.x < 256) {
+    asm volatile("bar.arrive 2, %0;" ::"n"(kThreads + 32) : "memory");   // does not block: see the consumers' bar.sync 2
+  } else {
     const float global = tensor_scale == nullptr ? 1.0f : __ldg(tensor_scale);
     lut[threadIdx.x] = __fmul_rn(q36::decode_e4m3(threadIdx.x), global);
   }
-  __syncthreads();
 
   if (warp == kWarps) {
     // ------------------------------------------------------------------ producer warp
@@ -186,18 +196,6 @@ nvfp4_matvec_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     uint32_t g = 0;                                          // running stage number
     if (TMAP) {
       if (lane == 0) {
-        // Two cursors over the same (unit, stage) sequence: `pf` runs kPrefetch stages ahead of
-        // `ld` and only asks L2 to fetch the tiles; `ld` fills the ring.
-        const uint32_t kPrefetch = g_prefetch_distance;
-        uint32_t pf_unit = blockIdx.x, pf_it = 0;
-        auto prefetch_one = [&]() {
-          if (pf_unit >= units) return;
-          const uint32_t rb = pf_unit / kUnitsPerBlock, r0 = (pf_unit % kUnitsPerBlock) * QUADS;
-          tma_prefetch_4d(&map_w, pf_it * 128u, r0, 0u, rb);
-          tma_prefetch_3d(&map_sf, r0 * 4u, pf_it * 16u, rb);
-          if (++pf_it == iters) { pf_it = 0; pf_unit += gridDim.x; }
-        };
-        for (uint32_t i = 0; i < kStages + kPrefetch; ++i) prefetch_one();
         for (uint32_t unit = blockIdx.x; unit < units; unit += gridDim.x) {
           const uint32_t rb = unit / kUnitsPerBlock, r0 = (unit % kUnitsPerBlock) * QUADS;
           for (uint32_t it = 0; it < iters; ++it, ++g) {
@@ -207,9 +205,10 @@ nvfp4_matvec_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             mbar_expect_tx(&full[stage], kStageBytes);      // whole boxes; out-of-range columns arrive as zeros
             tma_load_4d(dst, &map_w, it * 128u, r0, 0u, rb, &full[stage]);
             tma_load_3d(dst + kStageW, &map_sf, r0 * 4u, it * 16u, rb, &full[stage]);
-            prefetch_one();
+            if (g == 0) Q36_TRACE(1);
           }
         }
+        Q36_TRACE(2);
       }
       return;
     }
@@ -240,16 +239,19 @@ nvfp4_matvec_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   // -------------------------------------------------------------------- consumer warps
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (threadIdx.x == 0) Q36_TRACE(3);
 
   // Stage x once per CTA as float16.  Every 32-value slot (what one lane consumes per stage) is
   // scaled by its own power of two that brings the slot's max|x| into [2^14, 2^15): every
   // product e2m1 * x is then exact in the mixed-precision FMA, values below the slot maximum
   // times 2^-38 flush (far below the float32 accumulation error), and no pass over the whole
   // vector is needed to find a common scale.  The inverse scale of each slot is kept beside it
-  // and folded into the block scale.  Loads go out in batches of eight independent 16-byte L2
-  // reads per thread.
-  constexpr uint32_t kBatch = 8;
+  // and folded into the block scale.  This sits between the end of the producing kernel and the
+  // first FMA, so it is kept short: every 16-byte L2 read of a pass is issued before the first
+  // conversion (one round trip to L2), and warps past the end of x skip the conversion.
+  constexpr uint32_t kBatch = 9;                             // 18432 values per pass: one pass for every decode shape
   const uint32_t n_chunks = K / 8u;
+  const uint32_t warp_chunk0 = threadIdx.x & ~31u;           // first chunk of this warp inside a batch row
   for (uint32_t base = 0; base < n_chunks; base += kBatch * kThreads) {
     uint4 xr[kBatch];
 #pragma unroll
@@ -260,13 +262,14 @@ nvfp4_matvec_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     }
 #pragma unroll
     for (uint32_t i = 0; i < kBatch; ++i) {
+      if (base + warp_chunk0 + i * kThreads >= n_chunks) break;   // whole warp past the end (n_chunks % 4 == 0)
       const uint32_t c = base + threadIdx.x + i * kThreads;      // four consecutive lanes share a slot
       const uint32_t wv[4] = {xr[i].x, xr[i].y, xr[i].z, xr[i].w};
-      uint32_t mx = 0;
-#pragma unroll
-      for (int q = 0; q < 4; ++q) mx = max(mx, max(wv[q] & 0x7fffu, (wv[q] >> 16) & 0x7fffu));
-      mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-      mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      uint32_t m2 = max_u16x2(max_u16x2(wv[0] & 0x7fff7fffu, wv[1] & 0x7fff7fffu),
+                              max_u16x2(wv[2] & 0x7fff7fffu, wv[3] & 0x7fff7fffu));
+      m2 = max_u16x2(m2, __shfl_xor_sync(0xffffffffu, m2, 1));
+      m2 = max_u16x2(m2, __shfl_xor_sync(0xffffffffu, m2, 2));
+      const uint32_t mx = max(m2 & 0xffffu, m2 >> 16);
       const uint32_t e = (mx >> 7) & 0xffu;
       const int shift = e == 255u ? 0 : (e < 15u ? 126 : 141 - static_cast<int>(e));
       if (c < n_chunks) {
@@ -280,7 +283,9 @@ nvfp4_matvec_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       }
     }
   }
-  asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory");
+  // Meets the producer's arrival (barriers initialised) and publishes x and the scale table.
+  asm volatile("bar.sync 2, %0;" ::"n"(kThreads + 32) : "memory");
+  if (threadIdx.x == 0) Q36_TRACE(4);
 
   const uint32_t quad = warp % QUADS, kpart = warp / QUADS;
   const uint32_t rot0 = (16u * (lane & 1u) + 30u) & 31u;   // rotation that brings this lane's first scale byte to bits [9:2]
@@ -297,6 +302,7 @@ nvfp4_matvec_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       // A wait that gives up (never seen in practice) only stops the arithmetic: the warp keeps
       // walking its stages and barriers so that nobody else is left waiting for it.
       if (!dead && !mbar_wait(&full[stage], phase)) dead = true;
+      if (threadIdx.x == 0 && g == 0) Q36_TRACE(5);
       const uint8_t *st = ring + stage * kStageBytes;
       const uint32_t slot = lane + it * 32u;
       if (!dead && slot * 32u < K) {
@@ -362,6 +368,7 @@ nvfp4_matvec_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       }
     }
   }
+  if (threadIdx.x == 0) Q36_TRACE(6);
 }
 
 // Any shape, any alignment: one warp per row, byte loads.  Only taken when
@@ -393,6 +400,9 @@ nvfp4_matvec_generic_kernel(const __nv_bfloat16 *__restrict__ x, const uint8_t *
 }
 
 std::atomic<int> g_force_quads{0};
+#ifdef Q36_MATVEC_TRACE
+std::atomic<uint32_t> g_trace_id{0};
+#endif
 int g_sms = 0;
 int sm_count() {
   if (g_sms == 0) {
@@ -475,7 +485,11 @@ int launch_kernel(const qwen36_nvfp4_matvec_spec_t *s, const CUtensorMap &map_w,
   return q36::cuda_status(cudaLaunchKernelEx(
       &cfg, nvfp4_matvec_kernel<QUADS, TMAP>, map_w, map_sf, as_ptr<const __nv_bfloat16>(s->input_bf16),
       as_ptr<const uint8_t>(s->weight_u8), as_ptr<const uint8_t>(s->block_scale_e4m3),
-      as_ptr<const float>(s->tensor_scale_f32), as_ptr<__nv_bfloat16>(s->output_bf16), K, N));
+      as_ptr<const float>(s->tensor_scale_f32), as_ptr<__nv_bfloat16>(s->output_bf16), K, N
+#ifdef Q36_MATVEC_TRACE
+      , g_trace_id.fetch_add(1u)
+#endif
+      ));
 }
 
 int launch_fast(const qwen36_nvfp4_matvec_spec_t *s) {
@@ -508,14 +522,17 @@ int launch_fast(const qwen36_nvfp4_matvec_spec_t *s) {
 
 }  // namespace
 
-// Tuning hook (not part of the reference ABI): stages of L2 prefetch the producer keeps ahead of
-// the shared-memory ring.  Synchronises.
-extern "C" void qwen36_nvfp4_matvec_set_mode(int mode) {
-  const unsigned int v = mode < 0 ? 0u : static_cast<unsigned int>(mode);
-  cudaMemcpyToSymbol(g_prefetch_distance, &v, sizeof(v));
-}
 // Tuning hook: force the unit size (1, 2, 4 or 8 row quads); anything else restores the heuristic.
 extern "C" void qwen36_nvfp4_matvec_force_quads(int quads) { g_force_quads.store(quads); }
+
+#ifdef Q36_MATVEC_TRACE
+// Copies the timestamp table [64 launches][320 CTAs][8 events] (u64 ns) to `dst` and rewinds the
+// launch counter.  Synchronises.
+extern "C" int qwen36_nvfp4_matvec_trace_read(void *dst) {
+  g_trace_id.store(0);
+  return cudaMemcpyFromSymbol(dst, g_trace, sizeof(g_trace)) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 // 1 when a bounded wait inside the GEMV pipeline ever gave up (a stage never arrived); the
 // kernel then returns without finishing its rows.  Reads device memory: synchronises.

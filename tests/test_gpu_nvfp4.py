@@ -131,22 +131,24 @@ def test_matvec_known_answer(backend):
     assert backend.nvfp4_matvec(x, w, sf, None).float().item() == 2.5
 
 
-@pytest.mark.parametrize("mode", [1])
+@pytest.mark.parametrize("quads", [0, 8, 2])
 @pytest.mark.parametrize("n,k", [(5120, 5120), (1024, 5120), (5120, 6144), (12288, 5120), (5120, 17408),
-                                 (34816, 5120), (130, 96), (40, 2080), (7, 33)])
-def test_matvec_w4a16_vs_oracle(backend, n, k, mode):
-    """Config-0 bar: rel-L2 <= 1e-3 on the bf16 output against the reference's scalar semantics."""
-    rng = np.random.default_rng(n * 3 + k + mode)
+                                 (34816, 5120), (130, 96), (40, 2080), (7, 33), (256, 32768), (384, 8224)])
+def test_matvec_w4a16_vs_oracle(backend, n, k, quads):
+    """Config-0 bar: rel-L2 <= 1e-3 on the bf16 output against the reference's scalar semantics.
+    `quads` forces the work-unit size of the pipelined kernel (0 = the library's own choice)."""
+    rng = np.random.default_rng(n * 3 + k + 1)
     packed = rng.integers(0, 256, size=(n, (k + 1) // 2), dtype=np.uint8)
     sf_rm = rng.integers(synth.SF_CODE_LO, synth.SF_CODE_HI + 1, size=(n, (k + 15) // 16), dtype=np.uint8)
     sf = orc.retile_scales(sf_rm)
     x = synth.activations(rng, 1, k)[0]
     ts = torch.tensor([synth.WEIGHT_GLOBAL_SCALE], dtype=torch.float32, device="cuda")
-    backend.lib.qwen36_nvfp4_matvec_set_mode(mode)
+    backend.lib.qwen36_nvfp4_matvec_force_quads(quads)
     try:
         got = bf16_host(backend.nvfp4_matvec(to_dev(x), to_dev(packed), to_dev(sf), ts))
     finally:
-        backend.lib.qwen36_nvfp4_matvec_set_mode(1)
+        backend.lib.qwen36_nvfp4_matvec_force_quads(0)
+    assert backend.lib.qwen36_nvfp4_matvec_last_error() == 0
     want = orc.nvfp4_matvec(x, packed, sf, synth.WEIGHT_GLOBAL_SCALE, k)
     err = rel_l2(synth.bf16_bits_to_f32(got), synth.bf16_bits_to_f32(want))
     assert err <= 1e-3, err
