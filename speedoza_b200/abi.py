@@ -210,6 +210,10 @@ def load() -> C.CDLL:
     lib.qwen36_cuda_set_l2_access_window.argtypes = [DevicePtr, size_t, C.c_float]
     lib.qwen36_nvfp4_chunk_gemv_set_mtile.restype = None
     lib.qwen36_nvfp4_matvec_force_quads.restype = None
+    lib.qwen36_nvfp4_gemm_force_bn.restype = None
+    lib.qwen36_nvfp4_gemm_force_bn.argtypes = [C.c_int]
+    lib.qwen36_nvfp4_gemm_debug.restype = None
+    lib.qwen36_nvfp4_gemm_debug.argtypes = [C.c_int]
     lib.qwen36_nvfp4_matvec_force_quads.argtypes = [C.c_int]
     _lib = lib
     return lib

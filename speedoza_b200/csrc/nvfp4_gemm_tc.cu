@@ -35,7 +35,7 @@ constexpr uint32_t kSpinLimit = 1u << 26;
 
 __device__ unsigned int g_gemm_error = 0;
 int g_force_bn = 0;
-__device__ unsigned int g_debug = 0;        // timing experiments only (results become wrong): 1 skip scale copies, 2 skip stores
+__device__ unsigned int g_debug = 0;        // timing experiments only (results become wrong): 1 skip scale copies, 2 skip stores, 4 skip MMAs, 8 skip loads
 __device__ unsigned int g_prefetch = 0;     // stages of L2 prefetch ahead of the shared-memory ring
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -123,7 +123,7 @@ template <uint32_t BN> struct Cfg {
   static constexpr uint32_t kSfaBytes = 2048;
   static constexpr uint32_t kSfbBytes = 2048 * kSfbTiles;
   static constexpr uint32_t kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
-  static constexpr uint32_t kStages = BN >= 256 ? 3 : (BN >= 128 ? 5 : 6);
+  static constexpr uint32_t kStages = BN >= 256 ? 4 : (BN >= 128 ? 5 : 6);
   static constexpr uint32_t kAccStages = BN >= 256 ? 1 : 2;
   static constexpr uint32_t kAccCols = BN < 32 ? 32 : BN;              // columns reserved per accumulator stage
   static constexpr uint32_t kSfCols = 16 + 16 * kSfbTiles;             // per smem stage: SFA 4x4, SFB 4x4 per 128 tokens
@@ -204,6 +204,7 @@ nvfp4_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
 #pragma unroll
           for (uint32_t t = 0; t < C::kSfbTiles; ++t)
             if ((static_cast<size_t>(nb) * BN) / 128u + t < sf_tok_blocks) ++sfb_tiles;
+          if ((dbg & 8u) && g >= C::kStages) { mbar_arrive(&full[s]); continue; }   // timing experiment: no loads after the first ring fill
           mbar_expect_tx(&full[s], C::kABytes + C::kBRows * kBKBytes + C::kSfaBytes + sfb_tiles * 2048u);
           tma_load_2d(st, &map_a, kb * kBKBytes, mb * kBM, &full[s]);
           tma_load_2d(st + C::kABytes, &map_b, kb * kBKBytes, nb * BN, &full[s]);
@@ -231,16 +232,18 @@ nvfp4_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         const uint32_t d_tmem = tmem_base + as * C::kAccCols;
         for (uint32_t kb = 0; kb < k_blocks; ++kb, ++g) {
           const uint32_t s = g % C::kStages, ph = (g / C::kStages) & 1u;
-          if (!mbar_wait(&full[s], ph)) { dead = true; break; }
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t st = smem_u32(stages + s * C::kStageBytes);
           const uint32_t sfa_t = tmem_sf + s * C::kSfCols, sfb_t = sfa_t + 16u;
+          if (!mbar_wait(&full[s], ph)) { dead = true; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           if (!mbar_wait(&sf_full[s], ph)) { dead = true; break; }     // the copier warp has put this stage's scales in TMEM
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          if (!(dbg & 4u)) {                                            // timing experiment: 4 = no MMAs
 #pragma unroll
-          for (uint32_t kk = 0; kk < 4; ++kk)
-            mma_mxf4nvf4(d_tmem, desc_sw128(st + kk * 32u), desc_sw128(st + C::kABytes + kk * 32u), C::kIdesc,
-                         sfa_t + kk * 4u, sfb_t + kk * C::kSfbTiles * 4u, (kb | kk) != 0u);
+            for (uint32_t kk = 0; kk < 4; ++kk)
+              mma_mxf4nvf4(d_tmem, desc_sw128(st + kk * 32u), desc_sw128(st + C::kABytes + kk * 32u), C::kIdesc,
+                           sfa_t + kk * 4u, sfb_t + kk * C::kSfbTiles * 4u, (kb | kk) != 0u);
+          }
           mma_commit(&empty[s]);                 // frees the smem stage once these MMAs have read it
         }
         if (!dead) mma_commit(&acc_full[as]);    // accumulator complete
@@ -289,23 +292,38 @@ nvfp4_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       const uint32_t taddr = tmem_base + as * C::kAccCols + ((quarter * 32u) << 16);
       const uint32_t tok0 = nb * BN;
       if constexpr (BN >= 32) {
-#pragma unroll 1
+        // Drain the accumulator first: every 32-column slice is scaled, rounded to bf16 and kept
+        // as packed pairs (tokens 2j, 2j+1 of this lane's feature), the TMEM stage is handed
+        // back to the MMA warp, and only then do the (slow) global stores run, overlapped with
+        // the next tile's MMAs even when there is a single accumulator stage.
+        uint32_t packed[BN / 2];
+#pragma unroll
         for (uint32_t c0 = 0; c0 < BN; c0 += 32) {
           uint32_t r[32];
           tmem_ld32(taddr + c0, r);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-          // Lane pairs swap so that the even lane holds features (f, f+1) of token t and the odd
-          // lane those of token t+1: 4-byte stores, 64 contiguous bytes per token per warp.
 #pragma unroll
           for (uint32_t j = 0; j < 32; j += 2) {
-            const float mine_a = __uint_as_float(r[j]) * alpha, mine_b = __uint_as_float(r[j + 1]) * alpha;
-            const float send = (lane & 1u) ? mine_a : mine_b;
-            const float got = __shfl_xor_sync(0xffffffffu, send, 1);
-            const uint32_t tok = tok0 + c0 + j + (lane & 1u);
-            const __nv_bfloat162 v = (lane & 1u) ? __floats2bfloat162_rn(got, mine_b) : __floats2bfloat162_rn(mine_a, got);
-            if (tok < n && !(dbg & 2u)) *reinterpret_cast<__nv_bfloat162 *>(c + static_cast<size_t>(tok) * m + (row & ~1u)) = v;
+            const __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[j]) * alpha, __uint_as_float(r[j + 1]) * alpha);
+            packed[(c0 + j) / 2] = *reinterpret_cast<const uint32_t *>(&v);
           }
         }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[as]);
+        // Lane pairs swap halves so that the even lane holds features (f, f+1) of token 2j and the
+        // odd lane those of token 2j+1: 4-byte stores, 64 contiguous bytes per token per warp.
+        const bool odd = (lane & 1u) != 0u;
+        __nv_bfloat16 *crow = c + (row & ~1u);
+#pragma unroll
+        for (uint32_t j = 0; j < BN / 2; ++j) {
+          const uint32_t got = __shfl_xor_sync(0xffffffffu, packed[j], 1);
+          // even: (mine.lo, got.lo) = token 2j ; odd: (got.hi, mine.hi) = token 2j+1
+          const uint32_t v = odd ? __byte_perm(got, packed[j], 0x7632) : __byte_perm(packed[j], got, 0x5410);
+          const uint32_t tok = tok0 + 2u * j + (odd ? 1u : 0u);
+          if (tok < n && !(dbg & 2u)) *reinterpret_cast<uint32_t *>(crow + static_cast<size_t>(tok) * m) = v;
+        }
+        continue;
       } else {
         uint32_t r[8];
 #pragma unroll 1
@@ -331,6 +349,238 @@ nvfp4_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::kTmemCols) : "memory");
+  }
+}
+
+// ============================================================================================
+// CTA-pair form (tcgen05 cta_group::2) for large token counts: two CTAs of a cluster share one
+// 256-row x 256-token tile.  Each CTA stages its own 128 weight rows and only HALF of the
+// activation tile (128 tokens); the pair's MMAs read both halves, so the L2 -> shared-memory
+// traffic per CTA drops from 54 KB to 38 KB per 256 K, and five stages fit instead of four.
+// The even CTA of the pair ("leader") owns the full / scale / accumulator-free barriers and
+// issues every tcgen05.cp and tcgen05.mma for both CTAs; tcgen05.commit fans the "stage free"
+// and "accumulator ready" signals out to both.  Both CTAs run a TMA producer (signalling the
+// leader's barrier) and four epilogue warps (each CTA drains its own 128 TMEM lanes).
+// ============================================================================================
+namespace pair {
+constexpr uint32_t kBN = 256;                                   // tokens per pair tile
+constexpr uint32_t kHalfTok = 128;                              // tokens staged per CTA
+constexpr uint32_t kABytes = kBM * kBKBytes;                    // 16384
+constexpr uint32_t kBBytes = kHalfTok * kBKBytes;               // 16384
+constexpr uint32_t kSfaBytes = 2048;
+constexpr uint32_t kSfbBytes = 4096;                            // both 128-token scale blocks
+constexpr uint32_t kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;   // 38912
+constexpr uint32_t kStages = 5;
+constexpr uint32_t kSfCols = 16 + 32;
+constexpr uint32_t kTmemCols = 512;                             // 256 accumulator + 5 x 48 scale columns
+constexpr uint32_t kSmemBytes = 1024 + 1024 + kStages * kStageBytes;
+constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | ((kBN >> 3) << 17) | ((256u >> 4) << 24);
+static_assert(256 + kStages * kSfCols <= kTmemCols, "TMEM budget");
+}  // namespace pair
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t v;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(v));
+  return v;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(v) : "r"(smem_addr), "r"(rank));
+  return v;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Tiled TMA load whose completion is counted on a barrier that may live in the other CTA of the pair.
+__device__ __forceinline__ void tma_load_2d_pair(void *dst, const CUtensorMap *map, uint32_t c0, uint32_t c1, uint32_t bar_cluster_addr) {
+  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+               ::"r"(smem_u32(dst)), "l"(map), "r"(bar_cluster_addr), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tmem_cp_sf_pair(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+__device__ __forceinline__ void mma_mxf4nvf4_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                  uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+               ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem) : "memory");
+}
+// Arrives (once the pair's earlier tcgen05 operations have completed) on the barrier at the same
+// shared-memory offset in every CTA of `cta_mask`.
+__device__ __forceinline__ void mma_commit_pair_fanout(uint64_t *bar, uint16_t cta_mask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"(cta_mask) : "memory");
+}
+__device__ __forceinline__ void mma_commit_pair(uint64_t *bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                       const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
+                       __nv_bfloat16 *__restrict__ c, uint32_t m, uint32_t n, uint32_t k, float alpha) {
+  namespace P = pair;
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint64_t *full = reinterpret_cast<uint64_t *>(smem);                   // [kStages]   used in the leader
+  uint64_t *empty = full + 8;                                            // [kStages]   one per CTA
+  uint64_t *sf_full = empty + 8;                                         // [kStages]   used in the leader
+  uint64_t *acc_full = sf_full + 8;                                      // one per CTA
+  uint64_t *acc_empty = acc_full + 2;                                    // used in the leader: 8 epilogue warps
+  uint32_t *tmem_base_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
+  uint8_t *stages = smem + 1024;
+
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+  const uint32_t rank = cluster_rank() & 1u;
+  const bool leader = rank == 0u;
+  const uint32_t pair_id = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const uint32_t m_blocks = m / 256u, n_blocks = (n + P::kBN - 1) / P::kBN;
+  const uint32_t tiles = m_blocks * n_blocks;
+  const uint32_t k_blocks = k / 256u;
+  const uint32_t sf_tiles_per_block = k / 64u;                           // 512-byte tiles per 128 rows
+
+  if (threadIdx.x == 0) {
+    for (uint32_t s = 0; s < P::kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); mbar_init(&sf_full[s], 1); }
+    mbar_init(&acc_full[0], 1);
+    mbar_init(&acc_empty[0], 8);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_base_slot)), "r"(P::kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();                       // both CTAs' barriers exist before anything crosses over
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_base_slot;
+  const uint32_t tmem_sf = tmem_base + 256u;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer (both CTAs)
+    if (lane == 0) {
+      uint32_t g = 0;
+      for (uint32_t tile = pair_id; tile < tiles; tile += n_pairs) {
+        const uint32_t nb = tile % n_blocks, mb = tile / n_blocks;
+        const uint32_t row_block = mb * 2u + rank;                       // this CTA's 128 weight rows
+        bool dead = false;
+        for (uint32_t kb = 0; kb < k_blocks; ++kb, ++g) {
+          const uint32_t s = g % P::kStages, ph = (g / P::kStages) & 1u;
+          if (!mbar_wait(&empty[s], ph ^ 1u)) { dead = true; break; }
+          uint8_t *st = stages + s * P::kStageBytes;
+          const uint32_t bar = map_to_cta(smem_u32(&full[s]), 0u);       // the leader's barrier counts both CTAs' bytes
+          if (leader) mbar_expect_tx(&full[s], 2u * P::kStageBytes);
+          tma_load_2d_pair(st, &map_a, kb * kBKBytes, row_block * kBM, bar);
+          tma_load_2d_pair(st + P::kABytes, &map_b, kb * kBKBytes, nb * P::kBN + rank * P::kHalfTok, bar);
+          tma_load_2d_pair(st + P::kABytes + P::kBBytes, &map_sfa, 0u, row_block * sf_tiles_per_block + kb * 4u, bar);
+          // token blocks past the end of the activation tensor lie outside the map and arrive as zeros
+#pragma unroll
+          for (uint32_t t = 0; t < 2; ++t)
+            tma_load_2d_pair(st + P::kABytes + P::kBBytes + P::kSfaBytes + t * 2048u, &map_sfb, 0u,
+                             (nb * 2u + t) * sf_tiles_per_block + kb * 4u, bar);
+        }
+        if (dead) break;
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer (leader only)
+    if (leader && lane == 0) {
+      uint32_t g = 0, t_local = 0;
+      bool dead = false;
+      for (uint32_t tile = pair_id; tile < tiles && !dead; tile += n_pairs, ++t_local) {
+        if (!mbar_wait(&acc_empty[0], (t_local & 1u) ^ 1u)) { dead = true; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        for (uint32_t kb = 0; kb < k_blocks; ++kb, ++g) {
+          const uint32_t s = g % P::kStages, ph = (g / P::kStages) & 1u;
+          if (!mbar_wait(&full[s], ph)) { dead = true; break; }
+          if (!mbar_wait(&sf_full[s], ph)) { dead = true; break; }     // scales of this stage are in both TMEMs
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t st = smem_u32(stages + s * P::kStageBytes);
+          const uint32_t sfa_t = tmem_sf + s * P::kSfCols, sfb_t = sfa_t + 16u;
+#pragma unroll
+          for (uint32_t kk = 0; kk < 4; ++kk)
+            mma_mxf4nvf4_pair(tmem_base, desc_sw128(st + kk * 32u), desc_sw128(st + P::kABytes + kk * 32u), P::kIdesc,
+                              sfa_t + kk * 4u, sfb_t + kk * 8u, (kb | kk) != 0u);
+          mma_commit_pair_fanout(&empty[s], 3);  // frees the stage in both CTAs once these MMAs have read it
+        }
+        if (!dead) mma_commit_pair_fanout(&acc_full[0], 3);   // accumulator complete, in both CTAs
+      }
+    }
+  } else if (warp == 6) {
+    // ---------------------------------------------------------------- scale copier (leader only)
+    if (leader && lane == 0) {
+      uint32_t g = 0;
+      bool dead = false;
+      for (uint32_t tile = pair_id; tile < tiles && !dead; tile += n_pairs) {
+        for (uint32_t kb = 0; kb < k_blocks; ++kb, ++g) {
+          const uint32_t s = g % P::kStages, ph = (g / P::kStages) & 1u;
+          if (!mbar_wait(&full[s], ph)) { dead = true; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t st = smem_u32(stages + s * P::kStageBytes);
+          const uint32_t sfa_t = tmem_sf + s * P::kSfCols, sfb_t = sfa_t + 16u;
+#pragma unroll
+          for (uint32_t kk = 0; kk < 4; ++kk) {
+            tmem_cp_sf_pair(sfa_t + kk * 4u, desc_sf(st + P::kABytes + P::kBBytes + kk * 512u));
+#pragma unroll
+            for (uint32_t t = 0; t < 2; ++t)
+              tmem_cp_sf_pair(sfb_t + (kk * 2u + t) * 4u,
+                              desc_sf(st + P::kABytes + P::kBBytes + P::kSfaBytes + t * 2048u + kk * 512u));
+          }
+          mma_commit_pair(&sf_full[s]);
+        }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue warps 2..5 (both CTAs)
+    const uint32_t quarter = warp & 3u;           // TMEM lanes [32*quarter, +32) are this warp's
+    const uint32_t acc_empty_leader = map_to_cta(smem_u32(&acc_empty[0]), 0u);
+    uint32_t t_local = 0;
+    for (uint32_t tile = pair_id; tile < tiles; tile += n_pairs, ++t_local) {
+      const uint32_t nb = tile % n_blocks, mb = tile / n_blocks;
+      if (!mbar_wait(&acc_full[0], t_local & 1u)) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t row = (mb * 2u + rank) * kBM + quarter * 32u + lane;     // feature index
+      const uint32_t taddr = tmem_base + ((quarter * 32u) << 16);
+      const uint32_t tok0 = nb * P::kBN;
+      uint32_t packed[P::kBN / 2];
+#pragma unroll
+      for (uint32_t c0 = 0; c0 < P::kBN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(taddr + c0, r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (uint32_t j = 0; j < 32; j += 2) {
+          const __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[j]) * alpha, __uint_as_float(r[j + 1]) * alpha);
+          packed[(c0 + j) / 2] = *reinterpret_cast<const uint32_t *>(&v);
+        }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
+      const bool odd = (lane & 1u) != 0u;
+      __nv_bfloat16 *crow = c + (row & ~1u);
+#pragma unroll
+      for (uint32_t j = 0; j < P::kBN / 2; ++j) {
+        const uint32_t got = __shfl_xor_sync(0xffffffffu, packed[j], 1);
+        const uint32_t v = odd ? __byte_perm(got, packed[j], 0x7632) : __byte_perm(packed[j], got, 0x5410);
+        const uint32_t tok = tok0 + 2u * j + (odd ? 1u : 0u);
+        if (tok < n) *reinterpret_cast<uint32_t *>(crow + static_cast<size_t>(tok) * m) = v;
+      }
+    }
+  }
+
+  // Common exit: the pair meets (nobody may still read the other's shared or tensor memory),
+  // then both allocating warps release TMEM.
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(P::kTmemCols) : "memory");
   }
 }
 
@@ -396,6 +646,66 @@ int launch(const qwen36_nvfp4_gemm_spec_t *s, float alpha) {
   return q36::launch_status();
 }
 
+// Tiled scale buffer as uint32 [tiles][128]: one 512-byte scale tile per row, box = four tiles (one 256-K stage).
+bool make_scale_map(CUtensorMap *map, uint64_t ptr, uint64_t tiles) {
+  EncodeFn enc = encode_fn();
+  if (enc == nullptr) return false;
+  const cuuint64_t dims[2] = {128, tiles};
+  const cuuint64_t strides[1] = {512};
+  const cuuint32_t box[2] = {128, 4};
+  const cuuint32_t ones[2] = {1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, reinterpret_cast<void *>(ptr), dims, strides, box, ones,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int launch_pair(const qwen36_nvfp4_gemm_spec_t *s, float alpha) {
+  namespace P = pair;
+  CUtensorMap map_a, map_b, map_sfa, map_sfb;
+  const uint64_t sf_tiles = s->k / 64;
+  if (!make_operand_map(&map_a, s->a_fp4.ptr, s->m, s->k, kBM) ||
+      !make_operand_map(&map_b, s->b_fp4.ptr, s->n, s->k, P::kHalfTok) ||
+      !make_scale_map(&map_sfa, s->a_scale.ptr, (s->m / 128) * sf_tiles) ||
+      !make_scale_map(&map_sfb, s->b_scale.ptr, ((s->n + 127) / 128) * sf_tiles))
+    return QWEN36_STATUS_NOT_IMPLEMENTED;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(nvfp4_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    static_cast<int>(P::kSmemBytes));
+  });
+  if (attr_err != cudaSuccess) return QWEN36_STATUS_CUDA_ERROR;
+  const uint32_t tiles = static_cast<uint32_t>((s->m / 256) * ((s->n + P::kBN - 1) / P::kBN));
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<uint32_t>(sm_count()) & ~1u);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = P::kSmemBytes;
+  cfg.stream = q36::stream();
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  // The grid is persistent with a static tile stride, so it must never exceed the number of
+  // pairs the device can host at the same time (some SMs may have no free partner).
+  static int max_pairs = [&] {
+    int v = 0;
+    if (cudaOccupancyMaxActiveClusters(&v, nvfp4_gemm_pair_kernel, &cfg) != cudaSuccess) {
+      (void)cudaGetLastError();
+      v = 0;
+    }
+    return v;
+  }();
+  if (max_pairs <= 0) return QWEN36_STATUS_NOT_IMPLEMENTED;
+  const uint32_t pairs = tiles < static_cast<uint32_t>(max_pairs) ? tiles : static_cast<uint32_t>(max_pairs);
+  cfg.gridDim = dim3(pairs * 2u);
+  return q36::cuda_status(cudaLaunchKernelEx(&cfg, nvfp4_gemm_pair_kernel, map_a, map_b, map_sfa, map_sfb,
+                                             as_ptr<__nv_bfloat16>(s->c_bf16), static_cast<uint32_t>(s->m),
+                                             static_cast<uint32_t>(s->n), static_cast<uint32_t>(s->k), alpha));
+}
+
 }  // namespace
 
 int nvfp4_gemm_tc(const qwen36_nvfp4_gemm_spec_t *s, float alpha) {
@@ -404,6 +714,12 @@ int nvfp4_gemm_tc(const qwen36_nvfp4_gemm_spec_t *s, float alpha) {
     return QWEN36_STATUS_NOT_IMPLEMENTED;
   const int forced = g_force_bn;
   if (forced == 128 && s->n > 128) return launch<128>(s, alpha);
+  // CTA pairs (256 x 256 tiles): measured ahead of single-CTA tiles only for long K with many
+  // tokens (+5 % at k = 17408, n = 8192; level or slightly behind elsewhere).
+  if (s->n > 128 && s->m % 256 == 0 && (forced == 512 || (forced == 0 && s->k >= 8192 && s->n >= 4096))) {
+    const int rc = launch_pair(s, alpha);
+    if (rc != QWEN36_STATUS_NOT_IMPLEMENTED) return rc;      // pairs unavailable: single-CTA tiles below
+  }
   if (s->n <= 8) return launch<8>(s, alpha);
   if (s->n <= 16) return launch<16>(s, alpha);
   if (s->n <= 32) return launch<32>(s, alpha);
@@ -412,7 +728,8 @@ int nvfp4_gemm_tc(const qwen36_nvfp4_gemm_spec_t *s, float alpha) {
   return launch<256>(s, alpha);
 }
 
-// Tuning hook: 128 forces 128-token tiles (two accumulator stages) for large n; 0 = default.
+// Tuning hook: 128 forces 128-token tiles (two accumulator stages) for large n, 256 single-CTA
+// 256-token tiles, 512 CTA pairs (where the shape allows them); 0 = default.
 extern "C" void qwen36_nvfp4_gemm_force_bn(int bn) { g_force_bn = bn; }
 extern "C" void qwen36_nvfp4_gemm_debug(int mask) {
   const unsigned int v = static_cast<unsigned int>(mask);
