@@ -112,9 +112,11 @@ typedef struct {
 
 /* Replaces qwen36_nvfp4_gemm (kernels-cuda/nvfp4_gemm.cu:341-409, a cuBLASLt
  * call).  Any m, n, k with k % 16 == 0.  alpha == 0 is read as 1.  Shapes with
- * m % 128 == 0 and k % 256 == 0 run on tcgen05 block-scaled MMA (n <= 64: a
- * weight-streaming split-K form; larger n: the tiled GEMM); anything else
- * takes a generic SIMT kernel. */
+ * m % 128 == 0 and k % 256 == 0 run on tcgen05 block-scaled MMA: persistent
+ * 128-row x {8..256}-token tiles; for n <= 16 with fewer row blocks than SMs,
+ * clusters of CTAs split K and add their partial sums through distributed
+ * shared memory; for long K and thousands of tokens, CTA pairs (cta_group::2)
+ * share 256 x 256 tiles.  Anything else takes a generic SIMT kernel. */
 int qwen36_nvfp4_gemm(const qwen36_nvfp4_gemm_spec_t *spec);
 
 /* Replaces qwen36_decode_nvfp4_gemv

@@ -212,6 +212,8 @@ def load() -> C.CDLL:
     lib.qwen36_nvfp4_matvec_force_quads.restype = None
     lib.qwen36_nvfp4_gemm_force_bn.restype = None
     lib.qwen36_nvfp4_gemm_force_bn.argtypes = [C.c_int]
+    lib.qwen36_nvfp4_gemm_force_split.restype = None
+    lib.qwen36_nvfp4_gemm_force_split.argtypes = [C.c_int]
     lib.qwen36_nvfp4_gemm_debug.restype = None
     lib.qwen36_nvfp4_gemm_debug.argtypes = [C.c_int]
     lib.qwen36_nvfp4_matvec_force_quads.argtypes = [C.c_int]

@@ -35,6 +35,7 @@ constexpr uint32_t kSpinLimit = 1u << 26;
 
 __device__ unsigned int g_gemm_error = 0;
 int g_force_bn = 0;
+int g_force_split = 0;
 __device__ unsigned int g_debug = 0;        // timing experiments only (results become wrong): 1 skip scale copies, 2 skip stores, 4 skip MMAs, 8 skip loads
 __device__ unsigned int g_prefetch = 0;     // stages of L2 prefetch ahead of the shared-memory ring
 
@@ -584,6 +585,165 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
   }
 }
 
+// ============================================================================================
+// Split-K form for few tokens and few row blocks (decode: n <= 8, the k / v / o / down
+// projections have only 8 or 40 row blocks, far fewer than SMs).  A cluster of S CTAs shares one
+// 128-row x BN-token tile; CTA r streams K-blocks [r * kb / S, (r + 1) * kb / S) through the same
+// TMA -> tcgen05 pipeline into its own TMEM accumulator.  The partial sums meet in the first
+// CTA's shared memory (distributed shared memory stores, one cluster barrier), which adds them in
+// rank order, applies alpha and writes bf16: no workspace, no atomics, deterministic.
+// ============================================================================================
+constexpr uint32_t kMaxSplit = 8;
+
+__device__ __forceinline__ void st_cluster_v4f(uint32_t addr, float a, float b, float c4, float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c4), "f"(d) : "memory");
+}
+
+template <uint32_t BN>
+__global__ void __launch_bounds__(kThreads, 1)
+nvfp4_gemm_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                         const uint8_t *__restrict__ a_sf, const uint8_t *__restrict__ b_sf,
+                         __nv_bfloat16 *__restrict__ c, uint32_t m, uint32_t n, uint32_t k, float alpha) {
+  using C = Cfg<BN>;
+  static_assert(BN <= 64, "split-K form is for small token counts");
+  constexpr uint32_t kCols = C::kBRows;                                  // accumulator columns that hold data
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint64_t *full = reinterpret_cast<uint64_t *>(smem);
+  uint64_t *empty = full + 8;
+  uint64_t *sf_full = empty + 8;
+  uint64_t *acc_full = sf_full + 8;
+  uint32_t *tmem_base_slot = reinterpret_cast<uint32_t *>(acc_full + 2);
+  uint8_t *stages = smem + 1024;
+  float *partials = reinterpret_cast<float *>(stages + C::kStages * C::kStageBytes);   // [S-1][128 rows][kCols], first CTA only
+
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+  uint32_t S, rank;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(S));
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  const uint32_t mb = blockIdx.x / S;                                    // one tile per cluster, one token block
+  const uint32_t k_blocks = k / 256u;
+  const uint32_t kb_begin = rank * k_blocks / S, kb_end = (rank + 1u) * k_blocks / S;
+  const uint32_t sf_tiles_per_block = k / 64u;
+
+  if (threadIdx.x == 0) {
+    for (uint32_t s = 0; s < C::kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); mbar_init(&sf_full[s], 1); }
+    mbar_init(&acc_full[0], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_base_slot)), "r"(C::kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_base_slot;
+  const uint32_t tmem_sf = tmem_base + C::kAccStages * C::kAccCols;
+
+  float acc[kCols];                                                      // epilogue warps: this lane's row
+#pragma unroll
+  for (uint32_t j = 0; j < kCols; ++j) acc[j] = 0.f;
+  bool ok = true;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (uint32_t kb = kb_begin, g = 0; kb < kb_end; ++kb, ++g) {
+        const uint32_t s = g % C::kStages, ph = (g / C::kStages) & 1u;
+        if (!mbar_wait(&empty[s], ph ^ 1u)) break;
+        uint8_t *st = stages + s * C::kStageBytes;
+        mbar_expect_tx(&full[s], C::kABytes + C::kBRows * kBKBytes + C::kSfaBytes + 2048u);
+        tma_load_2d(st, &map_a, kb * kBKBytes, mb * kBM, &full[s]);
+        tma_load_2d(st + C::kABytes, &map_b, kb * kBKBytes, 0u, &full[s]);
+        bulk_g2s(st + C::kABytes + C::kBBytes, a_sf + (static_cast<size_t>(mb) * sf_tiles_per_block + kb * 4u) * 512u,
+                 2048u, &full[s]);
+        bulk_g2s(st + C::kABytes + C::kBBytes + C::kSfaBytes, b_sf + static_cast<size_t>(kb * 4u) * 512u, 2048u, &full[s]);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool dead = false;
+      for (uint32_t kb = kb_begin, g = 0; kb < kb_end; ++kb, ++g) {
+        const uint32_t s = g % C::kStages, ph = (g / C::kStages) & 1u;
+        if (!mbar_wait(&full[s], ph) || !mbar_wait(&sf_full[s], ph)) { dead = true; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t st = smem_u32(stages + s * C::kStageBytes);
+        const uint32_t sfa_t = tmem_sf + s * C::kSfCols, sfb_t = sfa_t + 16u;
+#pragma unroll
+        for (uint32_t kk = 0; kk < 4; ++kk)
+          mma_mxf4nvf4(tmem_base, desc_sw128(st + kk * 32u), desc_sw128(st + C::kABytes + kk * 32u), C::kIdesc,
+                       sfa_t + kk * 4u, sfb_t + kk * 4u, (g | kk) != 0u);
+        mma_commit(&empty[s]);
+      }
+      if (!dead) mma_commit(&acc_full[0]);
+    }
+  } else if (warp == 6) {
+    if (lane == 0) {
+      for (uint32_t kb = kb_begin, g = 0; kb < kb_end; ++kb, ++g) {
+        const uint32_t s = g % C::kStages, ph = (g / C::kStages) & 1u;
+        if (!mbar_wait(&full[s], ph)) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t st = smem_u32(stages + s * C::kStageBytes);
+        const uint32_t sfa_t = tmem_sf + s * C::kSfCols, sfb_t = sfa_t + 16u;
+#pragma unroll
+        for (uint32_t kk = 0; kk < 4; ++kk) {
+          tmem_cp_sf(sfa_t + kk * 4u, desc_sf(st + C::kABytes + C::kBBytes + kk * 512u));
+          tmem_cp_sf(sfb_t + kk * 4u, desc_sf(st + C::kABytes + C::kBBytes + C::kSfaBytes + kk * 512u));
+        }
+        mma_commit(&sf_full[s]);
+      }
+    }
+  } else {
+    // epilogue warps 2..5: drain this CTA's partial sums; ranks > 0 hand them to the first CTA
+    const uint32_t quarter = warp & 3u;
+    if (kb_end > kb_begin) {
+      ok = mbar_wait(&acc_full[0], 0u);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (ok) {
+        const uint32_t taddr = tmem_base + ((quarter * 32u) << 16);
+#pragma unroll
+        for (uint32_t c0 = 0; c0 < kCols; c0 += 8) {
+          uint32_t r[8];
+          tmem_ld8(taddr + c0, r);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+          for (uint32_t j = 0; j < 8; ++j) acc[c0 + j] = __uint_as_float(r[j]);
+        }
+      }
+    }
+    if (rank != 0u) {
+      const uint32_t row = quarter * 32u + lane;
+      const uint32_t dst = map_to_cta(smem_u32(partials + (static_cast<size_t>(rank - 1u) * kBM + row) * kCols), 0u);
+#pragma unroll
+      for (uint32_t j = 0; j < kCols; j += 4) st_cluster_v4f(dst + j * 4u, acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+    }
+  }
+
+  // The cluster meets: every partial sum has landed in the first CTA's shared memory.
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();
+  if (rank == 0u && warp >= 2u && warp <= 5u && ok) {
+    const uint32_t quarter = warp & 3u;
+    const uint32_t row_in = quarter * 32u + lane, row = mb * kBM + row_in;
+    for (uint32_t r = 1; r < S; ++r) {                                   // fixed order: rank 1, 2, ...
+      const float4 *src = reinterpret_cast<const float4 *>(partials + (static_cast<size_t>(r - 1u) * kBM + row_in) * kCols);
+#pragma unroll
+      for (uint32_t j = 0; j < kCols; j += 4) {
+        const float4 v = src[j / 4];
+        acc[j] += v.x; acc[j + 1] += v.y; acc[j + 2] += v.z; acc[j + 3] += v.w;
+      }
+    }
+#pragma unroll
+    for (uint32_t j = 0; j < kCols; ++j)
+      if (j < n) c[static_cast<size_t>(j) * m + row] = __float2bfloat16(acc[j] * alpha);
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::kTmemCols) : "memory");
+  }
+}
+
 using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                               const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -706,6 +866,53 @@ int launch_pair(const qwen36_nvfp4_gemm_spec_t *s, float alpha) {
                                              static_cast<uint32_t>(s->n), static_cast<uint32_t>(s->k), alpha));
 }
 
+// Split-K launch: `split` CTAs per 128-row block (cluster), one token block (n <= BN).
+template <uint32_t BN>
+int launch_splitk(const qwen36_nvfp4_gemm_spec_t *s, float alpha, uint32_t split) {
+  using C = Cfg<BN>;
+  CUtensorMap map_a, map_b;
+  if (!make_operand_map(&map_a, s->a_fp4.ptr, s->m, s->k, kBM) ||
+      !make_operand_map(&map_b, s->b_fp4.ptr, s->n, s->k, C::kBRows))
+    return QWEN36_STATUS_NOT_IMPLEMENTED;
+  constexpr uint32_t kSmem = C::kSmemBytes + (kMaxSplit - 1) * kBM * C::kBRows * 4u;
+  static_assert(kSmem <= 227u * 1024u, "split-K shared memory");
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(nvfp4_gemm_splitk_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    static_cast<int>(kSmem));
+  });
+  if (attr_err != cudaSuccess) return QWEN36_STATUS_CUDA_ERROR;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<uint32_t>(s->m / kBM) * split);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = kSmem;
+  cfg.stream = q36::stream();
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = split;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return q36::cuda_status(cudaLaunchKernelEx(&cfg, nvfp4_gemm_splitk_kernel<BN>, map_a, map_b,
+                                             as_ptr<const uint8_t>(s->a_scale), as_ptr<const uint8_t>(s->b_scale),
+                                             as_ptr<__nv_bfloat16>(s->c_bf16), static_cast<uint32_t>(s->m),
+                                             static_cast<uint32_t>(s->n), static_cast<uint32_t>(s->k), alpha));
+}
+
+// CTAs per row block for the split-K form, 1 when the plain persistent kernel should run: split
+// only when the row blocks alone leave most SMs idle, as far as that fills the device, keeping at
+// least two K-blocks per CTA.
+uint32_t choose_split(const qwen36_nvfp4_gemm_spec_t *s) {
+  const int forced = g_force_split;
+  const uint32_t m_blocks = static_cast<uint32_t>(s->m / kBM), k_blocks = static_cast<uint32_t>(s->k / 256);
+  uint32_t split = forced > 0 ? static_cast<uint32_t>(forced) : static_cast<uint32_t>(sm_count()) / m_blocks;
+  if (split > kMaxSplit) split = kMaxSplit;
+  if (split > k_blocks / 2u) split = k_blocks / 2u;
+  return split < 2u ? 1u : split;
+}
+
 }  // namespace
 
 int nvfp4_gemm_tc(const qwen36_nvfp4_gemm_spec_t *s, float alpha) {
@@ -720,6 +927,10 @@ int nvfp4_gemm_tc(const qwen36_nvfp4_gemm_spec_t *s, float alpha) {
     const int rc = launch_pair(s, alpha);
     if (rc != QWEN36_STATUS_NOT_IMPLEMENTED) return rc;      // pairs unavailable: single-CTA tiles below
   }
+  if (s->n <= 16) {
+    const uint32_t split = choose_split(s);
+    if (split > 1u) return s->n <= 8 ? launch_splitk<8>(s, alpha, split) : launch_splitk<16>(s, alpha, split);
+  }
   if (s->n <= 8) return launch<8>(s, alpha);
   if (s->n <= 16) return launch<16>(s, alpha);
   if (s->n <= 32) return launch<32>(s, alpha);
@@ -731,6 +942,8 @@ int nvfp4_gemm_tc(const qwen36_nvfp4_gemm_spec_t *s, float alpha) {
 // Tuning hook: 128 forces 128-token tiles (two accumulator stages) for large n, 256 single-CTA
 // 256-token tiles, 512 CTA pairs (where the shape allows them); 0 = default.
 extern "C" void qwen36_nvfp4_gemm_force_bn(int bn) { g_force_bn = bn; }
+// Tuning hook: CTAs per row block of the split-K form for n <= 16 (1 = never split, 0 = heuristic).
+extern "C" void qwen36_nvfp4_gemm_force_split(int split) { g_force_split = split; }
 extern "C" void qwen36_nvfp4_gemm_debug(int mask) {
   const unsigned int v = static_cast<unsigned int>(mask);
   cudaMemcpyToSymbol(g_debug, &v, sizeof(v));

@@ -227,6 +227,28 @@ def test_w4a4_gemm_tile_variants(backend, m, n, k):
         assert np.array_equal(got, outs[0])
 
 
+@pytest.mark.parametrize("m,n,k", [(1024, 1, 5120), (640, 8, 6144), (256, 3, 17408), (384, 16, 1024), (128, 5, 512)])
+def test_w4a4_decode_split_k(backend, m, n, k):
+    """Few tokens, few row blocks: clusters of CTAs split K and add their partial sums through
+    distributed shared memory.  Every split factor matches the oracle; split and unsplit results
+    differ only by float32 summation order."""
+    rng = np.random.default_rng(11 * m + n + k)
+    a, a_sf, x, b, b_sf, alpha = w4a4_case(rng, m, n, k)
+    want = synth.bf16_bits_to_f32(orc.nvfp4_gemm(a, a_sf, b, b_sf, alpha, m, n, k))
+    dev = [to_dev(t) for t in (a, a_sf, b, b_sf)]
+    try:
+        for split in (0, 1, 2, 3, 8):
+            backend.lib.qwen36_nvfp4_gemm_force_split(split)
+            out = torch.full((n, m), float("nan"), dtype=torch.bfloat16, device="cuda")
+            entry = backend.decode_nvfp4_gemv_raw if n <= 8 else backend.nvfp4_gemm_raw   # the decode entry takes n <= 8
+            assert entry(*dev, alpha, m, n, k, out) == abi.SUCCESS
+            got = synth.bf16_bits_to_f32(bf16_host(out))
+            assert rel_l2(got, want) <= 1e-2, split
+    finally:
+        backend.lib.qwen36_nvfp4_gemm_force_split(0)
+    assert backend.lib.qwen36_nvfp4_gemm_last_error() == 0
+
+
 def test_w4a4_known_answer_132_and_alpha_zero(backend):
     # kernels-cuda/smoke.cu:2140-2180
     k = m = 128
