@@ -208,6 +208,28 @@ def per_shape_cold(backend, torch, sweep, synth):
     return out
 
 
+def per_shape_w4a4_decode(backend, torch, sweep, synth, tokens: int = 1):
+    """The same shapes through the W4A4 decode entry (activations quantised to NVFP4 once, then
+    qwen36_decode_nvfp4_gemv per matrix): tcgen05 block-scaled MMA, split-K clusters where the
+    matrix has few row blocks.  Cold weights as in per_shape_cold."""
+    out = {}
+    for idx, (name, n, k) in enumerate(synth.DECODE_SHAPES):
+        x = torch.randn((tokens, k), device="cuda").to(torch.bfloat16)
+        fp4, sf, ts = backend.nvfp4_quantize_rows(x, 0.37)
+        y = torch.empty((tokens, n), dtype=torch.bfloat16, device="cuda")
+        mats = [layer[idx] for layer in sweep]
+        alpha = synth.WEIGHT_GLOBAL_SCALE * 0.37
+
+        def call(i, mats=mats, fp4=fp4, sf=sf, y=y, n=n, k=k):
+            m = mats[i % len(mats)]
+            rc = backend.decode_nvfp4_gemv_raw(m[3], m[4], fp4, sf, alpha, n, tokens, k, y)
+            if rc != 0:
+                raise RuntimeError(f"qwen36_decode_nvfp4_gemv returned {rc}")
+        us = _time_cuda(torch, call, 192, warm=20, backend=backend)
+        out[name] = {"n": n, "k": k, "us": round(us, 3), "gbs": round(gemv_bytes(n, k) / us / 1e3, 1)}
+    return out
+
+
 def _time_cuda(torch, fn, reps, warm=3, backend=None):
     """Microseconds per call of fn(i), timed with CUDA events around a CUDA-graph replay of `reps`
     calls (so that Python/ctypes launch overhead does not hide short kernels); eager if capture fails."""
@@ -504,6 +526,7 @@ def run_ours(args):
     extra = {}
     if rank == 0 and world == 1 and not args.no_extras:
         extra["per_shape_cold"] = per_shape_cold(backend, torch, sweep, synth)
+        extra["per_shape_w4a4_decode"] = per_shape_w4a4_decode(backend, torch, sweep, synth)
         run_step = None
         try:
             del runner.graph
