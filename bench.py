@@ -47,17 +47,54 @@ def gemv_bytes(n: int, k: int) -> int:
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    """Samples SM clocks and throttle reasons while the timed region runs: NVML from a thread every
+    2 ms (so that even a 30 ms region gets samples), `nvidia-smi -lms` when NVML cannot be loaded."""
 
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NVML_REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
-    def __init__(self, index: int):
+    def __init__(self, index: int, pci_bus_id: str | None = None):
         self.index = index
-        self.samples = []
+        self.pci_bus_id = pci_bus_id
+        self.samples = []          # nvidia-smi lines, or (sm_mhz, reasons_mask) tuples from NVML
         self.proc = None
+        self.nvml = None
+        self.handle = None
+        self.max_mhz = None
+        self._stop = False
+        self.thread = None
+
+    def _start_nvml(self) -> bool:
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.handle = (pynvml.nvmlDeviceGetHandleByPciBusId(self.pci_bus_id) if self.pci_bus_id
+                           else pynvml.nvmlDeviceGetHandleByIndex(self.index))
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            pynvml.nvmlDeviceGetClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+            pynvml.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
+            self.nvml = pynvml
+            return True
+        except Exception:
+            self.nvml = None
+            return False
+
+    def _poll_nvml(self):
+        nv = self.nvml
+        while not self._stop:
+            try:
+                self.samples.append((float(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)),
+                                     int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle))))
+            except Exception:
+                pass
+            time.sleep(0.002)
 
     def start(self):
+        if self._start_nvml():
+            self.thread = threading.Thread(target=self._poll_nvml, daemon=True)
+            self.thread.start()
+            return
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
@@ -72,6 +109,16 @@ class ClockSampler:
             self.samples.append(line.strip())
 
     def stop(self):
+        if self.nvml is not None:
+            self._stop = True
+            self.thread.join(timeout=2)
+            sm = sorted(s[0] for s in self.samples)
+            mask = 0
+            for s_ in self.samples:
+                mask |= s_[1]
+            reasons = sorted(name for bit, name in self.NVML_REASONS.items() if mask & bit)
+            return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": self.max_mhz, "reasons": reasons,
+                    "samples": len(sm), "source": "nvml"}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -94,7 +141,7 @@ class ClockSampler:
                     reasons.add(name)
         sm.sort()
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "source": "nvidia-smi"}
 
 
 # --------------------------------------------------------------------------- ours
@@ -490,7 +537,12 @@ def run_ours(args):
     for _ in range(args.warmup):
         run_step(x_dev)
     barrier()
-    sampler = ClockSampler(local_rank)
+    try:
+        props = torch.cuda.get_device_properties(torch.cuda.current_device())
+        bus = f"{props.pci_domain_id:08x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+    except AttributeError:
+        bus = None
+    sampler = ClockSampler(local_rank, bus)
     if rank == 0:
         sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

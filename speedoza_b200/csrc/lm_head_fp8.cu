@@ -71,7 +71,12 @@ __device__ __forceinline__ float2 e4m3x2_to_f32(uint32_t pair) {
   return __half22float2(*reinterpret_cast<__half2 *>(&h2));
 }
 
-template <int N> struct RowsPerWarp { static constexpr int value = N == 1 ? 4 : (N <= 4 ? 2 : 1); };
+// Rows a warp carries at once: more rows keep more 16-byte loads in flight and share every
+// activation load; bounded by registers (rows x tokens accumulators).  With float32 staging the
+// CTAs are larger (fewer warps per SM), so each warp carries twice as many rows.
+template <int N, bool XF32> struct RowsPerWarp {
+  static constexpr int value = N == 1 ? 4 : (XF32 ? (N <= 4 ? 4 : 2) : (N <= 4 ? 2 : 1));
+};
 
 // x lives in shared memory as bf16, 16-byte chunks, chunk c stored at
 // c ^ ((c >> 3) & 1) so that a quarter warp (chunks 2l+i, l = 0..7) hits eight
@@ -82,21 +87,35 @@ __device__ __forceinline__ uint32_t xswz(uint32_t chunk) { return chunk ^ ((chun
 // FUSED = true : keeps the running (value, index) of the bf16-rounded logits
 //   per token; per-CTA winners go to `partials`, the last CTA to finish (ticket
 //   counter) merges them, writes the tokens and re-zeroes the ticket.
-template <int N, bool FUSED>
+// XF32: the activations are staged as float32 (16-byte chunks, XOR-swizzled so that the eight
+// lanes of a quarter warp, 64 bytes apart, hit distinct bank groups) instead of bf16.  With
+// several tokens and only one or two rows per warp the bf16 -> f32 unpack would otherwise cost as
+// many instructions as the FMAs themselves.
+__device__ __forceinline__ uint32_t xswz32(uint32_t chunk) { return chunk ^ ((chunk >> 3) & 7u); }
+
+template <int N, bool FUSED, bool XF32>
 __global__ void __launch_bounds__(kThreads)
 lm_head_gemv_kernel(const uint8_t *__restrict__ weight, const float *__restrict__ row_scales,
                     const __nv_bfloat16 *__restrict__ x, __nv_bfloat16 *__restrict__ y, size_t rows,
                     uint32_t cols, uint32_t row_offset, uint32_t *__restrict__ out_tokens,
                     float *__restrict__ out_best, float2 *__restrict__ partials,
                     unsigned *__restrict__ ticket) {
-  constexpr int R = RowsPerWarp<N>::value;
+  constexpr int R = RowsPerWarp<N, XF32>::value;
   extern __shared__ __align__(16) uint8_t smem[];
   uint4 *xs = reinterpret_cast<uint4 *>(smem);        // N * cols bf16, swizzled chunks
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
   const uint32_t chunks_per_tok = cols / 8u;
 
-  for (uint32_t c = threadIdx.x; c < N * chunks_per_tok; c += kThreads)
-    xs[xswz(c)] = __ldcg(reinterpret_cast<const uint4 *>(x) + c);
+  if constexpr (XF32) {
+    for (uint32_t c = threadIdx.x; c < N * chunks_per_tok; c += kThreads) {
+      const uint4 v = __ldcg(reinterpret_cast<const uint4 *>(x) + c);
+      xs[xswz32(2u * c)] = make_uint4(v.x << 16, v.x & 0xffff0000u, v.y << 16, v.y & 0xffff0000u);
+      xs[xswz32(2u * c + 1u)] = make_uint4(v.z << 16, v.z & 0xffff0000u, v.w << 16, v.w & 0xffff0000u);
+    }
+  } else {
+    for (uint32_t c = threadIdx.x; c < N * chunks_per_tok; c += kThreads)
+      xs[xswz(c)] = __ldcg(reinterpret_cast<const uint4 *>(x) + c);
+  }
   __syncthreads();
 
   float best[N];
@@ -146,13 +165,20 @@ lm_head_gemv_kernel(const uint8_t *__restrict__ weight, const float *__restrict_
         }
 #pragma unroll
         for (int t = 0; t < N; ++t) {
-          const uint4 xc = xs[xswz(t * chunks_per_tok + chunk0 + half)];
-          const uint32_t xw[4] = {xc.x, xc.y, xc.z, xc.w};
           float xv[8];
+          if constexpr (XF32) {
+            const uint32_t c32 = 2u * (t * chunks_per_tok + chunk0 + half);
+            const uint4 xa = xs[xswz32(c32)], xb = xs[xswz32(c32 + 1u)];
+            xv[0] = __uint_as_float(xa.x); xv[1] = __uint_as_float(xa.y); xv[2] = __uint_as_float(xa.z); xv[3] = __uint_as_float(xa.w);
+            xv[4] = __uint_as_float(xb.x); xv[5] = __uint_as_float(xb.y); xv[6] = __uint_as_float(xb.z); xv[7] = __uint_as_float(xb.w);
+          } else {
+            const uint4 xc = xs[xswz(t * chunks_per_tok + chunk0 + half)];
+            const uint32_t xw[4] = {xc.x, xc.y, xc.z, xc.w};
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            xv[2 * i] = __uint_as_float(xw[i] << 16);
-            xv[2 * i + 1] = __uint_as_float(xw[i] & 0xffff0000u);
+            for (int i = 0; i < 4; ++i) {
+              xv[2 * i] = __uint_as_float(xw[i] << 16);
+              xv[2 * i + 1] = __uint_as_float(xw[i] & 0xffff0000u);
+            }
           }
 #pragma unroll
           for (int r = 0; r < R; ++r)
@@ -329,21 +355,36 @@ int sm_count() {
   return g_sm_count;
 }
 
+// Bytes of activation staging: float32 for 3..8 tokens while that fits, bf16 otherwise.
+bool stage_f32(size_t n, size_t cols) { return n >= 3 && n <= 8 && n * cols * 4 <= 200 * 1024; }
+size_t stage_bytes(size_t n, size_t cols) { return n * cols * (stage_f32(n, cols) ? 4 : 2); }
+
+template <int N, bool FUSED, bool XF32>
+int launch_gemv_x(const uint8_t *w, const float *scales, const __nv_bfloat16 *x, __nv_bfloat16 *y, size_t rows,
+                  size_t cols, uint32_t row_offset, uint32_t *tokens, float *best, float2 *partials,
+                  unsigned *ticket, unsigned grid) {
+  const size_t smem = static_cast<size_t>(N) * cols * (XF32 ? 4 : 2);
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(lm_head_gemv_kernel<N, FUSED, XF32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    200 * 1024);
+  });
+  if (attr_err != cudaSuccess) return QWEN36_STATUS_CUDA_ERROR;
+  lm_head_gemv_kernel<N, FUSED, XF32><<<grid, kThreads, smem, q36::stream()>>>(
+      w, scales, x, y, rows, static_cast<uint32_t>(cols), row_offset, tokens, best, partials, ticket);
+  return q36::launch_status();
+}
+
 template <int N, bool FUSED>
 int launch_gemv_n(const uint8_t *w, const float *scales, const __nv_bfloat16 *x, __nv_bfloat16 *y, size_t rows,
                   size_t cols, uint32_t row_offset, uint32_t *tokens, float *best, float2 *partials,
                   unsigned *ticket, unsigned grid) {
-  const size_t smem = static_cast<size_t>(N) * cols * 2;
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(lm_head_gemv_kernel<N, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    200 * 1024);
-  });
-  if (attr_err != cudaSuccess) return QWEN36_STATUS_CUDA_ERROR;
-  lm_head_gemv_kernel<N, FUSED><<<grid, kThreads, smem, q36::stream()>>>(
-      w, scales, x, y, rows, static_cast<uint32_t>(cols), row_offset, tokens, best, partials, ticket);
-  return q36::launch_status();
+  if constexpr (N >= 3 && N <= 8) {
+    if (stage_f32(N, cols))
+      return launch_gemv_x<N, FUSED, true>(w, scales, x, y, rows, cols, row_offset, tokens, best, partials, ticket, grid);
+  }
+  return launch_gemv_x<N, FUSED, false>(w, scales, x, y, rows, cols, row_offset, tokens, best, partials, ticket, grid);
 }
 
 template <bool FUSED>
@@ -362,9 +403,10 @@ int launch_gemv(size_t n, const uint8_t *w, const float *scales, const __nv_bflo
 
 // Persistent grid: enough CTAs to fill the GPU, never more than there is work.
 unsigned gemv_grid(size_t rows, size_t n, size_t cols) {
-  const int r = n == 1 ? 4 : (n <= 4 ? 2 : 1);
+  const bool f32 = stage_f32(n, cols);
+  const int r = n == 1 ? 4 : (f32 ? (n <= 4 ? 4 : 2) : (n <= 4 ? 2 : 1));
   const size_t need = q36::div_ceil(rows, static_cast<size_t>(kWarps) * r);
-  const size_t smem = n * cols * 2;
+  const size_t smem = stage_bytes(n, cols);
   const size_t per_sm = smem > 100 * 1024 ? 1 : (smem > 48 * 1024 ? 2 : 4);
   const size_t cap = static_cast<size_t>(sm_count()) * per_sm;
   return static_cast<unsigned>(need < cap ? need : cap);
