@@ -346,6 +346,19 @@ def other_configs(backend, torch, synth):
             del x, fp4, sf, c
         del ws
     out["prefill_gemm"] = gemm
+    # ---- fused producers of quantised activations (decode: one vector per call) -------------
+    hid, inter = synth.HIDDEN, 17408
+    xn = torch.randn(hid, generator=gen, device="cuda").to(torch.bfloat16)
+    wn = (torch.randn(hid, generator=gen, device="cuda") * 0.1).to(torch.bfloat16)
+    rn = torch.randn(hid, generator=gen, device="cuda").to(torch.bfloat16)
+    gt = (torch.randn(inter, generator=gen, device="cuda") * 2).to(torch.bfloat16)
+    up = torch.randn(inter, generator=gen, device="cuda").to(torch.bfloat16)
+    sw = backend.swiglu_nvfp4_quantize(gt, up, 0.37)
+    norm_us = _time_cuda(torch, lambda i: backend.rmsnorm_nvfp4_quantize(xn, wn, rn, 1e-6, 0.37, True, True), 50,
+                         backend=backend)
+    swiglu_us = _time_cuda(torch, lambda i: backend.swiglu_nvfp4_quantize(gt, up, 0.37, *sw), 50, backend=backend)
+    out["fused_producers"] = {"rmsnorm_nvfp4_quantize_us": round(norm_us, 2), "hidden": hid,
+                              "swiglu_nvfp4_quantize_us": round(swiglu_us, 2), "intermediate": inter}
     # ---- config 3: FP8 lm_head + greedy argmax ---------------------------------------------
     rows, cols = synth.VOCAB, synth.HIDDEN
     w = torch.randint(0, 0x7F, (rows, cols), generator=gen, dtype=torch.uint8, device="cuda")

@@ -110,6 +110,47 @@ typedef struct {
   qwen36_device_ptr_t input_row_major_u8, output_tiled_u8;
 } qwen36_nvfp4_retile_scales_spec_t;
 
+/* ---- fused producers of NVFP4 activations (decode path) -------------------- */
+
+/* qwen36_fp4.h:264-276.  out = (input [+ residual]) * rsqrt(mean(sq) + eps) *
+ * (1 + weight), written as bf16 (optional), as NVFP4 codes and as tiled block
+ * scales (outer row 0); residual_out (optional) receives input + residual. */
+typedef struct {
+  size_t hidden;
+  float eps;
+  qwen36_device_ptr_t input_bf16;
+  qwen36_device_ptr_t weight_bf16;
+  qwen36_device_ptr_t residual_bf16;
+  qwen36_device_ptr_t residual_out_bf16;
+  qwen36_device_ptr_t output_bf16;
+  qwen36_device_ptr_t output_fp4;
+  qwen36_device_ptr_t output_scale_e4m3;
+  qwen36_device_ptr_t output_tensor_scale_f32;
+  float input_tensor_scale_f32;
+} qwen36_rmsnorm_nvfp4_quantize_spec_t;
+
+/* qwen36_fp4.h:304-312.  y = silu(gate) * up in float32, quantised like
+ * qwen36_nvfp4_quantize_bf16 without the bf16 round trip. */
+typedef struct {
+  size_t intermediate;
+  qwen36_device_ptr_t gate_bf16;
+  qwen36_device_ptr_t up_bf16;
+  qwen36_device_ptr_t output_fp4;
+  qwen36_device_ptr_t output_scale_e4m3;
+  qwen36_device_ptr_t output_tensor_scale_f32;
+  float input_tensor_scale_f32;
+} qwen36_swiglu_nvfp4_quantize_spec_t;
+
+/* Replaces qwen36_rmsnorm_nvfp4_quantize (kernels-cuda/ops.cu:1007-1031, body
+ * interpreter/opcodes/rmsnorm_nvfp4_quant.cuh:113-281): one launch, same
+ * arithmetic order (256 strided partial sums + halving tree, rsqrtf), eps == 0
+ * is read as 1e-6. */
+int qwen36_rmsnorm_nvfp4_quantize(const qwen36_rmsnorm_nvfp4_quantize_spec_t *spec);
+
+/* Replaces qwen36_swiglu_nvfp4_quantize (kernels-cuda/ops.cu:1500-1521, body
+ * interpreter/opcodes/swiglu_nvfp4_quant.cuh:13-75). */
+int qwen36_swiglu_nvfp4_quantize(const qwen36_swiglu_nvfp4_quantize_spec_t *spec);
+
 /* Replaces qwen36_nvfp4_gemm (kernels-cuda/nvfp4_gemm.cu:341-409, a cuBLASLt
  * call).  Any m, n, k with k % 16 == 0.  alpha == 0 is read as 1.  Shapes with
  * m % 128 == 0 and k % 256 == 0 run on tcgen05 block-scaled MMA: persistent
@@ -371,10 +412,8 @@ int qwen36_interpreter_decode_sm120(const void *program);
 int qwen36_drafter_attention_block_bf16(const void *spec);
 int qwen36_drafter_attention_block_flash_bf16(const void *spec);
 int qwen36_rmsnorm(const void *spec);
-int qwen36_rmsnorm_nvfp4_quantize(const void *spec);
 int qwen36_partial_rope(const void *spec);
 int qwen36_swiglu(const void *spec);
-int qwen36_swiglu_nvfp4_quantize(const void *spec);
 int qwen36_topk_argmax(const void *spec);
 int qwen36_embedding_lookup(const void *spec);
 int qwen36_lm_head_top2_margin(const void *spec);

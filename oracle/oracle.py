@@ -142,6 +142,40 @@ def nvfp4_quantize_rows(x_bf16: np.ndarray, input_tensor_scale: float = 0.0):
     return fp4, sf, float(ts[0])
 
 
+def rmsnorm_nvfp4_quantize(x_bf16: np.ndarray, weight_bf16: np.ndarray, residual_bf16=None, eps: float = 1e-6,
+                           input_tensor_scale: float = 0.0):
+    """One vector.  -> dict(out_bf16, residual_out, fp4, sf (zero-initialised), ts, weighted_f32)."""
+    hidden = x_bf16.shape[0]
+    groups = (hidden + 15) // 16
+    out = np.zeros(hidden, dtype=np.uint16)
+    res_out = np.zeros(hidden, dtype=np.uint16)
+    fp4 = np.zeros((hidden + 1) // 2, dtype=np.uint8)
+    sf = np.zeros(sf_bytes(groups, 1), dtype=np.uint8)
+    ts = np.zeros(1, dtype=np.float32)
+    weighted = np.zeros(hidden, dtype=np.float32)
+    lib().orc_rmsnorm_nvfp4_quantize(_p(x_bf16, _u16p), _p(weight_bf16, _u16p),
+                                     None if residual_bf16 is None else _p(residual_bf16, _u16p), _sz(hidden),
+                                     C.c_float(eps), C.c_float(input_tensor_scale), _p(out, _u16p),
+                                     _p(res_out, _u16p), _p(fp4, _u8p), _p(sf, _u8p), _p(ts, _f32p),
+                                     _p(weighted, _f32p))
+    return {"out_bf16": out, "residual_out": res_out, "fp4": fp4, "sf": sf, "ts": float(ts[0]),
+            "weighted_f32": weighted}
+
+
+def swiglu_nvfp4_quantize(gate_bf16: np.ndarray, up_bf16: np.ndarray, input_tensor_scale: float = 0.0):
+    """One vector.  -> dict(fp4, sf (zero-initialised), ts, y_f32)."""
+    values = gate_bf16.shape[0]
+    groups = (values + 15) // 16
+    fp4 = np.zeros((values + 1) // 2, dtype=np.uint8)
+    sf = np.zeros(sf_bytes(groups, 1), dtype=np.uint8)
+    ts = np.zeros(1, dtype=np.float32)
+    y = np.zeros(values, dtype=np.float32)
+    lib().orc_swiglu_nvfp4_quantize(_p(gate_bf16, _u16p), _p(up_bf16, _u16p), _sz(values),
+                                    C.c_float(input_tensor_scale), _p(fp4, _u8p), _p(sf, _u8p), _p(ts, _f32p),
+                                    _p(y, _f32p))
+    return {"fp4": fp4, "sf": sf, "ts": float(ts[0]), "y_f32": y}
+
+
 def nvfp4_count_e2m1_ties(x_bf16: np.ndarray, input_tensor_scale: float = 0.0) -> int:
     rows, values = x_bf16.shape
     return int(lib().orc_nvfp4_count_e2m1_ties(_p(x_bf16, _u16p), _sz(rows), _sz(values),

@@ -57,6 +57,19 @@ class Nvfp4QuantizeRowsSpec(C.Structure):
                 ("output_tensor_scale_f32", DevicePtr), ("input_tensor_scale_f32", C.c_float)]
 
 
+class RmsnormNvfp4QuantizeSpec(C.Structure):
+    _fields_ = [("hidden", size_t), ("eps", C.c_float), ("input_bf16", DevicePtr), ("weight_bf16", DevicePtr),
+                ("residual_bf16", DevicePtr), ("residual_out_bf16", DevicePtr), ("output_bf16", DevicePtr),
+                ("output_fp4", DevicePtr), ("output_scale_e4m3", DevicePtr),
+                ("output_tensor_scale_f32", DevicePtr), ("input_tensor_scale_f32", C.c_float)]
+
+
+class SwigluNvfp4QuantizeSpec(C.Structure):
+    _fields_ = [("intermediate", size_t), ("gate_bf16", DevicePtr), ("up_bf16", DevicePtr),
+                ("output_fp4", DevicePtr), ("output_scale_e4m3", DevicePtr),
+                ("output_tensor_scale_f32", DevicePtr), ("input_tensor_scale_f32", C.c_float)]
+
+
 class Nvfp4RetileScalesSpec(C.Structure):
     _fields_ = [("rows", size_t), ("inner_groups", size_t), ("input_row_major_u8", DevicePtr),
                 ("output_tiled_u8", DevicePtr)]

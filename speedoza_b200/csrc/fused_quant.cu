@@ -1,0 +1,170 @@
+// Fused producers of NVFP4 activations for the decode path:
+//   qwen36_rmsnorm_nvfp4_quantize : (x [+ residual]) -> RMSNorm * (1 + w) -> bf16 copy + NVFP4 codes + scales
+//   qwen36_swiglu_nvfp4_quantize  : silu(gate) * up  -> NVFP4 codes + scales
+// (reference: kernels-cuda/interpreter/opcodes/rmsnorm_nvfp4_quant.cuh:113-281,
+//  swiglu_nvfp4_quant.cuh:13-75, entry points kernels-cuda/ops.cu:1007-1031,1500-1521).
+//
+// Both are single-vector, latency-bound launches that sit between two GEMVs of every decode
+// layer.  The arithmetic follows the reference expression by expression, because the codes they
+// emit must be the reference's: the sum of squares is taken as 256 strided partial sums met by a
+// halving tree, the normaliser is rsqrtf, silu divides by 1 + expf(-g), the group scale and the
+// codes use the shared NVFP4 codec.  What changes is the shape of the launch: the reference walks
+// whole 16-value groups with one thread each (two passes of 256 threads for hidden = 5120, sixteen
+// serial IEEE divisions per thread); here two lanes share a group in the norm kernel and sixteen
+// lanes share one in the SwiGLU kernel, 256 threads per CTA instead of 32.
+#include "common.cuh"
+
+namespace {
+
+using q36::as_ptr;
+
+constexpr uint32_t kNormSumThreads = 256;   // partial sums of the reference's reduction (ops.cu:1017)
+constexpr uint32_t kNormThreads = 1024;
+
+__device__ __forceinline__ float group_scale_value(float amax, float global_scale) {
+  return amax > 0.0f ? fmaxf(amax / (6.0f * global_scale), 1.0e-8f) : 1.0f;
+}
+
+__global__ void __launch_bounds__(kNormThreads)
+rmsnorm_nvfp4_quantize_kernel(const __nv_bfloat16 *__restrict__ input, const __nv_bfloat16 *__restrict__ weight,
+                              const __nv_bfloat16 *__restrict__ residual, __nv_bfloat16 *__restrict__ residual_out,
+                              __nv_bfloat16 *__restrict__ output_bf16, uint8_t *__restrict__ output_fp4,
+                              uint8_t *__restrict__ output_scale, float *__restrict__ tensor_scale, size_t hidden,
+                              float eps, float input_tensor_scale) {
+  __shared__ float scratch[kNormSumThreads];
+  // ---- sum of squares: thread t < 256 adds pairs t, t + 256, ... in that order ----------------
+  if (threadIdx.x < kNormSumThreads) {
+    float local_sum = 0.0f;
+    const size_t pairs = hidden / 2;
+    const __nv_bfloat162 *input2 = reinterpret_cast<const __nv_bfloat162 *>(input);
+    const __nv_bfloat162 *residual2 = reinterpret_cast<const __nv_bfloat162 *>(residual);
+    for (size_t p = threadIdx.x; p < pairs; p += kNormSumThreads) {
+      const __nv_bfloat162 vp = input2[p];
+      float a = __low2float(vp);
+      float b = __high2float(vp);
+      if (residual2 != nullptr) {
+        const __nv_bfloat162 rp = residual2[p];
+        a += __low2float(rp);
+        b += __high2float(rp);
+      }
+      local_sum += a * a + b * b;
+    }
+    if ((hidden & 1u) != 0u && threadIdx.x == 0u) {
+      float value = __bfloat162float(input[hidden - 1]);
+      if (residual != nullptr) value += __bfloat162float(residual[hidden - 1]);
+      local_sum += value * value;
+    }
+    scratch[threadIdx.x] = local_sum;
+  }
+  __syncthreads();
+  for (unsigned int stride = kNormSumThreads / 2; stride > 0; stride >>= 1) {
+    if (threadIdx.x < stride) scratch[threadIdx.x] += scratch[threadIdx.x + stride];
+    __syncthreads();
+  }
+  const float norm_scale = rsqrtf(scratch[0] / static_cast<float>(hidden) + eps);
+  const size_t groups = q36::div_ceil(hidden, 16);
+  const size_t sf_inner = q36::round_up(groups, 4);
+  const float global_scale = input_tensor_scale > 0.0f ? input_tensor_scale : 1.0f;
+
+  // ---- normalise, quantise: two adjacent lanes per 16-value group, eight values each ----------
+  const size_t half_groups = groups * 2;
+  for (size_t hg0 = 0; hg0 < half_groups; hg0 += kNormThreads) {     // uniform trip count: shuffles below
+    const size_t hg = hg0 + threadIdx.x;
+    const bool live = hg < half_groups;
+    const size_t group = hg >> 1, start = group * 16 + (hg & 1u) * 8;
+    float weighted[8];
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const size_t d = start + i;
+      weighted[i] = 0.0f;
+      if (live && d < hidden) {
+        float value = __bfloat162float(input[d]);
+        if (residual != nullptr) value += __bfloat162float(residual[d]);
+        const float w = value * norm_scale * (1.0f + __bfloat162float(weight[d]));
+        weighted[i] = w;
+        if (output_bf16 != nullptr) output_bf16[d] = __float2bfloat16(w);
+        if (residual_out != nullptr) residual_out[d] = __float2bfloat16(value);
+        amax = fmaxf(amax, fabsf(w));
+      }
+    }
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    const uint32_t scale_code = q36::encode_ue4m3(group_scale_value(amax, global_scale));
+    const float decoded_scale = fmaxf(q36::decode_e4m3(scale_code) * global_scale, 1.0e-8f);
+    if (live && (hg & 1u) == 0u) output_scale[q36::sf_offset(group, 0, sf_inner)] = static_cast<uint8_t>(scale_code);
+#pragma unroll
+    for (int i = 0; i < 8; i += 2) {
+      const size_t d = start + i;
+      if (live && d < hidden) {
+        uint32_t packed = q36::encode_e2m1(weighted[i] / decoded_scale);
+        if (d + 1 < hidden) packed |= q36::encode_e2m1(weighted[i + 1] / decoded_scale) << 4;
+        output_fp4[d / 2] = static_cast<uint8_t>(packed);
+      }
+    }
+  }
+  if (threadIdx.x == 0 && tensor_scale != nullptr) *tensor_scale = global_scale;
+}
+
+constexpr uint32_t kSwigluThreads = 256;
+
+// One lane per value, sixteen lanes per group.
+__global__ void __launch_bounds__(kSwigluThreads)
+swiglu_nvfp4_quantize_kernel(const __nv_bfloat16 *__restrict__ gate, const __nv_bfloat16 *__restrict__ up,
+                             uint8_t *__restrict__ output_fp4, uint8_t *__restrict__ output_scale,
+                             float *__restrict__ tensor_scale, size_t values, float input_tensor_scale) {
+  const float global_scale = input_tensor_scale > 0.0f ? input_tensor_scale : 1.0f;
+  const size_t idx = static_cast<size_t>(blockIdx.x) * kSwigluThreads + threadIdx.x;
+  const size_t group = idx >> 4;
+  const size_t sf_inner = q36::round_up(q36::div_ceil(values, 16), 4);
+  float y = 0.0f;
+  if (idx < values) {
+    const float g = __bfloat162float(gate[idx]);
+    const float u = __bfloat162float(up[idx]);
+    const float silu = g / (1.0f + expf(-g));
+    y = silu * u;
+  }
+  float amax = fabsf(y);
+#pragma unroll
+  for (int off = 8; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+  const uint32_t scale_code = q36::encode_ue4m3(group_scale_value(amax, global_scale));
+  const float decoded_scale = fmaxf(q36::decode_e4m3(scale_code) * global_scale, 1.0e-8f);
+  const uint32_t code = q36::encode_e2m1(y / decoded_scale);
+  const uint32_t other = __shfl_down_sync(0xffffffffu, code, 1);
+  if (idx < values) {
+    if ((idx & 15u) == 0u) output_scale[q36::sf_offset(group, 0, sf_inner)] = static_cast<uint8_t>(scale_code);
+    if ((idx & 1u) == 0u)
+      output_fp4[idx / 2] = static_cast<uint8_t>(code | (idx + 1 < values ? other << 4 : 0u));
+  }
+  if (idx == 0 && tensor_scale != nullptr) *tensor_scale = global_scale;
+}
+
+}  // namespace
+
+extern "C" int qwen36_rmsnorm_nvfp4_quantize(const qwen36_rmsnorm_nvfp4_quantize_spec_t *spec) {
+  if (spec == nullptr) return QWEN36_STATUS_NULL_POINTER;
+  if (spec->hidden == 0 || spec->input_bf16.ptr == 0 || spec->weight_bf16.ptr == 0 || spec->output_fp4.ptr == 0 ||
+      spec->output_scale_e4m3.ptr == 0)
+    return QWEN36_STATUS_INVALID_ARGUMENT;
+  const float eps = spec->eps == 0.0f ? 1.0e-6f : spec->eps;
+  rmsnorm_nvfp4_quantize_kernel<<<1, kNormThreads, 0, q36::stream()>>>(
+      as_ptr<const __nv_bfloat16>(spec->input_bf16), as_ptr<const __nv_bfloat16>(spec->weight_bf16),
+      as_ptr<const __nv_bfloat16>(spec->residual_bf16), as_ptr<__nv_bfloat16>(spec->residual_out_bf16),
+      as_ptr<__nv_bfloat16>(spec->output_bf16), as_ptr<uint8_t>(spec->output_fp4),
+      as_ptr<uint8_t>(spec->output_scale_e4m3), as_ptr<float>(spec->output_tensor_scale_f32), spec->hidden, eps,
+      spec->input_tensor_scale_f32);
+  return q36::launch_status();
+}
+
+extern "C" int qwen36_swiglu_nvfp4_quantize(const qwen36_swiglu_nvfp4_quantize_spec_t *spec) {
+  if (spec == nullptr) return QWEN36_STATUS_NULL_POINTER;
+  if (spec->intermediate == 0 || spec->gate_bf16.ptr == 0 || spec->up_bf16.ptr == 0 || spec->output_fp4.ptr == 0 ||
+      spec->output_scale_e4m3.ptr == 0)
+    return QWEN36_STATUS_INVALID_ARGUMENT;
+  const size_t padded = q36::round_up(spec->intermediate, 16);
+  const unsigned blocks = static_cast<unsigned>(q36::div_ceil(padded, kSwigluThreads));
+  swiglu_nvfp4_quantize_kernel<<<blocks, kSwigluThreads, 0, q36::stream()>>>(
+      as_ptr<const __nv_bfloat16>(spec->gate_bf16), as_ptr<const __nv_bfloat16>(spec->up_bf16),
+      as_ptr<uint8_t>(spec->output_fp4), as_ptr<uint8_t>(spec->output_scale_e4m3),
+      as_ptr<float>(spec->output_tensor_scale_f32), spec->intermediate, spec->input_tensor_scale_f32);
+  return q36::launch_status();
+}

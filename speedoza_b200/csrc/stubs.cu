@@ -20,10 +20,8 @@ Q36_STUB(qwen36_interpreter_decode_sm120)
 Q36_STUB(qwen36_drafter_attention_block_bf16)
 Q36_STUB(qwen36_drafter_attention_block_flash_bf16)
 Q36_STUB(qwen36_rmsnorm)
-Q36_STUB(qwen36_rmsnorm_nvfp4_quantize)
 Q36_STUB(qwen36_partial_rope)
 Q36_STUB(qwen36_swiglu)
-Q36_STUB(qwen36_swiglu_nvfp4_quantize)
 Q36_STUB(qwen36_topk_argmax)
 Q36_STUB(qwen36_embedding_lookup)
 Q36_STUB(qwen36_lm_head_top2_margin)

@@ -66,6 +66,13 @@ def test_struct_layouts_equal_reference_header(tmp_path):
         "qwen36_nvfp4_quantize_rows_spec_t": ["rows", "values", "input_bf16", "output_fp4", "output_scale_e4m3",
                                               "output_tensor_scale_f32", "input_tensor_scale_f32"],
         "qwen36_nvfp4_retile_scales_spec_t": ["rows", "inner_groups", "input_row_major_u8", "output_tiled_u8"],
+        "qwen36_rmsnorm_nvfp4_quantize_spec_t": ["hidden", "eps", "input_bf16", "weight_bf16", "residual_bf16",
+                                                 "residual_out_bf16", "output_bf16", "output_fp4",
+                                                 "output_scale_e4m3", "output_tensor_scale_f32",
+                                                 "input_tensor_scale_f32"],
+        "qwen36_swiglu_nvfp4_quantize_spec_t": ["intermediate", "gate_bf16", "up_bf16", "output_fp4",
+                                                "output_scale_e4m3", "output_tensor_scale_f32",
+                                                "input_tensor_scale_f32"],
         "qwen36_lm_head_fp8_quantize_spec_t": ["rows", "cols", "weight_bf16", "weight_e4m3", "row_scales_f32"],
         "qwen36_lm_head_fp8_gemv_spec_t": ["rows", "cols", "n", "weight_e4m3", "row_scales_f32", "input_bf16",
                                            "output_bf16"],
@@ -105,6 +112,8 @@ def test_struct_layouts_equal_reference_header(tmp_path):
 def test_ctypes_mirrors_match_header_sizes(tmp_path):
     names = {"qwen36_nvfp4_gemm_spec_t": abi.Nvfp4GemmSpec, "qwen36_nvfp4_matvec_spec_t": abi.Nvfp4MatvecSpec,
              "qwen36_nvfp4_quantize_rows_spec_t": abi.Nvfp4QuantizeRowsSpec,
+             "qwen36_rmsnorm_nvfp4_quantize_spec_t": abi.RmsnormNvfp4QuantizeSpec,
+             "qwen36_swiglu_nvfp4_quantize_spec_t": abi.SwigluNvfp4QuantizeSpec,
              "qwen36_lm_head_fp8_argmax_spec_t": abi.LmHeadFp8ArgmaxSpec,
              "qwen36_lm_head_fp8_gemv_spec_t": abi.LmHeadFp8GemvSpec,
              "qwen36_sampling_spec_t": abi.SamplingSpec, "qwen36_sampling_rows_spec_t": abi.SamplingRowsSpec,

@@ -135,3 +135,46 @@ def test_reference_int8_kv_equals_oracle(ref):
     want = synth.bf16_bits_to_f32(orc.kv_attention(q, kq_o, vq_o, meta_o, T - 1)).astype(np.float64)
     got = synth.bf16_bits_to_f32(bf16_host(out)).astype(np.float64)
     assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 2e-3     # expf differs by an ulp or two
+
+
+@pytest.mark.parametrize("hidden,with_residual,its", [(5120, True, 0.0), (5120, False, 0.37), (6144, True, 1.25),
+                                                      (33, True, 1.25), (100, False, 0.0)])
+def test_rmsnorm_nvfp4_quantize_equals_reference_bitwise(ref, backend, hidden, with_residual, its):
+    """This library's fused RMSNorm + quantise against the reference's own kernel, both on the GPU:
+    every output byte equal (bf16 copy, residual, codes, tiled scale bytes, tensor scale)."""
+    rng = np.random.default_rng(31 * hidden + int(its * 100))
+    x = to_dev(synth.activations(rng, 1, hidden, outlier_frac=0.01)[0])
+    w = to_dev(synth.f32_to_bf16_bits((rng.standard_normal(hidden) * 0.1).astype(np.float32)))
+    res = to_dev(synth.activations(rng, 1, hidden)[0]) if with_residual else None
+    outs = []
+    for entry in (ref.qwen36_rmsnorm_nvfp4_quantize, backend.lib.qwen36_rmsnorm_nvfp4_quantize):
+        out = torch.zeros(hidden, dtype=torch.bfloat16, device="cuda")
+        res_out = torch.zeros(hidden, dtype=torch.bfloat16, device="cuda")
+        fp4 = torch.zeros((hidden + 1) // 2, dtype=torch.uint8, device="cuda")
+        sf = torch.zeros(orc.sf_bytes((hidden + 15) // 16, 1), dtype=torch.uint8, device="cuda")
+        ts = torch.zeros(1, dtype=torch.float32, device="cuda")
+        spec = abi.RmsnormNvfp4QuantizeSpec(hidden, 1e-6, dp(x), dp(w), dp(res), dp(res_out), dp(out), dp(fp4), dp(sf),
+                                            dp(ts), its)
+        assert entry(C.byref(spec)) == 0
+        torch.cuda.synchronize()
+        outs.append([t.cpu().numpy() for t in (out.view(torch.int16), res_out.view(torch.int16), fp4, sf, ts)])
+    for a, b in zip(*outs):
+        assert np.array_equal(a, b)
+
+
+@pytest.mark.parametrize("n,its", [(17408, 0.0), (17408, 0.37), (33, 1.25), (1000, 0.0)])
+def test_swiglu_nvfp4_quantize_equals_reference_bitwise(ref, backend, n, its):
+    rng = np.random.default_rng(17 * n + int(its * 100))
+    gate = to_dev(synth.f32_to_bf16_bits((rng.standard_normal(n) * 2.0).astype(np.float32)))
+    up = to_dev(synth.activations(rng, 1, n, outlier_frac=0.01)[0])
+    outs = []
+    for entry in (ref.qwen36_swiglu_nvfp4_quantize, backend.lib.qwen36_swiglu_nvfp4_quantize):
+        fp4 = torch.zeros((n + 1) // 2, dtype=torch.uint8, device="cuda")
+        sf = torch.zeros(orc.sf_bytes((n + 15) // 16, 1), dtype=torch.uint8, device="cuda")
+        ts = torch.zeros(1, dtype=torch.float32, device="cuda")
+        spec = abi.SwigluNvfp4QuantizeSpec(n, dp(gate), dp(up), dp(fp4), dp(sf), dp(ts), its)
+        assert entry(C.byref(spec)) == 0
+        torch.cuda.synchronize()
+        outs.append([t.cpu().numpy() for t in (fp4, sf, ts)])
+    for a, b in zip(*outs):
+        assert np.array_equal(a, b)

@@ -5,6 +5,7 @@ known-answer vectors of the reference's kernel smoke test
 import numpy as np
 
 from oracle import oracle as orc
+from speedoza_b200 import synth
 
 LUT = np.array([0, .5, 1, 1.5, 2, 3, 4, 6, -0., -.5, -1, -1.5, -2, -3, -4, -6], dtype=np.float32)
 
@@ -220,3 +221,33 @@ def test_kv_encode_attention_and_split_merge():
     assert np.isneginf(pm[:, 1]).all() and (pl[:, 1] == 0).all()
     merged = orc.bf16_to_f32(orc.merge_partials(pm, pl, po))
     assert np.allclose(merged, want, rtol=2e-2, atol=2e-3)
+
+
+def test_fused_producers_known_answers():
+    """kernels-cuda/smoke.cu:1187-1215: RMSNorm + quantise of sixteen ones with zero weight gives bf16
+    1.0, scale byte 0x23 and codes 0x77.  SwiGLU + quantise equals the plain row quantiser applied
+    to the float32 product (same codec), checked on values that are exact in bf16."""
+    ones = synth.f32_to_bf16_bits(np.ones(16, np.float32))
+    zeros = synth.f32_to_bf16_bits(np.zeros(16, np.float32))
+    r = orc.rmsnorm_nvfp4_quantize(ones, zeros, None, 1e-6, 0.0)
+    assert np.all(r["fp4"] == 0x77) and r["sf"][0] == 0x23 and r["ts"] == 1.0
+    assert np.all(synth.bf16_bits_to_f32(r["out_bf16"]) == 1.0)
+    # residual path: input + residual is what gets normalised and what residual_out carries
+    half = synth.f32_to_bf16_bits(np.full(16, 0.5, np.float32))
+    r2 = orc.rmsnorm_nvfp4_quantize(half, zeros, half, 1e-6, 0.0)
+    assert np.array_equal(r2["fp4"], r["fp4"]) and np.array_equal(r2["residual_out"], ones)
+    # ragged vector (33 values), global-scale branch
+    x = synth.f32_to_bf16_bits(((np.arange(33) % 13) - 6).astype(np.float32) * 0.1875)
+    w = synth.f32_to_bf16_bits(np.linspace(-0.5, 0.5, 33).astype(np.float32))
+    r3 = orc.rmsnorm_nvfp4_quantize(x, w, None, 1e-6, 1.25)
+    assert r3["ts"] == 1.25 and r3["fp4"].shape == (17,) and (r3["fp4"][16] >> 4) == 0
+    # swiglu: gate = 0 gives silu = 0 -> all-zero codes and the amax == 0 scale byte 0x38
+    g0 = synth.f32_to_bf16_bits(np.zeros(32, np.float32))
+    up = synth.f32_to_bf16_bits(np.arange(32, dtype=np.float32))
+    s0 = orc.swiglu_nvfp4_quantize(g0, up, 0.0)
+    assert np.all(s0["fp4"] == 0) and s0["sf"][0] == 0x38 and s0["sf"][1] == 0x38
+    # the codes follow from y exactly as the row quantiser would produce them from bf16(y) when y is exact in bf16
+    g = synth.f32_to_bf16_bits(np.full(32, 40.0, np.float32))      # silu(40) == 40 in float32
+    s1 = orc.swiglu_nvfp4_quantize(g, up, 0.0)
+    want_fp4, want_sf, _ = orc.nvfp4_quantize_rows(synth.f32_to_bf16_bits(40.0 * np.arange(32, dtype=np.float32))[None, :], 0.0)
+    assert np.array_equal(s1["fp4"], want_fp4[0]) and np.array_equal(s1["sf"], want_sf)
