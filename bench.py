@@ -723,10 +723,31 @@ def measure_sharded(workload, tokens, steps, warmup, b, torch, dist, world, rank
     for _ in range(max(3, warmup)):
         step()
     barrier()
+    # One step (kernels + the combine collective) recorded into a CUDA graph, as a serving engine
+    # replays it; every rank must take the same route, so a failed capture anywhere means eager everywhere.
+    graph = None
+    try:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, capture_error_mode="thread_local" if world > 1 else "global"):
+            b.sync_stream()
+            step()
+        b.sync_stream()
+    except Exception:
+        graph = None
+        b.sync_stream()
+    if world > 1:
+        flag = torch.tensor([1 if graph is not None else 0], dtype=torch.int32, device="cuda")
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag[0]) == 0:
+            graph = None
+    run = graph.replay if graph is not None else step
+    for _ in range(3):
+        run()
+    barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(steps):
-        step()
+        run()
     e1.record()
     barrier()
     ms = e0.elapsed_time(e1)
@@ -736,7 +757,8 @@ def measure_sharded(workload, tokens, steps, warmup, b, torch, dist, world, rank
         ms = float(t[0])
     per = ms / steps
     value = work / (per * 1e-3) / (1e9 if unit == "GB/s" else 1e12)
-    return {"workload": name, "value": round(value, 1), "unit": unit, "ms_per_step": round(per, 4), "dtype": dtype}
+    return {"workload": name, "value": round(value, 1), "unit": unit, "ms_per_step": round(per, 4), "dtype": dtype,
+            "launch": "CUDA graph replay" if graph is not None else "eager"}
 
 
 def run_sharded_workload(args):
