@@ -104,6 +104,24 @@ __device__ static inline uint32_t encode_e2m1(float v) {
   return (v < 0.0f ? 8u : 0u) | idx;
 }
 
+// Two floats -> one packed byte (lo in the low nibble), same result as two encode_e2m1 calls,
+// built on the hardware conversion cvt.rn.satfinite.e2m1x2.f32.  The hardware rounds to nearest
+// with ties to even and saturates at 6; the reference rule sends ties toward zero, which differs
+// only at the exact magnitudes 0.75, 1.75 and 3.5 (even would go up), and reports -0.0 as code 0
+// where the hardware keeps the sign.  NaN gives +6 (code 7) on both.
+__device__ static inline uint32_t encode_e2m1x2(float lo, float hi) {
+  uint32_t packed;
+  asm("{\n\t.reg .b8 t;\n\tcvt.rn.satfinite.e2m1x2.f32 t, %1, %2;\n\tcvt.u32.u8 %0, t;\n\t}"
+      : "=r"(packed) : "f"(hi), "f"(lo));
+  const uint32_t bl = __float_as_uint(lo) & 0x7fffffffu, bh = __float_as_uint(hi) & 0x7fffffffu;
+  // ties that round-to-even takes up: step the magnitude back down
+  if (bl == 0x3f400000u || bl == 0x3fe00000u || bl == 0x40600000u) packed -= 1u;
+  if (bh == 0x3f400000u || bh == 0x3fe00000u || bh == 0x40600000u) packed -= 16u;
+  if (bl == 0u) packed &= 0xf0u;     // +-0 -> code 0
+  if (bh == 0u) packed &= 0x0fu;
+  return packed;
+}
+
 // E2M1 nibble -> float (kernels-cuda/ops.cu:520-523) without a table:
 // magnitude code c = (e << 1) | m is 0.5 * m for e == 0, else 2^(e-1)*(1+m/2).
 __device__ static inline float e2m1_value(uint32_t code) {

@@ -17,24 +17,27 @@ constexpr int kThreads = 256;
 // One thread per 16-group.  `quads` = ceil(groups / 4): the group index space
 // of a row is padded to a multiple of four so that the lanes 4q..4q+3 always
 // belong to one row and one 4-byte scale word.
+// Index: uint32_t when rows * padded groups and every byte offset fit 32 bits (index arithmetic is a
+// visible share of this kernel's instructions), size_t otherwise.
+template <typename Index>
 __global__ void __launch_bounds__(kThreads)
 nvfp4_quantize_kernel(const __nv_bfloat16 *__restrict__ in, uint8_t *__restrict__ out_fp4,
-                      uint8_t *__restrict__ out_sf, float *__restrict__ tensor_scale, size_t rows,
-                      size_t values, float input_tensor_scale) {
+                      uint8_t *__restrict__ out_sf, float *__restrict__ tensor_scale, Index rows,
+                      Index values, float input_tensor_scale) {
   const float g = input_tensor_scale > 0.0f ? input_tensor_scale : 1.0f;
-  const size_t groups = q36::div_ceil(values, 16);
-  const size_t padded = q36::round_up(groups, 4);
-  const size_t idx = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x;
-  const size_t row = idx / padded;
-  const size_t group = idx % padded;
+  const Index groups = (values + 15) / 16;
+  const Index padded = (groups + 3) / 4 * 4;
+  const Index idx = static_cast<Index>(blockIdx.x) * kThreads + threadIdx.x;
+  const Index row = idx / padded;
+  const Index group = idx - row * padded;
   const bool valid = row < rows && group < groups;
 
   if (idx == 0 && tensor_scale != nullptr) *tensor_scale = g;
 
   uint32_t sf_code = 0;
   if (valid) {
-    const size_t start = group * 16;
-    const __nv_bfloat16 *src = in + row * values + start;
+    const Index start = group * 16;
+    const __nv_bfloat16 *src = in + (row * values + start);
     const bool full = start + 16 <= values;
     float x[16];
     if (full && (reinterpret_cast<uintptr_t>(src) & 15u) == 0) {
@@ -59,13 +62,38 @@ nvfp4_quantize_kernel(const __nv_bfloat16 *__restrict__ in, uint8_t *__restrict_
     sf_code = q36::encode_ue4m3(sv);
     const float ds = fmaxf(__fmul_rn(q36::decode_e4m3(sf_code), g), 1.0e-8f);
 
+    // Codes.  The reference divides by ds in IEEE float32 and compares against fixed thresholds.
+    // Fast path: multiply by the correctly rounded reciprocal (quotient within 2 ulps of the IEEE
+    // one) and let the hardware conversion round to E2M1; that gives the reference's code unless
+    // the quotient lies within a few ulps of a rounding boundary (all seven boundaries have zero
+    // low 21 mantissa bits, so one masked compare finds them, plus infinities and NaN) or is a
+    // negative value so small that the IEEE quotient may underflow to -0 (which the reference
+    // encodes as +0).  Those rare groups are redone with the IEEE division.
     uint32_t lo = 0, hi = 0;
+    const float rcp = __frcp_rn(ds);
+    uint32_t near_boundary = 0xffffffffu, tiny_negative = 0xffffffffu;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) lo |= q36::encode_e2m1(__fdiv_rn(x[i], ds)) << (4 * i);
+    for (int i = 0; i < 8; ++i) {
+      const float q0 = __fmul_rn(x[2 * i], rcp), q1 = __fmul_rn(x[2 * i + 1], rcp);
+      uint32_t byte;
+      asm("{\n\t.reg .b8 t;\n\tcvt.rn.satfinite.e2m1x2.f32 t, %1, %2;\n\tcvt.u32.u8 %0, t;\n\t}"
+          : "=r"(byte) : "f"(q1), "f"(q0));
+      if (i < 4) lo |= byte << (8 * i); else hi |= byte << (8 * (i - 4));
+      const uint32_t b0 = __float_as_uint(q0), b1 = __float_as_uint(q1);
+      near_boundary = min(near_boundary, min((b0 + 4u) & 0x001ffff8u, (b1 + 4u) & 0x001ffff8u));
+      tiny_negative = min(tiny_negative, min(b0 - 0x80000000u, b1 - 0x80000000u));
+    }
+    if (near_boundary == 0u || tiny_negative < 0x0d800000u) {      // exact route
+      lo = hi = 0;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) hi |= q36::encode_e2m1(__fdiv_rn(x[8 + i], ds)) << (4 * i);
+      for (int i = 0; i < 4; ++i)
+        lo |= q36::encode_e2m1x2(__fdiv_rn(x[2 * i], ds), __fdiv_rn(x[2 * i + 1], ds)) << (8 * i);
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        hi |= q36::encode_e2m1x2(__fdiv_rn(x[8 + 2 * i], ds), __fdiv_rn(x[9 + 2 * i], ds)) << (8 * i);
+    }
 
-    uint8_t *dst = out_fp4 + row * q36::div_ceil(values, 2) + start / 2;
+    uint8_t *dst = out_fp4 + (row * ((values + 1) / 2) + start / 2);
     if (full && (reinterpret_cast<uintptr_t>(dst) & 7u) == 0) {
       *reinterpret_cast<uint2 *>(dst) = make_uint2(lo, hi);
     } else {
@@ -82,7 +110,9 @@ nvfp4_quantize_kernel(const __nv_bfloat16 *__restrict__ in, uint8_t *__restrict_
   word |= __shfl_xor_sync(0xffffffffu, word, 1);
   word |= __shfl_xor_sync(0xffffffffu, word, 2);
   if (valid) {
-    const size_t off = q36::sf_offset(group, row, padded);
+    // tiled scale layout (see q36::sf_offset), in Index arithmetic
+    const Index r128 = row % 128;
+    const Index off = ((group / 4) + (row / 128) * (padded / 4)) * 512 + (r128 % 32) * 16 + (r128 / 32) * 4 + (group % 4);
     if ((group | 3) < groups) {          // the whole quad is real: one 4-byte store
       if (lane4 == 0) *reinterpret_cast<uint32_t *>(out_sf + off) = word;
     } else {
@@ -147,9 +177,18 @@ int launch_quantize(qwen36_device_ptr_t in, qwen36_device_ptr_t fp4, qwen36_devi
   const size_t total = rows * padded;
   const size_t blocks = q36::div_ceil(total, kThreads);
   if (blocks > 0x7fffffffull) return QWEN36_STATUS_INVALID_ARGUMENT;
-  nvfp4_quantize_kernel<<<static_cast<unsigned>(blocks), kThreads, 0, q36::stream()>>>(
-      as_ptr<const __nv_bfloat16>(in), as_ptr<uint8_t>(fp4), as_ptr<uint8_t>(sf), as_ptr<float>(ts), rows,
-      values, its);
+  // 32-bit indices when the thread index space, the element offsets (rows * values) and the tiled
+  // scale offsets all stay below 2^32
+  const bool small = (rows + 128) * (values + 64) < (1ull << 32) && (blocks + 1) * kThreads < (1ull << 32);
+  if (small) {
+    nvfp4_quantize_kernel<uint32_t><<<static_cast<unsigned>(blocks), kThreads, 0, q36::stream()>>>(
+        as_ptr<const __nv_bfloat16>(in), as_ptr<uint8_t>(fp4), as_ptr<uint8_t>(sf), as_ptr<float>(ts),
+        static_cast<uint32_t>(rows), static_cast<uint32_t>(values), its);
+  } else {
+    nvfp4_quantize_kernel<size_t><<<static_cast<unsigned>(blocks), kThreads, 0, q36::stream()>>>(
+        as_ptr<const __nv_bfloat16>(in), as_ptr<uint8_t>(fp4), as_ptr<uint8_t>(sf), as_ptr<float>(ts), rows,
+        values, its);
+  }
   return q36::launch_status();
 }
 

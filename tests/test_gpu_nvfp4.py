@@ -183,6 +183,38 @@ def test_matvec_linearity_full_size(backend):
     assert torch.equal(y1.float() * 2, y2.float())
 
 
+def test_quantize_codes_at_every_rounding_boundary(backend):
+    """The device encoder (hardware e2m1 conversion + explicit tie handling) against the oracle's
+    threshold chain on inputs placed exactly on, one bf16 step below and one step above each of the
+    seven rounding boundaries, both signs, for several power-of-two scales (so the quotient is exact),
+    plus zeros of both signs, NaN, infinities and subnormals."""
+    ties = np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0], dtype=np.float32)
+    rows = []
+    for d in (2.0 ** -10, 0.25, 1.0, 8.0, 2.0 ** 20):
+        vals = []
+        for t in ties:
+            b = int(synth.f32_to_bf16_bits(np.array([t * d], np.float32))[0])
+            for step in (-2, -1, 0, 1, 2):
+                vals += [b + step, (b + step) | 0x8000]
+        vals += [0x0000, 0x8000, 0x7FC0, 0xFFC0, 0x7F80, 0xFF80, 0x0001, 0x8001, 0x0080, 0x8080]
+        vals = np.array(vals, dtype=np.uint16)
+        anchor = synth.f32_to_bf16_bits(np.array([6.0 * d], np.float32))[0]      # fixes the group scale at d
+        for i in range(0, len(vals), 15):
+            chunk = vals[i:i + 15]
+            group = np.full(16, 0, dtype=np.uint16)
+            group[0] = anchor
+            group[1:1 + len(chunk)] = chunk
+            rows.append(group)
+    x = np.stack(rows)
+    # groups that hold NaN or inf take their scale from that value: still compared, only the finite
+    # anchor groups exercise the boundaries
+    for its in (0.0, 2.0):
+        want_fp4, want_sf, _ = orc.nvfp4_quantize_rows(x, its)
+        fp4, sf, _ = backend.nvfp4_quantize_rows(to_dev(x), its)
+        assert np.array_equal(fp4.cpu().numpy(), want_fp4)
+        assert np.array_equal(sf.cpu().numpy(), want_sf)
+
+
 # ---------------------------------------------------------------- W4A4 product
 
 def w4a4_case(rng, m, n, k, its=1.25):
