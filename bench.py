@@ -32,6 +32,9 @@ sys.path.insert(0, ROOT)
 METRIC = "NVFP4 GEMV HBM GB/s & GEMM TFLOPS (% roofline) at Qwen3.6-27B shapes"
 
 
+NCU_TRAFFIC_RATIO = (100.314368 + 3.6608) / 100.349952      # dram bytes / algorithmic bytes, GEMV kernel
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -635,7 +638,13 @@ def run_ours(args):
                     "d2h_bytes_per_step": y_host.numel() * 2, "ms_per_step": round(ms_e2e / args.steps, 4),
                     "wall_ms_per_step": round(wall_e2e / args.steps, 4)},
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
-                         "frac": round(achieved / peak, 4), "traffic": None, "peak_kind": peak_kind,
+                         "frac": round(achieved / peak, 4),
+                         # DRAM bytes per launch: ncu measured 100.31 MB read + 3.66 MB written for the
+                         # 100.35 MB gate_up launch (profiles/nvfp4_matvec_gate_up.md); the sweep's
+                         # launches are too many to capture whole, so that ratio is applied to the
+                         # average launch (traffic grows with the units processed)
+                         "traffic": int(per_gpu_bytes // launches_per_step * NCU_TRAFFIC_RATIO),
+                         "traffic_source": "ncu, gate_up launch, scaled by bytes", "peak_kind": peak_kind,
                          "kernel": "nvfp4_matvec_kernel", "launch_us": round(launch_us, 3),
                          "bytes_per_launch": per_gpu_bytes // launches_per_step,
                          "frac_of_nominal_8TBs": round(achieved / 8000.0, 4)},
