@@ -383,6 +383,24 @@ def other_configs(backend, torch, synth):
                    "gemv_gbs": round(byts / us_gemv / 1e3, 1)})
     out["lm_head_fp8"] = lm
     del w, sc
+    # ---- exact-argmax guards: margin verdict over the logits, predicated bf16 lm_head ---------
+    guard = {}
+    logits4 = (torch.randn((4, rows), generator=gen, device="cuda") * 3).to(torch.bfloat16)
+    guard["top2_margin_rows4_us"] = round(_time_cuda(torch, lambda i: backend.lm_head_top2_margin(logits4, 0.5), 20,
+                                                     backend=backend), 2)
+    wb = torch.randn((rows, cols), generator=gen, device="cuda").to(torch.bfloat16)       # 2.5 GB bf16 lm_head
+    for m_tok in (1, 4):
+        xh = torch.randn((m_tok, cols), generator=gen, device="cuda").to(torch.bfloat16)
+        tk = torch.zeros(m_tok, dtype=torch.int32, device="cuda")
+        us = _time_cuda(torch, lambda i: backend.bf16_matvec_argmax_rows(xh, wb, tk), 5, backend=backend)
+        guard[f"bf16_matvec_argmax_rows{m_tok}_us"] = round(us, 1)
+        guard[f"bf16_matvec_argmax_rows{m_tok}_gbs"] = round(rows * cols * 2 / us / 1e3, 1)
+    lg = logits4[:1].contiguous()
+    x1 = torch.randn((1, cols), generator=gen, device="cuda").to(torch.bfloat16)
+    guard["top8_rescore_rows1_us"] = round(_time_cuda(torch, lambda i: backend.lm_head_top8_rescore(lg, wb, x1, 0.5), 20,
+                                                      backend=backend), 2)
+    out["lm_head_guards"] = guard
+    del wb, logits4
     # ---- config 4: int8 KV + decode attention ----------------------------------------------
     att = []
     T = 131072

@@ -110,6 +110,67 @@ typedef struct {
   qwen36_device_ptr_t input_row_major_u8, output_tiled_u8;
 } qwen36_nvfp4_retile_scales_spec_t;
 
+/* ---- exact-argmax guards of the FP8 lm_head -------------------------------- */
+
+#define QWEN36_LM_HEAD_TOP2_BLOCKS 240     /* qwen36_fp4.h:414: blocks of the vocabulary scan */
+
+/* qwen36_fp4.h:384-400.  Full bf16 lm_head + argmax for rows whose
+ * skip_flags_u32 entry is zero (NULL: every row); flagged rows keep their
+ * token.  workspace: rows * 8 bytes. */
+typedef struct {
+  size_t rows;
+  size_t out_features;
+  size_t in_features;
+  qwen36_device_ptr_t input_bf16;
+  qwen36_device_ptr_t weight_bf16;
+  qwen36_device_ptr_t output_token_u32;
+  qwen36_device_ptr_t mirror_last_output_token_u32;
+  qwen36_device_ptr_t workspace;
+  size_t workspace_bytes;
+  qwen36_device_ptr_t skip_flags_u32;
+} qwen36_bf16_matvec_argmax_rows_spec_t;
+
+/* qwen36_fp4.h:416-427.  tokens = argmax of the bf16 logits (lowest index on
+ * ties), flags = 1 when top1 - top2 >= eps.  workspace: rows * 240 * 16 bytes. */
+typedef struct {
+  size_t rows;
+  size_t vocab;
+  float eps;
+  qwen36_device_ptr_t logits_bf16;
+  qwen36_device_ptr_t tokens_u32;
+  qwen36_device_ptr_t flags_u32;
+  qwen36_device_ptr_t mirror_last_token_u32;
+  qwen36_device_ptr_t fallback_count_u32;
+  qwen36_device_ptr_t workspace;
+  size_t workspace_bytes;
+} qwen36_lm_head_top2_margin_spec_t;
+
+/* qwen36_fp4.h:447-461.  Top-8 block winners rescored against the bf16 weight. */
+typedef struct {
+  size_t rows;
+  size_t vocab;
+  size_t cols;
+  float eps;
+  qwen36_device_ptr_t logits_bf16;
+  qwen36_device_ptr_t weight_bf16;
+  qwen36_device_ptr_t input_bf16;
+  qwen36_device_ptr_t tokens_u32;
+  qwen36_device_ptr_t flags_u32;
+  qwen36_device_ptr_t mirror_last_token_u32;
+  qwen36_device_ptr_t fallback_count_u32;
+  qwen36_device_ptr_t workspace;
+  size_t workspace_bytes;
+} qwen36_lm_head_top8_rescore_spec_t;
+
+/* Replace kernels-cuda/lm_head_fp8.cu:528-590 and kernels-cuda/ops.cu:1104-1153.
+ * Same tokens and flags as the reference for every input (same vocabulary
+ * partition, same float64 / float32 summation orders, same tie rules); the
+ * bf16 lm_head reads the weight once for up to eight rows instead of once per
+ * row. */
+int qwen36_lm_head_top2_margin(const qwen36_lm_head_top2_margin_spec_t *spec);
+int qwen36_lm_head_top8_rescore(const qwen36_lm_head_top8_rescore_spec_t *spec);
+int qwen36_bf16_matvec_argmax_rows(const qwen36_bf16_matvec_argmax_rows_spec_t *spec);
+
 /* ---- fused producers of NVFP4 activations (decode path) -------------------- */
 
 /* qwen36_fp4.h:264-276.  out = (input [+ residual]) * rsqrt(mean(sq) + eps) *
@@ -397,7 +458,6 @@ int qwen36_mtp_assume_accept_chain_advance(qwen36_device_ptr_t position_i32, siz
  * spec struct for that operator (qwen36_fp4.h), which this build never reads. */
 int qwen36_bf16_gemm(const void *spec);
 int qwen36_bf16_matvec(const void *spec);
-int qwen36_bf16_matvec_argmax_rows(const void *spec);
 int qwen36_attention_prefill(const void *spec);
 int qwen36_attention_flash_prefill(const void *spec);
 int qwen36_attention_sage_prefill(const void *spec);
@@ -416,8 +476,6 @@ int qwen36_partial_rope(const void *spec);
 int qwen36_swiglu(const void *spec);
 int qwen36_topk_argmax(const void *spec);
 int qwen36_embedding_lookup(const void *spec);
-int qwen36_lm_head_top2_margin(const void *spec);
-int qwen36_lm_head_top8_rescore(const void *spec);
 int qwen36_conv1d_update(const void *spec);
 int qwen36_conv1d_prefill(const void *spec);
 int qwen36_gdn_gate(const void *spec);

@@ -176,6 +176,43 @@ def swiglu_nvfp4_quantize(gate_bf16: np.ndarray, up_bf16: np.ndarray, input_tens
     return {"fp4": fp4, "sf": sf, "ts": float(ts[0]), "y_f32": y}
 
 
+def lm_head_top2_margin(logits_bf16: np.ndarray, eps: float):
+    """[rows, vocab] bf16 bits -> (tokens u32, flags u32, rows whose guard failed)."""
+    rows, vocab = logits_bf16.shape
+    tokens = np.zeros(rows, dtype=np.uint32)
+    flags = np.zeros(rows, dtype=np.uint32)
+    L = lib()
+    L.orc_lm_head_top2_margin.restype = C.c_uint32
+    fb = L.orc_lm_head_top2_margin(_p(logits_bf16, _u16p), _sz(rows), _sz(vocab), C.c_float(eps),
+                                   _p(tokens, C.POINTER(C.c_uint32)), _p(flags, C.POINTER(C.c_uint32)))
+    return tokens, flags, int(fb)
+
+
+def lm_head_top8_rescore(logits_bf16: np.ndarray, weight_bf16: np.ndarray, input_bf16: np.ndarray, eps: float):
+    rows, vocab = logits_bf16.shape
+    cols = weight_bf16.shape[1]
+    tokens = np.zeros(rows, dtype=np.uint32)
+    flags = np.zeros(rows, dtype=np.uint32)
+    L = lib()
+    L.orc_lm_head_top8_rescore.restype = C.c_uint32
+    fb = L.orc_lm_head_top8_rescore(_p(logits_bf16, _u16p), _p(weight_bf16, _u16p), _p(input_bf16, _u16p), _sz(rows),
+                                    _sz(vocab), _sz(cols), C.c_float(eps), _p(tokens, C.POINTER(C.c_uint32)),
+                                    _p(flags, C.POINTER(C.c_uint32)))
+    return tokens, flags, int(fb)
+
+
+def bf16_matvec_argmax_rows(input_bf16: np.ndarray, weight_bf16: np.ndarray, skip_flags=None, tokens_in=None):
+    """input [rows, in], weight [out, in] -> tokens u32 [rows]; flagged rows keep tokens_in."""
+    rows, in_features = input_bf16.shape
+    out_features = weight_bf16.shape[0]
+    tokens = np.zeros(rows, dtype=np.uint32) if tokens_in is None else tokens_in.astype(np.uint32).copy()
+    lib().orc_bf16_matvec_argmax_rows(_p(input_bf16, _u16p), _p(weight_bf16, _u16p),
+                                      None if skip_flags is None else _p(skip_flags, C.POINTER(C.c_uint32)),
+                                      _sz(rows), _sz(out_features), _sz(in_features),
+                                      _p(tokens, C.POINTER(C.c_uint32)))
+    return tokens
+
+
 def nvfp4_count_e2m1_ties(x_bf16: np.ndarray, input_tensor_scale: float = 0.0) -> int:
     rows, values = x_bf16.shape
     return int(lib().orc_nvfp4_count_e2m1_ties(_p(x_bf16, _u16p), _sz(rows), _sz(values),

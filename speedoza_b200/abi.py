@@ -70,6 +70,26 @@ class SwigluNvfp4QuantizeSpec(C.Structure):
                 ("output_tensor_scale_f32", DevicePtr), ("input_tensor_scale_f32", C.c_float)]
 
 
+class Bf16MatvecArgmaxRowsSpec(C.Structure):
+    _fields_ = [("rows", size_t), ("out_features", size_t), ("in_features", size_t), ("input_bf16", DevicePtr),
+                ("weight_bf16", DevicePtr), ("output_token_u32", DevicePtr),
+                ("mirror_last_output_token_u32", DevicePtr), ("workspace", DevicePtr), ("workspace_bytes", size_t),
+                ("skip_flags_u32", DevicePtr)]
+
+
+class LmHeadTop2MarginSpec(C.Structure):
+    _fields_ = [("rows", size_t), ("vocab", size_t), ("eps", C.c_float), ("logits_bf16", DevicePtr),
+                ("tokens_u32", DevicePtr), ("flags_u32", DevicePtr), ("mirror_last_token_u32", DevicePtr),
+                ("fallback_count_u32", DevicePtr), ("workspace", DevicePtr), ("workspace_bytes", size_t)]
+
+
+class LmHeadTop8RescoreSpec(C.Structure):
+    _fields_ = [("rows", size_t), ("vocab", size_t), ("cols", size_t), ("eps", C.c_float), ("logits_bf16", DevicePtr),
+                ("weight_bf16", DevicePtr), ("input_bf16", DevicePtr), ("tokens_u32", DevicePtr),
+                ("flags_u32", DevicePtr), ("mirror_last_token_u32", DevicePtr), ("fallback_count_u32", DevicePtr),
+                ("workspace", DevicePtr), ("workspace_bytes", size_t)]
+
+
 class Nvfp4RetileScalesSpec(C.Structure):
     _fields_ = [("rows", size_t), ("inner_groups", size_t), ("input_row_major_u8", DevicePtr),
                 ("output_tiled_u8", DevicePtr)]

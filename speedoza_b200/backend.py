@@ -171,6 +171,46 @@ class CudaBackend:
         _check("lm_head_fp8_quantize", self.lib.qwen36_lm_head_fp8_quantize(C.byref(spec)))
         return q, s
 
+    # -- exact-argmax guards (crates/runtime/src/engine.rs:10705-10845) ------
+    TOP2_BLOCKS = 240
+
+    def lm_head_top2_margin(self, logits_bf16, eps: float, fallback_count=None, mirror=None):
+        """[rows, vocab] bf16 logits -> (tokens u32 (as int32 tensor), flags)."""
+        rows, vocab = logits_bf16.shape
+        dev = logits_bf16.device
+        tokens = torch.zeros(rows, dtype=torch.int32, device=dev)
+        flags = torch.zeros(rows, dtype=torch.int32, device=dev)
+        ws = torch.empty(rows * self.TOP2_BLOCKS * 16, dtype=torch.uint8, device=dev)
+        spec = abi.LmHeadTop2MarginSpec(rows, vocab, eps, _dp(logits_bf16), _dp(tokens), _dp(flags), _dp(mirror),
+                                        _dp(fallback_count), _dp(ws), ws.numel())
+        _check("lm_head_top2_margin", self.lib.qwen36_lm_head_top2_margin(C.byref(spec)))
+        return tokens, flags
+
+    def lm_head_top8_rescore(self, logits_bf16, weight_bf16, input_bf16, eps: float, fallback_count=None, mirror=None):
+        rows, vocab = logits_bf16.shape
+        cols = weight_bf16.shape[1]
+        dev = logits_bf16.device
+        tokens = torch.zeros(rows, dtype=torch.int32, device=dev)
+        flags = torch.zeros(rows, dtype=torch.int32, device=dev)
+        ws = torch.empty(rows * self.TOP2_BLOCKS * 16, dtype=torch.uint8, device=dev)
+        spec = abi.LmHeadTop8RescoreSpec(rows, vocab, cols, eps, _dp(logits_bf16), _dp(weight_bf16), _dp(input_bf16),
+                                         _dp(tokens), _dp(flags), _dp(mirror), _dp(fallback_count), _dp(ws), ws.numel())
+        _check("lm_head_top8_rescore", self.lib.qwen36_lm_head_top8_rescore(C.byref(spec)))
+        return tokens, flags
+
+    def bf16_matvec_argmax_rows(self, input_bf16, weight_bf16, tokens=None, skip_flags=None, mirror=None):
+        """Rows whose skip flag is zero get argmax_v <x_row, W[v]>; the others keep `tokens`."""
+        rows, in_features = input_bf16.shape
+        out_features = weight_bf16.shape[0]
+        dev = input_bf16.device
+        if tokens is None:
+            tokens = torch.zeros(rows, dtype=torch.int32, device=dev)
+        ws = torch.empty(rows * 8, dtype=torch.uint8, device=dev)
+        spec = abi.Bf16MatvecArgmaxRowsSpec(rows, out_features, in_features, _dp(input_bf16), _dp(weight_bf16),
+                                            _dp(tokens), _dp(mirror), _dp(ws), ws.numel(), _dp(skip_flags))
+        _check("bf16_matvec_argmax_rows", self.lib.qwen36_bf16_matvec_argmax_rows(C.byref(spec)))
+        return tokens
+
     def lm_head_fp8_gemv(self, w_e4m3, row_scales, x_bf16, out=None) -> torch.Tensor:
         rows, cols = w_e4m3.shape
         n = x_bf16.shape[0]

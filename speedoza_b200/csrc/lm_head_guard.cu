@@ -1,0 +1,434 @@
+// Exact-argmax guards of the FP8 lm_head (two-stage greedy decode):
+//   qwen36_lm_head_top2_margin     : per row top-1 token + "top1 - top2 >= eps" verdict over bf16 logits
+//   qwen36_lm_head_top8_rescore    : top-8 block winners rescored against the bf16 weight in float64
+//   qwen36_bf16_matvec_argmax_rows : predicated full bf16 lm_head + argmax for the rows whose guard failed
+// (reference: kernels-cuda/lm_head_fp8.cu:203-494,528-590 and kernels-cuda/ops.cu:19-37,453-515,1104-1153).
+//
+// The verdicts are defined by the reference's arithmetic, which these kernels keep: the 240-block
+// strided partition of the vocabulary whose block winners are the top-8 candidates, float64 lane
+// partials met by a shuffle-down tree for the rescore, float32 lane-strided partials met by the
+// same tree for the bf16 matvec, the (ordered float, 0xffffffff - token) key for its argmax.
+// What changes is how the bytes move: the scan reads 16 bytes per lane, and the bf16 lm_head makes
+// ONE pass over the 2.5 GB weight for all rows that still need it (the reference re-reads the
+// weight once per row), with the activations staged as float32 in shared memory.
+#include "common.cuh"
+
+#include <math.h>
+
+namespace {
+
+using q36::as_ptr;
+
+constexpr uint32_t kBlocks = QWEN36_LM_HEAD_TOP2_BLOCKS;     // vocabulary partition of the scan
+constexpr uint32_t kThreads = 256;
+constexpr uint32_t kNoToken = 0xffffffffu;
+
+struct Top2 {
+  float v1, v2;
+  uint32_t i1;
+};
+struct WsEntry {      // 16 bytes per (row, block): the reference's workspace layout
+  float v1, v2;
+  uint32_t i1, pad;
+};
+
+// Keeps the best value (lowest index among equals) and the second-best value of the multiset.
+__device__ __forceinline__ void consider(Top2 &t, float v, uint32_t i) {
+  if (v > t.v1 || (v == t.v1 && i < t.i1)) {
+    t.v2 = t.v1;
+    t.v1 = v;
+    t.i1 = i;
+  } else if (v > t.v2) {
+    t.v2 = v;
+  }
+}
+__device__ __forceinline__ void merge(Top2 &t, const Top2 &o) {
+  if (o.v1 > t.v1 || (o.v1 == t.v1 && o.i1 < t.i1)) {
+    t.v2 = fmaxf(t.v1, o.v2);
+    t.v1 = o.v1;
+    t.i1 = o.i1;
+  } else {
+    t.v2 = fmaxf(t.v2, o.v1);
+  }
+}
+__device__ __forceinline__ Top2 warp_merge(Top2 mine) {
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    Top2 other;
+    other.v1 = __shfl_down_sync(0xffffffffu, mine.v1, off);
+    other.v2 = __shfl_down_sync(0xffffffffu, mine.v2, off);
+    other.i1 = __shfl_down_sync(0xffffffffu, mine.i1, off);
+    merge(mine, other);
+  }
+  return mine;
+}
+// Result valid in thread 0.
+__device__ __forceinline__ Top2 block_merge(Top2 mine, Top2 *warp_smem) {
+  const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+  mine = warp_merge(mine);
+  if (lane == 0) warp_smem[warp] = mine;
+  __syncthreads();
+  if (warp == 0) {
+    mine = lane < kThreads / 32 ? warp_smem[lane] : Top2{-INFINITY, -INFINITY, kNoToken};
+    mine = warp_merge(mine);
+  }
+  return mine;
+}
+
+// Block b of a row owns the 256-token chunks b, b + 240, b + 480, ... (the reference's thread
+// striding, kernels-cuda/lm_head_fp8.cu:283-301).  Here one warp takes a chunk at a time and a lane
+// reads eight consecutive logits with one 16-byte load.
+__global__ void __launch_bounds__(kThreads)
+top2_scan_kernel(const __nv_bfloat16 *__restrict__ logits, WsEntry *__restrict__ ws, size_t vocab) {
+  __shared__ Top2 warp_smem[kThreads / 32];
+  const size_t row = blockIdx.y;
+  const __nv_bfloat16 *row_logits = logits + row * vocab;
+  const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+  const bool vec = (reinterpret_cast<uintptr_t>(row_logits) & 15u) == 0;
+  Top2 mine{-INFINITY, -INFINITY, kNoToken};
+  for (size_t chunk = blockIdx.x + static_cast<size_t>(warp) * kBlocks; chunk * 256 < vocab;
+       chunk += static_cast<size_t>(kBlocks) * (kThreads / 32)) {
+    const size_t base = chunk * 256 + lane * 8u;
+    if (vec && base + 8 <= vocab) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4 *>(row_logits + base));
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        consider(mine, __uint_as_float(w[i] << 16), static_cast<uint32_t>(base + 2 * i));
+        consider(mine, __uint_as_float(w[i] & 0xffff0000u), static_cast<uint32_t>(base + 2 * i + 1));
+      }
+    } else {
+      for (uint32_t i = 0; i < 8 && base + i < vocab; ++i)
+        consider(mine, __bfloat162float(row_logits[base + i]), static_cast<uint32_t>(base + i));
+    }
+  }
+  mine = block_merge(mine, warp_smem);
+  if (threadIdx.x == 0) ws[row * kBlocks + blockIdx.x] = WsEntry{mine.v1, mine.v2, mine.i1, 0u};
+}
+
+__global__ void __launch_bounds__(kThreads)
+top2_verdict_kernel(const WsEntry *__restrict__ ws, uint32_t *__restrict__ tokens, uint32_t *__restrict__ flags,
+                    uint32_t *__restrict__ mirror_last, uint32_t *__restrict__ fallback_count, size_t rows, float eps) {
+  __shared__ Top2 warp_smem[kThreads / 32];
+  const size_t row = blockIdx.x;
+  Top2 mine{-INFINITY, -INFINITY, kNoToken};
+  for (uint32_t b = threadIdx.x; b < kBlocks; b += kThreads) {
+    const WsEntry e = ws[row * kBlocks + b];
+    merge(mine, Top2{e.v1, e.v2, e.i1});
+  }
+  mine = block_merge(mine, warp_smem);
+  if (threadIdx.x == 0) {
+    const bool ok = (mine.v1 - mine.v2) >= eps;
+    tokens[row] = mine.i1;
+    flags[row] = ok ? 1u : 0u;
+    if (mirror_last != nullptr && row + 1 == rows) *mirror_last = mine.i1;
+    if (!ok && fallback_count != nullptr) atomicAdd(fallback_count, 1u);
+  }
+}
+
+constexpr int kCandidates = 8;
+
+// One CTA per row (kernels-cuda/lm_head_fp8.cu:338-494): the eight best block winners are the
+// candidates, everything else is bounded by B = max(ninth winner, best block runner-up); warp w
+// recomputes candidate w's logit from the bf16 weight in float64; the verdict is
+// best >= B + eps.
+__global__ void __launch_bounds__(kThreads)
+top8_rescore_kernel(const WsEntry *__restrict__ ws, const __nv_bfloat16 *__restrict__ weight,
+                    const __nv_bfloat16 *__restrict__ input, uint32_t *__restrict__ tokens,
+                    uint32_t *__restrict__ flags, uint32_t *__restrict__ mirror_last,
+                    uint32_t *__restrict__ fallback_count, size_t rows, size_t vocab, size_t cols, float eps) {
+  __shared__ float winner_v[kBlocks];
+  __shared__ uint32_t winner_i[kBlocks];
+  __shared__ float warp_max_v2[kThreads / 32];
+  __shared__ uint32_t cand_i[kCandidates];
+  __shared__ float ninth_v;
+  __shared__ double rescored[kCandidates];
+  const size_t row = blockIdx.x;
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+
+  float max_v2 = -INFINITY;
+  for (uint32_t b = threadIdx.x; b < kBlocks; b += kThreads) {
+    const WsEntry e = ws[row * kBlocks + b];
+    winner_v[b] = e.v1;
+    winner_i[b] = e.i1;
+    max_v2 = fmaxf(max_v2, e.v2);
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) max_v2 = fmaxf(max_v2, __shfl_down_sync(0xffffffffu, max_v2, off));
+  if (lane == 0) warp_max_v2[warp] = max_v2;
+  __syncthreads();
+
+  if (warp == 0) {
+    // nine extractions of the maximum (ties toward the smaller token), clearing the slot each time
+    for (int k = 0; k <= kCandidates; ++k) {
+      float best = -INFINITY;
+      uint32_t slot = kNoToken;
+      for (uint32_t b = lane; b < kBlocks; b += 32u) {
+        const float v = winner_v[b];
+        if (v > best || (v == best && slot != kNoToken && winner_i[b] < winner_i[slot])) {
+          best = v;
+          slot = b;
+        }
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) {
+        const float ov = __shfl_down_sync(0xffffffffu, best, off);
+        const uint32_t os = __shfl_down_sync(0xffffffffu, slot, off);
+        if (ov > best || (ov == best && os != kNoToken && (slot == kNoToken || winner_i[os] < winner_i[slot]))) {
+          best = ov;
+          slot = os;
+        }
+      }
+      slot = __shfl_sync(0xffffffffu, slot, 0);
+      best = __shfl_sync(0xffffffffu, best, 0);
+      if (lane == 0) {
+        if (k < kCandidates) {
+          cand_i[k] = slot == kNoToken ? kNoToken : winner_i[slot];
+          if (slot != kNoToken) winner_v[slot] = -INFINITY;
+        } else {
+          ninth_v = best;
+        }
+      }
+      __syncwarp();
+    }
+  }
+  __syncthreads();
+
+  if (warp < kCandidates) {
+    const uint32_t cand = cand_i[warp];
+    double sum = 0.0;
+    if (cand != kNoToken && static_cast<size_t>(cand) < vocab) {
+      const __nv_bfloat16 *w_row = weight + static_cast<size_t>(cand) * cols;
+      const __nv_bfloat16 *x_row = input + row * cols;
+      for (size_t c = lane; c < cols; c += 32u)
+        sum += static_cast<double>(__bfloat162float(w_row[c])) * static_cast<double>(__bfloat162float(x_row[c]));
+    } else {
+      sum = -INFINITY;
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) sum += __shfl_down_sync(0xffffffffu, sum, off);
+    if (lane == 0) rescored[warp] = cand == kNoToken ? -INFINITY : sum;
+  }
+  __syncthreads();
+
+  if (threadIdx.x == 0) {
+    double best = -INFINITY;
+    uint32_t best_token = 0;
+    for (int k = 0; k < kCandidates; ++k) {
+      const double v = rescored[k];
+      const uint32_t tok = cand_i[k];
+      if (tok != kNoToken && (v > best || (v == best && tok < best_token))) {
+        best = v;
+        best_token = tok;
+      }
+    }
+    float bound = ninth_v;
+    for (uint32_t w = 0; w < kThreads / 32; ++w) bound = fmaxf(bound, warp_max_v2[w]);
+    const bool ok = best >= static_cast<double>(bound) + static_cast<double>(eps);
+    tokens[row] = best_token;
+    flags[row] = ok ? 1u : 0u;
+    if (mirror_last != nullptr && row + 1 == rows) *mirror_last = best_token;
+    if (!ok && fallback_count != nullptr) atomicAdd(fallback_count, 1u);
+  }
+}
+
+// ---- predicated bf16 lm_head + argmax -------------------------------------------------------
+
+constexpr int kMaxActive = 8;          // rows handled per pass over the weight
+constexpr int kVocabPerWarp = 4;       // vocabulary rows a warp carries at once
+
+__device__ __forceinline__ unsigned long long argmax_key(float score, uint32_t token) {
+  if (!isfinite(score)) return 0ull;
+  const uint32_t bits = __float_as_uint(score);
+  const uint32_t ordered = (bits & 0x80000000u) != 0u ? ~bits : (bits ^ 0x80000000u);
+  return (static_cast<unsigned long long>(ordered) << 32) | (0xffffffffu - token);
+}
+
+// One pass over the weight for up to N rows that still need the bf16 answer.  Lane l accumulates
+// columns l, l + 32, ... in float32 in that order and the lanes meet in a shuffle-down tree: the
+// logit of every (row, token) pair has the reference's bits (kernels-cuda/ops.cu:474-487).
+template <int N>
+__global__ void __launch_bounds__(kThreads)
+bf16_argmax_kernel(const __nv_bfloat16 *__restrict__ input, const __nv_bfloat16 *__restrict__ weight,
+                   unsigned long long *__restrict__ best_keys, const uint32_t *__restrict__ skip_flags,
+                   size_t rows, size_t row_base, size_t out_features, uint32_t in_features) {
+  extern __shared__ __align__(16) float xs[];                // [N][in_features]
+  __shared__ int active_row[N];
+  __shared__ int n_active;
+  if (threadIdx.x == 0) {
+    int n = 0;
+    for (size_t r = row_base; r < rows && n < N; ++r)
+      if (skip_flags == nullptr || skip_flags[r] == 0u) active_row[n++] = static_cast<int>(r - row_base);
+    // rows beyond the N-th active one belong to the next pass: they are found again from row_base + last + 1
+    n_active = n;
+  }
+  __syncthreads();
+  const int n_act = n_active;
+  if (n_act == 0) return;
+  for (int t = 0; t < n_act; ++t) {
+    const __nv_bfloat16 *x_row = input + (row_base + active_row[t]) * in_features;
+    for (uint32_t c = threadIdx.x; c < in_features; c += kThreads) xs[t * in_features + c] = __bfloat162float(x_row[c]);
+  }
+  __syncthreads();
+
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+  const size_t warps_total = static_cast<size_t>(gridDim.x) * (kThreads / 32);
+  unsigned long long best[N];
+#pragma unroll
+  for (int t = 0; t < N; ++t) best[t] = 0ull;
+
+  for (size_t v0 = (static_cast<size_t>(blockIdx.x) * (kThreads / 32) + warp) * kVocabPerWarp; v0 < out_features;
+       v0 += warps_total * kVocabPerWarp) {
+    float acc[kVocabPerWarp][N];
+#pragma unroll
+    for (int r = 0; r < kVocabPerWarp; ++r)
+#pragma unroll
+      for (int t = 0; t < N; ++t) acc[r][t] = 0.f;
+    const unsigned short *w0 = reinterpret_cast<const unsigned short *>(weight) + v0 * in_features;
+#pragma unroll 4
+    for (uint32_t col = lane; col < in_features; col += 32u) {
+      float w[kVocabPerWarp];
+#pragma unroll
+      for (int r = 0; r < kVocabPerWarp; ++r)
+        w[r] = v0 + r < out_features
+                   ? __uint_as_float(static_cast<uint32_t>(__ldcs(w0 + static_cast<size_t>(r) * in_features + col)) << 16)
+                   : 0.f;
+#pragma unroll
+      for (int t = 0; t < N; ++t) {
+        const float x = xs[t * in_features + col];
+#pragma unroll
+        for (int r = 0; r < kVocabPerWarp; ++r) acc[r][t] = fmaf(x, w[r], acc[r][t]);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < kVocabPerWarp; ++r) {
+      if (v0 + r >= out_features) break;
+#pragma unroll
+      for (int t = 0; t < N; ++t) {
+        float s = acc[r][t];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) s += __shfl_down_sync(0xffffffffu, s, off);
+        const unsigned long long key = argmax_key(s, static_cast<uint32_t>(v0 + r));
+        if (key > best[t]) best[t] = key;
+      }
+    }
+  }
+  if (lane == 0) {
+#pragma unroll
+    for (int t = 0; t < N; ++t)
+      if (t < n_act && best[t] != 0ull) atomicMax(best_keys + row_base + active_row[t], best[t]);
+  }
+}
+
+__global__ void bf16_argmax_finalize_kernel(const unsigned long long *__restrict__ best_keys,
+                                            uint32_t *__restrict__ tokens, uint32_t *__restrict__ mirror_last,
+                                            const uint32_t *__restrict__ skip_flags, size_t rows) {
+  const size_t row = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (row >= rows) return;
+  if (skip_flags != nullptr && skip_flags[row] != 0u) return;      // the stage-1 token stands
+  const unsigned long long key = best_keys[row];
+  const uint32_t token = key == 0ull ? 0u : 0xffffffffu - static_cast<uint32_t>(key & 0xffffffffull);
+  tokens[row] = token;
+  if (mirror_last != nullptr && row + 1 == rows) *mirror_last = token;
+}
+
+int sm_count() {
+  static int n = [] {
+    int dev = 0, v = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0)
+      return 148;
+    return v;
+  }();
+  return n;
+}
+
+template <int N>
+int launch_bf16_argmax(const qwen36_bf16_matvec_argmax_rows_spec_t *s, size_t row_base) {
+  const size_t smem = static_cast<size_t>(N) * s->in_features * sizeof(float);
+  static cudaError_t attr_err = cudaFuncSetAttribute(bf16_argmax_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                     200 * 1024);
+  if (attr_err != cudaSuccess) return QWEN36_STATUS_CUDA_ERROR;
+  const size_t need = q36::div_ceil(s->out_features, static_cast<size_t>(kThreads / 32) * kVocabPerWarp);
+  const size_t per_sm = smem > 100 * 1024 ? 1 : (smem > 48 * 1024 ? 2 : 4);
+  const size_t cap = static_cast<size_t>(sm_count()) * per_sm;
+  bf16_argmax_kernel<N><<<static_cast<unsigned>(need < cap ? need : cap), kThreads, smem, q36::stream()>>>(
+      as_ptr<const __nv_bfloat16>(s->input_bf16), as_ptr<const __nv_bfloat16>(s->weight_bf16),
+      as_ptr<unsigned long long>(s->workspace), as_ptr<const uint32_t>(s->skip_flags_u32), s->rows, row_base,
+      s->out_features, static_cast<uint32_t>(s->in_features));
+  return q36::launch_status();
+}
+
+bool guard_args_ok(size_t rows, size_t vocab, uint64_t logits, uint64_t tokens, uint64_t flags, uint64_t ws,
+                   size_t ws_bytes) {
+  return rows != 0 && vocab != 0 && logits != 0 && tokens != 0 && flags != 0 && ws != 0 &&
+         ws_bytes >= rows * kBlocks * sizeof(WsEntry) && rows <= 65535 && vocab <= 0xffffffffull;
+}
+
+}  // namespace
+
+extern "C" int qwen36_lm_head_top2_margin(const qwen36_lm_head_top2_margin_spec_t *spec) {
+  if (spec == nullptr || !guard_args_ok(spec->rows, spec->vocab, spec->logits_bf16.ptr, spec->tokens_u32.ptr,
+                                        spec->flags_u32.ptr, spec->workspace.ptr, spec->workspace_bytes))
+    return QWEN36_STATUS_INVALID_ARGUMENT;                  // also for a null spec, as the reference does
+  top2_scan_kernel<<<dim3(kBlocks, static_cast<unsigned>(spec->rows)), kThreads, 0, q36::stream()>>>(
+      as_ptr<const __nv_bfloat16>(spec->logits_bf16), as_ptr<WsEntry>(spec->workspace), spec->vocab);
+  top2_verdict_kernel<<<static_cast<unsigned>(spec->rows), kThreads, 0, q36::stream()>>>(
+      as_ptr<const WsEntry>(spec->workspace), as_ptr<uint32_t>(spec->tokens_u32), as_ptr<uint32_t>(spec->flags_u32),
+      as_ptr<uint32_t>(spec->mirror_last_token_u32), as_ptr<uint32_t>(spec->fallback_count_u32), spec->rows, spec->eps);
+  return q36::launch_status();
+}
+
+extern "C" int qwen36_lm_head_top8_rescore(const qwen36_lm_head_top8_rescore_spec_t *spec) {
+  if (spec == nullptr || spec->cols == 0 || spec->weight_bf16.ptr == 0 || spec->input_bf16.ptr == 0 ||
+      !guard_args_ok(spec->rows, spec->vocab, spec->logits_bf16.ptr, spec->tokens_u32.ptr, spec->flags_u32.ptr,
+                     spec->workspace.ptr, spec->workspace_bytes))
+    return QWEN36_STATUS_INVALID_ARGUMENT;
+  top2_scan_kernel<<<dim3(kBlocks, static_cast<unsigned>(spec->rows)), kThreads, 0, q36::stream()>>>(
+      as_ptr<const __nv_bfloat16>(spec->logits_bf16), as_ptr<WsEntry>(spec->workspace), spec->vocab);
+  top8_rescore_kernel<<<static_cast<unsigned>(spec->rows), kThreads, 0, q36::stream()>>>(
+      as_ptr<const WsEntry>(spec->workspace), as_ptr<const __nv_bfloat16>(spec->weight_bf16),
+      as_ptr<const __nv_bfloat16>(spec->input_bf16), as_ptr<uint32_t>(spec->tokens_u32),
+      as_ptr<uint32_t>(spec->flags_u32), as_ptr<uint32_t>(spec->mirror_last_token_u32),
+      as_ptr<uint32_t>(spec->fallback_count_u32), spec->rows, spec->vocab, spec->cols, spec->eps);
+  return q36::launch_status();
+}
+
+extern "C" int qwen36_bf16_matvec_argmax_rows(const qwen36_bf16_matvec_argmax_rows_spec_t *spec) {
+  if (spec == nullptr) return QWEN36_STATUS_NULL_POINTER;
+  if (spec->rows == 0 || spec->out_features == 0 || spec->in_features == 0 || spec->input_bf16.ptr == 0 ||
+      spec->weight_bf16.ptr == 0 || spec->output_token_u32.ptr == 0 || spec->workspace.ptr == 0 ||
+      spec->workspace_bytes < spec->rows * sizeof(unsigned long long) || spec->out_features > 0xffffffffull ||
+      spec->in_features * sizeof(float) > 200 * 1024)
+    return QWEN36_STATUS_INVALID_ARGUMENT;
+  if (cudaMemsetAsync(as_ptr<void>(spec->workspace), 0, spec->rows * sizeof(unsigned long long), q36::stream()) !=
+      cudaSuccess)
+    return QWEN36_STATUS_CUDA_ERROR;
+  // Rows per pass: as many as the float32 staging of their activations allows (at most eight).
+  // Every pass skips flagged rows itself, so a pass over rows that are all flagged reads nothing.
+  size_t per_pass = (200 * 1024) / (spec->in_features * sizeof(float));
+  if (per_pass > kMaxActive) per_pass = kMaxActive;
+  if (per_pass > spec->rows) per_pass = spec->rows;
+  for (size_t base = 0; base < spec->rows; base += per_pass) {
+    // the window [base, base + per_pass) holds at most per_pass active rows
+    qwen36_bf16_matvec_argmax_rows_spec_t window = *spec;
+    window.rows = base + per_pass < spec->rows ? base + per_pass : spec->rows;
+    int rc;
+    switch (per_pass) {
+      case 1: rc = launch_bf16_argmax<1>(&window, base); break;
+      case 2: rc = launch_bf16_argmax<2>(&window, base); break;
+      case 3: rc = launch_bf16_argmax<3>(&window, base); break;
+      case 4: rc = launch_bf16_argmax<4>(&window, base); break;
+      case 5: rc = launch_bf16_argmax<5>(&window, base); break;
+      case 6: rc = launch_bf16_argmax<6>(&window, base); break;
+      case 7: rc = launch_bf16_argmax<7>(&window, base); break;
+      default: rc = launch_bf16_argmax<8>(&window, base); break;
+    }
+    if (rc != QWEN36_STATUS_SUCCESS) return rc;
+  }
+  const unsigned blocks = static_cast<unsigned>(q36::div_ceil(spec->rows, static_cast<size_t>(128)));
+  bf16_argmax_finalize_kernel<<<blocks, 128, 0, q36::stream()>>>(
+      as_ptr<const unsigned long long>(spec->workspace), as_ptr<uint32_t>(spec->output_token_u32),
+      as_ptr<uint32_t>(spec->mirror_last_output_token_u32), as_ptr<const uint32_t>(spec->skip_flags_u32), spec->rows);
+  return q36::launch_status();
+}

@@ -9,7 +9,6 @@
 
 Q36_STUB(qwen36_bf16_gemm)
 Q36_STUB(qwen36_bf16_matvec)
-Q36_STUB(qwen36_bf16_matvec_argmax_rows)
 Q36_STUB(qwen36_attention_prefill)
 Q36_STUB(qwen36_attention_flash_prefill)
 Q36_STUB(qwen36_attention_sage_prefill)
@@ -24,8 +23,6 @@ Q36_STUB(qwen36_partial_rope)
 Q36_STUB(qwen36_swiglu)
 Q36_STUB(qwen36_topk_argmax)
 Q36_STUB(qwen36_embedding_lookup)
-Q36_STUB(qwen36_lm_head_top2_margin)
-Q36_STUB(qwen36_lm_head_top8_rescore)
 Q36_STUB(qwen36_conv1d_update)
 Q36_STUB(qwen36_conv1d_prefill)
 Q36_STUB(qwen36_gdn_gate)

@@ -73,6 +73,15 @@ def test_struct_layouts_equal_reference_header(tmp_path):
         "qwen36_swiglu_nvfp4_quantize_spec_t": ["intermediate", "gate_bf16", "up_bf16", "output_fp4",
                                                 "output_scale_e4m3", "output_tensor_scale_f32",
                                                 "input_tensor_scale_f32"],
+        "qwen36_bf16_matvec_argmax_rows_spec_t": ["rows", "out_features", "in_features", "input_bf16", "weight_bf16",
+                                                  "output_token_u32", "mirror_last_output_token_u32", "workspace",
+                                                  "workspace_bytes", "skip_flags_u32"],
+        "qwen36_lm_head_top2_margin_spec_t": ["rows", "vocab", "eps", "logits_bf16", "tokens_u32", "flags_u32",
+                                              "mirror_last_token_u32", "fallback_count_u32", "workspace",
+                                              "workspace_bytes"],
+        "qwen36_lm_head_top8_rescore_spec_t": ["rows", "vocab", "cols", "eps", "logits_bf16", "weight_bf16",
+                                               "input_bf16", "tokens_u32", "flags_u32", "mirror_last_token_u32",
+                                               "fallback_count_u32", "workspace", "workspace_bytes"],
         "qwen36_lm_head_fp8_quantize_spec_t": ["rows", "cols", "weight_bf16", "weight_e4m3", "row_scales_f32"],
         "qwen36_lm_head_fp8_gemv_spec_t": ["rows", "cols", "n", "weight_e4m3", "row_scales_f32", "input_bf16",
                                            "output_bf16"],
@@ -113,6 +122,9 @@ def test_ctypes_mirrors_match_header_sizes(tmp_path):
     names = {"qwen36_nvfp4_gemm_spec_t": abi.Nvfp4GemmSpec, "qwen36_nvfp4_matvec_spec_t": abi.Nvfp4MatvecSpec,
              "qwen36_nvfp4_quantize_rows_spec_t": abi.Nvfp4QuantizeRowsSpec,
              "qwen36_rmsnorm_nvfp4_quantize_spec_t": abi.RmsnormNvfp4QuantizeSpec,
+             "qwen36_bf16_matvec_argmax_rows_spec_t": abi.Bf16MatvecArgmaxRowsSpec,
+             "qwen36_lm_head_top2_margin_spec_t": abi.LmHeadTop2MarginSpec,
+             "qwen36_lm_head_top8_rescore_spec_t": abi.LmHeadTop8RescoreSpec,
              "qwen36_swiglu_nvfp4_quantize_spec_t": abi.SwigluNvfp4QuantizeSpec,
              "qwen36_lm_head_fp8_argmax_spec_t": abi.LmHeadFp8ArgmaxSpec,
              "qwen36_lm_head_fp8_gemv_spec_t": abi.LmHeadFp8GemvSpec,

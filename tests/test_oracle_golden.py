@@ -251,3 +251,59 @@ def test_fused_producers_known_answers():
     s1 = orc.swiglu_nvfp4_quantize(g, up, 0.0)
     want_fp4, want_sf, _ = orc.nvfp4_quantize_rows(synth.f32_to_bf16_bits(40.0 * np.arange(32, dtype=np.float32))[None, :], 0.0)
     assert np.array_equal(s1["fp4"], want_fp4[0]) and np.array_equal(s1["sf"], want_sf)
+
+
+def planted_logits():
+    """The reference's own known-answer construction (kernels-cuda/smoke.cu:202-219): a pattern that
+    depends only on the indices, with two planted leaders per row.  Row 0 margin 2.0, row 1 margin 0.25."""
+    rows, vocab = 2, 250000
+    i = np.arange(vocab, dtype=np.int64)
+    logits = np.stack([-2.0 + ((r * 911 + i * 37) % 997).astype(np.float32) / 1000.0 for r in range(rows)]).astype(np.float32)
+    logits[0, 123456] = 7.0
+    logits[0, 7] = 5.0
+    logits[1, 99] = 3.25
+    logits[1, vocab - 1] = 3.0
+    return synth.f32_to_bf16_bits(logits)
+
+
+def test_top2_margin_known_answers():
+    # kernels-cuda/smoke.cu:237-262
+    logits = planted_logits()
+    tokens, flags, fb = orc.lm_head_top2_margin(logits, 1.0)
+    assert tokens.tolist() == [123456, 99] and flags.tolist() == [1, 0] and fb == 1
+    tokens, flags, fb = orc.lm_head_top2_margin(logits, 0.1)
+    assert tokens.tolist() == [123456, 99] and flags.tolist() == [1, 1] and fb == 0
+    # a tie for first place: lowest index wins, margin 0 fails any positive eps; NaN never wins
+    small = synth.f32_to_bf16_bits(np.array([[1.0, 5.0, np.nan, 5.0, -1.0]], np.float32))
+    tokens, flags, fb = orc.lm_head_top2_margin(small, 0.5)
+    assert tokens.tolist() == [1] and flags.tolist() == [0] and fb == 1
+    tokens, flags, _ = orc.lm_head_top2_margin(small, 0.0)
+    assert flags.tolist() == [1]
+
+
+def test_top8_rescore_and_bf16_argmax_small():
+    """Float64 rescore of the eight best block winners picks the bf16-exact leader even when the
+    (perturbed) first-stage logits rank another token first; the bf16 matvec argmax agrees with a
+    float64 dot product wherever the top two are clearly apart, and honours skip flags."""
+    rng = np.random.default_rng(3)
+    vocab, cols, rows = 3000, 256, 3
+    w = synth.f32_to_bf16_bits(rng.standard_normal((vocab, cols)).astype(np.float32))
+    x = synth.f32_to_bf16_bits(rng.standard_normal((rows, cols)).astype(np.float32))
+    exact = synth.bf16_bits_to_f32(x).astype(np.float64) @ synth.bf16_bits_to_f32(w).astype(np.float64).T
+    noisy = exact + rng.standard_normal(exact.shape) * 0.3          # stands in for the FP8 logits
+    logits = synth.f32_to_bf16_bits(noisy.astype(np.float32))
+    tokens, flags, fb = orc.lm_head_top8_rescore(logits, w, x, 0.5)
+    order = np.argsort(-exact, axis=1)
+    for r in range(rows):
+        # the rescored winner is the best exact logit among the eight candidates; when the guard
+        # certifies the row it is the global bf16 argmax
+        if flags[r]:
+            assert tokens[r] == order[r, 0]
+    assert fb == int((flags == 0).sum())
+    full = orc.bf16_matvec_argmax_rows(x, w)
+    for r in range(rows):
+        if exact[r, order[r, 0]] - exact[r, order[r, 1]] > 1e-3:
+            assert full[r] == order[r, 0]
+    skip = np.array([0, 1, 0], dtype=np.uint32)
+    kept = orc.bf16_matvec_argmax_rows(x, w, skip, np.array([11, 22, 33], dtype=np.uint32))
+    assert kept[1] == 22 and kept[0] == full[0] and kept[2] == full[2]
