@@ -357,7 +357,8 @@ def other_configs(backend, torch, synth):
     gt = (torch.randn(inter, generator=gen, device="cuda") * 2).to(torch.bfloat16)
     up = torch.randn(inter, generator=gen, device="cuda").to(torch.bfloat16)
     sw = backend.swiglu_nvfp4_quantize(gt, up, 0.37)
-    norm_us = _time_cuda(torch, lambda i: backend.rmsnorm_nvfp4_quantize(xn, wn, rn, 1e-6, 0.37, True, True), 50,
+    nb = backend.rmsnorm_nvfp4_quantize(xn, wn, rn, 1e-6, 0.37, True, True)
+    norm_us = _time_cuda(torch, lambda i: backend.rmsnorm_nvfp4_quantize(xn, wn, rn, 1e-6, 0.37, True, True, nb), 50,
                          backend=backend)
     swiglu_us = _time_cuda(torch, lambda i: backend.swiglu_nvfp4_quantize(gt, up, 0.37, *sw), 50, backend=backend)
     out["fused_producers"] = {"rmsnorm_nvfp4_quantize_us": round(norm_us, 2), "hidden": hid,

@@ -86,16 +86,21 @@ class CudaBackend:
         return out_fp4, out_sf, out_ts
 
     def rmsnorm_nvfp4_quantize(self, x_bf16, weight_bf16, residual_bf16=None, eps: float = 1e-6,
-                               input_tensor_scale: float = 0.0, want_bf16: bool = True, want_residual_out: bool = False):
+                               input_tensor_scale: float = 0.0, want_bf16: bool = True, want_residual_out: bool = False,
+                               buffers=None):
         """One vector (crates/kernels/src/backend.rs `rmsnorm_nvfp4_quantize`).
-        -> (out_bf16 | None, residual_out | None, fp4, tiled scales, tensor scale [1])."""
+        -> (out_bf16 | None, residual_out | None, fp4, tiled scales, tensor scale [1]);
+        `buffers` = a previous result to write into instead of allocating."""
         hidden = x_bf16.numel()
         dev = x_bf16.device
-        out = torch.empty(hidden, dtype=torch.bfloat16, device=dev) if want_bf16 else None
-        res_out = torch.empty(hidden, dtype=torch.bfloat16, device=dev) if want_residual_out else None
-        fp4 = torch.empty((hidden + 1) // 2, dtype=torch.uint8, device=dev)
-        sf = torch.zeros(tiled_scale_bytes(1, (hidden + 15) // 16), dtype=torch.uint8, device=dev)
-        ts = torch.empty(1, dtype=torch.float32, device=dev)
+        if buffers is not None:
+            out, res_out, fp4, sf, ts = buffers
+        else:
+            out = torch.empty(hidden, dtype=torch.bfloat16, device=dev) if want_bf16 else None
+            res_out = torch.empty(hidden, dtype=torch.bfloat16, device=dev) if want_residual_out else None
+            fp4 = torch.empty((hidden + 1) // 2, dtype=torch.uint8, device=dev)
+            sf = torch.zeros(tiled_scale_bytes(1, (hidden + 15) // 16), dtype=torch.uint8, device=dev)
+            ts = torch.empty(1, dtype=torch.float32, device=dev)
         spec = abi.RmsnormNvfp4QuantizeSpec(hidden, eps, _dp(x_bf16), _dp(weight_bf16), _dp(residual_bf16),
                                             _dp(res_out), _dp(out), _dp(fp4), _dp(sf), _dp(ts), input_tensor_scale)
         _check("rmsnorm_nvfp4_quantize", self.lib.qwen36_rmsnorm_nvfp4_quantize(C.byref(spec)))

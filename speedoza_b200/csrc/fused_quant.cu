@@ -10,8 +10,9 @@
 // halving tree, the normaliser is rsqrtf, silu divides by 1 + expf(-g), the group scale and the
 // codes use the shared NVFP4 codec.  What changes is the shape of the launch: the reference walks
 // whole 16-value groups with one thread each (two passes of 256 threads for hidden = 5120, sixteen
-// serial IEEE divisions per thread); here two lanes share a group in the norm kernel and sixteen
-// lanes share one in the SwiGLU kernel, 256 threads per CTA instead of 32.
+// serial IEEE divisions per thread); here the vector is fetched once, by 1024 threads in one round
+// trip, into shared memory as float32, two lanes share a group in the norm kernel and sixteen lanes
+// share one in the SwiGLU kernel, 256 threads per CTA instead of 32.
 #include "common.cuh"
 
 namespace {
@@ -32,36 +33,59 @@ rmsnorm_nvfp4_quantize_kernel(const __nv_bfloat16 *__restrict__ input, const __n
                               uint8_t *__restrict__ output_scale, float *__restrict__ tensor_scale, size_t hidden,
                               float eps, float input_tensor_scale) {
   __shared__ float scratch[kNormSumThreads];
+  __shared__ float total;
+  extern __shared__ __align__(16) float value[];            // input (+ residual) as float32, read three times below
+  // ---- one round trip to L2: every thread fetches its elements at once -------------------------
+  constexpr int kBatch = 8;                                  // 8192 elements per pass: loads issued before any use
+  for (size_t base = 0; base < hidden; base += static_cast<size_t>(kBatch) * kNormThreads) {
+    __nv_bfloat16 in_raw[kBatch], res_raw[kBatch];
+#pragma unroll
+    for (int i = 0; i < kBatch; ++i) {
+      const size_t d = base + threadIdx.x + static_cast<size_t>(i) * kNormThreads;
+      in_raw[i] = d < hidden ? input[d] : __float2bfloat16(0.0f);
+      res_raw[i] = (d < hidden && residual != nullptr) ? residual[d] : __float2bfloat16(0.0f);
+    }
+#pragma unroll
+    for (int i = 0; i < kBatch; ++i) {
+      const size_t d = base + threadIdx.x + static_cast<size_t>(i) * kNormThreads;
+      if (d < hidden) {
+        float v = __bfloat162float(in_raw[i]);
+        if (residual != nullptr) v += __bfloat162float(res_raw[i]);
+        value[d] = v;
+        if (residual_out != nullptr) residual_out[d] = __float2bfloat16(v);
+      }
+    }
+  }
+  __syncthreads();
   // ---- sum of squares: thread t < 256 adds pairs t, t + 256, ... in that order ----------------
   if (threadIdx.x < kNormSumThreads) {
     float local_sum = 0.0f;
     const size_t pairs = hidden / 2;
-    const __nv_bfloat162 *input2 = reinterpret_cast<const __nv_bfloat162 *>(input);
-    const __nv_bfloat162 *residual2 = reinterpret_cast<const __nv_bfloat162 *>(residual);
     for (size_t p = threadIdx.x; p < pairs; p += kNormSumThreads) {
-      const __nv_bfloat162 vp = input2[p];
-      float a = __low2float(vp);
-      float b = __high2float(vp);
-      if (residual2 != nullptr) {
-        const __nv_bfloat162 rp = residual2[p];
-        a += __low2float(rp);
-        b += __high2float(rp);
-      }
+      const float a = value[2 * p], b = value[2 * p + 1];
       local_sum += a * a + b * b;
     }
     if ((hidden & 1u) != 0u && threadIdx.x == 0u) {
-      float value = __bfloat162float(input[hidden - 1]);
-      if (residual != nullptr) value += __bfloat162float(residual[hidden - 1]);
-      local_sum += value * value;
+      const float v = value[hidden - 1];
+      local_sum += v * v;
     }
     scratch[threadIdx.x] = local_sum;
   }
   __syncthreads();
-  for (unsigned int stride = kNormSumThreads / 2; stride > 0; stride >>= 1) {
-    if (threadIdx.x < stride) scratch[threadIdx.x] += scratch[threadIdx.x + stride];
-    __syncthreads();
+  // The reference's halving tree over the 256 partials (s[t] += s[t + stride], stride = 128 ... 1),
+  // same pairings in the same order, evaluated by one warp without block barriers: strides 128, 64
+  // and 32 from shared memory, 16 ... 1 as shuffles.
+  if (threadIdx.x < 32) {
+    const uint32_t t = threadIdx.x;
+    const float lo = (scratch[t] + scratch[t + 128]) + (scratch[t + 64] + scratch[t + 192]);
+    const float hi = (scratch[t + 32] + scratch[t + 160]) + (scratch[t + 96] + scratch[t + 224]);
+    float s32 = lo + hi;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) s32 += __shfl_down_sync(0xffffffffu, s32, off);
+    if (t == 0) total = s32;
   }
-  const float norm_scale = rsqrtf(scratch[0] / static_cast<float>(hidden) + eps);
+  __syncthreads();
+  const float norm_scale = rsqrtf(total / static_cast<float>(hidden) + eps);
   const size_t groups = q36::div_ceil(hidden, 16);
   const size_t sf_inner = q36::round_up(groups, 4);
   const float global_scale = input_tensor_scale > 0.0f ? input_tensor_scale : 1.0f;
@@ -79,12 +103,9 @@ rmsnorm_nvfp4_quantize_kernel(const __nv_bfloat16 *__restrict__ input, const __n
       const size_t d = start + i;
       weighted[i] = 0.0f;
       if (live && d < hidden) {
-        float value = __bfloat162float(input[d]);
-        if (residual != nullptr) value += __bfloat162float(residual[d]);
-        const float w = value * norm_scale * (1.0f + __bfloat162float(weight[d]));
+        const float w = value[d] * norm_scale * (1.0f + __bfloat162float(weight[d]));
         weighted[i] = w;
         if (output_bf16 != nullptr) output_bf16[d] = __float2bfloat16(w);
-        if (residual_out != nullptr) residual_out[d] = __float2bfloat16(value);
         amax = fmaxf(amax, fabsf(w));
       }
     }
@@ -146,7 +167,12 @@ extern "C" int qwen36_rmsnorm_nvfp4_quantize(const qwen36_rmsnorm_nvfp4_quantize
       spec->output_scale_e4m3.ptr == 0)
     return QWEN36_STATUS_INVALID_ARGUMENT;
   const float eps = spec->eps == 0.0f ? 1.0e-6f : spec->eps;
-  rmsnorm_nvfp4_quantize_kernel<<<1, kNormThreads, 0, q36::stream()>>>(
+  const size_t smem = spec->hidden * sizeof(float);
+  if (smem > 200 * 1024) return QWEN36_STATUS_INVALID_ARGUMENT;
+  static cudaError_t attr_err = cudaFuncSetAttribute(rmsnorm_nvfp4_quantize_kernel,
+                                                     cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+  if (attr_err != cudaSuccess) return QWEN36_STATUS_CUDA_ERROR;
+  rmsnorm_nvfp4_quantize_kernel<<<1, kNormThreads, smem, q36::stream()>>>(
       as_ptr<const __nv_bfloat16>(spec->input_bf16), as_ptr<const __nv_bfloat16>(spec->weight_bf16),
       as_ptr<const __nv_bfloat16>(spec->residual_bf16), as_ptr<__nv_bfloat16>(spec->residual_out_bf16),
       as_ptr<__nv_bfloat16>(spec->output_bf16), as_ptr<uint8_t>(spec->output_fp4),

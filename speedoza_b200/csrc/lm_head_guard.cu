@@ -235,7 +235,7 @@ top8_rescore_kernel(const WsEntry *__restrict__ ws, const __nv_bfloat16 *__restr
 // ---- predicated bf16 lm_head + argmax -------------------------------------------------------
 
 constexpr int kMaxActive = 8;          // rows handled per pass over the weight
-constexpr int kVocabPerWarp = 4;       // vocabulary rows a warp carries at once
+constexpr int kVocabPerWarp = 8;       // vocabulary rows a warp carries at once (2-byte loads: many in flight)
 
 __device__ __forceinline__ unsigned long long argmax_key(float score, uint32_t token) {
   if (!isfinite(score)) return 0ull;
@@ -285,20 +285,41 @@ bf16_argmax_kernel(const __nv_bfloat16 *__restrict__ input, const __nv_bfloat16 
 #pragma unroll
       for (int t = 0; t < N; ++t) acc[r][t] = 0.f;
     const unsigned short *w0 = reinterpret_cast<const unsigned short *>(weight) + v0 * in_features;
-#pragma unroll 4
-    for (uint32_t col = lane; col < in_features; col += 32u) {
-      float w[kVocabPerWarp];
+    // Column steps of 32 (lane l owns column l of each step), software-pipelined kSteps at a time:
+    // the 2-byte loads of the next batch are in flight while the current one is multiplied.
+    constexpr int kSteps = 4;
+    const uint32_t steps = (in_features + 31u) / 32u;
+    unsigned short cur[kSteps][kVocabPerWarp], nxt[kSteps][kVocabPerWarp];
+    auto load_batch = [&](unsigned short (&dst)[kSteps][kVocabPerWarp], uint32_t s0) {
 #pragma unroll
-      for (int r = 0; r < kVocabPerWarp; ++r)
-        w[r] = v0 + r < out_features
-                   ? __uint_as_float(static_cast<uint32_t>(__ldcs(w0 + static_cast<size_t>(r) * in_features + col)) << 16)
-                   : 0.f;
+      for (int u = 0; u < kSteps; ++u) {
+        const uint32_t col = (s0 + u) * 32u + lane;
 #pragma unroll
-      for (int t = 0; t < N; ++t) {
-        const float x = xs[t * in_features + col];
-#pragma unroll
-        for (int r = 0; r < kVocabPerWarp; ++r) acc[r][t] = fmaf(x, w[r], acc[r][t]);
+        for (int r = 0; r < kVocabPerWarp; ++r)
+          dst[u][r] = (col < in_features && v0 + r < out_features)
+                          ? __ldcs(w0 + static_cast<size_t>(r) * in_features + col) : static_cast<unsigned short>(0);
       }
+    };
+    load_batch(cur, 0);
+    for (uint32_t s0 = 0; s0 < steps; s0 += kSteps) {
+      if (s0 + kSteps < steps) load_batch(nxt, s0 + kSteps);
+#pragma unroll
+      for (int u = 0; u < kSteps; ++u) {
+        const uint32_t col = (s0 + u) * 32u + lane;
+        if (col < in_features) {                            // no padding terms: the sums keep the reference's bits
+#pragma unroll
+          for (int t = 0; t < N; ++t) {
+            const float x = xs[t * in_features + col];
+#pragma unroll
+            for (int r = 0; r < kVocabPerWarp; ++r)
+              acc[r][t] = fmaf(x, __uint_as_float(static_cast<uint32_t>(cur[u][r]) << 16), acc[r][t]);
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kSteps; ++u)
+#pragma unroll
+        for (int r = 0; r < kVocabPerWarp; ++r) cur[u][r] = nxt[u][r];
     }
 #pragma unroll
     for (int r = 0; r < kVocabPerWarp; ++r) {
