@@ -427,7 +427,7 @@ def other_configs(backend, torch, synth):
 def profile_case(name: str):
     """Runs one small, fixed case of a single kernel a few times (for `ncu -k ... -c ...`):
     gemv_gate_up | gemv_down | gemm_gate_up_2048 | gemm_down_2048 | lm_head_m1 | lm_head_m4 |
-    attention_32768 | quantize_2048.  Inputs exceed L2 but stay well under a few GB."""
+    attention_32768 | quantize_2048 | bf16_argmax_m1 | bf16_argmax_m4.  Inputs exceed L2 but stay well under a few GB."""
     import torch
     from speedoza_b200 import synth
     from speedoza_b200.backend import CudaBackend
@@ -477,6 +477,14 @@ def profile_case(name: str):
         ws = b.attention_workspace(24, 256, "cuda")
         for _ in range(3):
             b.turboquant_attention(q_, kq, vq, meta, ctx - 1, ws)
+    elif name.startswith("bf16_argmax_m"):
+        m_tok = int(name.rsplit("m", 1)[1])
+        rows, cols = synth.VOCAB, synth.HIDDEN
+        wb = torch.randn((rows, cols), generator=gen, device="cuda").to(torch.bfloat16)
+        xh = torch.randn((m_tok, cols), generator=gen, device="cuda").to(torch.bfloat16)
+        tk = torch.zeros(m_tok, dtype=torch.int32, device="cuda")
+        for _ in range(3):
+            b.bf16_matvec_argmax_rows(xh, wb, tk)
     elif name.startswith("quantize_"):
         m_tok = int(name.rsplit("_", 1)[1])
         x = torch.randn((m_tok, 17408), generator=gen, device="cuda").to(torch.bfloat16)
