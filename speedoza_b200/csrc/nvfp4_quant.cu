@@ -68,7 +68,9 @@ nvfp4_quantize_kernel(const __nv_bfloat16 *__restrict__ in, uint8_t *__restrict_
     // the quotient lies within a few ulps of a rounding boundary (all seven boundaries have zero
     // low 21 mantissa bits, so one masked compare finds them, plus infinities and NaN) or is a
     // negative value so small that the IEEE quotient may underflow to -0 (which the reference
-    // encodes as +0).  Those rare groups are redone with the IEEE division.
+    // encodes as +0).  Those rare groups are redone with the IEEE division.  (+0 quotients also
+    // match the masked compare, so a group that mixes zeros with other values takes the exact
+    // route too; an all-zero group is answered directly.)
     uint32_t lo = 0, hi = 0;
     const float rcp = __frcp_rn(ds);
     uint32_t near_boundary = 0xffffffffu, tiny_negative = 0xffffffffu;
@@ -83,7 +85,12 @@ nvfp4_quantize_kernel(const __nv_bfloat16 *__restrict__ in, uint8_t *__restrict_
       near_boundary = min(near_boundary, min((b0 + 4u) & 0x001ffff8u, (b1 + 4u) & 0x001ffff8u));
       tiny_negative = min(tiny_negative, min(b0 - 0x80000000u, b1 - 0x80000000u));
     }
-    if (near_boundary == 0u || tiny_negative < 0x0d800000u) {      // exact route
+    uint32_t any_bits = 0;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) any_bits |= __float_as_uint(x[i]);
+    if ((any_bits & 0x7fffffffu) == 0u) {
+      lo = hi = 0;                                   // every value is +0 or -0 (padding): every code is +0
+    } else if (near_boundary == 0u || tiny_negative < 0x0d800000u) {      // exact route
       lo = hi = 0;
 #pragma unroll
       for (int i = 0; i < 4; ++i)

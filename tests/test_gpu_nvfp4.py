@@ -205,6 +205,10 @@ def test_quantize_codes_at_every_rounding_boundary(backend):
             group[0] = anchor
             group[1:1 + len(chunk)] = chunk
             rows.append(group)
+    rows.append(np.zeros(16, dtype=np.uint16))                                   # all +0
+    rows.append(np.full(16, 0x8000, dtype=np.uint16))                            # all -0
+    rows.append(np.array([0, 0x7FC0] + [0] * 14, dtype=np.uint16))               # zeros and one NaN
+    rows.append(np.array([0x8000, 0x3F80] + [0] * 14, dtype=np.uint16))          # zeros mixed with a value
     x = np.stack(rows)
     # groups that hold NaN or inf take their scale from that value: still compared, only the finite
     # anchor groups exercise the boundaries
