@@ -15,6 +15,8 @@
 // (kernels-cuda/attention.cu:1083-1094); a second kernel merges them.
 #include "common.cuh"
 
+#include <cuda_fp16.h>
+
 #include <mutex>
 
 namespace {
@@ -454,7 +456,7 @@ kv_merge_kernel(const float *__restrict__ part_o, const float *__restrict__ part
 }
 
 struct Scratch { float *o, *m, *l; };
-bool g_use_fast_attention = true;
+int g_use_fast_attention = 2;            // 2 tensor-core form, 1 SIMT fast path, 0 general kernel
 
 // Scratch for qwen36_turboquant_attention_static: lives in the library image, so every GPU that
 // loads the library holds these 4 MiB until the process exits.  Sized for
@@ -481,6 +483,257 @@ uint32_t pick_splits(size_t tokens, size_t ctas_per_split) {
   return static_cast<uint32_t>(n);
 }
 
+// ---- tensor-core form (head_dim 256, up to 8 q heads per kv head) ---------------------------
+//
+// The SIMT kernels above convert and multiply every int8 element once per q head and end up
+// issue-bound long before HBM is.  Here both products run on the tensor cores as
+// mma.sync.m16n8k16 with float16 operands and float32 accumulation; int8 -> float16 is exact
+// (0x6400 | (byte ^ 0x80) is 1024 + 128 + value; one packed subtraction removes the bias), q is
+// rounded to float16, probabilities to float16 after scaling by v_scale * 1024.
+//
+// A warp owns 16 tokens at a time (two blocks of eight).  Lane (g = lane / 4, t = lane % 4):
+//   S = Q K^T : A = Q (row g = q head g, rows >= G are zero), B = K^T with token g of the block as
+//       its column; the contraction index is permuted so that a lane's operands are the sixteen
+//       consecutive bytes it loads: step 4 j + i covers dims 64 j + 16 t + 4 i .. + 3.
+//       The accumulator leaves lane (g, t) with head g's scores of tokens 2t, 2t + 1 of the block.
+//   O^T = V^T P^T : those four scores (two blocks) are exactly the B fragment of the second
+//       product (column = head g, contraction slots 2t, 2t+1, 2t+8, 2t+9 = this lane's tokens),
+//       so probabilities never leave their registers.  A = V^T: a lane loads sixteen dims
+//       (16 (g + 8 h) ..) of its four tokens and pairs bytes of neighbouring tokens; mma (h, j)
+//       has dim 16 (g + 8 h) + 2 j in row g and the next dim in row g + 8.  Its accumulator holds
+//       heads 2t, 2t + 1 of those two dims.
+__device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                        uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+               "{%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// (lo byte of x, lo byte of y) as int8 -> float16x2; x and y already XORed with 0x80 per byte.
+template <int BYTE>
+__device__ __forceinline__ uint32_t s8pair_to_h2(uint32_t x, uint32_t y) {
+  const uint32_t sel = BYTE | ((4 + BYTE) << 4);                  // byte0 = x.b[BYTE], byte1 = y.b[BYTE]
+  const uint32_t two = __byte_perm(x, y, sel);                    // bytes: x.b, y.b, -, -
+  const uint32_t spread = __byte_perm(two, 0x64646464u, 0x5140);   // x.b, 0x64, y.b, 0x64
+  const __half2 biased = *reinterpret_cast<const __half2 *>(&spread);
+  const __half2 r = __hsub2(biased, __half2half2(__ushort_as_half(0x6480)));   // - (1024 + 128)
+  return *reinterpret_cast<const uint32_t *>(&r);
+}
+// bytes (2 * PAIR, 2 * PAIR + 1) of one word as int8 -> float16x2
+template <int PAIR>
+__device__ __forceinline__ uint32_t s8x2_to_h2(uint32_t x) {
+  const uint32_t spread = __byte_perm(x, 0x64646464u, PAIR == 0 ? 0x5140 : 0x7362);
+  const __half2 biased = *reinterpret_cast<const __half2 *>(&spread);
+  const __half2 r = __hsub2(biased, __half2half2(__ushort_as_half(0x6480)));
+  return *reinterpret_cast<const uint32_t *>(&r);
+}
+
+template <int G>
+__global__ void __launch_bounds__(kThreads, 1)
+kv_attention_mma_kernel(const __nv_bfloat16 *__restrict__ q, const int8_t *__restrict__ kq,
+                        const int8_t *__restrict__ vq, const float *__restrict__ meta,
+                        float *__restrict__ part_o, float *__restrict__ part_m, float *__restrict__ part_l,
+                        size_t t_begin, size_t t_end, uint32_t kv_heads, uint32_t q_per_kv, uint32_t n_splits) {
+  constexpr uint32_t D = 256;
+  constexpr float kPScale = 1024.0f;                              // keeps p * v_scale out of the float16 subnormals
+  __shared__ float s_m[kWarps][8], s_l[kWarps][8];
+  __shared__ float s_o[G][D];
+
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+  const uint32_t g = lane >> 2, t = lane & 3u;
+  const uint32_t head0 = blockIdx.x * G;
+  const uint32_t kvh = head0 / q_per_kv;
+  const uint32_t split = blockIdx.y;
+  const size_t total = t_end - t_begin;
+  const size_t per_split = q36::div_ceil(total, n_splits);
+  const size_t s_begin = t_begin + min(total, per_split * split);
+  const size_t s_end = t_begin + min(total, per_split * (split + 1));
+  const float sm_scale = 0.0625f * 1.4426950408889634f;           // rsqrt(256) * log2(e)
+
+  // Q fragments: step s = 4 j + i covers dims 64 j + 16 t + 4 i .. + 3 of head g
+  uint32_t qa[16][2];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint4 raw0 = make_uint4(0, 0, 0, 0), raw1 = make_uint4(0, 0, 0, 0);
+    if (g < G) {
+      const uint4 *src = reinterpret_cast<const uint4 *>(q + static_cast<size_t>(head0 + g) * D + 64 * j + 16 * t);
+      raw0 = __ldg(src);
+      raw1 = __ldg(src + 1);
+    }
+    const uint32_t w[8] = {raw0.x, raw0.y, raw0.z, raw0.w, raw1.x, raw1.y, raw1.z, raw1.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const uint32_t pair = w[2 * i + half];                    // two bf16: dims 4 i + 2 half, + 1
+        const __half2 h = __floats2half2_rn(__uint_as_float(pair << 16), __uint_as_float(pair & 0xffff0000u));
+        qa[4 * j + i][half] = *reinterpret_cast<const uint32_t *>(&h);
+      }
+    }
+  }
+
+  float o[2][8][4];
+#pragma unroll
+  for (int h = 0; h < 2; ++h)
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) o[h][j][c] = 0.f;
+  float m_run = -INFINITY, l_run = 0.f;                           // head g, identical on its four lanes
+
+  struct Batch { uint4 k[2][4]; uint4 v[4][2]; float2 sc[4]; };
+  // tokens of lane t inside a 16-token group: 2t, 2t + 1, 8 + 2t, 9 + 2t
+  auto load = [&](Batch &b, size_t t0) {
+#pragma unroll
+    for (int blk = 0; blk < 2; ++blk) {
+      const size_t tok = t0 + 8 * blk + g;
+      if (tok < s_end) {
+        const uint4 *src = reinterpret_cast<const uint4 *>(kq + (tok * kv_heads + kvh) * D) + t;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) b.k[blk][j] = __ldcs(src + 4 * j);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) b.k[blk][j] = make_uint4(0, 0, 0, 0);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const size_t tok = t0 + 2 * t + (i & 1) + 8 * (i >> 1);
+      if (tok < s_end) {
+        const size_t row = tok * kv_heads + kvh;
+        const uint4 *src = reinterpret_cast<const uint4 *>(vq + row * D) + g;
+        b.v[i][0] = __ldcs(src);
+        b.v[i][1] = __ldcs(src + 8);
+        b.sc[i] = __ldg(reinterpret_cast<const float2 *>(meta) + row);
+      } else {
+        b.v[i][0] = b.v[i][1] = make_uint4(0, 0, 0, 0);
+        b.sc[i] = make_float2(0.f, 0.f);
+      }
+    }
+  };
+
+  const size_t stride = static_cast<size_t>(kWarps) * 16;
+  Batch cur, nxt;
+  size_t t0 = s_begin + static_cast<size_t>(warp) * 16;
+  if (t0 < s_end) load(cur, t0);
+  for (; t0 < s_end; t0 += stride) {
+    if (t0 + stride < s_end) load(nxt, t0 + stride);
+    // ---- S = Q K^T for the two 8-token blocks
+    float sc_[4];                                                  // tokens 2t, 2t+1 (block 0), 8+2t, 9+2t (block 1)
+#pragma unroll
+    for (int blk = 0; blk < 2; ++blk) {
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t w[4] = {cur.k[blk][j].x ^ 0x80808080u, cur.k[blk][j].y ^ 0x80808080u,
+                               cur.k[blk][j].z ^ 0x80808080u, cur.k[blk][j].w ^ 0x80808080u};
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          mma_f16(acc, qa[4 * j + i][0], 0u, qa[4 * j + i][1], 0u, s8x2_to_h2<0>(w[i]), s8x2_to_h2<1>(w[i]));
+      }
+      sc_[2 * blk] = acc[0];
+      sc_[2 * blk + 1] = acc[1];
+    }
+    // ---- online softmax, head g: this lane's four tokens, then the four lanes of the head
+    float s_log2[4];
+    float tile_max = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const size_t tok = t0 + 2 * t + (i & 1) + 8 * (i >> 1);
+      const bool valid = g < G && tok < s_end;
+      s_log2[i] = valid ? sc_[i] * cur.sc[i].x * sm_scale : -INFINITY;
+      tile_max = fmaxf(tile_max, s_log2[i]);
+    }
+    tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 1));
+    tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 2));
+    const float m_new = fmaxf(m_run, tile_max);
+    const float corr = m_new == -INFINITY ? 1.f : exp2f(m_run - m_new);
+    float p[4], p_sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      p[i] = s_log2[i] == -INFINITY ? 0.f : exp2f(s_log2[i] - m_new);
+      p_sum += p[i];
+    }
+    p_sum += __shfl_xor_sync(0xffffffffu, p_sum, 1);
+    p_sum += __shfl_xor_sync(0xffffffffu, p_sum, 2);
+    l_run = l_run * corr + p_sum;
+    m_run = m_new;
+    const __half2 pb0 = __floats2half2_rn(p[0] * cur.sc[0].y * kPScale, p[1] * cur.sc[1].y * kPScale);
+    const __half2 pb1 = __floats2half2_rn(p[2] * cur.sc[2].y * kPScale, p[3] * cur.sc[3].y * kPScale);
+    const uint32_t b0 = *reinterpret_cast<const uint32_t *>(&pb0), b1 = *reinterpret_cast<const uint32_t *>(&pb1);
+    // ---- rescale the running output: this lane's accumulators belong to heads 2t and 2t + 1
+    const float c_even = __shfl_sync(0xffffffffu, corr, 8 * t), c_odd = __shfl_sync(0xffffffffu, corr, 8 * t + 4);
+    if (__any_sync(0xffffffffu, corr != 1.f)) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          o[h][j][0] *= c_even; o[h][j][1] *= c_odd; o[h][j][2] *= c_even; o[h][j][3] *= c_odd;
+        }
+    }
+    // ---- O^T += V^T P^T
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint32_t va[4] = {cur.v[0][h].x ^ 0x80808080u, cur.v[0][h].y ^ 0x80808080u, cur.v[0][h].z ^ 0x80808080u, cur.v[0][h].w ^ 0x80808080u};
+      const uint32_t vb[4] = {cur.v[1][h].x ^ 0x80808080u, cur.v[1][h].y ^ 0x80808080u, cur.v[1][h].z ^ 0x80808080u, cur.v[1][h].w ^ 0x80808080u};
+      const uint32_t vc[4] = {cur.v[2][h].x ^ 0x80808080u, cur.v[2][h].y ^ 0x80808080u, cur.v[2][h].z ^ 0x80808080u, cur.v[2][h].w ^ 0x80808080u};
+      const uint32_t vd[4] = {cur.v[3][h].x ^ 0x80808080u, cur.v[3][h].y ^ 0x80808080u, cur.v[3][h].z ^ 0x80808080u, cur.v[3][h].w ^ 0x80808080u};
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {                                // word w holds dims 4 w .. 4 w + 3 of the chunk
+        mma_f16(o[h][2 * w], s8pair_to_h2<0>(va[w], vb[w]), s8pair_to_h2<1>(va[w], vb[w]),
+                s8pair_to_h2<0>(vc[w], vd[w]), s8pair_to_h2<1>(vc[w], vd[w]), b0, b1);
+        mma_f16(o[h][2 * w + 1], s8pair_to_h2<2>(va[w], vb[w]), s8pair_to_h2<3>(va[w], vb[w]),
+                s8pair_to_h2<2>(vc[w], vd[w]), s8pair_to_h2<3>(vc[w], vd[w]), b0, b1);
+      }
+    }
+    cur = nxt;
+  }
+
+  // ---- merge the warps of the CTA: weights per head from the running maxima
+  if (t == 0 && g < G) { s_m[warp][g] = m_run; s_l[warp][g] = l_run; }
+  __syncthreads();
+  float wgt[2];                                                    // heads 2t, 2t + 1
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    const uint32_t head = 2 * t + e;
+    float M = -INFINITY;
+    if (head < G)
+      for (int w = 0; w < kWarps; ++w) M = fmaxf(M, s_m[w][head]);
+    const float mine = head < G ? s_m[warp][head] : -INFINITY;
+    wgt[e] = mine == -INFINITY ? 0.f : exp2f(mine - M) * (1.0f / kPScale);
+  }
+  for (int w = 0; w < kWarps; ++w) {
+    if (warp == w) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const uint32_t head = 2 * t + (c & 1), dim = 16 * (g + 8 * h) + 2 * j + (c >> 1);
+            if (head < G) {
+              float *dst = &s_o[head][dim];
+              *dst = w == 0 ? wgt[c & 1] * o[h][j][c] : fmaf(wgt[c & 1], o[h][j][c], *dst);
+            }
+          }
+    }
+    __syncthreads();
+  }
+  for (uint32_t idx = threadIdx.x; idx < G * D; idx += kThreads) {
+    const uint32_t hd = idx / D, d = idx % D;
+    const size_t slot = static_cast<size_t>(head0 + hd) * n_splits + split;
+    part_o[slot * D + d] = s_o[hd][d];
+    if (d == 0) {
+      float M = -INFINITY, den = 0.f;
+      for (int w = 0; w < kWarps; ++w) M = fmaxf(M, s_m[w][hd]);
+      for (int w = 0; w < kWarps; ++w)
+        den = fmaf(s_m[w][hd] == -INFINITY ? 0.f : exp2f(s_m[w][hd] - M), s_l[w][hd], den);
+      part_m[slot] = M * 0.6931471805599453f;
+      part_l[slot] = den;
+    }
+  }
+}
+
 template <int G>
 int launch_split_g(const __nv_bfloat16 *q, const int8_t *kq, const int8_t *vq, const float *meta, Scratch sc,
                    size_t t_begin, size_t t_end, const qwen36_attention_shape_t &sh, uint32_t q_per_kv,
@@ -491,6 +744,12 @@ int launch_split_g(const __nv_bfloat16 *q, const int8_t *kq, const int8_t *vq, c
 #define Q36_GO(DPL, VEC)                                                                              \
   kv_attention_split_kernel<G, DPL, VEC><<<grid, kThreads, 0, q36::stream()>>>(                        \
       q, kq, vq, meta, sc.o, sc.m, sc.l, t_begin, t_end, KV, q_per_kv, D, n_splits)
+  if (D == 256 && G <= 8 && g_use_fast_attention == 2 &&
+      ((reinterpret_cast<uintptr_t>(kq) | reinterpret_cast<uintptr_t>(vq) | reinterpret_cast<uintptr_t>(q)) & 15u) == 0) {
+    kv_attention_mma_kernel<G><<<grid, kThreads, 0, q36::stream()>>>(q, kq, vq, meta, sc.o, sc.m, sc.l, t_begin,
+                                                                      t_end, KV, q_per_kv, n_splits);
+    return q36::launch_status();
+  }
   if (D == 256 && aligned && (reinterpret_cast<uintptr_t>(q) & 15u) == 0 && g_use_fast_attention) {
     kv_attention_fast_kernel<G><<<grid, kThreads, 0, q36::stream()>>>(q, kq, vq, meta, sc.o, sc.m, sc.l, t_begin,
                                                                        t_end, KV, q_per_kv, n_splits);
@@ -567,7 +826,7 @@ extern "C" int qwen36_turboquant_encode_kv(const qwen36_turboquant_encode_spec_t
 }
 
 // Test hook: 0 routes head_dim 256 through the general kernel instead of the 4-token fast path.
-extern "C" void qwen36_turboquant_attention_set_fast(int enable) { g_use_fast_attention = enable != 0; }
+extern "C" void qwen36_turboquant_attention_set_fast(int mode) { g_use_fast_attention = mode < 0 ? 0 : (mode > 2 ? 2 : mode); }
 
 extern "C" size_t qwen36_turboquant_attention_workspace_bytes(size_t q_heads, size_t head_dim) {
   return scratch_bytes(q_heads, head_dim);
