@@ -537,7 +537,7 @@ kv_attention_mma_kernel(const __nv_bfloat16 *__restrict__ q, const int8_t *__res
   constexpr uint32_t D = 256;
   constexpr float kPScale = 1024.0f;                              // keeps p * v_scale out of the float16 subnormals
   __shared__ float s_m[kWarps][8], s_l[kWarps][8];
-  __shared__ float s_o[G][D];
+  __shared__ float s_o[4 * G][D];
 
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
   const uint32_t g = lane >> 2, t = lane & 3u;
@@ -550,8 +550,10 @@ kv_attention_mma_kernel(const __nv_bfloat16 *__restrict__ q, const int8_t *__res
   const size_t s_end = t_begin + min(total, per_split * (split + 1));
   const float sm_scale = 0.0625f * 1.4426950408889634f;           // rsqrt(256) * log2(e)
 
-  // Q fragments: step s = 4 j + i covers dims 64 j + 16 t + 4 i .. + 3 of head g
-  uint32_t qa[16][2];
+  // Q fragments (the same for every warp, so they live in shared memory): step s = 4 j + i covers
+  // dims 64 j + 16 t + 4 i .. + 3 of head g
+  __shared__ uint2 s_q[16][32];
+  if (warp == 0) {
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     uint4 raw0 = make_uint4(0, 0, 0, 0), raw1 = make_uint4(0, 0, 0, 0);
@@ -567,10 +569,12 @@ kv_attention_mma_kernel(const __nv_bfloat16 *__restrict__ q, const int8_t *__res
       for (int half = 0; half < 2; ++half) {
         const uint32_t pair = w[2 * i + half];                    // two bf16: dims 4 i + 2 half, + 1
         const __half2 h = __floats2half2_rn(__uint_as_float(pair << 16), __uint_as_float(pair & 0xffff0000u));
-        qa[4 * j + i][half] = *reinterpret_cast<const uint32_t *>(&h);
+        reinterpret_cast<uint32_t *>(&s_q[4 * j + i][lane])[half] = *reinterpret_cast<const uint32_t *>(&h);
       }
     }
   }
+  }
+  __syncthreads();
 
   float o[2][8][4];
 #pragma unroll
@@ -619,20 +623,35 @@ kv_attention_mma_kernel(const __nv_bfloat16 *__restrict__ q, const int8_t *__res
   for (; t0 < s_end; t0 += stride) {
     if (t0 + stride < s_end) load(nxt, t0 + stride);
     // ---- S = Q K^T for the two 8-token blocks
+    // four independent accumulator chains (two blocks x even / odd steps) keep the tensor pipe fed
     float sc_[4];                                                  // tokens 2t, 2t+1 (block 0), 8+2t, 9+2t (block 1)
+    float acc[2][2][4];
+#pragma unroll
+    for (int blk = 0; blk < 2; ++blk)
+#pragma unroll
+      for (int par = 0; par < 2; ++par)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[blk][par][c] = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint32_t w[2][4];
+#pragma unroll
+      for (int blk = 0; blk < 2; ++blk) {
+        w[blk][0] = cur.k[blk][j].x ^ 0x80808080u; w[blk][1] = cur.k[blk][j].y ^ 0x80808080u;
+        w[blk][2] = cur.k[blk][j].z ^ 0x80808080u; w[blk][3] = cur.k[blk][j].w ^ 0x80808080u;
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint2 qf = s_q[4 * j + i][lane];
+#pragma unroll
+        for (int blk = 0; blk < 2; ++blk)
+          mma_f16(acc[blk][i & 1], qf.x, 0u, qf.y, 0u, s8x2_to_h2<0>(w[blk][i]), s8x2_to_h2<1>(w[blk][i]));
+      }
+    }
 #pragma unroll
     for (int blk = 0; blk < 2; ++blk) {
-      float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const uint32_t w[4] = {cur.k[blk][j].x ^ 0x80808080u, cur.k[blk][j].y ^ 0x80808080u,
-                               cur.k[blk][j].z ^ 0x80808080u, cur.k[blk][j].w ^ 0x80808080u};
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-          mma_f16(acc, qa[4 * j + i][0], 0u, qa[4 * j + i][1], 0u, s8x2_to_h2<0>(w[i]), s8x2_to_h2<1>(w[i]));
-      }
-      sc_[2 * blk] = acc[0];
-      sc_[2 * blk + 1] = acc[1];
+      sc_[2 * blk] = acc[blk][0][0] + acc[blk][1][0];
+      sc_[2 * blk + 1] = acc[blk][0][1] + acc[blk][1][1];
     }
     // ---- online softmax, head g: this lane's four tokens, then the four lanes of the head
     float s_log2[4];
@@ -689,7 +708,9 @@ kv_attention_mma_kernel(const __nv_bfloat16 *__restrict__ q, const int8_t *__res
     cur = nxt;
   }
 
-  // ---- merge the warps of the CTA: weights per head from the running maxima
+  // ---- merge the warps of the CTA: weights per head from the running maxima; the weighted outputs
+  // meet in four shared-memory slices (warps 4..7 write, warps 0..3 add), then every thread sums
+  // the four slices of its outputs
   if (t == 0 && g < G) { s_m[warp][g] = m_run; s_l[warp][g] = l_run; }
   __syncthreads();
   float wgt[2];                                                    // heads 2t, 2t + 1
@@ -702,8 +723,9 @@ kv_attention_mma_kernel(const __nv_bfloat16 *__restrict__ q, const int8_t *__res
     const float mine = head < G ? s_m[warp][head] : -INFINITY;
     wgt[e] = mine == -INFINITY ? 0.f : exp2f(mine - M) * (1.0f / kPScale);
   }
-  for (int w = 0; w < kWarps; ++w) {
-    if (warp == w) {
+  float (*slice)[D] = &s_o[(warp & 3u) * G];
+  for (int round = 0; round < 2; ++round) {
+    if ((warp >> 2) == static_cast<uint32_t>(1 - round)) {
 #pragma unroll
       for (int h = 0; h < 2; ++h)
 #pragma unroll
@@ -712,8 +734,8 @@ kv_attention_mma_kernel(const __nv_bfloat16 *__restrict__ q, const int8_t *__res
           for (int c = 0; c < 4; ++c) {
             const uint32_t head = 2 * t + (c & 1), dim = 16 * (g + 8 * h) + 2 * j + (c >> 1);
             if (head < G) {
-              float *dst = &s_o[head][dim];
-              *dst = w == 0 ? wgt[c & 1] * o[h][j][c] : fmaf(wgt[c & 1], o[h][j][c], *dst);
+              float *dst = &slice[head][dim];
+              *dst = round == 0 ? wgt[c & 1] * o[h][j][c] : fmaf(wgt[c & 1], o[h][j][c], *dst);
             }
           }
     }
@@ -722,7 +744,7 @@ kv_attention_mma_kernel(const __nv_bfloat16 *__restrict__ q, const int8_t *__res
   for (uint32_t idx = threadIdx.x; idx < G * D; idx += kThreads) {
     const uint32_t hd = idx / D, d = idx % D;
     const size_t slot = static_cast<size_t>(head0 + hd) * n_splits + split;
-    part_o[slot * D + d] = s_o[hd][d];
+    part_o[slot * D + d] = (s_o[hd][d] + s_o[G + hd][d]) + (s_o[2 * G + hd][d] + s_o[3 * G + hd][d]);
     if (d == 0) {
       float M = -INFINITY, den = 0.f;
       for (int w = 0; w < kWarps; ++w) M = fmaxf(M, s_m[w][hd]);
