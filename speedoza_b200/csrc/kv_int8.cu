@@ -537,7 +537,8 @@ kv_attention_mma_kernel(const __nv_bfloat16 *__restrict__ q, const int8_t *__res
   constexpr uint32_t D = 256;
   constexpr float kPScale = 1024.0f;                              // keeps p * v_scale out of the float16 subnormals
   __shared__ float s_m[kWarps][8], s_l[kWarps][8];
-  __shared__ float s_o[4 * G][D];
+  constexpr uint32_t DP = D + 4;                                  // row stride: heads land a quarter of the banks apart
+  __shared__ float s_o[4 * G][DP];
 
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
   const uint32_t g = lane >> 2, t = lane & 3u;
@@ -545,7 +546,8 @@ kv_attention_mma_kernel(const __nv_bfloat16 *__restrict__ q, const int8_t *__res
   const uint32_t kvh = head0 / q_per_kv;
   const uint32_t split = blockIdx.y;
   const size_t total = t_end - t_begin;
-  const size_t per_split = q36::div_ceil(total, n_splits);
+  // whole rounds of 8 warps x 16 tokens per split, so that every warp runs the same number of groups
+  const size_t per_split = q36::round_up(q36::div_ceil(total, n_splits), static_cast<size_t>(kWarps) * 16);
   const size_t s_begin = t_begin + min(total, per_split * split);
   const size_t s_end = t_begin + min(total, per_split * (split + 1));
   const float sm_scale = 0.0625f * 1.4426950408889634f;           // rsqrt(256) * log2(e)
@@ -723,7 +725,7 @@ kv_attention_mma_kernel(const __nv_bfloat16 *__restrict__ q, const int8_t *__res
     const float mine = head < G ? s_m[warp][head] : -INFINITY;
     wgt[e] = mine == -INFINITY ? 0.f : exp2f(mine - M) * (1.0f / kPScale);
   }
-  float (*slice)[D] = &s_o[(warp & 3u) * G];
+  float (*slice)[DP] = &s_o[(warp & 3u) * G];
   for (int round = 0; round < 2; ++round) {
     if ((warp >> 2) == static_cast<uint32_t>(1 - round)) {
 #pragma unroll
@@ -732,7 +734,9 @@ kv_attention_mma_kernel(const __nv_bfloat16 *__restrict__ q, const int8_t *__res
         for (int j = 0; j < 8; ++j)
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
-            const uint32_t head = 2 * t + (c & 1), dim = 16 * (g + 8 * h) + 2 * j + (c >> 1);
+            // dims are stored XOR-swizzled inside their 16-float chunk (chunk index = g + 8 h), so
+            // that the eight chunks a warp writes at once fall on different banks
+            const uint32_t head = 2 * t + (c & 1), dim = 16 * (g + 8 * h) + ((2 * j + (c >> 1)) ^ (g + 8 * h));
             if (head < G) {
               float *dst = &slice[head][dim];
               *dst = round == 0 ? wgt[c & 1] * o[h][j][c] : fmaf(wgt[c & 1], o[h][j][c], *dst);
@@ -744,7 +748,8 @@ kv_attention_mma_kernel(const __nv_bfloat16 *__restrict__ q, const int8_t *__res
   for (uint32_t idx = threadIdx.x; idx < G * D; idx += kThreads) {
     const uint32_t hd = idx / D, d = idx % D;
     const size_t slot = static_cast<size_t>(head0 + hd) * n_splits + split;
-    part_o[slot * D + d] = (s_o[hd][d] + s_o[G + hd][d]) + (s_o[2 * G + hd][d] + s_o[3 * G + hd][d]);
+    const uint32_t ds = d ^ ((d >> 4) & 15u);                      // undo the swizzle
+    part_o[slot * D + d] = (s_o[hd][ds] + s_o[G + hd][ds]) + (s_o[2 * G + hd][ds] + s_o[3 * G + hd][ds]);
     if (d == 0) {
       float M = -INFINITY, den = 0.f;
       for (int w = 0; w < kWarps; ++w) M = fmaxf(M, s_m[w][hd]);
