@@ -504,7 +504,7 @@ uint32_t pick_splits(size_t tokens, size_t ctas_per_split) {
 //       heads 2t, 2t + 1 of those two dims.
 __device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                         uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
                "{%0, %1, %2, %3};"
                : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
@@ -587,9 +587,10 @@ kv_attention_mma_kernel(const __nv_bfloat16 *__restrict__ q, const int8_t *__res
       for (int c = 0; c < 4; ++c) o[h][j][c] = 0.f;
   float m_run = -INFINITY, l_run = 0.f;                           // head g, identical on its four lanes
 
-  struct Batch { uint4 k[2][4]; uint4 v[4][2]; float2 sc[4]; };
   // tokens of lane t inside a 16-token group: 2t, 2t + 1, 8 + 2t, 9 + 2t
-  auto load = [&](Batch &b, size_t t0) {
+  struct KBuf { uint4 k[2][4]; };
+  struct VBuf { uint4 v[4][2]; float2 sc[4]; };
+  auto load_k = [&](KBuf &b, size_t t0) {
 #pragma unroll
     for (int blk = 0; blk < 2; ++blk) {
       const size_t tok = t0 + 8 * blk + g;
@@ -602,6 +603,8 @@ kv_attention_mma_kernel(const __nv_bfloat16 *__restrict__ q, const int8_t *__res
         for (int j = 0; j < 4; ++j) b.k[blk][j] = make_uint4(0, 0, 0, 0);
       }
     }
+  };
+  auto load_v = [&](VBuf &b, size_t t0) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const size_t tok = t0 + 2 * t + (i & 1) + 8 * (i >> 1);
@@ -617,16 +620,9 @@ kv_attention_mma_kernel(const __nv_bfloat16 *__restrict__ q, const int8_t *__res
       }
     }
   };
-
-  const size_t stride = static_cast<size_t>(kWarps) * 16;
-  Batch cur, nxt;
-  size_t t0 = s_begin + static_cast<size_t>(warp) * 16;
-  if (t0 < s_end) load(cur, t0);
-  for (; t0 < s_end; t0 += stride) {
-    if (t0 + stride < s_end) load(nxt, t0 + stride);
-    // ---- S = Q K^T for the two 8-token blocks
-    // four independent accumulator chains (two blocks x even / odd steps) keep the tensor pipe fed
-    float sc_[4];                                                  // tokens 2t, 2t+1 (block 0), 8+2t, 9+2t (block 1)
+  // S = Q K^T for the two 8-token blocks of a group: four independent accumulator chains (two
+  // blocks x even / odd steps); out = this lane's scores of tokens 2t, 2t+1, 8+2t, 9+2t
+  auto scores = [&](const KBuf &b, float (&out)[4]) {
     float acc[2][2][4];
 #pragma unroll
     for (int blk = 0; blk < 2; ++blk)
@@ -639,8 +635,8 @@ kv_attention_mma_kernel(const __nv_bfloat16 *__restrict__ q, const int8_t *__res
       uint32_t w[2][4];
 #pragma unroll
       for (int blk = 0; blk < 2; ++blk) {
-        w[blk][0] = cur.k[blk][j].x ^ 0x80808080u; w[blk][1] = cur.k[blk][j].y ^ 0x80808080u;
-        w[blk][2] = cur.k[blk][j].z ^ 0x80808080u; w[blk][3] = cur.k[blk][j].w ^ 0x80808080u;
+        w[blk][0] = b.k[blk][j].x ^ 0x80808080u; w[blk][1] = b.k[blk][j].y ^ 0x80808080u;
+        w[blk][2] = b.k[blk][j].z ^ 0x80808080u; w[blk][3] = b.k[blk][j].w ^ 0x80808080u;
       }
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -652,9 +648,28 @@ kv_attention_mma_kernel(const __nv_bfloat16 *__restrict__ q, const int8_t *__res
     }
 #pragma unroll
     for (int blk = 0; blk < 2; ++blk) {
-      sc_[2 * blk] = acc[blk][0][0] + acc[blk][1][0];
-      sc_[2 * blk + 1] = acc[blk][0][1] + acc[blk][1][1];
+      out[2 * blk] = acc[blk][0][0] + acc[blk][1][0];
+      out[2 * blk + 1] = acc[blk][0][1] + acc[blk][1][1];
     }
+  };
+
+  // Software pipeline over this warp's groups: while the probabilities of group n multiply V, the
+  // scores of group n + 1 are already being formed (independent tensor-core work), K of group
+  // n + 2 and V of group n + 1 are in flight.
+  const size_t stride = static_cast<size_t>(kWarps) * 16;
+  KBuf k_now, k_next;               // K of group n + 1 (scored during iteration n), K of group n + 2
+  VBuf v_now, v_next;               // V and scales of group n, of group n + 1
+  float sc_[4] = {0.f, 0.f, 0.f, 0.f}, sc_next[4];
+  size_t t0 = s_begin + static_cast<size_t>(warp) * 16;
+  if (t0 < s_end) {
+    load_k(k_next, t0);
+    load_v(v_now, t0);
+    load_k(k_now, t0 + stride);                      // past-the-end groups load zeros
+    scores(k_next, sc_);
+  }
+  for (; t0 < s_end; t0 += stride) {
+    load_k(k_next, t0 + 2 * stride);
+    load_v(v_next, t0 + stride);
     // ---- online softmax, head g: this lane's four tokens, then the four lanes of the head
     float s_log2[4];
     float tile_max = -INFINITY;
@@ -662,7 +677,7 @@ kv_attention_mma_kernel(const __nv_bfloat16 *__restrict__ q, const int8_t *__res
     for (int i = 0; i < 4; ++i) {
       const size_t tok = t0 + 2 * t + (i & 1) + 8 * (i >> 1);
       const bool valid = g < G && tok < s_end;
-      s_log2[i] = valid ? sc_[i] * cur.sc[i].x * sm_scale : -INFINITY;
+      s_log2[i] = valid ? sc_[i] * v_now.sc[i].x * sm_scale : -INFINITY;
       tile_max = fmaxf(tile_max, s_log2[i]);
     }
     tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 1));
@@ -679,9 +694,11 @@ kv_attention_mma_kernel(const __nv_bfloat16 *__restrict__ q, const int8_t *__res
     p_sum += __shfl_xor_sync(0xffffffffu, p_sum, 2);
     l_run = l_run * corr + p_sum;
     m_run = m_new;
-    const __half2 pb0 = __floats2half2_rn(p[0] * cur.sc[0].y * kPScale, p[1] * cur.sc[1].y * kPScale);
-    const __half2 pb1 = __floats2half2_rn(p[2] * cur.sc[2].y * kPScale, p[3] * cur.sc[3].y * kPScale);
+    const __half2 pb0 = __floats2half2_rn(p[0] * v_now.sc[0].y * kPScale, p[1] * v_now.sc[1].y * kPScale);
+    const __half2 pb1 = __floats2half2_rn(p[2] * v_now.sc[2].y * kPScale, p[3] * v_now.sc[3].y * kPScale);
     const uint32_t b0 = *reinterpret_cast<const uint32_t *>(&pb0), b1 = *reinterpret_cast<const uint32_t *>(&pb1);
+    // ---- scores of the next group (nothing below depends on them)
+    scores(k_now, sc_next);
     // ---- rescale the running output: this lane's accumulators belong to heads 2t and 2t + 1
     const float c_even = __shfl_sync(0xffffffffu, corr, 8 * t), c_odd = __shfl_sync(0xffffffffu, corr, 8 * t + 4);
     if (__any_sync(0xffffffffu, corr != 1.f)) {
@@ -695,10 +712,10 @@ kv_attention_mma_kernel(const __nv_bfloat16 *__restrict__ q, const int8_t *__res
     // ---- O^T += V^T P^T
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-      const uint32_t va[4] = {cur.v[0][h].x ^ 0x80808080u, cur.v[0][h].y ^ 0x80808080u, cur.v[0][h].z ^ 0x80808080u, cur.v[0][h].w ^ 0x80808080u};
-      const uint32_t vb[4] = {cur.v[1][h].x ^ 0x80808080u, cur.v[1][h].y ^ 0x80808080u, cur.v[1][h].z ^ 0x80808080u, cur.v[1][h].w ^ 0x80808080u};
-      const uint32_t vc[4] = {cur.v[2][h].x ^ 0x80808080u, cur.v[2][h].y ^ 0x80808080u, cur.v[2][h].z ^ 0x80808080u, cur.v[2][h].w ^ 0x80808080u};
-      const uint32_t vd[4] = {cur.v[3][h].x ^ 0x80808080u, cur.v[3][h].y ^ 0x80808080u, cur.v[3][h].z ^ 0x80808080u, cur.v[3][h].w ^ 0x80808080u};
+      const uint32_t va[4] = {v_now.v[0][h].x ^ 0x80808080u, v_now.v[0][h].y ^ 0x80808080u, v_now.v[0][h].z ^ 0x80808080u, v_now.v[0][h].w ^ 0x80808080u};
+      const uint32_t vb[4] = {v_now.v[1][h].x ^ 0x80808080u, v_now.v[1][h].y ^ 0x80808080u, v_now.v[1][h].z ^ 0x80808080u, v_now.v[1][h].w ^ 0x80808080u};
+      const uint32_t vc[4] = {v_now.v[2][h].x ^ 0x80808080u, v_now.v[2][h].y ^ 0x80808080u, v_now.v[2][h].z ^ 0x80808080u, v_now.v[2][h].w ^ 0x80808080u};
+      const uint32_t vd[4] = {v_now.v[3][h].x ^ 0x80808080u, v_now.v[3][h].y ^ 0x80808080u, v_now.v[3][h].z ^ 0x80808080u, v_now.v[3][h].w ^ 0x80808080u};
 #pragma unroll
       for (int w = 0; w < 4; ++w) {                                // word w holds dims 4 w .. 4 w + 3 of the chunk
         mma_f16(o[h][2 * w], s8pair_to_h2<0>(va[w], vb[w]), s8pair_to_h2<1>(va[w], vb[w]),
@@ -707,7 +724,10 @@ kv_attention_mma_kernel(const __nv_bfloat16 *__restrict__ q, const int8_t *__res
                 s8pair_to_h2<2>(vc[w], vd[w]), s8pair_to_h2<3>(vc[w], vd[w]), b0, b1);
       }
     }
-    cur = nxt;
+    k_now = k_next;
+    v_now = v_next;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) sc_[i] = sc_next[i];
   }
 
   // ---- merge the warps of the CTA: weights per head from the running maxima; the weighted outputs
