@@ -519,13 +519,12 @@ __device__ __forceinline__ uint32_t s8pair_to_h2(uint32_t x, uint32_t y) {
   const __half2 r = __hsub2(biased, __half2half2(__ushort_as_half(0x6480)));   // - (1024 + 128)
   return *reinterpret_cast<const uint32_t *>(&r);
 }
-// bytes (2 * PAIR, 2 * PAIR + 1) of one word as int8 -> float16x2
+// bytes (2 * PAIR, 2 * PAIR + 1) of one word as int8 -> float16x2 of (value + 1152): the bias is
+// taken out of the finished dot product instead (1152 * sum of the other operand), which saves a
+// packed subtraction per pair
 template <int PAIR>
-__device__ __forceinline__ uint32_t s8x2_to_h2(uint32_t x) {
-  const uint32_t spread = __byte_perm(x, 0x64646464u, PAIR == 0 ? 0x5140 : 0x7362);
-  const __half2 biased = *reinterpret_cast<const __half2 *>(&spread);
-  const __half2 r = __hsub2(biased, __half2half2(__ushort_as_half(0x6480)));
-  return *reinterpret_cast<const uint32_t *>(&r);
+__device__ __forceinline__ uint32_t s8x2_to_h2_biased(uint32_t x) {
+  return __byte_perm(x, 0x64646464u, PAIR == 0 ? 0x5140 : 0x7362);
 }
 
 template <int G>
@@ -577,6 +576,19 @@ kv_attention_mma_kernel(const __nv_bfloat16 *__restrict__ q, const int8_t *__res
   }
   }
   __syncthreads();
+
+  // 1152 * (sum of head g's float16 q): the K operand carries that bias on every element
+  float q_bias = 0.f;
+#pragma unroll
+  for (int s16 = 0; s16 < 16; ++s16) {
+    const uint2 qf = s_q[s16][lane];
+    const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&qf.x));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&qf.y));
+    q_bias += (a.x + a.y) + (b.x + b.y);
+  }
+  q_bias += __shfl_xor_sync(0xffffffffu, q_bias, 1);
+  q_bias += __shfl_xor_sync(0xffffffffu, q_bias, 2);
+  q_bias *= 1152.0f;
 
   float o[2][8][4];
 #pragma unroll
@@ -643,13 +655,13 @@ kv_attention_mma_kernel(const __nv_bfloat16 *__restrict__ q, const int8_t *__res
         const uint2 qf = s_q[4 * j + i][lane];
 #pragma unroll
         for (int blk = 0; blk < 2; ++blk)
-          mma_f16(acc[blk][i & 1], qf.x, 0u, qf.y, 0u, s8x2_to_h2<0>(w[blk][i]), s8x2_to_h2<1>(w[blk][i]));
+          mma_f16(acc[blk][i & 1], qf.x, 0u, qf.y, 0u, s8x2_to_h2_biased<0>(w[blk][i]), s8x2_to_h2_biased<1>(w[blk][i]));
       }
     }
 #pragma unroll
     for (int blk = 0; blk < 2; ++blk) {
-      out[2 * blk] = acc[blk][0][0] + acc[blk][1][0];
-      out[2 * blk + 1] = acc[blk][0][1] + acc[blk][1][1];
+      out[2 * blk] = (acc[blk][0][0] + acc[blk][1][0]) - q_bias;
+      out[2 * blk + 1] = (acc[blk][0][1] + acc[blk][1][1]) - q_bias;
     }
   };
 
