@@ -639,8 +639,9 @@ def run_ours(args):
         run_step = None
         del runner, sweep
         torch.cuda.empty_cache()
-        extra["sharded"] = [measure_sharded(w, 0, 10, 3, backend, torch, dist, world, rank)
-                            for w in ("lm_head", "attention", "prefill")]
+        extra["sharded"] = [measure_sharded(w, 0, 10, 3, backend, torch, dist, world, rank, combine=c)
+                            for w, c in (("lm_head", "peer"), ("lm_head", "collective"), ("attention", "peer"),
+                                         ("attention", "collective"), ("prefill", "none"))]
     if rank == 0:
         peak, peak_kind = measured_peaks()
         ms_per_step = ms / args.steps
@@ -691,10 +692,21 @@ def run_ours(args):
         os._exit(0)
 
 
-def measure_sharded(workload, tokens, steps, warmup, b, torch, dist, world, rank):
+def peer_combine_usable(make, torch, dist, world):
+    """Builds a sharded operator with the NVLink peer-memory combine; every rank falls back to the
+    collective together when the peer mapping is refused on any of them."""
+    from speedoza_b200.abi import KernelError
+    try:
+        return make("peer"), "NVLink peer push (one kernel)"
+    except KernelError:
+        return make("collective"), "all-gather (NCCL)"
+
+
+def measure_sharded(workload, tokens, steps, warmup, b, torch, dist, world, rank, combine="peer"):
     """One sharded configuration at `world` GPUs (strong scaling: the total work is fixed, each rank
     holds 1/world of the vocab rows, of the KV range, or of the weight rows).  Returns a dict."""
     from speedoza_b200 import shard, synth
+    how = None
     gen = torch.Generator(device="cuda").manual_seed(4321)
     if workload == "lm_head":
         m_tok = tokens or 4
@@ -705,11 +717,17 @@ def measure_sharded(workload, tokens, steps, warmup, b, torch, dist, world, rank
         sc = torch.exp2(torch.rand(hi - lo, generator=gen, device="cuda") * 4 - 6)
         gen.manual_seed(7)
         x = torch.randn((m_tok, cols), generator=gen, device="cuda").to(torch.bfloat16)
-        head = shard.ShardedLmHead(b, rows, w, sc, lo, world, m_tok)
+        make = lambda c: shard.ShardedLmHead(b, rows, w, sc, lo, world, m_tok, combine=c)
+        head, how = peer_combine_usable(make, torch, dist, world) if (combine == "peer" and world > 1) else \
+            (make("collective"), "all-gather (NCCL)" if world > 1 else None)
+        if how is not None and how.startswith("NVLink"):
+            want = make("collective").argmax(x).to(torch.int64)      # the two combines must agree
+            got = head.argmax(x).to(torch.int64)
+            assert torch.equal(want, got), "peer argmax combine differs from the collective one"
         step = lambda: head.argmax(x)
         work, unit = rows * cols + 4 * rows + 2 * m_tok * cols + 8 * m_tok, "GB/s"
         name = (f"config 3: FP8 lm_head 248320x5120 + fused greedy argmax, M={m_tok}, vocab split {world}-way "
-                "+ all-gather of (value, index)")
+                "+ combine of (value, index)")
         dtype = "e4m3 x bf16 -> f32"
     elif workload == "attention":
         ctx = tokens or 131072
@@ -724,11 +742,17 @@ def measure_sharded(workload, tokens, steps, warmup, b, torch, dist, world, rank
         del k_, v_
         gen.manual_seed(7)
         q_ = torch.randn((24, 256), generator=gen, device="cuda").to(torch.bfloat16)
-        att = shard.ShardedKvAttention(b, kq, vq, meta, lo, world, 24, 256)
+        make = lambda c: shard.ShardedKvAttention(b, kq, vq, meta, lo, world, 24, 256, combine=c)
+        att, how = peer_combine_usable(make, torch, dist, world) if (combine == "peer" and world > 1) else \
+            (make("collective"), "all-gather (NCCL)" if world > 1 else None)
+        if how is not None and how.startswith("NVLink"):
+            want = make("collective").attend(q_, ctx - 1).float()    # same arithmetic, same order: same bits
+            got = att.attend(q_, ctx - 1).float()
+            assert torch.equal(want, got), "peer attention merge differs from the collective one"
         step = lambda: att.attend(q_, ctx - 1)
         work, unit = ctx * (2 * 4 * 256 + 32) + 24 * 256 * 4, "GB/s"
         name = (f"config 4: int8 KV decode attention, ctx {ctx}, 24 q / 4 kv heads, KV range split {world}-way "
-                "+ all-gather of (m, l, o)")
+                "+ merge of (m, l, o)")
         dtype = "int8 x bf16 -> f32"
     else:
         m_tok = tokens or 8192
@@ -793,8 +817,18 @@ def measure_sharded(workload, tokens, steps, warmup, b, torch, dist, world, rank
         ms = float(t[0])
     per = ms / steps
     value = work / (per * 1e-3) / (1e9 if unit == "GB/s" else 1e12)
-    return {"workload": name, "value": round(value, 1), "unit": unit, "ms_per_step": round(per, 4), "dtype": dtype,
-            "launch": "CUDA graph replay" if graph is not None else "eager"}
+    launch = "CUDA graph replay" if graph is not None else "eager"
+    del graph, run
+    for op in (locals().get("head"), locals().get("att")):
+        if op is not None and getattr(op, "peer", None) is not None:
+            op.peer.ex.close()                   # unmaps the peers' inboxes (collective: every rank gets here)
+    out = {"workload": name, "value": round(value, 1), "unit": unit, "ms_per_step": round(per, 4), "dtype": dtype,
+           "launch": launch}
+    if how is not None:
+        out["combine"] = how
+        if int(b.lib.qwen36_peer_last_error()) != 0:
+            out["combine"] += "; a wait for a peer ran out"
+    return out
 
 
 def run_sharded_workload(args):
@@ -808,12 +842,14 @@ def run_sharded_workload(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     b = CudaBackend()
-    r = measure_sharded(args.workload, args.tokens, args.steps, args.warmup, b, torch, dist, world, rank)
+    r = measure_sharded(args.workload, args.tokens, args.steps, args.warmup, b, torch, dist, world, rank,
+                        combine=args.combine)
     if rank == 0:
         print(json.dumps({"metric": METRIC, "value": r["value"], "unit": r["unit"], "n_gpus": world, "steps": args.steps,
                           "warmup": max(3, args.warmup), "ms_per_step": r["ms_per_step"], "higher_is_better": True,
                           "scaling": "strong", "vs_baseline": None, "dtype": r["dtype"], "data": "synthetic",
-                          "config": {"workload": r["workload"]}}), flush=True)
+                          "config": {"workload": r["workload"], "launch": r["launch"],
+                                     "combine": r.get("combine")}}), flush=True)
     if world > 1:
         dist.barrier()
         torch.cuda.synchronize()
@@ -887,6 +923,8 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--workload", default="sweep",
                     choices=["sweep", "sweep_split", "lm_head", "attention", "prefill"])
+    ap.add_argument("--combine", default="peer", choices=["peer", "collective"],
+                    help="cross-rank combine of the sharded lm_head / attention: NVLink peer push or all-gather")
     ap.add_argument("--tokens", type=int, default=0, help="M (lm_head, prefill) or context length (attention)")
     ap.add_argument("--profile-case", default=None, help="run one small kernel case (for ncu) and exit")
     args = ap.parse_args()

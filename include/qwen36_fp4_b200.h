@@ -376,6 +376,59 @@ typedef struct {
 } qwen36_attention_merge_spec_t;
 int qwen36_attention_merge_partials(const qwen36_attention_merge_spec_t *spec);
 
+/* ---- Multi-GPU combine over NVLink peer memory (no reference counterpart: the
+ * reference is single-GPU).  One process per GPU on one node.  Every rank
+ * allocates an inbox and a flag array with qwen36_cuda_malloc plus a local
+ * 2-word state, all zero-filled once; exports inbox and flags with
+ * qwen36_ipc_get_handle, opens the peers' handles with qwen36_ipc_open_handle,
+ * and keeps two device arrays of `world` pointers in rank order (its own
+ * entries are the local pointers).  A combine kernel pushes this rank's piece
+ * into every peer's inbox with plain peer stores, raises a flag there, waits
+ * on its own flags and combines out of its own memory.  Every wait is bounded
+ * (a few seconds at most), after which the output is left untouched and
+ * qwen36_peer_last_error() returns 1.  The call number is kept in `state` and
+ * advanced by the kernel, so a captured launch can be replayed; all ranks must
+ * make the same sequence of calls on one set of buffers. */
+int qwen36_ipc_get_handle(qwen36_device_ptr_t ptr, void *handle_out_64_bytes);
+int qwen36_ipc_open_handle(const void *handle_64_bytes, qwen36_device_ptr_t *out);
+int qwen36_ipc_close_handle(qwen36_device_ptr_t ptr);
+int qwen36_peer_last_error(void);   /* sticky */
+int qwen36_peer_reset_error(void);
+
+/* Cross-rank log-sum-exp merge of one (m, l, o) partial per q head and rank
+ * (the arithmetic of qwen36_attention_merge_partials with n_parts = world, in
+ * rank order, so every rank gets the same bits).  The three inputs are the
+ * outputs of qwen36_turboquant_attention_partial.  Inbox:
+ * qwen36_attention_peer_inbox_bytes(world, q_heads, head_dim); flag array:
+ * world * q_heads uint32; state: 2 uint32. */
+typedef struct {
+  size_t world, rank, q_heads, head_dim;
+  qwen36_device_ptr_t partial_acc_f32, partial_max_f32, partial_denom_f32;
+  qwen36_device_ptr_t peer_inbox;     /* device array: world x (float *)    */
+  qwen36_device_ptr_t peer_flags;     /* device array: world x (uint32_t *) */
+  qwen36_device_ptr_t state;          /* local, 2 x uint32                  */
+  qwen36_device_ptr_t output_bf16;    /* [q_heads, head_dim]                */
+} qwen36_attention_peer_merge_spec_t;
+size_t qwen36_attention_peer_inbox_bytes(size_t world, size_t q_heads, size_t head_dim);
+int qwen36_attention_peer_merge(const qwen36_attention_peer_merge_spec_t *spec);
+
+/* Cross-rank greedy argmax of one (value, index) pair per token and rank, the
+ * rule of kernels-cuda/ops.cu:19-23 (strictly greater wins, equal values keep
+ * the lower index).  The two inputs are best_value_f32 / output_token_u32 of
+ * qwen36_lm_head_fp8_gemv_argmax.  Inbox:
+ * qwen36_argmax_peer_inbox_bytes(world, tokens); flag array: world uint32;
+ * state: 2 uint32. */
+typedef struct {
+  size_t world, rank, tokens;
+  qwen36_device_ptr_t best_value_f32, best_index_u32;
+  qwen36_device_ptr_t peer_inbox;     /* device array: world x (uint32_t *) */
+  qwen36_device_ptr_t peer_flags;     /* device array: world x (uint32_t *) */
+  qwen36_device_ptr_t state;          /* local, 2 x uint32                  */
+  qwen36_device_ptr_t output_token_u32;
+} qwen36_argmax_peer_combine_spec_t;
+size_t qwen36_argmax_peer_inbox_bytes(size_t world, size_t tokens);
+int qwen36_argmax_peer_combine(const qwen36_argmax_peer_combine_spec_t *spec);
+
 /* lm_head GEMV fused with the greedy argmax: no logits are written.  Each
  * logit is rounded to bf16 exactly as qwen36_lm_head_fp8_gemv would store it
  * before it is compared, so the winner equals qwen36_sample_rows over that

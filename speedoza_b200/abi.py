@@ -163,6 +163,20 @@ class AttentionMergeSpec(C.Structure):
                 ("partial_denom_f32", DevicePtr), ("output_bf16", DevicePtr)]
 
 
+class AttentionPeerMergeSpec(C.Structure):
+    _fields_ = [("world", size_t), ("rank", size_t), ("q_heads", size_t), ("head_dim", size_t),
+                ("partial_acc_f32", DevicePtr), ("partial_max_f32", DevicePtr), ("partial_denom_f32", DevicePtr),
+                ("peer_inbox", DevicePtr), ("peer_flags", DevicePtr), ("state", DevicePtr),
+                ("output_bf16", DevicePtr)]
+
+
+class ArgmaxPeerCombineSpec(C.Structure):
+    _fields_ = [("world", size_t), ("rank", size_t), ("tokens", size_t),
+                ("best_value_f32", DevicePtr), ("best_index_u32", DevicePtr),
+                ("peer_inbox", DevicePtr), ("peer_flags", DevicePtr), ("state", DevicePtr),
+                ("output_token_u32", DevicePtr)]
+
+
 class CudaCounters(C.Structure):
     _fields_ = [(n, C.c_uint64) for n in (
         "malloc_calls", "free_calls", "h2d_calls", "h2d_bytes", "d2h_calls", "d2h_bytes", "d2d_calls",
@@ -241,6 +255,13 @@ def load() -> C.CDLL:
     lib.qwen36_mtp_assume_accept_chain_advance.argtypes = [DevicePtr, size_t, size_t, C.c_int32]
     lib.qwen36_l2_prefetch.argtypes = [DevicePtr, size_t, C.c_int]
     lib.qwen36_cuda_set_l2_access_window.argtypes = [DevicePtr, size_t, C.c_float]
+    lib.qwen36_ipc_get_handle.argtypes = [DevicePtr, C.c_void_p]
+    lib.qwen36_ipc_open_handle.argtypes = [C.c_void_p, C.POINTER(DevicePtr)]
+    lib.qwen36_ipc_close_handle.argtypes = [DevicePtr]
+    lib.qwen36_attention_peer_inbox_bytes.restype = size_t
+    lib.qwen36_attention_peer_inbox_bytes.argtypes = [size_t, size_t, size_t]
+    lib.qwen36_argmax_peer_inbox_bytes.restype = size_t
+    lib.qwen36_argmax_peer_inbox_bytes.argtypes = [size_t, size_t]
     lib.qwen36_nvfp4_chunk_gemv_set_mtile.restype = None
     lib.qwen36_nvfp4_matvec_force_quads.restype = None
     lib.qwen36_nvfp4_gemm_force_bn.restype = None

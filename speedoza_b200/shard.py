@@ -95,13 +95,28 @@ def gather_partials(part_m: torch.Tensor, part_l: torch.Tensor, part_o: torch.Te
 
 
 class ShardedLmHead:
-    """Vocab-sharded FP8 lm_head with fused greedy argmax."""
+    """Vocab-sharded FP8 lm_head with fused greedy argmax.  combine = "peer": the per-rank winners are
+    pushed into the peers' memory over NVLink by one kernel (speedoza_b200.peer, ranks of one node);
+    "collective": all-gather through torch.distributed plus a combine on every rank."""
 
-    def __init__(self, backend, w_e4m3_full_rows: int, w_local, scales_local, row_lo: int, world: int, max_tokens: int):
+    def __init__(self, backend, w_e4m3_full_rows: int, w_local, scales_local, row_lo: int, world: int,
+                 max_tokens: int, combine: str = "collective"):
         self.b, self.w, self.s, self.row_lo, self.world = backend, w_local, scales_local, row_lo, world
         self.ws = backend.lm_head_argmax_workspace(w_local.shape[0], max_tokens, w_local.device)
+        self.peer = None
+        if combine == "peer" and world > 1:
+            from .peer import ArgmaxPeerCombine
+            self.peer = ArgmaxPeerCombine(backend, max_tokens, w_local.device)
+            self.tok = torch.empty(max_tokens, dtype=torch.int32, device=w_local.device)
+            self.best = torch.empty(max_tokens, dtype=torch.float32, device=w_local.device)
+            self.out = torch.empty(max_tokens, dtype=torch.int32, device=w_local.device)
 
     def argmax(self, x_bf16):
+        if self.peer is not None:
+            n = x_bf16.shape[0]
+            self.b.lm_head_fp8_gemv_argmax(self.w, self.s, x_bf16, self.ws, row_offset=self.row_lo,
+                                           out_tokens=self.tok[:n], out_best=self.best[:n])
+            return self.peer(self.best[:n], self.tok[:n], self.out[:n])
         tok, best = self.b.lm_head_fp8_gemv_argmax(self.w, self.s, x_bf16, self.ws, row_offset=self.row_lo)
         if self.world == 1:
             return tok.to(torch.int64)
@@ -109,14 +124,29 @@ class ShardedLmHead:
 
 
 class ShardedKvAttention:
-    """KV-range-sharded int8 decode attention: this rank holds cache rows [t_lo, t_hi)."""
+    """KV-range-sharded int8 decode attention: this rank holds cache rows [t_lo, t_hi).  combine as in
+    ShardedLmHead: "peer" merges the ranks' (m, l, o) partials through NVLink peer memory."""
 
-    def __init__(self, backend, kq_local, vq_local, meta_local, t_lo: int, world: int, q_heads: int, head_dim: int):
+    def __init__(self, backend, kq_local, vq_local, meta_local, t_lo: int, world: int, q_heads: int, head_dim: int,
+                 combine: str = "collective"):
         self.b, self.kq, self.vq, self.meta, self.t_lo, self.world = backend, kq_local, vq_local, meta_local, t_lo, world
         self.ws = backend.attention_workspace(q_heads, head_dim, kq_local.device)
+        self.peer = None
+        if combine == "peer" and world > 1:
+            from .peer import AttentionPeerMerge
+            dev = kq_local.device
+            self.peer = AttentionPeerMerge(backend, q_heads, head_dim, dev)
+            self.part_o = torch.empty((q_heads, head_dim), dtype=torch.float32, device=dev)
+            self.part_m = torch.empty(q_heads, dtype=torch.float32, device=dev)
+            self.part_l = torch.empty(q_heads, dtype=torch.float32, device=dev)
+            self.out = torch.empty((q_heads, head_dim), dtype=torch.bfloat16, device=dev)
 
     def attend(self, q_bf16, position: int):
         local_end = max(0, min(self.kq.shape[0], position + 1 - self.t_lo))
+        if self.peer is not None:
+            self.b.turboquant_attention_partial(q_bf16, self.kq, self.vq, self.meta, 0, local_end, self.ws,
+                                                self.part_o, self.part_m, self.part_l)
+            return self.peer(self.part_m, self.part_l, self.part_o, self.out)
         m, l, o = self.b.turboquant_attention_partial(q_bf16, self.kq, self.vq, self.meta, 0, local_end, self.ws)
         if self.world == 1:
             return self.b.attention_merge_partials(m[:, None].contiguous(), l[:, None].contiguous(),

@@ -134,6 +134,8 @@ def test_ctypes_mirrors_match_header_sizes(tmp_path):
              "qwen36_turboquant_attention_spec_t": abi.TurboquantAttentionSpec,
              "qwen36_turboquant_attention_partial_spec_t": abi.TurboquantAttentionPartialSpec,
              "qwen36_attention_merge_spec_t": abi.AttentionMergeSpec,
+             "qwen36_attention_peer_merge_spec_t": abi.AttentionPeerMergeSpec,
+             "qwen36_argmax_peer_combine_spec_t": abi.ArgmaxPeerCombineSpec,
              "qwen36_nvfp4_dequantize_spec_t": abi.Nvfp4DequantizeSpec,
              "qwen36_cuda_diagnostics_t": abi.CudaDiagnostics, "qwen36_cuda_counters_t": abi.CudaCounters}
     body = "\n".join(f'  printf("{n} %zu\\n", sizeof({n}));' for n in names)
@@ -169,6 +171,10 @@ def test_argument_validation_needs_no_gpu(lib):
     assert lib.qwen36_lm_head_fp8_gemv(C.byref(abi.LmHeadFp8GemvSpec())) == abi.INVALID_ARGUMENT
     assert lib.qwen36_turboquant_attention(C.byref(abi.TurboquantAttentionSpec())) == abi.INVALID_ARGUMENT
     assert lib.qwen36_sample_rows(C.byref(abi.SamplingRowsSpec())) == abi.INVALID_ARGUMENT
+    assert lib.qwen36_attention_peer_merge(None) == abi.NULL_POINTER
+    assert lib.qwen36_attention_peer_merge(C.byref(abi.AttentionPeerMergeSpec())) == abi.INVALID_ARGUMENT
+    assert lib.qwen36_argmax_peer_combine(C.byref(abi.ArgmaxPeerCombineSpec())) == abi.INVALID_ARGUMENT
+    assert lib.qwen36_ipc_get_handle(abi.DevicePtr(0), None) == abi.NULL_POINTER
     # out-of-scope operators link and decline
     assert lib.qwen36_rmsnorm(None) == abi.NOT_IMPLEMENTED
     assert lib.qwen36_attention_flash_splitk_prefill_bf16(None, 4) == abi.NOT_IMPLEMENTED
