@@ -425,6 +425,10 @@ kv_merge_kernel(const float *__restrict__ part_o, const float *__restrict__ part
   const float *pm = part_m + qh * n_parts, *pl = part_l + qh * n_parts;
   const float *po = part_o + qh * n_parts * head_dim;
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+  // launched with programmatic stream serialisation after the split kernel: the CTAs are resident
+  // by the time the partials are complete (a no-op after an ordinary launch)
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   // one part per thread: global maximum, weights, weighted denominator
   const float my_m = threadIdx.x < n_parts ? __ldcg(pm + threadIdx.x) : -INFINITY;
@@ -447,12 +451,37 @@ kv_merge_kernel(const float *__restrict__ part_o, const float *__restrict__ part
 
   for (uint32_t d = threadIdx.x; d < head_dim; d += kThreads) {
     float acc = 0.f;
-#pragma unroll 8
-    for (uint32_t s = 0; s < n_parts; ++s) acc = fmaf(s_w[s], __ldcg(po + static_cast<size_t>(s) * head_dim + d), acc);
+    // sixteen loads in flight, then their multiply-adds in part order (a plain loop pays the L2
+    // latency once per part in its remainder iterations)
+    for (uint32_t s0 = 0; s0 < n_parts; s0 += 16) {
+      float v[16];
+#pragma unroll
+      for (uint32_t i = 0; i < 16; ++i)
+        v[i] = __ldcg(po + static_cast<size_t>(min(s0 + i, n_parts - 1)) * head_dim + d);   // clamped: no branch
+#pragma unroll
+      for (uint32_t i = 0; i < 16; ++i)
+        if (s0 + i < n_parts) acc = fmaf(s_w[s0 + i], v[i], acc);
+    }
     if (FINAL) out[qh * head_dim + d] = __float2bfloat16(den > 0.f ? __fdiv_rn(acc, den) : 0.f);
     else out_o[qh * head_dim + d] = acc;
   }
   if (!FINAL && threadIdx.x == 0) { out_m[qh] = M; out_l[qh] = den; }
+}
+
+template <bool FINAL>
+int launch_merge_after_splits(unsigned q_heads, const float *o, const float *m, const float *l, uint32_t n_parts,
+                              uint32_t head_dim, __nv_bfloat16 *out, float *out_o, float *out_m, float *out_l) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(q_heads);
+  cfg.blockDim = dim3(kThreads);
+  cfg.stream = q36::stream();
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return q36::cuda_status(cudaLaunchKernelEx(&cfg, kv_merge_kernel<FINAL>, o, m, l, n_parts, head_dim, out, out_o,
+                                             out_m, out_l));
 }
 
 struct Scratch { float *o, *m, *l; };
@@ -473,9 +502,26 @@ Scratch carve(float *base, size_t q_heads, size_t head_dim) {
   return {base, base + q_heads * kMaxSplits * head_dim, base + q_heads * kMaxSplits * (head_dim + 1)};
 }
 
-uint32_t pick_splits(size_t tokens, size_t ctas_per_split) {
-  // fill ~2 CTAs per SM on a 148-SM part, at least kMinTokensPerSplit tokens each
-  size_t want = q36::div_ceil(296, ctas_per_split);
+int g_force_splits = 0;                  // test hook: > 0 overrides the split count
+
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    cached[dev] = (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0) ? n : 148;
+  }
+  return cached[dev];
+}
+
+// one_wave: the kernel runs one CTA per SM (the tensor-core form: a CTA's start-up and merge cost
+// about as much as 1500 tokens, and nothing overlaps them), so the grid is one CTA per SM or less.
+uint32_t pick_splits(size_t tokens, size_t ctas_per_split, bool one_wave) {
+  if (g_force_splits > 0) return static_cast<uint32_t>(g_force_splits > kMaxSplits ? kMaxSplits : g_force_splits);
+  // otherwise fill ~2 CTAs per SM; at least kMinTokensPerSplit tokens each
+  const size_t sms = static_cast<size_t>(sm_count());
+  size_t want = one_wave ? sms / ctas_per_split : q36::div_ceil(2 * sms, ctas_per_split);
   size_t cap = q36::div_ceil(tokens, kMinTokensPerSplit);
   size_t n = want < cap ? want : cap;
   if (n < 1) n = 1;
@@ -551,45 +597,10 @@ kv_attention_mma_kernel(const __nv_bfloat16 *__restrict__ q, const int8_t *__res
   const size_t s_end = t_begin + min(total, per_split * (split + 1));
   const float sm_scale = 0.0625f * 1.4426950408889634f;           // rsqrt(256) * log2(e)
 
-  // Q fragments (the same for every warp, so they live in shared memory): step s = 4 j + i covers
-  // dims 64 j + 16 t + 4 i .. + 3 of head g
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the merge may take its seats early
+
   __shared__ uint2 s_q[16][32];
-  if (warp == 0) {
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    uint4 raw0 = make_uint4(0, 0, 0, 0), raw1 = make_uint4(0, 0, 0, 0);
-    if (g < G) {
-      const uint4 *src = reinterpret_cast<const uint4 *>(q + static_cast<size_t>(head0 + g) * D + 64 * j + 16 * t);
-      raw0 = __ldg(src);
-      raw1 = __ldg(src + 1);
-    }
-    const uint32_t w[8] = {raw0.x, raw0.y, raw0.z, raw0.w, raw1.x, raw1.y, raw1.z, raw1.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        const uint32_t pair = w[2 * i + half];                    // two bf16: dims 4 i + 2 half, + 1
-        const __half2 h = __floats2half2_rn(__uint_as_float(pair << 16), __uint_as_float(pair & 0xffff0000u));
-        reinterpret_cast<uint32_t *>(&s_q[4 * j + i][lane])[half] = *reinterpret_cast<const uint32_t *>(&h);
-      }
-    }
-  }
-  }
-  __syncthreads();
-
-  // 1152 * (sum of head g's float16 q): the K operand carries that bias on every element
   float q_bias = 0.f;
-#pragma unroll
-  for (int s16 = 0; s16 < 16; ++s16) {
-    const uint2 qf = s_q[s16][lane];
-    const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&qf.x));
-    const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&qf.y));
-    q_bias += (a.x + a.y) + (b.x + b.y);
-  }
-  q_bias += __shfl_xor_sync(0xffffffffu, q_bias, 1);
-  q_bias += __shfl_xor_sync(0xffffffffu, q_bias, 2);
-  q_bias *= 1152.0f;
-
   float o[2][8][4];
 #pragma unroll
   for (int h = 0; h < 2; ++h)
@@ -673,12 +684,50 @@ kv_attention_mma_kernel(const __nv_bfloat16 *__restrict__ q, const int8_t *__res
   VBuf v_now, v_next;               // V and scales of group n, of group n + 1
   float sc_[4] = {0.f, 0.f, 0.f, 0.f}, sc_next[4];
   size_t t0 = s_begin + static_cast<size_t>(warp) * 16;
-  if (t0 < s_end) {
+  if (t0 < s_end) {                                  // first loads fly while q is staged
     load_k(k_next, t0);
     load_v(v_now, t0);
     load_k(k_now, t0 + stride);                      // past-the-end groups load zeros
-    scores(k_next, sc_);
   }
+
+  // Q fragments (the same for every warp, so they live in shared memory): step s = 4 j + i covers
+  // dims 64 j + 16 t + 4 i .. + 3 of head g
+  if (warp == 0) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint4 raw0 = make_uint4(0, 0, 0, 0), raw1 = make_uint4(0, 0, 0, 0);
+    if (g < G) {
+      const uint4 *src = reinterpret_cast<const uint4 *>(q + static_cast<size_t>(head0 + g) * D + 64 * j + 16 * t);
+      raw0 = __ldg(src);
+      raw1 = __ldg(src + 1);
+    }
+    const uint32_t w[8] = {raw0.x, raw0.y, raw0.z, raw0.w, raw1.x, raw1.y, raw1.z, raw1.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const uint32_t pair = w[2 * i + half];                    // two bf16: dims 4 i + 2 half, + 1
+        const __half2 h = __floats2half2_rn(__uint_as_float(pair << 16), __uint_as_float(pair & 0xffff0000u));
+        reinterpret_cast<uint32_t *>(&s_q[4 * j + i][lane])[half] = *reinterpret_cast<const uint32_t *>(&h);
+      }
+    }
+  }
+  }
+  __syncthreads();
+
+  // 1152 * (sum of head g's float16 q): the K operand carries that bias on every element
+#pragma unroll
+  for (int s16 = 0; s16 < 16; ++s16) {
+    const uint2 qf = s_q[s16][lane];
+    const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&qf.x));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&qf.y));
+    q_bias += (a.x + a.y) + (b.x + b.y);
+  }
+  q_bias += __shfl_xor_sync(0xffffffffu, q_bias, 1);
+  q_bias += __shfl_xor_sync(0xffffffffu, q_bias, 2);
+  q_bias *= 1152.0f;
+
+  if (t0 < s_end) scores(k_next, sc_);
   for (; t0 < s_end; t0 += stride) {
     load_k(k_next, t0 + 2 * stride);
     load_v(v_next, t0 + stride);
@@ -833,9 +882,11 @@ uint32_t run_splits(qwen36_device_ptr_t q, qwen36_device_ptr_t kq, qwen36_device
   const int G = (q_per_kv == 1 || q_per_kv == 2 || q_per_kv == 4 || q_per_kv == 6 || q_per_kv == 8)
                     ? static_cast<int>(q_per_kv) : 1;
   const size_t tokens = t_end > t_begin ? t_end - t_begin : 0;
-  const uint32_t n_splits = pick_splits(tokens, sh.q_heads / G);
   const __nv_bfloat16 *qp = as_ptr<const __nv_bfloat16>(q);
   const int8_t *kp = as_ptr<const int8_t>(kq), *vp = as_ptr<const int8_t>(vq);
+  const bool tensor_core_form = sh.head_dim == 256 && g_use_fast_attention == 2 &&
+      ((reinterpret_cast<uintptr_t>(kp) | reinterpret_cast<uintptr_t>(vp) | reinterpret_cast<uintptr_t>(qp)) & 15u) == 0;
+  const uint32_t n_splits = pick_splits(tokens, sh.q_heads / G, tensor_core_form);
   const float *mp = as_ptr<const float>(meta);
   const size_t tb = t_begin, te = t_begin + tokens;
   switch (G) {
@@ -887,6 +938,9 @@ extern "C" int qwen36_turboquant_encode_kv(const qwen36_turboquant_encode_spec_t
 // Test hook: 0 routes head_dim 256 through the general kernel instead of the 4-token fast path.
 extern "C" void qwen36_turboquant_attention_set_fast(int mode) { g_use_fast_attention = mode < 0 ? 0 : (mode > 2 ? 2 : mode); }
 
+// Test hook: n > 0 fixes the number of KV splits, 0 restores the heuristic.
+extern "C" void qwen36_turboquant_attention_force_splits(int n) { g_force_splits = n < 0 ? 0 : n; }
+
 extern "C" size_t qwen36_turboquant_attention_workspace_bytes(size_t q_heads, size_t head_dim) {
   return scratch_bytes(q_heads, head_dim);
 }
@@ -905,10 +959,9 @@ extern "C" int qwen36_turboquant_attention(const qwen36_turboquant_attention_spe
   const uint32_t n = run_splits(spec->q_bf16, spec->k_quantized_i8, spec->v_quantized_i8, spec->metadata_f32,
                                 sc, 0, spec->position + 1, spec->shape, &status);
   if (n == 0) return status;
-  kv_merge_kernel<true><<<static_cast<unsigned>(spec->shape.q_heads), kThreads, 0, q36::stream()>>>(
+  return launch_merge_after_splits<true>(static_cast<unsigned>(spec->shape.q_heads),
       sc.o, sc.m, sc.l, n, static_cast<uint32_t>(spec->shape.head_dim), as_ptr<__nv_bfloat16>(spec->output_bf16),
       nullptr, nullptr, nullptr);
-  return q36::launch_status();
 }
 
 extern "C" int qwen36_turboquant_attention_partial(const qwen36_turboquant_attention_partial_spec_t *spec) {
@@ -926,11 +979,10 @@ extern "C" int qwen36_turboquant_attention_partial(const qwen36_turboquant_atten
   const uint32_t n = run_splits(spec->q_bf16, spec->k_quantized_i8, spec->v_quantized_i8, spec->metadata_f32,
                                 sc, spec->t_begin, spec->t_end, spec->shape, &status);
   if (n == 0) return status;
-  kv_merge_kernel<false><<<static_cast<unsigned>(spec->shape.q_heads), kThreads, 0, q36::stream()>>>(
+  return launch_merge_after_splits<false>(static_cast<unsigned>(spec->shape.q_heads),
       sc.o, sc.m, sc.l, n, static_cast<uint32_t>(spec->shape.head_dim), nullptr,
       as_ptr<float>(spec->partial_acc_f32), as_ptr<float>(spec->partial_max_f32),
       as_ptr<float>(spec->partial_denom_f32));
-  return q36::launch_status();
 }
 
 // Device address of g_static_attention_scratch on the current device, looked up once per
@@ -974,10 +1026,9 @@ extern "C" int qwen36_turboquant_attention_static(const qwen36_turboquant_attent
   const uint32_t n = run_splits(spec->q_bf16, spec->k_quantized_i8, spec->v_quantized_i8, spec->metadata_f32,
                                 sc, 0, spec->position + 1, spec->shape, &status);
   if (n == 0) return status;
-  kv_merge_kernel<true><<<static_cast<unsigned>(spec->shape.q_heads), kThreads, 0, q36::stream()>>>(
+  return launch_merge_after_splits<true>(static_cast<unsigned>(spec->shape.q_heads),
       sc.o, sc.m, sc.l, n, static_cast<uint32_t>(spec->shape.head_dim), as_ptr<__nv_bfloat16>(spec->output_bf16),
       nullptr, nullptr, nullptr);
-  return q36::launch_status();
 }
 
 extern "C" int qwen36_attention_merge_partials(const qwen36_attention_merge_spec_t *spec) {

@@ -90,6 +90,7 @@ attention_peer_merge_kernel(const float *__restrict__ part_o, const float *__res
                             const float *__restrict__ part_l, float *const *peer_inbox, uint32_t *const *peer_flags,
                             uint32_t *state, __nv_bfloat16 *__restrict__ out, uint32_t world, uint32_t rank,
                             uint32_t heads, uint32_t head_dim) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");          // the partials come from the kernel before
   const uint32_t h = blockIdx.x;
   const uint32_t epoch = begin_call(state);
   const uint32_t row = head_dim + 2;
@@ -120,9 +121,13 @@ attention_peer_merge_kernel(const float *__restrict__ part_o, const float *__res
     }
     __syncthreads();
     for (uint32_t d = threadIdx.x; d < head_dim; d += blockDim.x) {
-      float acc = 0.f;
-      for (uint32_t p = 0; p < world; ++p)
-        acc = fmaf(s_w[p], __uint_as_float(ld_inbox_u32(inbox + (static_cast<size_t>(p) * heads + h) * row + d)), acc);
+      float v[kMaxWorld], acc = 0.f;
+#pragma unroll
+      for (uint32_t p = 0; p < kMaxWorld; ++p)                  // all loads first, then the sum in rank order
+        v[p] = p < world ? __uint_as_float(ld_inbox_u32(inbox + (static_cast<size_t>(p) * heads + h) * row + d)) : 0.f;
+#pragma unroll
+      for (uint32_t p = 0; p < kMaxWorld; ++p)
+        if (p < world) acc = fmaf(s_w[p], v[p], acc);
       out[static_cast<size_t>(h) * head_dim + d] = __float2bfloat16(s_den > 0.f ? __fdiv_rn(acc, s_den) : 0.f);
     }
   }
@@ -151,12 +156,18 @@ argmax_peer_combine_kernel(const float *__restrict__ value, const uint32_t *__re
     for (uint32_t t = threadIdx.x; t < n_tokens; t += blockDim.x) {
       float best = -INFINITY;
       uint32_t best_i = 0;
-      for (uint32_t p = 0; p < world; ++p) {
-        const float v = __uint_as_float(ld_inbox_u32(inbox + static_cast<size_t>(p) * 2u * n_tokens + t));
-        const uint32_t i = ld_inbox_u32(inbox + static_cast<size_t>(p) * 2u * n_tokens + n_tokens + t);
-        if (v > best || (v == best && i < best_i)) {
+      uint32_t vs[kMaxWorld], is[kMaxWorld];
+#pragma unroll
+      for (uint32_t p = 0; p < kMaxWorld; ++p) {                // all loads first
+        vs[p] = p < world ? ld_inbox_u32(inbox + static_cast<size_t>(p) * 2u * n_tokens + t) : 0xff800000u;
+        is[p] = p < world ? ld_inbox_u32(inbox + static_cast<size_t>(p) * 2u * n_tokens + n_tokens + t) : 0u;
+      }
+#pragma unroll
+      for (uint32_t p = 0; p < kMaxWorld; ++p) {
+        const float v = __uint_as_float(vs[p]);
+        if (p < world && (v > best || (v == best && is[p] < best_i))) {
           best = v;
-          best_i = i;
+          best_i = is[p];
         }
       }
       tokens[t] = best_i;
@@ -208,13 +219,23 @@ extern "C" int qwen36_attention_peer_merge(const qwen36_attention_peer_merge_spe
       spec->partial_denom_f32.ptr == 0 || spec->peer_inbox.ptr == 0 || spec->peer_flags.ptr == 0 ||
       spec->state.ptr == 0 || spec->output_bf16.ptr == 0)
     return QWEN36_STATUS_INVALID_ARGUMENT;
-  attention_peer_merge_kernel<<<static_cast<unsigned>(spec->q_heads), 256, 0, q36::stream()>>>(
-      as_ptr<const float>(spec->partial_acc_f32), as_ptr<const float>(spec->partial_max_f32),
-      as_ptr<const float>(spec->partial_denom_f32), as_ptr<float *const>(spec->peer_inbox),
-      as_ptr<uint32_t *const>(spec->peer_flags), as_ptr<uint32_t>(spec->state), as_ptr<__nv_bfloat16>(spec->output_bf16),
-      static_cast<uint32_t>(spec->world), static_cast<uint32_t>(spec->rank), static_cast<uint32_t>(spec->q_heads),
-      static_cast<uint32_t>(spec->head_dim));
-  return q36::launch_status();
+  // programmatic stream serialisation: the CTAs take their seats while the kernel that writes the
+  // partials is still running and wait for it on the device
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>(spec->q_heads));
+  cfg.blockDim = dim3(256);
+  cfg.stream = q36::stream();
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return q36::cuda_status(cudaLaunchKernelEx(
+      &cfg, attention_peer_merge_kernel, as_ptr<const float>(spec->partial_acc_f32),
+      as_ptr<const float>(spec->partial_max_f32), as_ptr<const float>(spec->partial_denom_f32),
+      as_ptr<float *const>(spec->peer_inbox), as_ptr<uint32_t *const>(spec->peer_flags), as_ptr<uint32_t>(spec->state),
+      as_ptr<__nv_bfloat16>(spec->output_bf16), static_cast<uint32_t>(spec->world), static_cast<uint32_t>(spec->rank),
+      static_cast<uint32_t>(spec->q_heads), static_cast<uint32_t>(spec->head_dim)));
 }
 
 extern "C" int qwen36_argmax_peer_combine(const qwen36_argmax_peer_combine_spec_t *spec) {
