@@ -412,6 +412,21 @@ typedef struct {
 size_t qwen36_attention_peer_inbox_bytes(size_t world, size_t q_heads, size_t head_dim);
 int qwen36_attention_peer_merge(const qwen36_attention_peer_merge_spec_t *spec);
 
+/* qwen36_turboquant_attention_partial over this rank's rows [t_begin, t_end) of
+ * its local cache and the cross-rank merge in two launches (the split kernel,
+ * then one kernel that merges the splits, pushes and merges the peers'
+ * results); same bits as _partial + qwen36_attention_peer_merge. */
+typedef struct {
+  size_t t_begin, t_end;
+  qwen36_device_ptr_t q_bf16, k_quantized_i8, v_quantized_i8, metadata_f32;
+  qwen36_device_ptr_t workspace;
+  size_t workspace_bytes;
+  qwen36_attention_shape_t shape;
+  size_t world, rank;
+  qwen36_device_ptr_t peer_inbox, peer_flags, state, output_bf16;
+} qwen36_turboquant_attention_peer_spec_t;
+int qwen36_turboquant_attention_peer(const qwen36_turboquant_attention_peer_spec_t *spec);
+
 /* Cross-rank greedy argmax of one (value, index) pair per token and rank, the
  * rule of kernels-cuda/ops.cu:19-23 (strictly greater wins, equal values keep
  * the lower index).  The two inputs are best_value_f32 / output_token_u32 of

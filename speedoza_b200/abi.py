@@ -170,6 +170,14 @@ class AttentionPeerMergeSpec(C.Structure):
                 ("output_bf16", DevicePtr)]
 
 
+class TurboquantAttentionPeerSpec(C.Structure):
+    _fields_ = [("t_begin", size_t), ("t_end", size_t), ("q_bf16", DevicePtr),
+                ("k_quantized_i8", DevicePtr), ("v_quantized_i8", DevicePtr), ("metadata_f32", DevicePtr),
+                ("workspace", DevicePtr), ("workspace_bytes", size_t), ("shape", AttentionShape),
+                ("world", size_t), ("rank", size_t), ("peer_inbox", DevicePtr), ("peer_flags", DevicePtr),
+                ("state", DevicePtr), ("output_bf16", DevicePtr)]
+
+
 class ArgmaxPeerCombineSpec(C.Structure):
     _fields_ = [("world", size_t), ("rank", size_t), ("tokens", size_t),
                 ("best_value_f32", DevicePtr), ("best_index_u32", DevicePtr),

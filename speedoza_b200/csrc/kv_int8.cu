@@ -19,11 +19,15 @@
 
 #include <mutex>
 
+#include "lse_merge.cuh"
+#include "peer_combine.cuh"
+
 namespace {
 
 using q36::as_ptr;
 
 constexpr int kThreads = 256;
+static_assert(kThreads == q36::kMergeThreads, "merge block size");
 constexpr int kWarps = kThreads / 32;
 constexpr int kMaxSplits = 128;
 constexpr int kMinTokensPerSplit = 256;
@@ -424,44 +428,14 @@ kv_merge_kernel(const float *__restrict__ part_o, const float *__restrict__ part
   const size_t qh = blockIdx.x;
   const float *pm = part_m + qh * n_parts, *pl = part_l + qh * n_parts;
   const float *po = part_o + qh * n_parts * head_dim;
-  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
   // launched with programmatic stream serialisation after the split kernel: the CTAs are resident
   // by the time the partials are complete (a no-op after an ordinary launch)
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-
-  // one part per thread: global maximum, weights, weighted denominator
-  const float my_m = threadIdx.x < n_parts ? __ldcg(pm + threadIdx.x) : -INFINITY;
-  const float my_l = threadIdx.x < n_parts ? __ldcg(pl + threadIdx.x) : 0.f;
-  float M = my_m;
-  for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
-  if (lane == 0) s_red[warp] = M;
-  __syncthreads();
-  M = s_red[0];
-  for (int w = 1; w < kWarps; ++w) M = fmaxf(M, s_red[w]);
-  const float wgt = my_m == -INFINITY ? 0.f : __expf(my_m - M);
-  s_w[threadIdx.x] = wgt;
-  float den = wgt * my_l;
-  for (int off = 16; off > 0; off >>= 1) den += __shfl_xor_sync(0xffffffffu, den, off);
-  __syncthreads();
-  if (lane == 0) s_red[warp] = den;
-  __syncthreads();
-  den = 0.f;
-  for (int w = 0; w < kWarps; ++w) den += s_red[w];
-
+  float M, den;
+  q36::lse_weights(pm, pl, n_parts, s_w, s_red, M, den);
   for (uint32_t d = threadIdx.x; d < head_dim; d += kThreads) {
-    float acc = 0.f;
-    // sixteen loads in flight, then their multiply-adds in part order (a plain loop pays the L2
-    // latency once per part in its remainder iterations)
-    for (uint32_t s0 = 0; s0 < n_parts; s0 += 16) {
-      float v[16];
-#pragma unroll
-      for (uint32_t i = 0; i < 16; ++i)
-        v[i] = __ldcg(po + static_cast<size_t>(min(s0 + i, n_parts - 1)) * head_dim + d);   // clamped: no branch
-#pragma unroll
-      for (uint32_t i = 0; i < 16; ++i)
-        if (s0 + i < n_parts) acc = fmaf(s_w[s0 + i], v[i], acc);
-    }
+    const float acc = q36::lse_accumulate(po, s_w, n_parts, head_dim, d);
     if (FINAL) out[qh * head_dim + d] = __float2bfloat16(den > 0.f ? __fdiv_rn(acc, den) : 0.f);
     else out_o[qh * head_dim + d] = acc;
   }
@@ -962,6 +936,28 @@ extern "C" int qwen36_turboquant_attention(const qwen36_turboquant_attention_spe
   return launch_merge_after_splits<true>(static_cast<unsigned>(spec->shape.q_heads),
       sc.o, sc.m, sc.l, n, static_cast<uint32_t>(spec->shape.head_dim), as_ptr<__nv_bfloat16>(spec->output_bf16),
       nullptr, nullptr, nullptr);
+}
+
+// Attention over this rank's token range and the cross-rank merge, two launches: the split kernel,
+// then one kernel that merges the splits, pushes the result to the peers and merges theirs.
+extern "C" int qwen36_turboquant_attention_peer(const qwen36_turboquant_attention_peer_spec_t *spec) {
+  if (spec == nullptr) return QWEN36_STATUS_NULL_POINTER;
+  if (spec->q_bf16.ptr == 0 || spec->k_quantized_i8.ptr == 0 || spec->v_quantized_i8.ptr == 0 ||
+      spec->metadata_f32.ptr == 0 || spec->output_bf16.ptr == 0 || !shape_ok(spec->shape) ||
+      spec->t_end < spec->t_begin)
+    return QWEN36_STATUS_INVALID_ARGUMENT;
+  if (spec->shape.head_dim > 256) return QWEN36_STATUS_NOT_IMPLEMENTED;
+  if (spec->workspace.ptr == 0 || (spec->workspace.ptr & 15u) != 0 ||
+      spec->workspace_bytes < scratch_bytes(spec->shape.q_heads, spec->shape.head_dim))
+    return QWEN36_STATUS_INVALID_ARGUMENT;
+  const Scratch sc = carve(as_ptr<float>(spec->workspace), spec->shape.q_heads, spec->shape.head_dim);
+  int status = QWEN36_STATUS_SUCCESS;
+  const uint32_t n = run_splits(spec->q_bf16, spec->k_quantized_i8, spec->v_quantized_i8, spec->metadata_f32,
+                                sc, spec->t_begin, spec->t_end, spec->shape, &status);
+  if (n == 0) return status;
+  return q36::launch_attention_peer_merge(sc.o, sc.m, sc.l, n, spec->peer_inbox, spec->peer_flags, spec->state,
+                                          spec->output_bf16, spec->world, spec->rank, spec->shape.q_heads,
+                                          spec->shape.head_dim);
 }
 
 extern "C" int qwen36_turboquant_attention_partial(const qwen36_turboquant_attention_partial_spec_t *spec) {

@@ -20,6 +20,9 @@
 
 #include <math.h>
 
+#include "lse_merge.cuh"
+#include "peer_combine.cuh"
+
 namespace {
 
 using q36::as_ptr;
@@ -84,19 +87,29 @@ __device__ bool signal_and_wait(uint32_t *const *peer_flags, uint32_t world, uin
   return ok != 0;
 }
 
-// One CTA per q head.  Inbox: [2 slots][world][q_heads][head_dim + 2] floats, a row = o[head_dim], m, l.
-__global__ void __launch_bounds__(256)
+// One CTA of 256 threads per q head.  Inbox: [2 slots][world][q_heads][head_dim + 2] floats, a row =
+// o[head_dim], m, l.  The local input is n_parts split partials per head ([heads, n_parts(, head_dim)],
+// n_parts = 1: one finished partial per head); they are merged first, with the arithmetic of the
+// single-GPU merge kernel, and the result goes straight into the peers' inboxes.
+__global__ void __launch_bounds__(q36::kMergeThreads)
 attention_peer_merge_kernel(const float *__restrict__ part_o, const float *__restrict__ part_m,
-                            const float *__restrict__ part_l, float *const *peer_inbox, uint32_t *const *peer_flags,
-                            uint32_t *state, __nv_bfloat16 *__restrict__ out, uint32_t world, uint32_t rank,
-                            uint32_t heads, uint32_t head_dim) {
+                            const float *__restrict__ part_l, uint32_t n_parts, float *const *peer_inbox,
+                            uint32_t *const *peer_flags, uint32_t *state, __nv_bfloat16 *__restrict__ out,
+                            uint32_t world, uint32_t rank, uint32_t heads, uint32_t head_dim) {
   asm volatile("griddepcontrol.wait;" ::: "memory");          // the partials come from the kernel before
+  __shared__ float s_parts[q36::kMergeThreads];
+  __shared__ float s_red[q36::kMergeThreads / 32];
   const uint32_t h = blockIdx.x;
   const uint32_t epoch = begin_call(state);
   const uint32_t row = head_dim + 2;
   const size_t slot = static_cast<size_t>(epoch & 1u) * world * heads * row;
+  float local_m, local_l;
+  q36::lse_weights(part_m + static_cast<size_t>(h) * n_parts, part_l + static_cast<size_t>(h) * n_parts, n_parts,
+                   s_parts, s_red, local_m, local_l);
   for (uint32_t d = threadIdx.x; d < row; d += blockDim.x) {
-    const float v = d < head_dim ? part_o[static_cast<size_t>(h) * head_dim + d] : (d == head_dim ? part_m[h] : part_l[h]);
+    const float v = d < head_dim
+        ? q36::lse_accumulate(part_o + static_cast<size_t>(h) * n_parts * head_dim, s_parts, n_parts, head_dim, d)
+        : (d == head_dim ? local_m : local_l);
     const size_t at = slot + (static_cast<size_t>(rank) * heads + h) * row + d;
     for (uint32_t p = 0; p < world; ++p) st_peer_u32(reinterpret_cast<uint32_t *>(peer_inbox[p] + at), __float_as_uint(v));
   }
@@ -212,18 +225,19 @@ extern "C" size_t qwen36_argmax_peer_inbox_bytes(size_t world, size_t tokens) {
   return 2 * world * 2 * tokens * sizeof(uint32_t);
 }
 
-extern "C" int qwen36_attention_peer_merge(const qwen36_attention_peer_merge_spec_t *spec) {
-  if (spec == nullptr) return QWEN36_STATUS_NULL_POINTER;
-  if (spec->world == 0 || spec->world > kMaxWorld || spec->rank >= spec->world || spec->q_heads == 0 ||
-      spec->head_dim == 0 || spec->partial_acc_f32.ptr == 0 || spec->partial_max_f32.ptr == 0 ||
-      spec->partial_denom_f32.ptr == 0 || spec->peer_inbox.ptr == 0 || spec->peer_flags.ptr == 0 ||
-      spec->state.ptr == 0 || spec->output_bf16.ptr == 0)
+int q36::launch_attention_peer_merge(const float *part_o, const float *part_m, const float *part_l, uint32_t n_parts,
+                                     qwen36_device_ptr_t peer_inbox, qwen36_device_ptr_t peer_flags,
+                                     qwen36_device_ptr_t state, qwen36_device_ptr_t output_bf16, size_t world,
+                                     size_t rank, size_t q_heads, size_t head_dim) {
+  if (world == 0 || world > kMaxWorld || rank >= world || q_heads == 0 || head_dim == 0 || n_parts == 0 ||
+      n_parts > static_cast<uint32_t>(q36::kMergeThreads) || part_o == nullptr || part_m == nullptr ||
+      part_l == nullptr || peer_inbox.ptr == 0 || peer_flags.ptr == 0 || state.ptr == 0 || output_bf16.ptr == 0)
     return QWEN36_STATUS_INVALID_ARGUMENT;
   // programmatic stream serialisation: the CTAs take their seats while the kernel that writes the
   // partials is still running and wait for it on the device
   cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3(static_cast<unsigned>(spec->q_heads));
-  cfg.blockDim = dim3(256);
+  cfg.gridDim = dim3(static_cast<unsigned>(q_heads));
+  cfg.blockDim = dim3(q36::kMergeThreads);
   cfg.stream = q36::stream();
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -231,11 +245,19 @@ extern "C" int qwen36_attention_peer_merge(const qwen36_attention_peer_merge_spe
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   return q36::cuda_status(cudaLaunchKernelEx(
-      &cfg, attention_peer_merge_kernel, as_ptr<const float>(spec->partial_acc_f32),
-      as_ptr<const float>(spec->partial_max_f32), as_ptr<const float>(spec->partial_denom_f32),
-      as_ptr<float *const>(spec->peer_inbox), as_ptr<uint32_t *const>(spec->peer_flags), as_ptr<uint32_t>(spec->state),
-      as_ptr<__nv_bfloat16>(spec->output_bf16), static_cast<uint32_t>(spec->world), static_cast<uint32_t>(spec->rank),
-      static_cast<uint32_t>(spec->q_heads), static_cast<uint32_t>(spec->head_dim)));
+      &cfg, attention_peer_merge_kernel, part_o, part_m, part_l, n_parts, as_ptr<float *const>(peer_inbox),
+      as_ptr<uint32_t *const>(peer_flags), as_ptr<uint32_t>(state), as_ptr<__nv_bfloat16>(output_bf16),
+      static_cast<uint32_t>(world), static_cast<uint32_t>(rank), static_cast<uint32_t>(q_heads),
+      static_cast<uint32_t>(head_dim)));
+}
+
+extern "C" int qwen36_attention_peer_merge(const qwen36_attention_peer_merge_spec_t *spec) {
+  if (spec == nullptr) return QWEN36_STATUS_NULL_POINTER;
+  return q36::launch_attention_peer_merge(as_ptr<const float>(spec->partial_acc_f32),
+                                          as_ptr<const float>(spec->partial_max_f32),
+                                          as_ptr<const float>(spec->partial_denom_f32), 1, spec->peer_inbox,
+                                          spec->peer_flags, spec->state, spec->output_bf16, spec->world, spec->rank,
+                                          spec->q_heads, spec->head_dim);
 }
 
 extern "C" int qwen36_argmax_peer_combine(const qwen36_argmax_peer_combine_spec_t *spec) {

@@ -121,6 +121,20 @@ class AttentionPeerMerge:
         return out
 
 
+    def attend(self, q_bf16, kq, vq, meta, t_begin: int, t_end: int, workspace, out=None) -> torch.Tensor:
+        """Attention over rows [t_begin, t_end) of this rank's cache and the cross-rank merge, two
+        launches: qwen36_turboquant_attention_peer."""
+        if out is None:
+            out = torch.empty((self.q_heads, self.head_dim), dtype=torch.bfloat16, device=q_bf16.device)
+        shape = abi.AttentionShape(self.q_heads, kq.shape[1], self.head_dim, 0)
+        spec = abi.TurboquantAttentionPeerSpec(t_begin, t_end, _dp(q_bf16), _dp(kq), _dp(vq), _dp(meta),
+                                               _dp(workspace), workspace.numel(), shape, self.ex.world,
+                                               self.ex.rank, _dp(self.ex.inbox_table), _dp(self.ex.flag_table),
+                                               _dp(self.ex.state), _dp(out))
+        _check("turboquant_attention_peer", self.lib.qwen36_turboquant_attention_peer(C.byref(spec)))
+        return out
+
+
 class ArgmaxPeerCombine:
     """Cross-rank greedy argmax of per-rank (value, index) winners: qwen36_argmax_peer_combine.
     Every rank must pass the same number of tokens in a given call."""

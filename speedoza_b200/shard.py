@@ -136,17 +136,12 @@ class ShardedKvAttention:
             from .peer import AttentionPeerMerge
             dev = kq_local.device
             self.peer = AttentionPeerMerge(backend, q_heads, head_dim, dev)
-            self.part_o = torch.empty((q_heads, head_dim), dtype=torch.float32, device=dev)
-            self.part_m = torch.empty(q_heads, dtype=torch.float32, device=dev)
-            self.part_l = torch.empty(q_heads, dtype=torch.float32, device=dev)
             self.out = torch.empty((q_heads, head_dim), dtype=torch.bfloat16, device=dev)
 
     def attend(self, q_bf16, position: int):
         local_end = max(0, min(self.kq.shape[0], position + 1 - self.t_lo))
         if self.peer is not None:
-            self.b.turboquant_attention_partial(q_bf16, self.kq, self.vq, self.meta, 0, local_end, self.ws,
-                                                self.part_o, self.part_m, self.part_l)
-            return self.peer(self.part_m, self.part_l, self.part_o, self.out)
+            return self.peer.attend(q_bf16, self.kq, self.vq, self.meta, 0, local_end, self.ws, self.out)
         m, l, o = self.b.turboquant_attention_partial(q_bf16, self.kq, self.vq, self.meta, 0, local_end, self.ws)
         if self.world == 1:
             return self.b.attention_merge_partials(m[:, None].contiguous(), l[:, None].contiguous(),

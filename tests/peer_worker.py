@@ -34,6 +34,19 @@ def main():
         if call == 5:
             v[:] = 1.0                                          # ties across ranks
         assert torch.equal(pick(v, i).to(torch.int64), shard.gather_argmax(v, i, world)[1]), ("argmax", call)
+    # fused route: attention over this rank's rows + cross-rank merge in two launches
+    tokens = 3000 + 500 * rank
+    k = torch.randn((tokens, 4, dim), generator=gen, device="cuda").to(torch.bfloat16)
+    v = torch.randn((tokens, 4, dim), generator=gen, device="cuda").to(torch.bfloat16)
+    q = torch.randn((heads, dim), device="cuda", generator=torch.Generator(device="cuda").manual_seed(1)).to(torch.bfloat16)
+    kq = torch.empty((tokens, 4, dim), dtype=torch.int8, device="cuda"); vq = torch.empty_like(kq)
+    meta = torch.empty((tokens, 4, 2), dtype=torch.float32, device="cuda")
+    b.turboquant_encode_kv_rows(k, v, kq, vq, meta, 0)
+    ws = b.attention_workspace(heads, dim, "cuda")
+    for t_end in (tokens, 0 if rank == 1 else 77):
+        got = merge.attend(q, kq, vq, meta, 0, t_end, ws).clone()
+        pm, pl, po = shard.gather_partials(*b.turboquant_attention_partial(q, kq, vq, meta, 0, t_end, ws), world)
+        assert torch.equal(got, b.attention_merge_partials(pm, pl, po)), ("fused", t_end)
     # replayed graph: the call number advances on the device
     m = torch.randn(heads, generator=gen, device="cuda"); l = torch.rand(heads, generator=gen, device="cuda") + 1
     o = torch.randn((heads, dim), generator=gen, device="cuda")

@@ -136,6 +136,7 @@ def test_ctypes_mirrors_match_header_sizes(tmp_path):
              "qwen36_attention_merge_spec_t": abi.AttentionMergeSpec,
              "qwen36_attention_peer_merge_spec_t": abi.AttentionPeerMergeSpec,
              "qwen36_argmax_peer_combine_spec_t": abi.ArgmaxPeerCombineSpec,
+             "qwen36_turboquant_attention_peer_spec_t": abi.TurboquantAttentionPeerSpec,
              "qwen36_nvfp4_dequantize_spec_t": abi.Nvfp4DequantizeSpec,
              "qwen36_cuda_diagnostics_t": abi.CudaDiagnostics, "qwen36_cuda_counters_t": abi.CudaCounters}
     body = "\n".join(f'  printf("{n} %zu\\n", sizeof({n}));' for n in names)

@@ -55,6 +55,25 @@ def test_lone_rank_merge_is_the_local_merge_and_survives_many_calls(backend):
     pick.ex.close()
 
 
+@pytest.mark.parametrize("tokens", [1, 300, 5000])
+def test_lone_rank_fused_attention_equals_the_single_gpu_call(backend, tokens):
+    from speedoza_b200.peer import AttentionPeerMerge
+    gen = torch.Generator(device="cuda").manual_seed(tokens)
+    k = torch.randn((tokens, 4, 256), generator=gen, device="cuda").to(torch.bfloat16)
+    v = torch.randn((tokens, 4, 256), generator=gen, device="cuda").to(torch.bfloat16)
+    q = torch.randn((24, 256), generator=gen, device="cuda").to(torch.bfloat16)
+    kq = torch.empty((tokens, 4, 256), dtype=torch.int8, device="cuda"); vq = torch.empty_like(kq)
+    meta = torch.empty((tokens, 4, 2), dtype=torch.float32, device="cuda")
+    backend.turboquant_encode_kv_rows(k, v, kq, vq, meta, 0)
+    ws = backend.attention_workspace(24, 256, "cuda")
+    merge = AttentionPeerMerge(backend, 24, 256, "cuda")
+    for _ in range(3):
+        got = merge.attend(q, kq, vq, meta, 0, tokens, ws)
+        assert torch.equal(got, backend.turboquant_attention(q, kq, vq, meta, tokens - 1, ws))
+    assert not merge.ex.failed()
+    merge.ex.close()
+
+
 @pytest.mark.parametrize("world,rank", [(2, 0), (2, 1), (8, 3)])
 def test_merge_with_host_played_peers_equals_merge_partials(backend, world, rank):
     heads, dim = 24, 256
