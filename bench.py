@@ -420,6 +420,36 @@ def other_configs(backend, torch, synth):
         byts = ctx * (2 * 4 * 256 + 4 * 2 * 4) + 24 * 256 * 4
         att.append({"ctx": ctx, "us": round(us, 2), "gbs": round(byts / us / 1e3, 1)})
     out["int8_kv_attention"] = att
+    # ---- the same decode step over the FP8 (E4M3) and BF16 caches of qwen36_attention_decode:
+    # ctx - 1 cached rows + the new row, cache append included; small contexts rotate over
+    # slices of a 131072-row cache so that every call reads cold rows (>= 268 MB per round)
+    del k_, v_
+    dec = {}
+    kn = torch.randn((4, 256), generator=gen, device="cuda").to(torch.bfloat16)
+    parts = (torch.empty((24, 256, 256), device="cuda"), torch.empty((24, 256), device="cuda"),
+             torch.empty((24, 256), device="cuda"))
+    for name, code, width in (("fp8", 1, 1), ("bf16", 0, 2)):
+        if code == 1:
+            ck = torch.randint(0, 0x78, (T, 4, 256), generator=gen, dtype=torch.uint8, device="cuda")
+            ck |= torch.randint(0, 2, (T, 4, 256), generator=gen, dtype=torch.uint8, device="cuda") << 7
+            ck = (ck & 0xBF) | 0x20                                  # exponents 4..7: magnitudes 2^-3 .. 1.9
+            cv = ck.flip(0).contiguous()
+        else:
+            ck = torch.randn((T, 4, 256), generator=gen, device="cuda").to(torch.bfloat16)
+            cv = torch.randn((T, 4, 256), generator=gen, device="cuda").to(torch.bfloat16)
+        rows_ = []
+        for ctx in (8192, 32768, 131072):
+            nsl = T // ctx
+            def call(i, ctx=ctx, nsl=nsl, ck=ck, cv=cv, code=code):
+                s0 = (i % nsl) * ctx
+                backend.attention_decode(q_, kn, kn, ck[s0:s0 + ctx], cv[s0:s0 + ctx], ctx - 1, code, parts, 256,
+                                         out=o_)
+            us = _time_cuda(torch, call, 32, backend=backend)
+            byts = (ctx - 1) * 2 * 4 * 256 * width + 2 * 24 * 256 * 2 + 4 * 4 * 256 * 2
+            rows_.append({"ctx": ctx, "us": round(us, 2), "gbs": round(byts / us / 1e3, 1)})
+        dec[name] = rows_
+        del ck, cv
+    out["kv_decode_attention"] = dec
     out["int8_kv_encode"] = {"tokens": T, "us": round(enc_us, 1), "gbs": round(enc_bytes / enc_us / 1e3, 1)}
     return out
 
@@ -427,7 +457,7 @@ def other_configs(backend, torch, synth):
 def profile_case(name: str):
     """Runs one small, fixed case of a single kernel a few times (for `ncu -k ... -c ...`):
     gemv_gate_up | gemv_down | gemm_gate_up_2048 | gemm_down_2048 | lm_head_m1 | lm_head_m4 |
-    attention_32768 | quantize_2048 | bf16_argmax_m1 | bf16_argmax_m4.  Inputs exceed L2 but stay well under a few GB."""
+    attention_32768 | quantize_2048 | bf16_argmax_m1 | bf16_argmax_m4 | decode_fp8_32768 | decode_bf16_32768.  Inputs exceed L2 but stay well under a few GB."""
     import torch
     from speedoza_b200 import synth
     from speedoza_b200.backend import CudaBackend
@@ -477,6 +507,22 @@ def profile_case(name: str):
         ws = b.attention_workspace(24, 256, "cuda")
         for _ in range(3):
             b.turboquant_attention(q_, kq, vq, meta, ctx - 1, ws)
+    elif name.startswith("decode_fp8_") or name.startswith("decode_bf16_"):
+        ctx = int(name.rsplit("_", 1)[1])
+        fp8 = name.startswith("decode_fp8_")
+        caches = []
+        for _ in range(3):                                          # three caches in turn: every launch reads cold rows
+            if fp8:
+                c = torch.randint(0x20, 0x40, (ctx, 4, 256), generator=gen, dtype=torch.uint8, device="cuda")
+            else:
+                c = torch.randn((ctx, 4, 256), generator=gen, device="cuda").to(torch.bfloat16)
+            caches.append(c)
+        q_ = torch.randn((24, 256), generator=gen, device="cuda").to(torch.bfloat16)
+        kn = torch.randn((4, 256), generator=gen, device="cuda").to(torch.bfloat16)
+        parts = (torch.empty((24, 256, 256), device="cuda"), torch.empty((24, 256), device="cuda"),
+                 torch.empty((24, 256), device="cuda"))
+        for i in range(3):
+            b.attention_decode(q_, kn, kn, caches[i], caches[(i + 1) % 3], ctx - 1, 1 if fp8 else 0, parts, 256)
     elif name.startswith("bf16_argmax_m"):
         m_tok = int(name.rsplit("m", 1)[1])
         rows, cols = synth.VOCAB, synth.HIDDEN

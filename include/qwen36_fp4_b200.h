@@ -315,6 +315,38 @@ int qwen36_turboquant_encode_kv(const qwen36_turboquant_encode_spec_t *spec);
  * INVALID_ARGUMENT when it is missing or too small.  `mode` is ignored. */
 int qwen36_turboquant_attention(const qwen36_turboquant_attention_spec_t *spec);
 
+/* ---- decode attention over a BF16 / FP8 (E4M3) KV cache --------------------- */
+
+typedef struct {                         /* qwen36_fp4.h:151-183 */
+  size_t layer_index, position;
+  qwen36_device_ptr_t q_bf16, k_bf16, v_bf16, kv_cache_k, kv_cache_v, kv_cache_metadata, output_bf16;
+  qwen36_attention_shape_t shape;
+  int kv_cache_dtype;                    /* 0 = BF16, 1 = FP8 E4M3, 2 / 3 = TurboQuant3 / 3.5 */
+  qwen36_device_ptr_t position_device_i32;
+  qwen36_device_ptr_t partial_acc_f32, partial_max_f32, partial_denom_f32;
+  size_t decode_n_splits, split_timesteps_per_block;
+} qwen36_attention_decode_spec_t;
+
+/* Replaces qwen36_attention_decode (kernels-cuda/attention.cu:2716-2876 and the
+ * kernels it launches: attention.cu:842-1000, 1036-1223, 1225-1471, 1473-1554,
+ * attention_decode_tiled.cu:159-357) for kv_cache_dtype 0 and 1: one query token
+ * attends to cache rows [0, position) plus the new k_bf16 / v_bf16 row, and that
+ * row is appended to the cache at `position` (copied for BF16; for FP8 encoded
+ * with the reference's round-half-up E4M3 encoder, attention.cu:118-160).  The
+ * position comes from position_device_i32 when that is non-zero.  With the three
+ * partial buffers and decode_n_splits >= 2 the cached rows are split across up
+ * to decode_n_splits CTAs per head (the buffers are laid out as the reference
+ * says: [q_heads, decode_n_splits, head_dim] and 2 x [q_heads, decode_n_splits]);
+ * how many of them are used and which rows each one takes is this library's
+ * choice, so split_timesteps_per_block is only validated (>= 64 or 0).  Without
+ * the buffers one CTA per q head walks the whole context.  TurboQuant3 / 3.5
+ * caches (dtype 2 / 3) return QWEN36_STATUS_NOT_IMPLEMENTED. */
+int qwen36_attention_decode(const qwen36_attention_decode_spec_t *spec);
+/* Test hooks: mode 0 = general kernel only, 1 = tensor-core form where it applies
+ * (default); n > 0 overrides the number of splits used. */
+void qwen36_attention_decode_set_mode(int mode);
+void qwen36_attention_decode_force_splits(int n);
+
 /* ---- additions of this build (no ABI change to anything above) ------------ */
 
 /* Scratch needed by qwen36_turboquant_attention / _partial for a shape. */
@@ -529,7 +561,6 @@ int qwen36_bf16_matvec(const void *spec);
 int qwen36_attention_prefill(const void *spec);
 int qwen36_attention_flash_prefill(const void *spec);
 int qwen36_attention_sage_prefill(const void *spec);
-int qwen36_attention_decode(const void *spec);
 int qwen36_attention_decode_split_tiled(const void *spec, int a, int b);
 int qwen36_attention_flash_splitk_prefill_bf16(const void *spec, int n_splits);
 int qwen36_deltanet_decode(const void *spec);

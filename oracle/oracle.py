@@ -58,6 +58,10 @@ def lib() -> C.CDLL:
         L.orc_sf_bytes.argtypes = [_sz, _sz]
         L.orc_nvfp4_count_e2m1_ties.restype = _sz
         L.orc_num_threads.restype = C.c_int
+        L.orc_kv_e4m3_decode.restype = C.c_float
+        L.orc_kv_e4m3_decode.argtypes = [C.c_uint8]
+        L.orc_kv_e4m3_encode.restype = C.c_uint8
+        L.orc_kv_e4m3_encode.argtypes = [C.c_float]
     return _lib
 
 
@@ -324,6 +328,31 @@ def merge_partials(part_m: np.ndarray, part_l: np.ndarray, part_o: np.ndarray) -
                              _p(np.ascontiguousarray(part_l, dtype=np.float32), _f32p),
                              _p(np.ascontiguousarray(part_o, dtype=np.float32), _f32p),
                              _sz(q_heads), _sz(n_parts), _sz(head_dim), _p(out, _u16p))
+    return out
+
+
+def kv_e4m3_decode(code: int) -> float:
+    return float(lib().orc_kv_e4m3_decode(code))
+
+
+def kv_e4m3_encode(v: float) -> int:
+    return int(lib().orc_kv_e4m3_encode(float(v)))
+
+
+def attention_decode(q_bf16: np.ndarray, k_new: np.ndarray, v_new: np.ndarray, cache_k: np.ndarray,
+                     cache_v: np.ndarray, kv_cache_dtype: int, position: int) -> np.ndarray:
+    """q [q_heads, head_dim], k_new / v_new [kv_heads, head_dim] bf16 bits; caches
+    [>= position + 1, kv_heads, head_dim] of uint16 (BF16, dtype 0) or uint8 (E4M3, dtype 1).
+    Returns bf16 [q_heads, head_dim] and writes cache row `position` in place."""
+    q_heads, head_dim = q_bf16.shape
+    kv_heads = k_new.shape[0]
+    assert cache_k.dtype == (np.uint8 if kv_cache_dtype == 1 else np.uint16) and cache_k.flags.c_contiguous
+    assert cache_v.dtype == cache_k.dtype and cache_v.flags.c_contiguous and cache_k.shape[0] > position
+    out = np.empty((q_heads, head_dim), dtype=np.uint16)
+    lib().orc_attention_decode(_p(q_bf16, _u16p), _p(k_new, _u16p), _p(v_new, _u16p),
+                               cache_k.ctypes.data_as(C.c_void_p), cache_v.ctypes.data_as(C.c_void_p),
+                               C.c_int(kv_cache_dtype), _sz(position), _sz(q_heads), _sz(kv_heads),
+                               _sz(head_dim), _p(out, _u16p))
     return out
 
 

@@ -149,6 +149,15 @@ class TurboquantAttentionSpec(C.Structure):
                 ("workspace_bytes", size_t), ("shape", AttentionShape), ("mode", C.c_int)]
 
 
+class AttentionDecodeSpec(C.Structure):
+    _fields_ = [("layer_index", size_t), ("position", size_t), ("q_bf16", DevicePtr), ("k_bf16", DevicePtr),
+                ("v_bf16", DevicePtr), ("kv_cache_k", DevicePtr), ("kv_cache_v", DevicePtr),
+                ("kv_cache_metadata", DevicePtr), ("output_bf16", DevicePtr), ("shape", AttentionShape),
+                ("kv_cache_dtype", C.c_int), ("position_device_i32", DevicePtr),
+                ("partial_acc_f32", DevicePtr), ("partial_max_f32", DevicePtr), ("partial_denom_f32", DevicePtr),
+                ("decode_n_splits", size_t), ("split_timesteps_per_block", size_t)]
+
+
 class TurboquantAttentionPartialSpec(C.Structure):
     _fields_ = [("t_begin", size_t), ("t_end", size_t), ("q_bf16", DevicePtr),
                 ("k_quantized_i8", DevicePtr), ("v_quantized_i8", DevicePtr),
@@ -270,6 +279,10 @@ def load() -> C.CDLL:
     lib.qwen36_attention_peer_inbox_bytes.argtypes = [size_t, size_t, size_t]
     lib.qwen36_argmax_peer_inbox_bytes.restype = size_t
     lib.qwen36_argmax_peer_inbox_bytes.argtypes = [size_t, size_t]
+    lib.qwen36_attention_decode_set_mode.restype = None
+    lib.qwen36_attention_decode_set_mode.argtypes = [C.c_int]
+    lib.qwen36_attention_decode_force_splits.restype = None
+    lib.qwen36_attention_decode_force_splits.argtypes = [C.c_int]
     lib.qwen36_nvfp4_chunk_gemv_set_mtile.restype = None
     lib.qwen36_nvfp4_matvec_force_quads.restype = None
     lib.qwen36_nvfp4_gemm_force_bn.restype = None

@@ -288,6 +288,25 @@ class CudaBackend:
         _check("turboquant_attention", self.lib.qwen36_turboquant_attention(C.byref(spec)))
         return out
 
+    def attention_decode(self, q_bf16, k_new, v_new, cache_k, cache_v, position: int, kv_cache_dtype: int,
+                         partials=None, decode_n_splits: int = 0, position_device=None, out=None,
+                         split_timesteps_per_block: int = 0) -> torch.Tensor:
+        """Decode attention over a BF16 (dtype 0) or FP8 E4M3 (dtype 1) cache, with the reference's
+        side effect: k_new / v_new are appended to cache row `position`.  `partials` is the
+        (acc [q_heads, n, head_dim], max [q_heads, n], denom [q_heads, n]) float32 triple of the
+        reference's split path, n = decode_n_splits."""
+        q_heads, head_dim = q_bf16.shape
+        kv_heads = k_new.shape[0]
+        if out is None:
+            out = torch.empty((q_heads, head_dim), dtype=torch.bfloat16, device=q_bf16.device)
+        shape = abi.AttentionShape(q_heads, kv_heads, head_dim, 0)
+        pa, pm, pl = partials if partials is not None else (None, None, None)
+        spec = abi.AttentionDecodeSpec(0, position, _dp(q_bf16), _dp(k_new), _dp(v_new), _dp(cache_k), _dp(cache_v),
+                                       DevicePtr(0), _dp(out), shape, kv_cache_dtype, _dp(position_device),
+                                       _dp(pa), _dp(pm), _dp(pl), decode_n_splits, split_timesteps_per_block)
+        _check("attention_decode", self.lib.qwen36_attention_decode(C.byref(spec)))
+        return out
+
     def turboquant_attention_static(self, q_bf16, kq, vq, meta, position: int, out=None) -> torch.Tensor:
         """Same result as turboquant_attention, but the split-KV partials live in a fixed buffer
         inside the library, so no scratch is passed and nothing is allocated by the call."""

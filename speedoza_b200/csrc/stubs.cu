@@ -12,7 +12,6 @@ Q36_STUB(qwen36_bf16_matvec)
 Q36_STUB(qwen36_attention_prefill)
 Q36_STUB(qwen36_attention_flash_prefill)
 Q36_STUB(qwen36_attention_sage_prefill)
-Q36_STUB(qwen36_attention_decode)
 Q36_STUB(qwen36_deltanet_decode)
 Q36_STUB(qwen36_deltanet_prefill)
 Q36_STUB(qwen36_interpreter_decode_sm120)

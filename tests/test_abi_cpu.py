@@ -94,6 +94,11 @@ def test_struct_layouts_equal_reference_header(tmp_path):
         "qwen36_turboquant_attention_spec_t": ["layer_index", "position", "q_bf16", "k_quantized_i8",
                                                "v_quantized_i8", "metadata_f32", "output_bf16", "workspace",
                                                "workspace_bytes", "shape", "mode"],
+        "qwen36_attention_decode_spec_t": ["layer_index", "position", "q_bf16", "k_bf16", "v_bf16", "kv_cache_k",
+                                           "kv_cache_v", "kv_cache_metadata", "output_bf16", "shape",
+                                           "kv_cache_dtype", "position_device_i32", "partial_acc_f32",
+                                           "partial_max_f32", "partial_denom_f32", "decode_n_splits",
+                                           "split_timesteps_per_block"],
         "qwen36_attention_shape_t": ["q_heads", "kv_heads", "head_dim", "rope_dims"],
         "qwen36_cuda_counters_t": ["malloc_calls", "graph_launch_calls"],
         "qwen36_cuda_diagnostics_t": ["driver_version", "total_global_mem", "device_name", "last_cuda_error_string"],
@@ -132,6 +137,7 @@ def test_ctypes_mirrors_match_header_sizes(tmp_path):
              "qwen36_turboquant_encode_spec_t": abi.TurboquantEncodeSpec,
              "qwen36_turboquant_encode_rows_spec_t": abi.TurboquantEncodeRowsSpec,
              "qwen36_turboquant_attention_spec_t": abi.TurboquantAttentionSpec,
+             "qwen36_attention_decode_spec_t": abi.AttentionDecodeSpec,
              "qwen36_turboquant_attention_partial_spec_t": abi.TurboquantAttentionPartialSpec,
              "qwen36_attention_merge_spec_t": abi.AttentionMergeSpec,
              "qwen36_attention_peer_merge_spec_t": abi.AttentionPeerMergeSpec,

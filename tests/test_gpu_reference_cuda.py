@@ -178,3 +178,39 @@ def test_swiglu_nvfp4_quantize_equals_reference_bitwise(ref, backend, n, its):
         outs.append([t.cpu().numpy() for t in (fp4, sf, ts)])
     for a, b in zip(*outs):
         assert np.array_equal(a, b)
+
+
+@pytest.mark.parametrize("dtype", [0, 1])
+@pytest.mark.parametrize("position,n_splits", [(0, 0), (37, 0), (700, 0), (2100, 8), (5000, 64)])
+def test_reference_attention_decode_equals_oracle_and_this_library(ref, backend, dtype, position, n_splits):
+    """qwen36_attention_decode over a BF16 / FP8 cache: the reference's kernels (its one-block-per-head
+    kernel without partial buffers, its GQA split / register-tiled kernels with them), the oracle and
+    this library on the same inputs.  Outputs within rel-L2 1e-2 of the oracle; the cache after the
+    call (append side effect) is byte-identical in all three."""
+    from test_gpu_kv_decode import make_case, cache_to_dev, cache_host, partial_buffers, rel_l2
+    q, k_new, v_new, ck, cv = make_case(900 + position + dtype, position + 1, 24, 4, 256, dtype)
+    qd, kd, vd = to_dev(q), to_dev(k_new), to_dev(v_new)
+    ck_o, cv_o = ck.copy(), cv.copy()
+    want = synth.bf16_bits_to_f32(orc.attention_decode(q, k_new, v_new, ck_o, cv_o, dtype, position))
+
+    ck_r, cv_r = cache_to_dev(ck), cache_to_dev(cv)
+    out_r = torch.zeros((24, 256), dtype=torch.bfloat16, device="cuda")
+    parts = partial_buffers(24, n_splits, 256) if n_splits else (None, None, None)
+    spec = abi.AttentionDecodeSpec(0, position, dp(qd), dp(kd), dp(vd), dp(ck_r), dp(cv_r), dp(None), dp(out_r),
+                                   abi.AttentionShape(24, 4, 256, 0), dtype, dp(None), dp(parts[0]), dp(parts[1]),
+                                   dp(parts[2]), n_splits, 0)
+    torch.cuda.synchronize()
+    assert ref.qwen36_attention_decode(C.byref(spec)) == 0
+    torch.cuda.synchronize()
+    assert rel_l2(synth.bf16_bits_to_f32(bf16_host(out_r)), want) <= 1e-2
+    assert np.array_equal(cache_host(ck_r), ck_o) and np.array_equal(cache_host(cv_r), cv_o)
+
+    ck_m, cv_m = cache_to_dev(ck), cache_to_dev(cv)
+    out_m = backend.attention_decode(qd, kd, vd, ck_m, cv_m, position, dtype,
+                                     partial_buffers(24, n_splits, 256) if n_splits else None, n_splits)
+    torch.cuda.synchronize()
+    assert rel_l2(synth.bf16_bits_to_f32(bf16_host(out_m)), want) <= 1e-2
+    assert torch.equal(ck_m, ck_r) and torch.equal(cv_m, cv_r)
+    # the two GPU implementations against each other
+    assert rel_l2(synth.bf16_bits_to_f32(bf16_host(out_m)),
+                  synth.bf16_bits_to_f32(bf16_host(out_r)).astype(np.float64)) <= 1e-2

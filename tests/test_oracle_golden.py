@@ -307,3 +307,73 @@ def test_top8_rescore_and_bf16_argmax_small():
     skip = np.array([0, 1, 0], dtype=np.uint32)
     kept = orc.bf16_matvec_argmax_rows(x, w, skip, np.array([11, 22, 33], dtype=np.uint32))
     assert kept[1] == 22 and kept[0] == full[0] and kept[2] == full[2]
+
+
+def _e4m3_magnitudes():
+    """The 127 finite E4M3 magnitudes by the format's definition (code 0x7F excluded)."""
+    mags = []
+    for code in range(0x7F):
+        e, m = code >> 3, code & 7
+        mags.append(m * 2.0 ** -9 if e == 0 else (1 + m / 8) * 2.0 ** (e - 7))
+    return np.array(mags, np.float64)
+
+
+def test_kv_cache_e4m3_codec_all_values():
+    """The FP8 KV cache codec (kernels-cuda/attention.cu:101-160) against the format's definition:
+    decode of all 256 bytes (0x7F / 0xFF read as +-448), and the append's encoder on every bf16 bit
+    pattern: nearest magnitude with ties going UP, saturation at 0x7E, zero and non-finite -> 0."""
+    mags = _e4m3_magnitudes()
+    for code in range(256):
+        want = 448.0 if (code & 0x7F) == 0x7F else mags[code & 0x7F]
+        got = orc.kv_e4m3_decode(code)
+        assert got == (-want if code & 0x80 else want), code
+    bits = np.arange(65536, dtype=np.uint16)
+    vals = synth.bf16_bits_to_f32(bits)
+    mids = (mags[:-1] + mags[1:]) / 2
+    for b, v in zip(bits.tolist(), vals.tolist()):
+        got = orc.kv_e4m3_encode(v)
+        if v == 0 or not np.isfinite(v):
+            want = 0
+        else:
+            a = abs(v)
+            idx = 0x7E if a >= 448 else int(np.searchsorted(mids, a, side="right"))   # a == midpoint -> upper code
+            want = (0x80 if v < 0 else 0) | idx
+        assert got == want, (hex(b), v, got, want)
+
+
+def _decode_case(position, q_val, k_val, v_val, ck_val, cv_val, fp8=False):
+    """The reference's smoke shape (kernels-cuda/smoke.cu:508-532): 2 q heads, 1 kv head, 8 dims."""
+    q = synth.f32_to_bf16_bits(np.full((2, 8), q_val, np.float32))
+    k = synth.f32_to_bf16_bits(np.full((1, 8), k_val, np.float32))
+    v = synth.f32_to_bf16_bits(np.full((1, 8), v_val, np.float32))
+    if fp8:
+        ck = np.full((position + 1, 1, 8), orc.kv_e4m3_encode(ck_val), np.uint8)
+        cv = np.full((position + 1, 1, 8), orc.kv_e4m3_encode(cv_val), np.uint8)
+    else:
+        ck = synth.f32_to_bf16_bits(np.full((position + 1, 1, 8), ck_val, np.float32))
+        cv = synth.f32_to_bf16_bits(np.full((position + 1, 1, 8), cv_val, np.float32))
+    return q, k, v, ck, cv
+
+
+def test_attention_decode_known_answers():
+    # kernels-cuda/smoke.cu:519-532: position 0 -> the output is v_new and row 0 of the cache is k / v
+    q, k, v, ck, cv = _decode_case(0, 0.25, 0.5, 1.0, 0.0, 0.0)
+    out = synth.bf16_bits_to_f32(orc.attention_decode(q, k, v, ck, cv, 0, 0))
+    assert np.all(out == 1.0) and np.array_equal(ck[0], k) and np.array_equal(cv[0], v)
+    # kernels-cuda/smoke.cu:619-650: 513 cached rows of K = 0.5, V = 1.0 -> 1.0 +- 0.02
+    q, k, v, ck, cv = _decode_case(513, 0.25, 0.5, 1.0, 0.5, 1.0)
+    out = synth.bf16_bits_to_f32(orc.attention_decode(q, k, v, ck, cv, 0, 513))
+    assert np.all(np.abs(out - 1.0) <= 0.02)
+    # kernels-cuda/smoke.cu:546-566: one cached row (K 0.25, V 0.75) + the new row (0.5, 1.0)
+    for fp8 in (False, True):
+        q, k, v, ck, cv = _decode_case(1, 0.25, 0.5, 1.0, 0.25, 0.75, fp8)
+        before = ck[0].copy()
+        out = synth.bf16_bits_to_f32(orc.attention_decode(q, k, v, ck, cv, int(fp8), 1))
+        s_old, s_new = 8 * 0.25 * 0.25 / np.sqrt(8), 8 * 0.25 * 0.5 / np.sqrt(8)
+        want = (np.exp(s_old) * 0.75 + np.exp(s_new) * 1.0) / (np.exp(s_old) + np.exp(s_new))
+        assert np.all(np.abs(out - want) <= 4e-3)
+        assert np.array_equal(ck[0], before)
+        if fp8:
+            assert np.all(ck[1] == 0x30) and np.all(cv[1] == 0x38)      # 0.5 and 1.0 in E4M3
+        else:
+            assert np.array_equal(ck[1], k) and np.array_equal(cv[1], v)
