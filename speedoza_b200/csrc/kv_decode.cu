@@ -22,6 +22,8 @@
 
 #include <math.h>
 
+#include <mutex>
+
 #include "lse_merge.cuh"
 
 namespace {
@@ -35,7 +37,7 @@ constexpr int kMaxSplits = 256;              // the merge handles one partial pe
 constexpr uint32_t kMinTokensPerSplit = 256;
 constexpr int kKvBf16 = 0, kKvFp8 = 1;
 
-int g_decode_mode = 1;                       // test hook: 0 = general kernel only, 1 = tensor-core forms where they apply
+int g_decode_mode = 2;                       // test hook: 0 = general kernel only, 1 = tensor-core forms fed from registers, 2 = FP8 fed through shared memory
 int g_decode_force_splits = 0;               // test hook: > 0 overrides the split count
 
 // E4M3 byte -> float as the reference reads its cache (attention.cu:101-116): 0x7F / 0xFF are +-448.
@@ -556,6 +558,247 @@ decode_split_fp8_mma_kernel(const __nv_bfloat16 *__restrict__ q, const uint8_t *
   split_epilogue<G>(o, m_run, l_run, 1.0f / kPScale, s_m, s_l, s_o, part_o, part_m, part_l, head0, split, n_splits);
 }
 
+// ---- FP8 cache, staged form: the same two products, but K / V travel global -> shared memory
+// with 16-byte asynchronous copies (cp.async) into a private three-stage ring per warp, so the
+// bytes in flight (two stages = 16 KB per warp, 128 KB per SM) no longer have to fit in
+// registers.  A stage holds the K and the V rows of a 16-token group (256 bytes each); 16-byte
+// chunks are XOR-swizzled on the way in so that the fragment reads are free of bank conflicts:
+// K chunk c of row r sits at c ^ 4 (r & 1), V chunk c of row r at c ^ 2 ((r / 2) & 3).  No block
+// barrier inside the loop: a warp waits for its own copies (wait_group + __syncwarp).
+// The 0x7F / 0xFF bytes (which the cache append never writes) are handled out of line: the fast
+// pass converts bytes as they are; a NaN anywhere in the CTA's result sends the CTA through a
+// second pass that rewrites those bytes first (template flag FIX).
+constexpr int kStages = 3;
+constexpr uint32_t kTileBytes = 16 * 256;                         // 16 tokens x 256 bytes
+constexpr uint32_t kStageBytes = 2 * kTileBytes;                  // K tile + V tile
+constexpr uint32_t kRingBytes = kWarps * kStages * kStageBytes;   // 192 KB
+constexpr uint32_t kStagedSmemBytes = kRingBytes + 16 * 32 * 8 + 2 * kWarps * 8 * 4;
+
+__device__ __forceinline__ void cp_async_16(uint32_t dst_smem, const void *src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst_smem), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+
+template <int G, bool FIX>
+__device__ __forceinline__ void fp8_staged_pass(float (&o)[2][8][4], float &m_run, float &l_run,
+                                                const uint8_t *__restrict__ cache_k,
+                                                const uint8_t *__restrict__ cache_v, uint32_t ring /* this warp's */,
+                                                const uint2 (*s_q)[32], size_t s_begin, size_t s_end,
+                                                uint32_t kv_heads, uint32_t kvh) {
+  constexpr uint32_t D = 256;
+  constexpr float kPScale = 64.0f;
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+  const uint32_t g = lane >> 2, t = lane & 3u;
+  const float sm_scale = 0.0625f * 1.4426950408889634f;           // rsqrt(256) * log2(e)
+#pragma unroll
+  for (int h = 0; h < 2; ++h)
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) o[h][j][c] = 0.f;
+  m_run = -INFINITY;
+  l_run = 0.f;
+  const size_t stride = static_cast<size_t>(kWarps) * 16;
+  size_t t0 = s_begin + static_cast<size_t>(warp) * 16;
+  if (t0 >= s_end) return;
+
+  // one stage: lane copies chunk (lane & 15) of rows (lane >> 4) + 2 r, r = 0 .. 7, of K and of V;
+  // rows past the end of the split are zero-filled (source size 0, address kept inside the cache)
+  const uint32_t chunk = lane & 15u, row0 = lane >> 4;
+  auto issue = [&](uint32_t stage, size_t tg) {
+    const uint32_t base = ring + stage * kStageBytes;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      const uint32_t row = row0 + 2u * r;
+      const size_t tok = tg + row;
+      const bool valid = tok < s_end;
+      const size_t off = ((valid ? tok : s_begin) * kv_heads + kvh) * D + chunk * 16u;
+      const uint32_t bytes = valid ? 16u : 0u;
+      cp_async_16(base + row * 256u + ((chunk ^ ((row & 1u) << 2)) << 4), cache_k + off, bytes);
+      cp_async_16(base + kTileBytes + row * 256u + ((chunk ^ (((row >> 1) & 3u) << 1)) << 4), cache_v + off, bytes);
+    }
+    cp_async_commit();
+  };
+#pragma unroll
+  for (int s = 0; s < kStages - 1; ++s) issue(s, t0 + s * stride);
+
+  uint32_t stage = 0;
+  for (; t0 < s_end; t0 += stride) {
+    issue(stage == 0 ? kStages - 1 : stage - 1, t0 + (kStages - 1) * stride);   // refill the stage read last time
+    cp_async_wait<kStages - 1>();
+    __syncwarp();
+    const uint32_t kt = ring + stage * kStageBytes, vt = kt + kTileBytes;
+    // ---- S = Q K^T
+    float sc_[4];
+    {
+      float acc[2][2][4];
+#pragma unroll
+      for (int blk = 0; blk < 2; ++blk)
+#pragma unroll
+        for (int par = 0; par < 2; ++par)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) acc[blk][par][c] = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t w[2][4];
+#pragma unroll
+        for (int blk = 0; blk < 2; ++blk) {
+          uint4 kw = lds128(kt + (8u * blk + g) * 256u + (((t + 4u * j) ^ ((g & 1u) << 2)) << 4));
+          if (FIX) kw = e4m3_nan_to_448(kw);
+          w[blk][0] = kw.x; w[blk][1] = kw.y; w[blk][2] = kw.z; w[blk][3] = kw.w;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint2 qf = s_q[4 * j + i][lane];
+#pragma unroll
+          for (int blk = 0; blk < 2; ++blk) {
+            uint32_t b0, b1;
+            e4m3x4_to_h2x2(w[blk][i], b0, b1);
+            mma_f16(acc[blk][i & 1], qf.x, 0u, qf.y, 0u, b0, b1);
+          }
+        }
+      }
+#pragma unroll
+      for (int blk = 0; blk < 2; ++blk) {
+        sc_[2 * blk] = acc[blk][0][0] + acc[blk][1][0];
+        sc_[2 * blk + 1] = acc[blk][0][1] + acc[blk][1][1];
+      }
+    }
+    // ---- online softmax, head g
+    float s_log2[4];
+    float tile_max = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const size_t tok = t0 + 2 * t + (i & 1) + 8 * (i >> 1);
+      const bool valid = g < G && tok < s_end;
+      s_log2[i] = valid ? sc_[i] * sm_scale : -INFINITY;
+      tile_max = fmaxf(tile_max, s_log2[i]);
+    }
+    tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 1));
+    tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 2));
+    const float m_new = fmaxf(m_run, tile_max);
+    const float corr = m_new == -INFINITY ? 1.f : exp2f(m_run - m_new);
+    float p[4], p_sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      p[i] = s_log2[i] == -INFINITY ? 0.f : exp2f(s_log2[i] - m_new);
+      p_sum += p[i];
+    }
+    p_sum += __shfl_xor_sync(0xffffffffu, p_sum, 1);
+    p_sum += __shfl_xor_sync(0xffffffffu, p_sum, 2);
+    l_run = l_run * corr + p_sum;
+    m_run = m_new;
+    const __half2 pb0 = __floats2half2_rn(p[0] * kPScale, p[1] * kPScale);
+    const __half2 pb1 = __floats2half2_rn(p[2] * kPScale, p[3] * kPScale);
+    const uint32_t b0 = *reinterpret_cast<const uint32_t *>(&pb0), b1 = *reinterpret_cast<const uint32_t *>(&pb1);
+    const float c_even = __shfl_sync(0xffffffffu, corr, 8 * t), c_odd = __shfl_sync(0xffffffffu, corr, 8 * t + 4);
+    if (__any_sync(0xffffffffu, corr != 1.f)) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          o[h][j][0] *= c_even; o[h][j][1] *= c_odd; o[h][j][2] *= c_even; o[h][j][3] *= c_odd;
+        }
+    }
+    // ---- O^T += V^T P^T: rows 2t, 2t + 1, 2t + 8, 2t + 9 of the V tile, chunk g + 8 h
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      uint4 x[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        x[i] = lds128(vt + (2u * t + (i & 1) + 8u * (i >> 1)) * 256u + (((g + 8u * h) ^ (t << 1)) << 4));
+        if (FIX) x[i] = e4m3_nan_to_448(x[i]);
+      }
+      const uint32_t va[4] = {x[0].x, x[0].y, x[0].z, x[0].w}, vb[4] = {x[1].x, x[1].y, x[1].z, x[1].w};
+      const uint32_t vc[4] = {x[2].x, x[2].y, x[2].z, x[2].w}, vd[4] = {x[3].x, x[3].y, x[3].z, x[3].w};
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        uint32_t ab0, ab1, ab2, ab3, cd0, cd1, cd2, cd3;
+        e4m3x4_to_h2x2(__byte_perm(va[w], vb[w], 0x5140), ab0, ab1);
+        e4m3x4_to_h2x2(__byte_perm(va[w], vb[w], 0x7362), ab2, ab3);
+        e4m3x4_to_h2x2(__byte_perm(vc[w], vd[w], 0x5140), cd0, cd1);
+        e4m3x4_to_h2x2(__byte_perm(vc[w], vd[w], 0x7362), cd2, cd3);
+        mma_f16(o[h][2 * w], ab0, ab1, cd0, cd1, b0, b1);
+        mma_f16(o[h][2 * w + 1], ab2, ab3, cd2, cd3, b0, b1);
+      }
+    }
+    __syncwarp();                                    // every lane is done with this stage before it is refilled
+    stage = stage + 1 == kStages ? 0 : stage + 1;
+  }
+  cp_async_wait<0>();
+}
+
+template <int G>
+__global__ void __launch_bounds__(kThreads, 1)
+decode_split_fp8_staged_kernel(const __nv_bfloat16 *__restrict__ q, const uint8_t *__restrict__ cache_k,
+                               const uint8_t *__restrict__ cache_v, float *__restrict__ part_o,
+                               float *__restrict__ part_m, float *__restrict__ part_l, size_t position_scalar,
+                               const int32_t *__restrict__ position_device, uint32_t kv_heads, uint32_t q_per_kv,
+                               uint32_t n_splits) {
+  constexpr uint32_t D = 256;
+  extern __shared__ __align__(128) uint8_t smem[];
+  // ring | q fragments | per-warp maxima and sums; the epilogue's output slices reuse the ring
+  uint2 (*s_q)[32] = reinterpret_cast<uint2 (*)[32]>(smem + kRingBytes);
+  float (*s_m)[8] = reinterpret_cast<float (*)[8]>(smem + kRingBytes + 16 * 32 * 8);
+  float (*s_l)[8] = s_m + kWarps;
+  float (*s_o)[kEpiStride] = reinterpret_cast<float (*)[kEpiStride]>(smem);
+
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+  const uint32_t g = lane >> 2, t = lane & 3u;
+  const uint32_t head0 = blockIdx.x * G;
+  const uint32_t kvh = head0 / q_per_kv;
+  const uint32_t split = blockIdx.y;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const size_t position = read_position(position_scalar, position_device);
+  size_t s_begin, s_end;
+  split_range(position, n_splits, split, s_begin, s_end);
+
+  // Q fragments: step 4 j + i covers dims 64 j + 16 t + 4 i .. + 3 of head g, as float16
+  if (warp == 0) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint4 raw0 = make_uint4(0, 0, 0, 0), raw1 = make_uint4(0, 0, 0, 0);
+      if (g < G) {
+        const uint4 *src = reinterpret_cast<const uint4 *>(q + static_cast<size_t>(head0 + g) * D + 64 * j + 16 * t);
+        raw0 = __ldg(src);
+        raw1 = __ldg(src + 1);
+      }
+      const uint32_t w[8] = {raw0.x, raw0.y, raw0.z, raw0.w, raw1.x, raw1.y, raw1.z, raw1.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const uint32_t pair = w[2 * i + half];
+          const __half2 h = __floats2half2_rn(__uint_as_float(pair << 16), __uint_as_float(pair & 0xffff0000u));
+          reinterpret_cast<uint32_t *>(&s_q[4 * j + i][lane])[half] = *reinterpret_cast<const uint32_t *>(&h);
+        }
+      }
+    }
+  }
+  __syncthreads();
+
+  const uint32_t ring = static_cast<uint32_t>(__cvta_generic_to_shared(smem)) + warp * (kStages * kStageBytes);
+  float o[2][8][4];
+  float m_run, l_run;
+  fp8_staged_pass<G, false>(o, m_run, l_run, cache_k, cache_v, ring, s_q, s_begin, s_end, kv_heads, kvh);
+  float probe = l_run;                                            // NaN anywhere in this thread's state?
+#pragma unroll
+  for (int h = 0; h < 2; ++h)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) probe += (o[h][j][0] + o[h][j][1]) + (o[h][j][2] + o[h][j][3]);
+  if (__syncthreads_or(probe != probe))
+    fp8_staged_pass<G, true>(o, m_run, l_run, cache_k, cache_v, ring, s_q, s_begin, s_end, kv_heads, kvh);
+  __syncthreads();                                                // the ring becomes the epilogue's slices
+  split_epilogue<G>(o, m_run, l_run, 1.0f / 64.0f, s_m, s_l, s_o, part_o, part_m, part_l, head0, split, n_splits);
+}
+
 // ---- tensor-core form for the BF16 cache (head_dim 256, G <= 8 q heads per kv head).
 //
 // Same fragment plan as the FP8 kernel with bfloat16 operands (mma.sync.m16n8k16 bf16, float32
@@ -784,6 +1027,21 @@ int launch_fp8_mma(const Args &a, uint32_t n_splits) {
 }
 
 template <int G>
+int launch_fp8_staged(const Args &a, uint32_t n_splits) {
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(decode_split_fp8_staged_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    static_cast<int>(kStagedSmemBytes));
+  });
+  if (attr_err != cudaSuccess) return QWEN36_STATUS_CUDA_ERROR;
+  decode_split_fp8_staged_kernel<G><<<dim3(a.q_heads / G, n_splits), kThreads, kStagedSmemBytes, q36::stream()>>>(
+      a.q, static_cast<const uint8_t *>(a.cache_k), static_cast<const uint8_t *>(a.cache_v), a.part_o, a.part_m,
+      a.part_l, a.position, a.position_device, a.kv_heads, a.q_per_kv, n_splits);
+  return q36::launch_status();
+}
+
+template <int G>
 int launch_bf16_mma(const Args &a, uint32_t n_splits) {
   decode_split_bf16_mma_kernel<G><<<dim3(a.q_heads / G, n_splits), kThreads, 0, q36::stream()>>>(
       a.q, static_cast<const __nv_bfloat16 *>(a.cache_k), static_cast<const __nv_bfloat16 *>(a.cache_v), a.part_o,
@@ -834,9 +1092,10 @@ int run_split_path(const Args &a, size_t caller_splits) {
   const bool grouped = a.q_per_kv == 1 || a.q_per_kv == 2 || a.q_per_kv == 4 || a.q_per_kv == 6 || a.q_per_kv == 8;
   int status;
   uint32_t n;
-  if (g_decode_mode == 1 && a.head_dim == 256 && aligned16 && grouped) {
+  if (g_decode_mode >= 1 && a.head_dim == 256 && aligned16 && grouped) {
     n = pick_splits(a, caller_splits, a.kv_heads, true);
-#define Q36_DECODE_GO(G) status = FP8 ? launch_fp8_mma<G>(a, n) : launch_bf16_mma<G>(a, n)
+#define Q36_DECODE_GO(G) \
+  status = !FP8 ? launch_bf16_mma<G>(a, n) : (g_decode_mode == 2 ? launch_fp8_staged<G>(a, n) : launch_fp8_mma<G>(a, n))
     switch (a.q_per_kv) {
       case 1: Q36_DECODE_GO(1); break;
       case 2: Q36_DECODE_GO(2); break;
@@ -858,7 +1117,7 @@ int run_split_path(const Args &a, size_t caller_splits) {
 
 }  // namespace
 
-extern "C" void qwen36_attention_decode_set_mode(int mode) { g_decode_mode = mode != 0 ? 1 : 0; }
+extern "C" void qwen36_attention_decode_set_mode(int mode) { g_decode_mode = mode < 0 ? 0 : (mode > 2 ? 2 : mode); }
 extern "C" void qwen36_attention_decode_force_splits(int n) { g_decode_force_splits = n < 0 ? 0 : n; }
 
 extern "C" int qwen36_attention_decode(const qwen36_attention_decode_spec_t *spec) {
