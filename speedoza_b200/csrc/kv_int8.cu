@@ -19,6 +19,7 @@
 
 #include <mutex>
 
+#include "kv_split.cuh"
 #include "lse_merge.cuh"
 #include "peer_combine.cuh"
 
@@ -459,7 +460,7 @@ int launch_merge_after_splits(unsigned q_heads, const float *o, const float *m, 
 }
 
 struct Scratch { float *o, *m, *l; };
-int g_use_fast_attention = 2;            // 2 tensor-core form, 1 SIMT fast path, 0 general kernel
+int g_use_fast_attention = 3;            // 3 tensor-core form fed through shared memory, 2 tensor-core form fed from registers, 1 SIMT fast path, 0 general kernel
 
 // Scratch for qwen36_turboquant_attention_static: lives in the library image, so every GPU that
 // loads the library holds these 4 MiB until the process exits.  Sized for
@@ -522,13 +523,7 @@ uint32_t pick_splits(size_t tokens, size_t ctas_per_split, bool one_wave) {
 //       (16 (g + 8 h) ..) of its four tokens and pairs bytes of neighbouring tokens; mma (h, j)
 //       has dim 16 (g + 8 h) + 2 j in row g and the next dim in row g + 8.  Its accumulator holds
 //       heads 2t, 2t + 1 of those two dims.
-__device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                        uint32_t b1) {
-  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
-               "{%0, %1, %2, %3};"
-               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
+using q36::mma_f16;
 // (lo byte of x, lo byte of y) as int8 -> float16x2; x and y already XORed with 0x80 per byte.
 template <int BYTE>
 __device__ __forceinline__ uint32_t s8pair_to_h2(uint32_t x, uint32_t y) {
@@ -816,6 +811,234 @@ kv_attention_mma_kernel(const __nv_bfloat16 *__restrict__ q, const int8_t *__res
   }
 }
 
+// ---- tensor-core form fed through shared memory.  Same products and fragment plan as
+// kv_attention_mma_kernel, but K, V and the per-token scales travel global -> shared memory with
+// asynchronous copies (cp.async) into a private three-stage ring per warp, so that the bytes in
+// flight (two stages = 16 KB per warp, 128 KB per SM) do not have to fit in registers.  A stage
+// holds the K rows, the V rows and the (k_scale, v_scale) pairs of a 16-token group; 16-byte chunks
+// are XOR-swizzled on the way in so that the fragment reads are free of bank conflicts: K chunk c
+// of row r sits at c ^ 4 (r & 1), V chunk c of row r at c ^ 2 ((r / 2) & 3).  No block barrier
+// inside the loop: a warp waits for its own copies (wait_group + __syncwarp).
+constexpr int kStages = 3;
+constexpr uint32_t kTileBytes = 16 * 256;                         // 16 tokens x 256 bytes
+constexpr uint32_t kStageBytes = 2 * kTileBytes + 16 * 8;         // K tile, V tile, 16 scale pairs
+constexpr uint32_t kRingBytes = kWarps * kStages * kStageBytes;   // 195 KB
+constexpr uint32_t kStagedSmemBytes = kRingBytes + 16 * 32 * 8 + 2 * kWarps * 8 * 4;
+
+template <int G>
+__global__ void __launch_bounds__(kThreads, 1)
+kv_attention_staged_kernel(const __nv_bfloat16 *__restrict__ q, const int8_t *__restrict__ kq,
+                           const int8_t *__restrict__ vq, const float *__restrict__ meta,
+                           float *__restrict__ part_o, float *__restrict__ part_m, float *__restrict__ part_l,
+                           size_t t_begin, size_t t_end, uint32_t kv_heads, uint32_t q_per_kv, uint32_t n_splits) {
+  constexpr uint32_t D = 256;
+  constexpr float kPScale = 1024.0f;                              // keeps p * v_scale out of the float16 subnormals
+  extern __shared__ __align__(128) uint8_t smem[];
+  // ring | q fragments | per-warp maxima and sums; the epilogue's output slices reuse the ring
+  uint2 (*s_q)[32] = reinterpret_cast<uint2 (*)[32]>(smem + kRingBytes);
+  float (*s_m)[8] = reinterpret_cast<float (*)[8]>(smem + kRingBytes + 16 * 32 * 8);
+  float (*s_l)[8] = s_m + kWarps;
+  float (*s_o)[q36::kEpiStride] = reinterpret_cast<float (*)[q36::kEpiStride]>(smem);
+
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+  const uint32_t g = lane >> 2, t = lane & 3u;
+  const uint32_t head0 = blockIdx.x * G;
+  const uint32_t kvh = head0 / q_per_kv;
+  const uint32_t split = blockIdx.y;
+  const size_t total = t_end - t_begin;
+  const size_t per_split = q36::round_up(q36::div_ceil(total, n_splits), static_cast<size_t>(kWarps) * 16);
+  const size_t s_begin = t_begin + min(total, per_split * split);
+  const size_t s_end = t_begin + min(total, per_split * (split + 1));
+  const float sm_scale = 0.0625f * 1.4426950408889634f;           // rsqrt(256) * log2(e)
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+  const uint32_t ring = static_cast<uint32_t>(__cvta_generic_to_shared(smem)) + warp * (kStages * kStageBytes);
+  const size_t stride = static_cast<size_t>(kWarps) * 16;
+  size_t t0 = s_begin + static_cast<size_t>(warp) * 16;
+  // one stage: lane copies chunk (lane & 15) of rows (lane >> 4) + 2 r, r = 0 .. 7, of K and of V,
+  // lanes 0 .. 15 the scale pair of row `lane`; rows past the end of the split are zero-filled
+  // (source size 0, address kept inside the cache)
+  const uint32_t chunk = lane & 15u, row0 = lane >> 4;
+  auto issue = [&](uint32_t stage, size_t tg) {
+    const uint32_t base = ring + stage * kStageBytes;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      const uint32_t row = row0 + 2u * r;
+      const size_t tok = tg + row;
+      const bool valid = tok < s_end;
+      const size_t off = ((valid ? tok : s_begin) * kv_heads + kvh) * D + chunk * 16u;
+      const uint32_t bytes = valid ? 16u : 0u;
+      q36::cp_async_16(base + row * 256u + ((chunk ^ ((row & 1u) << 2)) << 4), kq + off, bytes);
+      q36::cp_async_16(base + kTileBytes + row * 256u + ((chunk ^ (((row >> 1) & 3u) << 1)) << 4), vq + off, bytes);
+    }
+    if (lane < 16u) {
+      const size_t tok = tg + lane;
+      const bool valid = tok < s_end;
+      const float *src = meta + ((valid ? tok : s_begin) * kv_heads + kvh) * 2;
+      asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(base + 2 * kTileBytes + lane * 8u), "l"(src),
+                   "r"(valid ? 8u : 0u) : "memory");
+    }
+    q36::cp_async_commit();
+  };
+  if (t0 < s_end) {
+#pragma unroll
+    for (int s = 0; s < kStages - 1; ++s) issue(s, t0 + s * stride);
+  }
+
+  // Q fragments (float16): step 4 j + i covers dims 64 j + 16 t + 4 i .. + 3 of head g
+  if (warp == 0) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint4 raw0 = make_uint4(0, 0, 0, 0), raw1 = make_uint4(0, 0, 0, 0);
+      if (g < G) {
+        const uint4 *src = reinterpret_cast<const uint4 *>(q + static_cast<size_t>(head0 + g) * D + 64 * j + 16 * t);
+        raw0 = __ldg(src);
+        raw1 = __ldg(src + 1);
+      }
+      const uint32_t w[8] = {raw0.x, raw0.y, raw0.z, raw0.w, raw1.x, raw1.y, raw1.z, raw1.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const uint32_t pair = w[2 * i + half];
+          const __half2 h = __floats2half2_rn(__uint_as_float(pair << 16), __uint_as_float(pair & 0xffff0000u));
+          reinterpret_cast<uint32_t *>(&s_q[4 * j + i][lane])[half] = *reinterpret_cast<const uint32_t *>(&h);
+        }
+      }
+    }
+  }
+  __syncthreads();
+  // 1152 * (sum of head g's float16 q): the K operand carries that bias on every element
+  float q_bias = 0.f;
+#pragma unroll
+  for (int s16 = 0; s16 < 16; ++s16) {
+    const uint2 qf = s_q[s16][lane];
+    const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&qf.x));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&qf.y));
+    q_bias += (a.x + a.y) + (b.x + b.y);
+  }
+  q_bias += __shfl_xor_sync(0xffffffffu, q_bias, 1);
+  q_bias += __shfl_xor_sync(0xffffffffu, q_bias, 2);
+  q_bias *= 1152.0f;
+
+  float o[2][8][4];
+#pragma unroll
+  for (int h = 0; h < 2; ++h)
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) o[h][j][c] = 0.f;
+  float m_run = -INFINITY, l_run = 0.f;
+
+  uint32_t stage = 0;
+  for (; t0 < s_end; t0 += stride) {
+    issue(stage == 0 ? kStages - 1 : stage - 1, t0 + (kStages - 1) * stride);   // refill the stage read last time
+    q36::cp_async_wait<kStages - 1>();
+    __syncwarp();
+    const uint32_t kt = ring + stage * kStageBytes, vt = kt + kTileBytes, mt = vt + kTileBytes;
+    // ---- S = Q K^T: four independent accumulator chains (two blocks x even / odd steps)
+    float sc_[4];
+    {
+      float acc[2][2][4];
+#pragma unroll
+      for (int blk = 0; blk < 2; ++blk)
+#pragma unroll
+        for (int par = 0; par < 2; ++par)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) acc[blk][par][c] = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t w[2][4];
+#pragma unroll
+        for (int blk = 0; blk < 2; ++blk) {
+          const uint4 kw = q36::lds128(kt + (8u * blk + g) * 256u + (((t + 4u * j) ^ ((g & 1u) << 2)) << 4));
+          w[blk][0] = kw.x ^ 0x80808080u; w[blk][1] = kw.y ^ 0x80808080u;
+          w[blk][2] = kw.z ^ 0x80808080u; w[blk][3] = kw.w ^ 0x80808080u;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint2 qf = s_q[4 * j + i][lane];
+#pragma unroll
+          for (int blk = 0; blk < 2; ++blk)
+            mma_f16(acc[blk][i & 1], qf.x, 0u, qf.y, 0u, s8x2_to_h2_biased<0>(w[blk][i]), s8x2_to_h2_biased<1>(w[blk][i]));
+        }
+      }
+#pragma unroll
+      for (int blk = 0; blk < 2; ++blk) {
+        sc_[2 * blk] = (acc[blk][0][0] + acc[blk][1][0]) - q_bias;
+        sc_[2 * blk + 1] = (acc[blk][0][1] + acc[blk][1][1]) - q_bias;
+      }
+    }
+    // ---- online softmax, head g: this lane's four tokens, then the four lanes of the head
+    float2 scl[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t row = 2u * t + (i & 1) + 8u * (i >> 1);
+      asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(scl[i].x), "=f"(scl[i].y) : "r"(mt + row * 8u));
+    }
+    float s_log2[4];
+    float tile_max = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const size_t tok = t0 + 2 * t + (i & 1) + 8 * (i >> 1);
+      const bool valid = g < G && tok < s_end;
+      s_log2[i] = valid ? sc_[i] * scl[i].x * sm_scale : -INFINITY;
+      tile_max = fmaxf(tile_max, s_log2[i]);
+    }
+    tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 1));
+    tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 2));
+    const float m_new = fmaxf(m_run, tile_max);
+    const float corr = m_new == -INFINITY ? 1.f : exp2f(m_run - m_new);
+    float p[4], p_sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      p[i] = s_log2[i] == -INFINITY ? 0.f : exp2f(s_log2[i] - m_new);
+      p_sum += p[i];
+    }
+    p_sum += __shfl_xor_sync(0xffffffffu, p_sum, 1);
+    p_sum += __shfl_xor_sync(0xffffffffu, p_sum, 2);
+    l_run = l_run * corr + p_sum;
+    m_run = m_new;
+    const __half2 pb0 = __floats2half2_rn(p[0] * scl[0].y * kPScale, p[1] * scl[1].y * kPScale);
+    const __half2 pb1 = __floats2half2_rn(p[2] * scl[2].y * kPScale, p[3] * scl[3].y * kPScale);
+    const uint32_t b0 = *reinterpret_cast<const uint32_t *>(&pb0), b1 = *reinterpret_cast<const uint32_t *>(&pb1);
+    // ---- rescale the running output: this lane's accumulators belong to heads 2t and 2t + 1
+    const float c_even = __shfl_sync(0xffffffffu, corr, 8 * t), c_odd = __shfl_sync(0xffffffffu, corr, 8 * t + 4);
+    if (__any_sync(0xffffffffu, corr != 1.f)) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          o[h][j][0] *= c_even; o[h][j][1] *= c_odd; o[h][j][2] *= c_even; o[h][j][3] *= c_odd;
+        }
+    }
+    // ---- O^T += V^T P^T: rows 2t, 2t + 1, 2t + 8, 2t + 9 of the V tile, chunk g + 8 h
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      uint4 x[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        x[i] = q36::lds128(vt + (2u * t + (i & 1) + 8u * (i >> 1)) * 256u + (((g + 8u * h) ^ (t << 1)) << 4));
+      const uint32_t va[4] = {x[0].x ^ 0x80808080u, x[0].y ^ 0x80808080u, x[0].z ^ 0x80808080u, x[0].w ^ 0x80808080u};
+      const uint32_t vb[4] = {x[1].x ^ 0x80808080u, x[1].y ^ 0x80808080u, x[1].z ^ 0x80808080u, x[1].w ^ 0x80808080u};
+      const uint32_t vc[4] = {x[2].x ^ 0x80808080u, x[2].y ^ 0x80808080u, x[2].z ^ 0x80808080u, x[2].w ^ 0x80808080u};
+      const uint32_t vd[4] = {x[3].x ^ 0x80808080u, x[3].y ^ 0x80808080u, x[3].z ^ 0x80808080u, x[3].w ^ 0x80808080u};
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        mma_f16(o[h][2 * w], s8pair_to_h2<0>(va[w], vb[w]), s8pair_to_h2<1>(va[w], vb[w]),
+                s8pair_to_h2<0>(vc[w], vd[w]), s8pair_to_h2<1>(vc[w], vd[w]), b0, b1);
+        mma_f16(o[h][2 * w + 1], s8pair_to_h2<2>(va[w], vb[w]), s8pair_to_h2<3>(va[w], vb[w]),
+                s8pair_to_h2<2>(vc[w], vd[w]), s8pair_to_h2<3>(vc[w], vd[w]), b0, b1);
+      }
+    }
+    __syncwarp();                                    // every lane is done with this stage before it is refilled
+    stage = stage + 1 == kStages ? 0 : stage + 1;
+  }
+  q36::cp_async_wait<0>();
+  __syncthreads();                                   // the ring becomes the epilogue's slices
+  q36::split_epilogue<G>(o, m_run, l_run, 1.0f / kPScale, s_m, s_l, s_o, part_o, part_m, part_l, head0, split, n_splits);
+}
+
 template <int G>
 int launch_split_g(const __nv_bfloat16 *q, const int8_t *kq, const int8_t *vq, const float *meta, Scratch sc,
                    size_t t_begin, size_t t_end, const qwen36_attention_shape_t &sh, uint32_t q_per_kv,
@@ -826,7 +1049,21 @@ int launch_split_g(const __nv_bfloat16 *q, const int8_t *kq, const int8_t *vq, c
 #define Q36_GO(DPL, VEC)                                                                              \
   kv_attention_split_kernel<G, DPL, VEC><<<grid, kThreads, 0, q36::stream()>>>(                        \
       q, kq, vq, meta, sc.o, sc.m, sc.l, t_begin, t_end, KV, q_per_kv, D, n_splits)
-  if (D == 256 && G <= 8 && g_use_fast_attention == 2 &&
+  if (D == 256 && G <= 8 && g_use_fast_attention == 3 &&
+      ((reinterpret_cast<uintptr_t>(kq) | reinterpret_cast<uintptr_t>(vq) | reinterpret_cast<uintptr_t>(q)) & 15u) == 0 &&
+      (reinterpret_cast<uintptr_t>(meta) & 7u) == 0) {
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [] {
+      attr_err = cudaFuncSetAttribute(kv_attention_staged_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      static_cast<int>(kStagedSmemBytes));
+    });
+    if (attr_err != cudaSuccess) return QWEN36_STATUS_CUDA_ERROR;
+    kv_attention_staged_kernel<G><<<grid, kThreads, kStagedSmemBytes, q36::stream()>>>(
+        q, kq, vq, meta, sc.o, sc.m, sc.l, t_begin, t_end, KV, q_per_kv, n_splits);
+    return q36::launch_status();
+  }
+  if (D == 256 && G <= 8 && g_use_fast_attention >= 2 &&
       ((reinterpret_cast<uintptr_t>(kq) | reinterpret_cast<uintptr_t>(vq) | reinterpret_cast<uintptr_t>(q)) & 15u) == 0) {
     kv_attention_mma_kernel<G><<<grid, kThreads, 0, q36::stream()>>>(q, kq, vq, meta, sc.o, sc.m, sc.l, t_begin,
                                                                       t_end, KV, q_per_kv, n_splits);
@@ -858,7 +1095,7 @@ uint32_t run_splits(qwen36_device_ptr_t q, qwen36_device_ptr_t kq, qwen36_device
   const size_t tokens = t_end > t_begin ? t_end - t_begin : 0;
   const __nv_bfloat16 *qp = as_ptr<const __nv_bfloat16>(q);
   const int8_t *kp = as_ptr<const int8_t>(kq), *vp = as_ptr<const int8_t>(vq);
-  const bool tensor_core_form = sh.head_dim == 256 && g_use_fast_attention == 2 &&
+  const bool tensor_core_form = sh.head_dim == 256 && g_use_fast_attention >= 2 &&
       ((reinterpret_cast<uintptr_t>(kp) | reinterpret_cast<uintptr_t>(vp) | reinterpret_cast<uintptr_t>(qp)) & 15u) == 0;
   const uint32_t n_splits = pick_splits(tokens, sh.q_heads / G, tensor_core_form);
   const float *mp = as_ptr<const float>(meta);
@@ -910,7 +1147,7 @@ extern "C" int qwen36_turboquant_encode_kv(const qwen36_turboquant_encode_spec_t
 }
 
 // Test hook: 0 routes head_dim 256 through the general kernel instead of the 4-token fast path.
-extern "C" void qwen36_turboquant_attention_set_fast(int mode) { g_use_fast_attention = mode < 0 ? 0 : (mode > 2 ? 2 : mode); }
+extern "C" void qwen36_turboquant_attention_set_fast(int mode) { g_use_fast_attention = mode < 0 ? 0 : (mode > 3 ? 3 : mode); }
 
 // Test hook: n > 0 fixes the number of KV splits, 0 restores the heuristic.
 extern "C" void qwen36_turboquant_attention_force_splits(int n) { g_force_splits = n < 0 ? 0 : n; }

@@ -1,0 +1,100 @@
+// Pieces shared by the split-KV attention kernels that run both products on the tensor cores
+// (int8, FP8 and BF16 caches, head size 256): the float16 MMA wrapper, the asynchronous-copy
+// helpers of the shared-memory staged forms, and the CTA epilogue that merges the eight warps'
+// running softmax states into one (m, l, o) partial per q head.
+#pragma once
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+namespace q36 {
+
+constexpr int kSplitThreads = 256;
+constexpr int kSplitWarps = kSplitThreads / 32;
+
+__device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                        uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ void cp_async_16(uint32_t dst_smem, const void *src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst_smem), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+
+
+// Epilogue shared by the tensor-core split kernels: merges the eight warps' running softmax states
+// (maxima in log2 units, outputs scaled by 1 / out_scale) and writes the CTA's partial.
+// o[h][j][c]: head 2t + (c & 1), dim 16 (g + 8 h) + 2 j + (c >> 1).
+constexpr uint32_t kEpiStride = 256 + 4;                          // row stride: heads land a quarter of the banks apart
+template <int G>
+__device__ __forceinline__ void split_epilogue(float (&o)[2][8][4], float m_run, float l_run, float out_scale,
+                                               float (*s_m)[8], float (*s_l)[8], float (*s_o)[kEpiStride],
+                                               float *__restrict__ part_o, float *__restrict__ part_m,
+                                               float *__restrict__ part_l, uint32_t head0, uint32_t split,
+                                               uint32_t n_splits) {
+  constexpr uint32_t D = 256, DP = kEpiStride;
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+  const uint32_t g = lane >> 2, t = lane & 3u;
+  // ---- merge the warps of the CTA: weights per head from the running maxima; the weighted outputs
+  // meet in four shared-memory slices (warps 4..7 write, warps 0..3 add), then every thread sums
+  // the four slices of its outputs
+  if (t == 0 && g < G) { s_m[warp][g] = m_run; s_l[warp][g] = l_run; }
+  __syncthreads();
+  float wgt[2];                                                    // heads 2t, 2t + 1
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    const uint32_t head = 2 * t + e;
+    float M = -INFINITY;
+    if (head < G)
+      for (int w = 0; w < kSplitWarps; ++w) M = fmaxf(M, s_m[w][head]);
+    const float mine = head < G ? s_m[warp][head] : -INFINITY;
+    wgt[e] = mine == -INFINITY ? 0.f : exp2f(mine - M) * out_scale;
+  }
+  float (*slice)[DP] = &s_o[(warp & 3u) * G];
+  for (int round = 0; round < 2; ++round) {
+    if ((warp >> 2) == static_cast<uint32_t>(1 - round)) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            // dims are stored XOR-swizzled inside their 16-float chunk (chunk index = g + 8 h), so
+            // that the eight chunks a warp writes at once fall on different banks
+            const uint32_t head = 2 * t + (c & 1), dim = 16 * (g + 8 * h) + ((2 * j + (c >> 1)) ^ (g + 8 * h));
+            if (head < G) {
+              float *dst = &slice[head][dim];
+              *dst = round == 0 ? wgt[c & 1] * o[h][j][c] : fmaf(wgt[c & 1], o[h][j][c], *dst);
+            }
+          }
+    }
+    __syncthreads();
+  }
+  for (uint32_t idx = threadIdx.x; idx < G * D; idx += kSplitThreads) {
+    const uint32_t hd = idx / D, d = idx % D;
+    const size_t slot = static_cast<size_t>(head0 + hd) * n_splits + split;
+    const uint32_t ds = d ^ ((d >> 4) & 15u);                      // undo the swizzle
+    part_o[slot * D + d] = (s_o[hd][ds] + s_o[G + hd][ds]) + (s_o[2 * G + hd][ds] + s_o[3 * G + hd][ds]);
+    if (d == 0) {
+      float M = -INFINITY, den = 0.f;
+      for (int w = 0; w < kSplitWarps; ++w) M = fmaxf(M, s_m[w][hd]);
+      for (int w = 0; w < kSplitWarps; ++w)
+        den = fmaf(s_m[w][hd] == -INFINITY ? 0.f : exp2f(s_m[w][hd] - M), s_l[w][hd], den);
+      part_m[slot] = M * 0.6931471805599453f;
+      part_l[slot] = den;
+    }
+  }
+}
+
+}  // namespace q36
