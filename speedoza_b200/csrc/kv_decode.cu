@@ -680,6 +680,7 @@ decode_split_fp8_staged_kernel(const __nv_bfloat16 *__restrict__ q, const uint8_
   const uint32_t head0 = blockIdx.x * G;
   const uint32_t kvh = head0 / q_per_kv;
   const uint32_t split = blockIdx.y;
+  asm volatile("griddepcontrol.wait;" ::: "memory");       // seated early; nothing is touched before the previous kernel is done
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const size_t position = read_position(position_scalar, position_device);
   size_t s_begin, s_end;
@@ -763,6 +764,7 @@ decode_split_bf16_mma_kernel(const __nv_bfloat16 *__restrict__ q, const __nv_bfl
   const uint32_t head0 = blockIdx.x * G;
   const uint32_t kvh = head0 / q_per_kv;
   const uint32_t split = blockIdx.y;
+  asm volatile("griddepcontrol.wait;" ::: "memory");       // seated early; nothing is touched before the previous kernel is done
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const size_t position = read_position(position_scalar, position_device);
   size_t s_begin, s_end;
@@ -960,18 +962,18 @@ int launch_fp8_staged(const Args &a, uint32_t n_splits) {
                                     static_cast<int>(kStagedSmemBytes));
   });
   if (attr_err != cudaSuccess) return QWEN36_STATUS_CUDA_ERROR;
-  decode_split_fp8_staged_kernel<G><<<dim3(a.q_heads / G, n_splits), kThreads, kStagedSmemBytes, q36::stream()>>>(
+  return q36::cuda_status(q36::launch_after_previous(
+      decode_split_fp8_staged_kernel<G>, dim3(a.q_heads / G, n_splits), dim3(kThreads), kStagedSmemBytes, q36::stream(),
       a.q, static_cast<const uint8_t *>(a.cache_k), static_cast<const uint8_t *>(a.cache_v), a.part_o, a.part_m,
-      a.part_l, a.position, a.position_device, a.kv_heads, a.q_per_kv, n_splits);
-  return q36::launch_status();
+      a.part_l, a.position, a.position_device, a.kv_heads, a.q_per_kv, n_splits));
 }
 
 template <int G>
 int launch_bf16_mma(const Args &a, uint32_t n_splits) {
-  decode_split_bf16_mma_kernel<G><<<dim3(a.q_heads / G, n_splits), kThreads, 0, q36::stream()>>>(
-      a.q, static_cast<const __nv_bfloat16 *>(a.cache_k), static_cast<const __nv_bfloat16 *>(a.cache_v), a.part_o,
-      a.part_m, a.part_l, a.position, a.position_device, a.kv_heads, a.q_per_kv, n_splits);
-  return q36::launch_status();
+  return q36::cuda_status(q36::launch_after_previous(
+      decode_split_bf16_mma_kernel<G>, dim3(a.q_heads / G, n_splits), dim3(kThreads), 0, q36::stream(), a.q,
+      static_cast<const __nv_bfloat16 *>(a.cache_k), static_cast<const __nv_bfloat16 *>(a.cache_v), a.part_o,
+      a.part_m, a.part_l, a.position, a.position_device, a.kv_heads, a.q_per_kv, n_splits));
 }
 
 template <bool FP8>

@@ -850,6 +850,10 @@ kv_attention_staged_kernel(const __nv_bfloat16 *__restrict__ q, const int8_t *__
   const size_t s_begin = t_begin + min(total, per_split * split);
   const size_t s_end = t_begin + min(total, per_split * (split + 1));
   const float sm_scale = 0.0625f * 1.4426950408889634f;           // rsqrt(256) * log2(e)
+  // launched with programmatic stream serialisation: seated while the previous kernel drains, but
+  // nothing is read or written before that kernel (the producer of q, of the newest cache row, or
+  // the reader of the partial buffers) has completed
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   const uint32_t ring = static_cast<uint32_t>(__cvta_generic_to_shared(smem)) + warp * (kStages * kStageBytes);
@@ -1059,9 +1063,9 @@ int launch_split_g(const __nv_bfloat16 *q, const int8_t *kq, const int8_t *vq, c
                                       static_cast<int>(kStagedSmemBytes));
     });
     if (attr_err != cudaSuccess) return QWEN36_STATUS_CUDA_ERROR;
-    kv_attention_staged_kernel<G><<<grid, kThreads, kStagedSmemBytes, q36::stream()>>>(
-        q, kq, vq, meta, sc.o, sc.m, sc.l, t_begin, t_end, KV, q_per_kv, n_splits);
-    return q36::launch_status();
+    return q36::cuda_status(q36::launch_after_previous(kv_attention_staged_kernel<G>, grid, dim3(kThreads),
+                                                       kStagedSmemBytes, q36::stream(), q, kq, vq, meta, sc.o, sc.m,
+                                                       sc.l, t_begin, t_end, KV, q_per_kv, n_splits));
   }
   if (D == 256 && G <= 8 && g_use_fast_attention >= 2 &&
       ((reinterpret_cast<uintptr_t>(kq) | reinterpret_cast<uintptr_t>(vq) | reinterpret_cast<uintptr_t>(q)) & 15u) == 0) {
