@@ -511,13 +511,34 @@ constexpr uint32_t kStageBytes = 2 * kTileBytes;                  // K tile + V 
 constexpr uint32_t kRingBytes = kWarps * kStages * kStageBytes;   // 192 KB
 constexpr uint32_t kStagedSmemBytes = kRingBytes + 16 * 32 * 8 + 2 * kWarps * 8 * 4;
 
+// One stage of the ring: lane copies chunk (lane & 15) of rows (lane >> 4) + 2 r, r = 0 .. 7, of K
+// and of V; rows past the end of the split are zero-filled (source size 0, address kept inside the
+// cache).  Ends with a commit: one group per stage.
+__device__ __forceinline__ void fp8_stage_issue(uint32_t base, size_t tg, size_t s_begin, size_t s_end,
+                                                const uint8_t *__restrict__ cache_k,
+                                                const uint8_t *__restrict__ cache_v, uint32_t kv_heads,
+                                                uint32_t kvh) {
+  const uint32_t lane = threadIdx.x & 31u;
+  const uint32_t chunk = lane & 15u, row0 = lane >> 4;
+#pragma unroll
+  for (int r = 0; r < 8; ++r) {
+    const uint32_t row = row0 + 2u * r;
+    const size_t tok = tg + row;
+    const bool valid = tok < s_end;
+    const size_t off = ((valid ? tok : s_begin) * kv_heads + kvh) * 256u + chunk * 16u;
+    const uint32_t bytes = valid ? 16u : 0u;
+    cp_async_16(base + row * 256u + ((chunk ^ ((row & 1u) << 2)) << 4), cache_k + off, bytes);
+    cp_async_16(base + kTileBytes + row * 256u + ((chunk ^ (((row >> 1) & 3u) << 1)) << 4), cache_v + off, bytes);
+  }
+  cp_async_commit();
+}
+
 template <int G, bool FIX>
 __device__ __forceinline__ void fp8_staged_pass(float (&o)[2][8][4], float &m_run, float &l_run,
                                                 const uint8_t *__restrict__ cache_k,
                                                 const uint8_t *__restrict__ cache_v, uint32_t ring /* this warp's */,
                                                 const uint2 (*s_q)[32], size_t s_begin, size_t s_end,
-                                                uint32_t kv_heads, uint32_t kvh) {
-  constexpr uint32_t D = 256;
+                                                uint32_t kv_heads, uint32_t kvh, bool primed) {
   constexpr float kPScale = 64.0f;
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
   const uint32_t g = lane >> 2, t = lane & 3u;
@@ -534,25 +555,13 @@ __device__ __forceinline__ void fp8_staged_pass(float (&o)[2][8][4], float &m_ru
   size_t t0 = s_begin + static_cast<size_t>(warp) * 16;
   if (t0 >= s_end) return;
 
-  // one stage: lane copies chunk (lane & 15) of rows (lane >> 4) + 2 r, r = 0 .. 7, of K and of V;
-  // rows past the end of the split are zero-filled (source size 0, address kept inside the cache)
-  const uint32_t chunk = lane & 15u, row0 = lane >> 4;
   auto issue = [&](uint32_t stage, size_t tg) {
-    const uint32_t base = ring + stage * kStageBytes;
-#pragma unroll
-    for (int r = 0; r < 8; ++r) {
-      const uint32_t row = row0 + 2u * r;
-      const size_t tok = tg + row;
-      const bool valid = tok < s_end;
-      const size_t off = ((valid ? tok : s_begin) * kv_heads + kvh) * D + chunk * 16u;
-      const uint32_t bytes = valid ? 16u : 0u;
-      cp_async_16(base + row * 256u + ((chunk ^ ((row & 1u) << 2)) << 4), cache_k + off, bytes);
-      cp_async_16(base + kTileBytes + row * 256u + ((chunk ^ (((row >> 1) & 3u) << 1)) << 4), cache_v + off, bytes);
-    }
-    cp_async_commit();
+    fp8_stage_issue(ring + stage * kStageBytes, tg, s_begin, s_end, cache_k, cache_v, kv_heads, kvh);
   };
+  if (!primed) {
 #pragma unroll
-  for (int s = 0; s < kStages - 1; ++s) issue(s, t0 + s * stride);
+    for (int s = 0; s < kStages - 1; ++s) issue(s, t0 + s * stride);
+  }
 
   uint32_t stage = 0;
   for (; t0 < s_end; t0 += stride) {
@@ -686,6 +695,17 @@ decode_split_fp8_staged_kernel(const __nv_bfloat16 *__restrict__ q, const uint8_
   size_t s_begin, s_end;
   split_range(position, n_splits, split, s_begin, s_end);
 
+  // the first two stages of this warp's ring fly while q is staged
+  const uint32_t ring = static_cast<uint32_t>(__cvta_generic_to_shared(smem)) + warp * (kStages * kStageBytes);
+  {
+    const size_t first = s_begin + static_cast<size_t>(warp) * 16;
+    if (first < s_end) {
+#pragma unroll
+      for (int st = 0; st < kStages - 1; ++st)
+        fp8_stage_issue(ring + st * kStageBytes, first + st * (static_cast<size_t>(kWarps) * 16), s_begin, s_end, cache_k,
+                        cache_v, kv_heads, kvh);
+    }
+  }
   // Q fragments: step 4 j + i covers dims 64 j + 16 t + 4 i .. + 3 of head g, as float16
   if (warp == 0) {
 #pragma unroll
@@ -710,17 +730,16 @@ decode_split_fp8_staged_kernel(const __nv_bfloat16 *__restrict__ q, const uint8_
   }
   __syncthreads();
 
-  const uint32_t ring = static_cast<uint32_t>(__cvta_generic_to_shared(smem)) + warp * (kStages * kStageBytes);
   float o[2][8][4];
   float m_run, l_run;
-  fp8_staged_pass<G, false>(o, m_run, l_run, cache_k, cache_v, ring, s_q, s_begin, s_end, kv_heads, kvh);
+  fp8_staged_pass<G, false>(o, m_run, l_run, cache_k, cache_v, ring, s_q, s_begin, s_end, kv_heads, kvh, true);
   float probe = l_run;                                            // NaN anywhere in this thread's state?
 #pragma unroll
   for (int h = 0; h < 2; ++h)
 #pragma unroll
     for (int j = 0; j < 8; ++j) probe += (o[h][j][0] + o[h][j][1]) + (o[h][j][2] + o[h][j][3]);
   if (__syncthreads_or(probe != probe))
-    fp8_staged_pass<G, true>(o, m_run, l_run, cache_k, cache_v, ring, s_q, s_begin, s_end, kv_heads, kvh);
+    fp8_staged_pass<G, true>(o, m_run, l_run, cache_k, cache_v, ring, s_q, s_begin, s_end, kv_heads, kvh, false);
   __syncthreads();                                                // the ring becomes the epilogue's slices
   split_epilogue<G>(o, m_run, l_run, 1.0f / 64.0f, s_m, s_l, s_o, part_o, part_m, part_l, head0, split, n_splits);
 }
