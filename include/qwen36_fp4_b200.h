@@ -342,9 +342,8 @@ typedef struct {                         /* qwen36_fp4.h:151-183 */
  * the buffers one CTA per q head walks the whole context.  TurboQuant3 / 3.5
  * caches (dtype 2 / 3) return QWEN36_STATUS_NOT_IMPLEMENTED. */
 int qwen36_attention_decode(const qwen36_attention_decode_spec_t *spec);
-/* Test hooks: mode 0 = general kernel only, 1 = tensor-core kernels fed from
- * registers, 2 = the same with the FP8 cache staged through shared memory
- * (default); n > 0 overrides the number of splits used. */
+/* Test hooks: mode 0 = general kernel only, 1 = tensor-core kernels where they
+ * apply (default); n > 0 overrides the number of splits used. */
 void qwen36_attention_decode_set_mode(int mode);
 void qwen36_attention_decode_force_splits(int n);
 

@@ -45,7 +45,7 @@ constexpr int kMaxSplits = 256;              // the merge handles one partial pe
 constexpr uint32_t kMinTokensPerSplit = 256;
 constexpr int kKvBf16 = 0, kKvFp8 = 1;
 
-int g_decode_mode = 2;                       // test hook: 0 = general kernel only, 1 = tensor-core forms fed from registers, 2 = FP8 fed through shared memory
+int g_decode_mode = 1;                       // test hook: 0 = general kernel only, 1 = tensor-core forms where they apply
 int g_decode_force_splits = 0;               // test hook: > 0 overrides the split count
 
 // E4M3 byte -> float as the reference reads its cache (attention.cu:101-116): 0x7F / 0xFF are +-448.
@@ -261,16 +261,15 @@ decode_merge_append_kernel(const float *__restrict__ part_o, const float *__rest
 //
 // Both products run as mma.sync.m16n8k16 with float16 operands and float32 accumulation: E4M3 ->
 // float16 is exact (cvt.rn.f16x2.e4m3x2), q is rounded to float16, probabilities to float16 after
-// scaling by kPScale.  The reference reads the bytes 0x7F / 0xFF as +-448, which is what 0x7E /
-// 0xFE decode to, so those two bytes are rewritten before the conversion (the hardware would give
-// NaN).  Fragment plan, lane (g = lane / 4, t = lane % 4), a warp owns 16 tokens at a time:
+// scaling by kPScale.  Fragment plan, lane (g = lane / 4, t = lane % 4), a warp owns 16 tokens at
+// a time:
 //   S = Q K^T : A = Q (row g = q head g, rows >= G zero), B = K^T with token g of an 8-token block
-//       as its column; the contraction index is permuted so that a lane's operands are the
-//       sixteen consecutive bytes it loads: step 4 j + i covers dims 64 j + 16 t + 4 i .. + 3.
+//       as its column; the contraction index is permuted so that a lane's operands are sixteen
+//       consecutive bytes of a row: step 4 j + i covers dims 64 j + 16 t + 4 i .. + 3.
 //       The accumulator leaves lane (g, t) with head g's scores of tokens 2t, 2t + 1 of the block.
 //   O^T = V^T P^T : those scores are exactly the B fragment of the second product (column =
 //       head g, contraction slots 2t, 2t+1, 2t+8, 2t+9 = this lane's tokens), so probabilities
-//       stay in registers.  A = V^T: a lane loads dims 16 (g + 8 h) .. + 15 of its four tokens and
+//       stay in registers.  A = V^T: a lane reads dims 16 (g + 8 h) .. + 15 of its four tokens and
 //       pairs bytes of neighbouring tokens; mma (h, j) has dim 16 (g + 8 h) + 2 j in row g and the
 //       next dim in row g + 8; its accumulator holds heads 2t, 2t + 1 of those two dims.
 // four E4M3 bytes -> two float16x2 (bytes 0, 1 and bytes 2, 3)
@@ -287,223 +286,16 @@ __device__ __forceinline__ uint4 e4m3_nan_to_448(uint4 v) {
   return make_uint4(e4m3_nan_to_448(v.x), e4m3_nan_to_448(v.y), e4m3_nan_to_448(v.z), e4m3_nan_to_448(v.w));
 }
 
-template <int G>
-__global__ void __launch_bounds__(kThreads, 1)
-decode_split_fp8_mma_kernel(const __nv_bfloat16 *__restrict__ q, const uint8_t *__restrict__ cache_k,
-                            const uint8_t *__restrict__ cache_v, float *__restrict__ part_o,
-                            float *__restrict__ part_m, float *__restrict__ part_l, size_t position_scalar,
-                            const int32_t *__restrict__ position_device, uint32_t kv_heads, uint32_t q_per_kv,
-                            uint32_t n_splits) {
-  constexpr uint32_t D = 256;
-  constexpr float kPScale = 64.0f;                                // keeps small probabilities out of the float16 subnormals
-  __shared__ float s_m[kWarps][8], s_l[kWarps][8];
-  __shared__ float s_o[4 * G][kEpiStride];
-  __shared__ uint2 s_q[16][32];
-
-  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-  const uint32_t g = lane >> 2, t = lane & 3u;
-  const uint32_t head0 = blockIdx.x * G;
-  const uint32_t kvh = head0 / q_per_kv;
-  const uint32_t split = blockIdx.y;
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the merge may take its seats early
-  const size_t position = read_position(position_scalar, position_device);
-  size_t s_begin, s_end;
-  split_range(position, n_splits, split, s_begin, s_end);         // whole rounds of 8 warps x 16 tokens
-  const float sm_scale = 0.0625f * 1.4426950408889634f;           // rsqrt(256) * log2(e)
-
-  float o[2][8][4];
-#pragma unroll
-  for (int h = 0; h < 2; ++h)
-#pragma unroll
-    for (int j = 0; j < 8; ++j)
-#pragma unroll
-      for (int c = 0; c < 4; ++c) o[h][j][c] = 0.f;
-  float m_run = -INFINITY, l_run = 0.f;                           // head g, identical on its four lanes
-
-  // tokens of lane t inside a 16-token group: 2t, 2t + 1, 8 + 2t, 9 + 2t
-  struct KBuf { uint4 k[2][4]; };
-  struct VBuf { uint4 v[4][2]; };
-  auto load_k = [&](KBuf &b, size_t t0) {
-#pragma unroll
-    for (int blk = 0; blk < 2; ++blk) {
-      const size_t tok = t0 + 8 * blk + g;
-      if (tok < s_end) {
-        const uint4 *src = reinterpret_cast<const uint4 *>(cache_k + (tok * kv_heads + kvh) * D) + t;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) b.k[blk][j] = __ldcs(src + 4 * j);
-      } else {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) b.k[blk][j] = make_uint4(0, 0, 0, 0);
-      }
-    }
-  };
-  auto load_v = [&](VBuf &b, size_t t0) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const size_t tok = t0 + 2 * t + (i & 1) + 8 * (i >> 1);
-      if (tok < s_end) {
-        const uint4 *src = reinterpret_cast<const uint4 *>(cache_v + (tok * kv_heads + kvh) * D) + g;
-        b.v[i][0] = __ldcs(src);
-        b.v[i][1] = __ldcs(src + 8);
-      } else {
-        b.v[i][0] = b.v[i][1] = make_uint4(0, 0, 0, 0);
-      }
-    }
-  };
-  // S = Q K^T for the two 8-token blocks of a group: four independent accumulator chains (two
-  // blocks x even / odd steps); out = this lane's scores of tokens 2t, 2t+1, 8+2t, 9+2t
-  auto scores = [&](const KBuf &b, float (&out)[4]) {
-    float acc[2][2][4];
-#pragma unroll
-    for (int blk = 0; blk < 2; ++blk)
-#pragma unroll
-      for (int par = 0; par < 2; ++par)
-#pragma unroll
-        for (int c = 0; c < 4; ++c) acc[blk][par][c] = 0.f;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      uint32_t w[2][4];
-#pragma unroll
-      for (int blk = 0; blk < 2; ++blk) {
-        const uint4 fixed = e4m3_nan_to_448(b.k[blk][j]);
-        w[blk][0] = fixed.x; w[blk][1] = fixed.y; w[blk][2] = fixed.z; w[blk][3] = fixed.w;
-      }
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const uint2 qf = s_q[4 * j + i][lane];
-#pragma unroll
-        for (int blk = 0; blk < 2; ++blk) {
-          uint32_t b0, b1;
-          e4m3x4_to_h2x2(w[blk][i], b0, b1);
-          mma_f16(acc[blk][i & 1], qf.x, 0u, qf.y, 0u, b0, b1);
-        }
-      }
-    }
-#pragma unroll
-    for (int blk = 0; blk < 2; ++blk) {
-      out[2 * blk] = acc[blk][0][0] + acc[blk][1][0];
-      out[2 * blk + 1] = acc[blk][0][1] + acc[blk][1][1];
-    }
-  };
-
-  // Software pipeline over this warp's groups: while the probabilities of group n multiply V, the
-  // scores of group n + 1 are already being formed, K of group n + 2 and V of group n + 1 are in flight.
-  const size_t stride = static_cast<size_t>(kWarps) * 16;
-  KBuf k_now, k_next;               // K of group n + 1 (scored during iteration n), K of group n + 2
-  VBuf v_now, v_next;               // V of group n, of group n + 1
-  float sc_[4] = {0.f, 0.f, 0.f, 0.f}, sc_next[4];
-  size_t t0 = s_begin + static_cast<size_t>(warp) * 16;
-  if (t0 < s_end) {                                  // first loads fly while q is staged
-    load_k(k_next, t0);
-    load_v(v_now, t0);
-    load_k(k_now, t0 + stride);                      // past-the-end groups load zeros
-  }
-
-  // Q fragments (the same for every warp, so they live in shared memory): step s = 4 j + i covers
-  // dims 64 j + 16 t + 4 i .. + 3 of head g
-  if (warp == 0) {
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      uint4 raw0 = make_uint4(0, 0, 0, 0), raw1 = make_uint4(0, 0, 0, 0);
-      if (g < G) {
-        const uint4 *src = reinterpret_cast<const uint4 *>(q + static_cast<size_t>(head0 + g) * D + 64 * j + 16 * t);
-        raw0 = __ldg(src);
-        raw1 = __ldg(src + 1);
-      }
-      const uint32_t w[8] = {raw0.x, raw0.y, raw0.z, raw0.w, raw1.x, raw1.y, raw1.z, raw1.w};
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          const uint32_t pair = w[2 * i + half];                  // two bf16: dims 4 i + 2 half, + 1
-          const __half2 h = __floats2half2_rn(__uint_as_float(pair << 16), __uint_as_float(pair & 0xffff0000u));
-          reinterpret_cast<uint32_t *>(&s_q[4 * j + i][lane])[half] = *reinterpret_cast<const uint32_t *>(&h);
-        }
-      }
-    }
-  }
-  __syncthreads();
-
-  if (t0 < s_end) scores(k_next, sc_);
-  for (; t0 < s_end; t0 += stride) {
-    load_k(k_next, t0 + 2 * stride);
-    load_v(v_next, t0 + stride);
-    // ---- online softmax, head g: this lane's four tokens, then the four lanes of the head
-    float s_log2[4];
-    float tile_max = -INFINITY;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const size_t tok = t0 + 2 * t + (i & 1) + 8 * (i >> 1);
-      const bool valid = g < G && tok < s_end;
-      s_log2[i] = valid ? sc_[i] * sm_scale : -INFINITY;
-      tile_max = fmaxf(tile_max, s_log2[i]);
-    }
-    tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 1));
-    tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 2));
-    const float m_new = fmaxf(m_run, tile_max);
-    const float corr = m_new == -INFINITY ? 1.f : exp2f(m_run - m_new);
-    float p[4], p_sum = 0.f;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      p[i] = s_log2[i] == -INFINITY ? 0.f : exp2f(s_log2[i] - m_new);
-      p_sum += p[i];
-    }
-    p_sum += __shfl_xor_sync(0xffffffffu, p_sum, 1);
-    p_sum += __shfl_xor_sync(0xffffffffu, p_sum, 2);
-    l_run = l_run * corr + p_sum;
-    m_run = m_new;
-    const __half2 pb0 = __floats2half2_rn(p[0] * kPScale, p[1] * kPScale);
-    const __half2 pb1 = __floats2half2_rn(p[2] * kPScale, p[3] * kPScale);
-    const uint32_t b0 = *reinterpret_cast<const uint32_t *>(&pb0), b1 = *reinterpret_cast<const uint32_t *>(&pb1);
-    // ---- scores of the next group (nothing below depends on them)
-    scores(k_now, sc_next);
-    // ---- rescale the running output: this lane's accumulators belong to heads 2t and 2t + 1
-    const float c_even = __shfl_sync(0xffffffffu, corr, 8 * t), c_odd = __shfl_sync(0xffffffffu, corr, 8 * t + 4);
-    if (__any_sync(0xffffffffu, corr != 1.f)) {
-#pragma unroll
-      for (int h = 0; h < 2; ++h)
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          o[h][j][0] *= c_even; o[h][j][1] *= c_odd; o[h][j][2] *= c_even; o[h][j][3] *= c_odd;
-        }
-    }
-    // ---- O^T += V^T P^T
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const uint4 fa = e4m3_nan_to_448(v_now.v[0][h]), fb = e4m3_nan_to_448(v_now.v[1][h]);
-      const uint4 fc = e4m3_nan_to_448(v_now.v[2][h]), fd = e4m3_nan_to_448(v_now.v[3][h]);
-      const uint32_t va[4] = {fa.x, fa.y, fa.z, fa.w}, vb[4] = {fb.x, fb.y, fb.z, fb.w};
-      const uint32_t vc[4] = {fc.x, fc.y, fc.z, fc.w}, vd[4] = {fd.x, fd.y, fd.z, fd.w};
-#pragma unroll
-      for (int w = 0; w < 4; ++w) {                                // word w holds dims 4 w .. 4 w + 3 of the chunk
-        // bytes of neighbouring tokens side by side: (a.b0, b.b0, a.b1, b.b1) and (a.b2, b.b2, a.b3, b.b3)
-        uint32_t ab0, ab1, ab2, ab3, cd0, cd1, cd2, cd3;
-        e4m3x4_to_h2x2(__byte_perm(va[w], vb[w], 0x5140), ab0, ab1);
-        e4m3x4_to_h2x2(__byte_perm(va[w], vb[w], 0x7362), ab2, ab3);
-        e4m3x4_to_h2x2(__byte_perm(vc[w], vd[w], 0x5140), cd0, cd1);
-        e4m3x4_to_h2x2(__byte_perm(vc[w], vd[w], 0x7362), cd2, cd3);
-        mma_f16(o[h][2 * w], ab0, ab1, cd0, cd1, b0, b1);
-        mma_f16(o[h][2 * w + 1], ab2, ab3, cd2, cd3, b0, b1);
-      }
-    }
-    k_now = k_next;
-    v_now = v_next;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) sc_[i] = sc_next[i];
-  }
-
-  split_epilogue<G>(o, m_run, l_run, 1.0f / kPScale, s_m, s_l, s_o, part_o, part_m, part_l, head0, split, n_splits);
-}
-
-// ---- FP8 cache, staged form: the same two products, but K / V travel global -> shared memory
-// with 16-byte asynchronous copies (cp.async) into a private three-stage ring per warp, so the
+// K / V travel global -> shared memory with 16-byte asynchronous copies (cp.async) into a private
+// three-stage ring per warp, so the
 // bytes in flight (two stages = 16 KB per warp, 128 KB per SM) no longer have to fit in
 // registers.  A stage holds the K and the V rows of a 16-token group (256 bytes each); 16-byte
 // chunks are XOR-swizzled on the way in so that the fragment reads are free of bank conflicts:
 // K chunk c of row r sits at c ^ 4 (r & 1), V chunk c of row r at c ^ 2 ((r / 2) & 3).  No block
 // barrier inside the loop: a warp waits for its own copies (wait_group + __syncwarp).
-// The 0x7F / 0xFF bytes (which the cache append never writes) are handled out of line: the fast
-// pass converts bytes as they are; a NaN anywhere in the CTA's result sends the CTA through a
+// The reference reads the bytes 0x7F / 0xFF as +-448 (what 0x7E / 0xFE decode to) where the
+// hardware conversion gives NaN.  The cache append never writes them, so they are handled out of
+// line: the fast pass converts bytes as they are; a NaN anywhere in the CTA's result sends the CTA through a
 // second pass that rewrites those bytes first (template flag FIX).
 constexpr int kStages = 3;
 constexpr uint32_t kTileBytes = 16 * 256;                         // 16 tokens x 256 bytes
@@ -605,42 +397,19 @@ __device__ __forceinline__ void fp8_staged_pass(float (&o)[2][8][4], float &m_ru
         sc_[2 * blk + 1] = acc[blk][0][1] + acc[blk][1][1];
       }
     }
-    // ---- online softmax, head g
+    // ---- online softmax, head g: this lane's four tokens, then the four lanes of the head
     float s_log2[4];
-    float tile_max = -INFINITY;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const size_t tok = t0 + 2 * t + (i & 1) + 8 * (i >> 1);
-      const bool valid = g < G && tok < s_end;
-      s_log2[i] = valid ? sc_[i] * sm_scale : -INFINITY;
-      tile_max = fmaxf(tile_max, s_log2[i]);
+      s_log2[i] = (g < G && tok < s_end) ? sc_[i] * sm_scale : -INFINITY;
     }
-    tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 1));
-    tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 2));
-    const float m_new = fmaxf(m_run, tile_max);
-    const float corr = m_new == -INFINITY ? 1.f : exp2f(m_run - m_new);
-    float p[4], p_sum = 0.f;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      p[i] = s_log2[i] == -INFINITY ? 0.f : exp2f(s_log2[i] - m_new);
-      p_sum += p[i];
-    }
-    p_sum += __shfl_xor_sync(0xffffffffu, p_sum, 1);
-    p_sum += __shfl_xor_sync(0xffffffffu, p_sum, 2);
-    l_run = l_run * corr + p_sum;
-    m_run = m_new;
+    float p[4];
+    const float corr = q36::online_softmax_step(s_log2, p, m_run, l_run);
     const __half2 pb0 = __floats2half2_rn(p[0] * kPScale, p[1] * kPScale);
     const __half2 pb1 = __floats2half2_rn(p[2] * kPScale, p[3] * kPScale);
     const uint32_t b0 = *reinterpret_cast<const uint32_t *>(&pb0), b1 = *reinterpret_cast<const uint32_t *>(&pb1);
-    const float c_even = __shfl_sync(0xffffffffu, corr, 8 * t), c_odd = __shfl_sync(0xffffffffu, corr, 8 * t + 4);
-    if (__any_sync(0xffffffffu, corr != 1.f)) {
-#pragma unroll
-      for (int h = 0; h < 2; ++h)
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          o[h][j][0] *= c_even; o[h][j][1] *= c_odd; o[h][j][2] *= c_even; o[h][j][3] *= c_odd;
-        }
-    }
+    q36::rescale_outputs(o, corr);
     // ---- O^T += V^T P^T: rows 2t, 2t + 1, 2t + 8, 2t + 9 of the V tile, chunk g + 8 h
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -883,39 +652,15 @@ decode_split_bf16_mma_kernel(const __nv_bfloat16 *__restrict__ q, const __nv_bfl
     load_k(kb, t0 + stride);                         // refill for the next group (zeros past the end)
     // ---- online softmax, head g: this lane's four tokens, then the four lanes of the head
     float s_log2[4];
-    float tile_max = -INFINITY;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const size_t tok = t0 + 2 * t + (i & 1) + 8 * (i >> 1);
-      const bool valid = g < G && tok < s_end;
-      s_log2[i] = valid ? sc_[i] * sm_scale : -INFINITY;
-      tile_max = fmaxf(tile_max, s_log2[i]);
+      s_log2[i] = (g < G && tok < s_end) ? sc_[i] * sm_scale : -INFINITY;
     }
-    tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 1));
-    tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 2));
-    const float m_new = fmaxf(m_run, tile_max);
-    const float corr = m_new == -INFINITY ? 1.f : exp2f(m_run - m_new);
-    float p[4], p_sum = 0.f;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      p[i] = s_log2[i] == -INFINITY ? 0.f : exp2f(s_log2[i] - m_new);
-      p_sum += p[i];
-    }
-    p_sum += __shfl_xor_sync(0xffffffffu, p_sum, 1);
-    p_sum += __shfl_xor_sync(0xffffffffu, p_sum, 2);
-    l_run = l_run * corr + p_sum;
-    m_run = m_new;
+    float p[4];
+    const float corr = q36::online_softmax_step(s_log2, p, m_run, l_run);
     const uint32_t b0 = pack_bf16x2(p[0], p[1]), b1 = pack_bf16x2(p[2], p[3]);
-    // ---- rescale the running output: this lane's accumulators belong to heads 2t and 2t + 1
-    const float c_even = __shfl_sync(0xffffffffu, corr, 8 * t), c_odd = __shfl_sync(0xffffffffu, corr, 8 * t + 4);
-    if (__any_sync(0xffffffffu, corr != 1.f)) {
-#pragma unroll
-      for (int h = 0; h < 2; ++h)
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          o[h][j][0] *= c_even; o[h][j][1] *= c_odd; o[h][j][2] *= c_even; o[h][j][3] *= c_odd;
-        }
-    }
+    q36::rescale_outputs(o, corr);
     // ---- O^T += V^T P^T: word w of a token's 32 bytes holds dims 2 w, 2 w + 1
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -961,14 +706,6 @@ int launch_direct(const Args &a) {
   decode_split_general_kernel<FP8, true><<<dim3(a.q_heads, 1), kThreads, 0, q36::stream()>>>(
       a.q, a.k_new, a.v_new, a.cache_k, a.cache_v, nullptr, nullptr, nullptr, a.out, a.position, a.position_device,
       a.kv_heads, a.q_per_kv, a.head_dim, 1u);
-  return q36::launch_status();
-}
-
-template <int G>
-int launch_fp8_mma(const Args &a, uint32_t n_splits) {
-  decode_split_fp8_mma_kernel<G><<<dim3(a.q_heads / G, n_splits), kThreads, 0, q36::stream()>>>(
-      a.q, static_cast<const uint8_t *>(a.cache_k), static_cast<const uint8_t *>(a.cache_v), a.part_o, a.part_m,
-      a.part_l, a.position, a.position_device, a.kv_heads, a.q_per_kv, n_splits);
   return q36::launch_status();
 }
 
@@ -1040,8 +777,7 @@ int run_split_path(const Args &a, size_t caller_splits) {
   uint32_t n;
   if (g_decode_mode >= 1 && a.head_dim == 256 && aligned16 && grouped) {
     n = pick_splits(a, caller_splits, a.kv_heads, true);
-#define Q36_DECODE_GO(G) \
-  status = !FP8 ? launch_bf16_mma<G>(a, n) : (g_decode_mode == 2 ? launch_fp8_staged<G>(a, n) : launch_fp8_mma<G>(a, n))
+#define Q36_DECODE_GO(G) status = FP8 ? launch_fp8_staged<G>(a, n) : launch_bf16_mma<G>(a, n)
     switch (a.q_per_kv) {
       case 1: Q36_DECODE_GO(1); break;
       case 2: Q36_DECODE_GO(2); break;
@@ -1063,7 +799,7 @@ int run_split_path(const Args &a, size_t caller_splits) {
 
 }  // namespace
 
-extern "C" void qwen36_attention_decode_set_mode(int mode) { g_decode_mode = mode < 0 ? 0 : (mode > 2 ? 2 : mode); }
+extern "C" void qwen36_attention_decode_set_mode(int mode) { g_decode_mode = mode != 0 ? 1 : 0; }
 extern "C" void qwen36_attention_decode_force_splits(int n) { g_decode_force_splits = n < 0 ? 0 : n; }
 
 extern "C" int qwen36_attention_decode(const qwen36_attention_decode_spec_t *spec) {

@@ -551,8 +551,7 @@ kv_attention_mma_kernel(const __nv_bfloat16 *__restrict__ q, const int8_t *__res
   constexpr uint32_t D = 256;
   constexpr float kPScale = 1024.0f;                              // keeps p * v_scale out of the float16 subnormals
   __shared__ float s_m[kWarps][8], s_l[kWarps][8];
-  constexpr uint32_t DP = D + 4;                                  // row stride: heads land a quarter of the banks apart
-  __shared__ float s_o[4 * G][DP];
+  __shared__ float s_o[4 * G][q36::kEpiStride];
 
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
   const uint32_t g = lane >> 2, t = lane & 3u;
@@ -702,43 +701,20 @@ kv_attention_mma_kernel(const __nv_bfloat16 *__restrict__ q, const int8_t *__res
     load_v(v_next, t0 + stride);
     // ---- online softmax, head g: this lane's four tokens, then the four lanes of the head
     float s_log2[4];
-    float tile_max = -INFINITY;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const size_t tok = t0 + 2 * t + (i & 1) + 8 * (i >> 1);
-      const bool valid = g < G && tok < s_end;
-      s_log2[i] = valid ? sc_[i] * v_now.sc[i].x * sm_scale : -INFINITY;
-      tile_max = fmaxf(tile_max, s_log2[i]);
+      s_log2[i] = (g < G && tok < s_end) ? sc_[i] * v_now.sc[i].x * sm_scale : -INFINITY;
     }
-    tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 1));
-    tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 2));
-    const float m_new = fmaxf(m_run, tile_max);
-    const float corr = m_new == -INFINITY ? 1.f : exp2f(m_run - m_new);
-    float p[4], p_sum = 0.f;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      p[i] = s_log2[i] == -INFINITY ? 0.f : exp2f(s_log2[i] - m_new);
-      p_sum += p[i];
-    }
-    p_sum += __shfl_xor_sync(0xffffffffu, p_sum, 1);
-    p_sum += __shfl_xor_sync(0xffffffffu, p_sum, 2);
-    l_run = l_run * corr + p_sum;
-    m_run = m_new;
+    float p[4];
+    const float corr = q36::online_softmax_step(s_log2, p, m_run, l_run);
     const __half2 pb0 = __floats2half2_rn(p[0] * v_now.sc[0].y * kPScale, p[1] * v_now.sc[1].y * kPScale);
     const __half2 pb1 = __floats2half2_rn(p[2] * v_now.sc[2].y * kPScale, p[3] * v_now.sc[3].y * kPScale);
     const uint32_t b0 = *reinterpret_cast<const uint32_t *>(&pb0), b1 = *reinterpret_cast<const uint32_t *>(&pb1);
     // ---- scores of the next group (nothing below depends on them)
     scores(k_now, sc_next);
     // ---- rescale the running output: this lane's accumulators belong to heads 2t and 2t + 1
-    const float c_even = __shfl_sync(0xffffffffu, corr, 8 * t), c_odd = __shfl_sync(0xffffffffu, corr, 8 * t + 4);
-    if (__any_sync(0xffffffffu, corr != 1.f)) {
-#pragma unroll
-      for (int h = 0; h < 2; ++h)
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          o[h][j][0] *= c_even; o[h][j][1] *= c_odd; o[h][j][2] *= c_even; o[h][j][3] *= c_odd;
-        }
-    }
+    q36::rescale_outputs(o, corr);
     // ---- O^T += V^T P^T
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -760,55 +736,7 @@ kv_attention_mma_kernel(const __nv_bfloat16 *__restrict__ q, const int8_t *__res
     for (int i = 0; i < 4; ++i) sc_[i] = sc_next[i];
   }
 
-  // ---- merge the warps of the CTA: weights per head from the running maxima; the weighted outputs
-  // meet in four shared-memory slices (warps 4..7 write, warps 0..3 add), then every thread sums
-  // the four slices of its outputs
-  if (t == 0 && g < G) { s_m[warp][g] = m_run; s_l[warp][g] = l_run; }
-  __syncthreads();
-  float wgt[2];                                                    // heads 2t, 2t + 1
-#pragma unroll
-  for (int e = 0; e < 2; ++e) {
-    const uint32_t head = 2 * t + e;
-    float M = -INFINITY;
-    if (head < G)
-      for (int w = 0; w < kWarps; ++w) M = fmaxf(M, s_m[w][head]);
-    const float mine = head < G ? s_m[warp][head] : -INFINITY;
-    wgt[e] = mine == -INFINITY ? 0.f : exp2f(mine - M) * (1.0f / kPScale);
-  }
-  float (*slice)[DP] = &s_o[(warp & 3u) * G];
-  for (int round = 0; round < 2; ++round) {
-    if ((warp >> 2) == static_cast<uint32_t>(1 - round)) {
-#pragma unroll
-      for (int h = 0; h < 2; ++h)
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            // dims are stored XOR-swizzled inside their 16-float chunk (chunk index = g + 8 h), so
-            // that the eight chunks a warp writes at once fall on different banks
-            const uint32_t head = 2 * t + (c & 1), dim = 16 * (g + 8 * h) + ((2 * j + (c >> 1)) ^ (g + 8 * h));
-            if (head < G) {
-              float *dst = &slice[head][dim];
-              *dst = round == 0 ? wgt[c & 1] * o[h][j][c] : fmaf(wgt[c & 1], o[h][j][c], *dst);
-            }
-          }
-    }
-    __syncthreads();
-  }
-  for (uint32_t idx = threadIdx.x; idx < G * D; idx += kThreads) {
-    const uint32_t hd = idx / D, d = idx % D;
-    const size_t slot = static_cast<size_t>(head0 + hd) * n_splits + split;
-    const uint32_t ds = d ^ ((d >> 4) & 15u);                      // undo the swizzle
-    part_o[slot * D + d] = (s_o[hd][ds] + s_o[G + hd][ds]) + (s_o[2 * G + hd][ds] + s_o[3 * G + hd][ds]);
-    if (d == 0) {
-      float M = -INFINITY, den = 0.f;
-      for (int w = 0; w < kWarps; ++w) M = fmaxf(M, s_m[w][hd]);
-      for (int w = 0; w < kWarps; ++w)
-        den = fmaf(s_m[w][hd] == -INFINITY ? 0.f : exp2f(s_m[w][hd] - M), s_l[w][hd], den);
-      part_m[slot] = M * 0.6931471805599453f;
-      part_l[slot] = den;
-    }
-  }
+  q36::split_epilogue<G>(o, m_run, l_run, 1.0f / kPScale, s_m, s_l, s_o, part_o, part_m, part_l, head0, split, n_splits);
 }
 
 // ---- tensor-core form fed through shared memory.  Same products and fragment plan as
@@ -981,41 +909,18 @@ kv_attention_staged_kernel(const __nv_bfloat16 *__restrict__ q, const int8_t *__
       asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(scl[i].x), "=f"(scl[i].y) : "r"(mt + row * 8u));
     }
     float s_log2[4];
-    float tile_max = -INFINITY;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const size_t tok = t0 + 2 * t + (i & 1) + 8 * (i >> 1);
-      const bool valid = g < G && tok < s_end;
-      s_log2[i] = valid ? sc_[i] * scl[i].x * sm_scale : -INFINITY;
-      tile_max = fmaxf(tile_max, s_log2[i]);
+      s_log2[i] = (g < G && tok < s_end) ? sc_[i] * scl[i].x * sm_scale : -INFINITY;
     }
-    tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 1));
-    tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 2));
-    const float m_new = fmaxf(m_run, tile_max);
-    const float corr = m_new == -INFINITY ? 1.f : exp2f(m_run - m_new);
-    float p[4], p_sum = 0.f;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      p[i] = s_log2[i] == -INFINITY ? 0.f : exp2f(s_log2[i] - m_new);
-      p_sum += p[i];
-    }
-    p_sum += __shfl_xor_sync(0xffffffffu, p_sum, 1);
-    p_sum += __shfl_xor_sync(0xffffffffu, p_sum, 2);
-    l_run = l_run * corr + p_sum;
-    m_run = m_new;
+    float p[4];
+    const float corr = q36::online_softmax_step(s_log2, p, m_run, l_run);
     const __half2 pb0 = __floats2half2_rn(p[0] * scl[0].y * kPScale, p[1] * scl[1].y * kPScale);
     const __half2 pb1 = __floats2half2_rn(p[2] * scl[2].y * kPScale, p[3] * scl[3].y * kPScale);
     const uint32_t b0 = *reinterpret_cast<const uint32_t *>(&pb0), b1 = *reinterpret_cast<const uint32_t *>(&pb1);
     // ---- rescale the running output: this lane's accumulators belong to heads 2t and 2t + 1
-    const float c_even = __shfl_sync(0xffffffffu, corr, 8 * t), c_odd = __shfl_sync(0xffffffffu, corr, 8 * t + 4);
-    if (__any_sync(0xffffffffu, corr != 1.f)) {
-#pragma unroll
-      for (int h = 0; h < 2; ++h)
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          o[h][j][0] *= c_even; o[h][j][1] *= c_odd; o[h][j][2] *= c_even; o[h][j][3] *= c_odd;
-        }
-    }
+    q36::rescale_outputs(o, corr);
     // ---- O^T += V^T P^T: rows 2t, 2t + 1, 2t + 8, 2t + 9 of the V tile, chunk g + 8 h
 #pragma unroll
     for (int h = 0; h < 2; ++h) {

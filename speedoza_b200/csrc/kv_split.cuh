@@ -52,6 +52,45 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
 }
 
 
+// One step of the online softmax for head g (the four lanes t = 0 .. 3 of a lane group hold its
+// sixteen tokens): s_log2[i] are this lane's four scores in log2 units (-inf = masked).  Updates
+// the running maximum and sum (identical on the four lanes), leaves the probabilities in p and
+// returns the factor by which everything accumulated so far has to be scaled.
+__device__ __forceinline__ float online_softmax_step(const float (&s_log2)[4], float (&p)[4], float &m_run,
+                                                     float &l_run) {
+  float tile_max = fmaxf(fmaxf(s_log2[0], s_log2[1]), fmaxf(s_log2[2], s_log2[3]));
+  tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 1));
+  tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 2));
+  const float m_new = fmaxf(m_run, tile_max);
+  const float corr = m_new == -INFINITY ? 1.f : exp2f(m_run - m_new);
+  float p_sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    p[i] = s_log2[i] == -INFINITY ? 0.f : exp2f(s_log2[i] - m_new);
+    p_sum += p[i];
+  }
+  p_sum += __shfl_xor_sync(0xffffffffu, p_sum, 1);
+  p_sum += __shfl_xor_sync(0xffffffffu, p_sum, 2);
+  l_run = l_run * corr + p_sum;
+  m_run = m_new;
+  return corr;
+}
+
+// Scales the running outputs by the heads' correction factors: lane (g, t) holds heads 2t and
+// 2t + 1 in its accumulators, whose factors live on lanes 8t and 8t + 4.
+__device__ __forceinline__ void rescale_outputs(float (&o)[2][8][4], float corr) {
+  const uint32_t t = threadIdx.x & 3u;
+  const float c_even = __shfl_sync(0xffffffffu, corr, 8 * t), c_odd = __shfl_sync(0xffffffffu, corr, 8 * t + 4);
+  if (__any_sync(0xffffffffu, corr != 1.f)) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        o[h][j][0] *= c_even; o[h][j][1] *= c_odd; o[h][j][2] *= c_even; o[h][j][3] *= c_odd;
+      }
+  }
+}
+
 // Epilogue shared by the tensor-core split kernels: merges the eight warps' running softmax states
 // (maxima in log2 units, outputs scaled by 1 / out_scale) and writes the CTA's partial.
 // o[h][j][c]: head 2t + (c & 1), dim 16 (g + 8 h) + 2 j + (c >> 1).
