@@ -246,12 +246,14 @@ decode_merge_append_kernel(const float *__restrict__ part_o, const float *__rest
   // the partials are complete (a no-op after an ordinary launch)
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const float *po = part_o + static_cast<size_t>(qh) * n_parts * head_dim;
+  const uint32_t d = min(threadIdx.x, head_dim - 1);              // idle threads fetch a valid address
+  float first[16];
+  q36::lse_prefetch(po, n_parts, head_dim, d, first);             // in flight while the weights are formed
   float M, den;
   q36::lse_weights(part_m + static_cast<size_t>(qh) * n_parts, part_l + static_cast<size_t>(qh) * n_parts, n_parts,
                    s_w, s_red, M, den);
-  const float acc = threadIdx.x < head_dim
-      ? q36::lse_accumulate(part_o + static_cast<size_t>(qh) * n_parts * head_dim, s_w, n_parts, head_dim, threadIdx.x)
-      : 0.f;
+  const float acc = threadIdx.x < head_dim ? q36::lse_accumulate(po, s_w, n_parts, head_dim, d, first) : 0.f;
   __syncthreads();                                                // s_red is reused below
   finish_head<FP8>(acc, M, den, q, k_new, v_new, cache_k, cache_v, out, position, qh, kv_heads, q_per_kv, head_dim,
                    s_red);

@@ -37,12 +37,24 @@ __device__ __forceinline__ void lse_weights(const float *pm, const float *pl, ui
   den_out = den;
 }
 
+// The first sixteen parts' values of output dim d, fetched ahead of the weights (the loads then
+// travel while lse_weights runs its reductions).  Clamped indices: no branch, no out-of-range read.
+__device__ __forceinline__ void lse_prefetch(const float *po, uint32_t n_parts, uint32_t head_dim, uint32_t d,
+                                             float (&v)[16]) {
+#pragma unroll
+  for (uint32_t i = 0; i < 16; ++i) v[i] = __ldcg(po + static_cast<size_t>(min(i, n_parts - 1)) * head_dim + d);
+}
+
 // sum over parts of s_w[s] * po[s * head_dim + d], in part order; sixteen loads in flight at a time
-// (a plain loop pays the L2 latency once per part in its remainder iterations)
+// (a plain loop pays the L2 latency once per part in its remainder iterations).  `first` holds the
+// values of parts 0 .. 15 from lse_prefetch.
 __device__ __forceinline__ float lse_accumulate(const float *po, const float *s_w, uint32_t n_parts,
-                                                uint32_t head_dim, uint32_t d) {
+                                                uint32_t head_dim, uint32_t d, const float (&first)[16]) {
   float acc = 0.f;
-  for (uint32_t s0 = 0; s0 < n_parts; s0 += 16) {
+#pragma unroll
+  for (uint32_t i = 0; i < 16; ++i)
+    if (i < n_parts) acc = fmaf(s_w[i], first[i], acc);
+  for (uint32_t s0 = 16; s0 < n_parts; s0 += 16) {
     float v[16];
 #pragma unroll
     for (uint32_t i = 0; i < 16; ++i)
@@ -52,6 +64,13 @@ __device__ __forceinline__ float lse_accumulate(const float *po, const float *s_
       if (s0 + i < n_parts) acc = fmaf(s_w[s0 + i], v[i], acc);
   }
   return acc;
+}
+
+__device__ __forceinline__ float lse_accumulate(const float *po, const float *s_w, uint32_t n_parts,
+                                                uint32_t head_dim, uint32_t d) {
+  float first[16];
+  lse_prefetch(po, n_parts, head_dim, d, first);
+  return lse_accumulate(po, s_w, n_parts, head_dim, d, first);
 }
 
 }  // namespace q36
