@@ -178,7 +178,8 @@ def shard_rows(n: int, rank: int, world: int):
 
 class SweepRunner:
     """Chains the six GEMVs of every layer: q_gate, k, v <- x ; o <- q_gate[:6144] ;
-    gate_up <- o ; down <- gate_up[:17408] ; next x <- down."""
+    gate_up <- o ; down <- gate_up[:17408] ; next x <- down.  On one GPU the three projections
+    that share x go out as ONE launch (qwen36_nvfp4_matvec_group), so a layer is four launches."""
 
     def __init__(self, backend, torch, sweep, world: int, dist=None):
         self.b, self.torch, self.sweep, self.world, self.dist = backend, torch, sweep, world, dist
@@ -188,6 +189,7 @@ class SweepRunner:
         self.local = {m[0]: torch.zeros(max(m[1], 1), dtype=torch.bfloat16, device=dev) for m in sweep[0]}
         self.x = torch.zeros(5120, dtype=torch.bfloat16, device=dev)
         self.launches = 0
+        self.group_qkv = True
 
     def gemv(self, mat, x):
         name, n_local, k, packed, sf, ts, n_full = mat
@@ -207,12 +209,20 @@ class SweepRunner:
         from speedoza_b200 import shard
         shard.all_gather_rows(out_local, n_full, self.world, out)
 
-    def step(self, x0):
-        x = x0
-        for mats in self.sweep:
+    def qkv(self, mats, x):
+        if self.world != 1 or not self.group_qkv:
             qg = self.gemv(mats[0], x)
             self.gemv(mats[1], x)
             self.gemv(mats[2], x)
+            return qg
+        self.b.nvfp4_matvec_group(x, [(m[3], m[4], m[5], self.full[m[0]]) for m in mats[:3]])
+        self.launches += 1
+        return self.full[mats[0][0]]
+
+    def step(self, x0):
+        x = x0
+        for mats in self.sweep:
+            qg = self.qkv(mats, x)
             o = self.gemv(mats[3], qg[:6144])
             gu = self.gemv(mats[4], o)
             x = self.gemv(mats[5], gu[:17408])
@@ -255,6 +265,31 @@ def per_shape_cold(backend, torch, sweep, synth):
             backend.nvfp4_matvec(x, m[3], m[4], m[5], y)
         us = _time_cuda(torch, call, 192, warm=20, backend=backend)
         out[name] = {"n": n, "k": k, "us": round(us, 3), "gbs": round(gemv_bytes(n, k) / us / 1e3, 1)}
+    # q_gate + k + v as one grouped launch (what the sweep issues)
+    x = torch.randn(5120, device="cuda").to(torch.bfloat16)
+    ys = [torch.empty(n, dtype=torch.bfloat16, device="cuda") for _, n, _ in synth.DECODE_SHAPES[:3]]
+
+    def call_group(i):
+        layer = sweep[i % len(sweep)]
+        backend.nvfp4_matvec_group(x, [(m[3], m[4], m[5], y) for m, y in zip(layer[:3], ys)])
+    us = _time_cuda(torch, call_group, 192, warm=20, backend=backend)
+    byts = sum(gemv_bytes(n, k) for _, n, k in synth.DECODE_SHAPES[:3]) - 2 * 2 * 5120
+    out["attn.qkv_group"] = {"n": 14336, "k": 5120, "us": round(us, 3), "gbs": round(byts / us / 1e3, 1)}
+    # config 0: the single 5120 x 5120 GEMV, 64 weight copies (0.94 GB) rotated so every launch is cold
+    gen = torch.Generator(device="cuda").manual_seed(500)
+    copies = []
+    for _ in range(64):
+        packed, sf_rm = synth.nvfp4_weight_device(gen, 5120, 5120, "cuda")
+        copies.append((packed, backend.nvfp4_retile_scales(sf_rm)))
+    ts = torch.tensor([synth.WEIGHT_GLOBAL_SCALE], dtype=torch.float32, device="cuda")
+    y0 = torch.empty(5120, dtype=torch.bfloat16, device="cuda")
+
+    def call0(i):
+        w, sf = copies[i % len(copies)]
+        backend.nvfp4_matvec(x, w, sf, ts, y0)
+    us = _time_cuda(torch, call0, 192, warm=20, backend=backend)
+    out["config0_5120x5120"] = {"n": 5120, "k": 5120, "us": round(us, 3), "gbs": round(gemv_bytes(5120, 5120) / us / 1e3, 1),
+                                "frac_of_measured_peak": round(gemv_bytes(5120, 5120) / us / 1e3 / measured_peaks()[0], 4)}
     return out
 
 
@@ -594,7 +629,7 @@ def run_ours(args):
     step_bytes = layers * sum(gemv_bytes(n, k) for _, n, k in synth.DECODE_SHAPES)
     if world > 1 and not split:
         step_bytes *= world                      # every rank streams its own replica
-    launches_per_step = layers * len(synth.DECODE_SHAPES)
+    launches_per_step = layers * (4 if shard_world == 1 else len(synth.DECODE_SHAPES))
 
     gen = torch.Generator(device="cuda").manual_seed(99 + (0 if split else rank))     # replicas: own hidden state
     x_dev = torch.randn(5120, generator=gen, device="cuda").to(torch.bfloat16)
@@ -623,6 +658,7 @@ def run_ours(args):
     else:
         per_step = launches_per_step
         run_step = runner.step
+    launches_per_step = per_step
     for _ in range(args.warmup):
         run_step(x_dev)
     barrier()
@@ -702,7 +738,9 @@ def run_ours(args):
             "scaling": "strong" if split else "weak", "vs_baseline": None, "dtype": "e2m1 x bf16 -> f32",
             "data": "synthetic",
             "config": {"workload": f"config 1: NVFP4 W4A16 decode GEMV sweep, {layers} layers x 6 shapes, M=1",
-                       "launch": "CUDA graph replay of the C-ABI calls" if use_graph else "eager C-ABI calls",
+                       "launch": ("CUDA graph replay of the C-ABI calls" if use_graph else "eager C-ABI calls") +
+                                 ("; q_gate + k + v (shared input) as one grouped launch: 4 launches per layer"
+                                  if shard_world == 1 else ""),
                        "bytes_per_step": step_bytes, "l2": "inputs larger than L2 (13.4 GB of weights per step)",
                        "parallelism": "1 GPU" if world == 1 else (
                            f"output rows split {world}-way + NCCL all-gather per GEMV" if split else
@@ -719,7 +757,7 @@ def run_ours(args):
                          # average launch (traffic grows with the units processed)
                          "traffic": int(per_gpu_bytes // launches_per_step * NCU_TRAFFIC_RATIO),
                          "traffic_source": "ncu, gate_up launch, scaled by bytes", "peak_kind": peak_kind,
-                         "kernel": "nvfp4_matvec_kernel", "launch_us": round(launch_us, 3),
+                         "kernel": "nvfp4_gemv_mma_kernel", "launch_us": round(launch_us, 3),
                          "bytes_per_launch": per_gpu_bytes // launches_per_step,
                          "frac_of_nominal_8TBs": round(achieved / 8000.0, 4)},
             "clocks": clocks,

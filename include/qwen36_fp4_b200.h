@@ -235,6 +235,13 @@ void qwen36_nvfp4_chunk_gemv_set_mtile(int mtile);
 /* Replaces qwen36_nvfp4_matvec (kernels-cuda/ops.cu:547-639,1155-1180). */
 int qwen36_nvfp4_matvec(const qwen36_nvfp4_matvec_spec_t *spec);
 
+/* Additive: `count` (1..4) GEMVs that share input_bf16 and in_features, as ONE launch whose work
+ * list spans all of the matrices (q / k / v projections of a decode layer).  Same results as
+ * `count` qwen36_nvfp4_matvec calls.  The reference reaches the same effect by concatenating such
+ * weights along N at load time (crates/runtime/src/gpu.rs:181-225,410-467); this entry needs no
+ * re-layout of the checkpoint.  INVALID_ARGUMENT when the specs do not share their input. */
+int qwen36_nvfp4_matvec_group(const qwen36_nvfp4_matvec_spec_t *specs, size_t count);
+
 /* Replace qwen36_nvfp4_quantize_bf16 / _rows
  * (kernels-cuda/ops.cu:641-761,1182-1227).  Codes, packing and scale bytes
  * follow the reference bit for bit (E2M1 ties toward zero, UE4M3 ties down).

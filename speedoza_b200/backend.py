@@ -131,6 +131,16 @@ class CudaBackend:
         _check("nvfp4_matvec", self.lib.qwen36_nvfp4_matvec(C.byref(spec)))
         return out
 
+    def nvfp4_matvec_group(self, x_bf16, mats) -> None:
+        """`mats`: up to four (weight_u8, sf_tiled, tensor_scale, out) tuples that share `x_bf16`;
+        one launch computes all of them (qwen36_nvfp4_matvec_group)."""
+        specs = (abi.Nvfp4MatvecSpec * len(mats))()
+        for i, (weight_u8, sf_tiled, tensor_scale, out) in enumerate(mats):
+            n, kh = weight_u8.shape
+            specs[i] = abi.Nvfp4MatvecSpec(n, x_bf16.numel(), _dp(x_bf16), _dp(weight_u8), _dp(sf_tiled),
+                                           _dp(tensor_scale), _dp(out))
+        _check("nvfp4_matvec_group", self.lib.qwen36_nvfp4_matvec_group(specs, len(mats)))
+
     def nvfp4_dequantize(self, weight_u8, sf_tiled, tensor_scale, in_features: int) -> torch.Tensor:
         n_out = weight_u8.shape[0]
         out = torch.empty((n_out, in_features), dtype=torch.float32, device=weight_u8.device)

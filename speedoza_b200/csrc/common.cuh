@@ -7,6 +7,12 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#ifdef __cplusplus
+#include <mutex>
+#include <utility>
+#include <vector>
+#endif
+
 #include "../../include/qwen36_fp4_b200.h"
 
 namespace q36 {
@@ -27,6 +33,42 @@ static inline int launch_status() { return cuda_status(cudaGetLastError()); }
 // The stream every launch goes to (runtime.cu).
 static inline cudaStream_t stream() {
   return reinterpret_cast<cudaStream_t>(qwen36_internal_active_stream());
+}
+
+// Opts a kernel in to `bytes` of dynamic shared memory (more than the 48 KB default).  The
+// attribute belongs to the (kernel, device) pair, so it is set once per pair: a process that drives
+// several GPUs gets it on each of them.
+inline cudaError_t ensure_dynamic_smem(const void *kernel, int bytes) {
+  static std::mutex mu;
+  static std::vector<std::pair<const void *, int>> done;
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return err;
+  std::lock_guard<std::mutex> lock(mu);
+  for (const auto &e : done)
+    if (e.first == kernel && e.second == dev) return cudaSuccess;
+  err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (err == cudaSuccess) done.emplace_back(kernel, dev);
+  return err;
+}
+
+// Multiprocessor count of the current device (cached per device ordinal).
+inline int sm_count_current_device() {
+  static std::mutex mu;
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+  if (dev >= 0 && dev < 64) {
+    std::lock_guard<std::mutex> lock(mu);
+    if (cached[dev] > 0) return cached[dev];
+  }
+  int n = 0;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 148;
+  if (dev >= 0 && dev < 64) {
+    std::lock_guard<std::mutex> lock(mu);
+    cached[dev] = n;
+  }
+  return n;
 }
 
 __host__ __device__ static inline size_t div_ceil(size_t a, size_t b) { return (a + b - 1) / b; }

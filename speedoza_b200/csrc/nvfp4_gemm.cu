@@ -4,6 +4,7 @@
 // shape the tensor-core kernels (nvfp4_gemm_tc.cu) decline.
 #include "common.cuh"
 #include "nvfp4_gemm_tc.cuh"
+#include "nvfp4_gemv_mma.cuh"
 
 namespace {
 
@@ -86,6 +87,10 @@ extern "C" int qwen36_nvfp4_gemm(const qwen36_nvfp4_gemm_spec_t *spec) {
   const int rc = check(spec);
   if (rc != QWEN36_STATUS_SUCCESS) return rc;
   const float alpha = spec->alpha == 0.0f ? 1.0f : spec->alpha;   // kernels-cuda/nvfp4_gemm.cu:380
+  if (spec->n == 1 && !q36::nvfp4_gemm_tc_forced()) {              // one token: the HBM-bound GEMV
+    const int gv = q36::nvfp4_gemv_mma_fp4(spec, alpha);
+    if (gv != QWEN36_STATUS_NOT_IMPLEMENTED) return gv;
+  }
   const int tc = q36::nvfp4_gemm_tc(spec, alpha);
   if (tc != QWEN36_STATUS_NOT_IMPLEMENTED) return tc;
   return launch_generic(spec, alpha);
@@ -95,6 +100,10 @@ extern "C" int qwen36_decode_nvfp4_gemv(const qwen36_nvfp4_gemm_spec_t *spec) {
   const int rc = check(spec);
   if (rc != QWEN36_STATUS_SUCCESS) return rc;
   if (spec->n > 8) return QWEN36_STATUS_NOT_IMPLEMENTED;
+  if (spec->n == 1 && !q36::nvfp4_gemm_tc_forced()) {
+    const int gv = q36::nvfp4_gemv_mma_fp4(spec, spec->alpha);
+    if (gv != QWEN36_STATUS_NOT_IMPLEMENTED) return gv;
+  }
   return q36::nvfp4_gemm_tc(spec, spec->alpha);   // NOT_IMPLEMENTED for shapes it declines
 }
 

@@ -16,12 +16,14 @@
 // warps 2..5 = epilogue (TMEM -> registers -> alpha, bf16 -> global), warp 6 = scale copier
 // (tcgen05.cp shared memory -> TMEM).  CTAs are persistent over
 // (row block, token block) tiles; with two accumulator stages the epilogue of one tile overlaps
-// the MMAs of the next.  No cluster, no multicast: every CTA loads its own tiles.
+// the MMAs of the next.  This single-CTA form uses no cluster; the CTA-pair and split-K forms
+// further down do.  No multicast loads anywhere: every CTA loads its own tiles.
 //
 // Every mbarrier wait is bounded; a wait that gives up sets g_gemm_error, and all roles fall
 // through to the common exit where TMEM is released.
 #include "nvfp4_gemm_tc.cuh"
 
+#include <atomic>
 #include <cuda.h>
 #include <mutex>
 
@@ -34,10 +36,8 @@ constexpr uint32_t kBKBytes = 128;            // 256 fp4 values
 constexpr uint32_t kSpinLimit = 1u << 26;
 
 __device__ unsigned int g_gemm_error = 0;
-int g_force_bn = 0;
-int g_force_split = 0;
-__device__ unsigned int g_debug = 0;        // timing experiments only (results become wrong): 1 skip scale copies, 2 skip stores, 4 skip MMAs, 8 skip loads
-__device__ unsigned int g_prefetch = 0;     // stages of L2 prefetch ahead of the shared-memory ring
+std::atomic<int> g_force_bn{0};
+std::atomic<int> g_force_split{0};
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -64,11 +64,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
 __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, uint32_t c0, uint32_t c1, uint64_t *bar) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
-}
-// L2 prefetch of a tile (no shared memory): the producer asks for the weight tile it will load a
-// few stages later, so that the load that fills shared memory hits L2 instead of waiting on HBM.
-__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap *map, uint32_t c0, uint32_t c1) {
-  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(c0), "r"(c1) : "memory");
 }
 __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -176,26 +171,15 @@ nvfp4_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_base_slot;
   const uint32_t tmem_sf = tmem_base + C::kAccStages * C::kAccCols;
-  const uint32_t dbg = g_debug;
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
       uint32_t g = 0;
       bool dead = false;
-      // prefetch cursor: runs `g_prefetch` stages ahead of the load cursor over the same sequence
-      const uint32_t ahead = g_prefetch;
-      uint32_t pf_tile = blockIdx.x, pf_kb = 0;
-      auto prefetch_one = [&]() {
-        if (pf_tile >= tiles) return;
-        tma_prefetch_2d(&map_a, pf_kb * kBKBytes, (pf_tile / n_blocks) * kBM);
-        if (++pf_kb == k_blocks) { pf_kb = 0; pf_tile += gridDim.x; }
-      };
-      for (uint32_t i = 0; i < ahead; ++i) prefetch_one();
       for (uint32_t tile = blockIdx.x; tile < tiles && !dead; tile += gridDim.x) {
         const uint32_t nb = tile % n_blocks, mb = tile / n_blocks;
         for (uint32_t kb = 0; kb < k_blocks; ++kb, ++g) {
-          if (ahead) prefetch_one();
           const uint32_t s = g % C::kStages, ph = (g / C::kStages) & 1u;
           if (!mbar_wait(&empty[s], ph ^ 1u)) { dead = true; break; }
           uint8_t *st = stages + s * C::kStageBytes;
@@ -205,7 +189,6 @@ nvfp4_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
 #pragma unroll
           for (uint32_t t = 0; t < C::kSfbTiles; ++t)
             if ((static_cast<size_t>(nb) * BN) / 128u + t < sf_tok_blocks) ++sfb_tiles;
-          if ((dbg & 8u) && g >= C::kStages) { mbar_arrive(&full[s]); continue; }   // timing experiment: no loads after the first ring fill
           mbar_expect_tx(&full[s], C::kABytes + C::kBRows * kBKBytes + C::kSfaBytes + sfb_tiles * 2048u);
           tma_load_2d(st, &map_a, kb * kBKBytes, mb * kBM, &full[s]);
           tma_load_2d(st + C::kABytes, &map_b, kb * kBKBytes, nb * BN, &full[s]);
@@ -239,12 +222,10 @@ nvfp4_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           if (!mbar_wait(&sf_full[s], ph)) { dead = true; break; }     // the copier warp has put this stage's scales in TMEM
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          if (!(dbg & 4u)) {                                            // timing experiment: 4 = no MMAs
 #pragma unroll
-            for (uint32_t kk = 0; kk < 4; ++kk)
-              mma_mxf4nvf4(d_tmem, desc_sw128(st + kk * 32u), desc_sw128(st + C::kABytes + kk * 32u), C::kIdesc,
-                           sfa_t + kk * 4u, sfb_t + kk * C::kSfbTiles * 4u, (kb | kk) != 0u);
-          }
+          for (uint32_t kk = 0; kk < 4; ++kk)
+            mma_mxf4nvf4(d_tmem, desc_sw128(st + kk * 32u), desc_sw128(st + C::kABytes + kk * 32u), C::kIdesc,
+                         sfa_t + kk * 4u, sfb_t + kk * C::kSfbTiles * 4u, (kb | kk) != 0u);
           mma_commit(&empty[s]);                 // frees the smem stage once these MMAs have read it
         }
         if (!dead) mma_commit(&acc_full[as]);    // accumulator complete
@@ -264,15 +245,13 @@ nvfp4_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t st = smem_u32(stages + s * C::kStageBytes);
           const uint32_t sfa_t = tmem_sf + s * C::kSfCols, sfb_t = sfa_t + 16u;
-          if (!(dbg & 1u) || g == 0) {
 #pragma unroll
-            for (uint32_t kk = 0; kk < 4; ++kk) {
-              tmem_cp_sf(sfa_t + kk * 4u, desc_sf(st + C::kABytes + C::kBBytes + kk * 512u));
+          for (uint32_t kk = 0; kk < 4; ++kk) {
+            tmem_cp_sf(sfa_t + kk * 4u, desc_sf(st + C::kABytes + C::kBBytes + kk * 512u));
 #pragma unroll
-              for (uint32_t t = 0; t < C::kSfbTiles; ++t)
-                tmem_cp_sf(sfb_t + (kk * C::kSfbTiles + t) * 4u,
-                           desc_sf(st + C::kABytes + C::kBBytes + C::kSfaBytes + t * 2048u + kk * 512u));
-            }
+            for (uint32_t t = 0; t < C::kSfbTiles; ++t)
+              tmem_cp_sf(sfb_t + (kk * C::kSfbTiles + t) * 4u,
+                         desc_sf(st + C::kABytes + C::kBBytes + C::kSfaBytes + t * 2048u + kk * 512u));
           }
           mma_commit(&sf_full[s]);
         }
@@ -322,7 +301,7 @@ nvfp4_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           // even: (mine.lo, got.lo) = token 2j ; odd: (got.hi, mine.hi) = token 2j+1
           const uint32_t v = odd ? __byte_perm(got, packed[j], 0x7632) : __byte_perm(packed[j], got, 0x5410);
           const uint32_t tok = tok0 + 2u * j + (odd ? 1u : 0u);
-          if (tok < n && !(dbg & 2u)) *reinterpret_cast<uint32_t *>(crow + static_cast<size_t>(tok) * m) = v;
+          if (tok < n) *reinterpret_cast<uint32_t *>(crow + static_cast<size_t>(tok) * m) = v;
         }
         continue;
       } else {
@@ -772,16 +751,7 @@ bool make_operand_map(CUtensorMap *map, uint64_t ptr, uint64_t rows, uint64_t k,
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-int sm_count() {
-  static int n = [] {
-    int dev = 0, v = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess ||
-        cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0)
-      return 148;
-    return v;
-  }();
-  return n;
-}
+int sm_count() { return q36::sm_count_current_device(); }
 
 template <uint32_t BN>
 int launch(const qwen36_nvfp4_gemm_spec_t *s, float alpha) {
@@ -790,13 +760,9 @@ int launch(const qwen36_nvfp4_gemm_spec_t *s, float alpha) {
   if (!make_operand_map(&map_a, s->a_fp4.ptr, s->m, s->k, kBM) ||
       !make_operand_map(&map_b, s->b_fp4.ptr, s->n, s->k, C::kBRows))
     return QWEN36_STATUS_NOT_IMPLEMENTED;
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(nvfp4_gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    static_cast<int>(C::kSmemBytes));
-  });
-  if (attr_err != cudaSuccess) return QWEN36_STATUS_CUDA_ERROR;
+  if (q36::ensure_dynamic_smem(reinterpret_cast<const void *>(nvfp4_gemm_tc_kernel<BN>), static_cast<int>(C::kSmemBytes)) !=
+      cudaSuccess)
+    return QWEN36_STATUS_CUDA_ERROR;
   const uint32_t tiles = static_cast<uint32_t>((s->m / kBM) * ((s->n + BN - 1) / BN));
   const uint32_t grid = tiles < static_cast<uint32_t>(sm_count()) ? tiles : static_cast<uint32_t>(sm_count());
   nvfp4_gemm_tc_kernel<BN><<<grid, kThreads, C::kSmemBytes, q36::stream()>>>(
@@ -828,13 +794,9 @@ int launch_pair(const qwen36_nvfp4_gemm_spec_t *s, float alpha) {
       !make_scale_map(&map_sfa, s->a_scale.ptr, (s->m / 128) * sf_tiles) ||
       !make_scale_map(&map_sfb, s->b_scale.ptr, ((s->n + 127) / 128) * sf_tiles))
     return QWEN36_STATUS_NOT_IMPLEMENTED;
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(nvfp4_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    static_cast<int>(P::kSmemBytes));
-  });
-  if (attr_err != cudaSuccess) return QWEN36_STATUS_CUDA_ERROR;
+  if (q36::ensure_dynamic_smem(reinterpret_cast<const void *>(nvfp4_gemm_pair_kernel), static_cast<int>(P::kSmemBytes)) !=
+      cudaSuccess)
+    return QWEN36_STATUS_CUDA_ERROR;
   const uint32_t tiles = static_cast<uint32_t>((s->m / 256) * ((s->n + P::kBN - 1) / P::kBN));
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(static_cast<uint32_t>(sm_count()) & ~1u);
@@ -876,13 +838,9 @@ int launch_splitk(const qwen36_nvfp4_gemm_spec_t *s, float alpha, uint32_t split
     return QWEN36_STATUS_NOT_IMPLEMENTED;
   constexpr uint32_t kSmem = C::kSmemBytes + (kMaxSplit - 1) * kBM * C::kBRows * 4u;
   static_assert(kSmem <= 227u * 1024u, "split-K shared memory");
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(nvfp4_gemm_splitk_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    static_cast<int>(kSmem));
-  });
-  if (attr_err != cudaSuccess) return QWEN36_STATUS_CUDA_ERROR;
+  if (q36::ensure_dynamic_smem(reinterpret_cast<const void *>(nvfp4_gemm_splitk_kernel<BN>), static_cast<int>(kSmem)) !=
+      cudaSuccess)
+    return QWEN36_STATUS_CUDA_ERROR;
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(static_cast<uint32_t>(s->m / kBM) * split);
   cfg.blockDim = dim3(kThreads);
@@ -905,7 +863,7 @@ int launch_splitk(const qwen36_nvfp4_gemm_spec_t *s, float alpha, uint32_t split
 // only when the row blocks alone leave most SMs idle, as far as that fills the device, keeping at
 // least two K-blocks per CTA.
 uint32_t choose_split(const qwen36_nvfp4_gemm_spec_t *s) {
-  const int forced = g_force_split;
+  const int forced = g_force_split.load();
   const uint32_t m_blocks = static_cast<uint32_t>(s->m / kBM), k_blocks = static_cast<uint32_t>(s->k / 256);
   uint32_t split = forced > 0 ? static_cast<uint32_t>(forced) : static_cast<uint32_t>(sm_count()) / m_blocks;
   if (split > kMaxSplit) split = kMaxSplit;
@@ -915,11 +873,13 @@ uint32_t choose_split(const qwen36_nvfp4_gemm_spec_t *s) {
 
 }  // namespace
 
+bool nvfp4_gemm_tc_forced() { return g_force_bn.load() != 0 || g_force_split.load() != 0; }
+
 int nvfp4_gemm_tc(const qwen36_nvfp4_gemm_spec_t *s, float alpha) {
   if (s->m % kBM != 0 || s->k % 256 != 0 || s->m > (1u << 30) || s->n > (1u << 30) || s->k > (1u << 30) ||
       ((s->a_fp4.ptr | s->b_fp4.ptr | s->a_scale.ptr | s->b_scale.ptr) & 15u) != 0 || (s->c_bf16.ptr & 3u) != 0)
     return QWEN36_STATUS_NOT_IMPLEMENTED;
-  const int forced = g_force_bn;
+  const int forced = g_force_bn.load();
   if (forced == 128 && s->n > 128) return launch<128>(s, alpha);
   // CTA pairs (256 x 256 tiles): measured ahead of single-CTA tiles only for long K with many
   // tokens (+5 % at k = 17408, n = 8192; level or slightly behind elsewhere).
@@ -941,18 +901,9 @@ int nvfp4_gemm_tc(const qwen36_nvfp4_gemm_spec_t *s, float alpha) {
 
 // Tuning hook: 128 forces 128-token tiles (two accumulator stages) for large n, 256 single-CTA
 // 256-token tiles, 512 CTA pairs (where the shape allows them); 0 = default.
-extern "C" void qwen36_nvfp4_gemm_force_bn(int bn) { g_force_bn = bn; }
+extern "C" void qwen36_nvfp4_gemm_force_bn(int bn) { g_force_bn.store(bn); }
 // Tuning hook: CTAs per row block of the split-K form for n <= 16 (1 = never split, 0 = heuristic).
-extern "C" void qwen36_nvfp4_gemm_force_split(int split) { g_force_split = split; }
-extern "C" void qwen36_nvfp4_gemm_debug(int mask) {
-  const unsigned int v = static_cast<unsigned int>(mask);
-  cudaMemcpyToSymbol(g_debug, &v, sizeof(v));
-}
-// Tuning hook: stages of L2 prefetch the TMA producer keeps ahead of its loads.  Synchronises.
-extern "C" void qwen36_nvfp4_gemm_set_prefetch(int stages) {
-  const unsigned int v = stages < 0 ? 0u : static_cast<unsigned int>(stages);
-  cudaMemcpyToSymbol(g_prefetch, &v, sizeof(v));
-}
+extern "C" void qwen36_nvfp4_gemm_force_split(int split) { g_force_split.store(split); }
 
 // 1 when a bounded wait inside the tensor-core GEMM ever gave up.  Synchronises.
 extern "C" int qwen36_nvfp4_gemm_last_error(void) {

@@ -1,0 +1,553 @@
+// NVFP4 GEMV for decode (one token), HBM-bound weight streaming with the arithmetic on the
+// tensor cores:
+//   W4A16  y[row] = bf16( global * sum_g ue4m3(sf[g,row]) * sum_{i<16} x[16g+i] * e2m1(w[row,16g+i]) )
+//          (semantics of kernels-cuda/ops.cu:547-639 in the reference; x is a bf16 vector)
+//   W4A4   the same with x = e2m1(b) * ue4m3(sfb), exact in float16, and alpha in place of global
+//          (kernels-cuda/decode_gemv/nvfp4_gemv_sm120.cu:203-331, n = 1)
+//
+// Why tensor cores for a matrix-vector product: at the HBM rate a SIMT inner loop (one
+// conversion per two weights, one FMA per weight, scale handling) needs nearly every issue slot
+// of the SM, so any stall of the weight stream is lost for good.  Here a warp turns a 16-row x
+// 16-column weight block into ONE mma.sync.m16n8k16 (float16 operands, float32 accumulation):
+// the only per-weight instruction left is the e2m1x2 -> f16x2 conversion, which leaves the SM
+// about twice the HBM rate in hand to catch up after the serial part of a launch.
+//
+// Block scales without a per-weight multiply.  The B operand (activations, 16 x 8) is filled so
+// that column n holds the activations of the four k-slots that lane-in-group n supplies and zeros
+// elsewhere.  Four chained MMAs then leave in D[row][n] the exact partial dot product of ONE
+// 16-column scale group per column n, and the block scale is applied to that sum with one
+// float32 FMA per (row, group), which is the reference's own order of operations.
+//
+// Pipeline.  Persistent CTAs, one producer warp + eight consumer warps.  A work unit is 32 rows
+// (rows r0+q+32j of a 128-row block, q < 8, j < 4) over all of K; a stage is 1024 columns of it:
+// ONE 5-D tiled TMA box of weights (128-byte swizzle, 16 KB) + ONE 3-D box of scale tiles (2 KB),
+// four stages in flight per CTA.  Every consumer warp owns 128 of a stage's 1024 columns for all
+// 32 rows, so all warps are busy on every stage whatever the matrix shape; their partial sums meet
+// in shared memory once per unit.  The activation slice of a warp is staged by that warp alone
+// (no CTA barrier between the end of the producing kernel and the first MMA).  Units are dealt
+// round-robin over a grid sized so that every CTA gets the same number of units.  Up to four
+// matrices that share the activation vector run as one launch.
+//
+// Weights and scales stream before griddepcontrol.wait: under programmatic dependent launch the
+// ring fills while the kernel that produces x is still finishing.
+#include "nvfp4_gemv_mma.cuh"
+
+#include <atomic>
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+
+namespace {
+
+using q36::as_ptr;
+
+constexpr int kWarps = 8;
+constexpr int kThreads = kWarps * 32;
+constexpr uint32_t kMaxMats = 4;
+constexpr uint32_t kStages = 4;
+constexpr uint32_t kStageW = 16384;                 // 32 rows x 512 B
+constexpr uint32_t kStageSf = 2048;                 // 16 scale tiles x 8 row-words x 16 B
+constexpr uint32_t kStageBytes = kStageW + kStageSf;
+constexpr uint32_t kRingBytes = kStages * kStageBytes;
+constexpr uint32_t kHeaderBytes = 3072;             // barriers, slice scales, zero chunk, partial sums
+constexpr uint32_t kSpinLimit = 1u << 24;
+constexpr uint32_t kMaxK = 32768;
+
+__device__ unsigned int g_gemv_mma_error = 0;       // set when a bounded wait gives up
+
+struct GemvParams {
+  CUtensorMap map_w[kMaxMats];
+  CUtensorMap map_sf[kMaxMats];
+  const uint8_t *w[kMaxMats];
+  const uint8_t *sf[kMaxMats];
+  __nv_bfloat16 *y[kMaxMats];
+  const float *tensor_scale[kMaxMats];   // W4A16: per-matrix global scale (may be null)
+  uint32_t unit_end[kMaxMats];           // running total of 32-row units
+  const void *x;                         // bf16 vector (W4A16) or packed E2M1 codes (W4A4)
+  const uint8_t *x_sf;                   // W4A4: tiled UE4M3 scales of the activation row
+  uint32_t K, iters, units, count;
+  float alpha;                           // W4A4
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Bounded wait: gives up after kSpinLimit polls, records it and returns false.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+    uint32_t done;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  atomicExch(&g_gemv_mma_error, 1u);
+  return false;
+}
+__device__ __forceinline__ void tma_load_5d(void *dst, const CUtensorMap *map, uint32_t c0, uint32_t c1, uint32_t c2,
+                                            uint32_t c3, uint32_t c4, uint64_t *bar) {
+  asm volatile("cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+               ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, uint32_t c0, uint32_t c1, uint32_t c2,
+                                            uint64_t *bar) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+               ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+
+// Four bytes of packed E2M1 -> four f16x2 (low nibble in the low half).
+__device__ __forceinline__ void e2m1x8_to_h2(uint32_t w, uint32_t (&h)[4]) {
+  asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+      "mov.b32 {b0, b1, b2, b3}, %4;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %0, b0;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %2, b2;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %3, b3;\n\t}"
+      : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3])
+      : "r"(w));
+}
+
+__device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                        uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t max_u16x2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("max.u16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
+// Two UE4M3 bytes -> two floats through the hardware E4M3 conversion (exact).  The bytes 0x7F and
+// 0xFF convert to NaN here while the reference reads them as 448: the NaN reaches the row's sum,
+// and a row whose sum is NaN is redone by exact_row() below with the reference's decoder.
+__device__ __forceinline__ float2 ue4m3x2_to_f32(uint32_t two_bytes) {
+  const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(two_bytes), __NV_E4M3);
+  return __half22float2(*reinterpret_cast<const __half2 *>(&h));
+}
+
+// Position of 16-byte chunk `chunk` (0..15) inside a warp's 256-byte activation slot: the four
+// chunks that the four reading lanes fetch together (64 bytes apart) land on different banks.
+__device__ __forceinline__ uint32_t x_chunk_pos(uint32_t chunk) {
+  const uint32_t kc = chunk >> 2, m = chunk & 3u;
+  return kc * 4u + (m ^ (kc >> 1));
+}
+
+// One row with the reference's scalar arithmetic, from global memory (rare: see ue4m3x2_to_f32).
+template <int XKIND>
+__device__ __noinline__ float exact_row(const GemvParams &p, uint32_t mat, uint32_t row, float global) {
+  const uint32_t K = p.K, groups = K / 16u;
+  const size_t sf_inner = q36::round_up(groups, 4);
+  const uint8_t *wrow = p.w[mat] + static_cast<size_t>(row) * (K / 2u);
+  float sum = 0.f;
+  for (uint32_t g = 0; g < groups; ++g) {
+    float scale = q36::decode_e4m3(p.sf[mat][q36::sf_offset(g, row, sf_inner)]);
+    float local = 0.f;
+    for (uint32_t i = 0; i < 8u; ++i) {
+      const uint32_t byte = wrow[g * 8u + i];
+      float x0, x1;
+      if (XKIND == 0) {
+        const __nv_bfloat16 *x = static_cast<const __nv_bfloat16 *>(p.x);
+        x0 = __bfloat162float(x[g * 16u + 2u * i]);
+        x1 = __bfloat162float(x[g * 16u + 2u * i + 1u]);
+      } else {
+        const uint32_t xb = static_cast<const uint8_t *>(p.x)[g * 8u + i];
+        x0 = q36::e2m1_value(xb);
+        x1 = q36::e2m1_value(xb >> 4);
+      }
+      local = fmaf(x0, q36::e2m1_value(byte), local);
+      local = fmaf(x1, q36::e2m1_value(byte >> 4), local);
+    }
+    if (XKIND == 0) scale = __fmul_rn(scale, global);
+    else scale = __fmul_rn(scale, q36::decode_e4m3(p.x_sf[q36::sf_offset(g, 0, sf_inner)]));
+    sum = fmaf(local, scale, sum);
+  }
+  return XKIND == 0 ? sum : sum * global;
+}
+
+// XKIND 0: x is a bf16 vector.  XKIND 1: x is one NVFP4-quantised activation row.
+template <int XKIND>
+__global__ void __launch_bounds__(kThreads + 32, 2)
+nvfp4_gemv_mma_kernel(const __grid_constant__ GemvParams p) {
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  // the swizzled boxes need 1024-byte aligned stages
+  uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint64_t *full = reinterpret_cast<uint64_t *>(smem);                 // [kStages]
+  uint64_t *empty = full + kStages;                                    // [kStages]
+  float *slice_inv = reinterpret_cast<float *>(smem + 64);             // [kWarps] inverse scale of a warp's x slice
+  uint4 *zero_chunk = reinterpret_cast<uint4 *>(smem + 128);           // 16 bytes of zeros
+  float *red = reinterpret_cast<float *>(smem + 1024);                 // [2][kWarps][32] partial row sums
+  uint8_t *ring = smem + kHeaderBytes;
+  uint8_t *xs = ring + kRingBytes;                                     // [kWarps][iters][256 B] float16 activations
+
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+  const uint32_t iters = p.iters;
+
+  if (warp == kWarps) {
+    // ------------------------------------------------------------------ producer warp
+    // It owns the barriers: initialises them, signals the consumers through a named barrier it
+    // does not wait on, and starts streaming at once (weights do not depend on the kernel that
+    // produced x).
+    if (lane < kStages) { mbar_init(&full[lane], 1); mbar_init(&empty[lane], kWarps); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("bar.arrive 2, %0;" ::"n"(kThreads + 32) : "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (lane == 0) {
+      uint32_t g = 0;
+      for (uint32_t unit = blockIdx.x; unit < p.units; unit += gridDim.x) {
+        uint32_t mat = 0, first = 0;
+        while (mat + 1u < p.count && unit >= p.unit_end[mat]) { first = p.unit_end[mat]; ++mat; }
+        const uint32_t lu = unit - first, rb = lu >> 2, r0 = (lu & 3u) * 8u;
+        for (uint32_t it = 0; it < iters; ++it, ++g) {
+          const uint32_t stage = g % kStages, phase = (g / kStages) & 1u;
+          if (!mbar_wait(&empty[stage], phase ^ 1u)) return;
+          uint8_t *dst = ring + stage * kStageBytes;
+          mbar_expect_tx(&full[stage], kStageBytes);        // whole boxes; columns past K arrive as zeros
+          tma_load_5d(dst, &p.map_w[mat], 0u, r0, 0u, it * 4u, rb, &full[stage]);
+          tma_load_3d(dst + kStageW, &p.map_sf[mat], r0 * 4u, it * 16u, rb, &full[stage]);
+        }
+      }
+    }
+    return;
+  }
+
+  // -------------------------------------------------------------------- consumer warps
+  if (threadIdx.x == 0) *zero_chunk = make_uint4(0u, 0u, 0u, 0u);
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+  // Each warp stages the activations of ITS columns (128 of every 1024) as float16, alone.
+  uint8_t *xw = xs + warp * iters * 256u;
+  if (XKIND == 0) {
+    // bf16 -> float16 times a power of two that brings the slice's max|x| into [2^14, 2^15):
+    // products with e2m1 weights stay exact, values more than 2^-38 below the maximum flush (far
+    // below the float32 accumulation error); the inverse scale is applied to the warp's partial sum.
+    constexpr uint32_t kPasses = kMaxK / 1024u / 2u;        // two stages' worth of chunks per pass
+    const uint4 *xg = static_cast<const uint4 *>(p.x);
+    uint4 xr[kPasses];
+    uint32_t m2 = 0;
+#pragma unroll
+    for (uint32_t ps = 0; ps < kPasses; ++ps) {
+      const uint32_t it = 2u * ps + (lane >> 4);
+      const uint32_t col = it * 1024u + warp * 128u + (lane & 15u) * 8u;
+      xr[ps] = (it < iters && col < p.K) ? __ldcg(xg + col / 8u) : make_uint4(0u, 0u, 0u, 0u);   // L2: x may be fresh
+      m2 = max_u16x2(m2, max_u16x2(max_u16x2(xr[ps].x & 0x7fff7fffu, xr[ps].y & 0x7fff7fffu),
+                                   max_u16x2(xr[ps].z & 0x7fff7fffu, xr[ps].w & 0x7fff7fffu)));
+    }
+    const uint32_t mx = __reduce_max_sync(0xffffffffu, max(m2 & 0xffffu, m2 >> 16));
+    const uint32_t e = (mx >> 7) & 0xffu;
+    const int shift = e == 255u ? 0 : (e < 15u ? 126 : 141 - static_cast<int>(e));
+    const float up = __uint_as_float(static_cast<uint32_t>(127 + shift) << 23);
+    if (lane == 0) slice_inv[warp] = __uint_as_float(static_cast<uint32_t>(127 - shift) << 23);
+#pragma unroll
+    for (uint32_t ps = 0; ps < kPasses; ++ps) {
+      const uint32_t it = 2u * ps + (lane >> 4);
+      if (it < iters) {
+        const uint32_t wv[4] = {xr[ps].x, xr[ps].y, xr[ps].z, xr[ps].w};
+        __half2 h[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          h[q] = __floats2half2_rn(__uint_as_float(wv[q] << 16) * up, __uint_as_float(wv[q] & 0xffff0000u) * up);
+        *reinterpret_cast<uint4 *>(xw + it * 256u + x_chunk_pos(lane & 15u) * 16u) = *reinterpret_cast<uint4 *>(h);
+      }
+    }
+  } else {
+    // e2m1 * ue4m3 is exact in float16 (at most 7 significant bits, magnitudes 2^-10 .. 2688).
+    const uint8_t *xb = static_cast<const uint8_t *>(p.x);
+    const uint32_t sub = lane & 7u;                                     // one 16-value group per lane
+    for (uint32_t it = lane >> 3; it < iters; it += 4u) {
+      const uint32_t col = it * 1024u + warp * 128u + sub * 16u;
+      uint2 codes = make_uint2(0u, 0u);
+      uint32_t sbyte = 0;
+      if (col < p.K) {
+        codes = __ldcg(reinterpret_cast<const uint2 *>(xb + col / 2u));
+        const uint32_t grp = col / 16u;
+        sbyte = __ldcg(p.x_sf + static_cast<size_t>(grp >> 2) * 512u + (grp & 3u));
+      }
+      const __half_raw sraw = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(sbyte), __NV_E4M3);
+      const __half2 s2 = __half2half2(*reinterpret_cast<const __half *>(&sraw));
+      uint32_t lo[4], hi[4];
+      e2m1x8_to_h2(codes.x, lo);
+      e2m1x8_to_h2(codes.y, hi);
+      __half2 h[8];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        h[q] = __hmul2(*reinterpret_cast<__half2 *>(&lo[q]), s2);
+        h[4 + q] = __hmul2(*reinterpret_cast<__half2 *>(&hi[q]), s2);
+      }
+      uint4 *dst = reinterpret_cast<uint4 *>(xw + it * 256u);
+      dst[x_chunk_pos(sub * 2u)] = *reinterpret_cast<uint4 *>(&h[0]);
+      dst[x_chunk_pos(sub * 2u + 1u)] = *reinterpret_cast<uint4 *>(&h[4]);
+    }
+    if (lane == 0) slice_inv[warp] = 1.0f;
+  }
+  // Meets the producer's arrival (barriers initialised); also publishes slice_inv and the zero chunk.
+  asm volatile("bar.sync 2, %0;" ::"n"(kThreads + 32) : "memory");
+
+  // Fragment geometry.  Lane (r = lane / 4, c = lane % 4) of the MMA holds weight rows r and r + 8 of a
+  // 16-row tile.  Tile t of a unit is {rows q + 32 (2t), q + 32 (2t + 1)}, q < 8, and MMA row r maps
+  // to q = (r >> 1) | ((r & 1) << 2): with the 128-byte swizzle of the TMA box (chunk ^= q) the eight
+  // lanes of a quarter warp then read eight different 16-byte bank groups.
+  const uint32_t r = lane >> 2, c = lane & 3u;
+  const uint32_t q = (r >> 1) | ((r & 1u) << 2);
+  const uint32_t kcol = warp >> 1, ch = (warp & 1u) * 4u + c;
+  const uint32_t w_off = (kcol * 32u + q) * 128u + ((ch ^ q) << 4);      // + j * 1024
+  const uint32_t tile = 2u * warp + (c & 1u);                            // scale tile of this lane's groups
+  const uint32_t sf_off = kStageW + tile * 128u + ((q ^ (tile & 7u)) << 4);
+  // B operand: only lanes with r == c carry activations (k-slots of lane c, column c); the rest read zeros.
+  const bool x_active = r == c;
+  const uint8_t *x_base = x_active ? xw : reinterpret_cast<const uint8_t *>(zero_chunk);
+  const uint32_t x_stride = x_active ? 256u : 0u;
+  uint32_t x_pos[4];
+#pragma unroll
+  for (uint32_t m = 0; m < 4u; ++m) x_pos[m] = x_active ? x_chunk_pos(c * 4u + m) * 16u : 0u;
+
+  uint32_t g = 0, flip = 0;
+  bool dead = false;
+  for (uint32_t unit = blockIdx.x; unit < p.units; unit += gridDim.x, flip ^= 1u) {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};                                 // rows q + 32 j, j = 0..3
+    for (uint32_t it = 0; it < iters; ++it, ++g) {
+      const uint32_t stage = g % kStages, phase = (g / kStages) & 1u;
+      // A wait that gives up (never seen in practice) only stops the arithmetic: the warp keeps
+      // walking its stages and barriers so that nobody else is left waiting for it.
+      if (!dead && !mbar_wait(&full[stage], phase)) dead = true;
+      if (!dead) {
+        const uint8_t *st = ring + stage * kStageBytes;
+        uint4 bx[4];
+#pragma unroll
+        for (uint32_t m = 0; m < 4u; ++m) bx[m] = *reinterpret_cast<const uint4 *>(x_base + it * x_stride + x_pos[m]);
+        const uint4 sq = *reinterpret_cast<const uint4 *>(st + sf_off);
+        const uint32_t sw[4] = {sq.x, sq.y, sq.z, sq.w};                 // scale bytes [j][group 0..3 of the tile]
+#pragma unroll
+        for (uint32_t t = 0; t < 2u; ++t) {
+          const uint4 wa = *reinterpret_cast<const uint4 *>(st + w_off + (2u * t) * 1024u);
+          const uint4 wb = *reinterpret_cast<const uint4 *>(st + w_off + (2u * t + 1u) * 1024u);
+          const uint32_t wav[4] = {wa.x, wa.y, wa.z, wa.w}, wbv[4] = {wb.x, wb.y, wb.z, wb.w};
+          float de[4] = {0.f, 0.f, 0.f, 0.f}, dod[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (uint32_t m = 0; m < 4u; ++m) {                             // 8 weights of each row per word
+            uint32_t ha[4], hb[4];
+            e2m1x8_to_h2(wav[m], ha);
+            e2m1x8_to_h2(wbv[m], hb);
+            if (m < 2u) {
+              mma_f16(de, ha[0], hb[0], ha[1], hb[1], bx[m].x, bx[m].y);
+              mma_f16(de, ha[2], hb[2], ha[3], hb[3], bx[m].z, bx[m].w);
+            } else {
+              mma_f16(dod, ha[0], hb[0], ha[1], hb[1], bx[m].x, bx[m].y);
+              mma_f16(dod, ha[2], hb[2], ha[3], hb[3], bx[m].z, bx[m].w);
+            }
+          }
+          // D columns 2c, 2c + 1 of lanes c < 2: groups 4c .. 4c + 3 of the warp's eight, i.e. scale tile
+          // 2 warp + c, bytes [j][0..3].
+          const float2 s01a = ue4m3x2_to_f32(sw[2u * t] & 0xffffu), s23a = ue4m3x2_to_f32(sw[2u * t] >> 16);
+          const float2 s01b = ue4m3x2_to_f32(sw[2u * t + 1u] & 0xffffu), s23b = ue4m3x2_to_f32(sw[2u * t + 1u] >> 16);
+          float a0 = acc[2u * t], a1 = acc[2u * t + 1u];
+          a0 = fmaf(de[0], s01a.x, a0); a0 = fmaf(dod[0], s01a.y, a0);
+          a0 = fmaf(de[1], s23a.x, a0); a0 = fmaf(dod[1], s23a.y, a0);
+          a1 = fmaf(de[2], s01b.x, a1); a1 = fmaf(dod[2], s01b.y, a1);
+          a1 = fmaf(de[3], s23b.x, a1); a1 = fmaf(dod[3], s23b.y, a1);
+          acc[2u * t] = a0; acc[2u * t + 1u] = a1;
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[stage]);
+    }
+    // Lanes c = 0 and c = 1 hold the two scale tiles of the warp's columns; lanes c >= 2 hold zeros.
+    float *buf = red + flip * (kWarps * 32u);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], 1);
+      if (c == 0u) buf[warp * 32u + static_cast<uint32_t>(j) * 8u + q] = acc[j];
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory");
+    if (threadIdx.x < 32u) {
+      uint32_t mat = 0, first = 0;
+      while (mat + 1u < p.count && unit >= p.unit_end[mat]) { first = p.unit_end[mat]; ++mat; }
+      const uint32_t lu = unit - first;
+      const uint32_t row = (lu >> 2) * 128u + (lu & 3u) * 8u + (threadIdx.x & 7u) + 32u * (threadIdx.x >> 3);
+      float v = 0.f;
+#pragma unroll
+      for (uint32_t w = 0; w < static_cast<uint32_t>(kWarps); ++w) v = fmaf(buf[w * 32u + threadIdx.x], slice_inv[w], v);
+      const float global = XKIND == 0 ? (p.tensor_scale[mat] == nullptr ? 1.0f : __ldg(p.tensor_scale[mat])) : p.alpha;
+      v *= global;
+      if (v != v && !dead) v = exact_row<XKIND>(p, mat, row, global);
+      p.y[mat][row] = __float2bfloat16(v);
+    }
+    // `buf` alternates between units: the next write to this buffer comes after the next unit's barrier,
+    // which warp 0 only reaches after the reads above.
+  }
+}
+
+// ---- host side ---------------------------------------------------------------------------------
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point lookup (no link against libcuda).
+using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                              const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeFn encode_fn() {
+  static EncodeFn fn = [] {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeFn>(p);
+  }();
+  return fn;
+}
+
+// Tensor maps depend only on (pointer, rows, K): a decode loop asks for the same few hundred pairs
+// on every token, so they are kept in a small direct-mapped cache instead of being encoded per call.
+struct MapEntry {
+  const void *w = nullptr, *sf = nullptr;
+  uint64_t n = 0, k = 0;
+  CUtensorMap map_w, map_sf;
+};
+constexpr size_t kMapCacheSize = 1024;
+std::mutex g_map_mu;
+MapEntry g_map_cache[kMapCacheSize];
+
+bool encode_maps(const void *w, const void *sf, uint64_t N, uint64_t K, CUtensorMap *map_w, CUtensorMap *map_sf) {
+  EncodeFn enc = encode_fn();
+  if (enc == nullptr) return false;
+  const uint64_t row_bytes = K / 2, blocks = N / 128, tiles = K / 64;
+  const cuuint32_t ones[5] = {1, 1, 1, 1, 1};
+  {   // weights as uint32 [blocks][K/256 column chunks][4 j][32 q][32 words = 128 B]
+    const cuuint64_t dims[5] = {32, 32, 4, K / 256, blocks};
+    const cuuint64_t strides[4] = {row_bytes, 32 * row_bytes, 128, 128 * row_bytes};
+    const cuuint32_t box[5] = {32, 8, 4, 4, 1};
+    if (enc(map_w, CU_TENSOR_MAP_DATA_TYPE_UINT32, 5, const_cast<void *>(w), dims, strides, box, ones,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return false;
+  }
+  {   // scales as uint32 [blocks][tiles][128 words = one 512-byte tile]
+    const cuuint64_t dims[3] = {128, tiles, blocks};
+    const cuuint64_t strides[2] = {512, tiles * 512};
+    const cuuint32_t box[3] = {32, 16, 1};
+    if (enc(map_sf, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<void *>(sf), dims, strides, box, ones,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return false;
+  }
+  return true;
+}
+
+bool get_maps(const void *w, const void *sf, uint64_t N, uint64_t K, CUtensorMap *map_w, CUtensorMap *map_sf) {
+  const uint64_t h = (reinterpret_cast<uintptr_t>(w) >> 8) * 0x9E3779B97F4A7C15ull ^ (N * 31u + K);
+  MapEntry &e = g_map_cache[(h >> 20) % kMapCacheSize];
+  {
+    std::lock_guard<std::mutex> lock(g_map_mu);
+    if (e.w == w && e.sf == sf && e.n == N && e.k == K) {
+      *map_w = e.map_w;
+      *map_sf = e.map_sf;
+      return true;
+    }
+  }
+  if (!encode_maps(w, sf, N, K, map_w, map_sf)) return false;
+  std::lock_guard<std::mutex> lock(g_map_mu);
+  e.w = w; e.sf = sf; e.n = N; e.k = K;
+  e.map_w = *map_w;
+  e.map_sf = *map_sf;
+  return true;
+}
+
+struct Mat {
+  const uint8_t *w, *sf;
+  __nv_bfloat16 *y;
+  const float *tensor_scale;
+  uint64_t n;
+};
+
+bool shape_ok(uint64_t n, uint64_t k) {
+  return n != 0 && n % 128 == 0 && n < (1ull << 31) && k >= 256 && k % 256 == 0 && k <= kMaxK;
+}
+
+template <int XKIND>
+int launch(const Mat *mats, uint32_t count, uint64_t K, const void *x, const uint8_t *x_sf, float alpha) {
+  GemvParams p{};
+  uint32_t units = 0;
+  for (uint32_t i = 0; i < count; ++i) {
+    if (!get_maps(mats[i].w, mats[i].sf, mats[i].n, K, &p.map_w[i], &p.map_sf[i])) return QWEN36_STATUS_NOT_IMPLEMENTED;
+    p.w[i] = mats[i].w;
+    p.sf[i] = mats[i].sf;
+    p.y[i] = mats[i].y;
+    p.tensor_scale[i] = mats[i].tensor_scale;
+    units += static_cast<uint32_t>(mats[i].n / 32);
+    p.unit_end[i] = units;
+  }
+  for (uint32_t i = count; i < kMaxMats; ++i) p.unit_end[i] = units;
+  p.x = x;
+  p.x_sf = x_sf;
+  p.K = static_cast<uint32_t>(K);
+  p.iters = static_cast<uint32_t>((K + 1023) / 1024);
+  p.units = units;
+  p.count = count;
+  p.alpha = alpha;
+  const size_t smem = 1024 + kHeaderBytes + kRingBytes + static_cast<size_t>(p.iters) * 2048;
+  if (q36::ensure_dynamic_smem(reinterpret_cast<const void *>(nvfp4_gemv_mma_kernel<XKIND>), 227 * 1024) != cudaSuccess)
+    return QWEN36_STATUS_CUDA_ERROR;
+  // Every CTA gets the same number of units: the grid is the unit count divided by the number of
+  // round-robin passes that two CTAs per SM need.
+  const uint32_t per_sm = smem * 2 + 2048 <= 228u * 1024u ? 2u : 1u;
+  const uint32_t cap = static_cast<uint32_t>(q36::sm_count_current_device()) * per_sm;
+  const uint32_t passes = (units + cap - 1) / cap;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((units + passes - 1) / passes);
+  cfg.blockDim = dim3(kThreads + 32);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = q36::stream();
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return q36::cuda_status(cudaLaunchKernelEx(&cfg, nvfp4_gemv_mma_kernel<XKIND>, p));
+}
+
+}  // namespace
+
+namespace q36 {
+
+int nvfp4_gemv_mma_bf16(const qwen36_nvfp4_matvec_spec_t *specs, size_t count) {
+  if (count == 0 || count > kMaxMats) return QWEN36_STATUS_NOT_IMPLEMENTED;
+  Mat mats[kMaxMats];
+  const uint64_t K = specs[0].in_features;
+  for (size_t i = 0; i < count; ++i) {
+    const qwen36_nvfp4_matvec_spec_t &s = specs[i];
+    if (s.in_features != K || s.input_bf16.ptr != specs[0].input_bf16.ptr || !shape_ok(s.out_features, K) ||
+        ((s.input_bf16.ptr | s.weight_u8.ptr | s.block_scale_e4m3.ptr) & 15u) != 0)
+      return QWEN36_STATUS_NOT_IMPLEMENTED;
+    mats[i] = Mat{as_ptr<const uint8_t>(s.weight_u8), as_ptr<const uint8_t>(s.block_scale_e4m3),
+                  as_ptr<__nv_bfloat16>(s.output_bf16), as_ptr<const float>(s.tensor_scale_f32), s.out_features};
+  }
+  return launch<0>(mats, static_cast<uint32_t>(count), K, as_ptr<const void>(specs[0].input_bf16), nullptr, 1.0f);
+}
+
+int nvfp4_gemv_mma_fp4(const qwen36_nvfp4_gemm_spec_t *s, float alpha) {
+  if (s->n != 1 || !shape_ok(s->m, s->k) || ((s->a_fp4.ptr | s->a_scale.ptr) & 15u) != 0 || (s->b_fp4.ptr & 7u) != 0)
+    return QWEN36_STATUS_NOT_IMPLEMENTED;
+  const Mat mat{as_ptr<const uint8_t>(s->a_fp4), as_ptr<const uint8_t>(s->a_scale), as_ptr<__nv_bfloat16>(s->c_bf16),
+                nullptr, s->m};
+  return launch<1>(&mat, 1u, s->k, as_ptr<const void>(s->b_fp4), as_ptr<const uint8_t>(s->b_scale), alpha);
+}
+
+}  // namespace q36
+
+// 1 when a bounded wait inside the tensor-core GEMV pipeline ever gave up (a stage never arrived);
+// the kernel then returns without finishing its rows.  Reads device memory: synchronises.
+extern "C" int qwen36_nvfp4_gemv_mma_last_error(void) {
+  unsigned int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_gemv_mma_error, sizeof(v)) != cudaSuccess) return -1;
+  return static_cast<int>(v);
+}

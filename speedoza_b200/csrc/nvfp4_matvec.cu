@@ -1,9 +1,13 @@
 // W4A16 NVFP4 GEMV: y[row] = bf16( sum_g (sum_{i<16} x[16g+i] * e2m1(w)) * (ue4m3(sf[g,row]) * global) )
 // (semantics of kernels-cuda/ops.cu:547-639 in the reference).
 //
-// HBM-bound weight streaming.  Persistent CTAs; a producer warp drives the TMA
-// engine (descriptor-free cp.async.bulk row segments, mbarrier ring of four
-// 18 KB stages per CTA), so the bytes in flight do not depend on occupancy or
+// Entry points qwen36_nvfp4_matvec / qwen36_nvfp4_matvec_group.  Shapes with out_features % 128
+// == 0 and in_features % 256 == 0 go to the tensor-core GEMV (nvfp4_gemv_mma.cu); this file holds
+// the SIMT pipeline that takes the other 32-column-aligned shapes, and the generic kernel.
+//
+// SIMT pipeline: HBM-bound weight streaming.  Persistent CTAs; a producer warp drives the TMA
+// engine (tiled TMA boxes when out_features % 128 == 0, else one cp.async.bulk per row segment;
+// mbarrier ring of 72 KB per CTA), so the bytes in flight do not depend on occupancy or
 // registers.  Eight consumer warps each own a "row quad": rows r, r+32, r+64,
 // r+96 of one 128-row block.  Those four rows share one 16-byte word per scale
 // tile (4 rows x 4 groups), so a lane fetches its scales with ONE 16-byte
@@ -16,6 +20,7 @@
 // programmatic dependent launch the ring fills while the kernel that produces
 // x is still finishing.
 #include "common.cuh"
+#include "nvfp4_gemv_mma.cuh"
 
 #include <atomic>
 #include <cuda.h>
@@ -403,17 +408,7 @@ std::atomic<int> g_force_quads{0};
 #ifdef Q36_MATVEC_TRACE
 std::atomic<uint32_t> g_trace_id{0};
 #endif
-int g_sms = 0;
-int sm_count() {
-  if (g_sms == 0) {
-    int dev = 0, n = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess ||
-        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
-      return 148;
-    g_sms = n;
-  }
-  return g_sms;
-}
+int sm_count() { return q36::sm_count_current_device(); }
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point lookup (no link against libcuda).
 using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -463,13 +458,8 @@ template <int QUADS, bool TMAP>
 int launch_kernel(const qwen36_nvfp4_matvec_spec_t *s, const CUtensorMap &map_w, const CUtensorMap &map_sf) {
   const uint32_t K = static_cast<uint32_t>(s->in_features), N = static_cast<uint32_t>(s->out_features);
   const size_t smem = 1024 + kHeaderBytes + kRingBytes + static_cast<size_t>(K) * 2 + static_cast<size_t>(K) / 8;
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(nvfp4_matvec_kernel<QUADS, TMAP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    227 * 1024);
-  });
-  if (attr_err != cudaSuccess) return QWEN36_STATUS_CUDA_ERROR;
+  if (q36::ensure_dynamic_smem(reinterpret_cast<const void *>(nvfp4_matvec_kernel<QUADS, TMAP>), 227 * 1024) != cudaSuccess)
+    return QWEN36_STATUS_CUDA_ERROR;
   const uint32_t units = ((N + 127u) / 128u) * (32u / QUADS);
   const uint32_t cap = static_cast<uint32_t>(sm_count()) * 2u;
   cudaLaunchConfig_t cfg{};
@@ -522,7 +512,8 @@ int launch_fast(const qwen36_nvfp4_matvec_spec_t *s) {
 
 }  // namespace
 
-// Tuning hook: force the unit size (1, 2, 4 or 8 row quads); anything else restores the heuristic.
+// Test hook: a unit size of 1, 2, 4 or 8 row quads sends every 32-column-aligned shape through the
+// SIMT pipeline with that unit size; anything else restores the library's own routing.
 extern "C" void qwen36_nvfp4_matvec_force_quads(int quads) { g_force_quads.store(quads); }
 
 #ifdef Q36_MATVEC_TRACE
@@ -558,5 +549,29 @@ extern "C" int qwen36_nvfp4_matvec(const qwen36_nvfp4_matvec_spec_t *spec) {
         as_ptr<__nv_bfloat16>(spec->output_bf16), spec->in_features, spec->out_features);
     return q36::launch_status();
   }
+  const int forced = g_force_quads.load();
+  if (!(forced == 1 || forced == 2 || forced == 4 || forced == 8)) {
+    const int rc = q36::nvfp4_gemv_mma_bf16(spec, 1);
+    if (rc != QWEN36_STATUS_NOT_IMPLEMENTED) return rc;
+  }
   return launch_fast(spec);
+}
+
+extern "C" int qwen36_nvfp4_matvec_group(const qwen36_nvfp4_matvec_spec_t *specs, size_t count) {
+  if (specs == nullptr) return QWEN36_STATUS_NULL_POINTER;
+  if (count == 0 || count > 4) return QWEN36_STATUS_INVALID_ARGUMENT;
+  for (size_t i = 0; i < count; ++i) {
+    const qwen36_nvfp4_matvec_spec_t &s = specs[i];
+    if (s.out_features == 0 || s.in_features == 0 || s.input_bf16.ptr == 0 || s.weight_u8.ptr == 0 ||
+        s.block_scale_e4m3.ptr == 0 || s.output_bf16.ptr == 0 || s.in_features != specs[0].in_features ||
+        s.input_bf16.ptr != specs[0].input_bf16.ptr)
+      return QWEN36_STATUS_INVALID_ARGUMENT;
+  }
+  const int rc = q36::nvfp4_gemv_mma_bf16(specs, count);
+  if (rc != QWEN36_STATUS_NOT_IMPLEMENTED) return rc;
+  for (size_t i = 0; i < count; ++i) {            // shapes the one-launch kernel declines: one call each
+    const int one = qwen36_nvfp4_matvec(&specs[i]);
+    if (one != QWEN36_STATUS_SUCCESS) return one;
+  }
+  return QWEN36_STATUS_SUCCESS;
 }

@@ -155,6 +155,90 @@ def test_matvec_w4a16_vs_oracle(backend, n, k, quads):
     assert (got == want).mean() > 0.98       # nearly every bf16 output identical
 
 
+@pytest.mark.parametrize("n,k", [(128, 256), (128, 1024), (256, 1280), (384, 7424), (640, 2048), (1152, 3328)])
+def test_matvec_tensor_core_path_small_shapes(backend, n, k):
+    """Shapes the tensor-core GEMV takes (rows % 128 == 0, columns % 256 == 0), chosen so that the
+    last pipeline stage is partial, a unit's 32 rows straddle every quarter of a 128-row block, and
+    a CTA walks several units; every UE4M3 byte value occurs among the block scales, including the
+    subnormal codes, 0x80 (zero) and 0x7F / 0xFF, which the reference reads as 448 (rows that hold
+    one are recomputed by the kernel's scalar fallback)."""
+    rng = np.random.default_rng(n * 5 + k)
+    packed = rng.integers(0, 256, size=(n, k // 2), dtype=np.uint8)
+    sf_rm = rng.integers(0, 256, size=(n, k // 16), dtype=np.uint8)
+    sf_rm[::3] &= 0x7F                         # a third of the rows without negative scales
+    sf_rm[1::2][sf_rm[1::2] == 0x7F] = 0x30    # half of the rows free of the 448 codes
+    sf_rm[1::2][sf_rm[1::2] == 0xFF] = 0x31
+    sf = orc.retile_scales(sf_rm)
+    x = synth.activations(rng, 1, k)[0]
+    ts = torch.tensor([0.37], dtype=torch.float32, device="cuda")
+    got = bf16_host(backend.nvfp4_matvec(to_dev(x), to_dev(packed), to_dev(sf), ts))
+    assert backend.lib.qwen36_nvfp4_gemv_mma_last_error() == 0
+    want = orc.nvfp4_matvec(x, packed, sf, 0.37, k)
+    assert rel_l2(synth.bf16_bits_to_f32(got), synth.bf16_bits_to_f32(want)) <= 1e-3
+    assert (got == want).mean() > 0.98
+
+
+def test_matvec_group_equals_single_calls(backend):
+    """qwen36_nvfp4_matvec_group over the q / k / v projections of a decode layer (one launch) gives
+    what three qwen36_nvfp4_matvec calls give, and the oracle's result; a group the one-launch
+    kernel declines (ragged rows) still returns the right answers; mismatched inputs are refused."""
+    import ctypes as C
+    rng = np.random.default_rng(606)
+    k = 5120
+    x = synth.activations(rng, 1, k)[0]
+    xd = to_dev(x)
+    mats, wants = [], []
+    for i, n in enumerate((12288, 1024, 1024, 256)):
+        packed, sf_rm, sf = make_weight(rng, n, k)
+        g = synth.WEIGHT_GLOBAL_SCALE * (i + 1)
+        ts = torch.tensor([g], dtype=torch.float32, device="cuda") if i != 3 else None
+        out = torch.full((n,), float("nan"), dtype=torch.bfloat16, device="cuda")
+        mats.append((to_dev(packed), to_dev(sf), ts, out))
+        wants.append(orc.nvfp4_matvec(x, packed, sf, g if i != 3 else None, k))
+    backend.nvfp4_matvec_group(xd, mats)
+    assert backend.lib.qwen36_nvfp4_gemv_mma_last_error() == 0
+    for (w, sf, ts, out), want in zip(mats, wants):
+        got = bf16_host(out)
+        assert rel_l2(synth.bf16_bits_to_f32(got), synth.bf16_bits_to_f32(want)) <= 1e-3
+        assert np.array_equal(got, bf16_host(backend.nvfp4_matvec(xd, w, sf, ts)))
+    # a group with a ragged matrix falls back to one launch per matrix
+    packed, sf_rm, sf = make_weight(rng, 130, k)
+    out = torch.empty(130, dtype=torch.bfloat16, device="cuda")
+    backend.nvfp4_matvec_group(xd, [mats[1], (to_dev(packed), to_dev(sf), None, out)])
+    want = orc.nvfp4_matvec(x, packed, sf, None, k)
+    assert rel_l2(synth.bf16_bits_to_f32(bf16_host(out)), synth.bf16_bits_to_f32(want)) <= 1e-3
+    # specs that do not share their input are an error
+    specs = (abi.Nvfp4MatvecSpec * 2)()
+    for i in range(2):
+        w, sf, ts, out = mats[i]
+        other = to_dev(x.copy())
+        specs[i] = abi.Nvfp4MatvecSpec(w.shape[0], k, abi.DevicePtr((xd if i == 0 else other).data_ptr()),
+                                       abi.DevicePtr(w.data_ptr()), abi.DevicePtr(sf.data_ptr()),
+                                       abi.DevicePtr(ts.data_ptr()), abi.DevicePtr(out.data_ptr()))
+    assert backend.lib.qwen36_nvfp4_matvec_group(specs, 2) == abi.INVALID_ARGUMENT
+    assert backend.lib.qwen36_nvfp4_matvec_group(specs, 5) == abi.INVALID_ARGUMENT
+    assert backend.lib.qwen36_nvfp4_matvec_group(None, 1) == abi.NULL_POINTER
+
+
+def test_matvec_non_finite_activations(backend):
+    """inf or NaN among the activations: rows whose reference result is NaN / inf come out NaN / inf
+    here too, all other outputs keep their tolerance (the kernel redoes NaN rows with the scalar
+    arithmetic of the reference)."""
+    rng = np.random.default_rng(88)
+    n, k = 256, 2048
+    packed, sf_rm, sf = make_weight(rng, n, k)
+    packed[7, :] = 0                            # a row of zero weights: inf * 0 = NaN
+    ts = torch.ones(1, dtype=torch.float32, device="cuda")
+    x = synth.activations(rng, 1, k)[0]
+    x[100] = 0x7F80                             # +inf
+    got = synth.bf16_bits_to_f32(bf16_host(backend.nvfp4_matvec(to_dev(x), to_dev(packed), to_dev(sf), ts)))
+    want = synth.bf16_bits_to_f32(orc.nvfp4_matvec(x, packed, sf, 1.0, k))
+    assert np.array_equal(np.isnan(got), np.isnan(want))
+    fin = np.isfinite(want)
+    assert np.array_equal(got[~fin & ~np.isnan(want)], want[~fin & ~np.isnan(want)])
+    assert rel_l2(got[fin], want[fin]) <= 1e-3
+
+
 def test_matvec_extreme_activation_ranges(backend):
     """Scaled-float16 activation path: tiny, huge and mixed magnitudes stay within tolerance."""
     rng = np.random.default_rng(77)
@@ -283,6 +367,23 @@ def test_w4a4_decode_split_k(backend, m, n, k):
     finally:
         backend.lib.qwen36_nvfp4_gemm_force_split(0)
     assert backend.lib.qwen36_nvfp4_gemm_last_error() == 0
+
+
+@pytest.mark.parametrize("m,k", [(1024, 5120), (5120, 6144), (5120, 17408), (12288, 5120), (128, 256), (384, 1280)])
+def test_w4a4_one_token_decode_vs_oracle(backend, m, k):
+    """One token through qwen36_decode_nvfp4_gemv and qwen36_nvfp4_gemm (the route of the
+    5120 x 17408 down projection): the tensor-core GEMV with the activation dequantised to float16
+    (exact).  rel-L2 <= 1e-2 against the float64 oracle (in fact ~1e-3: bf16 rounding of the output)."""
+    rng = np.random.default_rng(m + k)
+    a, a_sf, x, b, b_sf, alpha = w4a4_case(rng, m, 1, k)
+    want = synth.bf16_bits_to_f32(orc.nvfp4_gemm(a, a_sf, b, b_sf, alpha, m, 1, k))
+    dev = [to_dev(t) for t in (a, a_sf, b, b_sf)]
+    for entry in (backend.decode_nvfp4_gemv_raw, backend.nvfp4_gemm_raw):
+        out = torch.full((1, m), float("nan"), dtype=torch.bfloat16, device="cuda")
+        assert entry(*dev, alpha, m, 1, k, out) == abi.SUCCESS
+        got = synth.bf16_bits_to_f32(bf16_host(out))
+        assert rel_l2(got, want) <= 3e-3
+    assert backend.lib.qwen36_nvfp4_gemv_mma_last_error() == 0
 
 
 def test_w4a4_known_answer_132_and_alpha_zero(backend):
