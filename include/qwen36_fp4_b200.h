@@ -418,14 +418,18 @@ int qwen36_attention_merge_partials(const qwen36_attention_merge_spec_t *spec);
 /* ---- Multi-GPU combine over NVLink peer memory (no reference counterpart: the
  * reference is single-GPU).  One process per GPU on one node.  Every rank
  * allocates an inbox and a flag array with qwen36_cuda_malloc plus a local
- * 2-word state, all zero-filled once; exports inbox and flags with
+ * 4-word state, all zero-filled once; exports inbox and flags with
  * qwen36_ipc_get_handle, opens the peers' handles with qwen36_ipc_open_handle,
  * and keeps two device arrays of `world` pointers in rank order (its own
  * entries are the local pointers).  A combine kernel pushes this rank's piece
  * into every peer's inbox with plain peer stores, raises a flag there, waits
  * on its own flags and combines out of its own memory.  Every wait is bounded
- * (a few seconds at most), after which the output is left untouched and
- * qwen36_peer_last_error() returns 1.  The call number is kept in `state` and
+ * (a few seconds at most).  A wait that runs out is visible without a
+ * synchronising query: the call's output is poisoned (NaN rows of the merge,
+ * token 0xFFFFFFFF of the argmax), state[2] receives the number of the first
+ * failed call, and qwen36_peer_last_error() returns 1 from then on.  After any
+ * reported failure the exchange is out of step: state, flags and inbox must be
+ * re-zeroed on ALL ranks under a host barrier before it is used again.  The call number is kept in `state` and
  * advanced by the kernel, so a captured launch can be replayed; all ranks must
  * make the same sequence of calls on one set of buffers. */
 int qwen36_ipc_get_handle(qwen36_device_ptr_t ptr, void *handle_out_64_bytes);

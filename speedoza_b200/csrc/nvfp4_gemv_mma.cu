@@ -45,6 +45,10 @@ constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
 constexpr uint32_t kMaxMats = 4;
 constexpr uint32_t kStages = 4;
+#ifndef Q36_GEMV_AHEAD
+#define Q36_GEMV_AHEAD 4
+#endif
+constexpr uint32_t kAhead = Q36_GEMV_AHEAD;         // stages of L2 prefetch kept ahead of the ring
 constexpr uint32_t kStageW = 16384;                 // 32 rows x 512 B
 constexpr uint32_t kStageSf = 2048;                 // 16 scale tiles x 8 row-words x 16 B
 constexpr uint32_t kStageBytes = kStageW + kStageSf;
@@ -54,6 +58,20 @@ constexpr uint32_t kSpinLimit = 1u << 24;
 constexpr uint32_t kMaxK = 32768;
 
 __device__ unsigned int g_gemv_mma_error = 0;       // set when a bounded wait gives up
+
+// Per-CTA %globaltimer stamps for pipeline analysis; compiled in only with -DQ36_GEMV_TRACE.
+#ifdef Q36_GEMV_TRACE
+constexpr uint32_t kTraceLaunches = 64, kTraceCtas = 320, kTraceEvents = 8;
+__device__ unsigned long long g_trace[kTraceLaunches][kTraceCtas][kTraceEvents];
+#define Q36_TRACE(ev)                                                                       \
+  do {                                                                                      \
+    unsigned long long t_;                                                                  \
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                  \
+    if (blockIdx.x < kTraceCtas) g_trace[p.trace_id % kTraceLaunches][blockIdx.x][ev] = t_; \
+  } while (0)
+#else
+#define Q36_TRACE(ev)
+#endif
 
 struct GemvParams {
   CUtensorMap map_w[kMaxMats];
@@ -67,6 +85,9 @@ struct GemvParams {
   const uint8_t *x_sf;                   // W4A4: tiled UE4M3 scales of the activation row
   uint32_t K, iters, units, count;
   float alpha;                           // W4A4
+#ifdef Q36_GEMV_TRACE
+  uint32_t trace_id;
+#endif
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -96,6 +117,16 @@ __device__ __forceinline__ void tma_load_5d(void *dst, const CUtensorMap *map, u
                                             uint32_t c3, uint32_t c4, uint64_t *bar) {
   asm volatile("cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
                ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4) : "memory");
+}
+// L2 prefetch of the same boxes (no shared memory involved).
+__device__ __forceinline__ void tma_prefetch_5d(const CUtensorMap *map, uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3,
+                                                uint32_t c4) {
+  asm volatile("cp.async.bulk.prefetch.tensor.5d.L2.global.tile [%0, {%1, %2, %3, %4, %5}];"
+               ::"l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4) : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap *map, uint32_t c0, uint32_t c1, uint32_t c2) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];"
+               ::"l"(map), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
 __device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, uint32_t c0, uint32_t c1, uint32_t c2,
                                             uint64_t *bar) {
@@ -184,8 +215,9 @@ nvfp4_gemv_mma_kernel(const __grid_constant__ GemvParams p) {
   uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint64_t *full = reinterpret_cast<uint64_t *>(smem);                 // [kStages]
   uint64_t *empty = full + kStages;                                    // [kStages]
-  float *slice_inv = reinterpret_cast<float *>(smem + 64);             // [kWarps] inverse scale of a warp's x slice
-  uint4 *zero_chunk = reinterpret_cast<uint4 *>(smem + 128);           // 16 bytes of zeros
+  float *slice_inv = reinterpret_cast<float *>(smem + 256);            // [kWarps] inverse scale of a warp's x slice
+  uint4 *zero_chunk = reinterpret_cast<uint4 *>(smem + 320);           // 16 bytes of zeros
+  static_assert(2 * kStages * sizeof(uint64_t) <= 256, "barriers overlap the header fields");
   float *red = reinterpret_cast<float *>(smem + 1024);                 // [2][kWarps][32] partial row sums
   uint8_t *ring = smem + kHeaderBytes;
   uint8_t *xs = ring + kRingBytes;                                     // [kWarps][iters][256 B] float16 activations
@@ -193,6 +225,7 @@ nvfp4_gemv_mma_kernel(const __grid_constant__ GemvParams p) {
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
   const uint32_t iters = p.iters;
 
+  if (threadIdx.x == 0) Q36_TRACE(0);
   if (warp == kWarps) {
     // ------------------------------------------------------------------ producer warp
     // It owns the barriers: initialises them, signals the consumers through a named barrier it
@@ -203,6 +236,22 @@ nvfp4_gemv_mma_kernel(const __grid_constant__ GemvParams p) {
     asm volatile("bar.arrive 2, %0;" ::"n"(kThreads + 32) : "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (lane == 0) {
+      // Run-ahead cursor: asks L2 for the boxes the ring will want `kAhead` stages later.  The ring
+      // itself is full long before x is ready (that is the point of streaming early); without the
+      // run-ahead HBM would idle from then until the first stage is released.  With it the next
+      // stages are already in L2 when the consumers start, and they work them off faster than HBM
+      // could deliver them.
+      uint32_t pf_unit = blockIdx.x, pf_it = 0, pf_issued = 0;
+      auto prefetch_one = [&]() {
+        if (pf_unit >= p.units) return;
+        uint32_t mat = 0, first = 0;
+        while (mat + 1u < p.count && pf_unit >= p.unit_end[mat]) { first = p.unit_end[mat]; ++mat; }
+        const uint32_t lu = pf_unit - first, rb = lu >> 2, r0 = (lu & 3u) * 8u;
+        tma_prefetch_5d(&p.map_w[mat], 0u, r0, 0u, pf_it * 4u, rb);
+        tma_prefetch_3d(&p.map_sf[mat], r0 * 4u, pf_it * 16u, rb);
+        ++pf_issued;
+        if (++pf_it == iters) { pf_it = 0; pf_unit += gridDim.x; }
+      };
       uint32_t g = 0;
       for (uint32_t unit = blockIdx.x; unit < p.units; unit += gridDim.x) {
         uint32_t mat = 0, first = 0;
@@ -210,13 +259,18 @@ nvfp4_gemv_mma_kernel(const __grid_constant__ GemvParams p) {
         const uint32_t lu = unit - first, rb = lu >> 2, r0 = (lu & 3u) * 8u;
         for (uint32_t it = 0; it < iters; ++it, ++g) {
           const uint32_t stage = g % kStages, phase = (g / kStages) & 1u;
+          if (kAhead != 0u && g >= kStages)                  // the ring is full: keep L2 `kAhead` stages ahead
+            while (pf_issued < g + kAhead + 1u && pf_unit < p.units) prefetch_one();
           if (!mbar_wait(&empty[stage], phase ^ 1u)) return;
           uint8_t *dst = ring + stage * kStageBytes;
           mbar_expect_tx(&full[stage], kStageBytes);        // whole boxes; columns past K arrive as zeros
           tma_load_5d(dst, &p.map_w[mat], 0u, r0, 0u, it * 4u, rb, &full[stage]);
           tma_load_3d(dst + kStageW, &p.map_sf[mat], r0 * 4u, it * 16u, rb, &full[stage]);
+          if (kAhead != 0u && pf_issued <= g) prefetch_one();   // cursor never falls behind the loads (skips what they fetched)
+          if (g == 0) Q36_TRACE(1);
         }
       }
+      Q36_TRACE(2);
     }
     return;
   }
@@ -225,6 +279,7 @@ nvfp4_gemv_mma_kernel(const __grid_constant__ GemvParams p) {
   if (threadIdx.x == 0) *zero_chunk = make_uint4(0u, 0u, 0u, 0u);
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (threadIdx.x == 0) Q36_TRACE(3);
 
   // Each warp stages the activations of ITS columns (128 of every 1024) as float16, alone.
   uint8_t *xw = xs + warp * iters * 256u;
@@ -293,6 +348,7 @@ nvfp4_gemv_mma_kernel(const __grid_constant__ GemvParams p) {
   }
   // Meets the producer's arrival (barriers initialised); also publishes slice_inv and the zero chunk.
   asm volatile("bar.sync 2, %0;" ::"n"(kThreads + 32) : "memory");
+  if (threadIdx.x == 0) Q36_TRACE(4);
 
   // Fragment geometry.  Lane (r = lane / 4, c = lane % 4) of the MMA holds weight rows r and r + 8 of a
   // 16-row tile.  Tile t of a unit is {rows q + 32 (2t), q + 32 (2t + 1)}, q < 8, and MMA row r maps
@@ -321,6 +377,7 @@ nvfp4_gemv_mma_kernel(const __grid_constant__ GemvParams p) {
       // A wait that gives up (never seen in practice) only stops the arithmetic: the warp keeps
       // walking its stages and barriers so that nobody else is left waiting for it.
       if (!dead && !mbar_wait(&full[stage], phase)) dead = true;
+      if (threadIdx.x == 0 && g == 0) Q36_TRACE(5);
       if (!dead) {
         const uint8_t *st = ring + stage * kStageBytes;
         uint4 bx[4];
@@ -362,6 +419,7 @@ nvfp4_gemv_mma_kernel(const __grid_constant__ GemvParams p) {
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty[stage]);
     }
+    if (threadIdx.x == 0) Q36_TRACE(6);
     // Lanes c = 0 and c = 1 hold the two scale tiles of the warp's columns; lanes c >= 2 hold zeros.
     float *buf = red + flip * (kWarps * 32u);
 #pragma unroll
@@ -386,6 +444,7 @@ nvfp4_gemv_mma_kernel(const __grid_constant__ GemvParams p) {
     // `buf` alternates between units: the next write to this buffer comes after the next unit's barrier,
     // which warp 0 only reaches after the reads above.
   }
+  if (threadIdx.x == 0) Q36_TRACE(7);
 }
 
 // ---- host side ---------------------------------------------------------------------------------
@@ -462,6 +521,10 @@ bool get_maps(const void *w, const void *sf, uint64_t N, uint64_t K, CUtensorMap
   return true;
 }
 
+#ifdef Q36_GEMV_TRACE
+std::atomic<uint32_t> g_trace_id{0};
+#endif
+
 struct Mat {
   const uint8_t *w, *sf;
   __nv_bfloat16 *y;
@@ -494,6 +557,9 @@ int launch(const Mat *mats, uint32_t count, uint64_t K, const void *x, const uin
   p.units = units;
   p.count = count;
   p.alpha = alpha;
+#ifdef Q36_GEMV_TRACE
+  p.trace_id = g_trace_id.fetch_add(1u);
+#endif
   const size_t smem = 1024 + kHeaderBytes + kRingBytes + static_cast<size_t>(p.iters) * 2048;
   if (q36::ensure_dynamic_smem(reinterpret_cast<const void *>(nvfp4_gemv_mma_kernel<XKIND>), 227 * 1024) != cudaSuccess)
     return QWEN36_STATUS_CUDA_ERROR;
@@ -543,6 +609,15 @@ int nvfp4_gemv_mma_fp4(const qwen36_nvfp4_gemm_spec_t *s, float alpha) {
 }
 
 }  // namespace q36
+
+#ifdef Q36_GEMV_TRACE
+// Copies the timestamp table [64 launches][320 CTAs][8 events] (u64 ns) to `dst` and rewinds the
+// launch counter.  Synchronises.
+extern "C" int qwen36_nvfp4_gemv_trace_read(void *dst) {
+  g_trace_id.store(0);
+  return cudaMemcpyFromSymbol(dst, g_trace, sizeof(g_trace)) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 // 1 when a bounded wait inside the tensor-core GEMV pipeline ever gave up (a stage never arrived);
 // the kernel then returns without finishing its rows.  Reads device memory: synchronises.

@@ -95,21 +95,6 @@ constexpr uint32_t kSpinLimit = 1u << 24;
 
 __device__ unsigned int g_matvec_error = 0;                 // set when a bounded wait gives up
 
-// Per-CTA timestamps for pipeline analysis; compiled in only with -DQ36_MATVEC_TRACE.
-#ifdef Q36_MATVEC_TRACE
-constexpr uint32_t kTraceLaunches = 64, kTraceCtas = 320, kTraceEvents = 8;
-__device__ unsigned long long g_trace[kTraceLaunches][kTraceCtas][kTraceEvents];
-#define Q36_TRACE_PARAM , uint32_t trace_id
-#define Q36_TRACE(ev)                                                                   \
-  do {                                                                                  \
-    unsigned long long t_;                                                              \
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                              \
-    if (blockIdx.x < kTraceCtas) g_trace[trace_id % kTraceLaunches][blockIdx.x][ev] = t_; \
-  } while (0)
-#else
-#define Q36_TRACE_PARAM
-#define Q36_TRACE(ev)
-#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -156,7 +141,7 @@ __global__ void __launch_bounds__(kThreads + 32)
 nvfp4_matvec_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_sf,
                     const __nv_bfloat16 *__restrict__ x, const uint8_t *__restrict__ weight,
                     const uint8_t *__restrict__ sf, const float *__restrict__ tensor_scale,
-                    __nv_bfloat16 *__restrict__ y, uint32_t K, uint32_t N Q36_TRACE_PARAM) {
+                    __nv_bfloat16 *__restrict__ y, uint32_t K, uint32_t N) {
   constexpr uint32_t kStages = kRingStagesX8 * 8u / QUADS;  // 4, 8, 16, 32
   constexpr uint32_t KPARTS = kWarps / QUADS;               // warps that split K of one quad
   constexpr uint32_t kStageW = QUADS * 4u * kSegBytes;
@@ -182,7 +167,6 @@ nvfp4_matvec_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   const uint32_t units = ((N + 127u) / 128u) * kUnitsPerBlock;
   const uint32_t row_bytes = K / 2u;
 
-  if (threadIdx.x == 0) Q36_TRACE(0);
   if (warp == kWarps) {
     // The producer warp owns the barriers: it initialises them (one stage per lane), signals the
     // consumers through a named barrier it does not wait on, and starts streaming at once.
@@ -210,10 +194,8 @@ nvfp4_matvec_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             mbar_expect_tx(&full[stage], kStageBytes);      // whole boxes; out-of-range columns arrive as zeros
             tma_load_4d(dst, &map_w, it * 128u, r0, 0u, rb, &full[stage]);
             tma_load_3d(dst + kStageW, &map_sf, r0 * 4u, it * 16u, rb, &full[stage]);
-            if (g == 0) Q36_TRACE(1);
           }
         }
-        Q36_TRACE(2);
       }
       return;
     }
@@ -244,7 +226,6 @@ nvfp4_matvec_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   // -------------------------------------------------------------------- consumer warps
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  if (threadIdx.x == 0) Q36_TRACE(3);
 
   // Stage x once per CTA as float16.  Every 32-value slot (what one lane consumes per stage) is
   // scaled by its own power of two that brings the slot's max|x| into [2^14, 2^15): every
@@ -290,7 +271,6 @@ nvfp4_matvec_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   }
   // Meets the producer's arrival (barriers initialised) and publishes x and the scale table.
   asm volatile("bar.sync 2, %0;" ::"n"(kThreads + 32) : "memory");
-  if (threadIdx.x == 0) Q36_TRACE(4);
 
   const uint32_t quad = warp % QUADS, kpart = warp / QUADS;
   const uint32_t rot0 = (16u * (lane & 1u) + 30u) & 31u;   // rotation that brings this lane's first scale byte to bits [9:2]
@@ -307,7 +287,6 @@ nvfp4_matvec_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       // A wait that gives up (never seen in practice) only stops the arithmetic: the warp keeps
       // walking its stages and barriers so that nobody else is left waiting for it.
       if (!dead && !mbar_wait(&full[stage], phase)) dead = true;
-      if (threadIdx.x == 0 && g == 0) Q36_TRACE(5);
       const uint8_t *st = ring + stage * kStageBytes;
       const uint32_t slot = lane + it * 32u;
       if (!dead && slot * 32u < K) {
@@ -373,7 +352,6 @@ nvfp4_matvec_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       }
     }
   }
-  if (threadIdx.x == 0) Q36_TRACE(6);
 }
 
 // Any shape, any alignment: one warp per row, byte loads.  Only taken when
@@ -405,9 +383,6 @@ nvfp4_matvec_generic_kernel(const __nv_bfloat16 *__restrict__ x, const uint8_t *
 }
 
 std::atomic<int> g_force_quads{0};
-#ifdef Q36_MATVEC_TRACE
-std::atomic<uint32_t> g_trace_id{0};
-#endif
 int sm_count() { return q36::sm_count_current_device(); }
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point lookup (no link against libcuda).
@@ -476,9 +451,6 @@ int launch_kernel(const qwen36_nvfp4_matvec_spec_t *s, const CUtensorMap &map_w,
       &cfg, nvfp4_matvec_kernel<QUADS, TMAP>, map_w, map_sf, as_ptr<const __nv_bfloat16>(s->input_bf16),
       as_ptr<const uint8_t>(s->weight_u8), as_ptr<const uint8_t>(s->block_scale_e4m3),
       as_ptr<const float>(s->tensor_scale_f32), as_ptr<__nv_bfloat16>(s->output_bf16), K, N
-#ifdef Q36_MATVEC_TRACE
-      , g_trace_id.fetch_add(1u)
-#endif
       ));
 }
 
@@ -515,15 +487,6 @@ int launch_fast(const qwen36_nvfp4_matvec_spec_t *s) {
 // Test hook: a unit size of 1, 2, 4 or 8 row quads sends every 32-column-aligned shape through the
 // SIMT pipeline with that unit size; anything else restores the library's own routing.
 extern "C" void qwen36_nvfp4_matvec_force_quads(int quads) { g_force_quads.store(quads); }
-
-#ifdef Q36_MATVEC_TRACE
-// Copies the timestamp table [64 launches][320 CTAs][8 events] (u64 ns) to `dst` and rewinds the
-// launch counter.  Synchronises.
-extern "C" int qwen36_nvfp4_matvec_trace_read(void *dst) {
-  g_trace_id.store(0);
-  return cudaMemcpyFromSymbol(dst, g_trace, sizeof(g_trace)) == cudaSuccess ? 0 : -1;
-}
-#endif
 
 // 1 when a bounded wait inside the GEMV pipeline ever gave up (a stage never arrived); the
 // kernel then returns without finishing its rows.  Reads device memory: synchronises.

@@ -9,8 +9,9 @@
 // NVLink crossing, no round trip, a few microseconds.
 //
 //   * plain st over NVLink only: no multicast objects, no TMA, no remote polling;
-//   * every wait is bounded (a few seconds at most), after which the kernel records the failure and
-//     returns with its output untouched;
+//   * every wait is bounded (a few seconds at most), after which the kernel poisons its output (NaN
+//     rows, token 0xFFFFFFFF), writes the number of the failed call into state[2] and sets a sticky
+//     process-wide error word, so the failure shows in the data a caller reads anyway;
 //   * the call number lives in device memory and is advanced by the kernel itself, so a CUDA graph
 //     that holds the launch can be replayed;
 //   * two inbox slots alternate by call number: a rank can be at most one call ahead of a peer (it
@@ -29,6 +30,7 @@ using q36::as_ptr;
 
 constexpr uint32_t kMaxWorld = 16;
 constexpr uint32_t kSpinLimit = 1u << 21;          // x (200 ns back-off + one local load): 1-2 s
+constexpr uint32_t kEagerPolls = 1024;             // polls without back-off: the common case ends here
 
 __device__ unsigned int g_peer_error = 0;
 
@@ -43,13 +45,17 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
 __device__ __forceinline__ void st_peer_u32(uint32_t *p, uint32_t v) {
   asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+__device__ __forceinline__ void st_peer_v4(float *p, float4 v) {
+  asm volatile("st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
 __device__ __forceinline__ uint32_t ld_inbox_u32(const uint32_t *p) {
   uint32_t v;
   asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
 
-// state[0] = number of completed calls, state[1] = CTAs of the running call that are done.
+// state[0] = number of completed calls, state[1] = CTAs of the running call that are done,
+// state[2] = number of the first call whose wait ran out (0 = none), state[3] unused.
 __device__ __forceinline__ uint32_t begin_call(const uint32_t *state) {
   return *reinterpret_cast<const volatile uint32_t *>(state) + 1u;
 }
@@ -63,8 +69,8 @@ __device__ __forceinline__ void end_call(uint32_t *state, uint32_t epoch) {
 
 // After this CTA's pushes: thread p raises flag `slot_of_cta` of this rank in peer p's flag array,
 // then waits for peer p's flag in the local array.  flags layout: [world][flags_per_rank].
-__device__ bool signal_and_wait(uint32_t *const *peer_flags, uint32_t world, uint32_t rank, uint32_t epoch,
-                                uint32_t flags_per_rank, uint32_t flag) {
+__device__ bool signal_and_wait(uint32_t *const *peer_flags, uint32_t *state, uint32_t world, uint32_t rank,
+                                uint32_t epoch, uint32_t flags_per_rank, uint32_t flag) {
   __shared__ int ok;
   if (threadIdx.x == 0) ok = 1;
   __syncthreads();                                             // all pushes of the CTA are issued
@@ -78,17 +84,19 @@ __device__ bool signal_and_wait(uint32_t *const *peer_flags, uint32_t world, uin
       if (++spin > kSpinLimit) {
         ok = 0;
         atomicExch(&g_peer_error, 1u);
+        atomicCAS(&state[2], 0u, epoch);
         break;
       }
-      __nanosleep(200);
+      if (spin > kEagerPolls) __nanosleep(200);
     }
   }
   __syncthreads();
   return ok != 0;
 }
 
-// One CTA of 256 threads per q head.  Inbox: [2 slots][world][q_heads][head_dim + 2] floats, a row =
-// o[head_dim], m, l.  The local input is n_parts split partials per head ([heads, n_parts(, head_dim)],
+// One CTA of 256 threads per q head.  Inbox: [2 slots][world][q_heads][row] floats, a row =
+// o[head_dim], m, l, padded to a multiple of four floats so that rows start on 16-byte boundaries
+// and go out as 16-byte peer stores.  The local input is n_parts split partials per head ([heads, n_parts(, head_dim)],
 // n_parts = 1: one finished partial per head); they are merged first, with the arithmetic of the
 // single-GPU merge kernel, and the result goes straight into the peers' inboxes.
 __global__ void __launch_bounds__(q36::kMergeThreads)
@@ -101,19 +109,22 @@ attention_peer_merge_kernel(const float *__restrict__ part_o, const float *__res
   __shared__ float s_red[q36::kMergeThreads / 32];
   const uint32_t h = blockIdx.x;
   const uint32_t epoch = begin_call(state);
-  const uint32_t row = head_dim + 2;
+  const uint32_t row = (head_dim + 2u + 3u) & ~3u;
   const size_t slot = static_cast<size_t>(epoch & 1u) * world * heads * row;
   float local_m, local_l;
   q36::lse_weights(part_m + static_cast<size_t>(h) * n_parts, part_l + static_cast<size_t>(h) * n_parts, n_parts,
                    s_parts, s_red, local_m, local_l);
-  for (uint32_t d = threadIdx.x; d < row; d += blockDim.x) {
-    const float v = d < head_dim
-        ? q36::lse_accumulate(part_o + static_cast<size_t>(h) * n_parts * head_dim, s_parts, n_parts, head_dim, d)
-        : (d == head_dim ? local_m : local_l);
+  const float *my_o = part_o + static_cast<size_t>(h) * n_parts * head_dim;
+  auto value_at = [&](uint32_t d) {
+    return d < head_dim ? q36::lse_accumulate(my_o, s_parts, n_parts, head_dim, d)
+                        : (d == head_dim ? local_m : (d == head_dim + 1u ? local_l : 0.f));
+  };
+  for (uint32_t d = threadIdx.x * 4u; d < row; d += blockDim.x * 4u) {
+    const float4 v = make_float4(value_at(d), value_at(d + 1u), value_at(d + 2u), value_at(d + 3u));
     const size_t at = slot + (static_cast<size_t>(rank) * heads + h) * row + d;
-    for (uint32_t p = 0; p < world; ++p) st_peer_u32(reinterpret_cast<uint32_t *>(peer_inbox[p] + at), __float_as_uint(v));
+    for (uint32_t p = 0; p < world; ++p) st_peer_v4(peer_inbox[p] + at, v);
   }
-  if (signal_and_wait(peer_flags, world, rank, epoch, heads, h)) {
+  if (signal_and_wait(peer_flags, state, world, rank, epoch, heads, h)) {
     const uint32_t *inbox = reinterpret_cast<const uint32_t *>(peer_inbox[rank] + slot);
     __shared__ float s_w[kMaxWorld];
     __shared__ float s_den;
@@ -143,6 +154,9 @@ attention_peer_merge_kernel(const float *__restrict__ part_o, const float *__res
         if (p < world) acc = fmaf(s_w[p], v[p], acc);
       out[static_cast<size_t>(h) * head_dim + d] = __float2bfloat16(s_den > 0.f ? __fdiv_rn(acc, s_den) : 0.f);
     }
+  } else {
+    for (uint32_t d = threadIdx.x; d < head_dim; d += blockDim.x)   // a peer never answered: no silent stale row
+      out[static_cast<size_t>(h) * head_dim + d] = __ushort_as_bfloat16(0x7FC0);
   }
   end_call(state, epoch);
 }
@@ -164,7 +178,7 @@ argmax_peer_combine_kernel(const float *__restrict__ value, const uint32_t *__re
       st_peer_u32(peer_inbox[p] + at + n_tokens, i);
     }
   }
-  if (signal_and_wait(peer_flags, world, rank, epoch, 1, 0)) {
+  if (signal_and_wait(peer_flags, state, world, rank, epoch, 1, 0)) {
     const uint32_t *inbox = peer_inbox[rank] + slot;
     for (uint32_t t = threadIdx.x; t < n_tokens; t += blockDim.x) {
       float best = -INFINITY;
@@ -185,6 +199,8 @@ argmax_peer_combine_kernel(const float *__restrict__ value, const uint32_t *__re
       }
       tokens[t] = best_i;
     }
+  } else {
+    for (uint32_t t = threadIdx.x; t < n_tokens; t += blockDim.x) tokens[t] = 0xFFFFFFFFu;   // no token has this id
   }
   end_call(state, epoch);
 }
@@ -218,7 +234,7 @@ extern "C" int qwen36_ipc_close_handle(qwen36_device_ptr_t ptr) {
 }
 
 extern "C" size_t qwen36_attention_peer_inbox_bytes(size_t world, size_t q_heads, size_t head_dim) {
-  return 2 * world * q_heads * (head_dim + 2) * sizeof(float);
+  return 2 * world * q_heads * ((head_dim + 2 + 3) / 4 * 4) * sizeof(float);
 }
 
 extern "C" size_t qwen36_argmax_peer_inbox_bytes(size_t world, size_t tokens) {
@@ -274,8 +290,8 @@ extern "C" int qwen36_argmax_peer_combine(const qwen36_argmax_peer_combine_spec_
   return q36::launch_status();
 }
 
-// 1 when a peer never raised its flag within the wait limit (the call left its output untouched).
-// Sticky until qwen36_peer_reset_error.
+// 1 when a peer never raised its flag within the wait limit (that call poisoned its output and wrote
+// its number into state[2]).  Sticky until qwen36_peer_reset_error.
 extern "C" int qwen36_peer_last_error(void) {
   unsigned int v = 0;
   if (cudaMemcpyFromSymbol(&v, g_peer_error, sizeof(v)) != cudaSuccess) return -1;

@@ -86,6 +86,8 @@ void qwen36_set_prefetch_stream(qwen36_cuda_stream_t s) { g_prefetch.store(cs(s)
 
 int qwen36_cuda_malloc(qwen36_device_allocation_t *out, size_t bytes) {
   if (out == nullptr) return QWEN36_STATUS_NULL_POINTER;
+  out->ptr.ptr = 0;                       // a failed call leaves an empty allocation behind, as in the reference
+  out->bytes = 0;
   if (bytes == 0) return QWEN36_STATUS_INVALID_ARGUMENT;
   void *p = nullptr;
   bump(C_MALLOC);
@@ -204,8 +206,8 @@ int qwen36_cuda_clear_l2_access_window(void) {
 
 int qwen36_l2_prefetch(qwen36_device_ptr_t base, size_t bytes, int target_cta_count) {
   cudaStream_t s = g_prefetch.load(std::memory_order_acquire);
-  if (s == nullptr || base.ptr == 0 || (base.ptr & 15u) != 0) return QWEN36_STATUS_INVALID_ARGUMENT;
-  if (bytes < 16) return QWEN36_STATUS_SUCCESS;
+  if (s == nullptr || base.ptr == 0 || bytes == 0 || (base.ptr & 15u) != 0) return QWEN36_STATUS_INVALID_ARGUMENT;
+  if (bytes < 16) return QWEN36_STATUS_SUCCESS;      // fewer bytes than one 16-byte read: nothing to warm
   const int ctas = target_cta_count > 0 ? target_cta_count : 128;
   l2_warm_kernel<<<ctas, 256, 0, s>>>(static_cast<const uint4 *>(raw(base)), bytes / 16, nullptr);
   return q36::launch_status();
@@ -290,16 +292,17 @@ int qwen36_cuda_graph_launch(qwen36_cuda_graph_exec_t x, qwen36_cuda_stream_t s)
 }
 
 int qwen36_increment_i32(qwen36_device_ptr_t target) {
-  if (target.ptr == 0) return QWEN36_STATUS_NULL_POINTER;
+  if (target.ptr == 0) return QWEN36_STATUS_INVALID_ARGUMENT;     // the reference's code for a null target
   increment_i32_kernel<<<1, 1, 0, q36::stream()>>>(static_cast<int32_t *>(raw(target)));
   return q36::launch_status();
 }
 
 int qwen36_mtp_assume_accept_chain_advance(qwen36_device_ptr_t position_i32, size_t draft_count,
                                            size_t position_count, int32_t position_delta) {
-  (void)draft_count;
-  if (position_i32.ptr == 0) return QWEN36_STATUS_NULL_POINTER;
-  if (position_count == 0) return QWEN36_STATUS_SUCCESS;
+  // argument checks and codes of kernels-cuda/runtime.cu:257-266
+  if (position_i32.ptr == 0) return QWEN36_STATUS_INVALID_ARGUMENT;
+  if (draft_count == 0 || draft_count > 4 || position_count == 0 || position_delta <= 0)
+    return QWEN36_STATUS_INVALID_ARGUMENT;
   const unsigned blocks = static_cast<unsigned>((position_count + 127) / 128);
   advance_positions_kernel<<<blocks, 128, 0, q36::stream()>>>(static_cast<int32_t *>(raw(position_i32)),
                                                               position_count, position_delta);

@@ -60,7 +60,7 @@ class PeerExchange:
                 raise KernelError("peer_exchange (CUDA IPC mapping of a peer's buffers)", abi.CUDA_ERROR)
         self.inbox_table = torch.tensor(inbox_ptrs, dtype=torch.int64, device=self.device)
         self.flag_table = torch.tensor(flag_ptrs, dtype=torch.int64, device=self.device)
-        self.state = torch.zeros(2, dtype=torch.int32, device=self.device)
+        self.state = torch.zeros(4, dtype=torch.int32, device=self.device)
         torch.cuda.synchronize(self.device)
         if self._dist:
             dist.barrier(group=group)       # every inbox is mapped and zeroed before anybody pushes
@@ -86,6 +86,12 @@ class PeerExchange:
     def failed(self) -> bool:
         """True once a combine kernel of this process gave up waiting for a peer."""
         return int(self.lib.qwen36_peer_last_error()) != 0
+
+    def failed_call(self) -> int:
+        """Number of the first call on THIS exchange whose wait ran out (0 = none): state[2], which the
+        kernel writes beside the poisoned output.  After a failure the exchange must be rebuilt on
+        every rank (re-zeroed state, flags and inbox under a barrier) before it is used again."""
+        return int(self.state[2].item())
 
     def close(self, group=None) -> None:
         torch.cuda.synchronize(self.device)

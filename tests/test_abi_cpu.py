@@ -191,6 +191,28 @@ def test_argument_validation_needs_no_gpu(lib):
     assert lib.qwen36_decode_nvfp4_gemv(C.byref(spec)) == abi.NOT_IMPLEMENTED
 
 
+def test_runtime_entry_points_keep_the_reference_status_codes(lib):
+    """kernels-cuda/runtime.cu:247-287 and decode_gemv/l2_prefetch.cu:41-53: a null target is
+    INVALID_ARGUMENT (not NULL_POINTER), the MTP position advance refuses 0 or more than 4 drafts, an
+    empty position list and a non-positive delta, a zero-byte prefetch is refused, and a failed
+    malloc leaves an empty allocation behind.  All of it is decided before any CUDA call."""
+    null, some = abi.DevicePtr(0), abi.DevicePtr(256)
+    lib.qwen36_mtp_assume_accept_chain_advance.argtypes = [abi.DevicePtr, C.c_size_t, C.c_size_t, C.c_int32]
+    lib.qwen36_l2_prefetch.argtypes = [abi.DevicePtr, C.c_size_t, C.c_int]
+    lib.qwen36_increment_i32.argtypes = [abi.DevicePtr]
+    assert lib.qwen36_increment_i32(null) == abi.INVALID_ARGUMENT
+    adv = lib.qwen36_mtp_assume_accept_chain_advance
+    assert adv(null, 1, 1, 1) == abi.INVALID_ARGUMENT
+    for drafts, count, delta in ((0, 1, 1), (5, 1, 1), (2, 0, 1), (2, 3, 0), (2, 3, -1)):
+        assert adv(some, drafts, count, delta) == abi.INVALID_ARGUMENT
+    assert lib.qwen36_l2_prefetch(null, 64, 0) == abi.INVALID_ARGUMENT
+    assert lib.qwen36_l2_prefetch(some, 0, 0) == abi.INVALID_ARGUMENT
+    alloc = abi.DeviceAllocation(abi.DevicePtr(0xdead), 77)
+    assert lib.qwen36_cuda_malloc(C.byref(alloc), 0) == abi.INVALID_ARGUMENT
+    assert alloc.ptr.ptr == 0 and alloc.bytes == 0
+    assert lib.qwen36_cuda_malloc(None, 16) == abi.NULL_POINTER
+
+
 def test_product_code_never_touches_the_oracle():
     """Nothing under the package may import, load or mention the oracle."""
     pkg = os.path.join(ROOT, "speedoza_b200")

@@ -80,7 +80,7 @@ def test_merge_with_host_played_peers_equals_merge_partials(backend, world, rank
     gen = torch.Generator(device="cuda").manual_seed(world * 10 + rank)
     m, l, o = _partials(gen, world, heads, dim)
     m[world - 1, 3] = float("-inf"); l[world - 1, 3] = 0; o[world - 1, 3] = 0      # an empty shard
-    row = dim + 2
+    row = (dim + 2 + 3) // 4 * 4              # rows are padded to 16 bytes
     inbox = torch.zeros((2, world, heads, row), dtype=torch.float32, device="cuda")
     flags = torch.zeros((world, heads), dtype=torch.int32, device="cuda")
     sink = [torch.zeros_like(inbox) for _ in range(world)]      # where the pushes to the "peers" land
@@ -93,7 +93,7 @@ def test_merge_with_host_played_peers_equals_merge_partials(backend, world, rank
     boxes = [inbox if p == rank else sink[p] for p in range(world)]
     flgs = [flags if p == rank else sink_flags[p] for p in range(world)]
     t_in, t_fl = _tables(*boxes), _tables(*flgs)
-    state = torch.zeros(2, dtype=torch.int32, device="cuda")
+    state = torch.zeros(4, dtype=torch.int32, device="cuda")
     out = torch.zeros((heads, dim), dtype=torch.bfloat16, device="cuda")
     dp = lambda t: abi.DevicePtr(t.data_ptr())
     po, pm, pl = o[rank].contiguous(), m[rank].contiguous(), l[rank].contiguous()
@@ -129,7 +129,7 @@ def test_argmax_with_host_played_peers_follows_the_greedy_rule(backend):
             inbox[1, p, 0] = v[p].view(torch.int32); inbox[1, p, 1] = i[p]; flags[p] = 1
     t_in = _tables(*[inbox if p == rank else sink[p] for p in range(world)])
     t_fl = _tables(*[flags if p == rank else sink_flags[p] for p in range(world)])
-    state = torch.zeros(2, dtype=torch.int32, device="cuda")
+    state = torch.zeros(4, dtype=torch.int32, device="cuda")
     out = torch.full((n,), -1, dtype=torch.int32, device="cuda")
     dp = lambda t: abi.DevicePtr(t.data_ptr())
     mv, mi = v[rank].contiguous(), i[rank].contiguous()
@@ -142,14 +142,15 @@ def test_argmax_with_host_played_peers_follows_the_greedy_rule(backend):
 
 
 def test_a_peer_that_never_answers_ends_in_an_error_status_not_a_hang(backend):
-    """The flag of rank 1 is never raised: the wait runs out, the output stays as it was, the status
-    says so, and the context is still usable afterwards."""
+    """The flag of rank 1 is never raised: the wait runs out, the output is poisoned (token 0xFFFFFFFF),
+    state[2] names the failed call (both readable without a synchronising query), the sticky status
+    says so too, and the context is still usable afterwards."""
     world, rank, n = 2, 0, 4
     inbox = [torch.zeros((2, world, 2, n), dtype=torch.int32, device="cuda") for _ in range(world)]
     flags = [torch.zeros(world, dtype=torch.int32, device="cuda") for _ in range(world)]
     t_in, t_fl = _tables(*inbox), _tables(*flags)
-    state = torch.zeros(2, dtype=torch.int32, device="cuda")
-    out = torch.full((n,), -1, dtype=torch.int32, device="cuda")
+    state = torch.zeros(4, dtype=torch.int32, device="cuda")
+    out = torch.full((n,), 7, dtype=torch.int32, device="cuda")
     v = torch.ones(n, device="cuda"); i = torch.arange(n, dtype=torch.int32, device="cuda")
     dp = lambda t: abi.DevicePtr(t.data_ptr())
     spec = abi.ArgmaxPeerCombineSpec(world, rank, n, dp(v), dp(i), dp(t_in), dp(t_fl), dp(state), dp(out))
@@ -157,7 +158,20 @@ def test_a_peer_that_never_answers_ends_in_an_error_status_not_a_hang(backend):
     assert backend.lib.qwen36_argmax_peer_combine(C.byref(spec)) == abi.SUCCESS
     torch.cuda.synchronize()
     assert int(backend.lib.qwen36_peer_last_error()) == 1
-    assert bool((out == -1).all())
+    assert bool((out == -1).all())                              # 0xFFFFFFFF: no vocabulary has this token
+    assert state.tolist() == [1, 0, 1, 0]                       # call 1 completed, and call 1 is the failed one
+    # the attention merge poisons its rows the same way
+    heads, dim, row = 2, 64, 68
+    a_inbox = [torch.zeros((2, world, heads, row), device="cuda") for _ in range(world)]
+    a_flags = [torch.zeros((world, heads), dtype=torch.int32, device="cuda") for _ in range(world)]
+    a_state = torch.zeros(4, dtype=torch.int32, device="cuda")
+    a_out = torch.zeros((heads, dim), dtype=torch.bfloat16, device="cuda")
+    po = torch.ones((heads, dim), device="cuda"); pm = torch.zeros(heads, device="cuda"); pl = torch.ones(heads, device="cuda")
+    a_spec = abi.AttentionPeerMergeSpec(world, rank, heads, dim, dp(po), dp(pm), dp(pl), dp(_tables(*a_inbox)),
+                                        dp(_tables(*a_flags)), dp(a_state), dp(a_out))
+    assert backend.lib.qwen36_attention_peer_merge(C.byref(a_spec)) == abi.SUCCESS
+    torch.cuda.synchronize()
+    assert bool(torch.isnan(a_out.float()).all()) and int(a_state[2]) == 1
     assert backend.lib.qwen36_peer_reset_error() == abi.SUCCESS
     assert int(backend.lib.qwen36_peer_last_error()) == 0
     assert int((torch.ones(4, device="cuda") * 2).sum()) == 8
