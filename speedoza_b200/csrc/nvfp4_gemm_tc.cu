@@ -12,9 +12,12 @@
 // is exactly the shared-memory image that tcgen05.cp 32x128b.warpx4 turns into the TMEM
 // scale operand, so scales go HBM -> smem -> TMEM without being touched by a thread.
 //
-// Warp roles (224 threads): warp 0 = TMA producer, warp 1 = TMEM allocator + MMA issuer,
-// warps 2..5 = epilogue (TMEM -> registers -> alpha, bf16 -> global), warp 6 = scale copier
-// (tcgen05.cp shared memory -> TMEM).  CTAs are persistent over
+// Warp roles (384 threads): warp 0 = TMA producer, warp 1 = TMEM allocator + MMA issuer, warp 2 =
+// scale copier (tcgen05.cp shared memory -> TMEM), warps 4..11 = epilogue (TMEM -> registers ->
+// alpha, bf16 -> global; a 256-token tile is drained by all eight, two per 32-lane quarter, so that
+// no warp has to hold more than 64 packed registers: the accumulator is handed back to the MMA warp
+// only when the drain is over, so a drain that spills registers stalls the tensor pipe; narrower
+// tiles use warps 4..7 only).  CTAs are persistent over
 // (row block, token block) tiles; with two accumulator stages the epilogue of one tile overlaps
 // the MMAs of the next.  This single-CTA form uses no cluster; the CTA-pair and split-K forms
 // further down do.  No multicast loads anywhere: every CTA loads its own tiles.
@@ -30,12 +33,43 @@
 namespace q36 {
 namespace {
 
-constexpr uint32_t kThreads = 224;
+constexpr uint32_t kThreads = 384;            // 12 warps: 0 TMA, 1 MMA, 2 scale copier, 3 idle, 4..11 epilogue
+constexpr uint32_t kWarpCopier = 2;
+constexpr uint32_t kWarpEpilogue = 4;         // first epilogue warp; warp w drains TMEM lanes [32 (w % 4), +32)
 constexpr uint32_t kBM = 128;
 constexpr uint32_t kBKBytes = 128;            // 256 fp4 values
 constexpr uint32_t kSpinLimit = 1u << 26;
+#ifndef Q36_GEMM_AHEAD
+#define Q36_GEMM_AHEAD 0
+#endif
+constexpr uint32_t kAhead = Q36_GEMM_AHEAD;   // weight stages asked of L2 ahead of the shared-memory ring
 
 __device__ unsigned int g_gemm_error = 0;
+
+// %globaltimer stamps of one CTA's pipeline events, per stage; compiled in only with -DQ36_GEMM_TRACE.
+#ifdef Q36_GEMM_TRACE
+constexpr uint32_t kTraceStages = 512, kTraceEvents = 8;
+__device__ unsigned long long g_gemm_trace[kTraceStages][kTraceEvents];
+#define Q36_GTRACE(g_, ev)                                                              \
+  do {                                                                                  \
+    if (blockIdx.x == 0 && (g_) < kTraceStages) {                                       \
+      unsigned long long t_;                                                            \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                            \
+      g_gemm_trace[(g_)][ev] = t_;                                                      \
+    }                                                                                   \
+  } while (0)
+#define Q36_GTRACE1(g_, ev)                                                             \
+  do {                                                                                  \
+    if (blockIdx.x == 1 && (g_) < kTraceStages) {                                       \
+      unsigned long long t_;                                                            \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                            \
+      g_gemm_trace[(g_)][7 - (ev)] = t_;                                                \
+    }                                                                                   \
+  } while (0)
+#else
+#define Q36_GTRACE(g_, ev)
+#define Q36_GTRACE1(g_, ev)
+#endif
 std::atomic<int> g_force_bn{0};
 std::atomic<int> g_force_split{0};
 
@@ -64,6 +98,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
 __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, uint32_t c0, uint32_t c1, uint64_t *bar) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+// L2 prefetch of a tile (no shared memory): the producer asks for the weight tile it will load a
+// few stages later, so that the load that fills shared memory hits L2 instead of waiting on HBM.
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap *map, uint32_t c0, uint32_t c1) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(c0), "r"(c1) : "memory");
 }
 __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -121,6 +160,8 @@ template <uint32_t BN> struct Cfg {
   static constexpr uint32_t kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
   static constexpr uint32_t kStages = BN >= 256 ? 4 : (BN >= 128 ? 5 : 6);
   static constexpr uint32_t kAccStages = BN >= 256 ? 1 : 2;
+  static constexpr uint32_t kEpiWarps = BN >= 256 ? 8 : 4;             // warps that drain one accumulator
+  static constexpr uint32_t kEpiCols = BN >= 256 ? BN / 2 : BN;        // columns per epilogue warp
   static constexpr uint32_t kAccCols = BN < 32 ? 32 : BN;              // columns reserved per accumulator stage
   static constexpr uint32_t kSfCols = 16 + 16 * kSfbTiles;             // per smem stage: SFA 4x4, SFB 4x4 per 128 tokens
   static constexpr uint32_t kTmemUsed = kAccStages * kAccCols + kStages * kSfCols;
@@ -145,7 +186,8 @@ nvfp4_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   uint64_t *full = reinterpret_cast<uint64_t *>(smem);                   // [kStages]
   uint64_t *empty = full + 8;                                            // [kStages]
   uint64_t *sf_full = empty + 8;                                         // [kStages] scales are in TMEM
-  uint64_t *acc_full = sf_full + 8;                                      // [kAccStages]
+  uint64_t *sf_landed = sf_full + 8;                                     // [kStages] scale tiles are in shared memory
+  uint64_t *acc_full = sf_landed + 8;                                    // [kAccStages]
   uint64_t *acc_empty = acc_full + 2;                                    // [kAccStages]
   uint32_t *tmem_base_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
   uint8_t *stages = smem + 1024;
@@ -158,8 +200,10 @@ nvfp4_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   const uint32_t sf_tok_blocks = (n + 127u) / 128u;                      // 128-token scale blocks that exist
 
   if (threadIdx.x == 0) {
-    for (uint32_t s = 0; s < C::kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); mbar_init(&sf_full[s], 1); }
-    for (uint32_t s = 0; s < C::kAccStages; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 4); }
+    for (uint32_t s = 0; s < C::kStages; ++s) {
+      mbar_init(&full[s], 1); mbar_init(&empty[s], 1); mbar_init(&sf_full[s], 1); mbar_init(&sf_landed[s], 1);
+    }
+    for (uint32_t s = 0; s < C::kAccStages; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], C::kEpiWarps); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -177,11 +221,20 @@ nvfp4_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     if (lane == 0) {
       uint32_t g = 0;
       bool dead = false;
+      uint32_t pf_tile = blockIdx.x, pf_kb = 0;
+      auto prefetch_one = [&]() {
+        if (pf_tile >= tiles) return;
+        tma_prefetch_2d(&map_a, pf_kb * kBKBytes, (pf_tile / n_blocks) * kBM);
+        if (++pf_kb == k_blocks) { pf_kb = 0; pf_tile += gridDim.x; }
+      };
+      for (uint32_t i = 0; i < kAhead; ++i) prefetch_one();
       for (uint32_t tile = blockIdx.x; tile < tiles && !dead; tile += gridDim.x) {
         const uint32_t nb = tile % n_blocks, mb = tile / n_blocks;
         for (uint32_t kb = 0; kb < k_blocks; ++kb, ++g) {
+          if (kAhead != 0u) prefetch_one();
           const uint32_t s = g % C::kStages, ph = (g / C::kStages) & 1u;
           if (!mbar_wait(&empty[s], ph ^ 1u)) { dead = true; break; }
+          Q36_GTRACE(g, 0);
           uint8_t *st = stages + s * C::kStageBytes;
           // scale tiles of token blocks past the end of the activation tensor do not exist in
           // the caller's buffer: they are skipped (their columns are never stored)
@@ -189,18 +242,22 @@ nvfp4_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
 #pragma unroll
           for (uint32_t t = 0; t < C::kSfbTiles; ++t)
             if ((static_cast<size_t>(nb) * BN) / 128u + t < sf_tok_blocks) ++sfb_tiles;
-          mbar_expect_tx(&full[s], C::kABytes + C::kBRows * kBKBytes + C::kSfaBytes + sfb_tiles * 2048u);
-          tma_load_2d(st, &map_a, kb * kBKBytes, mb * kBM, &full[s]);
-          tma_load_2d(st + C::kABytes, &map_b, kb * kBKBytes, nb * BN, &full[s]);
+          // The (small) scale tiles go first and on a barrier of their own: the copier warp moves them
+          // into TMEM while the operand tiles are still on their way.
+          mbar_expect_tx(&sf_landed[s], C::kSfaBytes + sfb_tiles * 2048u);
           bulk_g2s(st + C::kABytes + C::kBBytes, a_sf + (static_cast<size_t>(mb) * sf_tiles_per_block + kb * 4u) * 512u,
-                   2048u, &full[s]);
+                   2048u, &sf_landed[s]);
 #pragma unroll
           for (uint32_t t = 0; t < C::kSfbTiles; ++t) {
             const size_t tok_block = (static_cast<size_t>(nb) * BN) / 128u + t;
             if (tok_block < sf_tok_blocks)
               bulk_g2s(st + C::kABytes + C::kBBytes + C::kSfaBytes + t * 2048u,
-                       b_sf + (tok_block * sf_tiles_per_block + kb * 4u) * 512u, 2048u, &full[s]);
+                       b_sf + (tok_block * sf_tiles_per_block + kb * 4u) * 512u, 2048u, &sf_landed[s]);
           }
+          mbar_expect_tx(&full[s], C::kABytes + C::kBRows * kBKBytes);
+          tma_load_2d(st, &map_a, kb * kBKBytes, mb * kBM, &full[s]);
+          tma_load_2d(st + C::kABytes, &map_b, kb * kBKBytes, nb * BN, &full[s]);
+          Q36_GTRACE(g, 1);
         }
       }
     }
@@ -219,19 +276,22 @@ nvfp4_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           const uint32_t st = smem_u32(stages + s * C::kStageBytes);
           const uint32_t sfa_t = tmem_sf + s * C::kSfCols, sfb_t = sfa_t + 16u;
           if (!mbar_wait(&full[s], ph)) { dead = true; break; }
+          Q36_GTRACE(g, 4);
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           if (!mbar_wait(&sf_full[s], ph)) { dead = true; break; }     // the copier warp has put this stage's scales in TMEM
+          Q36_GTRACE(g, 5);
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
           for (uint32_t kk = 0; kk < 4; ++kk)
             mma_mxf4nvf4(d_tmem, desc_sw128(st + kk * 32u), desc_sw128(st + C::kABytes + kk * 32u), C::kIdesc,
                          sfa_t + kk * 4u, sfb_t + kk * C::kSfbTiles * 4u, (kb | kk) != 0u);
           mma_commit(&empty[s]);                 // frees the smem stage once these MMAs have read it
+          Q36_GTRACE(g, 6);
         }
         if (!dead) mma_commit(&acc_full[as]);    // accumulator complete
       }
     }
-  } else if (warp == 6) {
+  } else if (warp == kWarpCopier) {
     // ---------------------------------------------------------------- scale copier
     // Moves each stage's scale tiles shared memory -> TMEM from its own instruction stream, so that
     // the copies of stage s+1 can run while the MMAs of stage s execute.
@@ -241,7 +301,8 @@ nvfp4_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       for (uint32_t tile = blockIdx.x; tile < tiles && !dead; tile += gridDim.x) {
         for (uint32_t kb = 0; kb < k_blocks; ++kb, ++g) {
           const uint32_t s = g % C::kStages, ph = (g / C::kStages) & 1u;
-          if (!mbar_wait(&full[s], ph)) { dead = true; break; }
+          if (!mbar_wait(&sf_landed[s], ph)) { dead = true; break; }
+          Q36_GTRACE(g, 2);
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t st = smem_u32(stages + s * C::kStageBytes);
           const uint32_t sfa_t = tmem_sf + s * C::kSfCols, sfb_t = sfa_t + 16u;
@@ -254,12 +315,14 @@ nvfp4_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                          desc_sf(st + C::kABytes + C::kBBytes + C::kSfaBytes + t * 2048u + kk * 512u));
           }
           mma_commit(&sf_full[s]);
+          Q36_GTRACE(g, 3);
         }
       }
     }
-  } else {
-    // ---------------------------------------------------------------- epilogue warps 2..5
+  } else if (warp >= kWarpEpilogue && warp < kWarpEpilogue + C::kEpiWarps) {
+    // ---------------------------------------------------------------- epilogue warps
     const uint32_t quarter = warp & 3u;           // TMEM lanes [32*quarter, +32) are this warp's
+    const uint32_t col0 = ((warp - kWarpEpilogue) >> 2) * C::kEpiCols;   // first accumulator column of this warp
     uint32_t t_local = 0;
     bool dead = false;
     for (uint32_t tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++t_local) {
@@ -269,16 +332,16 @@ nvfp4_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       if (dead) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t row = mb * kBM + quarter * 32u + lane;           // feature index
-      const uint32_t taddr = tmem_base + as * C::kAccCols + ((quarter * 32u) << 16);
-      const uint32_t tok0 = nb * BN;
+      const uint32_t taddr = tmem_base + as * C::kAccCols + col0 + ((quarter * 32u) << 16);
+      const uint32_t tok0 = nb * BN + col0;
       if constexpr (BN >= 32) {
         // Drain the accumulator first: every 32-column slice is scaled, rounded to bf16 and kept
         // as packed pairs (tokens 2j, 2j+1 of this lane's feature), the TMEM stage is handed
         // back to the MMA warp, and only then do the (slow) global stores run, overlapped with
         // the next tile's MMAs even when there is a single accumulator stage.
-        uint32_t packed[BN / 2];
+        uint32_t packed[C::kEpiCols / 2];
 #pragma unroll
-        for (uint32_t c0 = 0; c0 < BN; c0 += 32) {
+        for (uint32_t c0 = 0; c0 < C::kEpiCols; c0 += 32) {
           uint32_t r[32];
           tmem_ld32(taddr + c0, r);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -296,7 +359,7 @@ nvfp4_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         const bool odd = (lane & 1u) != 0u;
         __nv_bfloat16 *crow = c + (row & ~1u);
 #pragma unroll
-        for (uint32_t j = 0; j < BN / 2; ++j) {
+        for (uint32_t j = 0; j < C::kEpiCols / 2; ++j) {
           const uint32_t got = __shfl_xor_sync(0xffffffffu, packed[j], 1);
           // even: (mine.lo, got.lo) = token 2j ; odd: (got.hi, mine.hi) = token 2j+1
           const uint32_t v = odd ? __byte_perm(got, packed[j], 0x7632) : __byte_perm(packed[j], got, 0x5410);
@@ -409,7 +472,8 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
   uint64_t *full = reinterpret_cast<uint64_t *>(smem);                   // [kStages]   used in the leader
   uint64_t *empty = full + 8;                                            // [kStages]   one per CTA
   uint64_t *sf_full = empty + 8;                                         // [kStages]   used in the leader
-  uint64_t *acc_full = sf_full + 8;                                      // one per CTA
+  uint64_t *sf_landed = sf_full + 8;                                     // [kStages]   used in the leader
+  uint64_t *acc_full = sf_landed + 8;                                    // one per CTA
   uint64_t *acc_empty = acc_full + 2;                                    // used in the leader: 8 epilogue warps
   uint32_t *tmem_base_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
   uint8_t *stages = smem + 1024;
@@ -424,9 +488,11 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
   const uint32_t sf_tiles_per_block = k / 64u;                           // 512-byte tiles per 128 rows
 
   if (threadIdx.x == 0) {
-    for (uint32_t s = 0; s < P::kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); mbar_init(&sf_full[s], 1); }
+    for (uint32_t s = 0; s < P::kStages; ++s) {
+      mbar_init(&full[s], 1); mbar_init(&empty[s], 1); mbar_init(&sf_full[s], 1); mbar_init(&sf_landed[s], 1);
+    }
     mbar_init(&acc_full[0], 1);
-    mbar_init(&acc_empty[0], 8);
+    mbar_init(&acc_empty[0], 16);           // eight epilogue warps in each CTA of the pair
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -451,17 +517,24 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         for (uint32_t kb = 0; kb < k_blocks; ++kb, ++g) {
           const uint32_t s = g % P::kStages, ph = (g / P::kStages) & 1u;
           if (!mbar_wait(&empty[s], ph ^ 1u)) { dead = true; break; }
+          if (leader) Q36_GTRACE(g, 0); else Q36_GTRACE1(g, 0);
           uint8_t *st = stages + s * P::kStageBytes;
-          const uint32_t bar = map_to_cta(smem_u32(&full[s]), 0u);       // the leader's barrier counts both CTAs' bytes
-          if (leader) mbar_expect_tx(&full[s], 2u * P::kStageBytes);
-          tma_load_2d_pair(st, &map_a, kb * kBKBytes, row_block * kBM, bar);
-          tma_load_2d_pair(st + P::kABytes, &map_b, kb * kBKBytes, nb * P::kBN + rank * P::kHalfTok, bar);
-          tma_load_2d_pair(st + P::kABytes + P::kBBytes, &map_sfa, 0u, row_block * sf_tiles_per_block + kb * 4u, bar);
+          // the leader's barriers count both CTAs' bytes; the (small) scale tiles go first and on a barrier
+          // of their own, so that the copier warp moves them into TMEM while the operand tiles still travel
+          const uint32_t bar = map_to_cta(smem_u32(&full[s]), 0u), bar_sf = map_to_cta(smem_u32(&sf_landed[s]), 0u);
+          if (leader) {
+            mbar_expect_tx(&sf_landed[s], 2u * (P::kSfaBytes + P::kSfbBytes));
+            mbar_expect_tx(&full[s], 2u * (P::kABytes + P::kBBytes));
+          }
+          tma_load_2d_pair(st + P::kABytes + P::kBBytes, &map_sfa, 0u, row_block * sf_tiles_per_block + kb * 4u, bar_sf);
           // token blocks past the end of the activation tensor lie outside the map and arrive as zeros
 #pragma unroll
           for (uint32_t t = 0; t < 2; ++t)
             tma_load_2d_pair(st + P::kABytes + P::kBBytes + P::kSfaBytes + t * 2048u, &map_sfb, 0u,
-                             (nb * 2u + t) * sf_tiles_per_block + kb * 4u, bar);
+                             (nb * 2u + t) * sf_tiles_per_block + kb * 4u, bar_sf);
+          tma_load_2d_pair(st, &map_a, kb * kBKBytes, row_block * kBM, bar);
+          tma_load_2d_pair(st + P::kABytes, &map_b, kb * kBKBytes, nb * P::kBN + rank * P::kHalfTok, bar);
+          if (leader) Q36_GTRACE(g, 1); else Q36_GTRACE1(g, 1);
         }
         if (dead) break;
       }
@@ -477,7 +550,9 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         for (uint32_t kb = 0; kb < k_blocks; ++kb, ++g) {
           const uint32_t s = g % P::kStages, ph = (g / P::kStages) & 1u;
           if (!mbar_wait(&full[s], ph)) { dead = true; break; }
+          Q36_GTRACE(g, 4);
           if (!mbar_wait(&sf_full[s], ph)) { dead = true; break; }     // scales of this stage are in both TMEMs
+          Q36_GTRACE(g, 5);
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t st = smem_u32(stages + s * P::kStageBytes);
           const uint32_t sfa_t = tmem_sf + s * P::kSfCols, sfb_t = sfa_t + 16u;
@@ -486,11 +561,12 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             mma_mxf4nvf4_pair(tmem_base, desc_sw128(st + kk * 32u), desc_sw128(st + P::kABytes + kk * 32u), P::kIdesc,
                               sfa_t + kk * 4u, sfb_t + kk * 8u, (kb | kk) != 0u);
           mma_commit_pair_fanout(&empty[s], 3);  // frees the stage in both CTAs once these MMAs have read it
+          Q36_GTRACE(g, 6);
         }
         if (!dead) mma_commit_pair_fanout(&acc_full[0], 3);   // accumulator complete, in both CTAs
       }
     }
-  } else if (warp == 6) {
+  } else if (warp == kWarpCopier) {
     // ---------------------------------------------------------------- scale copier (leader only)
     if (leader && lane == 0) {
       uint32_t g = 0;
@@ -498,7 +574,8 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
       for (uint32_t tile = pair_id; tile < tiles && !dead; tile += n_pairs) {
         for (uint32_t kb = 0; kb < k_blocks; ++kb, ++g) {
           const uint32_t s = g % P::kStages, ph = (g / P::kStages) & 1u;
-          if (!mbar_wait(&full[s], ph)) { dead = true; break; }
+          if (!mbar_wait(&sf_landed[s], ph)) { dead = true; break; }
+          Q36_GTRACE(g, 2);
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t st = smem_u32(stages + s * P::kStageBytes);
           const uint32_t sfa_t = tmem_sf + s * P::kSfCols, sfb_t = sfa_t + 16u;
@@ -511,12 +588,14 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                               desc_sf(st + P::kABytes + P::kBBytes + P::kSfaBytes + t * 2048u + kk * 512u));
           }
           mma_commit_pair(&sf_full[s]);
+          Q36_GTRACE(g, 3);
         }
       }
     }
-  } else {
-    // ---------------------------------------------------------------- epilogue warps 2..5 (both CTAs)
+  } else if (warp >= kWarpEpilogue) {
+    // ---------------------------------------------------------------- epilogue warps 4..11 (both CTAs)
     const uint32_t quarter = warp & 3u;           // TMEM lanes [32*quarter, +32) are this warp's
+    const uint32_t col0 = ((warp - kWarpEpilogue) >> 2) * (P::kBN / 2u);   // this warp's half of the columns
     const uint32_t acc_empty_leader = map_to_cta(smem_u32(&acc_empty[0]), 0u);
     uint32_t t_local = 0;
     for (uint32_t tile = pair_id; tile < tiles; tile += n_pairs, ++t_local) {
@@ -524,11 +603,11 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
       if (!mbar_wait(&acc_full[0], t_local & 1u)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t row = (mb * 2u + rank) * kBM + quarter * 32u + lane;     // feature index
-      const uint32_t taddr = tmem_base + ((quarter * 32u) << 16);
-      const uint32_t tok0 = nb * P::kBN;
-      uint32_t packed[P::kBN / 2];
+      const uint32_t taddr = tmem_base + col0 + ((quarter * 32u) << 16);
+      const uint32_t tok0 = nb * P::kBN + col0;
+      uint32_t packed[P::kBN / 4];
 #pragma unroll
-      for (uint32_t c0 = 0; c0 < P::kBN; c0 += 32) {
+      for (uint32_t c0 = 0; c0 < P::kBN / 2u; c0 += 32) {
         uint32_t r[32];
         tmem_ld32(taddr + c0, r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -544,7 +623,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
       const bool odd = (lane & 1u) != 0u;
       __nv_bfloat16 *crow = c + (row & ~1u);
 #pragma unroll
-      for (uint32_t j = 0; j < P::kBN / 2; ++j) {
+      for (uint32_t j = 0; j < P::kBN / 4; ++j) {
         const uint32_t got = __shfl_xor_sync(0xffffffffu, packed[j], 1);
         const uint32_t v = odd ? __byte_perm(got, packed[j], 0x7632) : __byte_perm(packed[j], got, 0x5410);
         const uint32_t tok = tok0 + 2u * j + (odd ? 1u : 0u);
@@ -656,7 +735,7 @@ nvfp4_gemm_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       }
       if (!dead) mma_commit(&acc_full[0]);
     }
-  } else if (warp == 6) {
+  } else if (warp == kWarpCopier) {
     if (lane == 0) {
       for (uint32_t kb = kb_begin, g = 0; kb < kb_end; ++kb, ++g) {
         const uint32_t s = g % C::kStages, ph = (g / C::kStages) & 1u;
@@ -672,8 +751,8 @@ nvfp4_gemm_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         mma_commit(&sf_full[s]);
       }
     }
-  } else {
-    // epilogue warps 2..5: drain this CTA's partial sums; ranks > 0 hand them to the first CTA
+  } else if (warp >= kWarpEpilogue && warp < kWarpEpilogue + 4u) {
+    // epilogue warps 4..7: drain this CTA's partial sums; ranks > 0 hand them to the first CTA
     const uint32_t quarter = warp & 3u;
     if (kb_end > kb_begin) {
       ok = mbar_wait(&acc_full[0], 0u);
@@ -702,7 +781,7 @@ nvfp4_gemm_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   cluster_sync_all();
-  if (rank == 0u && warp >= 2u && warp <= 5u && ok) {
+  if (rank == 0u && warp >= kWarpEpilogue && warp < kWarpEpilogue + 4u && ok) {
     const uint32_t quarter = warp & 3u;
     const uint32_t row_in = quarter * 32u + lane, row = mb * kBM + row_in;
     for (uint32_t r = 1; r < S; ++r) {                                   // fixed order: rank 1, 2, ...
@@ -904,6 +983,12 @@ int nvfp4_gemm_tc(const qwen36_nvfp4_gemm_spec_t *s, float alpha) {
 extern "C" void qwen36_nvfp4_gemm_force_bn(int bn) { g_force_bn.store(bn); }
 // Tuning hook: CTAs per row block of the split-K form for n <= 16 (1 = never split, 0 = heuristic).
 extern "C" void qwen36_nvfp4_gemm_force_split(int split) { g_force_split.store(split); }
+
+#ifdef Q36_GEMM_TRACE
+extern "C" int qwen36_nvfp4_gemm_trace_read(void *dst) {
+  return cudaMemcpyFromSymbol(dst, g_gemm_trace, sizeof(g_gemm_trace)) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 // 1 when a bounded wait inside the tensor-core GEMM ever gave up.  Synchronises.
 extern "C" int qwen36_nvfp4_gemm_last_error(void) {
