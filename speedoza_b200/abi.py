@@ -291,5 +291,7 @@ def load() -> C.CDLL:
     lib.qwen36_nvfp4_gemm_force_split.argtypes = [C.c_int]
     lib.qwen36_nvfp4_matvec_group.argtypes = [C.POINTER(Nvfp4MatvecSpec), size_t]
     lib.qwen36_nvfp4_matvec_force_quads.argtypes = [C.c_int]
+    lib.qwen36_nvfp4_quantize_set_path.restype = None
+    lib.qwen36_nvfp4_quantize_set_path.argtypes = [C.c_int]
     _lib = lib
     return lib

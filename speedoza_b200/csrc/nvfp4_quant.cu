@@ -8,6 +8,8 @@
 // UE4M3 ties down.
 #include "common.cuh"
 
+#include <atomic>
+
 namespace {
 
 using q36::as_ptr;
@@ -128,6 +130,165 @@ nvfp4_quantize_kernel(const __nv_bfloat16 *__restrict__ in, uint8_t *__restrict_
   }
 }
 
+// The same quantisation for the common layout (values % 16 == 0, aligned rows), built to be bound
+// by HBM rather than by instruction issue: 64 x 4 threads, a thread owns one 16-group of one row
+// (no division to find its row), rows advance by the grid; the group's scale arithmetic takes the
+// branch-free route when the scale is a normal UE4M3 number:
+//   * amax / (6 g) by reciprocal + two FMAs (the quotient is recomputed with the IEEE division when it
+//     lies within two ulps of a UE4M3 rounding boundary, so the scale byte is always the reference's);
+//   * UE4M3 encode = (bits + 0x7FFFF) >> 20 rebased (the +0x7FFFF carries into the exponent exactly as
+//     the reference's mantissa overflow does), clamp at 0x7E; decode = code << 20 rebased;
+//   * codes by multiplication with the correctly rounded reciprocal + the hardware e2m1x2 conversion;
+//     the rare pairs on which that can differ from the reference's division + threshold chain are
+//     found by one masked compare and patched in place (see the loop).
+// Groups whose scale is subnormal, saturated or very large are done with the reference's own
+// arithmetic (IEEE divisions, threshold chain).
+__global__ void __launch_bounds__(256)
+nvfp4_quantize_fast_kernel(const __nv_bfloat16 *__restrict__ in, uint8_t *__restrict__ out_fp4,
+                           uint8_t *__restrict__ out_sf, float *__restrict__ tensor_scale, uint32_t rows,
+                           uint32_t values, float input_tensor_scale) {
+  const float g = input_tensor_scale > 0.0f ? input_tensor_scale : 1.0f;
+  const float six_g = __fmul_rn(6.0f, g), rcp6 = __frcp_rn(six_g);
+  const uint32_t groups = values >> 4, padded = (groups + 3u) & ~3u;
+  const uint32_t group = blockIdx.x * 64u + threadIdx.x;
+  const bool in_row = group < groups;
+  if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0 && threadIdx.y == 0 && tensor_scale != nullptr) *tensor_scale = g;
+
+  // A thread walks several rows; the two 16-byte loads of the next row are issued before the current
+  // row is worked on, so the arithmetic of one group hides the memory latency of the next.
+  const uint32_t row_step = gridDim.y * 4u;
+  uint32_t row = blockIdx.y * 4u + threadIdx.y;
+  uint4 n0 = make_uint4(0u, 0u, 0u, 0u), n1 = n0;
+  if (in_row && row < rows) {
+    const uint4 *src = reinterpret_cast<const uint4 *>(in + (static_cast<size_t>(row) * values + group * 16u));
+    n0 = __ldcs(src);
+    n1 = __ldcs(src + 1);
+  }
+  for (; row < rows; row += row_step) {
+    uint32_t sf_code = 0;
+    const uint4 v0 = n0, v1 = n1;
+    if (in_row && row + row_step < rows) {
+      const uint4 *src = reinterpret_cast<const uint4 *>(in + (static_cast<size_t>(row + row_step) * values + group * 16u));
+      n0 = __ldcs(src);
+      n1 = __ldcs(src + 1);
+    }
+    if (in_row) {
+      const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+      float x[16];
+      float amax = 0.0f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        x[2 * i] = __uint_as_float(w[i] << 16);
+        x[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        amax = fmaxf(amax, fmaxf(fabsf(x[2 * i]), fabsf(x[2 * i + 1])));
+      }
+      uint32_t lo = 0, hi = 0;
+      if (amax > 0.0f) {
+        // sv = max(amax / (6 g), 1e-8)
+        float sv = __fmul_rn(amax, rcp6);
+        sv = fmaf(fmaf(-sv, six_g, amax), rcp6, sv);
+        const uint32_t sbits = __float_as_uint(sv);
+        const bool scale_fast = sv >= 0x1p-6f && sv < 448.0f;
+        if (!scale_fast || ((sbits + 2u - 0x80000u) & 0xfffffu) < 5u) sv = __fdiv_rn(amax, six_g);   // also when sv is not finite
+        sv = fmaxf(sv, 1.0e-8f);
+        float dec;
+        if (scale_fast) {
+          sf_code = min(((__float_as_uint(sv) + 0x7ffffu) >> 20) - 960u, 0x7eu);
+          dec = __uint_as_float((sf_code << 20) + 0x3c000000u);
+        } else {
+          sf_code = q36::encode_ue4m3(sv);
+          dec = q36::decode_e4m3(sf_code);
+        }
+        const float ds = fmaxf(__fmul_rn(dec, g), 1.0e-8f);
+        // ds with an all-ones mantissa is the one case in which reciprocal + two FMAs may miss the
+        // correctly rounded quotient; a very large ds could underflow a negative quotient to -0
+        const bool exact = !scale_fast || sf_code < 8u || ds > 65536.0f || (__float_as_uint(ds) & 0x7fffffu) == 0x7fffffu;
+        if (!exact) {
+          const float rcp = __frcp_rn(ds), nds = -ds;
+          // Four pairs per word: x * rcp (within 2 ulps of the IEEE quotient) through the hardware
+          // e2m1x2 conversion.  That is the reference's code unless the quotient lies within 2 ulps of
+          // a value with at most three significant bits: all seven rounding boundaries are such values
+          // (the approximate quotient may sit on the wrong side of one, and the hardware breaks exact
+          // ties to even where the reference breaks them toward zero: 0.75, 1.75, 3.5), and so is -0,
+          // which the reference encodes as +0.  One masked compare per pair finds these; the pair is
+          // then redone from the correctly rounded quotient (reciprocal + two FMAs, Markstein).  Exactly
+          // representable quotients are common, about 0.2 % of all values when bf16 inputs meet a short
+          // scale, so this patch stays per pair: redoing whole groups would put most warps on it.
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            float q[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) q[i] = __fmul_rn(x[8 * h + i], rcp);
+            uint32_t word;
+            asm("{\n\t.reg .b8 t0, t1, t2, t3;\n\t"
+                "cvt.rn.satfinite.e2m1x2.f32 t0, %2, %1;\n\t"
+                "cvt.rn.satfinite.e2m1x2.f32 t1, %4, %3;\n\t"
+                "cvt.rn.satfinite.e2m1x2.f32 t2, %6, %5;\n\t"
+                "cvt.rn.satfinite.e2m1x2.f32 t3, %8, %7;\n\t"
+                "mov.b32 %0, {t0, t1, t2, t3};\n\t}"
+                : "=r"(word)
+                : "f"(q[0]), "f"(q[1]), "f"(q[2]), "f"(q[3]), "f"(q[4]), "f"(q[5]), "f"(q[6]), "f"(q[7]));
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const uint32_t b0 = __float_as_uint(q[2 * i]), b1 = __float_as_uint(q[2 * i + 1]);
+              if (min((b0 + 2u) & 0x001ffffcu, (b1 + 2u) & 0x001ffffcu) == 0u) {
+                const float x0 = x[8 * h + 2 * i], x1 = x[8 * h + 2 * i + 1];
+                const float e0 = fmaf(fmaf(q[2 * i], nds, x0), rcp, q[2 * i]);
+                const float e1 = fmaf(fmaf(q[2 * i + 1], nds, x1), rcp, q[2 * i + 1]);
+                uint32_t byte;
+                asm("{\n\t.reg .b8 t;\n\tcvt.rn.satfinite.e2m1x2.f32 t, %1, %2;\n\tcvt.u32.u8 %0, t;\n\t}"
+                    : "=r"(byte) : "f"(e1), "f"(e0));
+                const uint32_t a0 = __float_as_uint(e0) & 0x7fffffffu, a1 = __float_as_uint(e1) & 0x7fffffffu;
+                if (a0 == 0x3f400000u || a0 == 0x3fe00000u || a0 == 0x40600000u) byte -= 1u;
+                if (a1 == 0x3f400000u || a1 == 0x3fe00000u || a1 == 0x40600000u) byte -= 16u;
+                if (a0 == 0u) byte &= 0xf0u;
+                if (a1 == 0u) byte &= 0x0fu;
+                word = (word & ~(0xffu << (8 * i))) | (byte << (8 * i));
+              }
+            }
+            if (h == 0) lo = word; else hi = word;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            lo |= q36::encode_e2m1x2(__fdiv_rn(x[2 * i], ds), __fdiv_rn(x[2 * i + 1], ds)) << (8 * i);
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            hi |= q36::encode_e2m1x2(__fdiv_rn(x[8 + 2 * i], ds), __fdiv_rn(x[9 + 2 * i], ds)) << (8 * i);
+        }
+      } else {
+        // amax is 0 (all zeros) or every value is NaN (fmaxf never picks NaN): the reference's scale is
+        // 1.0 either way; zeros encode to 0, NaNs to +6
+        sf_code = 0x38u;
+        uint32_t any = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) any |= w[i];
+        if ((any & 0x7fff7fffu) != 0u) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) lo |= q36::encode_e2m1x2(x[2 * i], x[2 * i + 1]) << (8 * i);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) hi |= q36::encode_e2m1x2(x[8 + 2 * i], x[9 + 2 * i]) << (8 * i);
+        }
+      }
+      *reinterpret_cast<uint2 *>(out_fp4 + (static_cast<size_t>(row) * (values >> 1) + group * 8u)) = make_uint2(lo, hi);
+    }
+    // the four scale bytes of a quad of groups form one word of the tiled layout (see q36::sf_offset)
+    const uint32_t lane4 = threadIdx.x & 3u;
+    uint32_t word = sf_code << (8u * lane4);
+    word |= __shfl_xor_sync(0xffffffffu, word, 1);
+    word |= __shfl_xor_sync(0xffffffffu, word, 2);
+    if (in_row) {
+      const size_t off = (static_cast<size_t>(group >> 2) + static_cast<size_t>(row >> 7) * (padded >> 2)) * 512u +
+                         (row & 31u) * 16u + ((row >> 5) & 3u) * 4u + lane4;
+      if ((group | 3u) < groups) {
+        if (lane4 == 0u) *reinterpret_cast<uint32_t *>(out_sf + off) = word;
+      } else {
+        out_sf[off] = static_cast<uint8_t>(sf_code);
+      }
+    }
+  }
+}
+
 // Row-major [rows, inner_groups] scale bytes -> tiled layout.  One thread per
 // 4-byte word of the OUTPUT, so that every byte of the tiled buffer (padding
 // included, as zero) is written exactly once and no separate memset is needed.
@@ -178,9 +339,22 @@ nvfp4_dequantize_kernel(const uint8_t *__restrict__ weight, const uint8_t *__res
   }
 }
 
+std::atomic<int> g_quantize_path{0};      // test hook: 1 = always the general kernel
+
 int launch_quantize(qwen36_device_ptr_t in, qwen36_device_ptr_t fp4, qwen36_device_ptr_t sf,
                     qwen36_device_ptr_t ts, size_t rows, size_t values, float its) {
   const size_t padded = q36::round_up(q36::div_ceil(values, 16), 4);
+  if (values % 16 == 0 && values < (1ull << 31) && rows < (1ull << 31) && (in.ptr & 15u) == 0 && (fp4.ptr & 7u) == 0 &&
+      (sf.ptr & 3u) == 0 && g_quantize_path.load() != 1) {
+    // about three waves of eight 256-thread CTAs per SM; a CTA covers 64 groups of 4 rows per step
+    const size_t gx = q36::div_ceil(padded, 64), row_chunks = q36::div_ceil(rows, 4);
+    const size_t want = q36::div_ceil(static_cast<size_t>(q36::sm_count_current_device()) * 24, gx);
+    const dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(row_chunks < want ? row_chunks : want));
+    nvfp4_quantize_fast_kernel<<<grid, dim3(64, 4), 0, q36::stream()>>>(
+        as_ptr<const __nv_bfloat16>(in), as_ptr<uint8_t>(fp4), as_ptr<uint8_t>(sf), as_ptr<float>(ts),
+        static_cast<uint32_t>(rows), static_cast<uint32_t>(values), its);
+    return q36::launch_status();
+  }
   const size_t total = rows * padded;
   const size_t blocks = q36::div_ceil(total, kThreads);
   if (blocks > 0x7fffffffull) return QWEN36_STATUS_INVALID_ARGUMENT;
@@ -200,6 +374,9 @@ int launch_quantize(qwen36_device_ptr_t in, qwen36_device_ptr_t fp4, qwen36_devi
 }
 
 }  // namespace
+
+// Test hook: 1 sends every shape through the general kernel, 0 restores the library's own routing.
+extern "C" void qwen36_nvfp4_quantize_set_path(int path) { g_quantize_path.store(path); }
 
 extern "C" int qwen36_nvfp4_quantize_bf16(const qwen36_nvfp4_quantize_spec_t *spec) {
   if (spec == nullptr) return QWEN36_STATUS_NULL_POINTER;

@@ -51,16 +51,47 @@ def adversarial_activations(rng, rows, k):
     return synth.f32_to_bf16_bits(x)
 
 
+@pytest.mark.parametrize("general", [0, 1])
 @pytest.mark.parametrize("rows,k,its", [(1, 128, 0.0), (5, 5120, 0.0), (7, 40, 1.25), (130, 192, 0.5),
-                                        (3, 33, 1.25), (64, 17408, 1.0 / 2688.0), (512, 5120, 0.37)])
-def test_quantize_rows_bit_exact(backend, rows, k, its):
+                                        (3, 33, 1.25), (64, 17408, 1.0 / 2688.0), (512, 5120, 0.37),
+                                        (37, 6144, 37.0), (9, 1040, 1e-3), (300, 48, 2.0 ** 12)])
+def test_quantize_rows_bit_exact(backend, rows, k, its, general):
+    """`general` = 1 forces the kernel that takes every shape; 0 lets widths that are multiples of 16
+    take the streamlined kernel (branch-free scale arithmetic for normal UE4M3 scales, the reference's
+    own arithmetic for the rest).  The large and tiny tensor scales push whole rows into the
+    subnormal, saturated and clamped scale ranges."""
     rng = np.random.default_rng(rows * 7 + k)
     x = adversarial_activations(rng, rows, k)
     w_fp4, w_sf, w_ts = orc.nvfp4_quantize_rows(x, its)
-    fp4, sf, ts = backend.nvfp4_quantize_rows(to_dev(x), its)
+    backend.lib.qwen36_nvfp4_quantize_set_path(general)
+    try:
+        fp4, sf, ts = backend.nvfp4_quantize_rows(to_dev(x), its)
+    finally:
+        backend.lib.qwen36_nvfp4_quantize_set_path(0)
     assert float(ts.item()) == np.float32(w_ts)
     assert np.array_equal(fp4.cpu().numpy(), w_fp4), "packed codes"
     assert np.array_equal(sf.cpu().numpy(), w_sf), "scale bytes"
+
+
+def test_quantize_scale_bytes_at_every_ue4m3_boundary(backend):
+    """Group maxima placed on, just below and just above every rounding boundary of the UE4M3 scale
+    (amax = 6 * boundary, which bf16 holds exactly or within one step): the streamlined kernel's
+    reciprocal-multiply quotient must land on the reference's byte, ties included."""
+    vals = []
+    for code in range(0x08, 0x7E):
+        a = orc.e4m3_decode(code); b = orc.e4m3_decode(code + 1)
+        mid = np.float32((a + b) * 0.5 * 6.0)
+        bits = int(synth.f32_to_bf16_bits(np.array([mid], np.float32))[0])
+        vals += [bits - 1, bits, bits + 1]
+    vals = np.array(vals, dtype=np.uint16)
+    x = np.zeros((len(vals), 16), dtype=np.uint16)
+    x[:, 3] = vals
+    x[:, 7] = vals | 0x8000
+    for its in (0.0, 1.0 / 3.0, 0.37, 7.0):
+        w_fp4, w_sf, _ = orc.nvfp4_quantize_rows(x, its)
+        fp4, sf, _ = backend.nvfp4_quantize_rows(to_dev(x), its)
+        assert np.array_equal(sf.cpu().numpy(), w_sf), its
+        assert np.array_equal(fp4.cpu().numpy(), w_fp4), its
 
 
 def test_quantize_single_row_entry_and_known_answer(backend):
