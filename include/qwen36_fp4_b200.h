@@ -349,6 +349,44 @@ typedef struct {                         /* qwen36_fp4.h:151-183 */
  * the buffers one CTA per q head walks the whole context.  TurboQuant3 / 3.5
  * caches (dtype 2 / 3) return QWEN36_STATUS_NOT_IMPLEMENTED. */
 int qwen36_attention_decode(const qwen36_attention_decode_spec_t *spec);
+
+/* Replaces qwen36_attention_decode_split_tiled (kernels-cuda/attention_decode_tiled.cu:159-357,
+ * 370-403; not in the reference's public header, declared in attention.cu:2408-2418): the split-KV
+ * half of a decode step on its own.  Split s covers timesteps [s * split_timesteps_per_block,
+ * (s + 1) * split_timesteps_per_block) cut at position + 1, the timestep at `position` being the new
+ * k_bf16 / v_bf16 row; it writes only the partials ([q_heads, n_splits(, head_dim)], an empty split
+ * as (-inf, 0, 0)) and the split that owns `position` appends the row to the cache.  A merge
+ * (qwen36_attention_merge_partials) turns the partials into the output.  head_dim 256, 2..8 q heads
+ * per kv head, BF16 / FP8 cache, block a multiple of 8: other shapes return NOT_IMPLEMENTED, as the
+ * reference's entry does. */
+int qwen36_attention_decode_split_tiled(const qwen36_attention_decode_spec_t *spec, int n_splits,
+                                        int split_timesteps_per_block);
+
+/* ---- speculative-verify attention: a short query chunk over a long cache ---- */
+
+typedef struct {                         /* qwen36_fp4.h:108-147 */
+  size_t layer_index, start_position, tokens;
+  qwen36_device_ptr_t q_bf16, k_bf16, v_bf16, kv_cache_k, kv_cache_v, kv_cache_metadata, output_bf16;
+  qwen36_attention_shape_t shape;
+  int kv_cache_dtype;                    /* 0 = BF16, 1 = FP8 E4M3 */
+  qwen36_device_ptr_t start_position_device_i32;
+  qwen36_device_ptr_t partial_acc_f32, partial_max_f32, partial_denom_f32;
+  size_t prefill_n_splits, split_timesteps_per_block;
+  qwen36_device_ptr_t tree_ancestor_bitmap_u64;
+  size_t verify_chunk_rows;
+} qwen36_attention_prefill_spec_t;
+
+/* Replaces qwen36_attention_flash_splitk_prefill_bf16 (kernels-cuda/attention_flash_splitk.cu:96-420,
+ * 504-600; declared in attention.cu:2408): `tokens` <= 32 query rows x q_heads, already appended to
+ * the cache, attend to cache rows [0, start_position + tokens) under the causal mask of the chunk
+ * (row i sees rows <= start_position + i); head_dim 256, BF16 or FP8 cache.  The 64-row K iterations
+ * are dealt evenly to `n_splits` splits; partials are token-major
+ * ([tokens, q_heads, n_splits(, head_dim)]) in the spec's three partial buffers, or, when the spec
+ * has none, in a scratch the library grows on demand (growing allocates: during a stream capture the
+ * call returns NOT_IMPLEMENTED instead, which the reference's dispatcher treats as "use another
+ * path", attention.cu:2666-2671).  k_bf16 / v_bf16, the split fields and the tree bitmap of the spec
+ * are not read by this entry (nor by the reference's). */
+int qwen36_attention_flash_splitk_prefill_bf16(const qwen36_attention_prefill_spec_t *spec, int n_splits);
 /* Test hooks: mode 0 = general kernel only, 1 = tensor-core kernels where they
  * apply (default); n > 0 overrides the number of splits used. */
 void qwen36_attention_decode_set_mode(int mode);
@@ -572,8 +610,6 @@ int qwen36_bf16_matvec(const void *spec);
 int qwen36_attention_prefill(const void *spec);
 int qwen36_attention_flash_prefill(const void *spec);
 int qwen36_attention_sage_prefill(const void *spec);
-int qwen36_attention_decode_split_tiled(const void *spec, int a, int b);
-int qwen36_attention_flash_splitk_prefill_bf16(const void *spec, int n_splits);
 int qwen36_deltanet_decode(const void *spec);
 int qwen36_deltanet_prefill(const void *spec);
 void qwen36_deltanet_set_resident(int mode);

@@ -356,6 +356,40 @@ def attention_decode(q_bf16: np.ndarray, k_new: np.ndarray, v_new: np.ndarray, c
     return out
 
 
+def attention_verify(q_bf16: np.ndarray, cache_k: np.ndarray, cache_v: np.ndarray, kv_cache_dtype: int,
+                     start_position: int) -> np.ndarray:
+    """Speculative-verify attention, the arithmetic of kernels-cuda/attention_flash_splitk.cu:96-420
+    restated without tiles or splits: q [tokens, q_heads, 256] bf16 bits; caches [>= start + tokens,
+    kv_heads, 256] of uint16 (BF16) or uint8 (E4M3, read as attention_flash_splitk.cu:54-72 reads it:
+    0x7F / 0xFF are +-448); query row i attends to cache rows [0, start + i] (causal mask, lines
+    243-254) with scores q.k * rsqrt(256); float64 softmax; returns float64 [tokens, q_heads, 256]
+    (the kernel rounds probabilities to the operand type before P V and the result to bf16: the GPU
+    test allows rel-L2 1e-2 for that)."""
+    tokens, q_heads, head_dim = q_bf16.shape
+    kv_heads = cache_k.shape[1]
+    rows = start_position + tokens
+    if kv_cache_dtype == 1:
+        table = np.array([kv_e4m3_decode(c) for c in range(256)], dtype=np.float64)
+        k = table[cache_k[:rows]]
+        v = table[cache_v[:rows]]
+    else:
+        k = bf16_to_f32(cache_k[:rows]).astype(np.float64)
+        v = bf16_to_f32(cache_v[:rows]).astype(np.float64)
+    q = bf16_to_f32(q_bf16).astype(np.float64)
+    out = np.zeros((tokens, q_heads, head_dim), dtype=np.float64)
+    per = q_heads // kv_heads
+    for h in range(q_heads):
+        kvh = h // per
+        s = q[:, h, :] @ k[:, kvh, :].T / np.sqrt(float(head_dim))          # [tokens, rows]
+        t = np.arange(rows)[None, :]
+        s = np.where(t <= (start_position + np.arange(tokens))[:, None], s, -np.inf)
+        s = s - s.max(axis=1, keepdims=True)
+        pr = np.exp(s)
+        pr /= pr.sum(axis=1, keepdims=True)
+        out[:, h, :] = pr @ v[:, kvh, :]
+    return out
+
+
 def num_threads() -> int:
     return int(lib().orc_num_threads())
 

@@ -158,6 +158,16 @@ class AttentionDecodeSpec(C.Structure):
                 ("decode_n_splits", size_t), ("split_timesteps_per_block", size_t)]
 
 
+class AttentionPrefillSpec(C.Structure):
+    _fields_ = [("layer_index", size_t), ("start_position", size_t), ("tokens", size_t), ("q_bf16", DevicePtr),
+                ("k_bf16", DevicePtr), ("v_bf16", DevicePtr), ("kv_cache_k", DevicePtr), ("kv_cache_v", DevicePtr),
+                ("kv_cache_metadata", DevicePtr), ("output_bf16", DevicePtr), ("shape", AttentionShape),
+                ("kv_cache_dtype", C.c_int), ("start_position_device_i32", DevicePtr),
+                ("partial_acc_f32", DevicePtr), ("partial_max_f32", DevicePtr), ("partial_denom_f32", DevicePtr),
+                ("prefill_n_splits", size_t), ("split_timesteps_per_block", size_t),
+                ("tree_ancestor_bitmap_u64", DevicePtr), ("verify_chunk_rows", size_t)]
+
+
 class TurboquantAttentionPartialSpec(C.Structure):
     _fields_ = [("t_begin", size_t), ("t_end", size_t), ("q_bf16", DevicePtr),
                 ("k_quantized_i8", DevicePtr), ("v_quantized_i8", DevicePtr),
@@ -291,6 +301,8 @@ def load() -> C.CDLL:
     lib.qwen36_nvfp4_gemm_force_split.argtypes = [C.c_int]
     lib.qwen36_nvfp4_matvec_group.argtypes = [C.POINTER(Nvfp4MatvecSpec), size_t]
     lib.qwen36_nvfp4_matvec_force_quads.argtypes = [C.c_int]
+    lib.qwen36_attention_flash_splitk_prefill_bf16.argtypes = [C.POINTER(AttentionPrefillSpec), C.c_int]
+    lib.qwen36_attention_decode_split_tiled.argtypes = [C.POINTER(AttentionDecodeSpec), C.c_int, C.c_int]
     lib.qwen36_nvfp4_quantize_set_path.restype = None
     lib.qwen36_nvfp4_quantize_set_path.argtypes = [C.c_int]
     _lib = lib

@@ -317,6 +317,23 @@ class CudaBackend:
         _check("attention_decode", self.lib.qwen36_attention_decode(C.byref(spec)))
         return out
 
+    def attention_flash_splitk_prefill(self, q_bf16, cache_k, cache_v, start_position: int, kv_cache_dtype: int,
+                                       n_splits: int, partials=None, start_position_device=None, out=None):
+        """Speculative-verify attention (qwen36_attention_flash_splitk_prefill_bf16): q [tokens <= 32, q_heads,
+        256] over cache rows [0, start + tokens), causal inside the chunk.  `partials` = (acc [tokens, q_heads,
+        n_splits, 256], max, denom [tokens, q_heads, n_splits]) or None for the library's own scratch."""
+        tokens, q_heads, head_dim = q_bf16.shape
+        if out is None:
+            out = torch.empty((tokens, q_heads, head_dim), dtype=torch.bfloat16, device=q_bf16.device)
+        pa, pm, pl = partials if partials is not None else (None, None, None)
+        spec = abi.AttentionPrefillSpec(0, start_position, tokens, _dp(q_bf16), DevicePtr(0), DevicePtr(0), _dp(cache_k),
+                                        _dp(cache_v), DevicePtr(0), _dp(out),
+                                        abi.AttentionShape(q_heads, cache_k.shape[1], head_dim, 0), kv_cache_dtype,
+                                        _dp(start_position_device), _dp(pa), _dp(pm), _dp(pl), 0, 0, DevicePtr(0), 0)
+        _check("attention_flash_splitk_prefill_bf16",
+               self.lib.qwen36_attention_flash_splitk_prefill_bf16(C.byref(spec), n_splits))
+        return out
+
     def turboquant_attention_static(self, q_bf16, kq, vq, meta, position: int, out=None) -> torch.Tensor:
         """Same result as turboquant_attention, but the split-KV partials live in a fixed buffer
         inside the library, so no scratch is passed and nothing is allocated by the call."""

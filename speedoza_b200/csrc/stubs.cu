@@ -32,15 +32,5 @@ Q36_STUB(qwen36_q_proj_deinterleave)
 Q36_STUB(qwen36_q_proj_sigmoid_gate)
 Q36_STUB(qwen36_copy_strided_rows)
 
-extern "C" int qwen36_attention_decode_split_tiled(const void *spec, int a, int b) {
-  (void)spec; (void)a; (void)b;
-  return QWEN36_STATUS_NOT_IMPLEMENTED;
-}
-// The reference's callers treat NOT_IMPLEMENTED from this entry as "fall
-// through to the next attention path" (kernels-cuda/attention.cu:2666-2671).
-extern "C" int qwen36_attention_flash_splitk_prefill_bf16(const void *spec, int n_splits) {
-  (void)spec; (void)n_splits;
-  return QWEN36_STATUS_NOT_IMPLEMENTED;
-}
 extern "C" void qwen36_deltanet_set_resident(int mode) { (void)mode; }
 extern "C" void qwen36_deltanet_prefill_set_tiny(int mode) { (void)mode; }

@@ -99,6 +99,12 @@ def test_struct_layouts_equal_reference_header(tmp_path):
                                            "kv_cache_dtype", "position_device_i32", "partial_acc_f32",
                                            "partial_max_f32", "partial_denom_f32", "decode_n_splits",
                                            "split_timesteps_per_block"],
+        "qwen36_attention_prefill_spec_t": ["layer_index", "start_position", "tokens", "q_bf16", "k_bf16", "v_bf16",
+                                            "kv_cache_k", "kv_cache_v", "kv_cache_metadata", "output_bf16", "shape",
+                                            "kv_cache_dtype", "start_position_device_i32", "partial_acc_f32",
+                                            "partial_max_f32", "partial_denom_f32", "prefill_n_splits",
+                                            "split_timesteps_per_block", "tree_ancestor_bitmap_u64",
+                                            "verify_chunk_rows"],
         "qwen36_attention_shape_t": ["q_heads", "kv_heads", "head_dim", "rope_dims"],
         "qwen36_cuda_counters_t": ["malloc_calls", "graph_launch_calls"],
         "qwen36_cuda_diagnostics_t": ["driver_version", "total_global_mem", "device_name", "last_cuda_error_string"],
@@ -138,6 +144,7 @@ def test_ctypes_mirrors_match_header_sizes(tmp_path):
              "qwen36_turboquant_encode_rows_spec_t": abi.TurboquantEncodeRowsSpec,
              "qwen36_turboquant_attention_spec_t": abi.TurboquantAttentionSpec,
              "qwen36_attention_decode_spec_t": abi.AttentionDecodeSpec,
+             "qwen36_attention_prefill_spec_t": abi.AttentionPrefillSpec,
              "qwen36_turboquant_attention_partial_spec_t": abi.TurboquantAttentionPartialSpec,
              "qwen36_attention_merge_spec_t": abi.AttentionMergeSpec,
              "qwen36_attention_peer_merge_spec_t": abi.AttentionPeerMergeSpec,
@@ -184,7 +191,10 @@ def test_argument_validation_needs_no_gpu(lib):
     assert lib.qwen36_ipc_get_handle(abi.DevicePtr(0), None) == abi.NULL_POINTER
     # out-of-scope operators link and decline
     assert lib.qwen36_rmsnorm(None) == abi.NOT_IMPLEMENTED
-    assert lib.qwen36_attention_flash_splitk_prefill_bf16(None, 4) == abi.NOT_IMPLEMENTED
+    assert lib.qwen36_attention_flash_splitk_prefill_bf16(None, 4) == abi.NULL_POINTER
+    assert lib.qwen36_attention_flash_splitk_prefill_bf16(C.byref(abi.AttentionPrefillSpec()), 4) == abi.INVALID_ARGUMENT
+    assert lib.qwen36_attention_decode_split_tiled(None, 4, 64) == abi.NULL_POINTER
+    assert lib.qwen36_attention_decode_split_tiled(C.byref(abi.AttentionDecodeSpec()), 4, 64) == abi.NOT_IMPLEMENTED
     # n > 8 on the decode GEMV entry is the soft "use the GEMM" code
     spec = abi.Nvfp4GemmSpec(m=128, n=9, k=256, a_fp4=abi.DevicePtr(16), a_scale=abi.DevicePtr(16),
                              b_fp4=abi.DevicePtr(16), b_scale=abi.DevicePtr(16), c_bf16=abi.DevicePtr(16))

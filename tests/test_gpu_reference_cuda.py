@@ -216,6 +216,74 @@ def test_reference_attention_decode_equals_oracle_and_this_library(ref, backend,
                   synth.bf16_bits_to_f32(bf16_host(out_r)).astype(np.float64)) <= 1e-2
 
 
+@pytest.mark.parametrize("dtype", [0, 1])
+@pytest.mark.parametrize("start,tokens,n_splits", [(0, 16, 1), (100, 5, 3), (1000, 16, 16), (4093, 32, 48), (700, 9, 64)])
+def test_reference_verify_attention_equals_oracle_and_this_library(ref, backend, dtype, start, tokens, n_splits):
+    """qwen36_attention_flash_splitk_prefill_bf16: the reference's wmma kernel + reduce, this library's
+    kernel + reduce and the oracle on the same seeded inputs (seed 515151 as in the reference's own
+    kernel-vs-kernel gate, kernels-cuda/smoke.cu:3614-3773).  Outputs within rel-L2 1e-2 of the oracle
+    and of each other; the per-split partials (same partition, same token-major layout) agree too:
+    max within 1e-3, denominator and accumulator within rel 5e-3 (both round P to the operand type)."""
+    from test_gpu_attention_verify import make_verify_case, rel_l2
+    from test_gpu_kv_decode import cache_to_dev
+    q, ck, cv = make_verify_case(515151 + start + tokens + dtype, start, tokens, 24, 4, dtype)
+    want = orc.attention_verify(q, ck, cv, dtype, start)
+    qd, ckd, cvd = to_dev(q), cache_to_dev(ck), cache_to_dev(cv)
+    results = []
+    for lib in (ref, backend.lib):
+        out = torch.zeros((tokens, 24, 256), dtype=torch.bfloat16, device="cuda")
+        pa = torch.zeros((tokens, 24, n_splits, 256), device="cuda")
+        pm = torch.zeros((tokens, 24, n_splits), device="cuda")
+        pl = torch.zeros((tokens, 24, n_splits), device="cuda")
+        spec = abi.AttentionPrefillSpec(0, start, tokens, dp(qd), dp(None), dp(None), dp(ckd), dp(cvd), dp(None), dp(out),
+                                        abi.AttentionShape(24, 4, 256, 0), dtype, dp(None), dp(pa), dp(pm), dp(pl), 0, 0,
+                                        dp(None), 0)
+        torch.cuda.synchronize()
+        assert lib.qwen36_attention_flash_splitk_prefill_bf16(C.byref(spec), n_splits) == 0
+        torch.cuda.synchronize()
+        got = synth.bf16_bits_to_f32(bf16_host(out))
+        assert rel_l2(got, want) <= 1e-2
+        results.append((got, pa.cpu().numpy(), pm.cpu().numpy(), pl.cpu().numpy()))
+    (o_r, pa_r, pm_r, pl_r), (o_m, pa_m, pm_m, pl_m) = results
+    assert rel_l2(o_m, o_r) <= 1e-2
+    assert np.array_equal(np.isneginf(pm_r), np.isneginf(pm_m))
+    live = ~np.isneginf(pm_r)
+    assert np.allclose(pm_m[live], pm_r[live], rtol=0, atol=1e-3)
+    assert np.allclose(pl_m[live], pl_r[live], rtol=5e-3)
+    assert rel_l2(pa_m, pa_r) <= 5e-3
+
+
+@pytest.mark.parametrize("dtype", [0, 1])
+@pytest.mark.parametrize("position,block", [(0, 64), (513, 64), (3000, 128), (2049, 8)])
+def test_reference_decode_split_tiled_equals_this_library(ref, backend, dtype, position, block):
+    """qwen36_attention_decode_split_tiled: partials of the reference's register-tiled kernel and of this
+    library for the same fixed-size splits, and the cache after the call (append by the owning split)
+    byte-identical."""
+    from test_gpu_kv_decode import make_case, cache_to_dev, cache_host, partial_buffers
+    q, k_new, v_new, ck, cv = make_case(626262 + position + dtype, position + 1, 24, 4, 256, dtype)
+    qd, kd, vd = to_dev(q), to_dev(k_new), to_dev(v_new)
+    n_splits = position // block + 2
+    results = []
+    for lib in (ref, backend.lib):
+        ckd, cvd = cache_to_dev(ck), cache_to_dev(cv)
+        pa, pm, pl = partial_buffers(24, n_splits, 256)
+        out = torch.zeros((24, 256), dtype=torch.bfloat16, device="cuda")
+        spec = abi.AttentionDecodeSpec(0, position, dp(qd), dp(kd), dp(vd), dp(ckd), dp(cvd), dp(None), dp(out),
+                                       abi.AttentionShape(24, 4, 256, 0), dtype, dp(None), dp(pa), dp(pm), dp(pl),
+                                       n_splits, block)
+        torch.cuda.synchronize()
+        assert lib.qwen36_attention_decode_split_tiled(C.byref(spec), n_splits, block) == 0
+        torch.cuda.synchronize()
+        results.append((pa.cpu().numpy(), pm.cpu().numpy(), pl.cpu().numpy(), cache_host(ckd), cache_host(cvd)))
+    (pa_r, pm_r, pl_r, ck_r, cv_r), (pa_m, pm_m, pl_m, ck_m, cv_m) = results
+    assert np.array_equal(ck_r, ck_m) and np.array_equal(cv_r, cv_m)
+    assert np.array_equal(np.isneginf(pm_r), np.isneginf(pm_m))
+    live = ~np.isneginf(pm_r)
+    assert np.allclose(pm_m[live], pm_r[live], rtol=0, atol=2e-3)
+    assert np.allclose(pl_m[live], pl_r[live], rtol=1e-2)
+    assert np.linalg.norm(pa_m - pa_r) / np.linalg.norm(pa_r) <= 1e-2
+
+
 @pytest.mark.parametrize("m_out,k,tokens", [(1024, 5120, 1), (1024, 5120, 5), (2048, 5120, 128), (1024, 17408, 512),
                                             (4096, 5120, 2048)])
 def test_nvfp4_gemm_equals_reference_cublaslt(ref, backend, m_out, k, tokens):
