@@ -358,7 +358,7 @@ def other_configs(backend, torch, synth):
     gemm = []
     for name, n_out, k in (("mlp.gate_up", 34816, 5120), ("mlp.down", 5120, 17408)):
         ws = []
-        for _ in range(2):
+        for _ in range(3):                     # 3 x 50 MB (down) / 3 x 100 MB (gate_up): more than L2 in rotation
             packed, sf_rm = synth.nvfp4_weight_device(gen, n_out, k, "cuda")
             ws.append((packed, backend.nvfp4_retile_scales(sf_rm)))
         for m_tok in (512, 2048, 8192):
@@ -369,12 +369,12 @@ def other_configs(backend, torch, synth):
             fp4 = torch.empty((m_tok, k // 2), dtype=torch.uint8, device="cuda")
             sf = torch.zeros(backend_tiled_bytes(m_tok, k // 16), dtype=torch.uint8, device="cuda")
             ts = torch.empty(1, dtype=torch.float32, device="cuda")
-            q_us = _time_cuda(torch, lambda i: backend.nvfp4_quantize_rows(x, 0.37, fp4, sf, ts), 10, backend=backend)
+            q_us = _time_cuda(torch, lambda i: backend.nvfp4_quantize_rows(x, 0.37, fp4, sf, ts), 200, warm=20,
+                              backend=backend)
             alpha = synth.WEIGHT_GLOBAL_SCALE * 0.37
             c = torch.empty((m_tok, n_out), dtype=torch.bfloat16, device="cuda")
-            reps = 10 if m_tok >= 8192 else 20
-            g_us = _time_cuda(torch, lambda i: backend.nvfp4_gemm(ws[i & 1][0], ws[i & 1][1], fp4, sf, alpha,
-                                                                   n_out, m_tok, k, c), reps, backend=backend)
+            g_us = _time_cuda(torch, lambda i: backend.nvfp4_gemm(ws[i % 3][0], ws[i % 3][1], fp4, sf, alpha,
+                                                                   n_out, m_tok, k, c), 200, warm=20, backend=backend)
             flops = 2.0 * m_tok * n_out * k
             gemm.append({"shape": name, "M": m_tok, "N": n_out, "K": k, "gemm_us": round(g_us, 2),
                          "tflops": round(flops / g_us / 1e6, 1),
@@ -393,9 +393,10 @@ def other_configs(backend, torch, synth):
     up = torch.randn(inter, generator=gen, device="cuda").to(torch.bfloat16)
     sw = backend.swiglu_nvfp4_quantize(gt, up, 0.37)
     nb = backend.rmsnorm_nvfp4_quantize(xn, wn, rn, 1e-6, 0.37, True, True)
-    norm_us = _time_cuda(torch, lambda i: backend.rmsnorm_nvfp4_quantize(xn, wn, rn, 1e-6, 0.37, True, True, nb), 50,
-                         backend=backend)
-    swiglu_us = _time_cuda(torch, lambda i: backend.swiglu_nvfp4_quantize(gt, up, 0.37, *sw), 50, backend=backend)
+    norm_us = _time_cuda(torch, lambda i: backend.rmsnorm_nvfp4_quantize(xn, wn, rn, 1e-6, 0.37, True, True, nb), 200,
+                         warm=20, backend=backend)
+    swiglu_us = _time_cuda(torch, lambda i: backend.swiglu_nvfp4_quantize(gt, up, 0.37, *sw), 200, warm=20,
+                           backend=backend)
     out["fused_producers"] = {"rmsnorm_nvfp4_quantize_us": round(norm_us, 2), "hidden": hid,
                               "swiglu_nvfp4_quantize_us": round(swiglu_us, 2), "intermediate": inter}
     # ---- config 3: FP8 lm_head + greedy argmax ---------------------------------------------
@@ -411,9 +412,10 @@ def other_configs(backend, torch, synth):
         tok = torch.empty(m_tok, dtype=torch.int32, device="cuda")
         best = torch.empty(m_tok, dtype=torch.float32, device="cuda")
         byts = rows * cols + 4 * rows + 2 * m_tok * cols + 8 * m_tok
-        us_gemv = _time_cuda(torch, lambda i: backend.lm_head_fp8_gemv(w, sc, xh, logits), 10, backend=backend)
-        us_samp = _time_cuda(torch, lambda i: backend.sample_rows(logits), 10, backend=backend)
-        us_fused = _time_cuda(torch, lambda i: backend.lm_head_fp8_gemv_argmax(w, sc, xh, wsb, 0, tok, best), 10, backend=backend)
+        us_gemv = _time_cuda(torch, lambda i: backend.lm_head_fp8_gemv(w, sc, xh, logits), 200, warm=20, backend=backend)
+        us_samp = _time_cuda(torch, lambda i: backend.sample_rows(logits), 200, warm=20, backend=backend)
+        us_fused = _time_cuda(torch, lambda i: backend.lm_head_fp8_gemv_argmax(w, sc, xh, wsb, 0, tok, best), 200,
+                              warm=20, backend=backend)
         lm.append({"M": m_tok, "gemv_us": round(us_gemv, 1), "sample_rows_us": round(us_samp, 1),
                    "fused_us": round(us_fused, 1), "fused_gbs": round(byts / us_fused / 1e3, 1),
                    "gemv_gbs": round(byts / us_gemv / 1e3, 1)})
@@ -422,19 +424,19 @@ def other_configs(backend, torch, synth):
     # ---- exact-argmax guards: margin verdict over the logits, predicated bf16 lm_head ---------
     guard = {}
     logits4 = (torch.randn((4, rows), generator=gen, device="cuda") * 3).to(torch.bfloat16)
-    guard["top2_margin_rows4_us"] = round(_time_cuda(torch, lambda i: backend.lm_head_top2_margin(logits4, 0.5), 20,
-                                                     backend=backend), 2)
+    guard["top2_margin_rows4_us"] = round(_time_cuda(torch, lambda i: backend.lm_head_top2_margin(logits4, 0.5), 200,
+                                                     warm=20, backend=backend), 2)
     wb = torch.randn((rows, cols), generator=gen, device="cuda").to(torch.bfloat16)       # 2.5 GB bf16 lm_head
     for m_tok in (1, 4):
         xh = torch.randn((m_tok, cols), generator=gen, device="cuda").to(torch.bfloat16)
         tk = torch.zeros(m_tok, dtype=torch.int32, device="cuda")
-        us = _time_cuda(torch, lambda i: backend.bf16_matvec_argmax_rows(xh, wb, tk), 5, backend=backend)
+        us = _time_cuda(torch, lambda i: backend.bf16_matvec_argmax_rows(xh, wb, tk), 100, warm=20, backend=backend)
         guard[f"bf16_matvec_argmax_rows{m_tok}_us"] = round(us, 1)
         guard[f"bf16_matvec_argmax_rows{m_tok}_gbs"] = round(rows * cols * 2 / us / 1e3, 1)
     lg = logits4[:1].contiguous()
     x1 = torch.randn((1, cols), generator=gen, device="cuda").to(torch.bfloat16)
-    guard["top8_rescore_rows1_us"] = round(_time_cuda(torch, lambda i: backend.lm_head_top8_rescore(lg, wb, x1, 0.5), 20,
-                                                      backend=backend), 2)
+    guard["top8_rescore_rows1_us"] = round(_time_cuda(torch, lambda i: backend.lm_head_top8_rescore(lg, wb, x1, 0.5), 200,
+                                                      warm=20, backend=backend), 2)
     out["lm_head_guards"] = guard
     del wb, logits4
     # ---- config 4: int8 KV + decode attention ----------------------------------------------
@@ -446,14 +448,26 @@ def other_configs(backend, torch, synth):
     kq = torch.empty((T, 4, 256), dtype=torch.int8, device="cuda")
     vq = torch.empty_like(kq)
     meta = torch.empty((T, 4, 2), dtype=torch.float32, device="cuda")
-    enc_us = _time_cuda(torch, lambda i: backend.turboquant_encode_kv_rows(k_, v_, kq, vq, meta, 0), 5, backend=backend)
+    enc_us = _time_cuda(torch, lambda i: backend.turboquant_encode_kv_rows(k_, v_, kq, vq, meta, 0), 100, warm=20,
+                        backend=backend)
     enc_bytes = T * (2 * 4 * 256 * 2 + 2 * 4 * 256 + 32)
     wsa = backend.attention_workspace(24, 256, "cuda")
     o_ = torch.empty((24, 256), dtype=torch.bfloat16, device="cuda")
+    # a second 131072-row cache so that ctx 131072 alternates between two caches (2 x 273 MB) and the
+    # shorter contexts rotate over 32 / 8 disjoint slices: every launch reads rows that are not in L2
+    kq2, vq2, meta2 = kq.flip(0).contiguous(), vq.flip(0).contiguous(), meta.flip(0).contiguous()
+    caches = ((kq, vq, meta), (kq2, vq2, meta2))
     for ctx in (8192, 32768, 131072):
-        us = _time_cuda(torch, lambda i: backend.turboquant_attention(q_, kq, vq, meta, ctx - 1, wsa, o_), 20, backend=backend)
+        nsl = T // ctx
+
+        def call(i, ctx=ctx, nsl=nsl):
+            ck, cv, cm = caches[(i // nsl) & 1]
+            s0 = (i % nsl) * ctx
+            backend.turboquant_attention(q_, ck[s0:s0 + ctx], cv[s0:s0 + ctx], cm[s0:s0 + ctx], ctx - 1, wsa, o_)
+        us = _time_cuda(torch, call, 200, warm=20, backend=backend)
         byts = ctx * (2 * 4 * 256 + 4 * 2 * 4) + 24 * 256 * 4
         att.append({"ctx": ctx, "us": round(us, 2), "gbs": round(byts / us / 1e3, 1)})
+    del kq2, vq2, meta2, caches
     out["int8_kv_attention"] = att
     # ---- the same decode step over the FP8 (E4M3) and BF16 caches of qwen36_attention_decode:
     # ctx - 1 cached rows + the new row, cache append included; small contexts rotate over
@@ -479,10 +493,28 @@ def other_configs(backend, torch, synth):
                 s0 = (i % nsl) * ctx
                 backend.attention_decode(q_, kn, kn, ck[s0:s0 + ctx], cv[s0:s0 + ctx], ctx - 1, code, parts, 256,
                                          out=o_)
-            us = _time_cuda(torch, call, 32, backend=backend)
+            us = _time_cuda(torch, call, 200, warm=20, backend=backend)
             byts = (ctx - 1) * 2 * 4 * 256 * width + 2 * 24 * 256 * 2 + 4 * 4 * 256 * 2
             rows_.append({"ctx": ctx, "us": round(us, 2), "gbs": round(byts / us / 1e3, 1)})
         dec[name] = rows_
+        # speculative verify: 4 / 16 query tokens over the same caches (qwen36_attention_flash_splitk_prefill_bf16)
+        ver = []
+        for q_tok in (4, 16):
+            qv = torch.randn((q_tok, 24, 256), generator=gen, device="cuda").to(torch.bfloat16)
+            ov = torch.empty((q_tok, 24, 256), dtype=torch.bfloat16, device="cuda")
+            ns = 74
+            pv = (torch.empty((q_tok, 24, ns, 256), device="cuda"), torch.empty((q_tok, 24, ns), device="cuda"),
+                  torch.empty((q_tok, 24, ns), device="cuda"))
+            for ctx in (32768, 131072):
+                nsl = max(1, (T - 64) // ctx)
+
+                def vcall(i, ctx=ctx, nsl=nsl):
+                    s0 = (i % nsl) * ctx
+                    backend.attention_flash_splitk_prefill(qv, ck[s0:], cv[s0:], ctx - q_tok, code, ns, pv, out=ov)
+                us = _time_cuda(torch, vcall, 50, warm=10, backend=backend)
+                ver.append({"q_tokens": q_tok, "ctx": ctx, "n_splits": ns, "us": round(us, 1),
+                            "gbs": round(ctx * 2 * 4 * 256 * width / us / 1e3, 1)})
+        dec[name + "_verify"] = ver
         del ck, cv
     out["kv_decode_attention"] = dec
     out["int8_kv_encode"] = {"tokens": T, "us": round(enc_us, 1), "gbs": round(enc_bytes / enc_us / 1e3, 1)}
@@ -587,6 +619,7 @@ def cpu_baseline(seconds: float = 10.0):
     import numpy as np
     from oracle import oracle as orc
     from speedoza_b200 import synth
+    orc.set_num_threads(os.cpu_count() or 1)       # all host cores, whatever OMP_NUM_THREADS says
     rng = np.random.default_rng(0)
     n = k = 5120
     packed, sf_rm = synth.nvfp4_weight(rng, n, k)
@@ -721,9 +754,7 @@ def run_ours(args):
         run_step = None
         del runner, sweep
         torch.cuda.empty_cache()
-        extra["sharded"] = [measure_sharded(w, 0, 10, 3, backend, torch, dist, world, rank, combine=c)
-                            for w, c in (("lm_head", "peer"), ("lm_head", "collective"), ("attention", "peer"),
-                                         ("attention", "collective"), ("prefill", "none"))]
+        extra["sharded"] = sharded_suite(backend, torch, dist, world, rank, layers)
     if rank == 0:
         peak, peak_kind = measured_peaks()
         ms_per_step = ms / args.steps
@@ -786,95 +817,31 @@ def peer_combine_usable(make, torch, dist, world):
         return make("collective"), "all-gather (NCCL)"
 
 
-def measure_sharded(workload, tokens, steps, warmup, b, torch, dist, world, rank, combine="peer"):
-    """One sharded configuration at `world` GPUs (strong scaling: the total work is fixed, each rank
-    holds 1/world of the vocab rows, of the KV range, or of the weight rows).  Returns a dict."""
-    from speedoza_b200 import shard, synth
-    how = None
-    gen = torch.Generator(device="cuda").manual_seed(4321)
-    if workload == "lm_head":
-        m_tok = tokens or 4
-        rows, cols = synth.VOCAB, synth.HIDDEN
-        lo, hi = shard.shard_rows(rows, rank, world)
-        gen.manual_seed(100 + rank)
-        w = torch.randint(0, 0x7F, (hi - lo, cols), generator=gen, dtype=torch.uint8, device="cuda")
-        sc = torch.exp2(torch.rand(hi - lo, generator=gen, device="cuda") * 4 - 6)
-        gen.manual_seed(7)
-        x = torch.randn((m_tok, cols), generator=gen, device="cuda").to(torch.bfloat16)
-        make = lambda c: shard.ShardedLmHead(b, rows, w, sc, lo, world, m_tok, combine=c)
-        head, how = peer_combine_usable(make, torch, dist, world) if (combine == "peer" and world > 1) else \
-            (make("collective"), "all-gather (NCCL)" if world > 1 else None)
-        if how is not None and how.startswith("NVLink"):
-            want = make("collective").argmax(x).to(torch.int64)      # the two combines must agree
-            got = head.argmax(x).to(torch.int64)
-            assert torch.equal(want, got), "peer argmax combine differs from the collective one"
-        step = lambda: head.argmax(x)
-        work, unit = rows * cols + 4 * rows + 2 * m_tok * cols + 8 * m_tok, "GB/s"
-        name = (f"config 3: FP8 lm_head 248320x5120 + fused greedy argmax, M={m_tok}, vocab split {world}-way "
-                "+ combine of (value, index)")
-        dtype = "e4m3 x bf16 -> f32"
-    elif workload == "attention":
-        ctx = tokens or 131072
-        lo, hi = shard.shard_tokens(ctx, rank, world)
-        gen.manual_seed(200 + rank)
-        k_ = torch.randn((hi - lo, 4, 256), generator=gen, device="cuda").to(torch.bfloat16)
-        v_ = torch.randn((hi - lo, 4, 256), generator=gen, device="cuda").to(torch.bfloat16)
-        kq = torch.empty((hi - lo, 4, 256), dtype=torch.int8, device="cuda")
-        vq = torch.empty_like(kq)
-        meta = torch.empty((hi - lo, 4, 2), dtype=torch.float32, device="cuda")
-        b.turboquant_encode_kv_rows(k_, v_, kq, vq, meta, 0)
-        del k_, v_
-        gen.manual_seed(7)
-        q_ = torch.randn((24, 256), generator=gen, device="cuda").to(torch.bfloat16)
-        make = lambda c: shard.ShardedKvAttention(b, kq, vq, meta, lo, world, 24, 256, combine=c)
-        att, how = peer_combine_usable(make, torch, dist, world) if (combine == "peer" and world > 1) else \
-            (make("collective"), "all-gather (NCCL)" if world > 1 else None)
-        if how is not None and how.startswith("NVLink"):
-            want = make("collective").attend(q_, ctx - 1).float()    # same arithmetic, same order: same bits
-            got = att.attend(q_, ctx - 1).float()
-            assert torch.equal(want, got), "peer attention merge differs from the collective one"
-        step = lambda: att.attend(q_, ctx - 1)
-        work, unit = ctx * (2 * 4 * 256 + 32) + 24 * 256 * 4, "GB/s"
-        name = (f"config 4: int8 KV decode attention, ctx {ctx}, 24 q / 4 kv heads, KV range split {world}-way "
-                "+ merge of (m, l, o)")
-        dtype = "int8 x bf16 -> f32"
-    else:
-        m_tok = tokens or 8192
-        n_out, k = 34816, 5120
-        lo, hi = shard.shard_rows(n_out, rank, world)
-        gen.manual_seed(300 + rank)
-        packed, sf_rm = synth.nvfp4_weight_device(gen, hi - lo, k, "cuda")
-        a_sf = b.nvfp4_retile_scales(sf_rm)
-        gen.manual_seed(7)
-        x = torch.randn((m_tok, k), generator=gen, device="cuda").to(torch.bfloat16)
-        fp4 = torch.empty((m_tok, k // 2), dtype=torch.uint8, device="cuda")
-        sfb = torch.zeros(backend_tiled_bytes(m_tok, k // 16), dtype=torch.uint8, device="cuda")
-        ts = torch.empty(1, dtype=torch.float32, device="cuda")
-        c = torch.empty((m_tok, hi - lo), dtype=torch.bfloat16, device="cuda")
+def _rotation(shard_bytes: int, cap: int = 64) -> int:
+    """How many disjoint copies / slices of a per-rank shard a step sequence rotates over so that
+    every launch reads rows that have left L2 (126 MB): >= 300 MB in rotation."""
+    return max(1, min(cap, -(-300_000_000 // max(1, shard_bytes))))
 
-        def step():
-            b.nvfp4_quantize_rows(x, 0.37, fp4, sfb, ts)          # replicated on every rank
-            return b.nvfp4_gemm(packed, a_sf, fp4, sfb, 0.37 / 2688.0, hi - lo, m_tok, k, c)
-        work, unit = 2.0 * m_tok * n_out * k, "TFLOP/s"
-        name = (f"config 2: NVFP4 prefill (quantise + tcgen05 GEMM) gate_up 34816x5120, M={m_tok}, weight rows "
-                f"split {world}-way, output kept sharded")
-        dtype = "nvfp4 x nvfp4 -> f32"
 
+def _time_sequence(steps_fns, steps, warmup, b, torch, dist, world):
+    """Times a sequence of step callables (one per cold slice).  The whole sequence is recorded into
+    ONE CUDA graph (kernels + combine, the way a serving engine replays its step) and replayed until
+    at least `steps` steps have run; every rank takes the same route.  Returns (ms per step, route)."""
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
-    for _ in range(max(3, warmup)):
-        step()
+    seq = len(steps_fns)
+    for i in range(max(3, warmup)):
+        steps_fns[i % seq]()
     barrier()
-    # One step (kernels + the combine collective) recorded into a CUDA graph, as a serving engine
-    # replays it; every rank must take the same route, so a failed capture anywhere means eager everywhere.
     graph = None
     try:
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, capture_error_mode="thread_local" if world > 1 else "global"):
             b.sync_stream()
-            step()
+            for fn in steps_fns:
+                fn()
         b.sync_stream()
     except Exception:
         graph = None
@@ -884,13 +851,20 @@ def measure_sharded(workload, tokens, steps, warmup, b, torch, dist, world, rank
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
         if int(flag[0]) == 0:
             graph = None
-    run = graph.replay if graph is not None else step
-    for _ in range(3):
+
+    def run():
+        if graph is not None:
+            graph.replay()
+        else:
+            for fn in steps_fns:
+                fn()
+    reps = max(1, -(-steps // seq))
+    for _ in range(2):
         run()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(steps):
+    for _ in range(reps):
         run()
     e1.record()
     barrier()
@@ -899,12 +873,144 @@ def measure_sharded(workload, tokens, steps, warmup, b, torch, dist, world, rank
         t = torch.tensor([ms], dtype=torch.float64, device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t[0])
-    per = ms / steps
+    route = "CUDA graph replay" if graph is not None else "eager"
+    del graph
+    return ms / (reps * seq), route
+
+
+def measure_sharded(workload, tokens, steps, warmup, b, torch, dist, world, rank, combine="peer", shape="gate_up",
+                    gather=False, quantise="replicated"):
+    """One sharded configuration at `world` GPUs (strong scaling: the total work is fixed, each rank
+    holds 1/world of the vocab rows, of the KV range, or of the weight rows).  Every step of the
+    timed sequence reads a different copy / slice of the rank's shard, so the figures are cold-HBM
+    ones at every N.  Returns a dict."""
+    from speedoza_b200 import shard, synth
+    how = None
+    closers = []
+    gen = torch.Generator(device="cuda").manual_seed(4321)
+    if workload == "lm_head":
+        m_tok = tokens or 4
+        rows, cols = synth.VOCAB, synth.HIDDEN
+        lo, hi = shard.shard_rows(rows, rank, world)
+        copies = min(4, _rotation((hi - lo) * cols))
+        gen.manual_seed(100 + rank)
+        w = torch.randint(0, 0x7F, (hi - lo, cols), generator=gen, dtype=torch.uint8, device="cuda")
+        sc = torch.exp2(torch.rand(hi - lo, generator=gen, device="cuda") * 4 - 6)
+        ws_ = [w] + [w.roll(17 * (c + 1), 0) for c in range(copies - 1)]
+        scs = [sc] + [sc.roll(17 * (c + 1), 0) for c in range(copies - 1)]
+        gen.manual_seed(7)
+        x = torch.randn((m_tok, cols), generator=gen, device="cuda").to(torch.bfloat16)
+        make = lambda c, i=0: shard.ShardedLmHead(b, rows, ws_[i], scs[i], lo, world, m_tok, combine=c)
+        head, how = peer_combine_usable(make, torch, dist, world) if (combine == "peer" and world > 1) else \
+            (make("collective"), "all-gather (NCCL)" if world > 1 else None)
+        if how is not None and how.startswith("NVLink"):
+            want = make("collective").argmax(x).to(torch.int64)      # the two combines must agree
+            got = head.argmax(x).to(torch.int64)
+            assert torch.equal(want, got), "peer argmax combine differs from the collective one"
+
+        def lm_step(i):
+            def fn():
+                head.w, head.s = ws_[i], scs[i]
+                return head.argmax(x)
+            return fn
+        fns = [lm_step(i) for i in range(copies)]
+        closers.append(head)
+        work, unit = rows * cols + 4 * rows + 2 * m_tok * cols + 8 * m_tok, "GB/s"
+        name = (f"config 3: FP8 lm_head 248320x5120 + fused greedy argmax, M={m_tok}, vocab split {world}-way "
+                f"+ combine of (value, index); {copies} weight copies in rotation")
+        dtype = "e4m3 x bf16 -> f32"
+    elif workload == "attention":
+        ctx = tokens or 131072
+        lo, hi = shard.shard_tokens(ctx, rank, world)
+        n_loc = hi - lo
+        slices = _rotation(n_loc * 2080)
+        gen.manual_seed(200 + rank)
+        pool = n_loc * slices
+        kq = torch.empty((pool, 4, 256), dtype=torch.int8, device="cuda")
+        vq = torch.empty_like(kq)
+        meta = torch.empty((pool, 4, 2), dtype=torch.float32, device="cuda")
+        for s0 in range(0, pool, 32768):                          # encode in pieces: small bf16 temporaries
+            n = min(32768, pool - s0)
+            k_ = torch.randn((n, 4, 256), generator=gen, device="cuda").to(torch.bfloat16)
+            v_ = torch.randn((n, 4, 256), generator=gen, device="cuda").to(torch.bfloat16)
+            b.turboquant_encode_kv_rows(k_, v_, kq[s0:s0 + n], vq[s0:s0 + n], meta[s0:s0 + n], 0)
+        del k_, v_
+        gen.manual_seed(7)
+        q_ = torch.randn((24, 256), generator=gen, device="cuda").to(torch.bfloat16)
+        make = lambda c: shard.ShardedKvAttention(b, kq[:n_loc], vq[:n_loc], meta[:n_loc], lo, world, 24, 256, combine=c)
+        att, how = peer_combine_usable(make, torch, dist, world) if (combine == "peer" and world > 1) else \
+            (make("collective"), "all-gather (NCCL)" if world > 1 else None)
+        if how is not None and how.startswith("NVLink"):
+            want = make("collective").attend(q_, ctx - 1).float()    # same arithmetic, same order: same bits
+            got = att.attend(q_, ctx - 1).float()
+            assert torch.equal(want, got), "peer attention merge differs from the collective one"
+
+        def att_step(i):
+            def fn():
+                s0 = i * n_loc
+                att.kq, att.vq, att.meta = kq[s0:s0 + n_loc], vq[s0:s0 + n_loc], meta[s0:s0 + n_loc]
+                return att.attend(q_, ctx - 1)
+            return fn
+        fns = [att_step(i) for i in range(slices)]
+        closers.append(att)
+        work, unit = ctx * (2 * 4 * 256 + 32) + 24 * 256 * 4, "GB/s"
+        name = (f"config 4: int8 KV decode attention, ctx {ctx}, 24 q / 4 kv heads, KV range split {world}-way "
+                f"+ merge of (m, l, o); {slices} cache slices in rotation")
+        dtype = "int8 x bf16 -> f32"
+    else:
+        m_tok = tokens or 8192
+        n_out, k = (34816, 5120) if shape == "gate_up" else (5120, 17408)
+        lo, hi = shard.shard_rows(n_out, rank, world)
+        n_loc = hi - lo
+        copies = min(32, _rotation(n_loc * k // 2))
+        gen.manual_seed(300 + rank)
+        packed, sf_rm = synth.nvfp4_weight_device(gen, n_loc, k, "cuda")
+        a_sf = b.nvfp4_retile_scales(sf_rm)
+        wts = [(packed, a_sf)] + [(packed.roll(c + 1, 0), a_sf.roll(512 * (c + 1), 0)) for c in range(copies - 1)]
+        gen.manual_seed(7)
+        x = torch.randn((m_tok, k), generator=gen, device="cuda").to(torch.bfloat16)
+        fp4 = torch.empty((m_tok, k // 2), dtype=torch.uint8, device="cuda")
+        sfb = torch.zeros(backend_tiled_bytes(m_tok, k // 16), dtype=torch.uint8, device="cuda")
+        ts = torch.empty(1, dtype=torch.float32, device="cuda")
+        c = torch.empty((m_tok, n_loc), dtype=torch.bfloat16, device="cuda")
+        even = world > 1 and n_loc * world == n_out
+        gather = gather and even
+        full = torch.empty((world, m_tok, n_loc), dtype=torch.bfloat16, device="cuda") if gather else None
+        # activation quantisation: every rank quantises all M rows ("replicated", no exchange), or each
+        # rank quantises M / world rows and the codes + scale tiles are all-gathered ("sharded")
+        rows_loc = m_tok // world
+        split_q = quantise == "sharded" and world > 1 and rows_loc % 128 == 0
+        if split_q:
+            r0 = rank * rows_loc
+            sf_rows = backend_tiled_bytes(rows_loc, k // 16)
+            fp4_loc, sf_loc = fp4[r0:r0 + rows_loc], sfb[rank * sf_rows:(rank + 1) * sf_rows]
+
+        def pre_step(i):
+            def fn():
+                if split_q:
+                    b.nvfp4_quantize_rows(x[r0:r0 + rows_loc], 0.37, fp4_loc, sf_loc, ts)
+                    dist.all_gather_into_tensor(fp4.view(-1), fp4_loc.reshape(-1))
+                    dist.all_gather_into_tensor(sfb, sf_loc)
+                else:
+                    b.nvfp4_quantize_rows(x, 0.37, fp4, sfb, ts)
+                b.nvfp4_gemm(wts[i][0], wts[i][1], fp4, sfb, 0.37 / 2688.0, n_loc, m_tok, k, c)
+                if gather:
+                    dist.all_gather_into_tensor(full, c)
+                return c
+            return fn
+        fns = [pre_step(i) for i in range(copies)]
+        work, unit = 2.0 * m_tok * n_out * k, "TFLOP/s"
+        name = (f"config 2: NVFP4 prefill (quantise + tcgen05 GEMM) {shape} {n_out}x{k}, M={m_tok}, weight rows "
+                f"split {world}-way, activation quantise {'sharded + all-gather of codes' if split_q else 'replicated'}, "
+                f"output {'all-gathered (bf16, [rank, M, rows] layout)' if gather else 'kept sharded'}; "
+                f"{copies} weight copies in rotation")
+        dtype = "nvfp4 x nvfp4 -> f32"
+
+    per, launch = _time_sequence(fns, steps, warmup, b, torch, dist, world)
     value = work / (per * 1e-3) / (1e9 if unit == "GB/s" else 1e12)
-    launch = "CUDA graph replay" if graph is not None else "eager"
-    del graph, run
-    for op in (locals().get("head"), locals().get("att")):
-        if op is not None and getattr(op, "peer", None) is not None:
+    del fns
+    for op in closers:
+        if getattr(op, "peer", None) is not None:
             op.peer.ex.close()                   # unmaps the peers' inboxes (collective: every rank gets here)
     out = {"workload": name, "value": round(value, 1), "unit": unit, "ms_per_step": round(per, 4), "dtype": dtype,
            "launch": launch}
@@ -912,6 +1018,103 @@ def measure_sharded(workload, tokens, steps, warmup, b, torch, dist, world, rank
         out["combine"] = how
         if int(b.lib.qwen36_peer_last_error()) != 0:
             out["combine"] += "; a wait for a peer ran out"
+    return out
+
+
+class PeerSweepRunner:
+    """The sweep with every matrix's output rows split over the ranks and the slices exchanged by the
+    GEMV epilogue itself (qwen36_nvfp4_matvec_peer: stores into every rank's arena over NVLink, one
+    flag per rank, bounded wait in the consuming launch): 4 launches per layer, no collective."""
+
+    SLOT = {"qkv": 0, "o": 1, "gate_up": 2, "down": 3}
+
+    def __init__(self, backend, torch, sweep, world, rank):
+        from speedoza_b200 import synth
+        from speedoza_b200.peer import TensorParallelGemv
+        self.sweep, self.world, self.rank = sweep, world, rank
+        vectors = {name: n for name, n, _ in synth.DECODE_SHAPES}
+        self.tp = TensorParallelGemv(backend, vectors, 4, "cuda")
+        self.y = torch.empty(5120, dtype=torch.bfloat16, device="cuda")
+
+    def _mat(self, m):
+        name, n_local, k, packed, sf, ts, n_full = m
+        return (packed, sf, ts, name, shard_rows(n_full, self.rank, self.world)[0])
+
+    def step(self, x0):
+        tp, x, src = self.tp, x0, None
+        for mats in self.sweep:
+            tp.gemv(x, [self._mat(m) for m in mats[:3]], out_slot=0, in_slot=src)
+            tp.gemv((mats[0][0], 6144), [self._mat(mats[3])], out_slot=1, in_slot=0)
+            tp.gemv((mats[3][0], 5120), [self._mat(mats[4])], out_slot=2, in_slot=1)
+            tp.gemv((mats[4][0], 17408), [self._mat(mats[5])], out_slot=3, in_slot=2)
+            x, src = (mats[5][0], 5120), 3
+        return tp.collect(self.sweep[-1][5][0], 3, self.y)
+
+    def close(self):
+        self.tp.close()
+
+
+def measure_sweep_split(b, torch, dist, world, rank, layers, steps, warmup):
+    """The whole decode sweep with every GEMV's output rows split `world`-way (strong scaling), two
+    ways: NCCL all-gather after every GEMV, and the peer-store epilogue.  Both must give the bits of
+    each other.  Returns two dicts."""
+    from speedoza_b200 import synth
+    from speedoza_b200.abi import KernelError
+    sweep = build_sweep(b, torch, synth, rank, world, layers, seed=1234)
+    step_bytes = layers * sum(gemv_bytes(n, k) for _, n, k in synth.DECODE_SHAPES)
+    gen = torch.Generator(device="cuda").manual_seed(99)
+    x = torch.randn(5120, generator=gen, device="cuda").to(torch.bfloat16)
+    out = []
+    nccl = SweepRunner(b, torch, sweep, world, dist)
+    y_nccl = nccl.step(x).clone()
+    per, launch = _time_sequence([lambda: nccl.step(x)], steps, warmup, b, torch, dist, world)
+    out.append({"workload": f"config 1: decode sweep, {layers} layers x 6 shapes, output rows split {world}-way, "
+                            "NCCL all-gather after every GEMV (6 launches + 6 collectives per layer)",
+                "value": round(step_bytes / (per * 1e-3) / 1e9, 1), "unit": "GB/s", "ms_per_step": round(per, 4),
+                "dtype": "e2m1 x bf16 -> f32", "launch": launch, "combine": "all-gather (NCCL)"})
+    del nccl
+    try:
+        peer = PeerSweepRunner(b, torch, sweep, world, rank)
+    except KernelError:
+        peer = None
+    if peer is not None:
+        y_peer = peer.step(x).clone()
+        torch.cuda.synchronize()
+        same = bool(torch.equal(y_peer.view(torch.int16), y_nccl.view(torch.int16)))
+        per, launch = _time_sequence([lambda: peer.step(x)], steps, warmup, b, torch, dist, world)
+        failed = peer.tp.failed_call()
+        out.append({"workload": f"config 1: decode sweep, {layers} layers x 6 shapes, output rows split {world}-way, "
+                                "GEMV epilogue stores its rows into every rank's activation arena over NVLink "
+                                "(4 launches per layer, no collective)",
+                    "value": round(step_bytes / (per * 1e-3) / 1e9, 1), "unit": "GB/s", "ms_per_step": round(per, 4),
+                    "dtype": "e2m1 x bf16 -> f32", "launch": launch,
+                    "combine": "NVLink peer stores from the GEMV epilogue" + ("" if failed == 0 else "; a wait for a peer ran out"),
+                    "same_bits_as_all_gather": same})
+        peer.close()
+    else:
+        out.append({"workload": "config 1: decode sweep, peer-store epilogue", "unavailable": "CUDA IPC mapping refused"})
+    return out
+
+
+def sharded_suite(b, torch, dist, world, rank, layers):
+    """Every sharded path at this GPU count (strong scaling each), for the scaling record."""
+    out = measure_sweep_split(b, torch, dist, world, rank, layers, 10, 3)
+    torch.cuda.empty_cache()
+    ms = lambda *a, **k: out.append(measure_sharded(*a, b, torch, dist, world, rank, **k))
+    for m_tok in (1, 4):
+        for c in ("peer", "collective"):
+            ms("lm_head", m_tok, 200, 5, combine=c)
+            torch.cuda.empty_cache()
+    for ctx in (8192, 32768, 131072):
+        for c in ("peer", "collective"):
+            ms("attention", ctx, 200, 5, combine=c)
+            torch.cuda.empty_cache()
+    for shape in ("gate_up", "down"):
+        for m_tok in (512, 2048, 8192):
+            ms("prefill", m_tok, 50, 3, shape=shape)
+            ms("prefill", m_tok, 50, 3, shape=shape, gather=True)
+            torch.cuda.empty_cache()
+    ms("prefill", 8192, 50, 3, shape="down", quantise="sharded")
     return out
 
 
@@ -927,7 +1130,7 @@ def run_sharded_workload(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     b = CudaBackend()
     r = measure_sharded(args.workload, args.tokens, args.steps, args.warmup, b, torch, dist, world, rank,
-                        combine=args.combine)
+                        combine=args.combine, shape=args.shape, gather=args.gather, quantise=args.quantise)
     if rank == 0:
         print(json.dumps({"metric": METRIC, "value": r["value"], "unit": r["unit"], "n_gpus": world, "steps": args.steps,
                           "warmup": max(3, args.warmup), "ms_per_step": r["ms_per_step"], "higher_is_better": True,
@@ -953,6 +1156,8 @@ def run_reference(args):
     import numpy as np
     from oracle import oracle as orc
     from speedoza_b200 import synth
+    # torch.distributed.run exports OMP_NUM_THREADS=1 to its workers: the CPU arm uses every host core anyway
+    orc.set_num_threads(os.cpu_count() or 1)
     rng = np.random.default_rng(1234)
     mats = []
     for name, n, k in synth.DECODE_SHAPES:
@@ -1010,6 +1215,10 @@ def main():
     ap.add_argument("--combine", default="peer", choices=["peer", "collective"],
                     help="cross-rank combine of the sharded lm_head / attention: NVLink peer push or all-gather")
     ap.add_argument("--tokens", type=int, default=0, help="M (lm_head, prefill) or context length (attention)")
+    ap.add_argument("--shape", default="gate_up", choices=["gate_up", "down"], help="prefill workload: which MLP matrix")
+    ap.add_argument("--gather", action="store_true", help="prefill workload: all-gather the bf16 output as well")
+    ap.add_argument("--quantise", default="replicated", choices=["replicated", "sharded"],
+                    help="prefill workload: quantise all rows on every rank, or M / N rows + all-gather of the codes")
     ap.add_argument("--profile-case", default=None, help="run one small kernel case (for ncu) and exit")
     args = ap.parse_args()
     if args.profile_case:

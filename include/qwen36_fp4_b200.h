@@ -476,6 +476,51 @@ int qwen36_ipc_close_handle(qwen36_device_ptr_t ptr);
 int qwen36_peer_last_error(void);   /* sticky */
 int qwen36_peer_reset_error(void);
 
+/* Tensor-parallel W4A16 GEMV: the output rows of every matrix are split over
+ * the ranks in whole 128-row blocks (the blocking of the scale tiles,
+ * crates/runtime/src/gpu.rs:329-339 in the reference).  Each rank holds an
+ * ARENA (an inbox of the exchange above; the flag array is not used) with one
+ * full-length copy of every activation vector of the chain, kept as FLAGGED
+ * CELLS: 8 bytes per two values = {bf16 pair, uint32 number of the call that
+ * wrote them}, so a vector of n values takes 4 n bytes.
+ * qwen36_nvfp4_matvec_peer computes this rank's rows of 1..4 matrices that
+ * share their input (as qwen36_nvfp4_matvec_group does; output_bf16 of the
+ * specs is not used) and its epilogue stores them, as cells, at
+ * output_offset_bytes[i] + 4 * row_offset[i] of EVERY rank's arena.  A call
+ * whose input is such a vector passes the address of the cells as input_bf16
+ * and names the producing call's slot as `in_slot`: it then reads a cell only
+ * once the cell carries that call's number (bounded wait), while its weights
+ * stream.  QWEN36_PEER_INPUT_LOCAL = input_bf16 is a plain local bf16 vector.
+ * state: slots x 4 uint32, local, zero-filled once ({calls completed, CTA
+ * ticket, number of the first failed call, unused} per slot); the arenas
+ * start zero-filled too.  All ranks make the same sequence of calls.  A
+ * vector may be overwritten by a later call once it has been consumed on
+ * every rank, which a dependent chain (each call consuming the previous
+ * call's vector) guarantees.  A wait that runs out gives NaN rows that
+ * propagate down the chain, the call number in state[4 * slot + 2] and
+ * qwen36_nvfp4_gemv_mma_last_error() == 2.  NOT_IMPLEMENTED unless
+ * out_features % 128 == 0 and in_features % 256 == 0, in_features <= 32768.
+ * qwen36_nvfp4_matvec_peer_collect unpacks n values (a multiple of 4) of a
+ * flagged vector of this rank's arena into plain bf16, waiting the same way:
+ * for a consumer that is not one of these calls. */
+#define QWEN36_PEER_INPUT_LOCAL ((size_t)-1)
+typedef struct {
+  size_t world, rank;                 /* world <= 8 */
+  qwen36_device_ptr_t peer_arena;     /* device array: world x (uint8_t *)  */
+  qwen36_device_ptr_t state;          /* local, slots x 4 uint32            */
+  size_t slots, out_slot, in_slot;
+  size_t output_offset_bytes[4];      /* multiples of 16                    */
+  size_t row_offset[4];               /* multiples of 8                     */
+} qwen36_nvfp4_matvec_peer_spec_t;
+int qwen36_nvfp4_matvec_peer(const qwen36_nvfp4_matvec_spec_t *specs, size_t count,
+                             const qwen36_nvfp4_matvec_peer_spec_t *peer);
+int qwen36_nvfp4_matvec_peer_collect(const qwen36_nvfp4_matvec_peer_spec_t *peer, size_t slot,
+                                     qwen36_device_ptr_t cells, size_t n, qwen36_device_ptr_t output_bf16);
+/* 0 = no bounded wait of the tensor-core GEMV ever ran out in this process; 1 = a pipeline stage
+ * never arrived; 2 = a peer's cells never arrived.  Sticky; both calls synchronise. */
+int qwen36_nvfp4_gemv_mma_last_error(void);
+int qwen36_nvfp4_gemv_mma_reset_error(void);
+
 /* Cross-rank log-sum-exp merge of one (m, l, o) partial per q head and rank
  * (the arithmetic of qwen36_attention_merge_partials with n_parts = world, in
  * rank order, so every rank gets the same bits).  The three inputs are the

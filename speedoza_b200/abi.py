@@ -45,6 +45,14 @@ class Nvfp4MatvecSpec(C.Structure):
                 ("tensor_scale_f32", DevicePtr), ("output_bf16", DevicePtr)]
 
 
+PEER_INPUT_LOCAL = (1 << (8 * C.sizeof(size_t))) - 1
+
+
+class Nvfp4MatvecPeerSpec(C.Structure):
+    _fields_ = [("world", size_t), ("rank", size_t), ("peer_arena", DevicePtr), ("state", DevicePtr), ("slots", size_t), ("out_slot", size_t), ("in_slot", size_t),
+                ("output_offset_bytes", size_t * 4), ("row_offset", size_t * 4)]
+
+
 class Nvfp4QuantizeSpec(C.Structure):
     _fields_ = [("values", size_t), ("input_bf16", DevicePtr), ("output_fp4", DevicePtr),
                 ("output_scale_e4m3", DevicePtr), ("output_tensor_scale_f32", DevicePtr),
@@ -300,6 +308,8 @@ def load() -> C.CDLL:
     lib.qwen36_nvfp4_gemm_force_split.restype = None
     lib.qwen36_nvfp4_gemm_force_split.argtypes = [C.c_int]
     lib.qwen36_nvfp4_matvec_group.argtypes = [C.POINTER(Nvfp4MatvecSpec), size_t]
+    lib.qwen36_nvfp4_matvec_peer.argtypes = [C.POINTER(Nvfp4MatvecSpec), size_t, C.POINTER(Nvfp4MatvecPeerSpec)]
+    lib.qwen36_nvfp4_matvec_peer_collect.argtypes = [C.POINTER(Nvfp4MatvecPeerSpec), size_t, DevicePtr, size_t, DevicePtr]
     lib.qwen36_nvfp4_matvec_force_quads.argtypes = [C.c_int]
     lib.qwen36_attention_flash_splitk_prefill_bf16.argtypes = [C.POINTER(AttentionPrefillSpec), C.c_int]
     lib.qwen36_attention_decode_split_tiled.argtypes = [C.POINTER(AttentionDecodeSpec), C.c_int, C.c_int]

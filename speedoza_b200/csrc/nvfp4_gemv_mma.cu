@@ -30,6 +30,18 @@
 //
 // Weights and scales stream before griddepcontrol.wait: under programmatic dependent launch the
 // ring fills while the kernel that produces x is still finishing.
+//
+// Tensor-parallel form (PEER = true; the output rows of a matrix are split over the GPUs of a node).
+// The epilogue stores the rank's rows straight into EVERY rank's copy of the full output vector
+// (stores over NVLink into an arena the peers have mapped).  The vector travels in flagged cells:
+// 8 bytes = two bf16 values + the 32-bit number of the call that wrote them, two cells per 16-byte
+// store.  An 8-byte aligned word arrives whole, so a consumer that reads a cell with the expected
+// call number has its data: no fence, no flag, no ticket on the path between the producer's last
+// FMA and the consumer's first MMA, which is what a chain of dependent few-microsecond launches
+// needs (a system-scope fence alone costs about 4 us here).  The launch that consumes the vector
+// polls (bounded) the cells of ITS columns while it stages them, with its weight ring already
+// full.  Call numbers live in device memory and are advanced by the kernel, so a CUDA graph can
+// hold the launches.  A wait that runs out poisons the rows (NaN) and records the call number.
 #include "nvfp4_gemv_mma.cuh"
 
 #include <atomic>
@@ -56,6 +68,10 @@ constexpr uint32_t kRingBytes = kStages * kStageBytes;
 constexpr uint32_t kHeaderBytes = 3072;             // barriers, slice scales, zero chunk, partial sums
 constexpr uint32_t kSpinLimit = 1u << 24;
 constexpr uint32_t kMaxK = 32768;
+constexpr uint32_t kMaxPeers = 8;                   // tensor-parallel form: ranks of one node
+constexpr uint32_t kNoSlot = 0xffffffffu;
+constexpr uint32_t kPeerSpinLimit = 1u << 21;       // x (200 ns back-off + one read of the cells): 1-2 s
+constexpr uint32_t kPeerEagerPolls = 2048;
 
 __device__ unsigned int g_gemv_mma_error = 0;       // set when a bounded wait gives up
 
@@ -85,6 +101,12 @@ struct GemvParams {
   const uint8_t *x_sf;                   // W4A4: tiled UE4M3 scales of the activation row
   uint32_t K, iters, units, count;
   float alpha;                           // W4A4
+  // tensor-parallel form only
+  uint8_t *const *peer_arena;            // device array [world]: base of every rank's arena (own one included)
+  uint32_t *state;                       // local [slots][4]: calls completed, CTA ticket, first failed call, -
+  uint32_t world, rank, out_slot, in_slot;
+  uint32_t row_off[kMaxMats];            // first row of this rank's slice in the full vector
+  uint64_t y_off[kMaxMats];              // byte offset of the full output vector (flagged cells) inside an arena
 #ifdef Q36_GEMV_TRACE
   uint32_t trace_id;
 #endif
@@ -167,6 +189,15 @@ __device__ __forceinline__ float2 ue4m3x2_to_f32(uint32_t two_bytes) {
   return __half22float2(*reinterpret_cast<const __half2 *>(&h));
 }
 
+__device__ __forceinline__ void st_cells(void *p, uint32_t d0, uint32_t d1, uint32_t call) {
+  asm volatile("st.relaxed.sys.global.v4.b32 [%0], {%1, %2, %3, %2};" ::"l"(p), "r"(d0), "r"(call), "r"(d1) : "memory");
+}
+__device__ __forceinline__ uint4 ld_cells(const void *p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
 // Position of 16-byte chunk `chunk` (0..15) inside a warp's 256-byte activation slot: the four
 // chunks that the four reading lanes fetch together (64 bytes apart) land on different banks.
 __device__ __forceinline__ uint32_t x_chunk_pos(uint32_t chunk) {
@@ -207,7 +238,7 @@ __device__ __noinline__ float exact_row(const GemvParams &p, uint32_t mat, uint3
 }
 
 // XKIND 0: x is a bf16 vector.  XKIND 1: x is one NVFP4-quantised activation row.
-template <int XKIND>
+template <int XKIND, bool PEER>
 __global__ void __launch_bounds__(kThreads + 32, 2)
 nvfp4_gemv_mma_kernel(const __grid_constant__ GemvParams p) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -217,6 +248,7 @@ nvfp4_gemv_mma_kernel(const __grid_constant__ GemvParams p) {
   uint64_t *empty = full + kStages;                                    // [kStages]
   float *slice_inv = reinterpret_cast<float *>(smem + 256);            // [kWarps] inverse scale of a warp's x slice
   uint4 *zero_chunk = reinterpret_cast<uint4 *>(smem + 320);           // 16 bytes of zeros
+  uint32_t *peer_fail = reinterpret_cast<uint32_t *>(smem + 336);      // [kWarps] 1 = this warp's wait for a peer ran out
   static_assert(2 * kStages * sizeof(uint64_t) <= 256, "barriers overlap the header fields");
   float *red = reinterpret_cast<float *>(smem + 1024);                 // [2][kWarps][32] partial row sums
   uint8_t *ring = smem + kHeaderBytes;
@@ -280,6 +312,13 @@ nvfp4_gemv_mma_kernel(const __grid_constant__ GemvParams p) {
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (threadIdx.x == 0) Q36_TRACE(3);
+  bool dead = false;
+  // Tensor-parallel form: x may be a flagged vector that the ranks are still delivering.  Its cells
+  // must carry the number of the call that produced it; this rank's own producer ran earlier in
+  // the stream, so its count of completed calls is that number.
+  const bool flagged = PEER && p.in_slot != kNoSlot;
+  uint32_t want = 0;
+  if (flagged) want = *reinterpret_cast<const volatile uint32_t *>(p.state + p.in_slot * 4u);
 
   // Each warp stages the activations of ITS columns (128 of every 1024) as float16, alone.
   uint8_t *xw = xs + warp * iters * 256u;
@@ -289,31 +328,93 @@ nvfp4_gemv_mma_kernel(const __grid_constant__ GemvParams p) {
     // below the float32 accumulation error); the inverse scale is applied to the warp's partial sum.
     constexpr uint32_t kPasses = kMaxK / 1024u / 2u;        // two stages' worth of chunks per pass
     const uint4 *xg = static_cast<const uint4 *>(p.x);
-    uint4 xr[kPasses];
-    uint32_t m2 = 0;
+    auto max_abs = [](uint32_t m2, const uint4 &v) {
+      return max_u16x2(m2, max_u16x2(max_u16x2(v.x & 0x7fff7fffu, v.y & 0x7fff7fffu), max_u16x2(v.z & 0x7fff7fffu, v.w & 0x7fff7fffu)));
+    };
+    auto scale_of = [&](uint32_t m2) {          // power of two that lifts the slice maximum to [2^14, 2^15)
+      const uint32_t mx = __reduce_max_sync(0xffffffffu, max(m2 & 0xffffu, m2 >> 16));
+      const uint32_t e = (mx >> 7) & 0xffu;
+      const int shift = e == 255u ? 0 : (e < 15u ? 126 : 141 - static_cast<int>(e));
+      if (lane == 0) slice_inv[warp] = __uint_as_float(static_cast<uint32_t>(127 - shift) << 23);
+      return __uint_as_float(static_cast<uint32_t>(127 + shift) << 23);
+    };
+    auto to_f16 = [](const uint4 &v, float up) {
+      const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+      __half2 h[4];
 #pragma unroll
-    for (uint32_t ps = 0; ps < kPasses; ++ps) {
-      const uint32_t it = 2u * ps + (lane >> 4);
-      const uint32_t col = it * 1024u + warp * 128u + (lane & 15u) * 8u;
-      xr[ps] = (it < iters && col < p.K) ? __ldcg(xg + col / 8u) : make_uint4(0u, 0u, 0u, 0u);   // L2: x may be fresh
-      m2 = max_u16x2(m2, max_u16x2(max_u16x2(xr[ps].x & 0x7fff7fffu, xr[ps].y & 0x7fff7fffu),
-                                   max_u16x2(xr[ps].z & 0x7fff7fffu, xr[ps].w & 0x7fff7fffu)));
-    }
-    const uint32_t mx = __reduce_max_sync(0xffffffffu, max(m2 & 0xffffu, m2 >> 16));
-    const uint32_t e = (mx >> 7) & 0xffu;
-    const int shift = e == 255u ? 0 : (e < 15u ? 126 : 141 - static_cast<int>(e));
-    const float up = __uint_as_float(static_cast<uint32_t>(127 + shift) << 23);
-    if (lane == 0) slice_inv[warp] = __uint_as_float(static_cast<uint32_t>(127 - shift) << 23);
+      for (int q = 0; q < 4; ++q)
+        h[q] = __floats2half2_rn(__uint_as_float(wv[q] << 16) * up, __uint_as_float(wv[q] & 0xffff0000u) * up);
+      return *reinterpret_cast<uint4 *>(h);
+    };
+    if (!flagged) {
+      uint4 xr[kPasses];
+      uint32_t m2 = 0;
 #pragma unroll
-    for (uint32_t ps = 0; ps < kPasses; ++ps) {
-      const uint32_t it = 2u * ps + (lane >> 4);
-      if (it < iters) {
-        const uint32_t wv[4] = {xr[ps].x, xr[ps].y, xr[ps].z, xr[ps].w};
-        __half2 h[4];
+      for (uint32_t ps = 0; ps < kPasses; ++ps) {
+        const uint32_t it = 2u * ps + (lane >> 4);
+        const uint32_t col = it * 1024u + warp * 128u + (lane & 15u) * 8u;
+        xr[ps] = (it < iters && col < p.K) ? __ldcg(xg + col / 8u) : make_uint4(0u, 0u, 0u, 0u);   // L2: x may be fresh
+        m2 = max_abs(m2, xr[ps]);
+      }
+      const float up = scale_of(m2);
 #pragma unroll
-        for (int q = 0; q < 4; ++q)
-          h[q] = __floats2half2_rn(__uint_as_float(wv[q] << 16) * up, __uint_as_float(wv[q] & 0xffff0000u) * up);
-        *reinterpret_cast<uint4 *>(xw + it * 256u + x_chunk_pos(lane & 15u) * 16u) = *reinterpret_cast<uint4 *>(h);
+      for (uint32_t ps = 0; ps < kPasses; ++ps) {
+        const uint32_t it = 2u * ps + (lane >> 4);
+        if (it < iters) *reinterpret_cast<uint4 *>(xw + it * 256u + x_chunk_pos(lane & 15u) * 16u) = to_f16(xr[ps], up);
+      }
+    } else {
+      // Flagged cells: 16 bytes carry four values, so a lane's eight values are two loads.  Eight
+      // passes' worth are requested in one go (one round trip where everything has arrived); the set
+      // is read again while any cell still carries an older call number.  The bf16 pairs are parked
+      // in the warp's own float16 slot (same size) until the slice maximum is known.
+      constexpr uint32_t kChunk = 8;
+      const uint8_t *xc = static_cast<const uint8_t *>(p.x);
+      uint32_t m2 = 0;
+#pragma unroll 1
+      for (uint32_t base = 0; base < kPasses && 2u * base < iters; base += kChunk) {
+        uint4 v[kChunk];
+        for (uint32_t attempt = 0;; ++attempt) {
+          // all loads are issued before the first comparison, so that they share one round trip
+          uint4 ca[kChunk], cb[kChunk];
+#pragma unroll
+          for (uint32_t j = 0; j < kChunk; ++j) {
+            const uint32_t it = 2u * (base + j) + (lane >> 4);
+            const uint32_t col = it * 1024u + warp * 128u + (lane & 15u) * 8u;
+            if (it < iters && col < p.K) {
+              ca[j] = ld_cells(xc + static_cast<size_t>(col) * 4u);
+              cb[j] = ld_cells(xc + static_cast<size_t>(col) * 4u + 16u);
+            } else {
+              ca[j] = cb[j] = make_uint4(0u, 0u, 0u, 0u);
+            }
+          }
+          bool ok = true;
+#pragma unroll
+          for (uint32_t j = 0; j < kChunk; ++j) {
+            const uint32_t it = 2u * (base + j) + (lane >> 4);
+            const uint32_t col = it * 1024u + warp * 128u + (lane & 15u) * 8u;
+            const bool real = it < iters && col < p.K;
+            ok = ok && (!real || (ca[j].y == want && ca[j].w == want && cb[j].y == want && cb[j].w == want));
+            v[j] = real ? make_uint4(ca[j].x, ca[j].z, cb[j].x, cb[j].z) : make_uint4(0u, 0u, 0u, 0u);
+          }
+          if (__all_sync(0xffffffffu, ok)) break;
+          if (attempt >= kPeerSpinLimit) { dead = true; break; }
+          if (attempt > kPeerEagerPolls) __nanosleep(200);
+        }
+#pragma unroll
+        for (uint32_t j = 0; j < kChunk; ++j) {
+          const uint32_t it = 2u * (base + j) + (lane >> 4);
+          if (dead) v[j] = make_uint4(0u, 0u, 0u, 0u);
+          m2 = max_abs(m2, v[j]);
+          if (it < iters) *reinterpret_cast<uint4 *>(xw + it * 256u + x_chunk_pos(lane & 15u) * 16u) = v[j];
+        }
+        if (dead) break;
+      }
+      const float up = scale_of(m2);
+      // every lane converts the chunks it parked itself: no exchange between lanes
+#pragma unroll 1
+      for (uint32_t it = lane >> 4; it < iters; it += 2u) {
+        uint4 *slot = reinterpret_cast<uint4 *>(xw + it * 256u + x_chunk_pos(lane & 15u) * 16u);
+        *slot = dead ? make_uint4(0u, 0u, 0u, 0u) : to_f16(*slot, up);
       }
     }
   } else {
@@ -346,6 +447,11 @@ nvfp4_gemv_mma_kernel(const __grid_constant__ GemvParams p) {
     }
     if (lane == 0) slice_inv[warp] = 1.0f;
   }
+  if (PEER) {
+    dead = __any_sync(0xffffffffu, dead);
+    if (dead) atomicExch(&g_gemv_mma_error, 2u);
+    if (lane == 0) peer_fail[warp] = dead ? 1u : 0u;
+  }
   // Meets the producer's arrival (barriers initialised); also publishes slice_inv and the zero chunk.
   asm volatile("bar.sync 2, %0;" ::"n"(kThreads + 32) : "memory");
   if (threadIdx.x == 0) Q36_TRACE(4);
@@ -369,7 +475,18 @@ nvfp4_gemv_mma_kernel(const __grid_constant__ GemvParams p) {
   for (uint32_t m = 0; m < 4u; ++m) x_pos[m] = x_active ? x_chunk_pos(c * 4u + m) * 16u : 0u;
 
   uint32_t g = 0, flip = 0;
-  bool dead = false;
+  // tensor-parallel form: lane L of warp 0 stores cell pair L / 4 (four consecutive rows) to ranks
+  // L % 4 and L % 4 + 4
+  uint8_t *peer_lo = nullptr, *peer_hi = nullptr;
+  bool poisoned = false;
+  uint32_t call = 0;
+  if (PEER && warp == 0u) {
+    if ((lane & 3u) < p.world) peer_lo = p.peer_arena[lane & 3u];
+    if ((lane & 3u) + 4u < p.world) peer_hi = p.peer_arena[(lane & 3u) + 4u];
+    call = *reinterpret_cast<const volatile uint32_t *>(p.state + p.out_slot * 4u) + 1u;
+#pragma unroll
+    for (uint32_t w = 0; w < static_cast<uint32_t>(kWarps); ++w) poisoned |= peer_fail[w] != 0u;
+  }
   for (uint32_t unit = blockIdx.x; unit < p.units; unit += gridDim.x, flip ^= 1u) {
     float acc[4] = {0.f, 0.f, 0.f, 0.f};                                 // rows q + 32 j, j = 0..3
     for (uint32_t it = 0; it < iters; ++it, ++g) {
@@ -439,12 +556,57 @@ nvfp4_gemv_mma_kernel(const __grid_constant__ GemvParams p) {
       const float global = XKIND == 0 ? (p.tensor_scale[mat] == nullptr ? 1.0f : __ldg(p.tensor_scale[mat])) : p.alpha;
       v *= global;
       if (v != v && !dead) v = exact_row<XKIND>(p, mat, row, global);
-      p.y[mat][row] = __float2bfloat16(v);
+      if (!PEER) {
+        p.y[mat][row] = __float2bfloat16(v);
+      } else {
+        if (poisoned || dead) v = __uint_as_float(0x7fc00000u);
+        const uint32_t bits = __bfloat16_as_ushort(__float2bfloat16(v));
+        const uint32_t pair = bits | (__shfl_down_sync(0xffffffffu, bits, 1) << 16);      // even lanes: rows 2i, 2i + 1
+        const uint32_t d0 = __shfl_sync(0xffffffffu, pair, lane & 28u), d1 = __shfl_sync(0xffffffffu, pair, (lane & 28u) + 2u);
+        // lanes 4c .. 4c + 3 hold four consecutive rows: (4c & 7) + 32 (4c >> 3) of the unit
+        const uint32_t row4 = (lu >> 2) * 128u + (lu & 3u) * 8u + (lane & 4u) + 32u * (lane >> 3);
+        const size_t at = p.y_off[mat] + (static_cast<size_t>(p.row_off[mat]) + row4) * 4u;
+        if (peer_lo != nullptr) st_cells(peer_lo + at, d0, d1, call);
+        if (peer_hi != nullptr) st_cells(peer_hi + at, d0, d1, call);
+      }
     }
     // `buf` alternates between units: the next write to this buffer comes after the next unit's barrier,
     // which warp 0 only reaches after the reads above.
   }
   if (threadIdx.x == 0) Q36_TRACE(7);
+  if (PEER && warp == 0u && lane == 0u) {
+    // The last CTA of the launch advances the slot's call number.  Nothing here orders the stores
+    // above: the cells order themselves.
+    uint32_t *st = p.state + p.out_slot * 4u;
+    if (poisoned || dead) atomicCAS(&st[2], 0u, call);
+    if (atomicAdd(&st[1], 1u) == gridDim.x - 1u) {
+      st[1] = 0;
+      *reinterpret_cast<volatile uint32_t *>(&st[0]) = call;
+    }
+  }
+}
+
+// Unpacks a flagged vector of this rank's arena into plain bf16 once all of its cells carry the
+// call number of `slot` (bounded wait; NaN where it ran out): for a consumer that is not one of
+// these kernels.  One thread per four values.
+__global__ void __launch_bounds__(256)
+nvfp4_gemv_peer_collect_kernel(const uint8_t *cells, uint32_t *state, uint32_t slot, uint32_t n, __nv_bfloat16 *out) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const uint32_t want = *reinterpret_cast<const volatile uint32_t *>(state + slot * 4u);
+  const uint32_t i = (blockIdx.x * blockDim.x + threadIdx.x) * 4u;
+  if (i >= n) return;
+  uint2 v = make_uint2(0x7fc07fc0u, 0x7fc07fc0u);
+  bool ok = false;
+  for (uint32_t spin = 0; spin < kPeerSpinLimit && !ok; ++spin) {
+    const uint4 c = ld_cells(cells + static_cast<size_t>(i) * 4u);
+    if (c.y == want && c.w == want) { v = make_uint2(c.x, c.z); ok = true; }
+    else if (spin > kPeerEagerPolls) __nanosleep(200);
+  }
+  if (!ok) {
+    atomicExch(&g_gemv_mma_error, 2u);
+    atomicCAS(&state[slot * 4u + 2u], 0u, want);
+  }
+  *reinterpret_cast<uint2 *>(out + i) = v;
 }
 
 // ---- host side ---------------------------------------------------------------------------------
@@ -536,9 +698,22 @@ bool shape_ok(uint64_t n, uint64_t k) {
   return n != 0 && n % 128 == 0 && n < (1ull << 31) && k >= 256 && k % 256 == 0 && k <= kMaxK;
 }
 
-template <int XKIND>
-int launch(const Mat *mats, uint32_t count, uint64_t K, const void *x, const uint8_t *x_sf, float alpha) {
+template <int XKIND, bool PEER = false>
+int launch(const Mat *mats, uint32_t count, uint64_t K, const void *x, const uint8_t *x_sf, float alpha,
+           const qwen36_nvfp4_matvec_peer_spec_t *peer = nullptr) {
   GemvParams p{};
+  if (PEER) {
+    p.peer_arena = as_ptr<uint8_t *const>(peer->peer_arena);
+    p.state = as_ptr<uint32_t>(peer->state);
+    p.world = static_cast<uint32_t>(peer->world);
+    p.rank = static_cast<uint32_t>(peer->rank);
+    p.out_slot = static_cast<uint32_t>(peer->out_slot);
+    p.in_slot = peer->in_slot == QWEN36_PEER_INPUT_LOCAL ? kNoSlot : static_cast<uint32_t>(peer->in_slot);
+    for (uint32_t i = 0; i < count; ++i) {
+      p.row_off[i] = static_cast<uint32_t>(peer->row_offset[i]);
+      p.y_off[i] = peer->output_offset_bytes[i];
+    }
+  }
   uint32_t units = 0;
   for (uint32_t i = 0; i < count; ++i) {
     if (!get_maps(mats[i].w, mats[i].sf, mats[i].n, K, &p.map_w[i], &p.map_sf[i])) return QWEN36_STATUS_NOT_IMPLEMENTED;
@@ -561,7 +736,7 @@ int launch(const Mat *mats, uint32_t count, uint64_t K, const void *x, const uin
   p.trace_id = g_trace_id.fetch_add(1u);
 #endif
   const size_t smem = 1024 + kHeaderBytes + kRingBytes + static_cast<size_t>(p.iters) * 2048;
-  if (q36::ensure_dynamic_smem(reinterpret_cast<const void *>(nvfp4_gemv_mma_kernel<XKIND>), 227 * 1024) != cudaSuccess)
+  if (q36::ensure_dynamic_smem(reinterpret_cast<const void *>(nvfp4_gemv_mma_kernel<XKIND, PEER>), 227 * 1024) != cudaSuccess)
     return QWEN36_STATUS_CUDA_ERROR;
   // Every CTA gets the same number of units: the grid is the unit count divided by the number of
   // round-robin passes that two CTAs per SM need.
@@ -578,7 +753,7 @@ int launch(const Mat *mats, uint32_t count, uint64_t K, const void *x, const uin
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return q36::cuda_status(cudaLaunchKernelEx(&cfg, nvfp4_gemv_mma_kernel<XKIND>, p));
+  return q36::cuda_status(cudaLaunchKernelEx(&cfg, nvfp4_gemv_mma_kernel<XKIND, PEER>, p));
 }
 
 }  // namespace
@@ -600,6 +775,39 @@ int nvfp4_gemv_mma_bf16(const qwen36_nvfp4_matvec_spec_t *specs, size_t count) {
   return launch<0>(mats, static_cast<uint32_t>(count), K, as_ptr<const void>(specs[0].input_bf16), nullptr, 1.0f);
 }
 
+int nvfp4_gemv_mma_bf16_peer(const qwen36_nvfp4_matvec_spec_t *specs, size_t count,
+                             const qwen36_nvfp4_matvec_peer_spec_t *peer) {
+  if (count == 0 || count > kMaxMats) return QWEN36_STATUS_NOT_IMPLEMENTED;
+  Mat mats[kMaxMats];
+  const uint64_t K = specs[0].in_features;
+  for (size_t i = 0; i < count; ++i) {
+    const qwen36_nvfp4_matvec_spec_t &s = specs[i];
+    if (s.in_features != K || s.input_bf16.ptr != specs[0].input_bf16.ptr || !shape_ok(s.out_features, K) ||
+        ((s.input_bf16.ptr | s.weight_u8.ptr | s.block_scale_e4m3.ptr) & 15u) != 0)
+      return QWEN36_STATUS_NOT_IMPLEMENTED;
+    mats[i] = Mat{as_ptr<const uint8_t>(s.weight_u8), as_ptr<const uint8_t>(s.block_scale_e4m3), nullptr,
+                  as_ptr<const float>(s.tensor_scale_f32), s.out_features};
+  }
+  return launch<0, true>(mats, static_cast<uint32_t>(count), K, as_ptr<const void>(specs[0].input_bf16), nullptr, 1.0f, peer);
+}
+
+int nvfp4_gemv_peer_collect(const qwen36_nvfp4_matvec_peer_spec_t *peer, size_t slot, size_t vector_offset_bytes,
+                            size_t n, qwen36_device_ptr_t arena, qwen36_device_ptr_t out_bf16) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>((n / 4 + 255) / 256));
+  cfg.blockDim = dim3(256);
+  cfg.stream = q36::stream();
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return q36::cuda_status(cudaLaunchKernelEx(&cfg, nvfp4_gemv_peer_collect_kernel,
+                                             as_ptr<const uint8_t>(arena) + vector_offset_bytes, as_ptr<uint32_t>(peer->state),
+                                             static_cast<uint32_t>(slot), static_cast<uint32_t>(n),
+                                             as_ptr<__nv_bfloat16>(out_bf16)));
+}
+
 int nvfp4_gemv_mma_fp4(const qwen36_nvfp4_gemm_spec_t *s, float alpha) {
   if (s->n != 1 || !shape_ok(s->m, s->k) || ((s->a_fp4.ptr | s->a_scale.ptr) & 15u) != 0 || (s->b_fp4.ptr & 7u) != 0)
     return QWEN36_STATUS_NOT_IMPLEMENTED;
@@ -619,10 +827,16 @@ extern "C" int qwen36_nvfp4_gemv_trace_read(void *dst) {
 }
 #endif
 
-// 1 when a bounded wait inside the tensor-core GEMV pipeline ever gave up (a stage never arrived);
-// the kernel then returns without finishing its rows.  Reads device memory: synchronises.
+// 1 when a bounded wait inside the tensor-core GEMV pipeline ever gave up (a stage never arrived;
+// the kernel then returns without finishing its rows), 2 when a wait for a peer's flag ran out in
+// the tensor-parallel form (rows poisoned).  Sticky until reset.  Reads device memory: synchronises.
 extern "C" int qwen36_nvfp4_gemv_mma_last_error(void) {
   unsigned int v = 0;
   if (cudaMemcpyFromSymbol(&v, g_gemv_mma_error, sizeof(v)) != cudaSuccess) return -1;
   return static_cast<int>(v);
+}
+
+extern "C" int qwen36_nvfp4_gemv_mma_reset_error(void) {
+  const unsigned int v = 0;
+  return cudaMemcpyToSymbol(g_gemv_mma_error, &v, sizeof(v)) == cudaSuccess ? 0 : -1;
 }

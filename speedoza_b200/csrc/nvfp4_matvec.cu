@@ -538,3 +538,35 @@ extern "C" int qwen36_nvfp4_matvec_group(const qwen36_nvfp4_matvec_spec_t *specs
   }
   return QWEN36_STATUS_SUCCESS;
 }
+
+namespace {
+bool peer_spec_ok(const qwen36_nvfp4_matvec_peer_spec_t *p) {
+  return p->world >= 1 && p->world <= 8 && p->rank < p->world && p->slots >= 1 && p->slots <= 1024 &&
+         p->out_slot < p->slots && (p->in_slot == QWEN36_PEER_INPUT_LOCAL || p->in_slot < p->slots) &&
+         p->peer_arena.ptr != 0 && p->state.ptr != 0;
+}
+}  // namespace
+
+extern "C" int qwen36_nvfp4_matvec_peer(const qwen36_nvfp4_matvec_spec_t *specs, size_t count,
+                                        const qwen36_nvfp4_matvec_peer_spec_t *peer) {
+  if (specs == nullptr || peer == nullptr) return QWEN36_STATUS_NULL_POINTER;
+  if (count == 0 || count > 4 || !peer_spec_ok(peer)) return QWEN36_STATUS_INVALID_ARGUMENT;
+  for (size_t i = 0; i < count; ++i) {
+    const qwen36_nvfp4_matvec_spec_t &s = specs[i];
+    if (s.out_features == 0 || s.in_features == 0 || s.input_bf16.ptr == 0 || s.weight_u8.ptr == 0 ||
+        s.block_scale_e4m3.ptr == 0 || s.in_features != specs[0].in_features ||
+        s.input_bf16.ptr != specs[0].input_bf16.ptr || peer->row_offset[i] % 8 != 0 ||
+        peer->output_offset_bytes[i] % 16 != 0)
+      return QWEN36_STATUS_INVALID_ARGUMENT;
+  }
+  return q36::nvfp4_gemv_mma_bf16_peer(specs, count, peer);
+}
+
+extern "C" int qwen36_nvfp4_matvec_peer_collect(const qwen36_nvfp4_matvec_peer_spec_t *peer, size_t slot,
+                                                qwen36_device_ptr_t cells, size_t n, qwen36_device_ptr_t output_bf16) {
+  if (peer == nullptr) return QWEN36_STATUS_NULL_POINTER;
+  if (!peer_spec_ok(peer) || slot >= peer->slots || n == 0 || n % 4 != 0 || cells.ptr == 0 || cells.ptr % 16 != 0 ||
+      output_bf16.ptr == 0 || output_bf16.ptr % 8 != 0)
+    return QWEN36_STATUS_INVALID_ARGUMENT;
+  return q36::nvfp4_gemv_peer_collect(peer, slot, 0, n, cells, output_bf16);
+}

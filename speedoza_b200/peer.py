@@ -162,3 +162,67 @@ class ArgmaxPeerCombine:
                                          _dp(out))
         _check("argmax_peer_combine", self.lib.qwen36_argmax_peer_combine(C.byref(spec)))
         return out
+
+
+class TensorParallelGemv:
+    """Chain of row-split W4A16 GEMVs whose outputs meet in every rank's arena over NVLink:
+    qwen36_nvfp4_matvec_peer.  `vectors` = {name: length}: the activation vectors of the chain; each
+    rank keeps one full copy of every one of them in its arena, as flagged cells (8 bytes per two
+    values: bf16 pair + number of the call that wrote them).  A call names the slot (call counter)
+    its output travels under; the call that consumes the output names the same slot as its input
+    slot.  Every rank must make the same sequence of calls."""
+
+    def __init__(self, backend, vectors: dict, slots: int, device, group=None):
+        self.lib = backend.lib
+        self.offsets, at = {}, 0
+        for name, n in vectors.items():
+            self.offsets[name] = (at, n)
+            at += (4 * n + 255) // 256 * 256
+        self.slots = slots
+        self.ex = PeerExchange(backend, at, 1, device, group)
+        self.state = torch.zeros(4 * slots, dtype=torch.int32, device=self.ex.device)
+        self._arena = int(self.ex.inbox_table[self.ex.rank].item())
+
+    def _spec(self, out_names, row_offsets, out_slot: int, in_slot):
+        offs = (abi.size_t * 4)(*([self.offsets[n][0] for n in out_names] + [0] * (4 - len(out_names))))
+        rows = (abi.size_t * 4)(*(list(row_offsets) + [0] * (4 - len(row_offsets))))
+        return abi.Nvfp4MatvecPeerSpec(self.ex.world, self.ex.rank, _dp(self.ex.inbox_table), _dp(self.state),
+                                       self.slots, out_slot, abi.PEER_INPUT_LOCAL if in_slot is None else in_slot,
+                                       offs, rows)
+
+    def gemv(self, x, mats, out_slot: int, in_slot=None) -> None:
+        """`x`: a local bf16 tensor (in_slot None), or (vector name, length) for the first `length`
+        values of a vector of the arena that the call of slot `in_slot` produced.  `mats`: up to four
+        (weight_u8 [local rows, K/2], sf_tiled, tensor_scale, output vector name, first row of the
+        slice) that share `x`."""
+        if isinstance(x, tuple):
+            x_ptr, k = abi.DevicePtr(self._arena + self.offsets[x[0]][0]), x[1]
+        else:
+            x_ptr, k = _dp(x), x.numel()
+        specs = (abi.Nvfp4MatvecSpec * len(mats))()
+        for i, (weight_u8, sf_tiled, tensor_scale, _, _) in enumerate(mats):
+            specs[i] = abi.Nvfp4MatvecSpec(weight_u8.shape[0], k, x_ptr, _dp(weight_u8), _dp(sf_tiled),
+                                           _dp(tensor_scale), abi.DevicePtr(0))
+        peer = self._spec([m[3] for m in mats], [m[4] for m in mats], out_slot, in_slot)
+        _check("nvfp4_matvec_peer", self.lib.qwen36_nvfp4_matvec_peer(specs, len(mats), C.byref(peer)))
+
+    def collect(self, name: str, slot: int, out=None, n=None) -> torch.Tensor:
+        """The vector `name`, produced by the call of `slot`, as a plain bf16 tensor (waits, bounded,
+        for every rank's part)."""
+        off, full = self.offsets[name]
+        n = full if n is None else n
+        if out is None:
+            out = torch.empty(n, dtype=torch.bfloat16, device=self.ex.device)
+        peer = self._spec([], [], 0, None)
+        _check("nvfp4_matvec_peer_collect",
+               self.lib.qwen36_nvfp4_matvec_peer_collect(C.byref(peer), slot, abi.DevicePtr(self._arena + off), n, _dp(out)))
+        return out
+
+    def failed_call(self) -> int:
+        """Number of the first call, on any slot, that went out poisoned or whose wait ran out (0 = none)."""
+        bad = self.state.view(-1, 4)[:, 2]
+        bad = bad[bad != 0]
+        return int(bad.min().item()) if bad.numel() else 0
+
+    def close(self, group=None) -> None:
+        self.ex.close(group)
