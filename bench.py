@@ -524,7 +524,8 @@ def other_configs(backend, torch, synth):
 def profile_case(name: str):
     """Runs one small, fixed case of a single kernel a few times (for `ncu -k ... -c ...`):
     gemv_gate_up | gemv_down | gemm_gate_up_2048 | gemm_down_2048 | lm_head_m1 | lm_head_m4 |
-    attention_32768 | quantize_2048 | bf16_argmax_m1 | bf16_argmax_m4 | decode_fp8_32768 | decode_bf16_32768.  Inputs exceed L2 but stay well under a few GB."""
+    attention_32768 | quantize_2048 | bf16_argmax_m1 | bf16_argmax_m4 | decode_fp8_32768 | decode_bf16_32768 |
+    verify_fp8_32768 | verify_bf16_32768 | gemv_sweep_layer.  Inputs exceed L2 but stay well under a few GB."""
     import torch
     from speedoza_b200 import synth
     from speedoza_b200.backend import CudaBackend
@@ -590,6 +591,35 @@ def profile_case(name: str):
                  torch.empty((24, 256), device="cuda"))
         for i in range(3):
             b.attention_decode(q_, kn, kn, caches[i], caches[(i + 1) % 3], ctx - 1, 1 if fp8 else 0, parts, 256)
+    elif name.startswith("verify_fp8_") or name.startswith("verify_bf16_"):
+        ctx = int(name.rsplit("_", 1)[1])
+        fp8 = name.startswith("verify_fp8_")
+        caches = []
+        for _ in range(3):
+            if fp8:
+                c = torch.randint(0x20, 0x40, (ctx, 4, 256), generator=gen, dtype=torch.uint8, device="cuda")
+            else:
+                c = torch.randn((ctx, 4, 256), generator=gen, device="cuda").to(torch.bfloat16)
+            caches.append(c)
+        qv = torch.randn((4, 24, 256), generator=gen, device="cuda").to(torch.bfloat16)
+        for i in range(3):
+            b.attention_flash_splitk_prefill(qv, caches[i], caches[(i + 1) % 3], ctx - 4, 1 if fp8 else 0, 74)
+    elif name.startswith("gemv_sweep_layer"):
+        # one decode layer (4 launches: q_gate + k + v grouped, o, gate_up, down), three times over cold weights
+        layers = []
+        for _ in range(3):
+            mats = []
+            for _, n, k in synth.DECODE_SHAPES:
+                p_, sf = synth.nvfp4_weight_device(gen, n, k, "cuda")
+                mats.append((p_, b.nvfp4_retile_scales(sf), torch.empty(n, dtype=torch.bfloat16, device="cuda")))
+            layers.append(mats)
+        ts = torch.tensor([synth.WEIGHT_GLOBAL_SCALE], device="cuda")
+        x = torch.randn(5120, generator=gen, device="cuda").to(torch.bfloat16)
+        for mats in layers:
+            b.nvfp4_matvec_group(x, [(m[0], m[1], ts, m[2]) for m in mats[:3]])
+            b.nvfp4_matvec(mats[0][2][:6144], mats[3][0], mats[3][1], ts, mats[3][2])
+            b.nvfp4_matvec(mats[3][2], mats[4][0], mats[4][1], ts, mats[4][2])
+            b.nvfp4_matvec(mats[4][2][:17408], mats[5][0], mats[5][1], ts, mats[5][2])
     elif name.startswith("bf16_argmax_m"):
         m_tok = int(name.rsplit("m", 1)[1])
         rows, cols = synth.VOCAB, synth.HIDDEN

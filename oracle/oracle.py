@@ -23,6 +23,12 @@ _f32p = C.POINTER(C.c_float)
 _sz = C.c_size_t
 
 
+def reference_dir() -> str:
+    """Where the reference checkout lives on the build machine: QWEN36_REFERENCE_DIR, else the
+    default location.  The one place that names it; nothing that runs on a GPU box reads it."""
+    return os.environ.get("QWEN36_REFERENCE_DIR", "/root/reference")
+
+
 def build(force: bool = False) -> str:
     """Compile liboracle.so with the Makefile beside this file."""
     src = os.path.join(_HERE, "oracle.c")

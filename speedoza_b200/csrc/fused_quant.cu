@@ -169,9 +169,8 @@ extern "C" int qwen36_rmsnorm_nvfp4_quantize(const qwen36_rmsnorm_nvfp4_quantize
   const float eps = spec->eps == 0.0f ? 1.0e-6f : spec->eps;
   const size_t smem = spec->hidden * sizeof(float);
   if (smem > 200 * 1024) return QWEN36_STATUS_INVALID_ARGUMENT;
-  static cudaError_t attr_err = cudaFuncSetAttribute(rmsnorm_nvfp4_quantize_kernel,
-                                                     cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-  if (attr_err != cudaSuccess) return QWEN36_STATUS_CUDA_ERROR;
+  if (q36::ensure_dynamic_smem(reinterpret_cast<const void *>(rmsnorm_nvfp4_quantize_kernel), 200 * 1024) != cudaSuccess)
+    return QWEN36_STATUS_CUDA_ERROR;
   rmsnorm_nvfp4_quantize_kernel<<<1, kNormThreads, smem, q36::stream()>>>(
       as_ptr<const __nv_bfloat16>(spec->input_bf16), as_ptr<const __nv_bfloat16>(spec->weight_bf16),
       as_ptr<const __nv_bfloat16>(spec->residual_bf16), as_ptr<__nv_bfloat16>(spec->residual_out_bf16),

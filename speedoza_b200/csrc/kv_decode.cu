@@ -20,6 +20,8 @@
 // library.
 #include "common.cuh"
 
+#include <atomic>
+
 #include <math.h>
 
 #include <mutex>
@@ -45,8 +47,8 @@ constexpr int kMaxSplits = 256;              // the merge handles one partial pe
 constexpr uint32_t kMinTokensPerSplit = 256;
 constexpr int kKvBf16 = 0, kKvFp8 = 1;
 
-int g_decode_mode = 1;                       // test hook: 0 = general kernel only, 1 = tensor-core forms where they apply
-int g_decode_force_splits = 0;               // test hook: > 0 overrides the split count
+std::atomic<int> g_decode_mode{1};                       // test hook: 0 = general kernel only, 1 = tensor-core forms where they apply
+std::atomic<int> g_decode_force_splits{0};               // test hook: > 0 overrides the split count
 
 // E4M3 byte -> float as the reference reads its cache (attention.cu:101-116): 0x7F / 0xFF are +-448.
 __device__ __forceinline__ float kv_e4m3_to_f32(uint32_t code) {
@@ -713,13 +715,9 @@ int launch_direct(const Args &a) {
 
 template <int G>
 int launch_fp8_staged(const Args &a, uint32_t n_splits) {
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(decode_split_fp8_staged_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    static_cast<int>(kStagedSmemBytes));
-  });
-  if (attr_err != cudaSuccess) return QWEN36_STATUS_CUDA_ERROR;
+  if (q36::ensure_dynamic_smem(reinterpret_cast<const void *>(decode_split_fp8_staged_kernel<G>),
+                               static_cast<int>(kStagedSmemBytes)) != cudaSuccess)
+    return QWEN36_STATUS_CUDA_ERROR;
   return q36::cuda_status(q36::launch_after_previous(
       decode_split_fp8_staged_kernel<G>, dim3(a.q_heads / G, n_splits), dim3(kThreads), kStagedSmemBytes, q36::stream(),
       a.q, static_cast<const uint8_t *>(a.cache_k), static_cast<const uint8_t *>(a.cache_v), a.part_o, a.part_m,
@@ -759,7 +757,7 @@ int launch_merge(const Args &a, uint32_t n_parts) {
 uint32_t pick_splits(const Args &a, size_t caller_splits, size_t ctas_per_split, bool one_wave) {
   const size_t sms = static_cast<size_t>(sm_count());
   size_t n = one_wave ? sms / ctas_per_split : q36::div_ceil(2 * sms, ctas_per_split);
-  if (g_decode_force_splits > 0) n = static_cast<size_t>(g_decode_force_splits);
+  if (g_decode_force_splits > 0) n = static_cast<size_t>(g_decode_force_splits.load());
   else if (a.position_device == nullptr) {
     const size_t cap = q36::div_ceil(a.position, kMinTokensPerSplit);
     if (n > cap) n = cap;

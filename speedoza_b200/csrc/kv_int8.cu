@@ -15,6 +15,8 @@
 // (kernels-cuda/attention.cu:1083-1094); a second kernel merges them.
 #include "common.cuh"
 
+#include <atomic>
+
 #include <cuda_fp16.h>
 
 #include <mutex>
@@ -460,7 +462,7 @@ int launch_merge_after_splits(unsigned q_heads, const float *o, const float *m, 
 }
 
 struct Scratch { float *o, *m, *l; };
-int g_use_fast_attention = 3;            // 3 tensor-core form fed through shared memory, 2 tensor-core form fed from registers, 1 SIMT fast path, 0 general kernel
+std::atomic<int> g_use_fast_attention{3};            // 3 tensor-core form fed through shared memory, 2 tensor-core form fed from registers, 1 SIMT fast path, 0 general kernel
 
 // Scratch for qwen36_turboquant_attention_static: lives in the library image, so every GPU that
 // loads the library holds these 4 MiB until the process exits.  Sized for
@@ -477,7 +479,7 @@ Scratch carve(float *base, size_t q_heads, size_t head_dim) {
   return {base, base + q_heads * kMaxSplits * head_dim, base + q_heads * kMaxSplits * (head_dim + 1)};
 }
 
-int g_force_splits = 0;                  // test hook: > 0 overrides the split count
+std::atomic<int> g_force_splits{0};                  // test hook: > 0 overrides the split count
 
 int sm_count() {
   static int cached[64] = {0};
@@ -493,7 +495,7 @@ int sm_count() {
 // one_wave: the kernel runs one CTA per SM (the tensor-core form: a CTA's start-up and merge cost
 // about as much as 1500 tokens, and nothing overlaps them), so the grid is one CTA per SM or less.
 uint32_t pick_splits(size_t tokens, size_t ctas_per_split, bool one_wave) {
-  if (g_force_splits > 0) return static_cast<uint32_t>(g_force_splits > kMaxSplits ? kMaxSplits : g_force_splits);
+  if (g_force_splits > 0) { const int f = g_force_splits.load(); return static_cast<uint32_t>(f > static_cast<int>(kMaxSplits) ? static_cast<int>(kMaxSplits) : f); }
   // otherwise fill ~2 CTAs per SM; at least kMinTokensPerSplit tokens each
   const size_t sms = static_cast<size_t>(sm_count());
   size_t want = one_wave ? sms / ctas_per_split : q36::div_ceil(2 * sms, ctas_per_split);
@@ -961,13 +963,9 @@ int launch_split_g(const __nv_bfloat16 *q, const int8_t *kq, const int8_t *vq, c
   if (D == 256 && G <= 8 && g_use_fast_attention == 3 &&
       ((reinterpret_cast<uintptr_t>(kq) | reinterpret_cast<uintptr_t>(vq) | reinterpret_cast<uintptr_t>(q)) & 15u) == 0 &&
       (reinterpret_cast<uintptr_t>(meta) & 7u) == 0) {
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [] {
-      attr_err = cudaFuncSetAttribute(kv_attention_staged_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      static_cast<int>(kStagedSmemBytes));
-    });
-    if (attr_err != cudaSuccess) return QWEN36_STATUS_CUDA_ERROR;
+    if (q36::ensure_dynamic_smem(reinterpret_cast<const void *>(kv_attention_staged_kernel<G>),
+                                 static_cast<int>(kStagedSmemBytes)) != cudaSuccess)
+      return QWEN36_STATUS_CUDA_ERROR;
     return q36::cuda_status(q36::launch_after_previous(kv_attention_staged_kernel<G>, grid, dim3(kThreads),
                                                        kStagedSmemBytes, q36::stream(), q, kq, vq, meta, sc.o, sc.m,
                                                        sc.l, t_begin, t_end, KV, q_per_kv, n_splits));

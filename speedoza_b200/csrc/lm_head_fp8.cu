@@ -342,18 +342,7 @@ int launch_argmax(const __nv_bfloat16 *logits, uint32_t *out, uint32_t *mirror, 
   return q36::cuda_status(cudaLaunchKernelEx(&cfg, argmax_rows_kernel, logits, out, mirror, rows, vocab, temperature));
 }
 
-int g_sm_count = 0;
-int sm_count() {
-  if (g_sm_count == 0) {
-    int dev = 0, n = 0;
-    if (cudaGetDevice(&dev) == cudaSuccess &&
-        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
-      g_sm_count = n;
-    else
-      return 148;
-  }
-  return g_sm_count;
-}
+int sm_count() { return q36::sm_count_current_device(); }
 
 // Bytes of activation staging: float32 for 3..8 tokens while that fits, bf16 otherwise.
 bool stage_f32(size_t n, size_t cols) { return n >= 3 && n <= 8 && n * cols * 4 <= 200 * 1024; }
@@ -364,13 +353,8 @@ int launch_gemv_x(const uint8_t *w, const float *scales, const __nv_bfloat16 *x,
                   size_t cols, uint32_t row_offset, uint32_t *tokens, float *best, float2 *partials,
                   unsigned *ticket, unsigned grid) {
   const size_t smem = static_cast<size_t>(N) * cols * (XF32 ? 4 : 2);
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(lm_head_gemv_kernel<N, FUSED, XF32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    200 * 1024);
-  });
-  if (attr_err != cudaSuccess) return QWEN36_STATUS_CUDA_ERROR;
+  if (q36::ensure_dynamic_smem(reinterpret_cast<const void *>(lm_head_gemv_kernel<N, FUSED, XF32>), 200 * 1024) != cudaSuccess)
+    return QWEN36_STATUS_CUDA_ERROR;
   lm_head_gemv_kernel<N, FUSED, XF32><<<grid, kThreads, smem, q36::stream()>>>(
       w, scales, x, y, rows, static_cast<uint32_t>(cols), row_offset, tokens, best, partials, ticket);
   return q36::launch_status();

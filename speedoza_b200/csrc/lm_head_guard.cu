@@ -459,23 +459,13 @@ __global__ void bf16_argmax_finalize_kernel(const unsigned long long *__restrict
   if (mirror_last != nullptr && row + 1 == rows) *mirror_last = token;
 }
 
-int sm_count() {
-  static int n = [] {
-    int dev = 0, v = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess ||
-        cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0)
-      return 148;
-    return v;
-  }();
-  return n;
-}
+int sm_count() { return q36::sm_count_current_device(); }
 
 template <int N>
 int launch_bf16_argmax_fast(const qwen36_bf16_matvec_argmax_rows_spec_t *s, size_t row_base) {
   const size_t smem = static_cast<size_t>(N) * s->in_features * sizeof(float) + (kThreads / 32) * kFastRows * 512;
-  static cudaError_t attr_err = cudaFuncSetAttribute(bf16_argmax_fast_kernel<N>,
-                                                     cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
-  if (attr_err != cudaSuccess) return QWEN36_STATUS_CUDA_ERROR;
+  if (q36::ensure_dynamic_smem(reinterpret_cast<const void *>(bf16_argmax_fast_kernel<N>), 220 * 1024) != cudaSuccess)
+    return QWEN36_STATUS_CUDA_ERROR;
   const size_t need = q36::div_ceil(s->out_features, static_cast<size_t>(kThreads / 32) * kFastRows);
   const size_t per_sm = smem > 100 * 1024 ? 1 : (smem > 70 * 1024 ? 2 : (smem > 52 * 1024 ? 3 : (smem > 40 * 1024 ? 4 : 5)));
   const size_t cap = static_cast<size_t>(sm_count()) * per_sm;
@@ -490,9 +480,8 @@ template <int N>
 int launch_bf16_argmax(const qwen36_bf16_matvec_argmax_rows_spec_t *s, size_t row_base) {
   if (s->in_features % 256 == 0 && (s->weight_bf16.ptr & 15u) == 0) return launch_bf16_argmax_fast<N>(s, row_base);
   const size_t smem = static_cast<size_t>(N) * s->in_features * sizeof(float);
-  static cudaError_t attr_err = cudaFuncSetAttribute(bf16_argmax_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                     200 * 1024);
-  if (attr_err != cudaSuccess) return QWEN36_STATUS_CUDA_ERROR;
+  if (q36::ensure_dynamic_smem(reinterpret_cast<const void *>(bf16_argmax_kernel<N>), 200 * 1024) != cudaSuccess)
+    return QWEN36_STATUS_CUDA_ERROR;
   const size_t need = q36::div_ceil(s->out_features, static_cast<size_t>(kThreads / 32) * ArgmaxShape<N>::kVocab);
   const size_t per_sm = smem > 100 * 1024 ? 1 : (smem > 48 * 1024 ? 2 : (smem > 24 * 1024 ? 4 : 8));
   const size_t cap = static_cast<size_t>(sm_count()) * per_sm;

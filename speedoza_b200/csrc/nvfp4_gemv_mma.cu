@@ -18,15 +18,24 @@
 // 16-column scale group per column n, and the block scale is applied to that sum with one
 // float32 FMA per (row, group), which is the reference's own order of operations.
 //
-// Pipeline.  Persistent CTAs, one producer warp + eight consumer warps.  A work unit is 32 rows
-// (rows r0+q+32j of a 128-row block, q < 8, j < 4) over all of K; a stage is 1024 columns of it:
+// Pipeline.  Persistent CTAs: one producer warp, eight consumer warps, one epilogue warp.  A work
+// unit is 32 rows (rows r0+q+32j of a 128-row block, q < 8, j < 4); a stage is 1024 columns of it:
 // ONE 5-D tiled TMA box of weights (128-byte swizzle, 16 KB) + ONE 3-D box of scale tiles (2 KB),
 // four stages in flight per CTA.  Every consumer warp owns 128 of a stage's 1024 columns for all
-// 32 rows, so all warps are busy on every stage whatever the matrix shape; their partial sums meet
-// in shared memory once per unit.  The activation slice of a warp is staged by that warp alone
-// (no CTA barrier between the end of the producing kernel and the first MMA).  Units are dealt
-// round-robin over a grid sized so that every CTA gets the same number of units.  Up to four
-// matrices that share the activation vector run as one launch.
+// 32 rows, so all warps are busy on every stage whatever the matrix shape; their partial sums go
+// through shared memory to the epilogue warp, which forms the rows while the consumers are already
+// on the next item.  The activation slice of a warp is staged by that warp alone (no CTA barrier
+// between the end of the producing kernel and the first MMA).  Up to four matrices that share the
+// activation vector run as one launch.
+//
+// Work decomposition.  For K of more than kChunkStages stages a unit is cut along K into chunks, an
+// item is one chunk of one unit, and every CTA takes a contiguous run of the chunk-major item list
+// that holds 1 / grid of the launch's stages: matrices with few rows (o: 160 units, down: 160
+// units of 17 stages) then fill all CTA slots evenly instead of leaving half of them idle, and a
+// CTA stages only the part of x its chunks touch.  The chunks of a unit meet in global memory
+// (see the epilogue warp).  The cut depends on K alone, so a row's sum is formed in the same order
+// whatever the matrix height, the grouping or the GPU.  Units of shorter K stay whole and are
+// dealt round-robin over a grid sized so that every CTA gets the same number of them.
 //
 // Weights and scales stream before griddepcontrol.wait: under programmatic dependent launch the
 // ring fills while the kernel that produces x is still finishing.
@@ -45,6 +54,7 @@
 #include "nvfp4_gemv_mma.cuh"
 
 #include <atomic>
+#include <mutex>
 #include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
@@ -53,10 +63,20 @@ namespace {
 
 using q36::as_ptr;
 
-constexpr int kWarps = 8;
-constexpr int kThreads = kWarps * 32;
+constexpr int kWarps = 8;                           // consumer warps
+constexpr uint32_t kWarpProducer = kWarps, kWarpEpilogue = kWarps + 1;
+constexpr int kBlock = (kWarps + 2) * 32;
+constexpr uint32_t kRed = 3;                        // items' partial sums in flight to the epilogue warp
+#ifndef Q36_GEMV_CHUNK
+#define Q36_GEMV_CHUNK 6
+#endif
+constexpr uint32_t kChunkStages = Q36_GEMV_CHUNK;   // stages per K-chunk, at most
+constexpr uint32_t kMaxChunks = 16;                 // K-chunks per unit (kMaxK / 1024 stages over kChunkStages)
 constexpr uint32_t kMaxMats = 4;
-constexpr uint32_t kStages = 4;
+#ifndef Q36_GEMV_STAGES
+#define Q36_GEMV_STAGES 4
+#endif
+constexpr uint32_t kStages = Q36_GEMV_STAGES;
 #ifndef Q36_GEMV_AHEAD
 #define Q36_GEMV_AHEAD 4
 #endif
@@ -65,15 +85,19 @@ constexpr uint32_t kStageW = 16384;                 // 32 rows x 512 B
 constexpr uint32_t kStageSf = 2048;                 // 16 scale tiles x 8 row-words x 16 B
 constexpr uint32_t kStageBytes = kStageW + kStageSf;
 constexpr uint32_t kRingBytes = kStages * kStageBytes;
-constexpr uint32_t kHeaderBytes = 3072;             // barriers, slice scales, zero chunk, partial sums
+constexpr uint32_t kHeaderBytes = 4096;             // barriers, slice scales, zero chunk, partial sums
 constexpr uint32_t kSpinLimit = 1u << 24;
 constexpr uint32_t kMaxK = 32768;
 constexpr uint32_t kMaxPeers = 8;                   // tensor-parallel form: ranks of one node
 constexpr uint32_t kNoSlot = 0xffffffffu;
 constexpr uint32_t kPeerSpinLimit = 1u << 21;       // x (200 ns back-off + one read of the cells): 1-2 s
 constexpr uint32_t kPeerEagerPolls = 2048;
+constexpr uint32_t kParkSpinLimit = 1u << 20;       // x (100 ns back-off + one round trip to L2): about a second
 
 __device__ unsigned int g_gemv_mma_error = 0;       // set when a bounded wait gives up
+constexpr uint32_t kPoolSets = 8, kScratchCells = 1u << 19, kTicketWords = 1u << 15;
+__device__ unsigned long long g_scratch[kPoolSets * kScratchCells];   // 32 MB, zero-initialised like every device global
+__device__ uint32_t g_tickets[kPoolSets * kTicketWords];
 
 // Per-CTA %globaltimer stamps for pipeline analysis; compiled in only with -DQ36_GEMV_TRACE.
 #ifdef Q36_GEMV_TRACE
@@ -100,6 +124,10 @@ struct GemvParams {
   const void *x;                         // bf16 vector (W4A16) or packed E2M1 codes (W4A4)
   const uint8_t *x_sf;                   // W4A4: tiled UE4M3 scales of the activation row
   uint32_t K, iters, units, count;
+  uint32_t chunk, cpu;                   // stages per K-chunk, chunks per unit
+  unsigned long long *scratch;           // [units][cpu][32] parked partial sums of units cut along K: (float, launch tag)
+  uint32_t *tickets;                     // [units] chunks of a unit that have been parked (self-resetting)
+  uint32_t tag;                          // nonzero, differs between launches that may meet in one scratch set
   float alpha;                           // W4A4
   // tensor-parallel form only
   uint8_t *const *peer_arena;            // device array [world]: base of every rank's arena (own one included)
@@ -237,72 +265,248 @@ __device__ __noinline__ float exact_row(const GemvParams &p, uint32_t mat, uint3
   return XKIND == 0 ? sum : sum * global;
 }
 
+// Work decomposition.  A unit (32 rows over all of K) is cut along K into `cpu` chunks of `chunk`
+// stages (the last one may be shorter); the chunk boundaries depend on K alone.  An ITEM is one
+// chunk of one unit; items are numbered chunk-major (all units' chunk 0, then chunk 1, ...) and
+// every CTA takes a contiguous range of them holding 1/grid of the launch's stages.  So every CTA
+// streams the same number of bytes whatever the matrix shape (two CTAs per SM: every SM too),
+// and a CTA touches few distinct K-chunks, of which alone it stages the activations.
+struct Item {
+  uint32_t unit, kc, it0, nit;        // global unit, chunk index, first stage, stages
+  uint32_t mat, lu, rb, r0;           // matrix, unit inside it, 128-row block, first q-row of the unit
+};
+__device__ __forceinline__ Item decode_item(const GemvParams &p, uint32_t j) {
+  Item t;
+  t.kc = j / p.units;
+  t.unit = j - t.kc * p.units;
+  t.it0 = t.kc * p.chunk;
+  t.nit = min(p.chunk, p.iters - t.it0);
+  uint32_t mat = 0, first = 0;
+  while (mat + 1u < p.count && t.unit >= p.unit_end[mat]) { first = p.unit_end[mat]; ++mat; }
+  t.mat = mat;
+  t.lu = t.unit - first;
+  t.rb = t.lu >> 2;
+  t.r0 = (t.lu & 3u) * 8u;
+  return t;
+}
+// Units that stay whole (cpu == 1) are dealt round-robin instead: item k of CTA b is unit b + k * grid,
+// so that the CTAs running at the same time read neighbouring rows (measured faster than one
+// contiguous band per CTA); the grid is then sized so that every CTA gets the same number of units.
+// Items [begin, end) of CTA b otherwise: boundaries at b / grid of the launch's stages, rounded down
+// to an item.
+__device__ __forceinline__ uint32_t item_at(const GemvParams &p, uint32_t b, uint32_t grid) {
+  if (b >= grid) return p.units * p.cpu;
+  const uint32_t last = p.iters - (p.cpu - 1u) * p.chunk;
+  const uint64_t total = static_cast<uint64_t>(p.units) * p.iters;
+  const uint64_t full_part = static_cast<uint64_t>(p.cpu - 1u) * p.units * p.chunk;
+  const uint64_t pos = total * b / grid;
+  return pos < full_part ? static_cast<uint32_t>(pos / p.chunk)
+                         : (p.cpu - 1u) * p.units + static_cast<uint32_t>((pos - full_part) / last);
+}
+
+__device__ __forceinline__ uint32_t atom_add_acq_rel_gpu(uint32_t *p, uint32_t v) {
+  uint32_t old;
+  asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
+  return old;
+}
+
 // XKIND 0: x is a bf16 vector.  XKIND 1: x is one NVFP4-quantised activation row.
 template <int XKIND, bool PEER>
-__global__ void __launch_bounds__(kThreads + 32, 2)
+__global__ void __launch_bounds__(kBlock, 2)
 nvfp4_gemv_mma_kernel(const __grid_constant__ GemvParams p) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   // the swizzled boxes need 1024-byte aligned stages
   uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint64_t *full = reinterpret_cast<uint64_t *>(smem);                 // [kStages]
   uint64_t *empty = full + kStages;                                    // [kStages]
-  float *slice_inv = reinterpret_cast<float *>(smem + 256);            // [kWarps] inverse scale of a warp's x slice
-  uint4 *zero_chunk = reinterpret_cast<uint4 *>(smem + 320);           // 16 bytes of zeros
-  uint32_t *peer_fail = reinterpret_cast<uint32_t *>(smem + 336);      // [kWarps] 1 = this warp's wait for a peer ran out
-  static_assert(2 * kStages * sizeof(uint64_t) <= 256, "barriers overlap the header fields");
-  float *red = reinterpret_cast<float *>(smem + 1024);                 // [2][kWarps][32] partial row sums
+  uint64_t *red_full = empty + kStages;                                // [kRed]
+  uint64_t *red_empty = red_full + kRed;                               // [kRed]
+  static_assert((2 * kStages + 2 * kRed) * sizeof(uint64_t) <= 128, "barriers overlap the header fields");
+  uint4 *zero_chunk = reinterpret_cast<uint4 *>(smem + 128);           // 16 bytes of zeros
+  uint32_t *peer_fail = reinterpret_cast<uint32_t *>(smem + 160);      // [kWarps] 1 = this warp's wait for a peer ran out
+  float *slice_inv = reinterpret_cast<float *>(smem + 256);            // [kMaxChunks][kWarps] inverse scale of a warp's x slice
+  static_assert(256 + kMaxChunks * kWarps * sizeof(float) <= 1024, "slice scales overlap the partial sums");
+  float *red = reinterpret_cast<float *>(smem + 1024);                 // [kRed][kWarps][32] partial row sums
+  static_assert(1024 + kRed * kWarps * 32 * sizeof(float) <= kHeaderBytes, "partial sums overlap the ring");
   uint8_t *ring = smem + kHeaderBytes;
   uint8_t *xs = ring + kRingBytes;                                     // [kWarps][iters][256 B] float16 activations
 
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
   const uint32_t iters = p.iters;
+  const bool strided = p.cpu == 1u;
+  const uint32_t j_begin = strided ? blockIdx.x : item_at(p, blockIdx.x, gridDim.x);
+  const uint32_t j_end = strided ? p.units : item_at(p, blockIdx.x + 1u, gridDim.x);
+  const uint32_t j_step = strided ? gridDim.x : 1u;
 
   if (threadIdx.x == 0) Q36_TRACE(0);
-  if (warp == kWarps) {
+  if (warp == kWarpProducer) {
     // ------------------------------------------------------------------ producer warp
-    // It owns the barriers: initialises them, signals the consumers through a named barrier it
-    // does not wait on, and starts streaming at once (weights do not depend on the kernel that
+    // It owns the barriers: initialises them, signals the others through a named barrier it does
+    // not wait on, and starts streaming at once (weights do not depend on the kernel that
     // produced x).
     if (lane < kStages) { mbar_init(&full[lane], 1); mbar_init(&empty[lane], kWarps); }
+    if (lane < kRed) { mbar_init(&red_full[lane], kWarps); mbar_init(&red_empty[lane], 1); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("bar.arrive 2, %0;" ::"n"(kThreads + 32) : "memory");
+    asm volatile("bar.arrive 2, %0;" ::"n"(kBlock) : "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    if (lane == 0) {
+    if (lane == 0 && j_begin < j_end) {
       // Run-ahead cursor: asks L2 for the boxes the ring will want `kAhead` stages later.  The ring
       // itself is full long before x is ready (that is the point of streaming early); without the
       // run-ahead HBM would idle from then until the first stage is released.  With it the next
       // stages are already in L2 when the consumers start, and they work them off faster than HBM
       // could deliver them.
-      uint32_t pf_unit = blockIdx.x, pf_it = 0, pf_issued = 0;
+      uint32_t pf_j = j_begin, pf_issued = 0;
+      Item pf = decode_item(p, pf_j);
+      uint32_t pf_it = pf.it0;
       auto prefetch_one = [&]() {
-        if (pf_unit >= p.units) return;
-        uint32_t mat = 0, first = 0;
-        while (mat + 1u < p.count && pf_unit >= p.unit_end[mat]) { first = p.unit_end[mat]; ++mat; }
-        const uint32_t lu = pf_unit - first, rb = lu >> 2, r0 = (lu & 3u) * 8u;
-        tma_prefetch_5d(&p.map_w[mat], 0u, r0, 0u, pf_it * 4u, rb);
-        tma_prefetch_3d(&p.map_sf[mat], r0 * 4u, pf_it * 16u, rb);
+        if (pf_j >= j_end) return;
+        tma_prefetch_5d(&p.map_w[pf.mat], 0u, pf.r0, 0u, pf_it * 4u, pf.rb);
+        tma_prefetch_3d(&p.map_sf[pf.mat], pf.r0 * 4u, pf_it * 16u, pf.rb);
         ++pf_issued;
-        if (++pf_it == iters) { pf_it = 0; pf_unit += gridDim.x; }
+        if (++pf_it == pf.it0 + pf.nit && (pf_j += j_step) < j_end) { pf = decode_item(p, pf_j); pf_it = pf.it0; }
       };
       uint32_t g = 0;
-      for (uint32_t unit = blockIdx.x; unit < p.units; unit += gridDim.x) {
-        uint32_t mat = 0, first = 0;
-        while (mat + 1u < p.count && unit >= p.unit_end[mat]) { first = p.unit_end[mat]; ++mat; }
-        const uint32_t lu = unit - first, rb = lu >> 2, r0 = (lu & 3u) * 8u;
-        for (uint32_t it = 0; it < iters; ++it, ++g) {
+      for (uint32_t j = j_begin; j < j_end; j += j_step) {
+        const Item t = decode_item(p, j);
+        for (uint32_t it = t.it0; it < t.it0 + t.nit; ++it, ++g) {
           const uint32_t stage = g % kStages, phase = (g / kStages) & 1u;
           if (kAhead != 0u && g >= kStages)                  // the ring is full: keep L2 `kAhead` stages ahead
-            while (pf_issued < g + kAhead + 1u && pf_unit < p.units) prefetch_one();
+            while (pf_issued < g + kAhead + 1u && pf_j < j_end) prefetch_one();
           if (!mbar_wait(&empty[stage], phase ^ 1u)) return;
           uint8_t *dst = ring + stage * kStageBytes;
           mbar_expect_tx(&full[stage], kStageBytes);        // whole boxes; columns past K arrive as zeros
-          tma_load_5d(dst, &p.map_w[mat], 0u, r0, 0u, it * 4u, rb, &full[stage]);
-          tma_load_3d(dst + kStageW, &p.map_sf[mat], r0 * 4u, it * 16u, rb, &full[stage]);
+          tma_load_5d(dst, &p.map_w[t.mat], 0u, t.r0, 0u, it * 4u, t.rb, &full[stage]);
+          tma_load_3d(dst + kStageW, &p.map_sf[t.mat], t.r0 * 4u, it * 16u, t.rb, &full[stage]);
           if (kAhead != 0u && pf_issued <= g) prefetch_one();   // cursor never falls behind the loads (skips what they fetched)
           if (g == 0) Q36_TRACE(1);
         }
       }
       Q36_TRACE(2);
+    }
+    return;
+  }
+
+  if (warp == kWarpEpilogue) {
+    // ------------------------------------------------------------------ epilogue warp
+    // Takes the eight warps' partial row sums of an item out of shared memory, so that the
+    // consumers go straight on to the next item.  Lane = row of the unit.  A unit that was cut
+    // along K meets in global memory: every chunk's 32 sums are parked there, a ticket per unit
+    // tells the last chunk to arrive, and that one adds them in chunk order (the order of
+    // arrival plays no part in the result).
+    asm volatile("griddepcontrol.wait;" ::: "memory");        // outputs and scratch may still be in use by the grid before
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("bar.sync 2, %0;" ::"n"(kBlock) : "memory");
+    // tensor-parallel form: lane L stores cell pair L / 4 (four consecutive rows) to ranks L % 4 and L % 4 + 4
+    uint8_t *peer_lo = nullptr, *peer_hi = nullptr;
+    bool poisoned = false;
+    uint32_t call = 0;
+    if (PEER) {
+      if ((lane & 3u) < p.world) peer_lo = p.peer_arena[lane & 3u];
+      if ((lane & 3u) + 4u < p.world) peer_hi = p.peer_arena[(lane & 3u) + 4u];
+      call = *reinterpret_cast<const volatile uint32_t *>(p.state + p.out_slot * 4u) + 1u;
+#pragma unroll
+      for (uint32_t w = 0; w < static_cast<uint32_t>(kWarps); ++w) poisoned |= peer_fail[w] != 0u;
+    }
+    float gscale[kMaxMats];
+#pragma unroll
+    for (uint32_t i = 0; i < kMaxMats; ++i)
+      gscale[i] = XKIND == 0 ? ((i < p.count && p.tensor_scale[i] != nullptr) ? __ldg(p.tensor_scale[i]) : 1.0f) : p.alpha;
+    bool dead = false;
+    // Writes a unit's 32 rows: v = the row sums before the tensor scale.
+    auto write_rows = [&](const Item &t, float v) {
+      const uint32_t row = (t.lu >> 2) * 128u + (t.lu & 3u) * 8u + (lane & 7u) + 32u * (lane >> 3);
+      float global = gscale[0];
+#pragma unroll
+      for (uint32_t i = 1; i < kMaxMats; ++i) global = t.mat == i ? gscale[i] : global;
+      v *= global;
+      if (v != v && !dead) v = exact_row<XKIND>(p, t.mat, row, global);
+      if (!PEER) {
+        p.y[t.mat][row] = __float2bfloat16(v);
+      } else {
+        if (poisoned || dead) v = __uint_as_float(0x7fc00000u);
+        const uint32_t bits = __bfloat16_as_ushort(__float2bfloat16(v));
+        const uint32_t pair = bits | (__shfl_down_sync(0xffffffffu, bits, 1) << 16);      // even lanes: rows 2i, 2i + 1
+        const uint32_t d0 = __shfl_sync(0xffffffffu, pair, lane & 28u), d1 = __shfl_sync(0xffffffffu, pair, (lane & 28u) + 2u);
+        // lanes 4c .. 4c + 3 hold four consecutive rows: (4c & 7) + 32 (4c >> 3) of the unit
+        const uint32_t row4 = (t.lu >> 2) * 128u + (t.lu & 3u) * 8u + (lane & 4u) + 32u * (lane >> 3);
+        const size_t at = p.y_off[t.mat] + (static_cast<size_t>(p.row_off[t.mat]) + row4) * 4u;
+        if (peer_lo != nullptr) st_cells(peer_lo + at, d0, d1, call);
+        if (peer_hi != nullptr) st_cells(peer_hi + at, d0, d1, call);
+      }
+    };
+    // A unit cut along K: every chunk takes a ticket of the unit when its CTA turns to it, and the
+    // chunk that took the last one adds the unit up, in chunk order, once its own sums are there.
+    // The others park theirs in global memory as 8-byte cells (value, launch tag).  Nothing orders
+    // a parked cell before anything else: the reader looks again until the tag is there (its owner
+    // took its ticket earlier, so it is at most about one item behind), and then wipes the cell
+    // for the next launch that gets this scratch set.  The ticket is taken one item ahead, so its
+    // round trip to L2 runs under the wait for the item's sums.
+    auto add_up = [&](const Item &t, float own) {
+      unsigned long long *parked = p.scratch + static_cast<size_t>(t.unit) * p.cpu * 32u + lane;
+      float v = 0.f;
+      for (uint32_t k0 = 0; k0 < p.cpu; k0 += 4u) {
+        unsigned long long cell[4] = {0ull, 0ull, 0ull, 0ull};
+        for (uint32_t spin = 0;; ++spin) {
+#pragma unroll
+          for (uint32_t i = 0; i < 4u; ++i)             // all loads first: one round trip
+            if (k0 + i < p.cpu && k0 + i != t.kc)
+              asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(cell[i]) : "l"(parked + (k0 + i) * 32u) : "memory");
+          bool ok = true;
+#pragma unroll
+          for (uint32_t i = 0; i < 4u; ++i)
+            ok = ok && (k0 + i >= p.cpu || k0 + i == t.kc || static_cast<uint32_t>(cell[i] >> 32) == p.tag);
+          if (__all_sync(0xffffffffu, ok)) break;
+          if (spin >= kParkSpinLimit) { dead = true; atomicExch(&g_gemv_mma_error, 1u); break; }
+          if (spin > 64u) __nanosleep(100);
+        }
+#pragma unroll
+        for (uint32_t i = 0; i < 4u; ++i) {
+          if (k0 + i >= p.cpu) continue;
+          if (k0 + i == t.kc) { v += own; continue; }
+          v += __uint_as_float(static_cast<uint32_t>(cell[i]));
+          parked[(k0 + i) * 32u] = 0ull;
+        }
+      }
+      if (lane == 0) p.tickets[t.unit] = 0;                   // ready for the next launch that gets this scratch
+      write_rows(t, v);
+    };
+    uint32_t next_ticket = 0;
+    if (p.cpu > 1u && j_begin < j_end && lane == 0) next_ticket = atomicAdd(p.tickets + j_begin % p.units, 1u);
+    uint32_t n_local = 0;
+    for (uint32_t j = j_begin; j < j_end; j += j_step, ++n_local) {
+      const Item t = decode_item(p, j);
+      const uint32_t ticket = next_ticket;
+      const uint32_t slot = n_local % kRed, ph = (n_local / kRed) & 1u;
+      if (!dead && !mbar_wait(&red_full[slot], ph)) dead = true;
+      const float *buf = red + slot * (kWarps * 32u);
+      const float *inv = slice_inv + t.kc * kWarps;
+      float v = 0.f;
+#pragma unroll
+      for (uint32_t w = 0; w < static_cast<uint32_t>(kWarps); ++w) v = fmaf(buf[w * 32u + lane], inv[w], v);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&red_empty[slot]);
+      if (p.cpu == 1u) {
+        write_rows(t, v);
+        continue;
+      }
+      if (j + 1u < j_end && lane == 0) next_ticket = atomicAdd(p.tickets + (j + 1u) % p.units, 1u);
+      if (__shfl_sync(0xffffffffu, ticket, 0) == p.cpu - 1u) {
+        add_up(t, v);
+      } else {
+        const unsigned long long cell = (static_cast<unsigned long long>(p.tag) << 32) | __float_as_uint(v);
+        asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p.scratch + (static_cast<size_t>(t.unit) * p.cpu + t.kc) * 32u + lane), "l"(cell) : "memory");
+      }
+    }
+    if (threadIdx.x == kWarpEpilogue * 32u) Q36_TRACE(7);
+    if (PEER && lane == 0u) {
+      // The last CTA of the launch advances the slot's call number.  Nothing here orders the stores
+      // above: the cells order themselves.
+      uint32_t *st = p.state + p.out_slot * 4u;
+      if (poisoned || dead) atomicCAS(&st[2], 0u, call);
+      if (atomicAdd(&st[1], 1u) == gridDim.x - 1u) {
+        st[1] = 0;
+        *reinterpret_cast<volatile uint32_t *>(&st[0]) = call;
+      }
     }
     return;
   }
@@ -320,140 +524,123 @@ nvfp4_gemv_mma_kernel(const __grid_constant__ GemvParams p) {
   uint32_t want = 0;
   if (flagged) want = *reinterpret_cast<const volatile uint32_t *>(p.state + p.in_slot * 4u);
 
-  // Each warp stages the activations of ITS columns (128 of every 1024) as float16, alone.
+  // Each warp stages the activations of ITS columns (128 of every 1024) as float16, alone, and only
+  // for the K-chunks this CTA's items touch.
   uint8_t *xw = xs + warp * iters * 256u;
-  if (XKIND == 0) {
-    // bf16 -> float16 times a power of two that brings the slice's max|x| into [2^14, 2^15):
-    // products with e2m1 weights stay exact, values more than 2^-38 below the maximum flush (far
-    // below the float32 accumulation error); the inverse scale is applied to the warp's partial sum.
-    constexpr uint32_t kPasses = kMaxK / 1024u / 2u;        // two stages' worth of chunks per pass
-    const uint4 *xg = static_cast<const uint4 *>(p.x);
-    auto max_abs = [](uint32_t m2, const uint4 &v) {
-      return max_u16x2(m2, max_u16x2(max_u16x2(v.x & 0x7fff7fffu, v.y & 0x7fff7fffu), max_u16x2(v.z & 0x7fff7fffu, v.w & 0x7fff7fffu)));
-    };
-    auto scale_of = [&](uint32_t m2) {          // power of two that lifts the slice maximum to [2^14, 2^15)
+  const uint32_t kc_lo = j_begin < j_end ? j_begin / p.units : 1u, kc_hi = j_begin < j_end ? (j_end - 1u) / p.units : 0u;
+  for (uint32_t kc = kc_lo; kc <= kc_hi; ++kc) {
+    const uint32_t it0 = kc * p.chunk, it_end = min(it0 + p.chunk, iters);
+    if (XKIND == 0) {
+      // bf16 -> float16 times a power of two that brings the slice's max|x| into [2^14, 2^15):
+      // products with e2m1 weights stay exact, values more than 2^-38 below the maximum flush (far
+      // below the float32 accumulation error); the inverse scale is applied to the warp's partial sum.
+      // A pass of the warp covers two stages (16 lanes x 8 values each).  Four passes' loads go out
+      // together; the bf16 values are parked in the warp's own float16 slot (same size) until the
+      // chunk's maximum is known, then every lane converts what it parked.
+      constexpr uint32_t kBatch = 4;
+      const uint8_t *xc = static_cast<const uint8_t *>(p.x);
+      uint32_t m2 = 0;
+      for (uint32_t base = it0; base < it_end; base += 2u * kBatch) {
+        uint4 v[kBatch];
+        uint32_t its[kBatch];
+        bool real[kBatch];
+#pragma unroll
+        for (uint32_t ps = 0; ps < kBatch; ++ps) {
+          its[ps] = base + 2u * ps + (lane >> 4);
+          real[ps] = its[ps] < it_end && its[ps] * 1024u + warp * 128u + (lane & 15u) * 8u < p.K;
+        }
+        if (!flagged) {
+          const uint4 *xg = static_cast<const uint4 *>(p.x);
+#pragma unroll
+          for (uint32_t ps = 0; ps < kBatch; ++ps)
+            v[ps] = real[ps] ? __ldcg(xg + (its[ps] * 1024u + warp * 128u) / 8u + (lane & 15u)) : make_uint4(0u, 0u, 0u, 0u);   // L2: x may be fresh
+        } else {
+          // Flagged cells: 16 bytes carry four values, so a lane's eight values are two loads.  All of
+          // the batch's loads are issued before the first comparison (one round trip where everything
+          // has arrived); the set is read again while any cell still carries an older call number.
+          for (uint32_t attempt = 0; !dead; ++attempt) {
+            uint4 ca[kBatch], cb[kBatch];
+#pragma unroll
+            for (uint32_t ps = 0; ps < kBatch; ++ps) {
+              ca[ps] = cb[ps] = make_uint4(0u, want, 0u, want);
+              if (real[ps]) {
+                const uint8_t *src = xc + (static_cast<size_t>(its[ps]) * 1024u + warp * 128u + (lane & 15u) * 8u) * 4u;
+                ca[ps] = ld_cells(src);
+                cb[ps] = ld_cells(src + 16u);
+              }
+            }
+            bool ok = true;
+#pragma unroll
+            for (uint32_t ps = 0; ps < kBatch; ++ps) {
+              ok = ok && ca[ps].y == want && ca[ps].w == want && cb[ps].y == want && cb[ps].w == want;
+              v[ps] = make_uint4(ca[ps].x, ca[ps].z, cb[ps].x, cb[ps].z);
+            }
+            if (__all_sync(0xffffffffu, ok)) break;
+            if (attempt >= kPeerSpinLimit) dead = true;
+            else if (attempt > kPeerEagerPolls) __nanosleep(200);
+          }
+        }
+#pragma unroll
+        for (uint32_t ps = 0; ps < kBatch; ++ps) {
+          if (dead) v[ps] = make_uint4(0u, 0u, 0u, 0u);
+          m2 = max_u16x2(m2, max_u16x2(max_u16x2(v[ps].x & 0x7fff7fffu, v[ps].y & 0x7fff7fffu),
+                                       max_u16x2(v[ps].z & 0x7fff7fffu, v[ps].w & 0x7fff7fffu)));
+          if (its[ps] < it_end) *reinterpret_cast<uint4 *>(xw + its[ps] * 256u + x_chunk_pos(lane & 15u) * 16u) = v[ps];
+        }
+      }
       const uint32_t mx = __reduce_max_sync(0xffffffffu, max(m2 & 0xffffu, m2 >> 16));
       const uint32_t e = (mx >> 7) & 0xffu;
       const int shift = e == 255u ? 0 : (e < 15u ? 126 : 141 - static_cast<int>(e));
-      if (lane == 0) slice_inv[warp] = __uint_as_float(static_cast<uint32_t>(127 - shift) << 23);
-      return __uint_as_float(static_cast<uint32_t>(127 + shift) << 23);
-    };
-    auto to_f16 = [](const uint4 &v, float up) {
-      const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
-      __half2 h[4];
+      const float up = __uint_as_float(static_cast<uint32_t>(127 + shift) << 23);
+      if (lane == 0) slice_inv[kc * kWarps + warp] = __uint_as_float(static_cast<uint32_t>(127 - shift) << 23);
+      for (uint32_t it = it0 + (lane >> 4); it < it_end; it += 2u) {
+        uint4 *slot = reinterpret_cast<uint4 *>(xw + it * 256u + x_chunk_pos(lane & 15u) * 16u);
+        const uint4 raw = *slot;
+        const uint32_t wv[4] = {raw.x, raw.y, raw.z, raw.w};
+        __half2 h[4];
 #pragma unroll
-      for (int q = 0; q < 4; ++q)
-        h[q] = __floats2half2_rn(__uint_as_float(wv[q] << 16) * up, __uint_as_float(wv[q] & 0xffff0000u) * up);
-      return *reinterpret_cast<uint4 *>(h);
-    };
-    if (!flagged) {
-      uint4 xr[kPasses];
-      uint32_t m2 = 0;
-#pragma unroll
-      for (uint32_t ps = 0; ps < kPasses; ++ps) {
-        const uint32_t it = 2u * ps + (lane >> 4);
-        const uint32_t col = it * 1024u + warp * 128u + (lane & 15u) * 8u;
-        xr[ps] = (it < iters && col < p.K) ? __ldcg(xg + col / 8u) : make_uint4(0u, 0u, 0u, 0u);   // L2: x may be fresh
-        m2 = max_abs(m2, xr[ps]);
-      }
-      const float up = scale_of(m2);
-#pragma unroll
-      for (uint32_t ps = 0; ps < kPasses; ++ps) {
-        const uint32_t it = 2u * ps + (lane >> 4);
-        if (it < iters) *reinterpret_cast<uint4 *>(xw + it * 256u + x_chunk_pos(lane & 15u) * 16u) = to_f16(xr[ps], up);
+        for (int q = 0; q < 4; ++q)
+          h[q] = __floats2half2_rn(__uint_as_float(wv[q] << 16) * up, __uint_as_float(wv[q] & 0xffff0000u) * up);
+        *slot = *reinterpret_cast<uint4 *>(h);
       }
     } else {
-      // Flagged cells: 16 bytes carry four values, so a lane's eight values are two loads.  Eight
-      // passes' worth are requested in one go (one round trip where everything has arrived); the set
-      // is read again while any cell still carries an older call number.  The bf16 pairs are parked
-      // in the warp's own float16 slot (same size) until the slice maximum is known.
-      constexpr uint32_t kChunk = 8;
-      const uint8_t *xc = static_cast<const uint8_t *>(p.x);
-      uint32_t m2 = 0;
-#pragma unroll 1
-      for (uint32_t base = 0; base < kPasses && 2u * base < iters; base += kChunk) {
-        uint4 v[kChunk];
-        for (uint32_t attempt = 0;; ++attempt) {
-          // all loads are issued before the first comparison, so that they share one round trip
-          uint4 ca[kChunk], cb[kChunk];
-#pragma unroll
-          for (uint32_t j = 0; j < kChunk; ++j) {
-            const uint32_t it = 2u * (base + j) + (lane >> 4);
-            const uint32_t col = it * 1024u + warp * 128u + (lane & 15u) * 8u;
-            if (it < iters && col < p.K) {
-              ca[j] = ld_cells(xc + static_cast<size_t>(col) * 4u);
-              cb[j] = ld_cells(xc + static_cast<size_t>(col) * 4u + 16u);
-            } else {
-              ca[j] = cb[j] = make_uint4(0u, 0u, 0u, 0u);
-            }
-          }
-          bool ok = true;
-#pragma unroll
-          for (uint32_t j = 0; j < kChunk; ++j) {
-            const uint32_t it = 2u * (base + j) + (lane >> 4);
-            const uint32_t col = it * 1024u + warp * 128u + (lane & 15u) * 8u;
-            const bool real = it < iters && col < p.K;
-            ok = ok && (!real || (ca[j].y == want && ca[j].w == want && cb[j].y == want && cb[j].w == want));
-            v[j] = real ? make_uint4(ca[j].x, ca[j].z, cb[j].x, cb[j].z) : make_uint4(0u, 0u, 0u, 0u);
-          }
-          if (__all_sync(0xffffffffu, ok)) break;
-          if (attempt >= kPeerSpinLimit) { dead = true; break; }
-          if (attempt > kPeerEagerPolls) __nanosleep(200);
+      // e2m1 * ue4m3 is exact in float16 (at most 7 significant bits, magnitudes 2^-10 .. 2688).
+      const uint8_t *xb = static_cast<const uint8_t *>(p.x);
+      const uint32_t sub = lane & 7u;                                     // one 16-value group per lane
+      for (uint32_t it = it0 + (lane >> 3); it < it_end; it += 4u) {
+        const uint32_t col = it * 1024u + warp * 128u + sub * 16u;
+        uint2 codes = make_uint2(0u, 0u);
+        uint32_t sbyte = 0;
+        if (col < p.K) {
+          codes = __ldcg(reinterpret_cast<const uint2 *>(xb + col / 2u));
+          const uint32_t grp = col / 16u;
+          sbyte = __ldcg(p.x_sf + static_cast<size_t>(grp >> 2) * 512u + (grp & 3u));
         }
+        const __half_raw sraw = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(sbyte), __NV_E4M3);
+        const __half2 s2 = __half2half2(*reinterpret_cast<const __half *>(&sraw));
+        uint32_t lo[4], hi[4];
+        e2m1x8_to_h2(codes.x, lo);
+        e2m1x8_to_h2(codes.y, hi);
+        __half2 h[8];
 #pragma unroll
-        for (uint32_t j = 0; j < kChunk; ++j) {
-          const uint32_t it = 2u * (base + j) + (lane >> 4);
-          if (dead) v[j] = make_uint4(0u, 0u, 0u, 0u);
-          m2 = max_abs(m2, v[j]);
-          if (it < iters) *reinterpret_cast<uint4 *>(xw + it * 256u + x_chunk_pos(lane & 15u) * 16u) = v[j];
+        for (int q = 0; q < 4; ++q) {
+          h[q] = __hmul2(*reinterpret_cast<__half2 *>(&lo[q]), s2);
+          h[4 + q] = __hmul2(*reinterpret_cast<__half2 *>(&hi[q]), s2);
         }
-        if (dead) break;
+        uint4 *dst = reinterpret_cast<uint4 *>(xw + it * 256u);
+        dst[x_chunk_pos(sub * 2u)] = *reinterpret_cast<uint4 *>(&h[0]);
+        dst[x_chunk_pos(sub * 2u + 1u)] = *reinterpret_cast<uint4 *>(&h[4]);
       }
-      const float up = scale_of(m2);
-      // every lane converts the chunks it parked itself: no exchange between lanes
-#pragma unroll 1
-      for (uint32_t it = lane >> 4; it < iters; it += 2u) {
-        uint4 *slot = reinterpret_cast<uint4 *>(xw + it * 256u + x_chunk_pos(lane & 15u) * 16u);
-        *slot = dead ? make_uint4(0u, 0u, 0u, 0u) : to_f16(*slot, up);
-      }
+      if (lane == 0) slice_inv[kc * kWarps + warp] = 1.0f;
     }
-  } else {
-    // e2m1 * ue4m3 is exact in float16 (at most 7 significant bits, magnitudes 2^-10 .. 2688).
-    const uint8_t *xb = static_cast<const uint8_t *>(p.x);
-    const uint32_t sub = lane & 7u;                                     // one 16-value group per lane
-    for (uint32_t it = lane >> 3; it < iters; it += 4u) {
-      const uint32_t col = it * 1024u + warp * 128u + sub * 16u;
-      uint2 codes = make_uint2(0u, 0u);
-      uint32_t sbyte = 0;
-      if (col < p.K) {
-        codes = __ldcg(reinterpret_cast<const uint2 *>(xb + col / 2u));
-        const uint32_t grp = col / 16u;
-        sbyte = __ldcg(p.x_sf + static_cast<size_t>(grp >> 2) * 512u + (grp & 3u));
-      }
-      const __half_raw sraw = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(sbyte), __NV_E4M3);
-      const __half2 s2 = __half2half2(*reinterpret_cast<const __half *>(&sraw));
-      uint32_t lo[4], hi[4];
-      e2m1x8_to_h2(codes.x, lo);
-      e2m1x8_to_h2(codes.y, hi);
-      __half2 h[8];
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        h[q] = __hmul2(*reinterpret_cast<__half2 *>(&lo[q]), s2);
-        h[4 + q] = __hmul2(*reinterpret_cast<__half2 *>(&hi[q]), s2);
-      }
-      uint4 *dst = reinterpret_cast<uint4 *>(xw + it * 256u);
-      dst[x_chunk_pos(sub * 2u)] = *reinterpret_cast<uint4 *>(&h[0]);
-      dst[x_chunk_pos(sub * 2u + 1u)] = *reinterpret_cast<uint4 *>(&h[4]);
-    }
-    if (lane == 0) slice_inv[warp] = 1.0f;
   }
   if (PEER) {
     dead = __any_sync(0xffffffffu, dead);
     if (dead) atomicExch(&g_gemv_mma_error, 2u);
     if (lane == 0) peer_fail[warp] = dead ? 1u : 0u;
   }
-  // Meets the producer's arrival (barriers initialised); also publishes slice_inv and the zero chunk.
-  asm volatile("bar.sync 2, %0;" ::"n"(kThreads + 32) : "memory");
+  // Meets the producer's arrival (barriers initialised); also publishes the slice scales and the zero chunk.
+  asm volatile("bar.sync 2, %0;" ::"n"(kBlock) : "memory");
   if (threadIdx.x == 0) Q36_TRACE(4);
 
   // Fragment geometry.  Lane (r = lane / 4, c = lane % 4) of the MMA holds weight rows r and r + 8 of a
@@ -474,28 +661,19 @@ nvfp4_gemv_mma_kernel(const __grid_constant__ GemvParams p) {
 #pragma unroll
   for (uint32_t m = 0; m < 4u; ++m) x_pos[m] = x_active ? x_chunk_pos(c * 4u + m) * 16u : 0u;
 
-  uint32_t g = 0, flip = 0;
-  // tensor-parallel form: lane L of warp 0 stores cell pair L / 4 (four consecutive rows) to ranks
-  // L % 4 and L % 4 + 4
-  uint8_t *peer_lo = nullptr, *peer_hi = nullptr;
-  bool poisoned = false;
-  uint32_t call = 0;
-  if (PEER && warp == 0u) {
-    if ((lane & 3u) < p.world) peer_lo = p.peer_arena[lane & 3u];
-    if ((lane & 3u) + 4u < p.world) peer_hi = p.peer_arena[(lane & 3u) + 4u];
-    call = *reinterpret_cast<const volatile uint32_t *>(p.state + p.out_slot * 4u) + 1u;
-#pragma unroll
-    for (uint32_t w = 0; w < static_cast<uint32_t>(kWarps); ++w) poisoned |= peer_fail[w] != 0u;
-  }
-  for (uint32_t unit = blockIdx.x; unit < p.units; unit += gridDim.x, flip ^= 1u) {
+  uint32_t g = 0, n_local = 0;
+  bool stalled = false;
+  for (uint32_t j = j_begin; j < j_end; j += j_step, ++n_local) {
+    const uint32_t kc = j / p.units;
+    const uint32_t it0 = kc * p.chunk, it_end = min(it0 + p.chunk, iters);
     float acc[4] = {0.f, 0.f, 0.f, 0.f};                                 // rows q + 32 j, j = 0..3
-    for (uint32_t it = 0; it < iters; ++it, ++g) {
+    for (uint32_t it = it0; it < it_end; ++it, ++g) {
       const uint32_t stage = g % kStages, phase = (g / kStages) & 1u;
       // A wait that gives up (never seen in practice) only stops the arithmetic: the warp keeps
       // walking its stages and barriers so that nobody else is left waiting for it.
-      if (!dead && !mbar_wait(&full[stage], phase)) dead = true;
+      if (!stalled && !mbar_wait(&full[stage], phase)) stalled = true;
       if (threadIdx.x == 0 && g == 0) Q36_TRACE(5);
-      if (!dead) {
+      if (!stalled) {
         const uint8_t *st = ring + stage * kStageBytes;
         uint4 bx[4];
 #pragma unroll
@@ -537,52 +715,18 @@ nvfp4_gemv_mma_kernel(const __grid_constant__ GemvParams p) {
       if (lane == 0) mbar_arrive(&empty[stage]);
     }
     if (threadIdx.x == 0) Q36_TRACE(6);
-    // Lanes c = 0 and c = 1 hold the two scale tiles of the warp's columns; lanes c >= 2 hold zeros.
-    float *buf = red + flip * (kWarps * 32u);
+    // Hand the item's sums to the epilogue warp.  Lanes c = 0 and c = 1 hold the two scale tiles of the
+    // warp's columns; lanes c >= 2 hold zeros.
+    const uint32_t slot = n_local % kRed, ph = (n_local / kRed) & 1u;
+    if (!stalled && !mbar_wait(&red_empty[slot], ph ^ 1u)) stalled = true;
+    float *buf = red + slot * (kWarps * 32u);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], 1);
-      if (c == 0u) buf[warp * 32u + static_cast<uint32_t>(j) * 8u + q] = acc[j];
+    for (int jj = 0; jj < 4; ++jj) {
+      acc[jj] += __shfl_xor_sync(0xffffffffu, acc[jj], 1);
+      if (c == 0u) buf[warp * 32u + static_cast<uint32_t>(jj) * 8u + q] = acc[jj];
     }
-    asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory");
-    if (threadIdx.x < 32u) {
-      uint32_t mat = 0, first = 0;
-      while (mat + 1u < p.count && unit >= p.unit_end[mat]) { first = p.unit_end[mat]; ++mat; }
-      const uint32_t lu = unit - first;
-      const uint32_t row = (lu >> 2) * 128u + (lu & 3u) * 8u + (threadIdx.x & 7u) + 32u * (threadIdx.x >> 3);
-      float v = 0.f;
-#pragma unroll
-      for (uint32_t w = 0; w < static_cast<uint32_t>(kWarps); ++w) v = fmaf(buf[w * 32u + threadIdx.x], slice_inv[w], v);
-      const float global = XKIND == 0 ? (p.tensor_scale[mat] == nullptr ? 1.0f : __ldg(p.tensor_scale[mat])) : p.alpha;
-      v *= global;
-      if (v != v && !dead) v = exact_row<XKIND>(p, mat, row, global);
-      if (!PEER) {
-        p.y[mat][row] = __float2bfloat16(v);
-      } else {
-        if (poisoned || dead) v = __uint_as_float(0x7fc00000u);
-        const uint32_t bits = __bfloat16_as_ushort(__float2bfloat16(v));
-        const uint32_t pair = bits | (__shfl_down_sync(0xffffffffu, bits, 1) << 16);      // even lanes: rows 2i, 2i + 1
-        const uint32_t d0 = __shfl_sync(0xffffffffu, pair, lane & 28u), d1 = __shfl_sync(0xffffffffu, pair, (lane & 28u) + 2u);
-        // lanes 4c .. 4c + 3 hold four consecutive rows: (4c & 7) + 32 (4c >> 3) of the unit
-        const uint32_t row4 = (lu >> 2) * 128u + (lu & 3u) * 8u + (lane & 4u) + 32u * (lane >> 3);
-        const size_t at = p.y_off[mat] + (static_cast<size_t>(p.row_off[mat]) + row4) * 4u;
-        if (peer_lo != nullptr) st_cells(peer_lo + at, d0, d1, call);
-        if (peer_hi != nullptr) st_cells(peer_hi + at, d0, d1, call);
-      }
-    }
-    // `buf` alternates between units: the next write to this buffer comes after the next unit's barrier,
-    // which warp 0 only reaches after the reads above.
-  }
-  if (threadIdx.x == 0) Q36_TRACE(7);
-  if (PEER && warp == 0u && lane == 0u) {
-    // The last CTA of the launch advances the slot's call number.  Nothing here orders the stores
-    // above: the cells order themselves.
-    uint32_t *st = p.state + p.out_slot * 4u;
-    if (poisoned || dead) atomicCAS(&st[2], 0u, call);
-    if (atomicAdd(&st[1], 1u) == gridDim.x - 1u) {
-      st[1] = 0;
-      *reinterpret_cast<volatile uint32_t *>(&st[0]) = call;
-    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&red_full[slot]);
   }
 }
 
@@ -687,6 +831,40 @@ bool get_maps(const void *w, const void *sf, uint64_t N, uint64_t K, CUtensorMap
 std::atomic<uint32_t> g_trace_id{0};
 #endif
 
+// Parking area for the partial sums of units cut along K, and the per-unit tickets.  A launch
+// touches its set only after the grid before it on the stream has completed, so launches of one
+// stream never meet in a set; launches of different streams take different sets as long as
+// fewer than kPoolSets of them are in flight at once.
+struct ScratchSet {
+  unsigned long long *scratch;
+  uint32_t *tickets;
+  uint32_t tag;
+};
+std::atomic<uint32_t> g_pool_seq{0};
+std::mutex g_pool_mu;
+unsigned long long *g_pool_scratch[64];
+uint32_t *g_pool_tickets[64];
+
+bool scratch_for_launch(ScratchSet *out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+  {
+    std::lock_guard<std::mutex> lock(g_pool_mu);
+    if (g_pool_scratch[dev] == nullptr) {
+      void *a = nullptr, *b = nullptr;
+      if (cudaGetSymbolAddress(&a, g_scratch) != cudaSuccess || cudaGetSymbolAddress(&b, g_tickets) != cudaSuccess) return false;
+      g_pool_scratch[dev] = static_cast<unsigned long long *>(a);
+      g_pool_tickets[dev] = static_cast<uint32_t *>(b);
+    }
+  }
+  const uint32_t seq = g_pool_seq.fetch_add(1u);
+  const uint32_t set = seq % kPoolSets;
+  out->tag = seq % 0xfffffffeu + 1u;
+  out->scratch = g_pool_scratch[dev] + static_cast<size_t>(set) * kScratchCells;
+  out->tickets = g_pool_tickets[dev] + static_cast<size_t>(set) * kTicketWords;
+  return true;
+}
+
 struct Mat {
   const uint8_t *w, *sf;
   __nv_bfloat16 *y;
@@ -735,17 +913,34 @@ int launch(const Mat *mats, uint32_t count, uint64_t K, const void *x, const uin
 #ifdef Q36_GEMV_TRACE
   p.trace_id = g_trace_id.fetch_add(1u);
 #endif
+  // K-chunks of at most kChunkStages stages, as even as the stage count allows; the cut depends on K alone,
+  // so a row's sum is formed in the same order whatever the matrix height, grouping or GPU.
+  p.cpu = (p.iters + kChunkStages - 1u) / kChunkStages;
+  p.chunk = (p.iters + p.cpu - 1u) / p.cpu;
+  p.cpu = (p.iters + p.chunk - 1u) / p.chunk;
+  if (p.cpu > 1u) {
+    ScratchSet set;
+    if (static_cast<size_t>(units) * p.cpu * 32u > kScratchCells || units > kTicketWords || !scratch_for_launch(&set)) {
+      p.cpu = 1u;                          // too tall for the parking area: whole units, one CTA each
+      p.chunk = p.iters;
+    } else {
+      p.scratch = set.scratch;
+      p.tickets = set.tickets;
+      p.tag = set.tag;
+    }
+  }
   const size_t smem = 1024 + kHeaderBytes + kRingBytes + static_cast<size_t>(p.iters) * 2048;
   if (q36::ensure_dynamic_smem(reinterpret_cast<const void *>(nvfp4_gemv_mma_kernel<XKIND, PEER>), 227 * 1024) != cudaSuccess)
     return QWEN36_STATUS_CUDA_ERROR;
-  // Every CTA gets the same number of units: the grid is the unit count divided by the number of
-  // round-robin passes that two CTAs per SM need.
+  // One CTA per resident slot (two per SM while the activation vector leaves room), each with the
+  // same share of the launch's stages; never more CTAs than items.
   const uint32_t per_sm = smem * 2 + 2048 <= 228u * 1024u ? 2u : 1u;
   const uint32_t cap = static_cast<uint32_t>(q36::sm_count_current_device()) * per_sm;
+  const uint32_t items = units * p.cpu;
   const uint32_t passes = (units + cap - 1) / cap;
   cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3((units + passes - 1) / passes);
-  cfg.blockDim = dim3(kThreads + 32);
+  cfg.gridDim = dim3(p.cpu == 1u ? (units + passes - 1) / passes : (items < cap ? items : cap));
+  cfg.blockDim = dim3(kBlock);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = q36::stream();
   cudaLaunchAttribute attr[1];

@@ -43,7 +43,9 @@ def bf16_bits(t: torch.Tensor) -> np.ndarray:
 
 
 def main() -> None:
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+    from oracle import oracle as orc
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else orc.reference_dir()
     ref = load_reference(ref_root)
     out = {}
 

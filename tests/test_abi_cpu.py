@@ -17,7 +17,7 @@ from speedoza_b200.build import build_library
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 HEADER = os.path.join(ROOT, "include", "qwen36_fp4_b200.h")
-REF_HEADER = "/root/reference/kernels-cuda/include/qwen36_fp4.h"
+REF_HEADER = os.path.join(orc.reference_dir(), "kernels-cuda", "include", "qwen36_fp4.h")
 
 
 @pytest.fixture(scope="module")
