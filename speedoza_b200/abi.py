@@ -313,6 +313,8 @@ def load() -> C.CDLL:
     lib.qwen36_nvfp4_matvec_force_quads.argtypes = [C.c_int]
     lib.qwen36_attention_flash_splitk_prefill_bf16.argtypes = [C.POINTER(AttentionPrefillSpec), C.c_int]
     lib.qwen36_attention_decode_split_tiled.argtypes = [C.POINTER(AttentionDecodeSpec), C.c_int, C.c_int]
+    lib.qwen36_lm_head_fp8_gemv_set_route.restype = None
+    lib.qwen36_lm_head_fp8_gemv_set_route.argtypes = [C.c_int]
     lib.qwen36_nvfp4_quantize_set_path.restype = None
     lib.qwen36_nvfp4_quantize_set_path.argtypes = [C.c_int]
     _lib = lib

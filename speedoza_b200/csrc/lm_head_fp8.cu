@@ -13,6 +13,8 @@
 // reference's and the greedy argmax picks the same token.
 #include "common.cuh"
 
+#include <atomic>
+
 #include <cooperative_groups.h>
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
@@ -83,6 +85,48 @@ template <int N, bool XF32> struct RowsPerWarp {
 // distinct bank groups.
 __device__ __forceinline__ uint32_t xswz(uint32_t chunk) { return chunk ^ ((chunk >> 3) & 1u); }
 
+// Tail of the fused variant: per-warp winners -> CTA winner -> `partials`; the last CTA to finish
+// (ticket counter) merges them, writes the tokens and re-zeroes the ticket.
+template <int N>
+__device__ __forceinline__ void fused_argmax_tail(const float (&best)[N], const uint32_t (&best_idx)[N], uint32_t warp,
+                                                  uint32_t lane, float2 *__restrict__ partials, unsigned *__restrict__ ticket,
+                                                  uint32_t *__restrict__ out_tokens, float *__restrict__ out_best) {
+    __shared__ float s_val[kWarps][N];
+    __shared__ uint32_t s_idx[kWarps][N];
+    __shared__ bool s_last;
+    if (lane == 0) {
+#pragma unroll
+      for (int t = 0; t < N; ++t) { s_val[warp][t] = best[t]; s_idx[warp][t] = best_idx[t]; }
+    }
+    __syncthreads();
+    if (threadIdx.x < N) {
+      float bv = s_val[0][threadIdx.x];
+      uint32_t bi = s_idx[0][threadIdx.x];
+      for (int w = 1; w < kWarps; ++w)
+        if (better(s_val[w][threadIdx.x], s_idx[w][threadIdx.x], bv, bi)) { bv = s_val[w][threadIdx.x]; bi = s_idx[w][threadIdx.x]; }
+      partials[static_cast<size_t>(blockIdx.x) * N + threadIdx.x] = make_float2(bv, __uint_as_float(bi));
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = atomicAdd(ticket, 1u) == gridDim.x - 1;
+    __syncthreads();
+    if (s_last) {
+      __threadfence();
+      if (threadIdx.x < N) {
+        float bv = -INFINITY;
+        uint32_t bi = 0u;
+        for (uint32_t b = 0; b < gridDim.x; ++b) {
+          const float2 p = __ldcg(partials + static_cast<size_t>(b) * N + threadIdx.x);
+          const uint32_t pi = __float_as_uint(p.y);
+          if (better(p.x, pi, bv, bi)) { bv = p.x; bi = pi; }
+        }
+        out_tokens[threadIdx.x] = bi;
+        if (out_best != nullptr) out_best[threadIdx.x] = bv;
+      }
+      if (threadIdx.x == 0) *ticket = 0u;      // ready for the next call
+    }
+}
+
 // FUSED = false: writes y[t * rows + row] (bf16).
 // FUSED = true : keeps the running (value, index) of the bf16-rounded logits
 //   per token; per-CTA winners go to `partials`, the last CTA to finish (ticket
@@ -93,7 +137,61 @@ __device__ __forceinline__ uint32_t xswz(uint32_t chunk) { return chunk ^ ((chun
 // many instructions as the FMAs themselves.
 __device__ __forceinline__ uint32_t xswz32(uint32_t chunk) { return chunk ^ ((chunk >> 3) & 7u); }
 
-template <int N, bool FUSED, bool XF32>
+// Can token t's activations go through the float16 route below without changing a bit of the
+// result?  Yes when they are all finite, the largest magnitude lies within 2^-100 .. 2^100 (no
+// float32 overflow or subnormal in either computation) and every nonzero value lies within 2^28 of
+// the largest (so that, times the power of two that lifts the largest into [2^14, 2^15), every
+// value is a normal float16: a bf16 value has 8 significant bits, a float16 has 11).  Every CTA
+// evaluates this on the same data and reaches the same verdict.  max_e[t] = biased exponent of the
+// token's largest magnitude (0 for an all-zero token).
+template <int N>
+__device__ __forceinline__ bool x_fits_f16(const __nv_bfloat16 *__restrict__ x, uint32_t cols, uint32_t (&max_e)[N]) {
+  __shared__ uint32_t s_max[N], s_min[N], s_bad;
+  if (threadIdx.x < N) { s_max[threadIdx.x] = 0u; s_min[threadIdx.x] = 255u; }
+  if (threadIdx.x == 0) s_bad = 0u;
+  __syncthreads();
+  const uint32_t chunks_per_tok = cols / 8u;
+  for (uint32_t t = 0; t < static_cast<uint32_t>(N); ++t) {
+    uint32_t mx = 0u, mn = 255u, bad = 0u;
+    for (uint32_t c = threadIdx.x; c < chunks_per_tok; c += kThreads) {
+      const uint4 v = __ldcg(reinterpret_cast<const uint4 *>(x) + t * chunks_per_tok + c);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const uint32_t bits = (w[i] >> (16 * h)) & 0x7fffu;
+          const uint32_t e = bits >> 7;
+          if (bits != 0u) {
+            if (e == 0u || e == 255u) bad = 1u;                // bf16 subnormal, infinity or NaN
+            mx = max(mx, e);
+            mn = min(mn, e);
+          }
+        }
+      }
+    }
+    mx = __reduce_max_sync(0xffffffffu, mx);
+    mn = __reduce_min_sync(0xffffffffu, mn);
+    bad = __reduce_or_sync(0xffffffffu, bad);
+    if ((threadIdx.x & 31u) == 0u) {
+      atomicMax(&s_max[t], mx);
+      atomicMin(&s_min[t], mn);
+      if (bad) atomicOr(&s_bad, 1u);
+    }
+  }
+  __syncthreads();
+  bool fit = s_bad == 0u;
+#pragma unroll
+  for (int t = 0; t < N; ++t) {
+    max_e[t] = s_max[t];
+    if (s_max[t] != 0u) fit = fit && s_max[t] >= 27u && s_max[t] <= 227u && s_max[t] - s_min[t] <= 28u;
+  }
+  return fit;
+}
+
+// UNFIT_ONLY: the launch that follows a float16-route launch on the same inputs; it returns at
+// once when that one did the work.
+template <int N, bool FUSED, bool XF32, bool UNFIT_ONLY = false>
 __global__ void __launch_bounds__(kThreads)
 lm_head_gemv_kernel(const uint8_t *__restrict__ weight, const float *__restrict__ row_scales,
                     const __nv_bfloat16 *__restrict__ x, __nv_bfloat16 *__restrict__ y, size_t rows,
@@ -105,6 +203,10 @@ lm_head_gemv_kernel(const uint8_t *__restrict__ weight, const float *__restrict_
   uint4 *xs = reinterpret_cast<uint4 *>(smem);        // N * cols bf16, swizzled chunks
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
   const uint32_t chunks_per_tok = cols / 8u;
+  if constexpr (UNFIT_ONLY) {
+    uint32_t unused[N];
+    if (x_fits_f16<N>(x, cols, unused)) return;
+  }
 
   if constexpr (XF32) {
     for (uint32_t c = threadIdx.x; c < N * chunks_per_tok; c += kThreads) {
@@ -211,42 +313,141 @@ lm_head_gemv_kernel(const uint8_t *__restrict__ weight, const float *__restrict_
     }
   }
 
-  if (FUSED) {
-    __shared__ float s_val[kWarps][N];
-    __shared__ uint32_t s_idx[kWarps][N];
-    __shared__ bool s_last;
-    if (lane == 0) {
+  if (FUSED) fused_argmax_tail<N>(best, best_idx, warp, lane, partials, ticket, out_tokens, out_best);
+}
+
+// Float16 route for 3..8 tokens.  The reference's sum for (row, token) is a float32 FMA chain per
+// lane over exact products e4m3 x bf16.  Here the token's activations are staged as float16 times
+// a power of two (exact, see x_fits_f16), the weights are expanded to float16 by the hardware
+// conversion (exact) and the chain runs on the mixed-precision fma.rn.f32.f16: the same products,
+// the same order, every partial sum the reference's times that power of two, which is divided out
+// at the end.  Per weight that is one conversion slot and one FMA per token, against a conversion,
+// an unpack and an FMA per token on the float32 route, and the staged vector is half the size.
+// A warp carries four rows (every activation load from shared memory serves all four) and keeps
+// kAhead 512-byte steps of each in flight: with one step ahead a warp cannot finish a step faster
+// than one loaded-memory latency, which is what bounded the float32 route at a few tokens (16 warps x
+// 4 rows x 512 B per microsecond and SM = 3.3 TB/s).  The step loop is unrolled over the buffers so
+// that no register that still waits for its load is ever copied.
+constexpr int kF16Rows = 4;
+template <int N, bool FUSED>
+__global__ void __launch_bounds__(kThreads, 2)
+lm_head_gemv_f16_kernel(const uint8_t *__restrict__ weight, const float *__restrict__ row_scales,
+                        const __nv_bfloat16 *__restrict__ x, __nv_bfloat16 *__restrict__ y, size_t rows,
+                        uint32_t cols, uint32_t row_offset, uint32_t *__restrict__ out_tokens,
+                        float *__restrict__ out_best, float2 *__restrict__ partials,
+                        unsigned *__restrict__ ticket) {
+  constexpr int R = kF16Rows;
+  constexpr int kAhead = N <= 4 ? 2 : 1, kBufs = kAhead + 1;
+  extern __shared__ __align__(16) uint8_t smem[];
+  uint4 *xs = reinterpret_cast<uint4 *>(smem);        // N * cols float16, swizzled 16-byte chunks
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+  const uint32_t chunks_per_tok = cols / 8u;
+  uint32_t max_e[N];
+  if (!x_fits_f16<N>(x, cols, max_e)) return;         // the float32 route, launched next, does the work
+  float unscale[N];
 #pragma unroll
-      for (int t = 0; t < N; ++t) { s_val[warp][t] = best[t]; s_idx[warp][t] = best_idx[t]; }
-    }
-    __syncthreads();
-    if (threadIdx.x < N) {
-      float bv = s_val[0][threadIdx.x];
-      uint32_t bi = s_idx[0][threadIdx.x];
-      for (int w = 1; w < kWarps; ++w)
-        if (better(s_val[w][threadIdx.x], s_idx[w][threadIdx.x], bv, bi)) { bv = s_val[w][threadIdx.x]; bi = s_idx[w][threadIdx.x]; }
-      partials[static_cast<size_t>(blockIdx.x) * N + threadIdx.x] = make_float2(bv, __uint_as_float(bi));
-    }
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) s_last = atomicAdd(ticket, 1u) == gridDim.x - 1;
-    __syncthreads();
-    if (s_last) {
-      __threadfence();
-      if (threadIdx.x < N) {
-        float bv = -INFINITY;
-        uint32_t bi = 0u;
-        for (uint32_t b = 0; b < gridDim.x; ++b) {
-          const float2 p = __ldcg(partials + static_cast<size_t>(b) * N + threadIdx.x);
-          const uint32_t pi = __float_as_uint(p.y);
-          if (better(p.x, pi, bv, bi)) { bv = p.x; bi = pi; }
-        }
-        out_tokens[threadIdx.x] = bi;
-        if (out_best != nullptr) out_best[threadIdx.x] = bv;
-      }
-      if (threadIdx.x == 0) *ticket = 0u;      // ready for the next call
+  for (int t = 0; t < N; ++t) {
+    const uint32_t e = max_e[t];
+    const float up = e == 0u ? 1.0f : __uint_as_float((268u - e) << 23);       // 2^(141 - e)
+    unscale[t] = e == 0u ? 1.0f : __uint_as_float((e - 14u) << 23);            // 2^(e - 141)
+    for (uint32_t c = threadIdx.x; c < chunks_per_tok; c += kThreads) {
+      const uint4 v = __ldcg(reinterpret_cast<const uint4 *>(x) + t * chunks_per_tok + c);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+      __half2 h[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        h[i] = __floats2half2_rn(__uint_as_float(w[i] << 16) * up, __uint_as_float(w[i] & 0xffff0000u) * up);
+      xs[xswz(t * chunks_per_tok + c)] = *reinterpret_cast<uint4 *>(h);
     }
   }
+  __syncthreads();
+
+  float best[N];
+  uint32_t best_idx[N];
+#pragma unroll
+  for (int t = 0; t < N; ++t) { best[t] = -INFINITY; best_idx[t] = 0u; }
+
+  const size_t warps_total = static_cast<size_t>(gridDim.x) * kWarps;
+  const uint32_t steps = cols / 512u;
+  const bool tail = lane * 16u + steps * 512u + 15u < cols;     // the reference loop's ragged last step
+  for (size_t row0 = (static_cast<size_t>(blockIdx.x) * kWarps + warp) * R; row0 < rows; row0 += warps_total * R) {
+    const int r_count = static_cast<int>(min(static_cast<size_t>(R), rows - row0));
+    float acc[R][N];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int t = 0; t < N; ++t) acc[r][t] = 0.f;
+    const uint8_t *w0 = weight + row0 * cols + lane * 16u;
+    uint4 buf[kBufs][R];
+    auto load = [&](uint4 (&dst)[R], uint32_t step) {
+#pragma unroll
+      for (int r = 0; r < R; ++r)
+        dst[r] = r < r_count ? __ldcs(reinterpret_cast<const uint4 *>(w0 + static_cast<size_t>(r) * cols + step * 512u))
+                             : make_uint4(0, 0, 0, 0);
+    };
+    auto multiply = [&](const uint4 (&cur)[R], uint32_t s) {
+      const uint32_t chunk0 = (lane * 16u + s * 512u) / 8u;        // first of two x chunks
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t wh[R][4];                                          // eight weights of each row as four f16x2
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          const uint32_t w_lo = half == 0 ? cur[r].x : cur[r].z;
+          const uint32_t w_hi = half == 0 ? cur[r].y : cur[r].w;
+          asm("{\n\t.reg .b16 a, b, c, d;\n\tmov.b32 {a, b}, %4;\n\tmov.b32 {c, d}, %5;\n\t"
+              "cvt.rn.f16x2.e4m3x2 %0, a;\n\tcvt.rn.f16x2.e4m3x2 %1, b;\n\t"
+              "cvt.rn.f16x2.e4m3x2 %2, c;\n\tcvt.rn.f16x2.e4m3x2 %3, d;\n\t}"
+              : "=r"(wh[r][0]), "=r"(wh[r][1]), "=r"(wh[r][2]), "=r"(wh[r][3]) : "r"(w_lo), "r"(w_hi));
+        }
+#pragma unroll
+        for (int t = 0; t < N; ++t) {
+          const uint4 xc = xs[xswz(t * chunks_per_tok + chunk0 + half)];
+          const uint32_t xw[4] = {xc.x, xc.y, xc.z, xc.w};
+#pragma unroll
+          for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              asm("{\n\t.reg .f16 wl, wu, xl, xu;\n\tmov.b32 {wl, wu}, %1;\n\tmov.b32 {xl, xu}, %2;\n\t"
+                  "fma.rn.f32.f16 %0, wl, xl, %0;\n\tfma.rn.f32.f16 %0, wu, xu, %0;\n\t}"
+                  : "+f"(acc[r][t]) : "r"(wh[r][i]), "r"(xw[i]));
+        }
+      }
+    };
+    const uint32_t my_steps = steps + (tail ? 1u : 0u);
+#pragma unroll
+    for (int a = 0; a < kAhead; ++a)
+      if (static_cast<uint32_t>(a) < my_steps) load(buf[a], a);
+    for (uint32_t s0 = 0; s0 < my_steps; s0 += kBufs) {
+#pragma unroll
+      for (int k = 0; k < kBufs; ++k) {
+        const uint32_t s = s0 + k;
+        if (s < my_steps) {
+          if (s + kAhead < my_steps) load(buf[(k + kAhead) % kBufs], s + kAhead);
+          multiply(buf[k], s);
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      if (r >= r_count) break;
+      const float scale = __ldg(row_scales + row0 + r);
+#pragma unroll
+      for (int t = 0; t < N; ++t) {
+        float v = acc[r][t];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+        const __nv_bfloat16 logit = __float2bfloat16(__fmul_rn(v * unscale[t], scale));
+        if (!FUSED) {
+          if (lane == 0) y[static_cast<size_t>(t) * rows + row0 + r] = logit;
+        } else {
+          const float lv = __bfloat162float(logit);
+          const uint32_t idx = static_cast<uint32_t>(row0 + r) + row_offset;
+          if (better(lv, idx, best[t], best_idx[t])) { best[t] = lv; best_idx[t] = idx; }
+        }
+      }
+    }
+  }
+  if (FUSED) fused_argmax_tail<N>(best, best_idx, warp, lane, partials, ticket, out_tokens, out_best);
 }
 
 // ------------------------------------------------------------------ argmax
@@ -360,13 +561,34 @@ int launch_gemv_x(const uint8_t *w, const float *scales, const __nv_bfloat16 *x,
   return q36::launch_status();
 }
 
+std::atomic<int> g_gemv_route{0};      // test hook: 1 = never take the float16 route
+
 template <int N, bool FUSED>
 int launch_gemv_n(const uint8_t *w, const float *scales, const __nv_bfloat16 *x, __nv_bfloat16 *y, size_t rows,
                   size_t cols, uint32_t row_offset, uint32_t *tokens, float *best, float2 *partials,
                   unsigned *ticket, unsigned grid) {
   if constexpr (N >= 3 && N <= 8) {
-    if (stage_f32(N, cols))
+    if (stage_f32(N, cols)) {
+      if (g_gemv_route.load() == 0 && cols % 512 == 0) {
+        // float16 route first; the float32 route right behind it runs only for activations the
+        // float16 route declines (both decide on the same data, on the device, so nothing is read back)
+        const size_t smem16 = static_cast<size_t>(N) * cols * 2;
+        if (q36::ensure_dynamic_smem(reinterpret_cast<const void *>(lm_head_gemv_f16_kernel<N, FUSED>), 200 * 1024) != cudaSuccess)
+          return QWEN36_STATUS_CUDA_ERROR;
+        const size_t need = q36::div_ceil(rows, static_cast<size_t>(kWarps) * kF16Rows);
+        const size_t cap = static_cast<size_t>(sm_count()) * 2;
+        lm_head_gemv_f16_kernel<N, FUSED><<<static_cast<unsigned>(need < cap ? need : cap), kThreads, smem16, q36::stream()>>>(
+            w, scales, x, y, rows, static_cast<uint32_t>(cols), row_offset, tokens, best, partials, ticket);
+        if (q36::launch_status() != QWEN36_STATUS_SUCCESS) return QWEN36_STATUS_CUDA_ERROR;
+        const size_t smem = static_cast<size_t>(N) * cols * 4;
+        if (q36::ensure_dynamic_smem(reinterpret_cast<const void *>(lm_head_gemv_kernel<N, FUSED, true, true>), 200 * 1024) != cudaSuccess)
+          return QWEN36_STATUS_CUDA_ERROR;
+        lm_head_gemv_kernel<N, FUSED, true, true><<<grid, kThreads, smem, q36::stream()>>>(
+            w, scales, x, y, rows, static_cast<uint32_t>(cols), row_offset, tokens, best, partials, ticket);
+        return q36::launch_status();
+      }
       return launch_gemv_x<N, FUSED, true>(w, scales, x, y, rows, cols, row_offset, tokens, best, partials, ticket, grid);
+    }
   }
   return launch_gemv_x<N, FUSED, false>(w, scales, x, y, rows, cols, row_offset, tokens, best, partials, ticket, grid);
 }
@@ -471,3 +693,7 @@ extern "C" int qwen36_sample_rows(const qwen36_sampling_rows_spec_t *spec) {
                        as_ptr<uint32_t>(spec->mirror_last_output_token_u32), spec->rows, spec->vocab_size,
                        spec->temperature);
 }
+
+// Test hook: 1 keeps 3..8-token calls on the float32-staged kernel alone, 0 restores the default
+// (float16 route with the float32 route behind it).
+extern "C" void qwen36_lm_head_fp8_gemv_set_route(int route) { g_gemv_route.store(route != 0 ? 1 : 0); }

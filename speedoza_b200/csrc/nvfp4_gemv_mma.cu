@@ -95,8 +95,8 @@ constexpr uint32_t kPeerEagerPolls = 2048;
 constexpr uint32_t kParkSpinLimit = 1u << 20;       // x (100 ns back-off + one round trip to L2): about a second
 
 __device__ unsigned int g_gemv_mma_error = 0;       // set when a bounded wait gives up
-constexpr uint32_t kPoolSets = 8, kScratchCells = 1u << 19, kTicketWords = 1u << 15;
-__device__ unsigned long long g_scratch[kPoolSets * kScratchCells];   // 32 MB, zero-initialised like every device global
+constexpr uint32_t kPoolSets = 16, kScratchCells = 1u << 19, kTicketWords = 1u << 15;
+__device__ unsigned long long g_scratch[kPoolSets * kScratchCells];   // 64 MB, zero-initialised like every device global
 __device__ uint32_t g_tickets[kPoolSets * kTicketWords];
 
 // Per-CTA %globaltimer stamps for pipeline analysis; compiled in only with -DQ36_GEMV_TRACE.
@@ -832,9 +832,10 @@ std::atomic<uint32_t> g_trace_id{0};
 #endif
 
 // Parking area for the partial sums of units cut along K, and the per-unit tickets.  A launch
-// touches its set only after the grid before it on the stream has completed, so launches of one
-// stream never meet in a set; launches of different streams take different sets as long as
-// fewer than kPoolSets of them are in flight at once.
+// touches its set only after the grid before it on its stream has completed, so the launches of
+// one stream can share a set; every stream that launches through this file gets a set of its own,
+// up to kPoolSets streams per process (further streams share by hash: callers that drive more
+// than kPoolSets streams at once through these entry points must serialise the surplus).
 struct ScratchSet {
   unsigned long long *scratch;
   uint32_t *tickets;
@@ -842,6 +843,8 @@ struct ScratchSet {
 };
 std::atomic<uint32_t> g_pool_seq{0};
 std::mutex g_pool_mu;
+cudaStream_t g_pool_streams[kPoolSets];
+uint32_t g_pool_streams_used = 0;
 unsigned long long *g_pool_scratch[64];
 uint32_t *g_pool_tickets[64];
 
@@ -857,8 +860,19 @@ bool scratch_for_launch(ScratchSet *out) {
       g_pool_tickets[dev] = static_cast<uint32_t *>(b);
     }
   }
+  const cudaStream_t stream = q36::stream();
+  uint32_t set = kPoolSets;
+  {
+    std::lock_guard<std::mutex> lock(g_pool_mu);
+    for (uint32_t i = 0; i < g_pool_streams_used; ++i)
+      if (g_pool_streams[i] == stream) set = i;
+    if (set == kPoolSets && g_pool_streams_used < kPoolSets) {
+      set = g_pool_streams_used++;
+      g_pool_streams[set] = stream;
+    }
+  }
+  if (set == kPoolSets) set = static_cast<uint32_t>((reinterpret_cast<uintptr_t>(stream) >> 4) % kPoolSets);
   const uint32_t seq = g_pool_seq.fetch_add(1u);
-  const uint32_t set = seq % kPoolSets;
   out->tag = seq % 0xfffffffeu + 1u;
   out->scratch = g_pool_scratch[dev] + static_cast<size_t>(set) * kScratchCells;
   out->tickets = g_pool_tickets[dev] + static_cast<size_t>(set) * kTicketWords;

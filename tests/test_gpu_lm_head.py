@@ -81,6 +81,49 @@ def test_fused_gemv_argmax_bit_exact(backend, rows, n):
     assert np.array_equal(unfused.astype(np.uint32), want)
 
 
+def wide_range_activations(rng, n, cols, kind):
+    """Token rows that the float16 route must take (a few octaves), must decline (values 2^40 apart, an
+    infinity, a bf16 subnormal) or that are all zero."""
+    x = rng.standard_normal((n, cols)).astype(np.float32)
+    if kind == "octaves":
+        x *= np.exp2(rng.integers(-12, 13, (n, cols))).astype(np.float32)
+        x *= np.exp2(rng.integers(-60, 60, (n, 1))).astype(np.float32)      # every token on its own scale
+    elif kind == "too_wide":
+        x[0, ::7] *= np.float32(2.0 ** 40)
+    elif kind == "infinity":
+        x[n - 1, 5] = np.inf
+    elif kind == "subnormal":
+        x[0, 3] = np.float32(2.0 ** -130)
+    elif kind == "zero_token":
+        x[1] = 0.0
+    elif kind == "huge":
+        x *= np.float32(2.0 ** 110)
+    return synth.f32_to_bf16_bits(x)
+
+
+@pytest.mark.parametrize("n", [3, 4, 5, 8])
+@pytest.mark.parametrize("kind", ["octaves", "too_wide", "infinity", "subnormal", "zero_token", "huge"])
+def test_float16_route_keeps_every_bit(backend, n, kind):
+    """3..8 tokens go through the float16-staged kernel when the activations allow it and through the
+    float32-staged one otherwise; both must give the oracle's logits and tokens bit for bit."""
+    rows, cols = 1500, 5120
+    rng = np.random.default_rng(n * 31 + len(kind))
+    w, s = synth.lm_head_weight(rng, rows, cols)
+    x = wide_range_activations(rng, n, cols, kind)
+    wd, sd, xd = to_dev(w), to_dev(s), to_dev(x)
+    want = orc.lm_head_fp8_gemv(w, s, x)
+    ws = backend.lm_head_argmax_workspace(rows, n, "cuda")
+    try:
+        for route in (0, 1):
+            backend.lib.qwen36_lm_head_fp8_gemv_set_route(route)
+            got = bf16_host(backend.lm_head_fp8_gemv(wd, sd, xd))
+            assert np.array_equal(got, want), f"route {route}"
+            tok, _ = backend.lm_head_fp8_gemv_argmax(wd, sd, xd, ws)
+            assert np.array_equal(tok.cpu().numpy().astype(np.uint32), orc.argmax_rows(want)), f"route {route}"
+    finally:
+        backend.lib.qwen36_lm_head_fp8_gemv_set_route(0)
+
+
 def test_lm_head_checksum_full_vocab(backend):
     """Full config-3 size (248320 x 5120, M = 4): fused argmax == unfused device argmax, and a
     sample of 2048 logits is bit-identical to the oracle (the oracle over the whole vocab is
