@@ -644,6 +644,248 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
 }
 
 // ============================================================================================
+// CTA-pair form with the scale tiles on a pipeline of their own.  The pair form above keeps five
+// 38 KB stages (operands + scale tiles) in flight, which a 2.7-3 us load round trip turns into a
+// stage every 0.56 us although the SM could take one in every 0.43 us.  Here the operand ring holds
+// six 32 KB stages, and the scale tiles (6 KB per stage) travel separately: a second producer
+// thread loads them into a five-slot shared-memory ring, the copier moves a slot into one of five
+// TMEM buffers as soon as that buffer's previous user has been multiplied, and frees the slot at
+// once.  So the scales run up to ten stages ahead of the MMAs without holding operand space,
+// and while an accumulator drains the operand ring fills up, which lets the MMA warp make up part
+// of the bubble at its own rate afterwards.
+// ============================================================================================
+namespace pair6 {
+constexpr uint32_t kBN = 256, kHalfTok = 128;
+constexpr uint32_t kABytes = kBM * kBKBytes, kBBytes = kHalfTok * kBKBytes;   // 16384 each
+constexpr uint32_t kAbStage = kABytes + kBBytes;                              // 32768
+constexpr uint32_t kAbStages = 6;
+constexpr uint32_t kSfaBytes = 2048, kSfbBytes = 4096, kSfSlot = kSfaBytes + kSfbBytes;
+constexpr uint32_t kSfSlots = 5, kSfBufs = 5, kSfCols = 16 + 32;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kSmemBytes = 1024 + 1024 + kAbStages * kAbStage + kSfSlots * kSfSlot;
+constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | ((kBN >> 3) << 17) | ((256u >> 4) << 24);
+static_assert(256 + kSfBufs * kSfCols <= kTmemCols, "TMEM budget");
+static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
+}  // namespace pair6
+
+__global__ void __launch_bounds__(kThreads, 1)
+nvfp4_gemm_pair6_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                        const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
+                        __nv_bfloat16 *__restrict__ c, uint32_t m, uint32_t n, uint32_t k, float alpha) {
+  namespace P = pair6;
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint64_t *ab_full = reinterpret_cast<uint64_t *>(smem);                // [6]  used in the leader
+  uint64_t *ab_empty = ab_full + 8;                                      // [6]  one per CTA
+  uint64_t *sfs_full = ab_empty + 8;                                     // [5]  used in the leader
+  uint64_t *sfs_empty = sfs_full + 8;                                    // [5]  one per CTA
+  uint64_t *sft_ready = sfs_empty + 8;                                   // [5]  used in the leader
+  uint64_t *sft_free = sft_ready + 8;                                    // [5]  used in the leader
+  uint64_t *acc_full = sft_free + 8;                                     // one per CTA
+  uint64_t *acc_empty = acc_full + 2;                                    // used in the leader: 8 epilogue warps x 2 CTAs
+  uint32_t *tmem_base_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
+  uint8_t *ab = smem + 1024;
+  uint8_t *sfs = ab + P::kAbStages * P::kAbStage;
+
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+  const uint32_t rank = cluster_rank() & 1u;
+  const bool leader = rank == 0u;
+  const uint32_t pair_id = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const uint32_t m_blocks = m / 256u, n_blocks = (n + P::kBN - 1) / P::kBN;
+  const uint32_t tiles = m_blocks * n_blocks;
+  const uint32_t k_blocks = k / 256u;
+  const uint32_t sf_tiles_per_block = k / 64u;                           // 512-byte tiles per 128 rows
+
+  if (threadIdx.x == 0) {
+    for (uint32_t s = 0; s < P::kAbStages; ++s) { mbar_init(&ab_full[s], 1); mbar_init(&ab_empty[s], 1); }
+    for (uint32_t s = 0; s < P::kSfSlots; ++s) { mbar_init(&sfs_full[s], 1); mbar_init(&sfs_empty[s], 1); }
+    for (uint32_t s = 0; s < P::kSfBufs; ++s) { mbar_init(&sft_ready[s], 1); mbar_init(&sft_free[s], 1); }
+    mbar_init(&acc_full[0], 1);
+    mbar_init(&acc_empty[0], 16);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_base_slot)), "r"(P::kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();                       // both CTAs' barriers exist before anything crosses over
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_base_slot;
+  const uint32_t tmem_sf = tmem_base + 256u;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- operand producer (both CTAs)
+    if (lane == 0) {
+      uint32_t g = 0;
+      bool dead = false;
+      for (uint32_t tile = pair_id; tile < tiles && !dead; tile += n_pairs) {
+        const uint32_t nb = tile % n_blocks, mb = tile / n_blocks;
+        const uint32_t row_block = mb * 2u + rank;                       // this CTA's 128 weight rows
+        for (uint32_t kb = 0; kb < k_blocks; ++kb, ++g) {
+          const uint32_t s = g % P::kAbStages, ph = (g / P::kAbStages) & 1u;
+          if (!mbar_wait(&ab_empty[s], ph ^ 1u)) { dead = true; break; }
+          if (leader) Q36_GTRACE(g, 0);
+          uint8_t *st = ab + s * P::kAbStage;
+          const uint32_t bar = map_to_cta(smem_u32(&ab_full[s]), 0u);    // the leader's barrier counts both CTAs' bytes
+          if (leader) mbar_expect_tx(&ab_full[s], 2u * P::kAbStage);
+          tma_load_2d_pair(st, &map_a, kb * kBKBytes, row_block * kBM, bar);
+          // token blocks past the end of the activation tensor lie outside the map and arrive as zeros
+          tma_load_2d_pair(st + P::kABytes, &map_b, kb * kBKBytes, nb * P::kBN + rank * P::kHalfTok, bar);
+          if (leader) Q36_GTRACE(g, 1);
+        }
+      }
+    } else if (lane == 1) {
+      // -------------------------------------------------------------- scale-tile producer (both CTAs): the other
+      // side of the same branch, so that the two lanes run their loops side by side
+      uint32_t g = 0;
+      bool dead = false;
+      for (uint32_t tile = pair_id; tile < tiles && !dead; tile += n_pairs) {
+        const uint32_t nb = tile % n_blocks, mb = tile / n_blocks;
+        const uint32_t row_block = mb * 2u + rank;
+        for (uint32_t kb = 0; kb < k_blocks; ++kb, ++g) {
+          const uint32_t s = g % P::kSfSlots, ph = (g / P::kSfSlots) & 1u;
+          if (!mbar_wait(&sfs_empty[s], ph ^ 1u)) { dead = true; break; }
+          uint8_t *st = sfs + s * P::kSfSlot;
+          const uint32_t bar = map_to_cta(smem_u32(&sfs_full[s]), 0u);
+          if (leader) mbar_expect_tx(&sfs_full[s], 2u * P::kSfSlot);
+          tma_load_2d_pair(st, &map_sfa, 0u, row_block * sf_tiles_per_block + kb * 4u, bar);
+#pragma unroll
+          for (uint32_t t = 0; t < 2; ++t)
+            tma_load_2d_pair(st + P::kSfaBytes + t * 2048u, &map_sfb, 0u, (nb * 2u + t) * sf_tiles_per_block + kb * 4u, bar);
+        }
+      }
+    }
+  } else if (warp == kWarpCopier || warp == 3u) {
+    // ---------------------------------------------------------------- scale copiers (leader only)
+    // Twelve tcgen05.cp per stage take one thread longer to issue than a stage may last, so two
+    // threads (warps 2 and 3) take alternate stages.
+    if (leader && lane == 0) {
+      const uint32_t mine = warp == 3u ? 1u : 0u;
+      uint32_t g = 0;
+      bool dead = false;
+      for (uint32_t tile = pair_id; tile < tiles && !dead; tile += n_pairs) {
+        for (uint32_t kb = 0; kb < k_blocks; ++kb, ++g) {
+          if ((g & 1u) != mine) continue;
+          const uint32_t s = g % P::kSfSlots, phs = (g / P::kSfSlots) & 1u;
+          const uint32_t b = g % P::kSfBufs, phb = (g / P::kSfBufs) & 1u;
+          if (!mbar_wait(&sfs_full[s], phs)) { dead = true; break; }
+          Q36_GTRACE(g, 2);
+          // The TMEM buffer is free once the MMAs of stage g - 5 are done, which is what frees that
+          // stage's operand slot too: the copier watches the same barrier as the operand producer
+          // (the MMA thread issues one commit per stage, not two: it is the issue-bound one).  The
+          // barrier cannot be more than that one phase ahead, since the MMAs of stage g + 1 need this copy.
+          if (g >= P::kSfBufs) {
+            const uint32_t gp = g - P::kSfBufs;
+            if (!mbar_wait(&ab_empty[gp % P::kAbStages], (gp / P::kAbStages) & 1u)) { dead = true; break; }
+          }
+          (void)phb;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t st = smem_u32(sfs + s * P::kSfSlot);
+          const uint32_t sfa_t = tmem_sf + b * P::kSfCols, sfb_t = sfa_t + 16u;
+#pragma unroll
+          for (uint32_t kk = 0; kk < 4; ++kk) {
+            tmem_cp_sf_pair(sfa_t + kk * 4u, desc_sf(st + kk * 512u));
+#pragma unroll
+            for (uint32_t t = 0; t < 2; ++t)
+              tmem_cp_sf_pair(sfb_t + (kk * 2u + t) * 4u, desc_sf(st + P::kSfaBytes + t * 2048u + kk * 512u));
+          }
+          mma_commit_pair(&sft_ready[b]);                    // scales of this stage are in both TMEMs
+          mma_commit_pair_fanout(&sfs_empty[s], 3);          // and the slot is free again in both CTAs
+          Q36_GTRACE(g, 3);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer (leader only)
+    if (leader && lane == 0) {
+      uint32_t g = 0, t_local = 0;
+      bool dead = false;
+      for (uint32_t tile = pair_id; tile < tiles && !dead; tile += n_pairs, ++t_local) {
+        if (!mbar_wait(&acc_empty[0], (t_local & 1u) ^ 1u)) { dead = true; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        for (uint32_t kb = 0; kb < k_blocks; ++kb, ++g) {
+          const uint32_t s = g % P::kAbStages, ph = (g / P::kAbStages) & 1u;
+          const uint32_t b = g % P::kSfBufs, phb = (g / P::kSfBufs) & 1u;
+          if (!mbar_wait(&ab_full[s], ph)) { dead = true; break; }
+          Q36_GTRACE(g, 4);
+          if (!mbar_wait(&sft_ready[b], phb)) { dead = true; break; }
+          Q36_GTRACE(g, 5);
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t st = smem_u32(ab + s * P::kAbStage);
+          const uint32_t sfa_t = tmem_sf + b * P::kSfCols, sfb_t = sfa_t + 16u;
+#pragma unroll
+          for (uint32_t kk = 0; kk < 4; ++kk)
+            mma_mxf4nvf4_pair(tmem_base, desc_sw128(st + kk * 32u), desc_sw128(st + P::kABytes + kk * 32u), P::kIdesc,
+                              sfa_t + kk * 4u, sfb_t + kk * 8u, (kb | kk) != 0u);
+          mma_commit_pair_fanout(&ab_empty[s], 3);           // frees the operand stage in both CTAs (and, for the copier, the scale buffer)
+          Q36_GTRACE(g, 6);
+        }
+        if (!dead) mma_commit_pair_fanout(&acc_full[0], 3);  // accumulator complete, in both CTAs
+      }
+    }
+  } else if (warp >= kWarpEpilogue) {
+    // ---------------------------------------------------------------- epilogue warps 4..11 (both CTAs)
+    const uint32_t quarter = warp & 3u;           // TMEM lanes [32*quarter, +32) are this warp's
+    const uint32_t col0 = ((warp - kWarpEpilogue) >> 2) * (P::kBN / 2u);   // this warp's half of the columns
+    const uint32_t acc_empty_leader = map_to_cta(smem_u32(&acc_empty[0]), 0u);
+    uint32_t t_local = 0;
+    for (uint32_t tile = pair_id; tile < tiles; tile += n_pairs, ++t_local) {
+      const uint32_t nb = tile % n_blocks, mb = tile / n_blocks;
+      if (!mbar_wait(&acc_full[0], t_local & 1u)) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t row = (mb * 2u + rank) * kBM + quarter * 32u + lane;     // feature index
+      const uint32_t taddr = tmem_base + col0 + ((quarter * 32u) << 16);
+      const uint32_t tok0 = nb * P::kBN + col0;
+      // All four loads of the warp's 128 columns go out before the one wait, and the accumulator is
+      // handed back before anything is converted: the time the MMA warp stands still per tile is the
+      // commit, one TMEM read and this arrival, nothing else.
+      uint32_t r0[32], r1[32], r2[32], r3[32];
+      tmem_ld32(taddr, r0);
+      tmem_ld32(taddr + 32u, r1);
+      tmem_ld32(taddr + 64u, r2);
+      tmem_ld32(taddr + 96u, r3);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
+      uint32_t packed[P::kBN / 4];
+#pragma unroll
+      for (uint32_t j = 0; j < 32; j += 2) {
+        const __nv_bfloat162 v0 = __floats2bfloat162_rn(__uint_as_float(r0[j]) * alpha, __uint_as_float(r0[j + 1]) * alpha);
+        const __nv_bfloat162 v1 = __floats2bfloat162_rn(__uint_as_float(r1[j]) * alpha, __uint_as_float(r1[j + 1]) * alpha);
+        const __nv_bfloat162 v2 = __floats2bfloat162_rn(__uint_as_float(r2[j]) * alpha, __uint_as_float(r2[j + 1]) * alpha);
+        const __nv_bfloat162 v3 = __floats2bfloat162_rn(__uint_as_float(r3[j]) * alpha, __uint_as_float(r3[j + 1]) * alpha);
+        packed[j / 2] = *reinterpret_cast<const uint32_t *>(&v0);
+        packed[16 + j / 2] = *reinterpret_cast<const uint32_t *>(&v1);
+        packed[32 + j / 2] = *reinterpret_cast<const uint32_t *>(&v2);
+        packed[48 + j / 2] = *reinterpret_cast<const uint32_t *>(&v3);
+      }
+      const bool odd = (lane & 1u) != 0u;
+      __nv_bfloat16 *crow = c + (row & ~1u);
+#pragma unroll
+      for (uint32_t j = 0; j < P::kBN / 4; ++j) {
+        const uint32_t got = __shfl_xor_sync(0xffffffffu, packed[j], 1);
+        const uint32_t v = odd ? __byte_perm(got, packed[j], 0x7632) : __byte_perm(packed[j], got, 0x5410);
+        const uint32_t tok = tok0 + 2u * j + (odd ? 1u : 0u);
+        if (tok < n) *reinterpret_cast<uint32_t *>(crow + static_cast<size_t>(tok) * m) = v;
+      }
+    }
+  }
+
+  // Common exit: the pair meets (nobody may still read the other's shared or tensor memory),
+  // then both allocating warps release TMEM.
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(P::kTmemCols) : "memory");
+  }
+}
+
+// ============================================================================================
 // Split-K form for few tokens and few row blocks (decode: n <= 8, the k / v / o / down
 // projections have only 8 or 40 row blocks, far fewer than SMs).  A cluster of S CTAs shares one
 // 128-row x BN-token tile; CTA r streams K-blocks [r * kb / S, (r + 1) * kb / S) through the same
@@ -907,6 +1149,49 @@ int launch_pair(const qwen36_nvfp4_gemm_spec_t *s, float alpha) {
                                              static_cast<uint32_t>(s->n), static_cast<uint32_t>(s->k), alpha));
 }
 
+int launch_pair6(const qwen36_nvfp4_gemm_spec_t *s, float alpha) {
+  namespace P = pair6;
+  CUtensorMap map_a, map_b, map_sfa, map_sfb;
+  const uint64_t sf_tiles = s->k / 64;
+  if (!make_operand_map(&map_a, s->a_fp4.ptr, s->m, s->k, kBM) ||
+      !make_operand_map(&map_b, s->b_fp4.ptr, s->n, s->k, P::kHalfTok) ||
+      !make_scale_map(&map_sfa, s->a_scale.ptr, (s->m / 128) * sf_tiles) ||
+      !make_scale_map(&map_sfb, s->b_scale.ptr, ((s->n + 127) / 128) * sf_tiles))
+    return QWEN36_STATUS_NOT_IMPLEMENTED;
+  if (q36::ensure_dynamic_smem(reinterpret_cast<const void *>(nvfp4_gemm_pair6_kernel), static_cast<int>(P::kSmemBytes)) !=
+      cudaSuccess)
+    return QWEN36_STATUS_CUDA_ERROR;
+  const uint32_t tiles = static_cast<uint32_t>((s->m / 256) * ((s->n + P::kBN - 1) / P::kBN));
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<uint32_t>(sm_count()) & ~1u);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = P::kSmemBytes;
+  cfg.stream = q36::stream();
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  // The grid is persistent with a static tile stride, so it must never exceed the number of
+  // pairs the device can host at the same time (some SMs may have no free partner).
+  static int max_pairs = [&] {
+    int v = 0;
+    if (cudaOccupancyMaxActiveClusters(&v, nvfp4_gemm_pair6_kernel, &cfg) != cudaSuccess) {
+      (void)cudaGetLastError();
+      v = 0;
+    }
+    return v;
+  }();
+  if (max_pairs <= 0) return QWEN36_STATUS_NOT_IMPLEMENTED;
+  const uint32_t pairs = tiles < static_cast<uint32_t>(max_pairs) ? tiles : static_cast<uint32_t>(max_pairs);
+  cfg.gridDim = dim3(pairs * 2u);
+  return q36::cuda_status(cudaLaunchKernelEx(&cfg, nvfp4_gemm_pair6_kernel, map_a, map_b, map_sfa, map_sfb,
+                                             as_ptr<__nv_bfloat16>(s->c_bf16), static_cast<uint32_t>(s->m),
+                                             static_cast<uint32_t>(s->n), static_cast<uint32_t>(s->k), alpha));
+}
+
 // Split-K launch: `split` CTAs per 128-row block (cluster), one token block (n <= BN).
 template <uint32_t BN>
 int launch_splitk(const qwen36_nvfp4_gemm_spec_t *s, float alpha, uint32_t split) {
@@ -962,6 +1247,13 @@ int nvfp4_gemm_tc(const qwen36_nvfp4_gemm_spec_t *s, float alpha) {
   if (forced == 128 && s->n > 128) return launch<128>(s, alpha);
   // CTA pairs (256 x 256 tiles): measured ahead of single-CTA tiles only for long K with many
   // tokens (+5 % at k = 17408, n = 8192; level or slightly behind elsewhere).
+  // CTA pairs with six operand stages and a separate scale pipeline: ahead of every other form from
+  // 512 tokens up (gate_up 34816 x 5120: 56 / 178 / 673 us at 512 / 2048 / 8192 tokens against 58 / 187 / 724;
+  // down 5120 x 17408: 44 / 114 / 336 against 48 / 128 / 373).
+  if (s->n > 128 && s->m % 256 == 0 && (forced == 768 || (forced == 0 && s->n >= 512))) {
+    const int rc = launch_pair6(s, alpha);
+    if (rc != QWEN36_STATUS_NOT_IMPLEMENTED) return rc;      // pairs unavailable: the older forms below
+  }
   if (s->n > 128 && s->m % 256 == 0 && (forced == 512 || (forced == 0 && s->k >= 8192 && s->n >= 4096))) {
     const int rc = launch_pair(s, alpha);
     if (rc != QWEN36_STATUS_NOT_IMPLEMENTED) return rc;      // pairs unavailable: single-CTA tiles below
@@ -979,7 +1271,8 @@ int nvfp4_gemm_tc(const qwen36_nvfp4_gemm_spec_t *s, float alpha) {
 }
 
 // Tuning hook: 128 forces 128-token tiles (two accumulator stages) for large n, 256 single-CTA
-// 256-token tiles, 512 CTA pairs (where the shape allows them); 0 = default.
+// 256-token tiles, 512 CTA pairs with five combined stages, 768 CTA pairs with six operand stages
+// and the separate scale pipeline (where the shape allows pairs); 0 = default.
 extern "C" void qwen36_nvfp4_gemm_force_bn(int bn) { g_force_bn.store(bn); }
 // Tuning hook: CTAs per row block of the split-K form for n <= 16 (1 = never split, 0 = heuristic).
 extern "C" void qwen36_nvfp4_gemm_force_split(int split) { g_force_split.store(split); }

@@ -355,18 +355,20 @@ def test_w4a4_gemm_vs_oracle(backend, m, n, k):
     assert err <= 1e-2, err
 
 
-@pytest.mark.parametrize("m,n,k", [(256, 130, 512), (512, 300, 1024), (384, 257, 768), (256, 1000, 8192)])
+@pytest.mark.parametrize("m,n,k", [(256, 130, 512), (512, 300, 1024), (384, 257, 768), (256, 1000, 8192),
+                                   (1024, 640, 2560)])
 def test_w4a4_gemm_tile_variants(backend, m, n, k):
     """Every tile form of the tcgen05 kernel (128- and 256-token single-CTA tiles, 256 x 256 CTA
-    pairs; the pair form steps aside when m is not a multiple of 256) gives the oracle's result,
-    and all forms agree bit for bit: they accumulate K in the same order."""
+    pairs with five combined stages, and with six operand stages + the scale tiles on a pipeline of
+    their own; the pair forms step aside when m is not a multiple of 256) gives the oracle's
+    result, and all forms agree bit for bit: they accumulate K in the same order."""
     rng = np.random.default_rng(7 * m + n + k)
     a, a_sf, x, b, b_sf, alpha = w4a4_case(rng, m, n, k)
     want = synth.bf16_bits_to_f32(orc.nvfp4_gemm(a, a_sf, b, b_sf, alpha, m, n, k))
     dev = [to_dev(t) for t in (a, a_sf, b, b_sf)]
     outs = []
     try:
-        for tile in (0, 128, 256, 512):
+        for tile in (0, 128, 256, 512, 768):
             backend.lib.qwen36_nvfp4_gemm_force_bn(tile)
             got = bf16_host(backend.nvfp4_gemm(*dev, alpha, m, n, k))
             assert rel_l2(synth.bf16_bits_to_f32(got), want) <= 1e-2, tile
