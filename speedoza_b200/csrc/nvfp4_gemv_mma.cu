@@ -125,8 +125,7 @@ struct GemvParams {
   const uint8_t *x_sf;                   // W4A4: tiled UE4M3 scales of the activation row
   uint32_t K, iters, units, count;
   uint32_t chunk, cpu;                   // stages per K-chunk, chunks per unit
-  unsigned long long *scratch;           // [units][cpu][32] parked partial sums of units cut along K: (float, launch tag)
-  uint32_t *tickets;                     // [units] chunks of a unit that have been parked (self-resetting)
+  uint32_t set;                          // which parking set of g_scratch / g_tickets this launch uses
   uint32_t tag;                          // nonzero, differs between launches that may meet in one scratch set
   float alpha;                           // W4A4
   // tensor-parallel form only
@@ -407,6 +406,9 @@ nvfp4_gemv_mma_kernel(const __grid_constant__ GemvParams p) {
 #pragma unroll
       for (uint32_t w = 0; w < static_cast<uint32_t>(kWarps); ++w) poisoned |= peer_fail[w] != 0u;
     }
+    // [units][cpu][32] parked partial sums of units cut along K, (float, launch tag) per cell; [units] tickets
+    unsigned long long *const scratch = g_scratch + static_cast<size_t>(p.set) * kScratchCells;
+    uint32_t *const tickets = g_tickets + static_cast<size_t>(p.set) * kTicketWords;
     float gscale[kMaxMats];
 #pragma unroll
     for (uint32_t i = 0; i < kMaxMats; ++i)
@@ -442,7 +444,7 @@ nvfp4_gemv_mma_kernel(const __grid_constant__ GemvParams p) {
     // for the next launch that gets this scratch set.  The ticket is taken one item ahead, so its
     // round trip to L2 runs under the wait for the item's sums.
     auto add_up = [&](const Item &t, float own) {
-      unsigned long long *parked = p.scratch + static_cast<size_t>(t.unit) * p.cpu * 32u + lane;
+      unsigned long long *parked = scratch + static_cast<size_t>(t.unit) * p.cpu * 32u + lane;
       float v = 0.f;
       for (uint32_t k0 = 0; k0 < p.cpu; k0 += 4u) {
         unsigned long long cell[4] = {0ull, 0ull, 0ull, 0ull};
@@ -467,11 +469,11 @@ nvfp4_gemv_mma_kernel(const __grid_constant__ GemvParams p) {
           parked[(k0 + i) * 32u] = 0ull;
         }
       }
-      if (lane == 0) p.tickets[t.unit] = 0;                   // ready for the next launch that gets this scratch
+      if (lane == 0) tickets[t.unit] = 0;                   // ready for the next launch that gets this scratch
       write_rows(t, v);
     };
     uint32_t next_ticket = 0;
-    if (p.cpu > 1u && j_begin < j_end && lane == 0) next_ticket = atomicAdd(p.tickets + j_begin % p.units, 1u);
+    if (p.cpu > 1u && j_begin < j_end && lane == 0) next_ticket = atomicAdd(tickets + j_begin % p.units, 1u);
     uint32_t n_local = 0;
     for (uint32_t j = j_begin; j < j_end; j += j_step, ++n_local) {
       const Item t = decode_item(p, j);
@@ -489,12 +491,12 @@ nvfp4_gemv_mma_kernel(const __grid_constant__ GemvParams p) {
         write_rows(t, v);
         continue;
       }
-      if (j + 1u < j_end && lane == 0) next_ticket = atomicAdd(p.tickets + (j + 1u) % p.units, 1u);
+      if (j + 1u < j_end && lane == 0) next_ticket = atomicAdd(tickets + (j + 1u) % p.units, 1u);
       if (__shfl_sync(0xffffffffu, ticket, 0) == p.cpu - 1u) {
         add_up(t, v);
       } else {
         const unsigned long long cell = (static_cast<unsigned long long>(p.tag) << 32) | __float_as_uint(v);
-        asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p.scratch + (static_cast<size_t>(t.unit) * p.cpu + t.kc) * 32u + lane), "l"(cell) : "memory");
+        asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(scratch + (static_cast<size_t>(t.unit) * p.cpu + t.kc) * 32u + lane), "l"(cell) : "memory");
       }
     }
     if (threadIdx.x == kWarpEpilogue * 32u) Q36_TRACE(7);
@@ -837,29 +839,16 @@ std::atomic<uint32_t> g_trace_id{0};
 // up to kPoolSets streams per process (further streams share by hash: callers that drive more
 // than kPoolSets streams at once through these entry points must serialise the surplus).
 struct ScratchSet {
-  unsigned long long *scratch;
-  uint32_t *tickets;
-  uint32_t tag;
+  uint32_t set, tag;
 };
 std::atomic<uint32_t> g_pool_seq{0};
 std::mutex g_pool_mu;
 cudaStream_t g_pool_streams[kPoolSets];
 uint32_t g_pool_streams_used = 0;
-unsigned long long *g_pool_scratch[64];
-uint32_t *g_pool_tickets[64];
 
-bool scratch_for_launch(ScratchSet *out) {
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
-  {
-    std::lock_guard<std::mutex> lock(g_pool_mu);
-    if (g_pool_scratch[dev] == nullptr) {
-      void *a = nullptr, *b = nullptr;
-      if (cudaGetSymbolAddress(&a, g_scratch) != cudaSuccess || cudaGetSymbolAddress(&b, g_tickets) != cudaSuccess) return false;
-      g_pool_scratch[dev] = static_cast<unsigned long long *>(a);
-      g_pool_tickets[dev] = static_cast<uint32_t *>(b);
-    }
-  }
+// The kernel addresses the sets itself (they are device globals), so nothing here touches the device:
+// safe inside a stream capture, also as the first call of a process.
+void scratch_for_launch(ScratchSet *out) {
   const cudaStream_t stream = q36::stream();
   uint32_t set = kPoolSets;
   {
@@ -872,11 +861,8 @@ bool scratch_for_launch(ScratchSet *out) {
     }
   }
   if (set == kPoolSets) set = static_cast<uint32_t>((reinterpret_cast<uintptr_t>(stream) >> 4) % kPoolSets);
-  const uint32_t seq = g_pool_seq.fetch_add(1u);
-  out->tag = seq % 0xfffffffeu + 1u;
-  out->scratch = g_pool_scratch[dev] + static_cast<size_t>(set) * kScratchCells;
-  out->tickets = g_pool_tickets[dev] + static_cast<size_t>(set) * kTicketWords;
-  return true;
+  out->set = set;
+  out->tag = g_pool_seq.fetch_add(1u) % 0xfffffffeu + 1u;
 }
 
 struct Mat {
@@ -934,12 +920,12 @@ int launch(const Mat *mats, uint32_t count, uint64_t K, const void *x, const uin
   p.cpu = (p.iters + p.chunk - 1u) / p.chunk;
   if (p.cpu > 1u) {
     ScratchSet set;
-    if (static_cast<size_t>(units) * p.cpu * 32u > kScratchCells || units > kTicketWords || !scratch_for_launch(&set)) {
+    if (static_cast<size_t>(units) * p.cpu * 32u > kScratchCells || units > kTicketWords) {
       p.cpu = 1u;                          // too tall for the parking area: whole units, one CTA each
       p.chunk = p.iters;
     } else {
-      p.scratch = set.scratch;
-      p.tickets = set.tickets;
+      scratch_for_launch(&set);
+      p.set = set.set;
       p.tag = set.tag;
     }
   }
