@@ -29,6 +29,8 @@
 #include <atomic>
 #include <cuda.h>
 #include <mutex>
+#include <tuple>
+#include <vector>
 
 namespace q36 {
 namespace {
@@ -1060,9 +1062,42 @@ EncodeFn encode_fn() {
 }
 
 // Packed fp4 bytes [rows][k/2] -> 2-D map, box = 128 bytes x box_rows, 128-byte swizzle.
-bool make_operand_map(CUtensorMap *map, uint64_t ptr, uint64_t rows, uint64_t k, uint32_t box_rows) {
+// A tensor map depends only on (pointer, extents, box): weights and activation buffers come back
+// with the same few hundred combinations on every step, so the encoded maps are kept in a small
+// direct-mapped cache instead of being rebuilt by the driver on every launch (a cost only eager
+// callers see; a replayed graph holds the maps).
+struct MapKey {
+  uint64_t ptr = 0, rows = 0, k = 0;
+  uint32_t box = 0, kind = 0;          // kind 1 = operand map, 2 = scale map
+  bool operator==(const MapKey &o) const { return ptr == o.ptr && rows == o.rows && k == o.k && box == o.box && kind == o.kind; }
+};
+struct MapSlot {
+  MapKey key;
+  CUtensorMap map;
+};
+constexpr size_t kMapSlots = 512;
+std::mutex g_map_mu;
+MapSlot g_map_slots[kMapSlots];
+
+bool cached_map(const MapKey &key, CUtensorMap *out, bool (*build)(CUtensorMap *, const MapKey &)) {
+  const uint64_t h = ((key.ptr >> 8) * 0x9E3779B97F4A7C15ull) ^ (key.rows * 31u + key.k * 7u + key.box + key.kind);
+  MapSlot &slot = g_map_slots[(h >> 24) % kMapSlots];
+  {
+    std::lock_guard<std::mutex> lock(g_map_mu);
+    if (slot.key == key) { *out = slot.map; return true; }
+  }
+  if (!build(out, key)) return false;
+  std::lock_guard<std::mutex> lock(g_map_mu);
+  slot.key = key;
+  slot.map = *out;
+  return true;
+}
+
+bool build_operand_map(CUtensorMap *map, const MapKey &key) {
   EncodeFn enc = encode_fn();
   if (enc == nullptr) return false;
+  const uint64_t ptr = key.ptr, rows = key.rows, k = key.k;
+  const uint32_t box_rows = key.box;
   const cuuint64_t dims[2] = {k / 2, rows};
   const cuuint64_t strides[1] = {k / 2};
   const cuuint32_t box[2] = {kBKBytes, box_rows};
@@ -1070,6 +1105,12 @@ bool make_operand_map(CUtensorMap *map, uint64_t ptr, uint64_t rows, uint64_t k,
   return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, reinterpret_cast<void *>(ptr), dims, strides, box, ones,
              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool make_operand_map(CUtensorMap *map, uint64_t ptr, uint64_t rows, uint64_t k, uint32_t box_rows) {
+  MapKey key;
+  key.ptr = ptr; key.rows = rows; key.k = k; key.box = box_rows; key.kind = 1;
+  return cached_map(key, map, build_operand_map);
 }
 
 int sm_count() { return q36::sm_count_current_device(); }
@@ -1094,9 +1135,10 @@ int launch(const qwen36_nvfp4_gemm_spec_t *s, float alpha) {
 }
 
 // Tiled scale buffer as uint32 [tiles][128]: one 512-byte scale tile per row, box = four tiles (one 256-K stage).
-bool make_scale_map(CUtensorMap *map, uint64_t ptr, uint64_t tiles) {
+bool build_scale_map(CUtensorMap *map, const MapKey &key) {
   EncodeFn enc = encode_fn();
   if (enc == nullptr) return false;
+  const uint64_t ptr = key.ptr, tiles = key.rows;
   const cuuint64_t dims[2] = {128, tiles};
   const cuuint64_t strides[1] = {512};
   const cuuint32_t box[2] = {128, 4};
@@ -1104,6 +1146,33 @@ bool make_scale_map(CUtensorMap *map, uint64_t ptr, uint64_t tiles) {
   return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, reinterpret_cast<void *>(ptr), dims, strides, box, ones,
              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool make_scale_map(CUtensorMap *map, uint64_t ptr, uint64_t tiles) {
+  MapKey key;
+  key.ptr = ptr; key.rows = tiles; key.kind = 2;
+  return cached_map(key, map, build_scale_map);
+}
+
+// Pairs of CTAs of `kernel` that the current device can host at once (asked once per kernel and device).
+int max_active_pairs(const void *kernel, const cudaLaunchConfig_t *cfg) {
+  static std::mutex mu;
+  static std::vector<std::tuple<const void *, int, int>> known;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    for (const auto &e : known)
+      if (std::get<0>(e) == kernel && std::get<1>(e) == dev) return std::get<2>(e);
+  }
+  int v = 0;
+  if (cudaOccupancyMaxActiveClusters(&v, kernel, cfg) != cudaSuccess) {
+    (void)cudaGetLastError();
+    v = 0;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  known.emplace_back(kernel, dev, v);
+  return v;
 }
 
 int launch_pair(const qwen36_nvfp4_gemm_spec_t *s, float alpha) {
@@ -1133,14 +1202,7 @@ int launch_pair(const qwen36_nvfp4_gemm_spec_t *s, float alpha) {
   cfg.numAttrs = 1;
   // The grid is persistent with a static tile stride, so it must never exceed the number of
   // pairs the device can host at the same time (some SMs may have no free partner).
-  static int max_pairs = [&] {
-    int v = 0;
-    if (cudaOccupancyMaxActiveClusters(&v, nvfp4_gemm_pair_kernel, &cfg) != cudaSuccess) {
-      (void)cudaGetLastError();
-      v = 0;
-    }
-    return v;
-  }();
+  const int max_pairs = max_active_pairs(reinterpret_cast<const void *>(nvfp4_gemm_pair_kernel), &cfg);
   if (max_pairs <= 0) return QWEN36_STATUS_NOT_IMPLEMENTED;
   const uint32_t pairs = tiles < static_cast<uint32_t>(max_pairs) ? tiles : static_cast<uint32_t>(max_pairs);
   cfg.gridDim = dim3(pairs * 2u);
@@ -1176,14 +1238,7 @@ int launch_pair6(const qwen36_nvfp4_gemm_spec_t *s, float alpha) {
   cfg.numAttrs = 1;
   // The grid is persistent with a static tile stride, so it must never exceed the number of
   // pairs the device can host at the same time (some SMs may have no free partner).
-  static int max_pairs = [&] {
-    int v = 0;
-    if (cudaOccupancyMaxActiveClusters(&v, nvfp4_gemm_pair6_kernel, &cfg) != cudaSuccess) {
-      (void)cudaGetLastError();
-      v = 0;
-    }
-    return v;
-  }();
+  const int max_pairs = max_active_pairs(reinterpret_cast<const void *>(nvfp4_gemm_pair6_kernel), &cfg);
   if (max_pairs <= 0) return QWEN36_STATUS_NOT_IMPLEMENTED;
   const uint32_t pairs = tiles < static_cast<uint32_t>(max_pairs) ? tiles : static_cast<uint32_t>(max_pairs);
   cfg.gridDim = dim3(pairs * 2u);

@@ -43,8 +43,17 @@ def test_static_scratch_attention_matches_workspace_entry(backend):
         spec_static = abi.TurboquantAttentionSpec(0, tokens - 1, dp(q), dp(kq), dp(vq), dp(meta), dp(got),
                                                   abi.DevicePtr(0), 0, shape, 0)
         assert lib.qwen36_turboquant_attention(C.byref(spec_ws)) == abi.SUCCESS
+        torch.cuda.synchronize()
+        # the entry point itself must allocate nothing: neither through the library's allocator (its call
+        # counter stays put) nor behind its back (the device's free memory stays put)
+        before, free_before = abi.CudaCounters(), torch.cuda.mem_get_info()[0]
+        assert lib.qwen36_cuda_counters_read(C.byref(before)) == abi.SUCCESS
         assert lib.qwen36_turboquant_attention_static(C.byref(spec_static)) == abi.SUCCESS
         torch.cuda.synchronize()
+        after = abi.CudaCounters()
+        assert lib.qwen36_cuda_counters_read(C.byref(after)) == abi.SUCCESS
+        assert (after.malloc_calls, after.free_calls) == (before.malloc_calls, before.free_calls)
+        assert torch.cuda.mem_get_info()[0] == free_before
         assert rel_l2(got, want) <= 1e-2          # the tolerance of the attention parity tests
         assert torch.equal(got, want)              # same kernels, same order: in fact identical
 
