@@ -12,6 +12,7 @@
 // float32 (4-bit x 8-bit significands), so the logits are bit-identical to the
 // reference's and the greedy argmax picks the same token.
 #include "common.cuh"
+#include "kv_split.cuh"
 
 #include <atomic>
 
@@ -323,12 +324,17 @@ lm_head_gemv_kernel(const uint8_t *__restrict__ weight, const float *__restrict_
 // the same order, every partial sum the reference's times that power of two, which is divided out
 // at the end.  Per weight that is one conversion slot and one FMA per token, against a conversion,
 // an unpack and an FMA per token on the float32 route, and the staged vector is half the size.
-// A warp carries four rows (every activation load from shared memory serves all four) and keeps
-// kAhead 512-byte steps of each in flight: with one step ahead a warp cannot finish a step faster
-// than one loaded-memory latency, which is what bounded the float32 route at a few tokens (16 warps x
-// 4 rows x 512 B per microsecond and SM = 3.3 TB/s).  The step loop is unrolled over the buffers so
-// that no register that still waits for its load is ever copied.
+// A warp carries four rows (every activation load from shared memory serves all four).  Its weights
+// do not wait in registers: every lane copies its own 16 bytes of each row with cp.async into a ring
+// that belongs to the warp (a stage = four rows x 512 bytes) and reads them back when their turn
+// comes, so several steps are in flight without costing a register, and the ring runs on across
+// row groups (no cold start every ten steps).  With one step ahead in registers a warp could not
+// finish a step faster than one loaded-memory latency, which is what held the float32 route at
+// 3.3 TB/s at a few tokens.  A lane only ever reads what it copied itself, so nothing but its own
+// cp.async.wait_group orders the ring.
 constexpr int kF16Rows = 4;
+constexpr uint32_t kF16StageBytes = kF16Rows * 512u;
+template <int N> struct F16Ring { static constexpr int kStages = N <= 4 ? 4 : (N <= 6 ? 3 : 2); };
 template <int N, bool FUSED>
 __global__ void __launch_bounds__(kThreads, 2)
 lm_head_gemv_f16_kernel(const uint8_t *__restrict__ weight, const float *__restrict__ row_scales,
@@ -337,7 +343,7 @@ lm_head_gemv_f16_kernel(const uint8_t *__restrict__ weight, const float *__restr
                         float *__restrict__ out_best, float2 *__restrict__ partials,
                         unsigned *__restrict__ ticket) {
   constexpr int R = kF16Rows;
-  constexpr int kAhead = N <= 4 ? 2 : 1, kBufs = kAhead + 1;
+  constexpr int S = F16Ring<N>::kStages;
   extern __shared__ __align__(16) uint8_t smem[];
   uint4 *xs = reinterpret_cast<uint4 *>(smem);        // N * cols float16, swizzled 16-byte chunks
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
@@ -368,23 +374,36 @@ lm_head_gemv_f16_kernel(const uint8_t *__restrict__ weight, const float *__restr
   for (int t = 0; t < N; ++t) { best[t] = -INFINITY; best_idx[t] = 0u; }
 
   const size_t warps_total = static_cast<size_t>(gridDim.x) * kWarps;
-  const uint32_t steps = cols / 512u;
-  const bool tail = lane * 16u + steps * 512u + 15u < cols;     // the reference loop's ragged last step
-  for (size_t row0 = (static_cast<size_t>(blockIdx.x) * kWarps + warp) * R; row0 < rows; row0 += warps_total * R) {
+  const uint32_t steps = cols / 512u;                             // this route takes cols % 512 == 0 only
+  const size_t first_row = (static_cast<size_t>(blockIdx.x) * kWarps + warp) * R;
+  const uint32_t groups = first_row < rows ? static_cast<uint32_t>((rows - first_row + warps_total * R - 1) / (warps_total * R)) : 0u;
+  const uint32_t total = groups * steps;                          // (row group, step) pairs of this warp, in order
+  const uint32_t ring = static_cast<uint32_t>(__cvta_generic_to_shared(smem)) + static_cast<uint32_t>(N) * cols * 2u + warp * (S * kF16StageBytes) + lane * 16u;
+  // stage q of the warp's sequence: rows past the end are zero-filled (source size 0)
+  auto issue = [&](uint32_t q) {
+    if (q < total) {
+      const uint32_t grp = q / steps, step = q - grp * steps;
+      const size_t row0 = first_row + static_cast<size_t>(grp) * warps_total * R;
+      const uint32_t dst = ring + (q % S) * kF16StageBytes;
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const bool in = row0 + r < rows;
+        q36::cp_async_16(dst + r * 512u, weight + (in ? (row0 + r) * cols + step * 512u + lane * 16u : 0u), in ? 16u : 0u);
+      }
+    }
+    q36::cp_async_commit();                                       // one group per stage, empty or not
+  };
+#pragma unroll
+  for (int a = 0; a < S - 1; ++a) issue(a);
+  uint32_t q = 0;
+  for (uint32_t grp = 0; grp < groups; ++grp) {
+    const size_t row0 = first_row + static_cast<size_t>(grp) * warps_total * R;
     const int r_count = static_cast<int>(min(static_cast<size_t>(R), rows - row0));
     float acc[R][N];
 #pragma unroll
     for (int r = 0; r < R; ++r)
 #pragma unroll
       for (int t = 0; t < N; ++t) acc[r][t] = 0.f;
-    const uint8_t *w0 = weight + row0 * cols + lane * 16u;
-    uint4 buf[kBufs][R];
-    auto load = [&](uint4 (&dst)[R], uint32_t step) {
-#pragma unroll
-      for (int r = 0; r < R; ++r)
-        dst[r] = r < r_count ? __ldcs(reinterpret_cast<const uint4 *>(w0 + static_cast<size_t>(r) * cols + step * 512u))
-                             : make_uint4(0, 0, 0, 0);
-    };
     auto multiply = [&](const uint4 (&cur)[R], uint32_t s) {
       const uint32_t chunk0 = (lane * 16u + s * 512u) / 8u;        // first of two x chunks
 #pragma unroll
@@ -413,19 +432,13 @@ lm_head_gemv_f16_kernel(const uint8_t *__restrict__ weight, const float *__restr
         }
       }
     };
-    const uint32_t my_steps = steps + (tail ? 1u : 0u);
+    for (uint32_t step = 0; step < steps; ++step, ++q) {
+      q36::cp_async_wait<S - 2>();                                // stage q has landed (this lane's own copies)
+      uint4 cur[R];
 #pragma unroll
-    for (int a = 0; a < kAhead; ++a)
-      if (static_cast<uint32_t>(a) < my_steps) load(buf[a], a);
-    for (uint32_t s0 = 0; s0 < my_steps; s0 += kBufs) {
-#pragma unroll
-      for (int k = 0; k < kBufs; ++k) {
-        const uint32_t s = s0 + k;
-        if (s < my_steps) {
-          if (s + kAhead < my_steps) load(buf[(k + kAhead) % kBufs], s + kAhead);
-          multiply(buf[k], s);
-        }
-      }
+      for (int r = 0; r < R; ++r) cur[r] = q36::lds128(ring + (q % S) * kF16StageBytes + r * 512u);
+      issue(q + S - 1);                                           // into the slot that was read one step ago
+      multiply(cur, step);
     }
 #pragma unroll
     for (int r = 0; r < R; ++r) {
@@ -574,7 +587,7 @@ int launch_gemv_n(const uint8_t *w, const float *scales, const __nv_bfloat16 *x,
       if (g_gemv_route.load() == 0 && cols % 512 == 0 && !(FUSED && N == 4)) {
         // float16 route first; the float32 route right behind it runs only for activations the
         // float16 route declines (both decide on the same data, on the device, so nothing is read back)
-        const size_t smem16 = static_cast<size_t>(N) * cols * 2;
+        const size_t smem16 = static_cast<size_t>(N) * cols * 2 + static_cast<size_t>(kWarps) * F16Ring<N>::kStages * kF16StageBytes;
         if (q36::ensure_dynamic_smem(reinterpret_cast<const void *>(lm_head_gemv_f16_kernel<N, FUSED>), 200 * 1024) != cudaSuccess)
           return QWEN36_STATUS_CUDA_ERROR;
         const size_t need = q36::div_ceil(rows, static_cast<size_t>(kWarps) * kF16Rows);
