@@ -375,6 +375,8 @@ def other_configs(backend, torch, synth, make_sampler=None):
             c = torch.empty((m_tok, n_out), dtype=torch.bfloat16, device="cuda")
             # 200 launches back to back run into the power cap at the larger sizes: the SM clock seen during the
             # timing is recorded beside the figure (sw_power_cap is kept and noted, not rejected)
+            torch.cuda.synchronize()
+            time.sleep(0.2)                     # let the power state settle: the burst figure is a cool-start one
             burst_us = _time_cuda(torch, lambda i: backend.nvfp4_gemm(ws[i % 3][0], ws[i % 3][1], fp4, sf, alpha,
                                                                        n_out, m_tok, k, c), 9, warm=3, backend=backend)
             sampler = make_sampler() if make_sampler is not None else None
