@@ -174,10 +174,8 @@ class TensorParallelGemv:
 
     def __init__(self, backend, vectors: dict, slots: int, device, group=None):
         self.lib = backend.lib
-        self.offsets, at = {}, 0
-        for name, n in vectors.items():
-            self.offsets[name] = (at, n)
-            at += (4 * n + 255) // 256 * 256
+        from .shard import arena_layout
+        self.offsets, at = arena_layout(vectors)
         self.slots = slots
         self.ex = PeerExchange(backend, at, 1, device, group)
         self.state = torch.zeros(4 * slots, dtype=torch.int32, device=self.ex.device)

@@ -36,6 +36,24 @@ def shard_tokens(tokens: int, rank: int, world: int) -> Tuple[int, int]:
     return min(tokens, per * rank), min(tokens, per * (rank + 1))
 
 
+def arena_layout(vectors: dict, bytes_per_value: int = 4, align: int = 256):
+    """Byte offsets of the activation vectors of a tensor-parallel GEMV chain inside a rank's arena
+    ({name: (offset, length)}, total bytes).  Flagged cells take 4 bytes per value (two bf16 values +
+    the call number per 8 bytes); every vector starts on an `align`-byte boundary.  The same on every
+    rank, since a rank stores into its peers' arenas at the offsets of its own."""
+    offsets, at = {}, 0
+    for name, n in vectors.items():
+        offsets[name] = (at, n)
+        at += (bytes_per_value * n + align - 1) // align * align
+    return offsets, at
+
+
+def tp_slices(shapes, rank: int, world: int):
+    """Row slice [lo, hi) of every matrix of a tensor-parallel chain for `rank`: whole 128-row blocks,
+    so that the scale tiles of a slice stay whole.  shapes = [(name, rows, cols), ...]."""
+    return {name: shard_rows(rows, rank, world) for name, rows, _ in shapes}
+
+
 def all_gather_rows(local: torch.Tensor, n_full: int, world: int, out: torch.Tensor = None) -> torch.Tensor:
     """Gathers 1-D row slices produced by shard_rows() back into the full vector."""
     per = ((n_full // 128 + world - 1) // world) * 128

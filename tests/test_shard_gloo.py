@@ -65,15 +65,44 @@ def _worker(rank, world, port, case, ret):
                 want = synth.bf16_bits_to_f32(orc.kv_attention(q, kq, vq, meta, position))
                 err = np.linalg.norm(got - want) / np.linalg.norm(want)
                 assert err < 1e-2, (position, err)
+        elif case == "tp_chain":
+            # the data flow of the tensor-parallel GEMV chain: every rank computes its row slices, the
+            # slices meet in every rank's full vector (an all-gather stands in for the peer stores),
+            # the next GEMV consumes the full vector; two chained layers must equal the unsplit chain
+            shapes = [("a", 512, 256), ("b", 256, 512)]
+            mats = {}
+            for name, n, k in shapes:
+                packed, sf_rm = synth.nvfp4_weight(rng, n, k)
+                mats[name] = (packed, sf_rm, n, k)
+            x0 = synth.activations(rng, 1, 256)[0]
+            gain = synth.WEIGHT_GLOBAL_SCALE * 40.0
+            full = x0
+            for _ in range(2):
+                for name, n, k in shapes:
+                    full = orc.nvfp4_matvec(full, mats[name][0], orc.retile_scales(mats[name][1]), gain, k)
+            mine = x0
+            slices = shard.tp_slices(shapes, rank, world)
+            offsets, total = shard.arena_layout({name: n for name, n, _ in shapes})
+            assert total % 256 == 0 and all(off % 256 == 0 for off, _ in offsets.values())
+            assert offsets["b"][0] >= 4 * 512                 # vectors do not overlap
+            for _ in range(2):
+                for name, n, k in shapes:
+                    lo, hi = slices[name]
+                    assert lo % 128 == 0 and (hi - lo) % 128 == 0
+                    part = orc.nvfp4_matvec(mine, mats[name][0][lo:hi].copy(), orc.retile_scales(mats[name][1][lo:hi].copy()),
+                                            gain, k)
+                    got = shard.all_gather_rows(torch.from_numpy(synth.bf16_bits_to_f32(part).copy()), n, world)
+                    mine = synth.f32_to_bf16_bits(got.numpy())        # bf16 values travel as float32: exact both ways
+            assert np.array_equal(mine, full)
         ret[rank] = "ok"
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("case", ["rows", "argmax", "attention"])
+@pytest.mark.parametrize("case", ["rows", "argmax", "attention", "tp_chain"])
 def test_two_rank_gloo(case):
     world = 2
-    port = 29500 + (os.getpid() % 2000) + {"rows": 0, "argmax": 1, "attention": 2}[case]
+    port = 29500 + (os.getpid() % 2000) + {"rows": 0, "argmax": 1, "attention": 2, "tp_chain": 3}[case]
     mgr = mp.Manager()
     ret = mgr.dict()
     mp.spawn(_worker, args=(world, port, case, ret), nprocs=world, join=True)
