@@ -27,6 +27,25 @@
 
 namespace {
 
+// %globaltimer stamps (time, CTA, event) appended to a log for a timeline of a few calls; compiled in
+// only with -DQ36_ATTN_TRACE.
+#ifdef Q36_ATTN_TRACE
+constexpr uint32_t kTraceEntries = 1u << 15;
+__device__ unsigned long long g_attn_trace[kTraceEntries][2];
+__device__ unsigned int g_attn_trace_n = 0;
+#define Q36_ATRACE(cta_, ev)                                                        \
+  do {                                                                             \
+    if (threadIdx.x == 0) {                                                        \
+      unsigned long long t_;                                                       \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                       \
+      const unsigned int at_ = atomicAdd(&g_attn_trace_n, 1u);                     \
+      if (at_ < kTraceEntries) { g_attn_trace[at_][0] = t_; g_attn_trace[at_][1] = (static_cast<unsigned long long>(cta_) << 8) | (ev); } \
+    }                                                                              \
+  } while (0)
+#else
+#define Q36_ATRACE(cta_, ev)
+#endif
+
 using q36::as_ptr;
 
 constexpr int kThreads = 256;
@@ -433,16 +452,20 @@ kv_merge_kernel(const float *__restrict__ part_o, const float *__restrict__ part
   const float *po = part_o + qh * n_parts * head_dim;
   // launched with programmatic stream serialisation after the split kernel: the CTAs are resident
   // by the time the partials are complete (a no-op after an ordinary launch)
+  Q36_ATRACE(1000u + blockIdx.x, 0);
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  Q36_ATRACE(1000u + blockIdx.x, 1);
   float M, den;
   q36::lse_weights(pm, pl, n_parts, s_w, s_red, M, den);
+  Q36_ATRACE(1000u + blockIdx.x, 2);
   for (uint32_t d = threadIdx.x; d < head_dim; d += kThreads) {
     const float acc = q36::lse_accumulate(po, s_w, n_parts, head_dim, d);
     if (FINAL) out[qh * head_dim + d] = __float2bfloat16(den > 0.f ? __fdiv_rn(acc, den) : 0.f);
     else out_o[qh * head_dim + d] = acc;
   }
   if (!FINAL && threadIdx.x == 0) { out_m[qh] = M; out_l[qh] = den; }
+  Q36_ATRACE(1000u + blockIdx.x, 3);
 }
 
 template <bool FINAL>
@@ -783,8 +806,12 @@ kv_attention_staged_kernel(const __nv_bfloat16 *__restrict__ q, const int8_t *__
   // launched with programmatic stream serialisation: seated while the previous kernel drains, but
   // nothing is read or written before that kernel (the producer of q, of the newest cache row, or
   // the reader of the partial buffers) has completed
+  const uint32_t cta_flat = blockIdx.y * gridDim.x + blockIdx.x;
+  (void)cta_flat;
+  Q36_ATRACE(cta_flat, 0);
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  Q36_ATRACE(cta_flat, 1);
 
   const uint32_t ring = static_cast<uint32_t>(__cvta_generic_to_shared(smem)) + warp * (kStages * kStageBytes);
   const size_t stride = static_cast<size_t>(kWarps) * 16;
@@ -842,6 +869,7 @@ kv_attention_staged_kernel(const __nv_bfloat16 *__restrict__ q, const int8_t *__
     }
   }
   __syncthreads();
+  Q36_ATRACE(cta_flat, 2);
   // 1152 * (sum of head g's float16 q): the K operand carries that bias on every element
   float q_bias = 0.f;
 #pragma unroll
@@ -868,6 +896,7 @@ kv_attention_staged_kernel(const __nv_bfloat16 *__restrict__ q, const int8_t *__
   for (; t0 < s_end; t0 += stride) {
     issue(stage == 0 ? kStages - 1 : stage - 1, t0 + (kStages - 1) * stride);   // refill the stage read last time
     q36::cp_async_wait<kStages - 1>();
+    if (t0 == s_begin) Q36_ATRACE(cta_flat, 3);
     __syncwarp();
     const uint32_t kt = ring + stage * kStageBytes, vt = kt + kTileBytes, mt = vt + kTileBytes;
     // ---- S = Q K^T: four independent accumulator chains (two blocks x even / odd steps)
@@ -945,9 +974,12 @@ kv_attention_staged_kernel(const __nv_bfloat16 *__restrict__ q, const int8_t *__
     __syncwarp();                                    // every lane is done with this stage before it is refilled
     stage = stage + 1 == kStages ? 0 : stage + 1;
   }
+  Q36_ATRACE(cta_flat, 4);
   q36::cp_async_wait<0>();
   __syncthreads();                                   // the ring becomes the epilogue's slices
+  Q36_ATRACE(cta_flat, 5);
   q36::split_epilogue<G>(o, m_run, l_run, 1.0f / kPScale, s_m, s_l, s_o, part_o, part_m, part_l, head0, split, n_splits);
+  Q36_ATRACE(cta_flat, 6);
 }
 
 template <int G>
@@ -1183,3 +1215,16 @@ extern "C" int qwen36_attention_merge_partials(const qwen36_attention_merge_spec
       static_cast<uint32_t>(spec->head_dim), as_ptr<__nv_bfloat16>(spec->output_bf16), nullptr, nullptr, nullptr);
   return q36::launch_status();
 }
+
+#ifdef Q36_ATTN_TRACE
+// Copies the stamp log (32768 entries of {time ns, cta << 8 | event}) to `dst`, returns the number of
+// entries written since the last read (or -1) and rewinds the log.
+extern "C" int qwen36_attention_trace_read(void *dst) {
+  unsigned int n = 0;
+  const unsigned int zero = 0;
+  if (cudaMemcpyFromSymbol(&n, g_attn_trace_n, sizeof(n)) != cudaSuccess) return -1;
+  if (cudaMemcpyFromSymbol(dst, g_attn_trace, sizeof(g_attn_trace)) != cudaSuccess) return -1;
+  if (cudaMemcpyToSymbol(g_attn_trace_n, &zero, sizeof(zero)) != cudaSuccess) return -1;
+  return static_cast<int>(n < kTraceEntries ? n : kTraceEntries);
+}
+#endif
