@@ -514,7 +514,7 @@ def other_configs(backend, torch, synth, make_sampler=None):
         for q_tok in (4, 16):
             qv = torch.randn((q_tok, 24, 256), generator=gen, device="cuda").to(torch.bfloat16)
             ov = torch.empty((q_tok, 24, 256), dtype=torch.bfloat16, device="cuda")
-            ns = 74
+            ns = backend.attention_verify_splits(q_tok, 24, 4, torch.cuda.get_device_properties(0).multi_processor_count)
             pv = (torch.empty((q_tok, 24, ns, 256), device="cuda"), torch.empty((q_tok, 24, ns), device="cuda"),
                   torch.empty((q_tok, 24, ns), device="cuda"))
             for ctx in (32768, 131072):
@@ -615,7 +615,8 @@ def profile_case(name: str):
             caches.append(c)
         qv = torch.randn((4, 24, 256), generator=gen, device="cuda").to(torch.bfloat16)
         for i in range(3):
-            b.attention_flash_splitk_prefill(qv, caches[i], caches[(i + 1) % 3], ctx - 4, 1 if fp8 else 0, 74)
+            b.attention_flash_splitk_prefill(qv, caches[i], caches[(i + 1) % 3], ctx - 4, 1 if fp8 else 0,
+                                             b.attention_verify_splits(4, 24, 4))
     elif name.startswith("gemv_sweep_layer"):
         # one decode layer (4 launches: q_gate + k + v grouped, o, gate_up, down), three times over cold weights
         layers = []

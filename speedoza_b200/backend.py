@@ -317,6 +317,13 @@ class CudaBackend:
         _check("attention_decode", self.lib.qwen36_attention_decode(C.byref(spec)))
         return out
 
+    @staticmethod
+    def attention_verify_splits(tokens: int, q_heads: int, kv_heads: int, sms: int = 148) -> int:
+        """Split count that gives the verify kernel one CTA per SM: a CTA covers one kv head and up to 64
+        (token, q head) rows of it, so the grid is kv_heads x ceil(rows / 64) x n_splits."""
+        rows = tokens * (q_heads // kv_heads)
+        return max(1, sms // (kv_heads * ((rows + 63) // 64)))
+
     def attention_flash_splitk_prefill(self, q_bf16, cache_k, cache_v, start_position: int, kv_cache_dtype: int,
                                        n_splits: int, partials=None, start_position_device=None, out=None):
         """Speculative-verify attention (qwen36_attention_flash_splitk_prefill_bf16): q [tokens <= 32, q_heads,

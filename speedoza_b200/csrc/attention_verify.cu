@@ -36,11 +36,24 @@ using q36::as_ptr;
 
 constexpr uint32_t kD = 256;                 // head_dim
 constexpr uint32_t kTile = 64;               // KV rows per iteration
-constexpr uint32_t kWarps = 4;
-constexpr uint32_t kThreads = kWarps * 32;
-constexpr uint32_t kRows = kWarps * 16;      // (token, q head) rows per CTA
-constexpr uint32_t kRowBytes = kD * 2;       // one staged row, 2-byte elements
-constexpr uint32_t kSmemBytes = (kRows + 2 * kTile) * kRowBytes;   // Q + K + V = 96 KB
+constexpr uint32_t kRowBytes = kD * 2;       // one row of 2-byte elements
+constexpr uint32_t kStages = 3;              // K / V tiles in flight (cp.async ring)
+constexpr uint32_t kMergeStride = kD + 8;    // floats per row of the warps' meeting area
+
+// Shared memory of a CTA with MT 16-row tiles of (token, q head) rows:
+//   Q (16 MT rows) | FP8 only: K and V of the current tile expanded to f16 | ring of kStages tiles in
+//   the cache's own format (K then V; bf16 rows are stored chunk-swizzled, ready for ldmatrix).
+// After the loop the area behind Q is reused for the warps' (m, l, o).
+template <bool FP8, int MT>
+struct Layout {
+  static constexpr uint32_t kRows = 16u * MT;
+  static constexpr uint32_t kQBytes = kRows * kRowBytes;
+  static constexpr uint32_t kWorkBytes = FP8 ? 2u * kTile * kRowBytes : 0u;
+  static constexpr uint32_t kCacheRowBytes = FP8 ? kD : kRowBytes;
+  static constexpr uint32_t kStageBytes = 2u * kTile * kCacheRowBytes;
+  static constexpr uint32_t kSmemBytes = kQBytes + kWorkBytes + kStages * kStageBytes;
+  static_assert(kSmemBytes <= 227u * 1024u, "shared memory budget");
+};
 
 struct Params {
   const __nv_bfloat16 *q;                    // [tokens, q_heads, 256]
@@ -52,6 +65,14 @@ struct Params {
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+// 16 bytes global -> shared without passing through registers; src_bytes == 0 writes zeros.
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
@@ -136,13 +157,22 @@ __device__ __forceinline__ uint8_t encode_e4m3_append(float v) {
 
 // FP8: the cache holds E4M3 bytes and the product runs in f16; otherwise bf16 throughout.
 // DECODE: one token, timestep == position comes from k_new / v_new, the owning split appends it.
-template <bool FP8, bool DECODE>
-__global__ void __launch_bounds__(kThreads, 2)
+// MT: 16-row tiles of (token, q head) rows per CTA.  The four warps form MT x TH: warp w works on row
+// tile w % MT and on the timesteps [th * 64 / TH, (th + 1) * 64 / TH) of every 64-row KV tile, th =
+// w / MT, with an online-softmax state of its own; the TH states of a row meet once, after the loop.
+// So 4 query tokens x 6 heads (24 rows, MT = 2) or a decode token (6 rows, MT = 1) keep all four
+// tensor cores busy on rows that exist, instead of three warps out of four multiplying padding.
+// K / V tiles arrive through a three-deep cp.async ring, two tiles ahead of the one being multiplied.
+template <bool FP8, bool DECODE, int MT, int NW>
+__global__ void __launch_bounds__(NW * 32, 1)
 attention_splitk_tc_kernel(const Params p) {
+  using L = Layout<FP8, MT>;
+  constexpr uint32_t NT = NW * 32u, TH = NW / MT, W = kTile / TH;               // timesteps per warp per tile
   extern __shared__ __align__(128) uint8_t smem[];
-  uint8_t *sq = smem, *sk = smem + kRows * kRowBytes, *sv = sk + kTile * kRowBytes;
+  uint8_t *sq = smem, *work = smem + L::kQBytes, *ring = work + L::kWorkBytes;
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
   const uint32_t gid = lane >> 2, tig = lane & 3u;
+  const uint32_t mt = warp % MT, th = warp / MT;
   const uint32_t kvh = blockIdx.x, chunk = blockIdx.y, split = blockIdx.z;
   const uint32_t q_per_kv = p.q_heads / p.kv_heads;
   const uint32_t m_rows = p.tokens * q_per_kv;                       // rows of this kv head
@@ -160,17 +190,52 @@ attention_splitk_tc_kernel(const Params p) {
     t0 = min(split * per, iters) * kTile;
     t1 = min(min((split + 1u) * per, iters) * kTile, visible);
   }
+  const uint32_t n_tiles = t1 > t0 ? (t1 - t0 + kTile - 1u) / kTile : 0u;
 
   // this lane's two rows: (token, q head) pairs, token-major
-  const uint32_t row_lo = chunk * kRows + warp * 16u + gid, row_hi = row_lo + 8u;
+  const uint32_t row_lo = chunk * L::kRows + mt * 16u + gid, row_hi = row_lo + 8u;
   const bool ok_lo = row_lo < m_rows, ok_hi = row_hi < m_rows;
+  const bool warp_has_rows = chunk * L::kRows + mt * 16u < m_rows;
   const uint32_t tok_lo = row_lo / q_per_kv, tok_hi = row_hi / q_per_kv;
   // last visible timestep of each row (inclusive)
   const uint32_t lim_lo = DECODE ? start : start + tok_lo, lim_hi = DECODE ? start : start + tok_hi;
 
-  // ---- stage Q: 64 rows x 512 bytes, chunk c of row r at chunk c ^ (r & 7)
-  for (uint32_t i = threadIdx.x; i < kRows * 32u; i += kThreads) {
-    const uint32_t r = i >> 5, c = i & 31u, row = chunk * kRows + r;
+  // ---- tile `idx` of the split -> ring slot idx % kStages, in the cache's format.  Rows at or past t1
+  // arrive as zeros; the decode step's own row comes from k_new / v_new (directly for a bf16 cache,
+  // at the expansion for an FP8 cache).
+  const uint8_t *ck = static_cast<const uint8_t *>(p.cache_k), *cv = static_cast<const uint8_t *>(p.cache_v);
+  auto load_tile = [&](uint32_t idx) {
+    const uint32_t base = t0 + idx * kTile;
+    const uint32_t dst = smem_u32(ring + (idx % kStages) * L::kStageBytes);
+    constexpr uint32_t kChunks = L::kCacheRowBytes / 16u;             // 16-byte chunks per row: 16 or 32
+#pragma unroll 4
+    for (uint32_t i = threadIdx.x; i < kTile * kChunks; i += NT) {
+      const uint32_t r = i / kChunks, c = i % kChunks, t = base + r;
+      const size_t off = (static_cast<size_t>(t) * p.kv_heads + kvh) * L::kCacheRowBytes + c * 16u;
+      const uint8_t *ks = ck + off, *vs = cv + off;
+      uint32_t bytes = t < t1 ? 16u : 0u;
+      if (DECODE && t == start) {
+        if (FP8) {
+          bytes = 0u;
+        } else {
+          ks = reinterpret_cast<const uint8_t *>(p.k_new + kvh * kD) + c * 16u;
+          vs = reinterpret_cast<const uint8_t *>(p.v_new + kvh * kD) + c * 16u;
+        }
+      }
+      if (bytes == 0u) { ks = ck; vs = cv; }
+      const uint32_t at = FP8 ? r * kD + c * 16u : r * kRowBytes + ((c ^ (r & 7u)) << 4);
+      cp_async16(dst + at, ks, bytes);
+      cp_async16(dst + kTile * L::kCacheRowBytes + at, vs, bytes);
+    }
+  };
+  for (uint32_t s = 0; s + 1u < kStages; ++s) {
+    if (s < n_tiles) load_tile(s);
+    cp_async_commit();
+  }
+
+  // ---- stage Q: chunk c of row r at chunk c ^ (r & 7)
+  for (uint32_t i = threadIdx.x; i < L::kRows * 32u; i += NT) {
+    const uint32_t r = i >> 5, c = i & 31u, row = chunk * L::kRows + r;
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
     if (row < m_rows) {
       const uint32_t tok = row / q_per_kv, qh = kvh * q_per_kv + row % q_per_kv;
@@ -186,64 +251,56 @@ attention_splitk_tc_kernel(const Params p) {
   float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
   constexpr float kScaleLog2 = 0.0625f * 1.4426950408889634f;        // rsqrt(256) * log2(e)
 
-  for (uint32_t base = t0; base < t1; base += kTile) {
-    __syncthreads();                                                  // previous tile fully consumed (and Q staged)
-    // ---- stage K and V rows [base, base + 64): rows past t1 are zeros
+  for (uint32_t it = 0; it < n_tiles; ++it) {
+    const uint32_t base = t0 + it * kTile;
+    cp_async_wait<kStages - 2>();                                     // this thread's part of tile `it` has landed
+    __syncthreads();                                                  // everybody's has; tile it - 1 is consumed (and Q staged)
+    if (it + kStages - 1u < n_tiles) load_tile(it + kStages - 1u);    // into the slot tile it - 1 left
+    cp_async_commit();
+    const uint8_t *slot = ring + (it % kStages) * L::kStageBytes;
+    const uint8_t *sk = slot, *sv = slot + kTile * L::kCacheRowBytes;
     if (FP8) {
-      for (uint32_t i = threadIdx.x; i < kTile * 16u; i += kThreads) {
+      // ---- expand E4M3 -> f16 into the work tile (chunk-swizzled rows of 512 bytes)
+      uint8_t *wk = work, *wv = work + kTile * kRowBytes;
+#pragma unroll 2
+      for (uint32_t i = threadIdx.x; i < kTile * 16u; i += NT) {
         const uint32_t r = i >> 4, c = i & 15u, t = base + r;
-        uint4 klo = make_uint4(0u, 0u, 0u, 0u), khi = klo, vlo = klo, vhi = klo;
-        if (t < t1) {
-          if (DECODE && t == start) {
-            klo = bf16x8_to_f16(__ldg(reinterpret_cast<const uint4 *>(p.k_new + kvh * kD) + 2u * c));
-            khi = bf16x8_to_f16(__ldg(reinterpret_cast<const uint4 *>(p.k_new + kvh * kD) + 2u * c + 1u));
-            vlo = bf16x8_to_f16(__ldg(reinterpret_cast<const uint4 *>(p.v_new + kvh * kD) + 2u * c));
-            vhi = bf16x8_to_f16(__ldg(reinterpret_cast<const uint4 *>(p.v_new + kvh * kD) + 2u * c + 1u));
-          } else {
-            const size_t off = (static_cast<size_t>(t) * p.kv_heads + kvh) * kD;
-            e4m3x16_to_f16(__ldcs(reinterpret_cast<const uint4 *>(static_cast<const uint8_t *>(p.cache_k) + off) + c), klo, khi);
-            e4m3x16_to_f16(__ldcs(reinterpret_cast<const uint4 *>(static_cast<const uint8_t *>(p.cache_v) + off) + c), vlo, vhi);
-          }
+        uint4 klo, khi, vlo, vhi;
+        if (DECODE && t == start && t < t1) {
+          klo = bf16x8_to_f16(__ldg(reinterpret_cast<const uint4 *>(p.k_new + kvh * kD) + 2u * c));
+          khi = bf16x8_to_f16(__ldg(reinterpret_cast<const uint4 *>(p.k_new + kvh * kD) + 2u * c + 1u));
+          vlo = bf16x8_to_f16(__ldg(reinterpret_cast<const uint4 *>(p.v_new + kvh * kD) + 2u * c));
+          vhi = bf16x8_to_f16(__ldg(reinterpret_cast<const uint4 *>(p.v_new + kvh * kD) + 2u * c + 1u));
+        } else {
+          e4m3x16_to_f16(*reinterpret_cast<const uint4 *>(sk + r * kD + c * 16u), klo, khi);
+          e4m3x16_to_f16(*reinterpret_cast<const uint4 *>(sv + r * kD + c * 16u), vlo, vhi);
         }
         const uint32_t sw = r & 7u;
-        *reinterpret_cast<uint4 *>(sk + r * kRowBytes + (((2u * c) ^ sw) << 4)) = klo;
-        *reinterpret_cast<uint4 *>(sk + r * kRowBytes + (((2u * c + 1u) ^ sw) << 4)) = khi;
-        *reinterpret_cast<uint4 *>(sv + r * kRowBytes + (((2u * c) ^ sw) << 4)) = vlo;
-        *reinterpret_cast<uint4 *>(sv + r * kRowBytes + (((2u * c + 1u) ^ sw) << 4)) = vhi;
+        *reinterpret_cast<uint4 *>(wk + r * kRowBytes + (((2u * c) ^ sw) << 4)) = klo;
+        *reinterpret_cast<uint4 *>(wk + r * kRowBytes + (((2u * c + 1u) ^ sw) << 4)) = khi;
+        *reinterpret_cast<uint4 *>(wv + r * kRowBytes + (((2u * c) ^ sw) << 4)) = vlo;
+        *reinterpret_cast<uint4 *>(wv + r * kRowBytes + (((2u * c + 1u) ^ sw) << 4)) = vhi;
       }
-    } else {
-      for (uint32_t i = threadIdx.x; i < kTile * 32u; i += kThreads) {
-        const uint32_t r = i >> 5, c = i & 31u, t = base + r;
-        uint4 kk = make_uint4(0u, 0u, 0u, 0u), vv = kk;
-        if (t < t1) {
-          if (DECODE && t == start) {
-            kk = __ldg(reinterpret_cast<const uint4 *>(p.k_new + kvh * kD) + c);
-            vv = __ldg(reinterpret_cast<const uint4 *>(p.v_new + kvh * kD) + c);
-          } else {
-            const size_t off = (static_cast<size_t>(t) * p.kv_heads + kvh) * kD;
-            kk = __ldcs(reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(p.cache_k) + off) + c);
-            vv = __ldcs(reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(p.cache_v) + off) + c);
-          }
-        }
-        *reinterpret_cast<uint4 *>(sk + r * kRowBytes + ((c ^ (r & 7u)) << 4)) = kk;
-        *reinterpret_cast<uint4 *>(sv + r * kRowBytes + ((c ^ (r & 7u)) << 4)) = vv;
-      }
+      __syncthreads();
+      sk = wk;
+      sv = wv;
     }
-    __syncthreads();
+    const uint32_t tw = base + th * W;                                // first timestep of this warp's slice
+    if (!warp_has_rows || tw >= t1) continue;                         // padding rows / nothing visible: no work (warp-uniform)
 
-    // ---- S = Q K^T for this warp's 16 rows x 64 timesteps
-    float s[8][4];
+    // ---- S = Q K^T for this warp's 16 rows x W timesteps
+    float s[W / 8][4];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
-    const uint32_t q_row = warp * 16u + (lane & 15u);
+    for (uint32_t j = 0; j < W / 8u; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+    const uint32_t q_row = mt * 16u + (lane & 15u);
     const uint32_t q_addr = smem_u32(sq) + q_row * kRowBytes, q_sw = q_row & 7u;
 #pragma unroll 4
     for (uint32_t kk = 0; kk < 16u; ++kk) {
       uint32_t a[4];
       ldmatrix_x4(a, q_addr + (((2u * kk + (lane >> 4)) ^ q_sw) << 4));
 #pragma unroll
-      for (uint32_t jp = 0; jp < 4u; ++jp) {                          // two 8-timestep tiles per load
-        const uint32_t n_row = 16u * jp + 8u * (lane >> 4) + (lane & 7u);
+      for (uint32_t jp = 0; jp < W / 16u; ++jp) {                     // two 8-timestep tiles per load
+        const uint32_t n_row = th * W + 16u * jp + 8u * (lane >> 4) + (lane & 7u);
         uint32_t b[4];
         ldmatrix_x4(b, smem_u32(sk) + n_row * kRowBytes + (((2u * kk + ((lane >> 3) & 1u)) ^ (n_row & 7u)) << 4));
         mma16816<FP8>(s[2 * jp], a, b[0], b[1]);
@@ -254,10 +311,10 @@ attention_splitk_tc_kernel(const Params p) {
     // ---- mask + online softmax (row gid: c0, c1 ; row gid + 8: c2, c3)
     float mx_lo = -INFINITY, mx_hi = -INFINITY;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
+    for (uint32_t j = 0; j < W / 8u; ++j) {
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const uint32_t t = base + 8u * j + 2u * tig + e;
+      for (uint32_t e = 0; e < 2u; ++e) {
+        const uint32_t t = tw + 8u * j + 2u * tig + e;
         if (!(ok_lo && t <= lim_lo && t < t1)) s[j][e] = -INFINITY;
         if (!(ok_hi && t <= lim_hi && t < t1)) s[j][2 + e] = -INFINITY;
         mx_lo = fmaxf(mx_lo, s[j][e]);
@@ -274,15 +331,15 @@ attention_splitk_tc_kernel(const Params p) {
     const float al_hi = m_hi == -INFINITY ? 0.f : exp2f((m_hi - mn_hi) * kScaleLog2);
     const float ref_lo = mn_lo == -INFINITY ? 0.f : mn_lo, ref_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
     float sum_lo = 0.f, sum_hi = 0.f;
-    uint32_t pa[4][4];                                               // P as A fragments, 4 k-steps of 16 timesteps
+    uint32_t pa[W / 16][4];                                          // P as A fragments, k-steps of 16 timesteps
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
+    for (uint32_t j = 0; j < W / 8u; ++j) {
       const float p0 = exp2f((s[j][0] - ref_lo) * kScaleLog2), p1 = exp2f((s[j][1] - ref_lo) * kScaleLog2);
       const float p2 = exp2f((s[j][2] - ref_hi) * kScaleLog2), p3 = exp2f((s[j][3] - ref_hi) * kScaleLog2);
       sum_lo += p0 + p1;
       sum_hi += p2 + p3;
-      pa[j >> 1][(j & 1) * 2] = pack2<FP8>(p0, p1);
-      pa[j >> 1][(j & 1) * 2 + 1] = pack2<FP8>(p2, p3);
+      pa[j >> 1][(j & 1u) * 2u] = pack2<FP8>(p0, p1);
+      pa[j >> 1][(j & 1u) * 2u + 1u] = pack2<FP8>(p2, p3);
     }
     sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, 1);
     sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, 2);
@@ -298,10 +355,10 @@ attention_splitk_tc_kernel(const Params p) {
       o[j][2] *= al_hi; o[j][3] *= al_hi;
     }
 
-    // ---- O += P V: k = timestep (4 steps of 16), n = head dimension (32 tiles of 8)
+    // ---- O += P V: k = timestep (steps of 16), n = head dimension (32 tiles of 8)
 #pragma unroll
-    for (uint32_t ks = 0; ks < 4u; ++ks) {
-      const uint32_t v_row = 16u * ks + 8u * ((lane >> 3) & 1u) + (lane & 7u);
+    for (uint32_t ks = 0; ks < W / 16u; ++ks) {
+      const uint32_t v_row = th * W + 16u * ks + 8u * ((lane >> 3) & 1u) + (lane & 7u);
       const uint32_t v_addr = smem_u32(sv) + v_row * kRowBytes, v_sw = v_row & 7u;
 #pragma unroll
       for (uint32_t jd = 0; jd < 32u; jd += 2u) {
@@ -312,26 +369,68 @@ attention_splitk_tc_kernel(const Params p) {
       }
     }
   }
+  cp_async_wait<0>();
 
   // ---- partials: unnormalised O, m in scaled units, l
-  if (ok_lo || ok_hi) {
-    const uint32_t qh_lo = kvh * q_per_kv + row_lo % q_per_kv, qh_hi = kvh * q_per_kv + row_hi % q_per_kv;
-    const size_t idx_lo = (static_cast<size_t>(tok_lo) * p.q_heads + qh_lo) * p.n_splits + split;
-    const size_t idx_hi = (static_cast<size_t>(tok_hi) * p.q_heads + qh_hi) * p.n_splits + split;
+  if (TH == 1u) {
+    if (ok_lo || ok_hi) {
+      const uint32_t qh_lo = kvh * q_per_kv + row_lo % q_per_kv, qh_hi = kvh * q_per_kv + row_hi % q_per_kv;
+      const size_t idx_lo = (static_cast<size_t>(tok_lo) * p.q_heads + qh_lo) * p.n_splits + split;
+      const size_t idx_hi = (static_cast<size_t>(tok_hi) * p.q_heads + qh_hi) * p.n_splits + split;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        if (ok_lo) *reinterpret_cast<float2 *>(p.pacc + idx_lo * kD + 8 * j + 2 * tig) = make_float2(o[j][0], o[j][1]);
+        if (ok_hi) *reinterpret_cast<float2 *>(p.pacc + idx_hi * kD + 8 * j + 2 * tig) = make_float2(o[j][2], o[j][3]);
+      }
+      if (tig == 0u) {
+        if (ok_lo) { p.pmax[idx_lo] = m_lo == -INFINITY ? -INFINITY : m_lo * 0.0625f; p.pden[idx_lo] = l_lo; }
+        if (ok_hi) { p.pmax[idx_hi] = m_hi == -INFINITY ? -INFINITY : m_hi * 0.0625f; p.pden[idx_hi] = l_hi; }
+      }
+    }
+  } else {
+    // the TH states of a row meet in shared memory (the ring is free now), in slice order
+    float *so = reinterpret_cast<float *>(work);                      // [TH][16 MT][kMergeStride]
+    float *sm = so + TH * L::kRows * kMergeStride, *sl = sm + TH * L::kRows;
+    static_assert((TH * L::kRows * (kMergeStride + 2u)) * 4u <= L::kWorkBytes + kStages * L::kStageBytes, "meeting area");
+    __syncthreads();
+    const uint32_t r_lo = th * L::kRows + mt * 16u + gid, r_hi = r_lo + 8u;
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
-      if (ok_lo) *reinterpret_cast<float2 *>(p.pacc + idx_lo * kD + 8 * j + 2 * tig) = make_float2(o[j][0], o[j][1]);
-      if (ok_hi) *reinterpret_cast<float2 *>(p.pacc + idx_hi * kD + 8 * j + 2 * tig) = make_float2(o[j][2], o[j][3]);
+      *reinterpret_cast<float2 *>(so + r_lo * kMergeStride + 8 * j + 2 * tig) = make_float2(o[j][0], o[j][1]);
+      *reinterpret_cast<float2 *>(so + r_hi * kMergeStride + 8 * j + 2 * tig) = make_float2(o[j][2], o[j][3]);
     }
     if (tig == 0u) {
-      if (ok_lo) { p.pmax[idx_lo] = m_lo == -INFINITY ? -INFINITY : m_lo * 0.0625f; p.pden[idx_lo] = l_lo; }
-      if (ok_hi) { p.pmax[idx_hi] = m_hi == -INFINITY ? -INFINITY : m_hi * 0.0625f; p.pden[idx_hi] = l_hi; }
+      sm[r_lo] = m_lo; sl[r_lo] = l_lo;
+      sm[r_hi] = m_hi; sl[r_hi] = l_hi;
+    }
+    __syncthreads();
+    for (uint32_t i = threadIdx.x; i < L::kRows * (kD / 4u); i += NT) {
+      const uint32_t r = i / (kD / 4u), d = (i % (kD / 4u)) * 4u, row = chunk * L::kRows + r;
+      if (row >= m_rows) continue;
+      float M = -INFINITY;
+#pragma unroll
+      for (uint32_t h = 0; h < TH; ++h) M = fmaxf(M, sm[h * L::kRows + r]);
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      float den = 0.f;
+#pragma unroll
+      for (uint32_t h = 0; h < TH; ++h) {
+        const float mh = sm[h * L::kRows + r];
+        const float w = mh == -INFINITY ? 0.f : exp2f((mh - M) * kScaleLog2);
+        const float4 v = *reinterpret_cast<const float4 *>(so + (h * L::kRows + r) * kMergeStride + d);
+        acc.x = fmaf(w, v.x, acc.x); acc.y = fmaf(w, v.y, acc.y);
+        acc.z = fmaf(w, v.z, acc.z); acc.w = fmaf(w, v.w, acc.w);
+        den = fmaf(w, sl[h * L::kRows + r], den);
+      }
+      const uint32_t tok = row / q_per_kv, qh = kvh * q_per_kv + row % q_per_kv;
+      const size_t idx = (static_cast<size_t>(tok) * p.q_heads + qh) * p.n_splits + split;
+      *reinterpret_cast<float4 *>(p.pacc + idx * kD + d) = acc;
+      if (d == 0u) { p.pmax[idx] = M == -INFINITY ? -INFINITY : M * 0.0625f; p.pden[idx] = den; }
     }
   }
 
   // ---- decode: the split that owns `position` appends the new row to the cache
   if (DECODE && chunk == 0u && t0 <= start && start < t1) {
-    for (uint32_t d = threadIdx.x; d < kD; d += kThreads) {
+    for (uint32_t d = threadIdx.x; d < kD; d += NT) {
       const size_t off = (static_cast<size_t>(start) * p.kv_heads + kvh) * kD + d;
       const __nv_bfloat16 kn = p.k_new[kvh * kD + d], vn = p.v_new[kvh * kD + d];
       if (FP8) {
@@ -400,14 +499,26 @@ int reserve_scratch(size_t rows, float **acc, float **mx, float **dn) {
   return QWEN36_STATUS_SUCCESS;
 }
 
-template <bool FP8, bool DECODE>
-int launch(const Params &p, uint32_t chunks) {
-  if (q36::ensure_dynamic_smem(reinterpret_cast<const void *>(attention_splitk_tc_kernel<FP8, DECODE>),
-                               static_cast<int>(kSmemBytes)) != cudaSuccess)
+template <bool FP8, bool DECODE, int MT, int NW>
+int launch_mt(const Params &p, uint32_t chunks) {
+  using L = Layout<FP8, MT>;
+  if (q36::ensure_dynamic_smem(reinterpret_cast<const void *>(attention_splitk_tc_kernel<FP8, DECODE, MT, NW>),
+                               static_cast<int>(L::kSmemBytes)) != cudaSuccess)
     return QWEN36_STATUS_CUDA_ERROR;
   const dim3 grid(p.kv_heads, chunks, p.n_splits);
-  attention_splitk_tc_kernel<FP8, DECODE><<<grid, kThreads, kSmemBytes, q36::stream()>>>(p);
+  attention_splitk_tc_kernel<FP8, DECODE, MT, NW><<<grid, NW * 32, L::kSmemBytes, q36::stream()>>>(p);
   return q36::launch_status();
+}
+
+// Rows of one kv head (tokens x q heads per kv head) decide the CTA's shape: up to 16 rows, one row
+// tile and four timestep slices; up to 32, two and two; more, four row tiles per CTA and as many
+// CTAs (blockIdx.y) as that takes.
+template <bool FP8, bool DECODE>
+int launch(const Params &p) {
+  const uint32_t m_rows = p.tokens * (p.q_heads / p.kv_heads);
+  if (m_rows <= 16u) return launch_mt<FP8, DECODE, 1, 4>(p, 1);
+  if (m_rows <= 32u) return launch_mt<FP8, DECODE, 2, 8>(p, 1);
+  return launch_mt<FP8, DECODE, 4, 8>(p, (m_rows + 63u) / 64u);
 }
 
 }  // namespace
@@ -441,9 +552,7 @@ extern "C" int qwen36_attention_flash_splitk_prefill_bf16(const qwen36_attention
     const int rc = reserve_scratch(rows, &p.pacc, &p.pmax, &p.pden);
     if (rc != QWEN36_STATUS_SUCCESS) return rc;
   }
-  const uint32_t m_rows = p.tokens * (p.q_heads / p.kv_heads);
-  const uint32_t chunks = (m_rows + kRows - 1) / kRows;
-  const int rc = spec->kv_cache_dtype == 1 ? launch<true, false>(p, chunks) : launch<false, false>(p, chunks);
+  const int rc = spec->kv_cache_dtype == 1 ? launch<true, false>(p) : launch<false, false>(p);
   if (rc != QWEN36_STATUS_SUCCESS) return rc;
   attention_splitk_reduce_kernel<<<static_cast<unsigned>(spec->tokens * spec->shape.q_heads), kD, 0, q36::stream()>>>(
       p.pacc, p.pmax, p.pden, as_ptr<__nv_bfloat16>(spec->output_bf16), p.n_splits);
@@ -479,5 +588,5 @@ extern "C" int qwen36_attention_decode_split_tiled(const qwen36_attention_decode
   p.kv_heads = static_cast<uint32_t>(spec->shape.kv_heads);
   p.n_splits = static_cast<uint32_t>(n_splits);
   p.split_block = static_cast<uint32_t>(split_timesteps_per_block);
-  return spec->kv_cache_dtype == 1 ? launch<true, true>(p, 1) : launch<false, true>(p, 1);
+  return spec->kv_cache_dtype == 1 ? launch<true, true>(p) : launch<false, true>(p);
 }
