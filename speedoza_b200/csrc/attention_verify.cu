@@ -208,6 +208,25 @@ attention_splitk_tc_kernel(const Params p) {
     const uint32_t base = t0 + idx * kTile;
     const uint32_t dst = smem_u32(ring + (idx % kStages) * L::kStageBytes);
     constexpr uint32_t kChunks = L::kCacheRowBytes / 16u;             // 16-byte chunks per row: 16 or 32
+    if (base + kTile <= t1 && !(DECODE && start < base + kTile)) {
+      // whole tile of cache rows: a thread's copies differ by a fixed stride (its chunk, and the
+      // row's swizzle, stay the same from one of its rows to the next)
+      constexpr uint32_t kRowStep = NT / kChunks;                     // rows between two copies of a thread: 8 or 16 (4 / 8 with four warps)
+      const uint32_t r0 = threadIdx.x / kChunks, c = threadIdx.x % kChunks;
+      const size_t off = (static_cast<size_t>(base + r0) * p.kv_heads + kvh) * L::kCacheRowBytes + c * 16u;
+      const size_t step = static_cast<size_t>(kRowStep) * p.kv_heads * L::kCacheRowBytes;
+      const uint8_t *ks = ck + off, *vs = cv + off;
+#pragma unroll
+      for (uint32_t n = 0; n < kTile / kRowStep; ++n) {
+        const uint32_t r = r0 + n * kRowStep;
+        const uint32_t at = dst + (FP8 ? r * kD + c * 16u : r * kRowBytes + ((c ^ (r & 7u)) << 4));
+        cp_async16(at, ks, 16u);
+        cp_async16(at + kTile * L::kCacheRowBytes, vs, 16u);
+        ks += step;
+        vs += step;
+      }
+      return;
+    }
 #pragma unroll 4
     for (uint32_t i = threadIdx.x; i < kTile * kChunks; i += NT) {
       const uint32_t r = i / kChunks, c = i % kChunks, t = base + r;
@@ -289,34 +308,50 @@ attention_splitk_tc_kernel(const Params p) {
     if (!warp_has_rows || tw >= t1) continue;                         // padding rows / nothing visible: no work (warp-uniform)
 
     // ---- S = Q K^T for this warp's 16 rows x W timesteps
-    float s[W / 8][4];
+    // two accumulators per 8-timestep tile (even / odd k-steps): twice as many independent MMA chains
+    float s[W / 8][4], s2[W / 8][4];
 #pragma unroll
-    for (uint32_t j = 0; j < W / 8u; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+    for (uint32_t j = 0; j < W / 8u; ++j) {
+      s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+      s2[j][0] = s2[j][1] = s2[j][2] = s2[j][3] = 0.f;
+    }
     const uint32_t q_row = mt * 16u + (lane & 15u);
     const uint32_t q_addr = smem_u32(sq) + q_row * kRowBytes, q_sw = q_row & 7u;
 #pragma unroll 4
-    for (uint32_t kk = 0; kk < 16u; ++kk) {
-      uint32_t a[4];
-      ldmatrix_x4(a, q_addr + (((2u * kk + (lane >> 4)) ^ q_sw) << 4));
+    for (uint32_t kk = 0; kk < 16u; kk += 2u) {
 #pragma unroll
-      for (uint32_t jp = 0; jp < W / 16u; ++jp) {                     // two 8-timestep tiles per load
-        const uint32_t n_row = th * W + 16u * jp + 8u * (lane >> 4) + (lane & 7u);
-        uint32_t b[4];
-        ldmatrix_x4(b, smem_u32(sk) + n_row * kRowBytes + (((2u * kk + ((lane >> 3) & 1u)) ^ (n_row & 7u)) << 4));
-        mma16816<FP8>(s[2 * jp], a, b[0], b[1]);
-        mma16816<FP8>(s[2 * jp + 1], a, b[2], b[3]);
+      for (uint32_t par = 0; par < 2u; ++par) {
+        uint32_t a[4];
+        ldmatrix_x4(a, q_addr + (((2u * (kk + par) + (lane >> 4)) ^ q_sw) << 4));
+#pragma unroll
+        for (uint32_t jp = 0; jp < W / 16u; ++jp) {                   // two 8-timestep tiles per load
+          const uint32_t n_row = th * W + 16u * jp + 8u * (lane >> 4) + (lane & 7u);
+          uint32_t b[4];
+          ldmatrix_x4(b, smem_u32(sk) + n_row * kRowBytes + (((2u * (kk + par) + ((lane >> 3) & 1u)) ^ (n_row & 7u)) << 4));
+          mma16816<FP8>(par == 0u ? s[2 * jp] : s2[2 * jp], a, b[0], b[1]);
+          mma16816<FP8>(par == 0u ? s[2 * jp + 1] : s2[2 * jp + 1], a, b[2], b[3]);
+        }
       }
     }
+#pragma unroll
+    for (uint32_t j = 0; j < W / 8u; ++j) {
+      s[j][0] += s2[j][0]; s[j][1] += s2[j][1]; s[j][2] += s2[j][2]; s[j][3] += s2[j][3];
+    }
 
-    // ---- mask + online softmax (row gid: c0, c1 ; row gid + 8: c2, c3)
+    // ---- mask + online softmax (row gid: c0, c1 ; row gid + 8: c2, c3).  A slice that ends at or
+    // before `start` and before t1 is visible to every row that exists: nothing to mask (padding
+    // rows hold zero queries, their finite scores go nowhere).
     float mx_lo = -INFINITY, mx_hi = -INFINITY;
+    const bool all_visible = tw + W <= t1 && tw + W <= start + 1u;
 #pragma unroll
     for (uint32_t j = 0; j < W / 8u; ++j) {
 #pragma unroll
       for (uint32_t e = 0; e < 2u; ++e) {
-        const uint32_t t = tw + 8u * j + 2u * tig + e;
-        if (!(ok_lo && t <= lim_lo && t < t1)) s[j][e] = -INFINITY;
-        if (!(ok_hi && t <= lim_hi && t < t1)) s[j][2 + e] = -INFINITY;
+        if (!all_visible) {
+          const uint32_t t = tw + 8u * j + 2u * tig + e;
+          if (!(ok_lo && t <= lim_lo && t < t1)) s[j][e] = -INFINITY;
+          if (!(ok_hi && t <= lim_hi && t < t1)) s[j][2 + e] = -INFINITY;
+        }
         mx_lo = fmaxf(mx_lo, s[j][e]);
         mx_hi = fmaxf(mx_hi, s[j][2 + e]);
       }
@@ -347,13 +382,15 @@ attention_splitk_tc_kernel(const Params p) {
     sum_hi += __shfl_xor_sync(0xffffffffu, sum_hi, 2);
     l_lo = l_lo * al_lo + sum_lo;
     l_hi = l_hi * al_hi + sum_hi;
+    if (__any_sync(0xffffffffu, mn_lo != m_lo || mn_hi != m_hi)) {    // a running maximum moved (rare after the first tiles)
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        o[j][0] *= al_lo; o[j][1] *= al_lo;
+        o[j][2] *= al_hi; o[j][3] *= al_hi;
+      }
+    }
     m_lo = mn_lo;
     m_hi = mn_hi;
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      o[j][0] *= al_lo; o[j][1] *= al_lo;
-      o[j][2] *= al_hi; o[j][3] *= al_hi;
-    }
 
     // ---- O += P V: k = timestep (steps of 16), n = head dimension (32 tiles of 8)
 #pragma unroll
