@@ -491,11 +491,19 @@ attention_splitk_reduce_kernel(const float *__restrict__ pacc, const float *__re
   float m = -INFINITY;
   for (uint32_t s = 0; s < n_splits; ++s) m = fmaxf(m, pmax[flat * n_splits + s]);
   float dn = 0.f, acc = 0.f;
-  for (uint32_t s = 0; s < n_splits; ++s) {
-    const float pm = pmax[flat * n_splits + s];
-    const float w = pm == -INFINITY ? 0.f : expf(pm - m);
-    dn = fmaf(pden[flat * n_splits + s], w, dn);
-    acc = fmaf(pacc[(flat * n_splits + s) * kD + d], w, acc);
+  for (uint32_t s0 = 0; s0 < n_splits; s0 += 16u) {                  // sixteen loads in flight, sums in split order
+    float v[16];
+#pragma unroll
+    for (uint32_t i = 0; i < 16u; ++i) v[i] = __ldcg(pacc + (flat * n_splits + min(s0 + i, n_splits - 1u)) * kD + d);
+#pragma unroll
+    for (uint32_t i = 0; i < 16u; ++i) {
+      if (s0 + i < n_splits) {
+        const float pm = pmax[flat * n_splits + s0 + i];
+        const float w = pm == -INFINITY ? 0.f : expf(pm - m);
+        dn = fmaf(pden[flat * n_splits + s0 + i], w, dn);
+        acc = fmaf(v[i], w, acc);
+      }
+    }
   }
   out[flat * kD + d] = __float2bfloat16(dn > 0.f ? acc / dn : 0.f);
 }

@@ -250,7 +250,7 @@ decode_merge_append_kernel(const float *__restrict__ part_o, const float *__rest
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const float *po = part_o + static_cast<size_t>(qh) * n_parts * head_dim;
   const uint32_t d = min(threadIdx.x, head_dim - 1);              // idle threads fetch a valid address
-  float first[16];
+  float first[48];                                                // one CTA per SM and kv head gives 37 parts
   q36::lse_prefetch(po, n_parts, head_dim, d, first);             // in flight while the weights are formed
   float M, den;
   q36::lse_weights(part_m + static_cast<size_t>(qh) * n_parts, part_l + static_cast<size_t>(qh) * n_parts, n_parts,

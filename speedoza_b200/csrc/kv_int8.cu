@@ -456,11 +456,16 @@ kv_merge_kernel(const float *__restrict__ part_o, const float *__restrict__ part
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   Q36_ATRACE(1000u + blockIdx.x, 1);
+  // the outputs of the first 48 parts (one CTA per SM and kv head gives 37) travel with the (m, l)
+  // pairs: one round trip to L2 for the whole merge
+  float first[48];
+  if (threadIdx.x < head_dim) q36::lse_prefetch(po, n_parts, head_dim, threadIdx.x, first);
   float M, den;
   q36::lse_weights(pm, pl, n_parts, s_w, s_red, M, den);
   Q36_ATRACE(1000u + blockIdx.x, 2);
   for (uint32_t d = threadIdx.x; d < head_dim; d += kThreads) {
-    const float acc = q36::lse_accumulate(po, s_w, n_parts, head_dim, d);
+    const float acc = d == threadIdx.x ? q36::lse_accumulate(po, s_w, n_parts, head_dim, d, first)
+                                       : q36::lse_accumulate(po, s_w, n_parts, head_dim, d);
     if (FINAL) out[qh * head_dim + d] = __float2bfloat16(den > 0.f ? __fdiv_rn(acc, den) : 0.f);
     else out_o[qh * head_dim + d] = acc;
   }

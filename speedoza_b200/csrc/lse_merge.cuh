@@ -37,24 +37,28 @@ __device__ __forceinline__ void lse_weights(const float *pm, const float *pl, ui
   den_out = den;
 }
 
-// The first sixteen parts' values of output dim d, fetched ahead of the weights (the loads then
-// travel while lse_weights runs its reductions).  Clamped indices: no branch, no out-of-range read.
+// The first N parts' values of output dim d, fetched ahead of the weights (the loads then travel
+// while lse_weights runs its reductions: with N >= n_parts the whole merge costs one round trip to
+// L2 instead of one per batch).  Clamped indices: no branch, no out-of-range read.
+template <int N>
 __device__ __forceinline__ void lse_prefetch(const float *po, uint32_t n_parts, uint32_t head_dim, uint32_t d,
-                                             float (&v)[16]) {
+                                             float (&v)[N]) {
 #pragma unroll
-  for (uint32_t i = 0; i < 16; ++i) v[i] = __ldcg(po + static_cast<size_t>(min(i, n_parts - 1)) * head_dim + d);
+  for (uint32_t i = 0; i < static_cast<uint32_t>(N); ++i)
+    v[i] = __ldcg(po + static_cast<size_t>(min(i, n_parts - 1)) * head_dim + d);
 }
 
-// sum over parts of s_w[s] * po[s * head_dim + d], in part order; sixteen loads in flight at a time
-// (a plain loop pays the L2 latency once per part in its remainder iterations).  `first` holds the
-// values of parts 0 .. 15 from lse_prefetch.
+// sum over parts of s_w[s] * po[s * head_dim + d], in part order; `first` holds the values of parts
+// 0 .. N - 1 from lse_prefetch, the rest is fetched sixteen loads at a time (a plain loop pays the L2
+// latency once per part in its remainder iterations).
+template <int N>
 __device__ __forceinline__ float lse_accumulate(const float *po, const float *s_w, uint32_t n_parts,
-                                                uint32_t head_dim, uint32_t d, const float (&first)[16]) {
+                                                uint32_t head_dim, uint32_t d, const float (&first)[N]) {
   float acc = 0.f;
 #pragma unroll
-  for (uint32_t i = 0; i < 16; ++i)
+  for (uint32_t i = 0; i < static_cast<uint32_t>(N); ++i)
     if (i < n_parts) acc = fmaf(s_w[i], first[i], acc);
-  for (uint32_t s0 = 16; s0 < n_parts; s0 += 16) {
+  for (uint32_t s0 = N; s0 < n_parts; s0 += 16) {
     float v[16];
 #pragma unroll
     for (uint32_t i = 0; i < 16; ++i)
