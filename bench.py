@@ -411,6 +411,20 @@ def other_configs(backend, torch, synth, make_sampler=None):
                            backend=backend)
     out["fused_producers"] = {"rmsnorm_nvfp4_quantize_us": round(norm_us, 2), "hidden": hid,
                               "swiglu_nvfp4_quantize_us": round(swiglu_us, 2), "intermediate": inter}
+    # prefill form: silu(gate) * up of a [M, 2 * 17408] GEMM output straight to the down projection's NVFP4
+    # operand (qwen36_swiglu_nvfp4_quantize_rows); beside it the quantiser alone on a bf16 [M, 17408] block,
+    # which is the second half of the unfused chain.  Three input blocks in rotation (M = 8192: 1.7 GB > L2).
+    rows_out = []
+    for m_tok in (2048, 8192):
+        gus = [(torch.randn((m_tok, 2 * inter), generator=gen, device="cuda")).to(torch.bfloat16) for _ in range(3)]
+        res = backend.swiglu_nvfp4_quantize_rows(gus[0][:, :inter], gus[0][:, inter:], 0.37)
+        fused_us = _time_cuda(torch, lambda i: backend.swiglu_nvfp4_quantize_rows(gus[i % 3][:, :inter], gus[i % 3][:, inter:],
+                                                                                  0.37, *res), 60, warm=10, backend=backend)
+        byts = m_tok * inter * (4 + 0.5 + 1 / 16)
+        rows_out.append({"M": m_tok, "us": round(fused_us, 1), "gbs": round(byts / fused_us / 1e3, 1),
+                         "unfused_bf16_round_trip_bytes": m_tok * inter * 4})
+        del gus, res
+    out["fused_producers"]["swiglu_nvfp4_quantize_rows"] = rows_out
     # ---- config 3: FP8 lm_head + greedy argmax ---------------------------------------------
     rows, cols = synth.VOCAB, synth.HIDDEN
     w = torch.randint(0, 0x7F, (rows, cols), generator=gen, dtype=torch.uint8, device="cuda")

@@ -212,6 +212,30 @@ int qwen36_rmsnorm_nvfp4_quantize(const qwen36_rmsnorm_nvfp4_quantize_spec_t *sp
  * interpreter/opcodes/swiglu_nvfp4_quant.cuh:13-75). */
 int qwen36_swiglu_nvfp4_quantize(const qwen36_swiglu_nvfp4_quantize_spec_t *spec);
 
+/* Additive (no counterpart in qwen36_fp4.h): the prefill form of
+ * qwen36_swiglu_nvfp4_quantize.  y[r] = silu(gate[r]) * up[r] for `rows` rows of
+ * `intermediate` values (a multiple of 16), quantised row by row exactly as the
+ * single-vector entry does it (float32, no bf16 round trip): output_fp4 is
+ * [rows, intermediate / 2], output_scale_e4m3 the tiled 128 x 4 layout of
+ * [rows, intermediate / 16], i.e. the activation operand of qwen36_nvfp4_gemm for the
+ * down projection.  It replaces the reference's prefill chain "SwiGLU kernel ->
+ * bf16 [rows, intermediate] -> qwen36_nvfp4_quantize_rows"
+ * (crates/runtime/src/engine.rs:7395-7413) without the intermediate.  gate and up
+ * are rows of `input_row_stride` elements (>= intermediate, a multiple of 8; both
+ * halves of one [rows, 2 * intermediate] GEMM output qualify), 16-byte aligned. */
+typedef struct {
+  size_t rows;
+  size_t intermediate;
+  size_t input_row_stride;
+  qwen36_device_ptr_t gate_bf16;
+  qwen36_device_ptr_t up_bf16;
+  qwen36_device_ptr_t output_fp4;
+  qwen36_device_ptr_t output_scale_e4m3;
+  qwen36_device_ptr_t output_tensor_scale_f32;
+  float input_tensor_scale_f32;
+} qwen36_swiglu_nvfp4_quantize_rows_spec_t;
+int qwen36_swiglu_nvfp4_quantize_rows(const qwen36_swiglu_nvfp4_quantize_rows_spec_t *spec);
+
 /* Replaces qwen36_nvfp4_gemm (kernels-cuda/nvfp4_gemm.cu:341-409, a cuBLASLt
  * call).  Any m, n, k with k % 16 == 0.  alpha == 0 is read as 1.  Shapes with
  * m % 128 == 0 and k % 256 == 0 run on tcgen05 block-scaled MMA: persistent

@@ -78,6 +78,12 @@ class SwigluNvfp4QuantizeSpec(C.Structure):
                 ("output_tensor_scale_f32", DevicePtr), ("input_tensor_scale_f32", C.c_float)]
 
 
+class SwigluNvfp4QuantizeRowsSpec(C.Structure):
+    _fields_ = [("rows", size_t), ("intermediate", size_t), ("input_row_stride", size_t), ("gate_bf16", DevicePtr),
+                ("up_bf16", DevicePtr), ("output_fp4", DevicePtr), ("output_scale_e4m3", DevicePtr),
+                ("output_tensor_scale_f32", DevicePtr), ("input_tensor_scale_f32", C.c_float)]
+
+
 class Bf16MatvecArgmaxRowsSpec(C.Structure):
     _fields_ = [("rows", size_t), ("out_features", size_t), ("in_features", size_t), ("input_bf16", DevicePtr),
                 ("weight_bf16", DevicePtr), ("output_token_u32", DevicePtr),

@@ -121,6 +121,24 @@ class CudaBackend:
         _check("swiglu_nvfp4_quantize", self.lib.qwen36_swiglu_nvfp4_quantize(C.byref(spec)))
         return fp4, sf, ts
 
+    def swiglu_nvfp4_quantize_rows(self, gate_bf16, up_bf16, input_tensor_scale: float = 0.0, fp4=None, sf=None,
+                                   ts=None):
+        """[rows, n] blocks (views into one [rows, 2n] buffer are fine): silu(gate) * up, row by row as
+        swiglu_nvfp4_quantize -> (fp4 [rows, n / 2], tiled scales of [rows, n / 16], tensor scale [1])."""
+        rows, n = gate_bf16.shape
+        dev = gate_bf16.device
+        assert gate_bf16.stride(1) == 1 and up_bf16.stride(1) == 1 and gate_bf16.stride(0) == up_bf16.stride(0)
+        if fp4 is None:
+            fp4 = torch.empty((rows, n // 2), dtype=torch.uint8, device=dev)
+        if sf is None:
+            sf = torch.zeros(tiled_scale_bytes(rows, n // 16), dtype=torch.uint8, device=dev)
+        if ts is None:
+            ts = torch.empty(1, dtype=torch.float32, device=dev)
+        spec = abi.SwigluNvfp4QuantizeRowsSpec(rows, n, gate_bf16.stride(0), _dp(gate_bf16), _dp(up_bf16), _dp(fp4),
+                                               _dp(sf), _dp(ts), input_tensor_scale)
+        _check("swiglu_nvfp4_quantize_rows", self.lib.qwen36_swiglu_nvfp4_quantize_rows(C.byref(spec)))
+        return fp4, sf, ts
+
     def nvfp4_matvec(self, x_bf16, weight_u8, sf_tiled, tensor_scale, out=None) -> torch.Tensor:
         n_out, packed = weight_u8.shape
         k = x_bf16.numel()

@@ -14,6 +14,7 @@
 // trip, into shared memory as float32, two lanes share a group in the norm kernel and sixteen lanes
 // share one in the SwiGLU kernel, 256 threads per CTA instead of 32.
 #include "common.cuh"
+#include "nvfp4_quant_group.cuh"
 
 namespace {
 
@@ -159,7 +160,105 @@ swiglu_nvfp4_quantize_kernel(const __nv_bfloat16 *__restrict__ gate, const __nv_
   if (idx == 0 && tensor_scale != nullptr) *tensor_scale = global_scale;
 }
 
+// silu(gate) * up for a whole [rows, values] activation block -> NVFP4 codes + tiled scales, the
+// prefill form of the producer above: the bf16 [rows, values] intermediate of the unfused chain
+// (SwiGLU kernel, then qwen36_nvfp4_quantize_rows) is never written or read back.  Row r of the
+// output is what swiglu_nvfp4_quantize_kernel gives for row r alone (same expressions in float32,
+// no bf16 round trip), its scale bytes at the tiled position of (group, r).  Launch shape of the row
+// quantiser: blockDim (64, 4), a thread owns one 16-group of a row, rows advance by the grid with
+// the next row's 64 bytes already in flight.
+__global__ void __launch_bounds__(256)
+swiglu_nvfp4_quantize_rows_kernel(const __nv_bfloat16 *__restrict__ gate, const __nv_bfloat16 *__restrict__ up,
+                                  uint8_t *__restrict__ out_fp4, uint8_t *__restrict__ out_sf,
+                                  float *__restrict__ tensor_scale, uint32_t rows, uint32_t values, size_t stride,
+                                  float input_tensor_scale) {
+  const float g = input_tensor_scale > 0.0f ? input_tensor_scale : 1.0f;
+  const float six_g = __fmul_rn(6.0f, g), rcp6 = __frcp_rn(six_g);
+  const uint32_t groups = values >> 4, padded = (groups + 3u) & ~3u;
+  const uint32_t group = blockIdx.x * 64u + threadIdx.x;
+  const bool in_row = group < groups;
+  if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0 && threadIdx.y == 0 && tensor_scale != nullptr) *tensor_scale = g;
+
+  const uint32_t row_step = gridDim.y * 4u;
+  uint32_t row = blockIdx.y * 4u + threadIdx.y;
+  uint4 ng0 = make_uint4(0u, 0u, 0u, 0u), ng1 = ng0, nu0 = ng0, nu1 = ng0;
+  if (in_row && row < rows) {
+    const size_t at = static_cast<size_t>(row) * stride + group * 16u;
+    ng0 = __ldcs(reinterpret_cast<const uint4 *>(gate + at));
+    ng1 = __ldcs(reinterpret_cast<const uint4 *>(gate + at) + 1);
+    nu0 = __ldcs(reinterpret_cast<const uint4 *>(up + at));
+    nu1 = __ldcs(reinterpret_cast<const uint4 *>(up + at) + 1);
+  }
+  for (; row < rows; row += row_step) {
+    uint32_t sf_code = 0;
+    const uint32_t gw[8] = {ng0.x, ng0.y, ng0.z, ng0.w, ng1.x, ng1.y, ng1.z, ng1.w};
+    const uint32_t uw[8] = {nu0.x, nu0.y, nu0.z, nu0.w, nu1.x, nu1.y, nu1.z, nu1.w};
+    if (in_row && row + row_step < rows) {
+      const size_t at = static_cast<size_t>(row + row_step) * stride + group * 16u;
+      ng0 = __ldcs(reinterpret_cast<const uint4 *>(gate + at));
+      ng1 = __ldcs(reinterpret_cast<const uint4 *>(gate + at) + 1);
+      nu0 = __ldcs(reinterpret_cast<const uint4 *>(up + at));
+      nu1 = __ldcs(reinterpret_cast<const uint4 *>(up + at) + 1);
+    }
+    if (in_row) {
+      float y[16];
+      float amax = 0.0f;
+      uint32_t any = 0u, smallest = 0xffffffffu;                  // smallest nonzero magnitude, as bits - 1
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float gv = __uint_as_float((i & 1) ? (gw[i >> 1] & 0xffff0000u) : (gw[i >> 1] << 16));
+        const float uv = __uint_as_float((i & 1) ? (uw[i >> 1] & 0xffff0000u) : (uw[i >> 1] << 16));
+        const float silu = gv / (1.0f + expf(-gv));
+        y[i] = silu * uv;
+        amax = fmaxf(amax, fabsf(y[i]));
+        const uint32_t mag = __float_as_uint(y[i]) & 0x7fffffffu;
+        any |= mag;
+        smallest = min(smallest, mag - 1u);
+      }
+      uint32_t lo, hi;
+      q36::nvfp4_quantize_group(y, amax, any != 0u, smallest < 0x0f800000u, g, six_g, rcp6, lo, hi, sf_code);
+      *reinterpret_cast<uint2 *>(out_fp4 + (static_cast<size_t>(row) * (values >> 1) + group * 8u)) = make_uint2(lo, hi);
+    }
+    // the four scale bytes of a quad of groups form one word of the tiled layout (see q36::sf_offset)
+    const uint32_t lane4 = threadIdx.x & 3u;
+    uint32_t word = sf_code << (8u * lane4);
+    word |= __shfl_xor_sync(0xffffffffu, word, 1);
+    word |= __shfl_xor_sync(0xffffffffu, word, 2);
+    if (in_row) {
+      const size_t off = (static_cast<size_t>(group >> 2) + static_cast<size_t>(row >> 7) * (padded >> 2)) * 512u +
+                         (row & 31u) * 16u + ((row >> 5) & 3u) * 4u + lane4;
+      if ((group | 3u) < groups) {
+        if (lane4 == 0u) *reinterpret_cast<uint32_t *>(out_sf + off) = word;
+      } else {
+        out_sf[off] = static_cast<uint8_t>(sf_code);
+      }
+    }
+  }
+}
+
 }  // namespace
+
+extern "C" int qwen36_swiglu_nvfp4_quantize_rows(const qwen36_swiglu_nvfp4_quantize_rows_spec_t *spec) {
+  if (spec == nullptr) return QWEN36_STATUS_NULL_POINTER;
+  if (spec->rows == 0 || spec->intermediate == 0 || spec->gate_bf16.ptr == 0 || spec->up_bf16.ptr == 0 ||
+      spec->output_fp4.ptr == 0 || spec->output_scale_e4m3.ptr == 0)
+    return QWEN36_STATUS_INVALID_ARGUMENT;
+  // whole groups, 16-byte loads, 8-byte code stores, 4-byte scale words
+  if (spec->intermediate % 16 != 0 || spec->input_row_stride < spec->intermediate || spec->input_row_stride % 8 != 0 ||
+      (spec->gate_bf16.ptr & 15u) != 0 || (spec->up_bf16.ptr & 15u) != 0 || (spec->output_fp4.ptr & 7u) != 0 ||
+      (spec->output_scale_e4m3.ptr & 3u) != 0 || spec->rows >= (1ull << 31) || spec->intermediate >= (1ull << 31))
+    return QWEN36_STATUS_INVALID_ARGUMENT;
+  const size_t padded = q36::round_up(spec->intermediate / 16, 4);
+  const size_t gx = q36::div_ceil(padded, 64), row_chunks = q36::div_ceil(spec->rows, 4);
+  const size_t want = q36::div_ceil(static_cast<size_t>(q36::sm_count_current_device()) * 24, gx);
+  const dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(row_chunks < want ? row_chunks : want));
+  swiglu_nvfp4_quantize_rows_kernel<<<grid, dim3(64, 4), 0, q36::stream()>>>(
+      as_ptr<const __nv_bfloat16>(spec->gate_bf16), as_ptr<const __nv_bfloat16>(spec->up_bf16),
+      as_ptr<uint8_t>(spec->output_fp4), as_ptr<uint8_t>(spec->output_scale_e4m3),
+      as_ptr<float>(spec->output_tensor_scale_f32), static_cast<uint32_t>(spec->rows),
+      static_cast<uint32_t>(spec->intermediate), spec->input_row_stride, spec->input_tensor_scale_f32);
+  return q36::launch_status();
+}
 
 extern "C" int qwen36_rmsnorm_nvfp4_quantize(const qwen36_rmsnorm_nvfp4_quantize_spec_t *spec) {
   if (spec == nullptr) return QWEN36_STATUS_NULL_POINTER;

@@ -137,6 +137,7 @@ def test_ctypes_mirrors_match_header_sizes(tmp_path):
              "qwen36_lm_head_top2_margin_spec_t": abi.LmHeadTop2MarginSpec,
              "qwen36_lm_head_top8_rescore_spec_t": abi.LmHeadTop8RescoreSpec,
              "qwen36_swiglu_nvfp4_quantize_spec_t": abi.SwigluNvfp4QuantizeSpec,
+             "qwen36_swiglu_nvfp4_quantize_rows_spec_t": abi.SwigluNvfp4QuantizeRowsSpec,
              "qwen36_lm_head_fp8_argmax_spec_t": abi.LmHeadFp8ArgmaxSpec,
              "qwen36_lm_head_fp8_gemv_spec_t": abi.LmHeadFp8GemvSpec,
              "qwen36_sampling_spec_t": abi.SamplingSpec, "qwen36_sampling_rows_spec_t": abi.SamplingRowsSpec,

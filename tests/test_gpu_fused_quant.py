@@ -103,3 +103,92 @@ def test_swiglu_feeds_the_down_projection(backend):
     got = synth.bf16_bits_to_f32(bf16_host(out))
     ref = synth.bf16_bits_to_f32(want)
     assert np.linalg.norm(got - ref) / np.linalg.norm(ref) <= 1e-2
+
+
+def _special_rows(rng, rows, n):
+    """gate / up blocks with the values the codec treats specially planted in: all-zero groups, a
+    NaN, infinities, float32-subnormal products, exact E2M1 ties, huge and tiny magnitudes."""
+    gate = synth.f32_to_bf16_bits((rng.standard_normal((rows, n)) * 2.0).astype(np.float32))
+    up = np.stack([synth.activations(rng, 1, n, outlier_frac=0.01)[0] for _ in range(rows)])
+    f2b = lambda v: synth.f32_to_bf16_bits(np.array([v], np.float32))[0]
+    gate[0, :32] = 0; up[0, 16:48] = 0                       # zero groups (either factor)
+    gate[1, 40] = f2b(np.nan); up[1, 70] = f2b(np.inf); gate[1, 90] = f2b(-np.inf)
+    gate[2, :16] = f2b(-80.0); up[2, :16] = f2b(1e-10); up[2, 3] = f2b(3.0)      # products far below 2^-96 beside a normal one
+    gate[2, 16:32] = f2b(-87.0); up[2, 16:32] = f2b(1e-8)   # a whole group of subnormal products
+    gate[3, :16] = f2b(30.0)                                 # silu(30) = 30: exact quotients, E2M1 ties
+    up[3, :16] = synth.f32_to_bf16_bits(np.array([6, 0.75, 1.75, 3.5, 0.25, 1.25, 2.5, 5, -0.75, -1.75, -3.5, -6, 3, 1, 0.5, 4],
+                                                 np.float32) / 30.0)
+    up[min(4, rows - 1), 100:116] = f2b(3e38); gate[min(4, rows - 1), 100:116] = f2b(20.0)   # overflow to inf
+    return gate, up
+
+
+@pytest.mark.parametrize("rows,n,its", [(5, 17408, 0.37), (130, 1088, 0.0), (3, 16, 1.25), (257, 80, 0.0)])
+def test_swiglu_rows_equal_the_single_vector_entry_row_by_row(backend, rows, n, its):
+    """qwen36_swiglu_nvfp4_quantize_rows: every row's code bytes and scale bytes are those of
+    qwen36_swiglu_nvfp4_quantize on that row (itself byte-identical to the reference's kernel), also
+    with gate and up as the two halves of one [rows, 2 n] buffer; untouched scale bytes stay zero."""
+    rng = np.random.default_rng(rows * 7 + n)
+    gate, up = _special_rows(rng, rows, n) if n >= 128 else (
+        synth.f32_to_bf16_bits((rng.standard_normal((rows, n)) * 2.0).astype(np.float32)),
+        np.stack([synth.activations(rng, 1, n)[0] for _ in range(rows)]))
+    both = to_dev(np.concatenate([gate, up], axis=1))        # [rows, 2 n]: the gate_up GEMM's output layout
+    groups = n // 16
+    inner = (groups + 3) // 4 * 4
+    for g_d, u_d in ((to_dev(gate), to_dev(up)), (both[:, :n], both[:, n:])):
+        fp4, sf, ts = backend.swiglu_nvfp4_quantize_rows(g_d, u_d, its)
+        fp4_h, sf_h = fp4.cpu().numpy(), sf.cpu().numpy()
+        written = np.zeros(sf_h.size, dtype=bool)
+        check = range(rows) if rows <= 8 else sorted({0, 1, 2, 3, 4, 31, 32, 127, 128, 129, rows - 1} & set(range(rows)))
+        for r in check:
+            f1, s1, t1 = backend.swiglu_nvfp4_quantize(g_d[r].contiguous(), u_d[r].contiguous(), its)
+            assert ts.item() == t1.item()
+            assert np.array_equal(fp4_h[r], f1.cpu().numpy()), r
+            s1_h = s1.cpu().numpy()
+            for g in range(groups):
+                assert sf_h[orc.sf_offset(g, r, inner)] == s1_h[orc.sf_offset(g, 0, inner)], (r, g)
+        for r in range(rows):
+            for g in range(groups):
+                written[orc.sf_offset(g, r, inner)] = True
+        assert not sf_h[~written].any()
+
+
+def test_swiglu_rows_vs_oracle_and_down_projection(backend):
+    """Against the host oracle row by row (neighbouring codes only where libm and the device differ in
+    the last place), and as the activation operand of the down projection's GEMM."""
+    rng = np.random.default_rng(2025)
+    rows, n, n_out = 48, 2048, 256
+    gate = synth.f32_to_bf16_bits((rng.standard_normal((rows, n)) * 2.0).astype(np.float32))
+    up = np.stack([synth.activations(rng, 1, n, outlier_frac=0.01)[0] for _ in range(rows)])
+    fp4, sf, ts = backend.swiglu_nvfp4_quantize_rows(to_dev(gate), to_dev(up), 0.37)
+    fp4_h, sf_h = fp4.cpu().numpy(), sf.cpu().numpy()
+    groups, inner = n // 16, n // 16
+    for r in (0, 17, 47):
+        want = orc.swiglu_nvfp4_quantize(gate[r], up[r], 0.37)
+        row_sf = np.zeros_like(want["sf"])
+        for g in range(groups):
+            row_sf[orc.sf_offset(g, 0, inner)] = sf_h[orc.sf_offset(g, r, inner)]
+        assert_codes_close(fp4_h[r], row_sf, want["fp4"], want["sf"], n)
+    packed, sf_rm = synth.nvfp4_weight(rng, n_out, n)
+    a_sf = orc.retile_scales(sf_rm)
+    alpha = synth.WEIGHT_GLOBAL_SCALE * 0.37
+    c = backend.nvfp4_gemm(to_dev(packed), to_dev(a_sf), fp4, sf, alpha, n_out, rows, n)
+    want = synth.bf16_bits_to_f32(orc.nvfp4_gemm(packed, a_sf, fp4_h, sf_h, alpha, n_out, rows, n))
+    got = synth.bf16_bits_to_f32(bf16_host(c))
+    assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 1e-2
+
+
+def test_swiglu_rows_argument_checks(backend):
+    import ctypes as C
+    lib = backend.lib
+    g = torch.zeros((4, 64), dtype=torch.bfloat16, device="cuda")
+    fp4 = torch.zeros((4, 32), dtype=torch.uint8, device="cuda")
+    sf = torch.zeros(512, dtype=torch.uint8, device="cuda")
+    dp = lambda t: abi.DevicePtr(0 if t is None else t.data_ptr())
+
+    def spec(rows=4, n=64, stride=64, gate=g, up=g, out=fp4, scales=sf):
+        return abi.SwigluNvfp4QuantizeRowsSpec(rows, n, stride, dp(gate), dp(up), dp(out), dp(scales), dp(None), 0.0)
+    assert lib.qwen36_swiglu_nvfp4_quantize_rows(None) == abi.NULL_POINTER
+    assert lib.qwen36_swiglu_nvfp4_quantize_rows(C.byref(spec())) == abi.SUCCESS
+    for bad in (spec(rows=0), spec(n=0), spec(n=40), spec(stride=48), spec(stride=68), spec(gate=None), spec(up=None),
+                spec(out=None), spec(scales=None), spec(gate=g.view(-1)[4:].view(-1))):
+        assert lib.qwen36_swiglu_nvfp4_quantize_rows(C.byref(bad)) == abi.INVALID_ARGUMENT
