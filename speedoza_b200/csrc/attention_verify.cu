@@ -294,11 +294,14 @@ attention_splitk_tc_kernel(const Params p) {
           e4m3x16_to_f16(*reinterpret_cast<const uint4 *>(sk + r * kD + c * 16u), klo, khi);
           e4m3x16_to_f16(*reinterpret_cast<const uint4 *>(sv + r * kD + c * 16u), vlo, vhi);
         }
-        const uint32_t sw = r & 7u;
-        *reinterpret_cast<uint4 *>(wk + r * kRowBytes + (((2u * c) ^ sw) << 4)) = klo;
-        *reinterpret_cast<uint4 *>(wk + r * kRowBytes + (((2u * c + 1u) ^ sw) << 4)) = khi;
-        *reinterpret_cast<uint4 *>(wv + r * kRowBytes + (((2u * c) ^ sw) << 4)) = vlo;
-        *reinterpret_cast<uint4 *>(wv + r * kRowBytes + (((2u * c + 1u) ^ sw) << 4)) = vhi;
+        // A 16-byte store is served eight lanes at a time: lanes c and c + 4 of such a group own chunk
+        // pairs that fall on the same banks, so the upper four store their odd chunk first.
+        const uint32_t sw = r & 7u, flip = (c >> 2) & 1u;
+        const uint32_t first = ((2u * c + flip) ^ sw) << 4, second = ((2u * c + 1u - flip) ^ sw) << 4;
+        *reinterpret_cast<uint4 *>(wk + r * kRowBytes + first) = flip ? khi : klo;
+        *reinterpret_cast<uint4 *>(wv + r * kRowBytes + first) = flip ? vhi : vlo;
+        *reinterpret_cast<uint4 *>(wk + r * kRowBytes + second) = flip ? klo : khi;
+        *reinterpret_cast<uint4 *>(wv + r * kRowBytes + second) = flip ? vlo : vhi;
       }
       __syncthreads();
       sk = wk;
