@@ -7,15 +7,16 @@
 //     reference's fixed-size splits, partials only, plus the cache append by the split that owns
 //     the position; replaces kernels-cuda/attention_decode_tiled.cu:159-357,370-403.
 //
-// One kernel serves both.  A CTA = (kv head, 64-row chunk of the (token, q head) rows, split): the
+// One kernel serves both.  A CTA = (kv head, chunk of up to 64 (token, q head) rows, split): the
 // rows of ALL q heads that share the kv head ride in one CTA, so K / V are read once per kv head
-// (the reference launches one CTA per q head and reads them q_per_kv times).  Four warps, each owns
-// 16 rows: S = Q K^T and O += P V as mma.sync.m16n8k16 with float32 accumulation, online softmax
-// in registers (a row lives in the four lanes of a quad), probabilities rounded to the operand
-// type before P V as in the reference, l accumulated from the unrounded values.  K / V tiles of 64
-// rows are staged in shared memory in 16-byte chunks XOR-swizzled by row, which makes every
-// ldmatrix conflict-free.  A BF16 cache multiplies in bf16; an FP8 cache is expanded E4M3 -> f16
-// (exact) and multiplies in f16 with q rounded to f16 (11 significant bits, q needs 8).
+// (the reference launches one CTA per q head and reads them q_per_kv times).  A warp owns a 16-row
+// tile of those rows and a slice of the timesteps of every 64-row K / V tile (see the kernel):
+// S = Q K^T and O += P V as mma.sync.m16n8k16 with float32 accumulation, online softmax in
+// registers (a row lives in the four lanes of a quad), probabilities rounded to the operand type
+// before P V as in the reference, l accumulated from the unrounded values.  K / V tiles travel
+// through a cp.async ring and sit in shared memory in 16-byte chunks XOR-swizzled by row, which
+// makes every ldmatrix conflict-free.  A BF16 cache multiplies in bf16; an FP8 cache is expanded
+// E4M3 -> f16 (exact) and multiplies in f16 with q rounded to f16 (11 significant bits, q needs 8).
 //
 // Partial contract (what the reduce and the reference's callers see):
 //   acc[((token * q_heads + qh) * n_splits + split) * head_dim + d]  unnormalised, float32
@@ -157,11 +158,11 @@ __device__ __forceinline__ uint8_t encode_e4m3_append(float v) {
 
 // FP8: the cache holds E4M3 bytes and the product runs in f16; otherwise bf16 throughout.
 // DECODE: one token, timestep == position comes from k_new / v_new, the owning split appends it.
-// MT: 16-row tiles of (token, q head) rows per CTA.  The four warps form MT x TH: warp w works on row
+// MT: 16-row tiles of (token, q head) rows per CTA.  The NW warps form MT x TH: warp w works on row
 // tile w % MT and on the timesteps [th * 64 / TH, (th + 1) * 64 / TH) of every 64-row KV tile, th =
 // w / MT, with an online-softmax state of its own; the TH states of a row meet once, after the loop.
-// So 4 query tokens x 6 heads (24 rows, MT = 2) or a decode token (6 rows, MT = 1) keep all four
-// tensor cores busy on rows that exist, instead of three warps out of four multiplying padding.
+// So 4 query tokens x 6 heads (24 rows, MT = 2) or a decode token (6 rows, MT = 1) keep every
+// tensor core busy on rows that exist, instead of three warps out of four multiplying padding.
 // K / V tiles arrive through a three-deep cp.async ring, two tiles ahead of the one being multiplied.
 template <bool FP8, bool DECODE, int MT, int NW>
 __global__ void __launch_bounds__(NW * 32, 1)
