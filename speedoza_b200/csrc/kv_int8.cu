@@ -112,6 +112,85 @@ kv_encode_kernel(const __nv_bfloat16 *__restrict__ k, const __nv_bfloat16 *__res
   }
 }
 
+// The same encode for head_dim 256 and many vectors (prefill: tokens x kv_heads x 2 of them), built
+// to run at the HBM rate: a warp walks vectors with a stride of the grid, a lane owns eight values
+// (one 16-byte load, kept in registers for both passes) and the next vector's load is in flight
+// while the current ones are worked on.  v / scale becomes v * (1 / scale) with the correctly rounded
+// reciprocal: that product is within 2^-16 of the IEEE quotient (|quotient| <= 127), so it rounds to
+// the same integer unless it lies within 2^-14 of a tie, and those values (and every vector whose
+// maximum is zero, tiny, huge, infinite or a NaN) take the reference's division.
+__device__ __forceinline__ void kv_encode_vector256(const uint4 &cur, size_t vec, unsigned lane, int8_t *__restrict__ kq,
+                                                    int8_t *__restrict__ vq, float *__restrict__ meta, size_t position,
+                                                    size_t kv_heads) {
+  constexpr size_t D = 256;
+  const size_t which = vec & 1, row = position * kv_heads + (vec >> 1);
+  const uint32_t w[4] = {cur.x, cur.y, cur.z, cur.w};
+  // max |x| on the bf16 bit patterns, two at a time (for finite values the order of magnitudes is the
+  // order of their bits); a NaN shows up as a maximum above the infinity pattern
+  uint32_t m2 = __vmaxu2(__vmaxu2(w[0] & 0x7fff7fffu, w[1] & 0x7fff7fffu), __vmaxu2(w[2] & 0x7fff7fffu, w[3] & 0x7fff7fffu));
+  const uint32_t mx = __reduce_max_sync(0xffffffffu, max(m2 & 0xffffu, m2 >> 16));
+  float x[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    x[2 * i] = __uint_as_float(w[i] << 16);
+    x[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+  uint32_t b[8];
+  float scale;
+  if (mx >= 0x0100u && mx <= 0x7e00u) {                             // warp-uniform: amax finite, in [2^-124, 2^125), no NaN
+    scale = __fdiv_rn(__uint_as_float(mx << 16), 127.0f);
+    // Round to nearest even by adding 1.5 * 2^23 (no conversion instructions: they run at a fraction
+    // of the FP32 rate): |q| <= 127 (1 + 2^-23) because |x| <= amax, so the sum's low mantissa bits
+    // are the integer in two's complement and its low byte is the code, already within +-127.
+    const float rcp = __frcp_rn(scale);
+    constexpr float kMagic = 12582912.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float q = __fmul_rn(x[i], rcp);
+      const float t = __fadd_rn(q, kMagic), rf = __fsub_rn(t, kMagic);
+      b[i] = __float_as_uint(t);
+      if (fabsf(__fsub_rn(q, rf)) > 0.5f - 0x1p-14f) b[i] = static_cast<uint32_t>(quantize_s8(x[i], scale));
+    }
+  } else {
+    // zero, tiny, huge, infinite or NaN-bearing vectors: the reference's own arithmetic
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(x[i]));
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    scale = __fdiv_rn(amax, 127.0f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) b[i] = static_cast<uint32_t>(quantize_s8(x[i], scale));
+  }
+  if (lane == 0) meta[row * 2 + which] = scale;
+  const uint32_t lo = __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);
+  const uint32_t hi = __byte_perm(__byte_perm(b[4], b[5], 0x0040), __byte_perm(b[6], b[7], 0x0040), 0x5410);
+  *reinterpret_cast<uint2 *>((which ? vq : kq) + row * D + lane * 8u) = make_uint2(lo, hi);
+}
+
+__global__ void __launch_bounds__(kThreads)
+kv_encode_rows256_kernel(const __nv_bfloat16 *__restrict__ k, const __nv_bfloat16 *__restrict__ v,
+                         int8_t *__restrict__ kq, int8_t *__restrict__ vq, float *__restrict__ meta, size_t position,
+                         size_t vecs, size_t kv_heads) {
+  constexpr size_t D = 256;
+  const unsigned lane = threadIdx.x & 31u;
+  const size_t step = static_cast<size_t>(gridDim.x) * kWarps;
+  size_t vec = static_cast<size_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
+  auto fetch = [&](size_t i) {
+    return i < vecs ? __ldcs(reinterpret_cast<const uint4 *>(((i & 1) ? v : k) + (i >> 1) * D) + lane)
+                    : make_uint4(0u, 0u, 0u, 0u);
+  };
+  // two vectors per turn, the next two already requested: two 16-byte loads per lane always in flight
+  uint4 n0 = fetch(vec), n1 = fetch(vec + step);
+  for (; vec < vecs; vec += 2 * step) {
+    const uint4 c0 = n0, c1 = n1;
+    n0 = fetch(vec + 2 * step);
+    n1 = fetch(vec + 3 * step);
+    kv_encode_vector256(c0, vec, lane, kq, vq, meta, position, kv_heads);
+    if (vec + step < vecs) kv_encode_vector256(c1, vec + step, lane, kq, vq, meta, position, kv_heads);
+  }
+}
+
 // --------------------------------------------------------------- attention
 
 // 4 signed bytes -> 4 floats without integer-to-float conversions: flip the
@@ -1068,6 +1147,20 @@ extern "C" int qwen36_turboquant_encode_kv_rows(const qwen36_turboquant_encode_r
     return QWEN36_STATUS_INVALID_ARGUMENT;
   if (spec->tokens == 0) return QWEN36_STATUS_SUCCESS;
   const size_t vecs = spec->tokens * spec->shape.kv_heads * 2;
+  if (spec->shape.head_dim == 256 && vecs >= 4096 &&
+      ((spec->k_bf16.ptr | spec->v_bf16.ptr) & 15u) == 0 && ((spec->k_quantized_i8.ptr | spec->v_quantized_i8.ptr) & 7u) == 0) {
+    // one wave: every block must be resident at once, or the strided walk leaves the late blocks a tail of their own
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kv_encode_rows256_kernel, kThreads, 0) != cudaSuccess || per_sm < 1)
+      per_sm = 4;
+    const size_t blocks = std::min(q36::div_ceil(vecs, static_cast<size_t>(kWarps)),
+                                   static_cast<size_t>(sm_count()) * static_cast<size_t>(per_sm));
+    kv_encode_rows256_kernel<<<static_cast<unsigned>(blocks), kThreads, 0, q36::stream()>>>(
+        as_ptr<const __nv_bfloat16>(spec->k_bf16), as_ptr<const __nv_bfloat16>(spec->v_bf16),
+        as_ptr<int8_t>(spec->k_quantized_i8), as_ptr<int8_t>(spec->v_quantized_i8),
+        as_ptr<float>(spec->metadata_f32), spec->position, vecs, spec->shape.kv_heads);
+    return q36::launch_status();
+  }
   kv_encode_kernel<<<static_cast<unsigned>(q36::div_ceil(vecs, kWarps)), kThreads, 0, q36::stream()>>>(
       as_ptr<const __nv_bfloat16>(spec->k_bf16), as_ptr<const __nv_bfloat16>(spec->v_bf16),
       as_ptr<int8_t>(spec->k_quantized_i8), as_ptr<int8_t>(spec->v_quantized_i8),

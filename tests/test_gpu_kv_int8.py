@@ -38,6 +38,43 @@ def test_encode_bit_exact(backend, tokens, kv_heads, head_dim):
     assert np.array_equal(kq.cpu().numpy(), kq_o) and np.array_equal(vq.cpu().numpy(), vq_o)
 
 
+def test_encode_bulk_rows_bit_exact_with_special_vectors(backend):
+    """The many-vector route of qwen36_turboquant_encode_kv_rows (head_dim 256, 4096 vectors or more):
+    codes and scales equal the oracle's, with vectors planted that leave its fast arithmetic: zero, exact
+    ties at scale 1 and at other scales, NaN, infinity, magnitudes near both ends of the bf16 range, and
+    a power-of-two ladder whose quotients sit on or next to half-integers."""
+    rng = np.random.default_rng(77)
+    tokens, kv_heads, head_dim = 1536, 4, 256
+    _, k, v = synth.qkv(rng, tokens, 2 * kv_heads, kv_heads, head_dim, outliers=4)
+    f2b = lambda a: synth.f32_to_bf16_bits(np.asarray(a, np.float32))
+    ties = np.resize(np.array([127, 0.5, 1.5, 2.5, -0.5, -1.5, 126.5, -126.5, 63.5, -63.5, 3.5, 100.5], np.float32), head_dim)
+    k[0, 0] = 0
+    k[1, 1] = f2b(ties)                                     # scale 1
+    v[2, 2] = f2b(ties * 0.25)                              # scale 2^-2: the same ties
+    v[3, 0] = f2b(ties * 3.0)                               # scale 3: quotients next to, not on, half-integers
+    k[4, 3] = f2b(np.resize(np.array([1e-38, -3e-39, 2e-38, 5e-39], np.float32), head_dim))      # tiny: scale < 2^-60
+    v[5, 1] = f2b(np.resize(np.array([3e38, -1e38, 2e37, 1e30], np.float32), head_dim))          # huge: scale > 2^60
+    k[8, 0] = f2b(np.resize(127.0 * 2.0 ** -np.arange(0, 20, dtype=np.float32), head_dim))       # 127, 63.5, 31.75, ...
+    ladder = (np.arange(head_dim, dtype=np.float32) - 128.0) * 0.5                                # every half-integer in [-64, 63.5]
+    ladder[0] = 127.0
+    v[9, 2] = f2b(ladder)
+    (kq, vq, meta), (kq_o, vq_o, meta_o) = encode_both(backend, k, v, tokens, kv_heads, head_dim)
+    assert np.array_equal(meta.cpu().numpy().view(np.uint32), meta_o.view(np.uint32))
+    assert np.array_equal(kq.cpu().numpy(), kq_o) and np.array_equal(vq.cpu().numpy(), vq_o)
+    # and the few-vector route gives the same bytes (500 tokens per call stay below the switch), also for
+    # NaN and infinity, whose conversion to an integer the host leaves undefined (the device gives 0)
+    k[6, 2, 7] = f2b([np.nan])[0]
+    v[7, 3, 9] = f2b([np.inf])[0]
+    v[10, 1, 3] = f2b([-np.inf])[0]
+    k[10, 1, 200] = f2b([np.nan])[0]
+    backend.turboquant_encode_kv_rows(to_dev(k), to_dev(v), kq, vq, meta, 0)
+    kq2 = torch.zeros_like(kq); vq2 = torch.zeros_like(vq); meta2 = torch.zeros_like(meta)
+    for t0 in range(0, tokens, 500):
+        t1 = min(t0 + 500, tokens)
+        backend.turboquant_encode_kv_rows(to_dev(k[t0:t1]), to_dev(v[t0:t1]), kq2, vq2, meta2, t0)
+    assert torch.equal(kq, kq2) and torch.equal(vq, vq2) and torch.equal(meta.view(torch.int32), meta2.view(torch.int32))
+
+
 def test_encode_single_position_entry_appends(backend):
     rng = np.random.default_rng(4)
     _, k, v = synth.qkv(rng, 6, 8, 4, 256)
