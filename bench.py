@@ -551,7 +551,8 @@ def profile_case(name: str):
     """Runs one small, fixed case of a single kernel a few times (for `ncu -k ... -c ...`):
     gemv_gate_up | gemv_down | gemm_gate_up_2048 | gemm_down_2048 | lm_head_m1 | lm_head_m4 |
     attention_32768 | quantize_2048 | bf16_argmax_m1 | bf16_argmax_m4 | decode_fp8_32768 | decode_bf16_32768 |
-    verify_fp8_32768 | verify_bf16_32768 | gemv_sweep_layer.  Inputs exceed L2 but stay well under a few GB."""
+    verify_fp8_32768 | verify_bf16_32768 | gemv_sweep_layer | swiglu_rows_2048 | kv_encode_65536.  Inputs exceed L2
+    but stay well under a few GB."""
     import torch
     from speedoza_b200 import synth
     from speedoza_b200.backend import CudaBackend
@@ -660,6 +661,20 @@ def profile_case(name: str):
         x = torch.randn((m_tok, 17408), generator=gen, device="cuda").to(torch.bfloat16)
         for _ in range(3):
             b.nvfp4_quantize_rows(x, 0.37)
+    elif name.startswith("swiglu_rows_"):
+        m_tok = int(name.rsplit("_", 1)[1])
+        gu = torch.randn((m_tok, 2 * 17408), generator=gen, device="cuda").to(torch.bfloat16)
+        for _ in range(3):
+            b.swiglu_nvfp4_quantize_rows(gu[:, :17408], gu[:, 17408:], 0.37)
+    elif name.startswith("kv_encode_"):
+        tokens = int(name.rsplit("_", 1)[1])
+        kk = torch.randn((tokens, 4, 256), generator=gen, device="cuda").to(torch.bfloat16)
+        vv = torch.randn((tokens, 4, 256), generator=gen, device="cuda").to(torch.bfloat16)
+        kq = torch.empty((tokens, 4, 256), dtype=torch.int8, device="cuda")
+        vq = torch.empty_like(kq)
+        meta = torch.empty((tokens, 4, 2), dtype=torch.float32, device="cuda")
+        for _ in range(3):
+            b.turboquant_encode_kv_rows(kk, vv, kq, vq, meta, 0)
     else:
         raise SystemExit(f"unknown profile case {name}")
     torch.cuda.synchronize()

@@ -119,11 +119,8 @@ kv_encode_kernel(const __nv_bfloat16 *__restrict__ k, const __nv_bfloat16 *__res
 // reciprocal: that product is within 2^-16 of the IEEE quotient (|quotient| <= 127), so it rounds to
 // the same integer unless it lies within 2^-14 of a tie, and those values (and every vector whose
 // maximum is zero, tiny, huge, infinite or a NaN) take the reference's division.
-__device__ __forceinline__ void kv_encode_vector256(const uint4 &cur, size_t vec, unsigned lane, int8_t *__restrict__ kq,
-                                                    int8_t *__restrict__ vq, float *__restrict__ meta, size_t position,
-                                                    size_t kv_heads) {
-  constexpr size_t D = 256;
-  const size_t which = vec & 1, row = position * kv_heads + (vec >> 1);
+__device__ __forceinline__ void kv_encode_vector256(const uint4 &cur, unsigned lane, int8_t *__restrict__ dst,
+                                                    float *__restrict__ meta_slot) {
   const uint32_t w[4] = {cur.x, cur.y, cur.z, cur.w};
   // max |x| on the bf16 bit patterns, two at a time (for finite values the order of magnitudes is the
   // order of their bits); a NaN shows up as a maximum above the infinity pattern
@@ -137,19 +134,31 @@ __device__ __forceinline__ void kv_encode_vector256(const uint4 &cur, size_t vec
   }
   uint32_t b[8];
   float scale;
-  if (mx >= 0x0100u && mx <= 0x7e00u) {                             // warp-uniform: amax finite, in [2^-124, 2^125), no NaN
-    scale = __fdiv_rn(__uint_as_float(mx << 16), 127.0f);
+  bool redo = !(mx >= 0x0100u && mx <= 0x7e00u);                    // warp-uniform: amax finite, in [2^-124, 2^125), no NaN
+  if (!redo) {
+    // amax / 127, correctly rounded, from the rounded reciprocal and two FMAs (127 is far from an
+    // all-ones significand and the quotient is a normal number here, so the correction is exact)
+    const float amax = __uint_as_float(mx << 16);
+    constexpr float kR127 = 0x1.020408p-7f;                         // RN(1 / 127)
+    const float s0 = __fmul_rn(amax, kR127);
+    scale = fmaf(fmaf(-s0, 127.0f, amax), kR127, s0);
     // Round to nearest even by adding 1.5 * 2^23 (no conversion instructions: they run at a fraction
     // of the FP32 rate): |q| <= 127 (1 + 2^-23) because |x| <= amax, so the sum's low mantissa bits
     // are the integer in two's complement and its low byte is the code, already within +-127.
     const float rcp = __frcp_rn(scale);
     constexpr float kMagic = 12582912.0f;
+    float worst = 0.f;                                              // largest distance of a product from its integer
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const float q = __fmul_rn(x[i], rcp);
-      const float t = __fadd_rn(q, kMagic), rf = __fsub_rn(t, kMagic);
+      const float t = __fadd_rn(q, kMagic);
       b[i] = __float_as_uint(t);
-      if (fabsf(__fsub_rn(q, rf)) > 0.5f - 0x1p-14f) b[i] = static_cast<uint32_t>(quantize_s8(x[i], scale));
+      worst = fmaxf(worst, fabsf(__fsub_rn(q, __fsub_rn(t, kMagic))));
+    }
+    redo = worst > 0.5f - 0x1p-14f;                                 // some product too close to a tie: this lane's eight again, exactly
+    if (redo) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) b[i] = static_cast<uint32_t>(quantize_s8(x[i], scale));
     }
   } else {
     // zero, tiny, huge, infinite or NaN-bearing vectors: the reference's own arithmetic
@@ -162,32 +171,39 @@ __device__ __forceinline__ void kv_encode_vector256(const uint4 &cur, size_t vec
 #pragma unroll
     for (int i = 0; i < 8; ++i) b[i] = static_cast<uint32_t>(quantize_s8(x[i], scale));
   }
-  if (lane == 0) meta[row * 2 + which] = scale;
+  if (lane == 0) *meta_slot = scale;
   const uint32_t lo = __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);
   const uint32_t hi = __byte_perm(__byte_perm(b[4], b[5], 0x0040), __byte_perm(b[6], b[7], 0x0040), 0x5410);
-  *reinterpret_cast<uint2 *>((which ? vq : kq) + row * D + lane * 8u) = make_uint2(lo, hi);
+  *reinterpret_cast<uint2 *>(dst + lane * 8u) = make_uint2(lo, hi);
 }
 
+// The grid holds an even number of warps, so a warp stays with K or with V for its whole walk and
+// its source, destination and scale pointers advance by constants.
 __global__ void __launch_bounds__(kThreads)
 kv_encode_rows256_kernel(const __nv_bfloat16 *__restrict__ k, const __nv_bfloat16 *__restrict__ v,
                          int8_t *__restrict__ kq, int8_t *__restrict__ vq, float *__restrict__ meta, size_t position,
                          size_t vecs, size_t kv_heads) {
   constexpr size_t D = 256;
   const unsigned lane = threadIdx.x & 31u;
-  const size_t step = static_cast<size_t>(gridDim.x) * kWarps;
+  const size_t step = static_cast<size_t>(gridDim.x) * kWarps;     // even
   size_t vec = static_cast<size_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
-  auto fetch = [&](size_t i) {
-    return i < vecs ? __ldcs(reinterpret_cast<const uint4 *>(((i & 1) ? v : k) + (i >> 1) * D) + lane)
-                    : make_uint4(0u, 0u, 0u, 0u);
-  };
+  const size_t which = vec & 1, th0 = vec >> 1, th_step = step >> 1;
+  const uint4 *src = reinterpret_cast<const uint4 *>((which ? v : k) + th0 * D) + lane;
+  int8_t *dst = (which ? vq : kq) + (position * kv_heads + th0) * D;
+  float *slot = meta + (position * kv_heads + th0) * 2 + which;
+  const size_t src_step = th_step * (D / 8);                        // in 16-byte units
   // two vectors per turn, the next two already requested: two 16-byte loads per lane always in flight
-  uint4 n0 = fetch(vec), n1 = fetch(vec + step);
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+  uint4 n0 = vec < vecs ? __ldcs(src) : zero, n1 = vec + step < vecs ? __ldcs(src + src_step) : zero;
   for (; vec < vecs; vec += 2 * step) {
     const uint4 c0 = n0, c1 = n1;
-    n0 = fetch(vec + 2 * step);
-    n1 = fetch(vec + 3 * step);
-    kv_encode_vector256(c0, vec, lane, kq, vq, meta, position, kv_heads);
-    if (vec + step < vecs) kv_encode_vector256(c1, vec + step, lane, kq, vq, meta, position, kv_heads);
+    src += 2 * src_step;
+    n0 = vec + 2 * step < vecs ? __ldcs(src) : zero;
+    n1 = vec + 3 * step < vecs ? __ldcs(src + src_step) : zero;
+    kv_encode_vector256(c0, lane, dst, slot);
+    if (vec + step < vecs) kv_encode_vector256(c1, lane, dst + th_step * D, slot + th_step * 2);
+    dst += 2 * th_step * D;
+    slot += 4 * th_step;
   }
 }
 
