@@ -36,6 +36,14 @@ rmsnorm_nvfp4_quantize_kernel(const __nv_bfloat16 *__restrict__ input, const __n
   __shared__ float scratch[kNormSumThreads];
   __shared__ float total;
   extern __shared__ __align__(16) float value[];            // input (+ residual) as float32, read three times below
+  // The norm weights of this thread's eight values (first pass of the quantise loop below) travel
+  // with the input instead of after the reductions.
+  float w_first[8];
+  {
+    const size_t start = (static_cast<size_t>(threadIdx.x) >> 1) * 16 + (threadIdx.x & 1u) * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) w_first[i] = start + i < hidden ? __bfloat162float(weight[start + i]) : 0.0f;
+  }
   // ---- one round trip to L2: every thread fetches its elements at once -------------------------
   constexpr int kBatch = 8;                                  // 8192 elements per pass: loads issued before any use
   for (size_t base = 0; base < hidden; base += static_cast<size_t>(kBatch) * kNormThreads) {
@@ -104,7 +112,7 @@ rmsnorm_nvfp4_quantize_kernel(const __nv_bfloat16 *__restrict__ input, const __n
       const size_t d = start + i;
       weighted[i] = 0.0f;
       if (live && d < hidden) {
-        const float w = value[d] * norm_scale * (1.0f + __bfloat162float(weight[d]));
+        const float w = value[d] * norm_scale * (1.0f + (hg0 == 0 ? w_first[i] : __bfloat162float(weight[d])));
         weighted[i] = w;
         if (output_bf16 != nullptr) output_bf16[d] = __float2bfloat16(w);
         amax = fmaxf(amax, fabsf(w));
@@ -118,8 +126,10 @@ rmsnorm_nvfp4_quantize_kernel(const __nv_bfloat16 *__restrict__ input, const __n
     for (int i = 0; i < 8; i += 2) {
       const size_t d = start + i;
       if (live && d < hidden) {
-        uint32_t packed = q36::encode_e2m1(weighted[i] / decoded_scale);
-        if (d + 1 < hidden) packed |= q36::encode_e2m1(weighted[i + 1] / decoded_scale) << 4;
+        // (two encode_e2m1 calls in one: hardware conversion + the reference's tie and -0 rules)
+        const uint32_t packed = d + 1 < hidden
+                                    ? q36::encode_e2m1x2(weighted[i] / decoded_scale, weighted[i + 1] / decoded_scale)
+                                    : q36::encode_e2m1(weighted[i] / decoded_scale);
         output_fp4[d / 2] = static_cast<uint8_t>(packed);
       }
     }
