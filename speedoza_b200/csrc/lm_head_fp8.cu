@@ -113,16 +113,40 @@ __device__ __forceinline__ void fused_argmax_tail(const float (&best)[N], const 
     __syncthreads();
     if (s_last) {
       __threadfence();
-      if (threadIdx.x < N) {
-        float bv = -INFINITY;
-        uint32_t bi = 0u;
-        for (uint32_t b = 0; b < gridDim.x; ++b) {
-          const float2 p = __ldcg(partials + static_cast<size_t>(b) * N + threadIdx.x);
+      // Every thread takes the CTAs b = thread, thread + 256, ... of every token (all loads of a
+      // thread are independent: one round trip), then the winners meet by shuffles and through the
+      // same shared arrays.  `better` is a total order (value, then lower index), so the order in
+      // which candidates meet does not change the winner.
+      float bv[N];
+      uint32_t bi[N];
+#pragma unroll
+      for (int t = 0; t < N; ++t) { bv[t] = -INFINITY; bi[t] = 0u; }   // what a scan that nothing beats returns
+      for (uint32_t b = threadIdx.x; b < gridDim.x; b += kThreads) {
+#pragma unroll
+        for (int t = 0; t < N; ++t) {
+          const float2 p = __ldcg(partials + static_cast<size_t>(b) * N + t);
           const uint32_t pi = __float_as_uint(p.y);
-          if (better(p.x, pi, bv, bi)) { bv = p.x; bi = pi; }
+          if (better(p.x, pi, bv[t], bi[t])) { bv[t] = p.x; bi[t] = pi; }
         }
-        out_tokens[threadIdx.x] = bi;
-        if (out_best != nullptr) out_best[threadIdx.x] = bv;
+      }
+#pragma unroll
+      for (int t = 0; t < N; ++t) {
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+          const float ov = __shfl_xor_sync(0xffffffffu, bv[t], off);
+          const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi[t], off);
+          if (better(ov, oi, bv[t], bi[t])) { bv[t] = ov; bi[t] = oi; }
+        }
+        if (lane == 0) { s_val[warp][t] = bv[t]; s_idx[warp][t] = bi[t]; }
+      }
+      __syncthreads();
+      if (threadIdx.x < N) {
+        float fv = s_val[0][threadIdx.x];
+        uint32_t fi = s_idx[0][threadIdx.x];
+        for (int w = 1; w < kWarps; ++w)
+          if (better(s_val[w][threadIdx.x], s_idx[w][threadIdx.x], fv, fi)) { fv = s_val[w][threadIdx.x]; fi = s_idx[w][threadIdx.x]; }
+        out_tokens[threadIdx.x] = fi;
+        if (out_best != nullptr) out_best[threadIdx.x] = fv;
       }
       if (threadIdx.x == 0) *ticket = 0u;      // ready for the next call
     }
