@@ -73,7 +73,14 @@ typedef struct {                         /* qwen36_fp4.h:36-52 */
  * column) with UE4M3 block scales in the 128x4 tiled layout (outer = feature);
  * B = activations [n, k/2] with tiled scales (outer = token).  alpha carries
  * both per-tensor scales; a_scale_2 / b_scale_2 are accepted and ignored.
- * workspace is accepted and unused. */
+ * workspace (the buffer the reference hands to cuBLASLt) is optional: when it is
+ * 16-byte aligned and holds 256 KB + 64 B per pair of SMs (19.4 MB on a B200),
+ * prefill shapes whose tiles fill the SMs badly (e.g. 5120 x 17408 at 512-2048
+ * tokens) are cut along K and their partial tiles meet in it; its contents need no
+ * initialisation and mean nothing afterwards.  Calls that share a workspace must
+ * not overlap (same rule as for cuBLASLt).  Without it every tile is summed by
+ * one CTA pair, and the two routes differ only in the grouping of float32
+ * additions. */
 typedef struct {
   size_t m, n, k;
   qwen36_device_ptr_t a_fp4, a_scale, a_scale_2;

@@ -311,6 +311,8 @@ def load() -> C.CDLL:
     lib.qwen36_nvfp4_matvec_force_quads.restype = None
     lib.qwen36_nvfp4_gemm_force_bn.restype = None
     lib.qwen36_nvfp4_gemm_force_bn.argtypes = [C.c_int]
+    lib.qwen36_nvfp4_gemm_stream_k.restype = None
+    lib.qwen36_nvfp4_gemm_stream_k.argtypes = [C.c_int]
     lib.qwen36_nvfp4_gemm_force_split.restype = None
     lib.qwen36_nvfp4_gemm_force_split.argtypes = [C.c_int]
     lib.qwen36_nvfp4_matvec_group.argtypes = [C.POINTER(Nvfp4MatvecSpec), size_t]

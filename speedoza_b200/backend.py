@@ -167,9 +167,23 @@ class CudaBackend:
         _check("nvfp4_dequantize", self.lib.qwen36_nvfp4_dequantize(C.byref(spec)))
         return out
 
+    GEMM_WORKSPACE_BYTES = 32 << 20
+
+    def gemm_workspace(self, device):
+        """The workspace the reference's callers hand to qwen36_nvfp4_gemm (there for cuBLASLt; here the
+        stream-K form of the prefill GEMM parks partial tiles in it: 256 KB + 64 B per CTA pair).  One
+        buffer per device, kept for the life of the backend; calls that share it must share a stream."""
+        if not hasattr(self, "_gemm_ws"):
+            self._gemm_ws = {}
+        key = str(device)
+        if key not in self._gemm_ws:
+            self._gemm_ws[key] = torch.empty(self.GEMM_WORKSPACE_BYTES, dtype=torch.uint8, device=device)
+        return self._gemm_ws[key]
+
     def _gemm_spec(self, a_fp4, a_sf, b_fp4, b_sf, alpha, m, n, k, out):
+        ws = self.gemm_workspace(a_fp4.device) if n >= 512 else None
         return abi.Nvfp4GemmSpec(m, n, k, _dp(a_fp4), _dp(a_sf), DevicePtr(0), _dp(b_fp4), _dp(b_sf),
-                                 DevicePtr(0), _dp(out), DevicePtr(0), 0, alpha)
+                                 DevicePtr(0), _dp(out), _dp(ws), 0 if ws is None else ws.numel(), alpha)
 
     def nvfp4_gemm(self, a_fp4, a_sf, b_fp4, b_sf, alpha: float, m: int, n: int, k: int,
                    out=None) -> torch.Tensor:

@@ -668,12 +668,53 @@ constexpr uint32_t kSmemBytes = 1024 + 1024 + kAbStages * kAbStage + kSfSlots * 
 constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | ((kBN >> 3) << 17) | ((256u >> 4) << 24);
 static_assert(256 + kSfBufs * kSfCols <= kTmemCols, "TMEM budget");
 static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
+// Stream-K form: a (tile, K-block) pair is a unit and every CTA pair takes an equal, contiguous run
+// of units, so a launch whose tiles do not fill the last round (40 tiles on 74 pairs) still keeps
+// every pair busy to the end.  A pair's run may begin and end inside a tile.  The pair that holds a
+// tile's FIRST K-blocks owns its output; pairs that hold later K-blocks of it (always the first
+// thing they do) leave their float32 accumulator in a slot of the caller's workspace, epilogue
+// thread by epilogue thread, and raise a per-warp flag that carries the launch's tag; the owner
+// (for which that tile is the last thing it does) adds the slots in K order.  Bits differ from the
+// one-pass sum only by that regrouping of float32 additions; they do not depend on timing.
+constexpr uint32_t kSlotFloats = 2u * 8u * 128u * 32u;           // pair x epilogue warps x columns x lanes = 256 KB
+constexpr uint32_t kFlagsPerPair = 16u;
 }  // namespace pair6
 
+// The segments (tile, K-blocks [kb0, kb1)) of one CTA pair, in the order every role walks them.
+template <bool SK>
+struct PairWalk {
+  uint32_t a, b, step, k_blocks;       // tiles form: next tile, tile count, stride.  Stream-K: next unit, end unit
+  __device__ __forceinline__ PairWalk(uint32_t pair_id, uint32_t n_pairs, uint32_t tiles, uint32_t kb) : k_blocks(kb) {
+    if (SK) {
+      const uint64_t total = static_cast<uint64_t>(tiles) * kb;
+      a = static_cast<uint32_t>(total * pair_id / n_pairs);
+      b = static_cast<uint32_t>(total * (pair_id + 1u) / n_pairs);
+      step = 0u;
+    } else {
+      a = pair_id; b = tiles; step = n_pairs;
+    }
+  }
+  __device__ __forceinline__ bool next(uint32_t &tile, uint32_t &kb0, uint32_t &kb1) {
+    if (a >= b) return false;
+    if (SK) {
+      tile = a / k_blocks;
+      kb0 = a - tile * k_blocks;
+      kb1 = min(k_blocks, kb0 + (b - a));
+      a += kb1 - kb0;
+    } else {
+      tile = a; kb0 = 0u; kb1 = k_blocks; a += step;
+    }
+    return true;
+  }
+};
+
+
+template <bool SK>
 __global__ void __launch_bounds__(kThreads, 1)
 nvfp4_gemm_pair6_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                         const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
-                        __nv_bfloat16 *__restrict__ c, uint32_t m, uint32_t n, uint32_t k, float alpha) {
+                        __nv_bfloat16 *__restrict__ c, uint32_t m, uint32_t n, uint32_t k, float alpha,
+                        float *__restrict__ ws, uint32_t tag) {
   namespace P = pair6;
   extern __shared__ __align__(128) uint8_t smem_raw[];
   uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -722,10 +763,12 @@ nvfp4_gemm_pair6_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     if (lane == 0) {
       uint32_t g = 0;
       bool dead = false;
-      for (uint32_t tile = pair_id; tile < tiles && !dead; tile += n_pairs) {
+      PairWalk<SK> walk(pair_id, n_pairs, tiles, k_blocks);
+      uint32_t tile, kb0, kb1;
+      while (!dead && walk.next(tile, kb0, kb1)) {
         const uint32_t nb = tile % n_blocks, mb = tile / n_blocks;
         const uint32_t row_block = mb * 2u + rank;                       // this CTA's 128 weight rows
-        for (uint32_t kb = 0; kb < k_blocks; ++kb, ++g) {
+        for (uint32_t kb = kb0; kb < kb1; ++kb, ++g) {
           const uint32_t s = g % P::kAbStages, ph = (g / P::kAbStages) & 1u;
           if (!mbar_wait(&ab_empty[s], ph ^ 1u)) { dead = true; break; }
           if (leader) Q36_GTRACE(g, 0);
@@ -743,10 +786,12 @@ nvfp4_gemm_pair6_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
       // side of the same branch, so that the two lanes run their loops side by side
       uint32_t g = 0;
       bool dead = false;
-      for (uint32_t tile = pair_id; tile < tiles && !dead; tile += n_pairs) {
+      PairWalk<SK> walk(pair_id, n_pairs, tiles, k_blocks);
+      uint32_t tile, kb0, kb1;
+      while (!dead && walk.next(tile, kb0, kb1)) {
         const uint32_t nb = tile % n_blocks, mb = tile / n_blocks;
         const uint32_t row_block = mb * 2u + rank;
-        for (uint32_t kb = 0; kb < k_blocks; ++kb, ++g) {
+        for (uint32_t kb = kb0; kb < kb1; ++kb, ++g) {
           const uint32_t s = g % P::kSfSlots, ph = (g / P::kSfSlots) & 1u;
           if (!mbar_wait(&sfs_empty[s], ph ^ 1u)) { dead = true; break; }
           uint8_t *st = sfs + s * P::kSfSlot;
@@ -767,8 +812,10 @@ nvfp4_gemm_pair6_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
       const uint32_t mine = warp == 3u ? 1u : 0u;
       uint32_t g = 0;
       bool dead = false;
-      for (uint32_t tile = pair_id; tile < tiles && !dead; tile += n_pairs) {
-        for (uint32_t kb = 0; kb < k_blocks; ++kb, ++g) {
+      PairWalk<SK> walk(pair_id, n_pairs, tiles, k_blocks);
+      uint32_t tile, kb0, kb1;
+      while (!dead && walk.next(tile, kb0, kb1)) {
+        for (uint32_t kb = kb0; kb < kb1; ++kb, ++g) {
           if ((g & 1u) != mine) continue;
           const uint32_t s = g % P::kSfSlots, phs = (g / P::kSfSlots) & 1u;
           const uint32_t b = g % P::kSfBufs, phb = (g / P::kSfBufs) & 1u;
@@ -804,10 +851,12 @@ nvfp4_gemm_pair6_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     if (leader && lane == 0) {
       uint32_t g = 0, t_local = 0;
       bool dead = false;
-      for (uint32_t tile = pair_id; tile < tiles && !dead; tile += n_pairs, ++t_local) {
+      PairWalk<SK> walk(pair_id, n_pairs, tiles, k_blocks);
+      uint32_t tile, kb0, kb1;
+      for (; !dead && walk.next(tile, kb0, kb1); ++t_local) {
         if (!mbar_wait(&acc_empty[0], (t_local & 1u) ^ 1u)) { dead = true; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        for (uint32_t kb = 0; kb < k_blocks; ++kb, ++g) {
+        for (uint32_t kb = kb0; kb < kb1; ++kb, ++g) {
           const uint32_t s = g % P::kAbStages, ph = (g / P::kAbStages) & 1u;
           const uint32_t b = g % P::kSfBufs, phb = (g / P::kSfBufs) & 1u;
           if (!mbar_wait(&ab_full[s], ph)) { dead = true; break; }
@@ -820,7 +869,7 @@ nvfp4_gemm_pair6_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
 #pragma unroll
           for (uint32_t kk = 0; kk < 4; ++kk)
             mma_mxf4nvf4_pair(tmem_base, desc_sw128(st + kk * 32u), desc_sw128(st + P::kABytes + kk * 32u), P::kIdesc,
-                              sfa_t + kk * 4u, sfb_t + kk * 8u, (kb | kk) != 0u);
+                              sfa_t + kk * 4u, sfb_t + kk * 8u, kb != kb0 || kk != 0u);
           mma_commit_pair_fanout(&ab_empty[s], 3);           // frees the operand stage in both CTAs (and, for the copier, the scale buffer)
           Q36_GTRACE(g, 6);
         }
@@ -833,7 +882,9 @@ nvfp4_gemm_pair6_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     const uint32_t col0 = ((warp - kWarpEpilogue) >> 2) * (P::kBN / 2u);   // this warp's half of the columns
     const uint32_t acc_empty_leader = map_to_cta(smem_u32(&acc_empty[0]), 0u);
     uint32_t t_local = 0;
-    for (uint32_t tile = pair_id; tile < tiles; tile += n_pairs, ++t_local) {
+    PairWalk<SK> walk(pair_id, n_pairs, tiles, k_blocks);
+    uint32_t tile, kb0, kb1;
+    for (; walk.next(tile, kb0, kb1); ++t_local) {
       const uint32_t nb = tile % n_blocks, mb = tile / n_blocks;
       if (!mbar_wait(&acc_full[0], t_local & 1u)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -852,6 +903,62 @@ nvfp4_gemm_pair6_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
+      if (SK && (kb0 != 0u || kb1 != k_blocks)) {
+        // this thread's 128 sums of a partial tile, as 32 groups of four columns:
+        // [pair][CTA][epilogue warp][group][lane] float4, so that a warp moves 512 contiguous bytes per access
+        const uint32_t ew = warp - kWarpEpilogue;
+        const size_t mine = ((static_cast<size_t>(rank) * 8u + ew) * 32u) * 32u + lane;
+        uint32_t *flags = reinterpret_cast<uint32_t *>(ws + static_cast<size_t>(n_pairs) * P::kSlotFloats);
+        if (kb0 != 0u) {
+          float4 *slot = reinterpret_cast<float4 *>(ws + static_cast<size_t>(pair_id) * P::kSlotFloats) + mine;
+#pragma unroll
+          for (uint32_t g4 = 0; g4 < 8; ++g4) {
+            slot[g4 * 32u] = make_float4(__uint_as_float(r0[4 * g4]), __uint_as_float(r0[4 * g4 + 1]),
+                                         __uint_as_float(r0[4 * g4 + 2]), __uint_as_float(r0[4 * g4 + 3]));
+            slot[(8u + g4) * 32u] = make_float4(__uint_as_float(r1[4 * g4]), __uint_as_float(r1[4 * g4 + 1]),
+                                                __uint_as_float(r1[4 * g4 + 2]), __uint_as_float(r1[4 * g4 + 3]));
+            slot[(16u + g4) * 32u] = make_float4(__uint_as_float(r2[4 * g4]), __uint_as_float(r2[4 * g4 + 1]),
+                                                 __uint_as_float(r2[4 * g4 + 2]), __uint_as_float(r2[4 * g4 + 3]));
+            slot[(24u + g4) * 32u] = make_float4(__uint_as_float(r3[4 * g4]), __uint_as_float(r3[4 * g4 + 1]),
+                                                 __uint_as_float(r3[4 * g4 + 2]), __uint_as_float(r3[4 * g4 + 3]));
+          }
+          __threadfence();
+          __syncwarp();
+          if (lane == 0) *reinterpret_cast<volatile uint32_t *>(flags + pair_id * P::kFlagsPerPair + rank * 8u + ew) = tag;
+          continue;                                           // the owner of the tile writes the output
+        }
+        // owner: the pairs after this one whose runs begin inside the tile, in K order
+        const uint64_t total = static_cast<uint64_t>(tiles) * k_blocks;
+        const uint64_t tile_end = static_cast<uint64_t>(tile + 1u) * k_blocks;
+        for (uint32_t q = pair_id + 1u; q < n_pairs && total * q / n_pairs < tile_end; ++q) {
+          const volatile uint32_t *flag = flags + q * P::kFlagsPerPair + rank * 8u + ew;
+          bool there = false;
+          for (uint32_t spin = 0; spin < (1u << 22); ++spin) {        // x 64 ns: a quarter of a second
+            if (*flag == tag) { there = true; break; }
+            __nanosleep(64);
+          }
+          if (!there) atomicExch(&g_gemm_error, 1u);
+          __threadfence();
+          const float4 *slot = reinterpret_cast<const float4 *>(ws + static_cast<size_t>(q) * P::kSlotFloats) + mine;
+          // eight 16-byte loads in flight at a time: four round trips to L2 for the 128 values
+          auto add8 = [&](uint32_t (&r)[32], uint32_t first) {
+            float4 v[8];
+#pragma unroll
+            for (uint32_t g4 = 0; g4 < 8; ++g4) v[g4] = __ldcg(slot + (first + g4) * 32u);
+#pragma unroll
+            for (uint32_t g4 = 0; g4 < 8; ++g4) {
+              r[4 * g4] = __float_as_uint(__uint_as_float(r[4 * g4]) + v[g4].x);
+              r[4 * g4 + 1] = __float_as_uint(__uint_as_float(r[4 * g4 + 1]) + v[g4].y);
+              r[4 * g4 + 2] = __float_as_uint(__uint_as_float(r[4 * g4 + 2]) + v[g4].z);
+              r[4 * g4 + 3] = __float_as_uint(__uint_as_float(r[4 * g4 + 3]) + v[g4].w);
+            }
+          };
+          add8(r0, 0u);
+          add8(r1, 8u);
+          add8(r2, 16u);
+          add8(r3, 24u);
+        }
+      }
       uint32_t packed[P::kBN / 4];
 #pragma unroll
       for (uint32_t j = 0; j < 32; j += 2) {
@@ -1211,6 +1318,38 @@ int launch_pair(const qwen36_nvfp4_gemm_spec_t *s, float alpha) {
                                              static_cast<uint32_t>(s->n), static_cast<uint32_t>(s->k), alpha));
 }
 
+std::atomic<uint32_t> g_streamk_tag{0};
+std::atomic<int> g_streamk_mode{0};       // test hook: 0 = by the fill of the last round, 1 = never, 2 = whenever the workspace allows
+
+// Does cutting tiles along K pay for this launch?  Whole tiles cost ceil(tiles / pairs) rounds of k_blocks
+// stages.  Stream-K costs tiles * k_blocks / pairs stages, each about a tenth slower (pairs that run side
+// by side no longer share weight rows in L2), plus the fix-up and the extra segment turn-arounds (8 us,
+// 17 stages).  Measured on down 5120 x 17408: 46 -> 43 / 82 -> 61 / 110 -> 93 us at 512 / 1024 / 2048
+// tokens, and the other way round (170 -> 182 us) at 4096, where this rule declines.
+bool stream_k_pays(uint32_t tiles, uint32_t pairs, uint32_t k_blocks) {
+  const uint64_t whole = static_cast<uint64_t>((tiles + pairs - 1u) / pairs) * k_blocks;
+  const uint64_t cut = (static_cast<uint64_t>(tiles) * k_blocks + pairs - 1u) / pairs;
+  return cut * 11u + 170u < whole * 10u;
+}
+
+template <bool SK>
+int launch_pair6_form(const qwen36_nvfp4_gemm_spec_t *s, float alpha, const CUtensorMap &map_a, const CUtensorMap &map_b,
+                      const CUtensorMap &map_sfa, const CUtensorMap &map_sfb, cudaLaunchConfig_t &cfg, uint32_t pairs) {
+  namespace P = pair6;
+  if (q36::ensure_dynamic_smem(reinterpret_cast<const void *>(nvfp4_gemm_pair6_kernel<SK>), static_cast<int>(P::kSmemBytes)) !=
+      cudaSuccess)
+    return QWEN36_STATUS_CUDA_ERROR;
+  cfg.gridDim = dim3(pairs * 2u);
+  uint32_t tag = 0;
+  if (SK) {
+    do { tag = g_streamk_tag.fetch_add(1u) + 1u; } while (tag == 0u);   // never 0: a cleared workspace must not look flagged
+  }
+  return q36::cuda_status(cudaLaunchKernelEx(&cfg, nvfp4_gemm_pair6_kernel<SK>, map_a, map_b, map_sfa, map_sfb,
+                                             as_ptr<__nv_bfloat16>(s->c_bf16), static_cast<uint32_t>(s->m),
+                                             static_cast<uint32_t>(s->n), static_cast<uint32_t>(s->k), alpha,
+                                             as_ptr<float>(s->workspace), tag));
+}
+
 int launch_pair6(const qwen36_nvfp4_gemm_spec_t *s, float alpha) {
   namespace P = pair6;
   CUtensorMap map_a, map_b, map_sfa, map_sfb;
@@ -1220,9 +1359,6 @@ int launch_pair6(const qwen36_nvfp4_gemm_spec_t *s, float alpha) {
       !make_scale_map(&map_sfa, s->a_scale.ptr, (s->m / 128) * sf_tiles) ||
       !make_scale_map(&map_sfb, s->b_scale.ptr, ((s->n + 127) / 128) * sf_tiles))
     return QWEN36_STATUS_NOT_IMPLEMENTED;
-  if (q36::ensure_dynamic_smem(reinterpret_cast<const void *>(nvfp4_gemm_pair6_kernel), static_cast<int>(P::kSmemBytes)) !=
-      cudaSuccess)
-    return QWEN36_STATUS_CUDA_ERROR;
   const uint32_t tiles = static_cast<uint32_t>((s->m / 256) * ((s->n + P::kBN - 1) / P::kBN));
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(static_cast<uint32_t>(sm_count()) & ~1u);
@@ -1236,15 +1372,23 @@ int launch_pair6(const qwen36_nvfp4_gemm_spec_t *s, float alpha) {
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  // The grid is persistent with a static tile stride, so it must never exceed the number of
+  // The grid is persistent with a static walk over the work, so it must never exceed the number of
   // pairs the device can host at the same time (some SMs may have no free partner).
-  const int max_pairs = max_active_pairs(reinterpret_cast<const void *>(nvfp4_gemm_pair6_kernel), &cfg);
+  if (q36::ensure_dynamic_smem(reinterpret_cast<const void *>(nvfp4_gemm_pair6_kernel<false>), static_cast<int>(P::kSmemBytes)) !=
+      cudaSuccess)
+    return QWEN36_STATUS_CUDA_ERROR;
+  const int max_pairs = max_active_pairs(reinterpret_cast<const void *>(nvfp4_gemm_pair6_kernel<false>), &cfg);
   if (max_pairs <= 0) return QWEN36_STATUS_NOT_IMPLEMENTED;
-  const uint32_t pairs = tiles < static_cast<uint32_t>(max_pairs) ? tiles : static_cast<uint32_t>(max_pairs);
-  cfg.gridDim = dim3(pairs * 2u);
-  return q36::cuda_status(cudaLaunchKernelEx(&cfg, nvfp4_gemm_pair6_kernel, map_a, map_b, map_sfa, map_sfb,
-                                             as_ptr<__nv_bfloat16>(s->c_bf16), static_cast<uint32_t>(s->m),
-                                             static_cast<uint32_t>(s->n), static_cast<uint32_t>(s->k), alpha));
+  const uint32_t all = static_cast<uint32_t>(max_pairs);
+  const uint64_t units = static_cast<uint64_t>(tiles) * (s->k / 256);
+  const size_t need = static_cast<size_t>(all) * (P::kSlotFloats * sizeof(float) + P::kFlagsPerPair * sizeof(uint32_t));
+  const int mode = g_streamk_mode.load();
+  const bool fits = s->workspace.ptr != 0 && (s->workspace.ptr & 15u) == 0 && s->workspace_bytes >= need && units >= all &&
+                    units < (1ull << 32);
+  if (fits && (mode == 2 || (mode == 0 && stream_k_pays(tiles, all, static_cast<uint32_t>(s->k / 256)))))
+    return launch_pair6_form<true>(s, alpha, map_a, map_b, map_sfa, map_sfb, cfg, all);
+  const uint32_t pairs = tiles < all ? tiles : all;
+  return launch_pair6_form<false>(s, alpha, map_a, map_b, map_sfa, map_sfb, cfg, pairs);
 }
 
 // Split-K launch: `split` CTAs per 128-row block (cluster), one token block (n <= BN).
@@ -1329,6 +1473,9 @@ int nvfp4_gemm_tc(const qwen36_nvfp4_gemm_spec_t *s, float alpha) {
 // 256-token tiles, 512 CTA pairs with five combined stages, 768 CTA pairs with six operand stages
 // and the separate scale pipeline (where the shape allows pairs); 0 = default.
 extern "C" void qwen36_nvfp4_gemm_force_bn(int bn) { g_force_bn.store(bn); }
+// Tuning / test hook for the stream-K form of the CTA-pair kernel: 0 = by the fill of the last round of
+// tiles (default), 1 = never, 2 = whenever the workspace allows.
+extern "C" void qwen36_nvfp4_gemm_stream_k(int mode) { g_streamk_mode.store(mode < 0 || mode > 2 ? 0 : mode); }
 // Tuning hook: CTAs per row block of the split-K form for n <= 16 (1 = never split, 0 = heuristic).
 extern "C" void qwen36_nvfp4_gemm_force_split(int split) { g_force_split.store(split); }
 

@@ -368,6 +368,7 @@ def test_w4a4_gemm_tile_variants(backend, m, n, k):
     dev = [to_dev(t) for t in (a, a_sf, b, b_sf)]
     outs = []
     try:
+        backend.lib.qwen36_nvfp4_gemm_stream_k(1)          # whole tiles only: the stream-K form regroups the K sum
         for tile in (0, 128, 256, 512, 768):
             backend.lib.qwen36_nvfp4_gemm_force_bn(tile)
             got = bf16_host(backend.nvfp4_gemm(*dev, alpha, m, n, k))
@@ -375,9 +376,48 @@ def test_w4a4_gemm_tile_variants(backend, m, n, k):
             outs.append(got)
     finally:
         backend.lib.qwen36_nvfp4_gemm_force_bn(0)
+        backend.lib.qwen36_nvfp4_gemm_stream_k(0)
     assert backend.lib.qwen36_nvfp4_gemm_last_error() == 0
     for got in outs[1:]:
         assert np.array_equal(got, outs[0])
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 1000, 8192), (512, 600, 4096), (1024, 512, 8704), (256, 512, 2560)])
+def test_w4a4_gemm_stream_k(backend, m, n, k):
+    """Stream-K form of the CTA-pair kernel (tiles cut along K so that every pair gets the same number of
+    K-blocks; partial tiles meet in the caller's workspace, added in K order): the oracle's result, the
+    whole-tile form's result up to the regrouping of float32 additions, the same bits on every run (a
+    second launch finds the first one's flags in the workspace), and the whole-tile form when no
+    workspace is passed.  Shapes: a tile shared by up to eighteen pairs, ragged token counts, fewer
+    K-blocks per pair than a tile has."""
+    rng = np.random.default_rng(11 * m + n + k)
+    a, a_sf, x, b, b_sf, alpha = w4a4_case(rng, m, n, k)
+    want = synth.bf16_bits_to_f32(orc.nvfp4_gemm(a, a_sf, b, b_sf, alpha, m, n, k))
+    dev = [to_dev(t) for t in (a, a_sf, b, b_sf)]
+    try:
+        backend.lib.qwen36_nvfp4_gemm_force_bn(768)
+        backend.lib.qwen36_nvfp4_gemm_stream_k(1)
+        whole = bf16_host(backend.nvfp4_gemm(*dev, alpha, m, n, k))
+        backend.lib.qwen36_nvfp4_gemm_stream_k(2)
+        cut = [bf16_host(backend.nvfp4_gemm(*dev, alpha, m, n, k)) for _ in range(3)]
+        out = torch.zeros((n, m), dtype=torch.bfloat16, device="cuda")
+        spec = abi.Nvfp4GemmSpec(m, n, k, *[abi.DevicePtr(t.data_ptr()) for t in dev[:2]], abi.DevicePtr(0),
+                                 *[abi.DevicePtr(t.data_ptr()) for t in dev[2:]], abi.DevicePtr(0),
+                                 abi.DevicePtr(out.data_ptr()), abi.DevicePtr(0), 0, alpha)
+        import ctypes as C
+        assert backend.lib.qwen36_nvfp4_gemm(C.byref(spec)) == abi.SUCCESS
+        no_ws = bf16_host(out)
+    finally:
+        backend.lib.qwen36_nvfp4_gemm_force_bn(0)
+        backend.lib.qwen36_nvfp4_gemm_stream_k(0)
+    assert backend.lib.qwen36_nvfp4_gemm_last_error() == 0
+    assert np.array_equal(no_ws, whole)
+    assert np.array_equal(cut[1], cut[0]) and np.array_equal(cut[2], cut[0])
+    got, ref = synth.bf16_bits_to_f32(cut[0]), synth.bf16_bits_to_f32(whole)
+    assert rel_l2(got, want) <= 1e-2
+    assert rel_l2(got, ref) <= 2e-4
+    assert (cut[0] == whole).mean() >= 0.995
+    assert not np.array_equal(cut[0], whole) or k <= 2560     # the cut really happened where the shape is large enough
 
 
 @pytest.mark.parametrize("m,n,k", [(1024, 1, 5120), (640, 8, 6144), (256, 3, 17408), (384, 16, 1024), (128, 5, 512)])
