@@ -957,6 +957,10 @@ nvfp4_gemm_pair6_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
           add8(r1, 8u);
           add8(r2, 16u);
           add8(r3, 24u);
+          // This warp is the flag's only reader: clear it, so that a replay of a captured launch (same
+          // tag) does not find the flag of the replay before it.
+          __syncwarp();
+          if (lane == 0) *const_cast<volatile uint32_t *>(flag) = 0u;
         }
       }
       uint32_t packed[P::kBN / 4];

@@ -485,3 +485,38 @@ def test_quantise_then_gemm_end_to_end(backend):
     b, b_sf, ts_o = orc.nvfp4_quantize_rows(x, 0.37)
     want = orc.nvfp4_gemm(packed, a_sf, b, b_sf, synth.WEIGHT_GLOBAL_SCALE * ts_o, m, n, k)
     assert rel_l2(synth.bf16_bits_to_f32(got), synth.bf16_bits_to_f32(want)) <= 1e-2
+
+
+def test_w4a4_gemm_stream_k_under_graph_replay(backend):
+    """A captured stream-K launch replays with the same tag: the flags of one replay must not satisfy the
+    next.  Three replays on fresh activations, each against the eager result for the same operands."""
+    m, n, k = 256, 1000, 8192
+    rng = np.random.default_rng(5)
+    a, a_sf, x, b, b_sf, alpha = w4a4_case(rng, m, n, k)
+    a_d, sfa_d = to_dev(a), to_dev(a_sf)
+    cases = [(to_dev(b), to_dev(b_sf))]
+    for _ in range(2):
+        _, _, _, b2, b2_sf, _ = w4a4_case(rng, m, n, k)
+        cases.append((to_dev(b2), to_dev(b2_sf)))
+    try:
+        backend.lib.qwen36_nvfp4_gemm_force_bn(768)
+        backend.lib.qwen36_nvfp4_gemm_stream_k(2)
+        eager = [backend.nvfp4_gemm(a_d, sfa_d, bb, bs, alpha, m, n, k).clone() for bb, bs in cases]
+        torch.cuda.synchronize()
+        b_buf, s_buf = cases[0][0].clone(), cases[0][1].clone()
+        out = torch.zeros((n, m), dtype=torch.bfloat16, device="cuda")
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            backend.sync_stream()
+            backend.nvfp4_gemm(a_d, sfa_d, b_buf, s_buf, alpha, m, n, k, out)
+        backend.sync_stream()
+        for (bb, bs), want in zip(cases, eager):
+            b_buf.copy_(bb); s_buf.copy_(bs)
+            graph.replay()
+            torch.cuda.synchronize()
+            assert torch.equal(out, want)
+    finally:
+        backend.lib.qwen36_nvfp4_gemm_force_bn(0)
+        backend.lib.qwen36_nvfp4_gemm_stream_k(0)
+        backend.sync_stream()
+    assert backend.lib.qwen36_nvfp4_gemm_last_error() == 0
