@@ -606,9 +606,9 @@ int launch_gemv_n(const uint8_t *w, const float *scales, const __nv_bfloat16 *x,
                   unsigned *ticket, unsigned grid) {
   if constexpr (N >= 3 && N <= 8) {
     if (stage_f32(N, cols)) {
-      // (the fused four-token instance sits at the 128-register limit and measured 391 us against 380 us
-      // on the float32 route, so it alone stays there; 3 and 5..8 tokens gain 15-40 % either way)
-      if (g_gemv_route.load() == 0 && cols % 512 == 0 && !(FUSED && N == 4)) {
+      // (3..8 tokens gain 7-40 % on the float16 route, fused or not; the fused four-token instance, at the
+      // 128-register limit, only since the last CTA's merge of the winners stopped being a serial scan)
+      if (g_gemv_route.load() == 0 && cols % 512 == 0) {
         // float16 route first; the float32 route right behind it runs only for activations the
         // float16 route declines (both decide on the same data, on the device, so nothing is read back)
         const size_t smem16 = static_cast<size_t>(N) * cols * 2 + static_cast<size_t>(kWarps) * F16Ring<N>::kStages * kF16StageBytes;
