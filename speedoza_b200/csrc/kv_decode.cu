@@ -548,7 +548,7 @@ decode_split_bf16_mma_kernel(const __nv_bfloat16 *__restrict__ q, const __nv_bfl
                              uint32_t n_splits) {
   constexpr uint32_t D = 256;
   __shared__ float s_m[kWarps][8], s_l[kWarps][8];
-  __shared__ float s_o[4 * G][kEpiStride];
+  __shared__ __align__(16) float s_o[4 * G][kEpiStride];
   __shared__ uint2 s_q[16][32];
 
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;

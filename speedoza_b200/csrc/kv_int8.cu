@@ -676,7 +676,7 @@ kv_attention_mma_kernel(const __nv_bfloat16 *__restrict__ q, const int8_t *__res
   constexpr uint32_t D = 256;
   constexpr float kPScale = 1024.0f;                              // keeps p * v_scale out of the float16 subnormals
   __shared__ float s_m[kWarps][8], s_l[kWarps][8];
-  __shared__ float s_o[4 * G][q36::kEpiStride];
+  __shared__ __align__(16) float s_o[4 * G][q36::kEpiStride];
 
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
   const uint32_t g = lane >> 2, t = lane & 3u;

@@ -106,7 +106,8 @@ __device__ __forceinline__ void split_epilogue(float (&o)[2][8][4], float m_run,
   const uint32_t g = lane >> 2, t = lane & 3u;
   // ---- merge the warps of the CTA: weights per head from the running maxima; the weighted outputs
   // meet in four shared-memory slices (warps 4..7 write, warps 0..3 add), then every thread sums
-  // the four slices of its outputs
+  // the four slices of its outputs.  A lane holds all sixteen dims of chunk g + 8 h for its two
+  // heads (dims 2 j from c = e, 2 j + 1 from c = e + 2), so it moves them as four 16-byte vectors.
   if (t == 0 && g < G) { s_m[warp][g] = m_run; s_l[warp][g] = l_run; }
   __syncthreads();
   float wgt[2];                                                    // heads 2t, 2t + 1
@@ -125,25 +126,39 @@ __device__ __forceinline__ void split_epilogue(float (&o)[2][8][4], float m_run,
 #pragma unroll
       for (int h = 0; h < 2; ++h)
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
+        for (int e = 0; e < 2; ++e) {
+          const uint32_t head = 2 * t + e;
+          if (head < G) {
+            float4 *dst = reinterpret_cast<float4 *>(&slice[head][16 * (g + 8 * h)]);
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            // dims are stored XOR-swizzled inside their 16-float chunk (chunk index = g + 8 h), so
-            // that the eight chunks a warp writes at once fall on different banks
-            const uint32_t head = 2 * t + (c & 1), dim = 16 * (g + 8 * h) + ((2 * j + (c >> 1)) ^ (g + 8 * h));
-            if (head < G) {
-              float *dst = &slice[head][dim];
-              *dst = round == 0 ? wgt[c & 1] * o[h][j][c] : fmaf(wgt[c & 1], o[h][j][c], *dst);
+            for (int q = 0; q < 4; ++q) {
+              const float a0 = o[h][2 * q][e], a1 = o[h][2 * q][e + 2], a2 = o[h][2 * q + 1][e], a3 = o[h][2 * q + 1][e + 2];
+              if (round == 0) {
+                dst[q] = make_float4(wgt[e] * a0, wgt[e] * a1, wgt[e] * a2, wgt[e] * a3);
+              } else {
+                const float4 p = dst[q];
+                dst[q] = make_float4(fmaf(wgt[e], a0, p.x), fmaf(wgt[e], a1, p.y), fmaf(wgt[e], a2, p.z), fmaf(wgt[e], a3, p.w));
+              }
             }
           }
+        }
     }
     __syncthreads();
   }
-  for (uint32_t idx = threadIdx.x; idx < G * D; idx += kSplitThreads) {
-    const uint32_t hd = idx / D, d = idx % D;
+  const bool vec_out = (reinterpret_cast<uintptr_t>(part_o) & 15u) == 0;
+  for (uint32_t idx = threadIdx.x; idx < G * (D / 4); idx += kSplitThreads) {
+    const uint32_t hd = idx / (D / 4), d = (idx % (D / 4)) * 4;
     const size_t slot = static_cast<size_t>(head0 + hd) * n_splits + split;
-    const uint32_t ds = d ^ ((d >> 4) & 15u);                      // undo the swizzle
-    part_o[slot * D + d] = (s_o[hd][ds] + s_o[G + hd][ds]) + (s_o[2 * G + hd][ds] + s_o[3 * G + hd][ds]);
+    const float4 s0 = *reinterpret_cast<const float4 *>(&s_o[hd][d]), s1 = *reinterpret_cast<const float4 *>(&s_o[G + hd][d]);
+    const float4 s2 = *reinterpret_cast<const float4 *>(&s_o[2 * G + hd][d]), s3 = *reinterpret_cast<const float4 *>(&s_o[3 * G + hd][d]);
+    const float4 r = make_float4((s0.x + s1.x) + (s2.x + s3.x), (s0.y + s1.y) + (s2.y + s3.y),
+                                 (s0.z + s1.z) + (s2.z + s3.z), (s0.w + s1.w) + (s2.w + s3.w));
+    float *out = part_o + slot * D + d;
+    if (vec_out) {
+      *reinterpret_cast<float4 *>(out) = r;
+    } else {
+      out[0] = r.x; out[1] = r.y; out[2] = r.z; out[3] = r.w;
+    }
     if (d == 0) {
       float M = -INFINITY, den = 0.f;
       for (int w = 0; w < kSplitWarps; ++w) M = fmaxf(M, s_m[w][hd]);
