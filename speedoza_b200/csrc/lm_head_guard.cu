@@ -200,8 +200,23 @@ top8_rescore_kernel(const WsEntry *__restrict__ ws, const __nv_bfloat16 *__restr
     if (cand != kNoToken && static_cast<size_t>(cand) < vocab) {
       const __nv_bfloat16 *w_row = weight + static_cast<size_t>(cand) * cols;
       const __nv_bfloat16 *x_row = input + row * cols;
-      for (size_t c = lane; c < cols; c += 32u)
-        sum += static_cast<double>(__bfloat162float(w_row[c])) * static_cast<double>(__bfloat162float(x_row[c]));
+      // Same elements per lane, same order of additions as a plain strided loop; the loads of eighty
+      // steps go out together (a plain loop pays one round trip to memory every few steps, and the
+      // row's address is only known here).
+      constexpr uint32_t kBatch = 80;
+      for (size_t c0 = lane; c0 < cols; c0 += 32u * kBatch) {
+        __nv_bfloat16 wv[kBatch], xv[kBatch];
+#pragma unroll
+        for (uint32_t i = 0; i < kBatch; ++i) {
+          const size_t c = c0 + 32u * i;
+          wv[i] = c < cols ? w_row[c] : __float2bfloat16(0.0f);
+          xv[i] = c < cols ? x_row[c] : __float2bfloat16(0.0f);
+        }
+#pragma unroll
+        for (uint32_t i = 0; i < kBatch; ++i)
+          if (c0 + 32u * i < cols)
+            sum += static_cast<double>(__bfloat162float(wv[i])) * static_cast<double>(__bfloat162float(xv[i]));
+      }
     } else {
       sum = -INFINITY;
     }
