@@ -101,7 +101,7 @@ def wide_range_activations(rng, n, cols, kind):
     return synth.f32_to_bf16_bits(x)
 
 
-@pytest.mark.parametrize("n", [3, 4, 5, 8])
+@pytest.mark.parametrize("n", [2, 3, 4, 5, 8])
 @pytest.mark.parametrize("kind", ["octaves", "too_wide", "infinity", "subnormal", "zero_token", "huge"])
 def test_float16_route_keeps_every_bit(backend, n, kind):
     """3..8 tokens go through the float16-staged kernel when the activations allow it and through the
