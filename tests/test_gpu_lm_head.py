@@ -22,7 +22,7 @@ def test_quantize_bit_exact(backend):
 
 
 @pytest.mark.parametrize("rows,cols,n", [(1000, 5120, 1), (1003, 5120, 4), (517, 1024, 5), (64, 528, 2),
-                                         (33, 16, 1), (200, 5120, 16), (9, 2048, 8)])
+                                         (33, 16, 1), (200, 5120, 16), (9, 2048, 8), (700, 5120, 11)])
 def test_gemv_logits_bit_exact(backend, rows, cols, n):
     rng = np.random.default_rng(rows + cols + n)
     w, s = synth.lm_head_weight(rng, rows, cols)
@@ -59,7 +59,7 @@ def test_argmax_rows_vs_oracle(backend, rows, vocab, temp):
         assert backend.sample(t[1:], temp).item() == orc.argmax_rows(logits[0:1, 1:].copy(), temp)[0]
 
 
-@pytest.mark.parametrize("rows,n", [(4096, 1), (5003, 4), (777, 2), (31040, 4)])
+@pytest.mark.parametrize("rows,n", [(4096, 1), (5003, 4), (777, 2), (31040, 4), (3001, 9), (2000, 16)])
 def test_fused_gemv_argmax_bit_exact(backend, rows, n):
     cols = 5120 if rows != 777 else 1024
     rng = np.random.default_rng(rows + n)
