@@ -1015,6 +1015,9 @@ nvfp4_gemm_pair6_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
 // rank order, applies alpha and writes bf16: no workspace, no atomics, deterministic.
 // ============================================================================================
 constexpr uint32_t kMaxSplit = 8;
+// CTAs per row block that still leave room for the partial sums in the first CTA's shared memory
+// ((S - 1) x 128 rows x BN floats beside the operand ring): 8 up to 16 tokens, 5 at 32, 2 at 64.
+template <uint32_t BN> constexpr uint32_t max_split_for() { return BN <= 16 ? kMaxSplit : (BN <= 32 ? 5u : 2u); }
 
 __device__ __forceinline__ void st_cluster_v4f(uint32_t addr, float a, float b, float c4, float d) {
   asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c4), "f"(d) : "memory");
@@ -1411,8 +1414,9 @@ int launch_splitk(const qwen36_nvfp4_gemm_spec_t *s, float alpha, uint32_t split
   if (!make_operand_map(&map_a, s->a_fp4.ptr, s->m, s->k, kBM) ||
       !make_operand_map(&map_b, s->b_fp4.ptr, s->n, s->k, C::kBRows))
     return QWEN36_STATUS_NOT_IMPLEMENTED;
-  constexpr uint32_t kSmem = C::kSmemBytes + (kMaxSplit - 1) * kBM * C::kBRows * 4u;
+  constexpr uint32_t kSmem = C::kSmemBytes + (max_split_for<BN>() - 1) * kBM * C::kBRows * 4u;
   static_assert(kSmem <= 227u * 1024u, "split-K shared memory");
+  if (split > max_split_for<BN>()) split = max_split_for<BN>();
   if (q36::ensure_dynamic_smem(reinterpret_cast<const void *>(nvfp4_gemm_splitk_kernel<BN>), static_cast<int>(kSmem)) !=
       cudaSuccess)
     return QWEN36_STATUS_CUDA_ERROR;
@@ -1469,9 +1473,18 @@ int nvfp4_gemm_tc(const qwen36_nvfp4_gemm_spec_t *s, float alpha) {
     const int rc = launch_pair(s, alpha);
     if (rc != QWEN36_STATUS_NOT_IMPLEMENTED) return rc;      // pairs unavailable: single-CTA tiles below
   }
-  if (s->n <= 16) {
+  if (s->n <= 64) {
+    // few row blocks (k / v / o / down: 8 or 40 on 148 SMs): clusters share a tile along K.  Up to 16 tokens
+    // as many CTAs per row block as fit the GPU; 32 and 64 tokens as many as the partial sums leave room for
+    // (down 5120 x 17408 at 32 tokens: 29 -> 16 us).
     const uint32_t split = choose_split(s);
-    if (split > 1u) return s->n <= 8 ? launch_splitk<8>(s, alpha, split) : launch_splitk<16>(s, alpha, split);
+    if (split > 1u) {
+      if (s->n <= 8) return launch_splitk<8>(s, alpha, split);
+      if (s->n <= 16) return launch_splitk<16>(s, alpha, split);
+      if (s->n <= 32) return launch_splitk<32>(s, alpha, split);
+      // two CTAs per row block: pays for long K only (k = 17408: 30 -> 23 us; k = 6144: 13.7 -> 14.6 us)
+      if (s->k >= 48u * 256u) return launch_splitk<64>(s, alpha, split);
+    }
   }
   if (s->n <= 8) return launch<8>(s, alpha);
   if (s->n <= 16) return launch<16>(s, alpha);

@@ -420,7 +420,8 @@ def test_w4a4_gemm_stream_k(backend, m, n, k):
     assert not np.array_equal(cut[0], whole) or k <= 2560     # the cut really happened where the shape is large enough
 
 
-@pytest.mark.parametrize("m,n,k", [(1024, 1, 5120), (640, 8, 6144), (256, 3, 17408), (384, 16, 1024), (128, 5, 512)])
+@pytest.mark.parametrize("m,n,k", [(1024, 1, 5120), (640, 8, 6144), (256, 3, 17408), (384, 16, 1024), (128, 5, 512),
+                                   (384, 24, 2048), (256, 32, 17408), (640, 33, 6144), (256, 64, 4096)])
 def test_w4a4_decode_split_k(backend, m, n, k):
     """Few tokens, few row blocks: clusters of CTAs split K and add their partial sums through
     distributed shared memory.  Every split factor matches the oracle; split and unsplit results
