@@ -190,6 +190,12 @@ def test_argument_validation_needs_no_gpu(lib):
     assert lib.qwen36_attention_peer_merge(C.byref(abi.AttentionPeerMergeSpec())) == abi.INVALID_ARGUMENT
     assert lib.qwen36_argmax_peer_combine(C.byref(abi.ArgmaxPeerCombineSpec())) == abi.INVALID_ARGUMENT
     assert lib.qwen36_ipc_get_handle(abi.DevicePtr(0), None) == abi.NULL_POINTER
+    assert lib.qwen36_swiglu_nvfp4_quantize_rows(None) == abi.NULL_POINTER
+    assert lib.qwen36_swiglu_nvfp4_quantize_rows(C.byref(abi.SwigluNvfp4QuantizeRowsSpec())) == abi.INVALID_ARGUMENT
+    ragged = abi.SwigluNvfp4QuantizeRowsSpec(rows=4, intermediate=40, input_row_stride=40, gate_bf16=abi.DevicePtr(16),
+                                             up_bf16=abi.DevicePtr(16), output_fp4=abi.DevicePtr(16),
+                                             output_scale_e4m3=abi.DevicePtr(16))
+    assert lib.qwen36_swiglu_nvfp4_quantize_rows(C.byref(ragged)) == abi.INVALID_ARGUMENT      # whole 16-groups only
     # out-of-scope operators link and decline
     assert lib.qwen36_rmsnorm(None) == abi.NOT_IMPLEMENTED
     assert lib.qwen36_attention_flash_splitk_prefill_bf16(None, 4) == abi.NULL_POINTER
@@ -234,3 +240,12 @@ def test_product_code_never_touches_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".h", ".cpp", ".hpp")):
                 text = open(os.path.join(dirpath, f)).read()
                 assert "liboracle" not in text and "import oracle" not in text and "from oracle" not in text, f
+
+
+def test_verify_attention_split_count_fills_the_sms_once():
+    from speedoza_b200.backend import CudaBackend
+    f = CudaBackend.attention_verify_splits
+    assert f(4, 24, 4) == 37            # 24 rows per kv head: one CTA per (kv head, split) on 148 SMs
+    assert f(16, 24, 4) == 18           # 96 rows: two row chunks per split
+    assert f(32, 24, 4) == 12           # 192 rows: three
+    assert f(1, 24, 4, sms=4) == 1 and f(32, 64, 1, sms=2) == 1      # never below one split
