@@ -136,7 +136,12 @@ __global__ void __launch_bounds__(kThreads)
 top8_rescore_kernel(const WsEntry *__restrict__ ws, const __nv_bfloat16 *__restrict__ weight,
                     const __nv_bfloat16 *__restrict__ input, uint32_t *__restrict__ tokens,
                     uint32_t *__restrict__ flags, uint32_t *__restrict__ mirror_last,
-                    uint32_t *__restrict__ fallback_count, size_t rows, size_t vocab, size_t cols, float eps) {
+                    uint32_t *__restrict__ fallback_count, size_t rows, size_t vocab, size_t cols, float eps,
+                    uint32_t staged) {
+  // staged: the activation row and the eight candidates' weight rows travel into shared memory by
+  // cp.async (all of a row's copies in flight at once; the row's address is only known after the
+  // extraction), and the float64 sums read them from there, element by element in the same order.
+  extern __shared__ __align__(16) uint8_t rows_smem[];               // [1 + kCandidates][cols] bf16 when staged
   __shared__ float winner_v[kBlocks];
   __shared__ uint32_t winner_i[kBlocks];
   __shared__ float warp_max_v2[kThreads / 32];
@@ -146,6 +151,13 @@ top8_rescore_kernel(const WsEntry *__restrict__ ws, const __nv_bfloat16 *__restr
   const size_t row = blockIdx.x;
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
 
+  if (staged) {
+    const __nv_bfloat16 *x_row = input + row * cols;
+    for (size_t c = static_cast<size_t>(threadIdx.x) * 8; c < cols; c += static_cast<size_t>(kThreads) * 8)
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(rows_smem + c * 2))),
+                   "l"(x_row + c) : "memory");
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
   float max_v2 = -INFINITY;
   for (uint32_t b = threadIdx.x; b < kBlocks; b += kThreads) {
     const WsEntry e = ws[row * kBlocks + b];
@@ -192,12 +204,25 @@ top8_rescore_kernel(const WsEntry *__restrict__ ws, const __nv_bfloat16 *__restr
       __syncwarp();
     }
   }
+  if (staged) asm volatile("cp.async.wait_group 0;" ::: "memory");
   __syncthreads();
 
   if (warp < kCandidates) {
     const uint32_t cand = cand_i[warp];
     double sum = 0.0;
-    if (cand != kNoToken && static_cast<size_t>(cand) < vocab) {
+    if (staged && cand != kNoToken && static_cast<size_t>(cand) < vocab) {
+      const __nv_bfloat16 *w_row = weight + static_cast<size_t>(cand) * cols;
+      const __nv_bfloat16 *xs = reinterpret_cast<const __nv_bfloat16 *>(rows_smem);
+      __nv_bfloat16 *wsm = reinterpret_cast<__nv_bfloat16 *>(rows_smem) + static_cast<size_t>(1u + warp) * cols;
+      for (size_t c = static_cast<size_t>(lane) * 8; c < cols; c += 256)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(wsm + c))),
+                     "l"(w_row + c) : "memory");
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+      __syncwarp();
+      for (size_t c = lane; c < cols; c += 32u)
+        sum += static_cast<double>(__bfloat162float(wsm[c])) * static_cast<double>(__bfloat162float(xs[c]));
+    } else if (cand != kNoToken && static_cast<size_t>(cand) < vocab) {
       const __nv_bfloat16 *w_row = weight + static_cast<size_t>(cand) * cols;
       const __nv_bfloat16 *x_row = input + row * cols;
       // Same elements per lane, same order of additions as a plain strided loop; the loads of eighty
@@ -534,11 +559,16 @@ extern "C" int qwen36_lm_head_top8_rescore(const qwen36_lm_head_top8_rescore_spe
     return QWEN36_STATUS_INVALID_ARGUMENT;
   top2_scan_kernel<<<dim3(kBlocks, static_cast<unsigned>(spec->rows)), kThreads, 0, q36::stream()>>>(
       as_ptr<const __nv_bfloat16>(spec->logits_bf16), as_ptr<WsEntry>(spec->workspace), spec->vocab);
-  top8_rescore_kernel<<<static_cast<unsigned>(spec->rows), kThreads, 0, q36::stream()>>>(
+  // rows through shared memory when they are made of whole 16-byte pieces and nine of them fit
+  const size_t stage_bytes = (1 + kCandidates) * spec->cols * sizeof(__nv_bfloat16);
+  const bool staged = spec->cols % 8 == 0 && ((spec->weight_bf16.ptr | spec->input_bf16.ptr) & 15u) == 0 &&
+                      stage_bytes <= 200 * 1024 &&
+                      q36::ensure_dynamic_smem(reinterpret_cast<const void *>(top8_rescore_kernel), 200 * 1024) == cudaSuccess;
+  top8_rescore_kernel<<<static_cast<unsigned>(spec->rows), kThreads, staged ? stage_bytes : 0, q36::stream()>>>(
       as_ptr<const WsEntry>(spec->workspace), as_ptr<const __nv_bfloat16>(spec->weight_bf16),
       as_ptr<const __nv_bfloat16>(spec->input_bf16), as_ptr<uint32_t>(spec->tokens_u32),
       as_ptr<uint32_t>(spec->flags_u32), as_ptr<uint32_t>(spec->mirror_last_token_u32),
-      as_ptr<uint32_t>(spec->fallback_count_u32), spec->rows, spec->vocab, spec->cols, spec->eps);
+      as_ptr<uint32_t>(spec->fallback_count_u32), spec->rows, spec->vocab, spec->cols, spec->eps, staged ? 1u : 0u);
   return q36::launch_status();
 }
 
