@@ -138,17 +138,23 @@ top8_rescore_kernel(const WsEntry *__restrict__ ws, const __nv_bfloat16 *__restr
                     uint32_t *__restrict__ flags, uint32_t *__restrict__ mirror_last,
                     uint32_t *__restrict__ fallback_count, size_t rows, size_t vocab, size_t cols, float eps,
                     uint32_t staged) {
-  // staged: the activation row and the eight candidates' weight rows travel into shared memory by
-  // cp.async (all of a row's copies in flight at once; the row's address is only known after the
-  // extraction), and the float64 sums read them from there, element by element in the same order.
-  extern __shared__ __align__(16) uint8_t rows_smem[];               // [1 + kCandidates][cols] bf16 when staged
+  // staged: a cluster of eight CTAs serves a row.  Every CTA repeats the (cheap, deterministic)
+  // extraction; CTA r then recomputes candidate r alone, one warp with the float64 units of an SM to
+  // itself, and leaves its sum in the first CTA's shared memory, which gives the verdict.  The sum is
+  // a chain of cols / 32 dependent float64 multiply-adds per lane in the reference's order (about
+  // 4 us at 5120 columns), which no layout shortens.  The activation row and the candidate's weight
+  // row travel into shared memory by cp.async (all of a row's copies in flight at once; the row's
+  // address is only known after the extraction) and the sum reads them from there.
+  extern __shared__ __align__(16) uint8_t rows_smem[];               // [2][cols] bf16 when staged
   __shared__ float winner_v[kBlocks];
   __shared__ uint32_t winner_i[kBlocks];
   __shared__ float warp_max_v2[kThreads / 32];
   __shared__ uint32_t cand_i[kCandidates];
   __shared__ float ninth_v;
   __shared__ double rescored[kCandidates];
-  const size_t row = blockIdx.x;
+  uint32_t rank = 0;
+  if (staged) asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  const size_t row = staged ? blockIdx.x / kCandidates : blockIdx.x;
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
 
   if (staged) {
@@ -171,57 +177,78 @@ top8_rescore_kernel(const WsEntry *__restrict__ ws, const __nv_bfloat16 *__restr
   __syncthreads();
 
   if (warp == 0) {
-    // nine extractions of the maximum (ties toward the smaller token), clearing the slot each time
-    for (int k = 0; k <= kCandidates; ++k) {
-      float best = -INFINITY;
-      uint32_t slot = kNoToken;
-      for (uint32_t b = lane; b < kBlocks; b += 32u) {
-        const float v = winner_v[b];
-        if (v > best || (v == best && slot != kNoToken && winner_i[b] < winner_i[slot])) {
-          best = v;
-          slot = b;
-        }
-      }
+    // Nine extractions of the maximum (ties toward the smaller token; -inf and NaN are never taken,
+    // as in the reference's scan).  Every block winner becomes a 64-bit key, value bits made monotonic
+    // on top and the complemented token below, eight keys per lane in registers; an extraction is
+    // a local maximum and two warp reductions, and the owner clears its key.
+    constexpr uint32_t kPerLane = (kBlocks + 31) / 32;
+    uint32_t key_hi[kPerLane], key_lo[kPerLane];
 #pragma unroll
-      for (int off = 16; off > 0; off >>= 1) {
-        const float ov = __shfl_down_sync(0xffffffffu, best, off);
-        const uint32_t os = __shfl_down_sync(0xffffffffu, slot, off);
-        if (ov > best || (ov == best && os != kNoToken && (slot == kNoToken || winner_i[os] < winner_i[slot]))) {
-          best = ov;
-          slot = os;
+    for (uint32_t i = 0; i < kPerLane; ++i) {
+      const uint32_t b = lane + 32u * i;
+      key_hi[i] = 0u;
+      key_lo[i] = 0u;
+      if (b < kBlocks) {
+        const float v = winner_v[b];
+        const uint32_t bits = __float_as_uint(v);
+        if (v == v && v != -INFINITY) {
+          key_hi[i] = (bits & 0x80000000u) != 0u ? ~bits : (bits | 0x80000000u);
+          key_lo[i] = ~winner_i[b];
         }
       }
-      slot = __shfl_sync(0xffffffffu, slot, 0);
-      best = __shfl_sync(0xffffffffu, best, 0);
+    }
+    for (int k = 0; k <= kCandidates; ++k) {
+      uint32_t hi = 0u, lo = 0u;
+#pragma unroll
+      for (uint32_t i = 0; i < kPerLane; ++i)
+        if (key_hi[i] > hi || (key_hi[i] == hi && key_lo[i] > lo)) { hi = key_hi[i]; lo = key_lo[i]; }
+      const uint32_t top_hi = __reduce_max_sync(0xffffffffu, hi);
+      const uint32_t top_lo = __reduce_max_sync(0xffffffffu, hi == top_hi ? lo : 0u);
+      if (top_hi != 0u) {
+#pragma unroll
+        for (uint32_t i = 0; i < kPerLane; ++i)
+          if (key_hi[i] == top_hi && key_lo[i] == top_lo) key_hi[i] = key_lo[i] = 0u;     // tokens are unique: one owner
+      }
       if (lane == 0) {
         if (k < kCandidates) {
-          cand_i[k] = slot == kNoToken ? kNoToken : winner_i[slot];
-          if (slot != kNoToken) winner_v[slot] = -INFINITY;
+          cand_i[k] = top_hi == 0u ? kNoToken : ~top_lo;
         } else {
-          ninth_v = best;
+          ninth_v = top_hi == 0u ? -INFINITY
+                                 : __uint_as_float((top_hi & 0x80000000u) != 0u ? (top_hi & 0x7fffffffu) : ~top_hi);
         }
       }
-      __syncwarp();
     }
   }
   if (staged) asm volatile("cp.async.wait_group 0;" ::: "memory");
   __syncthreads();
 
-  if (warp < kCandidates) {
-    const uint32_t cand = cand_i[warp];
+  if (staged ? warp == 0u : warp < kCandidates) {
+    const uint32_t which = staged ? rank : warp;                    // the candidate this warp recomputes
+    const uint32_t cand = cand_i[which];
     double sum = 0.0;
     if (staged && cand != kNoToken && static_cast<size_t>(cand) < vocab) {
       const __nv_bfloat16 *w_row = weight + static_cast<size_t>(cand) * cols;
       const __nv_bfloat16 *xs = reinterpret_cast<const __nv_bfloat16 *>(rows_smem);
-      __nv_bfloat16 *wsm = reinterpret_cast<__nv_bfloat16 *>(rows_smem) + static_cast<size_t>(1u + warp) * cols;
+      __nv_bfloat16 *wsm = reinterpret_cast<__nv_bfloat16 *>(rows_smem) + cols;
       for (size_t c = static_cast<size_t>(lane) * 8; c < cols; c += 256)
         asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(wsm + c))),
                      "l"(w_row + c) : "memory");
       asm volatile("cp.async.commit_group;" ::: "memory");
       asm volatile("cp.async.wait_group 0;" ::: "memory");
       __syncwarp();
-      for (size_t c = lane; c < cols; c += 32u)
-        sum += static_cast<double>(__bfloat162float(wsm[c])) * static_cast<double>(__bfloat162float(xs[c]));
+      // bf16 -> float64 on the integer units where the value is zero or a normal number (sign, exponent
+      // rebased by 896, seven fraction bits on top of the 52): the conversion instructions share the
+      // float64 pipe, which a single warp cannot afford twice per product
+      const uint16_t *wb = reinterpret_cast<const uint16_t *>(wsm), *xb = reinterpret_cast<const uint16_t *>(xs);
+      auto widen = [](uint32_t b) -> double {
+        const uint32_t mag = b & 0x7fffu, e = mag >> 7;
+        if (e - 1u < 254u || mag == 0u) {
+          const uint32_t hi = ((b & 0x8000u) << 16) | (mag == 0u ? 0u : (mag << 13) + 0x38000000u);
+          return __hiloint2double(static_cast<int>(hi), 0);
+        }
+        return static_cast<double>(__uint_as_float(b << 16));       // subnormal, infinity, NaN
+      };
+      for (size_t c = lane; c < cols; c += 32u) sum += widen(wb[c]) * widen(xb[c]);
     } else if (cand != kNoToken && static_cast<size_t>(cand) < vocab) {
       const __nv_bfloat16 *w_row = weight + static_cast<size_t>(cand) * cols;
       const __nv_bfloat16 *x_row = input + row * cols;
@@ -247,9 +274,25 @@ top8_rescore_kernel(const WsEntry *__restrict__ ws, const __nv_bfloat16 *__restr
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) sum += __shfl_down_sync(0xffffffffu, sum, off);
-    if (lane == 0) rescored[warp] = cand == kNoToken ? -INFINITY : sum;
+    if (lane == 0) {
+      const double mine = cand == kNoToken ? -INFINITY : sum;
+      if (staged) {
+        uint32_t remote;                                              // rescored[which] of the cluster's first CTA
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote)
+                     : "r"(static_cast<uint32_t>(__cvta_generic_to_shared(&rescored[which]))), "r"(0u));
+        asm volatile("st.shared::cluster.f64 [%0], %1;" ::"r"(remote), "d"(mine) : "memory");
+      } else {
+        rescored[which] = mine;
+      }
+    }
   }
-  __syncthreads();
+  if (staged) {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (rank != 0u) return;
+  } else {
+    __syncthreads();
+  }
 
   if (threadIdx.x == 0) {
     double best = -INFINITY;
@@ -559,17 +602,30 @@ extern "C" int qwen36_lm_head_top8_rescore(const qwen36_lm_head_top8_rescore_spe
     return QWEN36_STATUS_INVALID_ARGUMENT;
   top2_scan_kernel<<<dim3(kBlocks, static_cast<unsigned>(spec->rows)), kThreads, 0, q36::stream()>>>(
       as_ptr<const __nv_bfloat16>(spec->logits_bf16), as_ptr<WsEntry>(spec->workspace), spec->vocab);
-  // rows through shared memory when they are made of whole 16-byte pieces and nine of them fit
-  const size_t stage_bytes = (1 + kCandidates) * spec->cols * sizeof(__nv_bfloat16);
+  // a cluster of eight CTAs per row, rows through shared memory, when they are made of whole 16-byte
+  // pieces and two of them fit
+  const size_t stage_bytes = 2 * spec->cols * sizeof(__nv_bfloat16);
   const bool staged = spec->cols % 8 == 0 && ((spec->weight_bf16.ptr | spec->input_bf16.ptr) & 15u) == 0 &&
-                      stage_bytes <= 200 * 1024 &&
+                      stage_bytes <= 200 * 1024 && spec->rows <= (1u << 24) &&
                       q36::ensure_dynamic_smem(reinterpret_cast<const void *>(top8_rescore_kernel), 200 * 1024) == cudaSuccess;
-  top8_rescore_kernel<<<static_cast<unsigned>(spec->rows), kThreads, staged ? stage_bytes : 0, q36::stream()>>>(
-      as_ptr<const WsEntry>(spec->workspace), as_ptr<const __nv_bfloat16>(spec->weight_bf16),
-      as_ptr<const __nv_bfloat16>(spec->input_bf16), as_ptr<uint32_t>(spec->tokens_u32),
-      as_ptr<uint32_t>(spec->flags_u32), as_ptr<uint32_t>(spec->mirror_last_token_u32),
-      as_ptr<uint32_t>(spec->fallback_count_u32), spec->rows, spec->vocab, spec->cols, spec->eps, staged ? 1u : 0u);
-  return q36::launch_status();
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>(spec->rows) * (staged ? kCandidates : 1));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = staged ? stage_bytes : 0;
+  cfg.stream = q36::stream();
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = staged ? kCandidates : 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return q36::cuda_status(cudaLaunchKernelEx(
+      &cfg, top8_rescore_kernel, as_ptr<const WsEntry>(spec->workspace), as_ptr<const __nv_bfloat16>(spec->weight_bf16),
+      as_ptr<const __nv_bfloat16>(spec->input_bf16), as_ptr<uint32_t>(spec->tokens_u32), as_ptr<uint32_t>(spec->flags_u32),
+      as_ptr<uint32_t>(spec->mirror_last_token_u32), as_ptr<uint32_t>(spec->fallback_count_u32),
+      static_cast<size_t>(spec->rows), static_cast<size_t>(spec->vocab), static_cast<size_t>(spec->cols), spec->eps,
+      staged ? 1u : 0u));
 }
 
 extern "C" int qwen36_bf16_matvec_argmax_rows(const qwen36_bf16_matvec_argmax_rows_spec_t *spec) {
