@@ -488,6 +488,34 @@ def test_quantise_then_gemm_end_to_end(backend):
     assert rel_l2(synth.bf16_bits_to_f32(got), synth.bf16_bits_to_f32(want)) <= 1e-2
 
 
+@pytest.mark.parametrize("m,n", [(1280, 2048), (2560, 512), (1280, 8192)])
+def test_w4a4_gemm_stream_k_on_row_shards_of_down(backend, m, n):
+    """The down projection split by rows over two or four GPUs (K = 17408) at prefill token counts: the
+    library's own choice with a workspace (stream-K: few tiles, long K) against the whole-tile form,
+    which other tests pin to the oracle."""
+    k = 17408
+    gen = torch.Generator(device="cuda").manual_seed(m + n)
+    packed, sf_rm = synth.nvfp4_weight_device(gen, m, k, "cuda")
+    sfa = backend.nvfp4_retile_scales(sf_rm)
+    x = torch.randn((n, k), generator=gen, device="cuda").to(torch.bfloat16)
+    fp4, sfb, ts = backend.nvfp4_quantize_rows(x, 0.37)
+    alpha = float(np.float32(synth.WEIGHT_GLOBAL_SCALE) * np.float32(ts.item()))
+    try:
+        backend.lib.qwen36_nvfp4_gemm_stream_k(1)
+        whole = backend.nvfp4_gemm(packed, sfa, fp4, sfb, alpha, m, n, k).clone()
+        backend.lib.qwen36_nvfp4_gemm_stream_k(0)
+        chosen = [backend.nvfp4_gemm(packed, sfa, fp4, sfb, alpha, m, n, k).clone() for _ in range(2)]
+    finally:
+        backend.lib.qwen36_nvfp4_gemm_stream_k(0)
+    torch.cuda.synchronize()
+    assert backend.lib.qwen36_nvfp4_gemm_last_error() == 0
+    assert torch.equal(chosen[0], chosen[1])
+    diff = (chosen[0].float() - whole.float()).norm().item() / whole.float().norm().item()
+    same = (chosen[0].view(torch.int16) == whole.view(torch.int16)).float().mean().item()
+    assert diff <= 2e-4 and same >= 0.995, (diff, same)
+    assert same < 1.0              # the cut really happened: some float32 sums were regrouped
+
+
 def test_w4a4_gemm_stream_k_under_graph_replay(backend):
     """A captured stream-K launch replays with the same tag: the flags of one replay must not satisfy the
     next.  Three replays on fresh activations, each against the eager result for the same operands."""
