@@ -13,7 +13,11 @@
 // serial IEEE divisions per thread); here the vector is fetched once, by 1024 threads in one round
 // trip, into shared memory as float32, two lanes share a group in the norm kernel and sixteen lanes
 // share one in the SwiGLU kernel, 256 threads per CTA instead of 32.
+// Both launch with programmatic stream serialisation: the CTA takes its seat (and the norm kernel
+// fetches its norm weights, which are model state) while the kernel ahead drains, and lets the
+// kernel behind (a GEMV that streams its weights before it needs this output) take its seats at once.
 #include "common.cuh"
+#include "kv_split.cuh"
 #include "nvfp4_quant_group.cuh"
 
 namespace {
@@ -44,6 +48,8 @@ rmsnorm_nvfp4_quantize_kernel(const __nv_bfloat16 *__restrict__ input, const __n
 #pragma unroll
     for (int i = 0; i < 8; ++i) w_first[i] = start + i < hidden ? __bfloat162float(weight[start + i]) : 0.0f;
   }
+  asm volatile("griddepcontrol.wait;" ::: "memory");               // input and residual come from the kernel ahead
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   // ---- one round trip to L2: every thread fetches its elements at once -------------------------
   constexpr int kBatch = 8;                                  // 8192 elements per pass: loads issued before any use
   for (size_t base = 0; base < hidden; base += static_cast<size_t>(kBatch) * kNormThreads) {
@@ -144,6 +150,8 @@ __global__ void __launch_bounds__(kSwigluThreads)
 swiglu_nvfp4_quantize_kernel(const __nv_bfloat16 *__restrict__ gate, const __nv_bfloat16 *__restrict__ up,
                              uint8_t *__restrict__ output_fp4, uint8_t *__restrict__ output_scale,
                              float *__restrict__ tensor_scale, size_t values, float input_tensor_scale) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const float global_scale = input_tensor_scale > 0.0f ? input_tensor_scale : 1.0f;
   const size_t idx = static_cast<size_t>(blockIdx.x) * kSwigluThreads + threadIdx.x;
   const size_t group = idx >> 4;
@@ -280,13 +288,13 @@ extern "C" int qwen36_rmsnorm_nvfp4_quantize(const qwen36_rmsnorm_nvfp4_quantize
   if (smem > 200 * 1024) return QWEN36_STATUS_INVALID_ARGUMENT;
   if (q36::ensure_dynamic_smem(reinterpret_cast<const void *>(rmsnorm_nvfp4_quantize_kernel), 200 * 1024) != cudaSuccess)
     return QWEN36_STATUS_CUDA_ERROR;
-  rmsnorm_nvfp4_quantize_kernel<<<1, kNormThreads, smem, q36::stream()>>>(
+  return q36::cuda_status(q36::launch_after_previous(
+      rmsnorm_nvfp4_quantize_kernel, dim3(1), dim3(kNormThreads), smem, q36::stream(),
       as_ptr<const __nv_bfloat16>(spec->input_bf16), as_ptr<const __nv_bfloat16>(spec->weight_bf16),
       as_ptr<const __nv_bfloat16>(spec->residual_bf16), as_ptr<__nv_bfloat16>(spec->residual_out_bf16),
       as_ptr<__nv_bfloat16>(spec->output_bf16), as_ptr<uint8_t>(spec->output_fp4),
       as_ptr<uint8_t>(spec->output_scale_e4m3), as_ptr<float>(spec->output_tensor_scale_f32), spec->hidden, eps,
-      spec->input_tensor_scale_f32);
-  return q36::launch_status();
+      spec->input_tensor_scale_f32));
 }
 
 extern "C" int qwen36_swiglu_nvfp4_quantize(const qwen36_swiglu_nvfp4_quantize_spec_t *spec) {
@@ -296,9 +304,9 @@ extern "C" int qwen36_swiglu_nvfp4_quantize(const qwen36_swiglu_nvfp4_quantize_s
     return QWEN36_STATUS_INVALID_ARGUMENT;
   const size_t padded = q36::round_up(spec->intermediate, 16);
   const unsigned blocks = static_cast<unsigned>(q36::div_ceil(padded, kSwigluThreads));
-  swiglu_nvfp4_quantize_kernel<<<blocks, kSwigluThreads, 0, q36::stream()>>>(
+  return q36::cuda_status(q36::launch_after_previous(
+      swiglu_nvfp4_quantize_kernel, dim3(blocks), dim3(kSwigluThreads), size_t{0}, q36::stream(),
       as_ptr<const __nv_bfloat16>(spec->gate_bf16), as_ptr<const __nv_bfloat16>(spec->up_bf16),
       as_ptr<uint8_t>(spec->output_fp4), as_ptr<uint8_t>(spec->output_scale_e4m3),
-      as_ptr<float>(spec->output_tensor_scale_f32), spec->intermediate, spec->input_tensor_scale_f32);
-  return q36::launch_status();
+      as_ptr<float>(spec->output_tensor_scale_f32), spec->intermediate, spec->input_tensor_scale_f32));
 }
