@@ -68,6 +68,8 @@ __global__ void __launch_bounds__(kThreads)
 kv_encode_kernel(const __nv_bfloat16 *__restrict__ k, const __nv_bfloat16 *__restrict__ v,
                  int8_t *__restrict__ kq, int8_t *__restrict__ vq, float *__restrict__ meta, size_t position,
                  size_t tokens, size_t kv_heads, size_t head_dim) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");               // launched with programmatic stream serialisation
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const size_t vec = static_cast<size_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
   const unsigned lane = threadIdx.x & 31u;
   if (vec >= tokens * kv_heads * 2) return;
@@ -1177,12 +1179,12 @@ extern "C" int qwen36_turboquant_encode_kv_rows(const qwen36_turboquant_encode_r
         as_ptr<float>(spec->metadata_f32), spec->position, vecs, spec->shape.kv_heads);
     return q36::launch_status();
   }
-  kv_encode_kernel<<<static_cast<unsigned>(q36::div_ceil(vecs, kWarps)), kThreads, 0, q36::stream()>>>(
+  return q36::cuda_status(q36::launch_after_previous(
+      kv_encode_kernel, dim3(static_cast<unsigned>(q36::div_ceil(vecs, kWarps))), dim3(kThreads), size_t{0}, q36::stream(),
       as_ptr<const __nv_bfloat16>(spec->k_bf16), as_ptr<const __nv_bfloat16>(spec->v_bf16),
       as_ptr<int8_t>(spec->k_quantized_i8), as_ptr<int8_t>(spec->v_quantized_i8),
       as_ptr<float>(spec->metadata_f32), spec->position, spec->tokens, spec->shape.kv_heads,
-      spec->shape.head_dim);
-  return q36::launch_status();
+      spec->shape.head_dim));
 }
 
 extern "C" int qwen36_turboquant_encode_kv(const qwen36_turboquant_encode_spec_t *spec) {

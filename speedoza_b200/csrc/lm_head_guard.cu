@@ -12,6 +12,7 @@
 // ONE pass over the 2.5 GB weight for all rows that still need it (the reference re-reads the
 // weight once per row), with the activations staged as float32 in shared memory.
 #include "common.cuh"
+#include "kv_split.cuh"
 
 #include <math.h>
 
@@ -80,6 +81,8 @@ __device__ __forceinline__ Top2 block_merge(Top2 mine, Top2 *warp_smem) {
 // reads eight consecutive logits with one 16-byte load.
 __global__ void __launch_bounds__(kThreads)
 top2_scan_kernel(const __nv_bfloat16 *__restrict__ logits, WsEntry *__restrict__ ws, size_t vocab) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");               // launched with programmatic stream serialisation
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   __shared__ Top2 warp_smem[kThreads / 32];
   const size_t row = blockIdx.y;
   const __nv_bfloat16 *row_logits = logits + row * vocab;
@@ -109,6 +112,8 @@ top2_scan_kernel(const __nv_bfloat16 *__restrict__ logits, WsEntry *__restrict__
 __global__ void __launch_bounds__(kThreads)
 top2_verdict_kernel(const WsEntry *__restrict__ ws, uint32_t *__restrict__ tokens, uint32_t *__restrict__ flags,
                     uint32_t *__restrict__ mirror_last, uint32_t *__restrict__ fallback_count, size_t rows, float eps) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");               // launched with programmatic stream serialisation
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   __shared__ Top2 warp_smem[kThreads / 32];
   const size_t row = blockIdx.x;
   Top2 mine{-INFINITY, -INFINITY, kNoToken};
@@ -156,6 +161,8 @@ top8_rescore_kernel(const WsEntry *__restrict__ ws, const __nv_bfloat16 *__restr
   if (staged) asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
   const size_t row = staged ? blockIdx.x / kCandidates : blockIdx.x;
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+  asm volatile("griddepcontrol.wait;" ::: "memory");               // launched with programmatic stream serialisation
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   if (staged) {
     const __nv_bfloat16 *x_row = input + row * cols;
@@ -587,12 +594,14 @@ extern "C" int qwen36_lm_head_top2_margin(const qwen36_lm_head_top2_margin_spec_
   if (spec == nullptr || !guard_args_ok(spec->rows, spec->vocab, spec->logits_bf16.ptr, spec->tokens_u32.ptr,
                                         spec->flags_u32.ptr, spec->workspace.ptr, spec->workspace_bytes))
     return QWEN36_STATUS_INVALID_ARGUMENT;                  // also for a null spec, as the reference does
-  top2_scan_kernel<<<dim3(kBlocks, static_cast<unsigned>(spec->rows)), kThreads, 0, q36::stream()>>>(
-      as_ptr<const __nv_bfloat16>(spec->logits_bf16), as_ptr<WsEntry>(spec->workspace), spec->vocab);
-  top2_verdict_kernel<<<static_cast<unsigned>(spec->rows), kThreads, 0, q36::stream()>>>(
+  if (q36::launch_after_previous(top2_scan_kernel, dim3(kBlocks, static_cast<unsigned>(spec->rows)), dim3(kThreads), size_t{0},
+                                 q36::stream(), as_ptr<const __nv_bfloat16>(spec->logits_bf16),
+                                 as_ptr<WsEntry>(spec->workspace), spec->vocab) != cudaSuccess)
+    return QWEN36_STATUS_CUDA_ERROR;
+  return q36::cuda_status(q36::launch_after_previous(
+      top2_verdict_kernel, dim3(static_cast<unsigned>(spec->rows)), dim3(kThreads), size_t{0}, q36::stream(),
       as_ptr<const WsEntry>(spec->workspace), as_ptr<uint32_t>(spec->tokens_u32), as_ptr<uint32_t>(spec->flags_u32),
-      as_ptr<uint32_t>(spec->mirror_last_token_u32), as_ptr<uint32_t>(spec->fallback_count_u32), spec->rows, spec->eps);
-  return q36::launch_status();
+      as_ptr<uint32_t>(spec->mirror_last_token_u32), as_ptr<uint32_t>(spec->fallback_count_u32), spec->rows, spec->eps));
 }
 
 extern "C" int qwen36_lm_head_top8_rescore(const qwen36_lm_head_top8_rescore_spec_t *spec) {
@@ -600,8 +609,10 @@ extern "C" int qwen36_lm_head_top8_rescore(const qwen36_lm_head_top8_rescore_spe
       !guard_args_ok(spec->rows, spec->vocab, spec->logits_bf16.ptr, spec->tokens_u32.ptr, spec->flags_u32.ptr,
                      spec->workspace.ptr, spec->workspace_bytes))
     return QWEN36_STATUS_INVALID_ARGUMENT;
-  top2_scan_kernel<<<dim3(kBlocks, static_cast<unsigned>(spec->rows)), kThreads, 0, q36::stream()>>>(
-      as_ptr<const __nv_bfloat16>(spec->logits_bf16), as_ptr<WsEntry>(spec->workspace), spec->vocab);
+  if (q36::launch_after_previous(top2_scan_kernel, dim3(kBlocks, static_cast<unsigned>(spec->rows)), dim3(kThreads), size_t{0},
+                                 q36::stream(), as_ptr<const __nv_bfloat16>(spec->logits_bf16),
+                                 as_ptr<WsEntry>(spec->workspace), spec->vocab) != cudaSuccess)
+    return QWEN36_STATUS_CUDA_ERROR;
   // a cluster of eight CTAs per row, rows through shared memory, when they are made of whole 16-byte
   // pieces and two of them fit
   const size_t stage_bytes = 2 * spec->cols * sizeof(__nv_bfloat16);
@@ -613,13 +624,15 @@ extern "C" int qwen36_lm_head_top8_rescore(const qwen36_lm_head_top8_rescore_spe
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = staged ? stage_bytes : 0;
   cfg.stream = q36::stream();
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = staged ? kCandidates : 1;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = 2;
   return q36::cuda_status(cudaLaunchKernelEx(
       &cfg, top8_rescore_kernel, as_ptr<const WsEntry>(spec->workspace), as_ptr<const __nv_bfloat16>(spec->weight_bf16),
       as_ptr<const __nv_bfloat16>(spec->input_bf16), as_ptr<uint32_t>(spec->tokens_u32), as_ptr<uint32_t>(spec->flags_u32),

@@ -7,6 +7,7 @@
 // 704-761): IEEE float32 division by the decoded scale, E2M1 ties toward zero,
 // UE4M3 ties down.
 #include "common.cuh"
+#include "kv_split.cuh"
 #include "nvfp4_quant_group.cuh"
 
 #include <atomic>
@@ -27,6 +28,8 @@ __global__ void __launch_bounds__(kThreads)
 nvfp4_quantize_kernel(const __nv_bfloat16 *__restrict__ in, uint8_t *__restrict__ out_fp4,
                       uint8_t *__restrict__ out_sf, float *__restrict__ tensor_scale, Index rows,
                       Index values, float input_tensor_scale) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");               // launched with programmatic stream serialisation
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const float g = input_tensor_scale > 0.0f ? input_tensor_scale : 1.0f;
   const Index groups = (values + 15) / 16;
   const Index padded = (groups + 3) / 4 * 4;
@@ -279,16 +282,15 @@ int launch_quantize(qwen36_device_ptr_t in, qwen36_device_ptr_t fp4, qwen36_devi
   // 32-bit indices when the thread index space, the element offsets (rows * values) and the tiled
   // scale offsets all stay below 2^32
   const bool small = (rows + 128) * (values + 64) < (1ull << 32) && (blocks + 1) * kThreads < (1ull << 32);
-  if (small) {
-    nvfp4_quantize_kernel<uint32_t><<<static_cast<unsigned>(blocks), kThreads, 0, q36::stream()>>>(
-        as_ptr<const __nv_bfloat16>(in), as_ptr<uint8_t>(fp4), as_ptr<uint8_t>(sf), as_ptr<float>(ts),
-        static_cast<uint32_t>(rows), static_cast<uint32_t>(values), its);
-  } else {
-    nvfp4_quantize_kernel<size_t><<<static_cast<unsigned>(blocks), kThreads, 0, q36::stream()>>>(
-        as_ptr<const __nv_bfloat16>(in), as_ptr<uint8_t>(fp4), as_ptr<uint8_t>(sf), as_ptr<float>(ts), rows,
-        values, its);
-  }
-  return q36::launch_status();
+  const dim3 grid(static_cast<unsigned>(blocks)), block(kThreads);
+  if (small)
+    return q36::cuda_status(q36::launch_after_previous(
+        nvfp4_quantize_kernel<uint32_t>, grid, block, size_t{0}, q36::stream(), as_ptr<const __nv_bfloat16>(in),
+        as_ptr<uint8_t>(fp4), as_ptr<uint8_t>(sf), as_ptr<float>(ts), static_cast<uint32_t>(rows),
+        static_cast<uint32_t>(values), its));
+  return q36::cuda_status(q36::launch_after_previous(
+      nvfp4_quantize_kernel<size_t>, grid, block, size_t{0}, q36::stream(), as_ptr<const __nv_bfloat16>(in),
+      as_ptr<uint8_t>(fp4), as_ptr<uint8_t>(sf), as_ptr<float>(ts), rows, values, its));
 }
 
 }  // namespace
