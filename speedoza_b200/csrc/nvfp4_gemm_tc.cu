@@ -899,6 +899,78 @@ nvfp4_gemm_pair6_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
       const uint32_t row = (mb * 2u + rank) * kBM + quarter * 32u + lane;     // feature index
       const uint32_t taddr = tmem_base + col0 + ((quarter * 32u) << 16);
       const uint32_t tok0 = nb * P::kBN + col0;
+      if (SK && kb0 == 0u && kb1 != k_blocks) {
+        // Owner of a tile that other pairs finish (always the last piece of this pair's run, so the
+        // accumulator can stay in tensor memory meanwhile): 32 columns at a time, the partial sums of
+        // kFly contributors in flight together, added in K order.
+        constexpr uint32_t kFly = 3;
+        const uint32_t ew = warp - kWarpEpilogue;
+        const size_t mine = ((static_cast<size_t>(rank) * 8u + ew) * 32u) * 32u + lane;
+        uint32_t *flags = reinterpret_cast<uint32_t *>(ws + static_cast<size_t>(n_pairs) * P::kSlotFloats);
+        const uint64_t total = static_cast<uint64_t>(tiles) * k_blocks;
+        const uint64_t tile_end = static_cast<uint64_t>(tile + 1u) * k_blocks;
+        uint32_t q_end = pair_id + 1u;                          // contributors: pairs [pair_id + 1, q_end)
+        while (q_end < n_pairs && total * q_end / n_pairs < tile_end) ++q_end;
+        for (uint32_t q = pair_id + 1u; q < q_end; ++q) {
+          const volatile uint32_t *flag = flags + q * P::kFlagsPerPair + rank * 8u + ew;
+          bool there = false;
+          for (uint32_t spin = 0; spin < (1u << 22); ++spin) {        // x 64 ns: a quarter of a second
+            if (*flag == tag) { there = true; break; }
+            __nanosleep(64);
+          }
+          if (!there) atomicExch(&g_gemm_error, 1u);
+        }
+        __threadfence();
+        const bool odd = (lane & 1u) != 0u;
+        __nv_bfloat16 *crow = c + (row & ~1u);
+#pragma unroll 1
+        for (uint32_t chunk = 0; chunk < 4; ++chunk) {
+          uint32_t r[32];
+          tmem_ld32(taddr + chunk * 32u, r);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          for (uint32_t q0 = pair_id + 1u; q0 < q_end; q0 += kFly) {
+            float4 v[kFly][8];
+#pragma unroll
+            for (uint32_t f = 0; f < kFly; ++f) {
+              const uint32_t q = q0 + f < q_end ? q0 + f : q0;    // a repeat of the first one where the group is short (not added)
+              const float4 *slot = reinterpret_cast<const float4 *>(ws + static_cast<size_t>(q) * P::kSlotFloats) + mine;
+#pragma unroll
+              for (uint32_t g4 = 0; g4 < 8; ++g4) v[f][g4] = __ldcg(slot + (chunk * 8u + g4) * 32u);
+            }
+#pragma unroll
+            for (uint32_t f = 0; f < kFly; ++f) {
+              if (q0 + f < q_end) {
+#pragma unroll
+                for (uint32_t g4 = 0; g4 < 8; ++g4) {
+                  r[4 * g4] = __float_as_uint(__uint_as_float(r[4 * g4]) + v[f][g4].x);
+                  r[4 * g4 + 1] = __float_as_uint(__uint_as_float(r[4 * g4 + 1]) + v[f][g4].y);
+                  r[4 * g4 + 2] = __float_as_uint(__uint_as_float(r[4 * g4 + 2]) + v[f][g4].z);
+                  r[4 * g4 + 3] = __float_as_uint(__uint_as_float(r[4 * g4 + 3]) + v[f][g4].w);
+                }
+              }
+            }
+          }
+#pragma unroll
+          for (uint32_t j = 0; j < 32; j += 2) {
+            const __nv_bfloat162 pv = __floats2bfloat162_rn(__uint_as_float(r[j]) * alpha, __uint_as_float(r[j + 1]) * alpha);
+            const uint32_t mine_bits = *reinterpret_cast<const uint32_t *>(&pv);
+            const uint32_t got = __shfl_xor_sync(0xffffffffu, mine_bits, 1);
+            const uint32_t out = odd ? __byte_perm(got, mine_bits, 0x7632) : __byte_perm(mine_bits, got, 0x5410);
+            const uint32_t tok = tok0 + chunk * 32u + j + (odd ? 1u : 0u);
+            if (tok < n) *reinterpret_cast<uint32_t *>(crow + static_cast<size_t>(tok) * m) = out;
+          }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive_cluster(acc_empty_leader);
+          // This warp is the flags' only reader: clear them, so that a replay of a captured launch (same
+          // tag) does not find the flags of the replay before it.
+          for (uint32_t q = pair_id + 1u; q < q_end; ++q)
+            *reinterpret_cast<volatile uint32_t *>(flags + q * P::kFlagsPerPair + rank * 8u + ew) = 0u;
+        }
+        continue;
+      }
       // All four loads of the warp's 128 columns go out before the one wait, and the accumulator is
       // handed back before anything is converted: the time the MMA warp stands still per tile is the
       // commit, one TMEM read and this arrival, nothing else.
@@ -911,65 +983,29 @@ nvfp4_gemm_pair6_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
-      if (SK && (kb0 != 0u || kb1 != k_blocks)) {
-        // this thread's 128 sums of a partial tile, as 32 groups of four columns:
-        // [pair][CTA][epilogue warp][group][lane] float4, so that a warp moves 512 contiguous bytes per access
+      if (SK && kb0 != 0u) {
+        // A partial tile whose first K-blocks belong to another pair: this thread's 128 sums, as 32 groups
+        // of four columns, [pair][CTA][epilogue warp][group][lane] float4, so that a warp moves 512 contiguous
+        // bytes per access; the owner of the tile adds them and writes the output.
         const uint32_t ew = warp - kWarpEpilogue;
         const size_t mine = ((static_cast<size_t>(rank) * 8u + ew) * 32u) * 32u + lane;
         uint32_t *flags = reinterpret_cast<uint32_t *>(ws + static_cast<size_t>(n_pairs) * P::kSlotFloats);
-        if (kb0 != 0u) {
-          float4 *slot = reinterpret_cast<float4 *>(ws + static_cast<size_t>(pair_id) * P::kSlotFloats) + mine;
+        float4 *slot = reinterpret_cast<float4 *>(ws + static_cast<size_t>(pair_id) * P::kSlotFloats) + mine;
 #pragma unroll
-          for (uint32_t g4 = 0; g4 < 8; ++g4) {
-            slot[g4 * 32u] = make_float4(__uint_as_float(r0[4 * g4]), __uint_as_float(r0[4 * g4 + 1]),
-                                         __uint_as_float(r0[4 * g4 + 2]), __uint_as_float(r0[4 * g4 + 3]));
-            slot[(8u + g4) * 32u] = make_float4(__uint_as_float(r1[4 * g4]), __uint_as_float(r1[4 * g4 + 1]),
-                                                __uint_as_float(r1[4 * g4 + 2]), __uint_as_float(r1[4 * g4 + 3]));
-            slot[(16u + g4) * 32u] = make_float4(__uint_as_float(r2[4 * g4]), __uint_as_float(r2[4 * g4 + 1]),
-                                                 __uint_as_float(r2[4 * g4 + 2]), __uint_as_float(r2[4 * g4 + 3]));
-            slot[(24u + g4) * 32u] = make_float4(__uint_as_float(r3[4 * g4]), __uint_as_float(r3[4 * g4 + 1]),
-                                                 __uint_as_float(r3[4 * g4 + 2]), __uint_as_float(r3[4 * g4 + 3]));
-          }
-          __threadfence();
-          __syncwarp();
-          if (lane == 0) *reinterpret_cast<volatile uint32_t *>(flags + pair_id * P::kFlagsPerPair + rank * 8u + ew) = tag;
-          continue;                                           // the owner of the tile writes the output
+        for (uint32_t g4 = 0; g4 < 8; ++g4) {
+          slot[g4 * 32u] = make_float4(__uint_as_float(r0[4 * g4]), __uint_as_float(r0[4 * g4 + 1]),
+                                       __uint_as_float(r0[4 * g4 + 2]), __uint_as_float(r0[4 * g4 + 3]));
+          slot[(8u + g4) * 32u] = make_float4(__uint_as_float(r1[4 * g4]), __uint_as_float(r1[4 * g4 + 1]),
+                                              __uint_as_float(r1[4 * g4 + 2]), __uint_as_float(r1[4 * g4 + 3]));
+          slot[(16u + g4) * 32u] = make_float4(__uint_as_float(r2[4 * g4]), __uint_as_float(r2[4 * g4 + 1]),
+                                               __uint_as_float(r2[4 * g4 + 2]), __uint_as_float(r2[4 * g4 + 3]));
+          slot[(24u + g4) * 32u] = make_float4(__uint_as_float(r3[4 * g4]), __uint_as_float(r3[4 * g4 + 1]),
+                                               __uint_as_float(r3[4 * g4 + 2]), __uint_as_float(r3[4 * g4 + 3]));
         }
-        // owner: the pairs after this one whose runs begin inside the tile, in K order
-        const uint64_t total = static_cast<uint64_t>(tiles) * k_blocks;
-        const uint64_t tile_end = static_cast<uint64_t>(tile + 1u) * k_blocks;
-        for (uint32_t q = pair_id + 1u; q < n_pairs && total * q / n_pairs < tile_end; ++q) {
-          const volatile uint32_t *flag = flags + q * P::kFlagsPerPair + rank * 8u + ew;
-          bool there = false;
-          for (uint32_t spin = 0; spin < (1u << 22); ++spin) {        // x 64 ns: a quarter of a second
-            if (*flag == tag) { there = true; break; }
-            __nanosleep(64);
-          }
-          if (!there) atomicExch(&g_gemm_error, 1u);
-          __threadfence();
-          const float4 *slot = reinterpret_cast<const float4 *>(ws + static_cast<size_t>(q) * P::kSlotFloats) + mine;
-          // eight 16-byte loads in flight at a time: four round trips to L2 for the 128 values
-          auto add8 = [&](uint32_t (&r)[32], uint32_t first) {
-            float4 v[8];
-#pragma unroll
-            for (uint32_t g4 = 0; g4 < 8; ++g4) v[g4] = __ldcg(slot + (first + g4) * 32u);
-#pragma unroll
-            for (uint32_t g4 = 0; g4 < 8; ++g4) {
-              r[4 * g4] = __float_as_uint(__uint_as_float(r[4 * g4]) + v[g4].x);
-              r[4 * g4 + 1] = __float_as_uint(__uint_as_float(r[4 * g4 + 1]) + v[g4].y);
-              r[4 * g4 + 2] = __float_as_uint(__uint_as_float(r[4 * g4 + 2]) + v[g4].z);
-              r[4 * g4 + 3] = __float_as_uint(__uint_as_float(r[4 * g4 + 3]) + v[g4].w);
-            }
-          };
-          add8(r0, 0u);
-          add8(r1, 8u);
-          add8(r2, 16u);
-          add8(r3, 24u);
-          // This warp is the flag's only reader: clear it, so that a replay of a captured launch (same
-          // tag) does not find the flag of the replay before it.
-          __syncwarp();
-          if (lane == 0) *const_cast<volatile uint32_t *>(flag) = 0u;
-        }
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) *reinterpret_cast<volatile uint32_t *>(flags + pair_id * P::kFlagsPerPair + rank * 8u + ew) = tag;
+        continue;
       }
       uint32_t packed[P::kBN / 4];
 #pragma unroll
