@@ -447,6 +447,21 @@ def other_configs(backend, torch, synth, make_sampler=None):
                    "gemv_gbs": round(byts / us_gemv / 1e3, 1)})
     out["lm_head_fp8"] = lm
     del w, sc
+    # ---- the reference's NVFP4 lm_head: its W4A4 GEMM at m = vocabulary, n <= 16 (one token: decode GEMV) ----
+    packed_v, sf_rm_v = synth.nvfp4_weight_device(gen, rows, cols, "cuda")
+    sfa_v = backend.nvfp4_retile_scales(sf_rm_v)
+    del sf_rm_v
+    scan = []
+    for m_tok in (1, 4, 16):
+        xq = torch.randn((m_tok, cols), generator=gen, device="cuda").to(torch.bfloat16)
+        fp4_v, sfb_v, _ = backend.nvfp4_quantize_rows(xq, 0.37)
+        c_v = torch.empty((m_tok, rows), dtype=torch.bfloat16, device="cuda")
+        us = _time_cuda(torch, lambda i: backend.nvfp4_gemm(packed_v, sfa_v, fp4_v, sfb_v, 0.37 / 2688.0, rows, m_tok,
+                                                            cols, c_v), 100, warm=10, backend=backend)
+        byts = rows * cols / 2 + rows * cols / 16 + m_tok * (cols / 2 + cols / 16) + 2 * m_tok * rows
+        scan.append({"M": m_tok, "us": round(us, 1), "gbs": round(byts / us / 1e3, 1)})
+    out["nvfp4_lm_head_scan"] = scan
+    del packed_v, sfa_v
     # ---- exact-argmax guards: margin verdict over the logits, predicated bf16 lm_head ---------
     guard = {}
     logits4 = (torch.randn((4, rows), generator=gen, device="cuda") * 3).to(torch.bfloat16)

@@ -101,6 +101,45 @@ def test_prefill_chain_at_config_sizes(backend, prefill_weights, shape, tokens):
             assert diff <= 1e-3 and same >= 0.99, (diff, same)
 
 
+# ------------------------------------------------------------------ NVFP4 lm_head scan
+
+@pytest.fixture(scope="module")
+def nvfp4_lm_head_weight(backend):
+    gen = torch.Generator(device="cuda").manual_seed(777)
+    packed, sf_rm = synth.nvfp4_weight_device(gen, synth.VOCAB, synth.HIDDEN, "cuda")
+    sfa = backend.nvfp4_retile_scales(sf_rm)
+    return packed, sfa, packed.cpu().numpy(), sfa.cpu().numpy()
+
+
+@pytest.mark.parametrize("tokens", [1, 4, 16])
+def test_nvfp4_lm_head_scan_shape_vs_oracle(backend, nvfp4_lm_head_weight, tokens):
+    """The reference's NVFP4 lm_head is its W4A4 GEMM at m = vocabulary, n <= 16 tokens, k = hidden
+    (crates/runtime/src/engine.rs:11609-11663; one token goes to the decode GEMV first, as
+    crates/kernels/src/backend.rs:213-233 routes it).  4096 sampled logits, corners and tile borders
+    included, against the float64 dequantise-and-dot of the oracle."""
+    n_out, k = synth.VOCAB, synth.HIDDEN
+    packed, sfa, packed_h, sfa_h = nvfp4_lm_head_weight
+    gen = torch.Generator(device="cuda").manual_seed(tokens + 99)
+    x = torch.randn((tokens, k), generator=gen, device="cuda").to(torch.bfloat16)
+    its = 0.37
+    fp4, sfb, ts = backend.nvfp4_quantize_rows(x, its)
+    w_fp4, w_sf, w_ts = orc.nvfp4_quantize_rows(bf16_host(x), its)
+    assert np.array_equal(fp4.cpu().numpy(), w_fp4) and np.array_equal(sfb.cpu().numpy(), w_sf)
+    alpha = float(np.float32(synth.WEIGHT_GLOBAL_SCALE) * np.float32(w_ts))
+    c = backend.nvfp4_gemm(packed, sfa, fp4, sfb, alpha, n_out, tokens, k)
+    torch.cuda.synchronize()
+    assert backend.lib.qwen36_nvfp4_gemm_last_error() == 0
+    rng = np.random.default_rng(tokens + n_out)
+    tok = rng.integers(0, tokens, 4096).astype(np.uint32)
+    feat = rng.integers(0, n_out, 4096).astype(np.uint32)
+    tok[:4] = [0, 0, tokens - 1, tokens - 1]
+    feat[:8] = [0, n_out - 1, 0, n_out - 1, 127, 128, n_out - 129, n_out - 128]
+    want = orc.nvfp4_gemm_sampled(packed_h, sfa_h, w_fp4, w_sf, alpha, n_out, tokens, k, tok, feat)
+    got = c[torch.from_numpy(tok.astype(np.int64)).cuda(), torch.from_numpy(feat.astype(np.int64)).cuda()].float().cpu().numpy()
+    assert rel_l2(got, want) <= 1e-2
+    assert np.all(np.abs(got - want) <= np.abs(want) * 2.0 ** -7 + 1e-6)
+
+
 # ------------------------------------------------------------------ config 4: long contexts
 
 @pytest.fixture(scope="module")
