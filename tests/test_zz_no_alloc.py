@@ -8,8 +8,9 @@ import numpy as np
 import pytest
 import torch
 
+from oracle import oracle as orc
 from speedoza_b200 import abi, synth
-from conftest import to_dev
+from conftest import bf16_host, to_dev
 
 pytestmark = pytest.mark.gpu
 
@@ -24,7 +25,7 @@ def make_cache(backend, rng, tokens):
     kq = torch.zeros((tokens, 4, 256), dtype=torch.int8, device="cuda"); vq = torch.zeros_like(kq)
     meta = torch.zeros((tokens, 4, 2), dtype=torch.float32, device="cuda")
     backend.turboquant_encode_kv_rows(to_dev(k), to_dev(v), kq, vq, meta, 0)
-    return to_dev(q), kq, vq, meta
+    return to_dev(q), kq, vq, meta, q
 
 
 def test_static_scratch_attention_matches_workspace_entry(backend):
@@ -34,7 +35,7 @@ def test_static_scratch_attention_matches_workspace_entry(backend):
     shape = abi.AttentionShape(24, 4, 256, 0)
     # long context first, short second: the second call must not see the first call's partials
     for tokens in (5000, 130):
-        q, kq, vq, meta = make_cache(backend, rng, tokens)
+        q, kq, vq, meta, q_host = make_cache(backend, rng, tokens)
         want = torch.empty((24, 256), dtype=torch.bfloat16, device="cuda")
         got = torch.full((24, 256), float("nan"), dtype=torch.bfloat16, device="cuda")
         dp = lambda t: abi.DevicePtr(t.data_ptr())
@@ -56,6 +57,11 @@ def test_static_scratch_attention_matches_workspace_entry(backend):
         assert torch.cuda.mem_get_info()[0] == free_before
         assert rel_l2(got, want) <= 1e-2          # the tolerance of the attention parity tests
         assert torch.equal(got, want)              # same kernels, same order: in fact identical
+        # and against the CPU restatement of the reference's attention over the same cache bytes
+        oracle_out = orc.kv_attention(q_host, kq.cpu().numpy(), vq.cpu().numpy(), meta.cpu().numpy(), tokens - 1)
+        a = synth.bf16_bits_to_f32(bf16_host(got)).astype(np.float64)
+        b = synth.bf16_bits_to_f32(oracle_out).astype(np.float64)
+        assert np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30) <= 1e-2
 
 
 def test_static_scratch_rejects_shapes_beyond_its_size(backend):
