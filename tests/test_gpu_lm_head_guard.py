@@ -80,6 +80,27 @@ def test_top8_rescore_vs_oracle(backend, rows, vocab, cols):
         assert np.array_equal(u32(tokens), want_t) and np.array_equal(u32(flags), want_f) and fb.item() == want_fb
 
 
+def test_top8_rescore_special_logits_vs_oracle(backend):
+    """Block winners that are NaN, infinite or tied: NaN and -inf are never candidates, +inf is, equal
+    values go to the smaller token; rows with fewer than eight (or no) candidates."""
+    rows, vocab, cols = 5, 70000, 512
+    rng = np.random.default_rng(99)
+    w, x, logits = make_head(rng, vocab, cols, rows, 0.3)
+    bits = lambda v: synth.f32_to_bf16_bits(np.array([v], np.float32))[0]
+    logits[0, rng.integers(0, vocab, 4000)] = bits(np.nan)
+    logits[0, rng.integers(0, vocab, 4000)] = bits(-np.inf)
+    logits[1, [7, 40000, 69999]] = bits(np.inf)                       # three ties at the top
+    logits[2, :] = bits(-np.inf)                                      # no candidate at all
+    logits[2, [123, 50000]] = bits(3.0)                               # ... but two
+    logits[3, :] = bits(1.5)                                          # every block winner tied
+    logits[4, :] = bits(np.nan)                                       # nothing comparable
+    for eps in (0.0, 0.5):
+        want_t, want_f, want_fb = orc.lm_head_top8_rescore(logits, w, x, eps)
+        fb = torch.zeros(1, dtype=torch.int32, device="cuda")
+        tokens, flags = backend.lm_head_top8_rescore(to_dev(logits), to_dev(w), to_dev(x), eps, fb)
+        assert np.array_equal(u32(tokens), want_t) and np.array_equal(u32(flags), want_f) and fb.item() == want_fb
+
+
 @pytest.mark.parametrize("rows,vocab,cols", [(1, 5000, 5120), (4, 3000, 512), (11, 1000, 96), (3, 257, 33)])
 def test_bf16_matvec_argmax_rows_vs_oracle(backend, rows, vocab, cols):
     rng = np.random.default_rng(rows + vocab + cols)
